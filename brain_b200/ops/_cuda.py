@@ -1,0 +1,94 @@
+"""ctypes binding to the in-tree sm_100a kernel library (``brain_b200/_lib/libbrain_b200.so``).
+
+Every exported launcher takes raw device pointers plus a CUDA stream handle and returns an int
+(0 = ok, >0 = cudaError_t, <0 = argument/setup error).  ``call`` raises on non-zero so a missing
+or failing native path is loud: there is no silent PyTorch fallback on a GPU box.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+_LIB: ctypes.CDLL | None = None
+_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "libbrain_b200.so"
+
+#: number of native kernel launches issued through :func:`call` (bench.py reports it)
+launch_count = 0
+
+_ERR_NAMES = {
+    1: "TMA producer timed out waiting for a free shared-memory slot",
+    2: "MMA issuer timed out waiting for TMA data",
+    3: "MMA issuer timed out waiting for a free TMEM accumulator",
+    4: "epilogue timed out waiting for the accumulator",
+    5: "softmax warps timed out",
+    6: "peer flag never arrived",
+    7: "bad argument seen on device",
+}
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        if not _LIB_PATH.exists():
+            if os.environ.get("BRAIN_B200_NO_AUTOBUILD") == "1":
+                raise NativeError(f"native library missing: {_LIB_PATH} (run __graft_entry__.build())")
+            from .. import _build
+            _build.build_cuda()
+        _LIB = ctypes.CDLL(str(_LIB_PATH))
+    return _LIB
+
+
+def available() -> bool:
+    """True when the kernels can run: library present (or buildable) and a CUDA device visible."""
+    return torch.cuda.is_available()
+
+
+def _conv(a):
+    if isinstance(a, torch.Tensor):
+        return ctypes.c_void_p(a.data_ptr())
+    if a is None:
+        return ctypes.c_void_p(0)
+    if isinstance(a, bool):
+        return ctypes.c_int(int(a))
+    if isinstance(a, int):
+        return ctypes.c_int(a)
+    if isinstance(a, float):
+        return ctypes.c_float(a)
+    return a
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def call(name: str, *args) -> None:
+    """Launch ``bb_<name>``; tensors become device pointers, ints c_int, floats c_float.
+    Pass ``ctypes.c_long(x)`` explicitly for 64-bit parameters."""
+    global launch_count
+    fn = getattr(lib(), "bb_" + name)
+    rc = fn(*[_conv(a) for a in args])
+    launch_count += 1
+    if rc != 0:
+        raise NativeError(f"bb_{name} failed with code {rc}")
+
+
+def read_error(clear: bool = True) -> int:
+    """Synchronise and return the device error word (0 = no kernel reported a bounded-wait timeout)."""
+    return int(lib().bb_read_error(ctypes.c_int(1 if clear else 0)))
+
+
+def check_error() -> None:
+    code = read_error(True)
+    if code != 0:
+        raise NativeError(f"device error {code}: {_ERR_NAMES.get(code, 'unknown')}")
+
+
+def L(x: int) -> ctypes.c_long:
+    return ctypes.c_long(int(x))

@@ -1,0 +1,417 @@
+// Persistent warp-specialised GEMM on the 5th-gen tensor cores (tcgen05.mma, accumulators in TMEM,
+// operands staged by TMA into a 128-byte-swizzled shared-memory ring).
+//
+//   C[M,N] (op)= alpha * A[M,K] * B[N,K]^T (+ bias[N])
+//
+// A and B can each be K-major ([rows][K], K contiguous — the nn.Linear layout) or MN-major
+// ([K][rows], rows contiguous), so forward (x·Wᵀ), dX (dy·W) and dW (dyᵀ·x) all run on the same
+// kernel without a transpose pass.  The int8 variant (kind::i8, s32 accumulate) applies per-row
+// and per-column scales in the epilogue (W8A8).
+//
+// Replaces the reference's register-tiled fp32 GEMM family (crates/kernels/wgsl/matmul_reg3.wgsl,
+// matmul_dx_reg.wgsl, matmul_dw_reg.wgsl, matmul_i8_dyn.wgsl).
+//
+// Roles (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane),
+// warp 2 = TMEM allocator, warps 4..7 = epilogue (TMEM -> registers -> global).
+// Two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+#include "../common/host.hpp"
+#include "../common/ptx.cuh"
+
+namespace bb {
+
+struct GemmArgs {
+  void* C;
+  const float* bias;     // [N] or null
+  const float* scale_m;  // int8: per-row (token) scale, else null
+  const float* scale_n;  // int8: per-column (channel) scale, else null
+  float alpha;
+  int M, N, K;
+  int ldc;
+  int a_mn, b_mn;
+  int out_mode;  // 0 bf16 store, 1 fp32 store, 2 fp32 accumulate, 3 bf16 store of gelu(x) (tanh)
+  int* err;
+};
+
+static constexpr int BM = 128;
+static constexpr int TILE_K_BYTES = 128;  // one swizzle row
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = BM * TILE_K_BYTES;  // 16 KB
+  static constexpr int B_BYTES = BN * TILE_K_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * x * (1.f + tanhf(k0 * (x + k1 * x * x * x)));
+}
+
+template <int BN, bool I8>
+__global__ void __launch_bounds__(256, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const GemmArgs args) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int S = Cfg::STAGES;
+  constexpr int BK = I8 ? 128 : 64;      // elements per k-block (128 bytes)
+  constexpr int UK = I8 ? 32 : 16;       // elements per tcgen05.mma
+  constexpr int NK = BK / UK;            // 4 MMAs per k-block
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + S;
+  uint64_t* tmem_full = bars + 2 * S;
+  uint64_t* tmem_empty = bars + 2 * S + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int M = args.M, N = args.N, K = args.K;
+  const int tiles_m = (M + BM - 1) / BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int ntiles = tiles_m * tiles_n;
+  const int nkb = (K + BK - 1) / BK;
+  constexpr int GROUP_M = 16;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 128);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coords = [&](int t, int& tm, int& tn) {
+    const int per_group = GROUP_M * tiles_n;
+    const int g = t / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsz = min(tiles_m - first_m, GROUP_M);
+    tm = first_m + (t % per_group) % gsz;
+    tn = (t % per_group) / gsz;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int armed_stage = -1;
+      uint32_t armed_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) {
+            set_error(args.err, ERR_WAIT_PRODUCER);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!args.a_mn) {
+            tma_load_2d(sa, &tmA, &full[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(sa + c * (BK * 128), &tmA, &full[stage], m0 + c * 64, k0);
+          }
+          if (!args.b_mn) {
+            tma_load_2d(sb, &tmB, &full[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (BK * 128), &tmB, &full[stage], n0 + c * 64, k0);
+          }
+          armed_stage = stage;
+          armed_phase = phase;
+          if (++stage == S) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      // On the error path give copies still in flight a bounded chance to land before exit.
+      if (!ok && armed_stage >= 0) (void)mbar_wait(&full[armed_stage], armed_phase);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_base = I8 ? umma_idesc(2, 1, 1, 0, 0, BM, BN)
+                                         : umma_idesc(1, 1, 1, 0, 0, BM, BN);
+      const uint32_t idesc =
+          idesc_base | (uint32_t)(args.a_mn & 1) << 15 | (uint32_t)(args.b_mn & 1) << 16;
+      // K-major: advance 32 B per MMA inside the swizzle row; MN-major: UK k-rows of 128 B.
+      const uint32_t a_adv = args.a_mn ? UK * 128 : 32;
+      const uint32_t b_adv = args.b_mn ? UK * 128 : 32;
+      const uint32_t a_lbo = args.a_mn ? BK * 128 : 16;
+      const uint32_t b_lbo = args.b_mn ? BK * 128 : 16;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
+          set_error(args.err, ERR_WAIT_MMA_TMEM);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&full[stage], phase)) {
+            set_error(args.err, ERR_WAIT_MMA_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < NK; ++k) {
+            const uint64_t da = umma_smem_desc(sa + k * a_adv, a_lbo, 1024);
+            const uint64_t db = umma_smem_desc(sb + k * b_adv, b_lbo, 1024);
+            if (I8)
+              umma_i8_ss(d_tmem, da, db, idesc, (kb | k) != 0);
+            else
+              umma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty[stage]);  // frees the smem slot once these MMAs have read it
+          if (++stage == S) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue
+    const int ew = warp & 3;  // TMEM lane quarter this warp may touch
+    int it = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      bool ok = mbar_wait(&tmem_full[acc], acc_phase);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) set_error(args.err, ERR_WAIT_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      int tm, tn;
+      tile_coords(t, tm, tn);
+      const int row = tm * BM + ew * 32 + lane;
+      const int n0 = tn * BN;
+      const bool row_ok = row < M;
+      const float sm = (I8 && row_ok && args.scale_m) ? args.scale_m[row] : 1.f;
+      const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld32(t_row + c * 32, r);
+        tmem_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float x = I8 ? (float)(int)r[j] : __uint_as_float(r[j]);
+          x *= args.alpha;
+          if (I8) {
+            x *= sm;
+            if (args.scale_n) x *= (col0 + j < N) ? args.scale_n[col0 + j] : 0.f;
+          }
+          if (args.bias && col0 + j < N) x += args.bias[col0 + j];
+          v[j] = x;
+        }
+        const bool full_chunk = (col0 + 32 <= N);
+        if (args.out_mode == 0 || args.out_mode == 3) {
+          if (args.out_mode == 3) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+          }
+          __nv_bfloat16* crow =
+              reinterpret_cast<__nv_bfloat16*>(args.C) + (size_t)row * args.ldc + col0;
+          if (full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+            uint4* dst = reinterpret_cast<uint4*>(crow);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              dst[q] = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < N; ++j) crow[j] = __float2bfloat16(v[j]);
+          }
+        } else {
+          float* crow = reinterpret_cast<float*>(args.C) + (size_t)row * args.ldc + col0;
+          const bool accum = args.out_mode == 2;
+          if (full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+            float4* dst = reinterpret_cast<float4*>(crow);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+              if (accum) {
+                const float4 old = dst[q];
+                o.x += old.x;
+                o.y += old.y;
+                o.z += old.z;
+                o.w += old.w;
+              }
+              dst[q] = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < N; ++j) crow[j] = accum ? crow[j] + v[j] : v[j];
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+template <int BN, bool I8>
+static int launch_gemm(const void* A, const void* B, const GemmArgs& args, int lda, int ldb,
+                       cudaStream_t stream, int max_ctas) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int ES = I8 ? 1 : 2;
+  constexpr int BK = I8 ? 128 : 64;
+  const CUtensorMapDataType dt = I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!args.a_mn)
+    rc = make_tmap_2d(&tmA, dt, ES, A, args.K, args.M, (uint64_t)lda * ES, BK, BM);
+  else
+    rc = make_tmap_2d(&tmA, dt, ES, A, args.M, args.K, (uint64_t)lda * ES, 64, BK);
+  if (rc) return rc;
+  if (!args.b_mn)
+    rc = make_tmap_2d(&tmB, dt, ES, B, args.K, args.N, (uint64_t)ldb * ES, BK, BN);
+  else
+    rc = make_tmap_2d(&tmB, dt, ES, B, args.N, args.K, (uint64_t)ldb * ES, 64, BK);
+  if (rc) return rc;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, I8>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int tiles = ((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN);
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  gemm_kernel<BN, I8><<<grid, 256, Cfg::SMEM, stream>>>(tmA, tmB, args);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace bb
+
+// C ABI ------------------------------------------------------------------------------------------
+// bf16 GEMM.  a_mn/b_mn: 0 = operand stored [rows][K] (K contiguous), 1 = stored [K][rows].
+// lda/ldb/ldc in elements.  out_mode: 0 bf16, 1 fp32, 2 fp32 accumulate, 3 bf16 gelu.
+// bn: tile width (256/128/64/32) or 0 = choose.  max_ctas: 0 = all SMs (leave SMs to a
+// concurrent communication kernel by passing fewer).
+BB_API int bb_gemm_bf16(const void* A, const void* B, void* C, const float* bias, int M, int N,
+                        int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_mode,
+                        float alpha, int bn, int max_ctas, void* stream) {
+  using namespace bb;
+  if (M <= 0 || N <= 0 || K <= 0) return BB_EARG;
+  GemmArgs a{};
+  a.C = C;
+  a.bias = bias;
+  a.alpha = alpha;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.ldc = ldc;
+  a.a_mn = a_mn;
+  a.b_mn = b_mn;
+  a.out_mode = out_mode;
+  a.err = device_error_word();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn == 0) {
+    const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
+    const long tiles128 = (long)((M + 127) / 128) * ((N + 127) / 128);
+    const int sms = sm_count();
+    bn = (tiles256 >= sms) ? 256 : (tiles128 >= sms / 2 ? 128 : 64);
+    if (N <= 64) bn = 64;
+  }
+  switch (bn) {
+    case 256: return launch_gemm<256, false>(A, B, a, lda, ldb, s, max_ctas);
+    case 128: return launch_gemm<128, false>(A, B, a, lda, ldb, s, max_ctas);
+    case 64: return launch_gemm<64, false>(A, B, a, lda, ldb, s, max_ctas);
+    default: return BB_EARG;
+  }
+}
+
+// W8A8: C[M,N] bf16 = (A_i8[M,K] · B_i8[N,K]^T) * scale_m[M] * scale_n[N]; both operands K-major.
+BB_API int bb_gemm_i8(const void* A, const void* B, void* C, const float* scale_m,
+                      const float* scale_n, int M, int N, int K, int lda, int ldb, int ldc, int bn,
+                      int max_ctas, void* stream) {
+  using namespace bb;
+  if (M <= 0 || N <= 0 || K <= 0) return BB_EARG;
+  GemmArgs a{};
+  a.C = C;
+  a.scale_m = scale_m;
+  a.scale_n = scale_n;
+  a.alpha = 1.f;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.ldc = ldc;
+  a.out_mode = 0;
+  a.err = device_error_word();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn == 0) {
+    const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
+    const long tiles128 = (long)((M + 127) / 128) * ((N + 127) / 128);
+    const int sms = sm_count();
+    bn = (tiles256 >= sms) ? 256 : (tiles128 >= sms / 2 ? 128 : 64);
+  }
+  switch (bn) {
+    case 256: return launch_gemm<256, true>(A, B, a, lda, ldb, s, max_ctas);
+    case 128: return launch_gemm<128, true>(A, B, a, lda, ldb, s, max_ctas);
+    case 64: return launch_gemm<64, true>(A, B, a, lda, ldb, s, max_ctas);
+    default: return BB_EARG;
+  }
+}

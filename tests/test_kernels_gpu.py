@@ -1,0 +1,297 @@
+"""sm_100a kernels vs the plain PyTorch fp32 reference of the same op (small + odd shapes)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from brain_b200.ops import _cuda, functional as F, reference as ref  # noqa: E402
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _check_device_error():
+    yield
+    _cuda.check_error()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 1024), (300, 200, 136), (4096, 1024, 1024),
+                                   (1024, 3072, 1024), (64, 64, 64), (129, 1000, 72)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_bf16(M, N, K, a_mn, b_mn):
+    torch.manual_seed(M + N + K)
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operand needs a 16-byte row pitch")
+    a = torch.randn(M, K, device=dev()).bfloat16()
+    b = torch.randn(N, K, device=dev()).bfloat16()
+    want = a.float() @ b.float().t()
+    aa = a.t().contiguous() if a_mn else a
+    bb = b.t().contiguous() if b_mn else b
+    got = F.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn)
+    assert rel_err(got, want) < 1e-2
+    got32 = F.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    assert rel_err(got32, want) < 2e-3
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_gemm_tile_widths_and_accumulate(bn):
+    torch.manual_seed(0)
+    M, N, K = 640, 768, 512
+    a = torch.randn(M, K, device=dev()).bfloat16()
+    b = torch.randn(N, K, device=dev()).bfloat16()
+    base = torch.randn(M, N, device=dev())
+    out = base.clone()
+    F.gemm(a, b, out=out, accumulate=True, bn=bn)
+    want = base + a.float() @ b.float().t()
+    assert rel_err(out, want) < 2e-3
+    bias = torch.randn(N, device=dev())
+    got = F.gemm(a, b, bias=bias, alpha=0.5, bn=bn)
+    assert rel_err(got, 0.5 * (a.float() @ b.float().t()) + bias) < 1e-2
+
+
+def test_gemm_strided_views_and_canaries():
+    torch.manual_seed(1)
+    M, N, K = 200, 328, 256
+    big = torch.randn(M, K + 64, device=dev()).bfloat16()
+    a = big[:, 32:32 + K]
+    w = torch.randn(N, K, device=dev()).bfloat16()
+    pad = torch.full((M + 2, N + 16), 7.0, device=dev(), dtype=torch.bfloat16)
+    out = pad[1:M + 1, 8:8 + N]
+    F.gemm(a, w, out=out)
+    assert rel_err(out, a.float() @ w.float().t()) < 1e-2
+    assert (pad[0] == 7).all() and (pad[-1] == 7).all()
+    assert (pad[:, :8] == 7).all() and (pad[:, 8 + N:] == 7).all()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 1024), (70, 200, 384), (512, 1536, 4096)])
+def test_gemm_i8(M, N, K):
+    torch.manual_seed(2)
+    x = torch.randn(M, K, device=dev())
+    w = torch.randn(N, K, device=dev()) * 0.05
+    xq, sx = ref.quant_rows(x)
+    wq, sw = ref.quant_rows(w)
+    want = (xq.float() @ wq.float().t()) * sx[:, None] * sw[None, :]
+    got = F.gemm_i8(xq, wq, sx, sw)
+    assert rel_err(got, want) < 1e-2
+    assert rel_err(got, x @ w.t()) < 5e-2
+
+
+def test_linear_autograd_matches_reference():
+    torch.manual_seed(3)
+    x = torch.randn(4, 96, 256, device=dev()).bfloat16().requires_grad_()
+    w = torch.randn(384, 256, device=dev()).bfloat16().requires_grad_()
+    b = torch.randn(384, device=dev()).bfloat16().requires_grad_()
+    y = F.linear(x, w, b)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = ref.linear(xr, wr, br)
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < 1e-2
+    assert rel_err(x.grad, xr.grad) < 1e-2
+    assert rel_err(w.grad, wr.grad) < 1e-2
+    assert rel_err(b.grad, br.grad) < 1e-2
+
+
+def test_linear_main_grad_accumulates():
+    torch.manual_seed(4)
+    x = torch.randn(512, 128, device=dev()).bfloat16().requires_grad_()
+    w = torch.randn(256, 128, device=dev()).bfloat16().requires_grad_()
+    w.main_grad = torch.ones(256, 128, device=dev())
+    dy = torch.randn(512, 256, device=dev()).bfloat16()
+    F.linear(x, w).backward(dy)
+    assert w.grad is None
+    assert rel_err(w.main_grad, 1 + dy.float().t() @ x.detach().float()) < 2e-3
+
+
+@pytest.mark.parametrize("rows,d", [(37, 1024), (1000, 64), (5, 5120), (4096, 768)])
+def test_rmsnorm(rows, d):
+    torch.manual_seed(5)
+    x = torch.randn(rows, d, device=dev()).bfloat16().requires_grad_()
+    r = torch.randn(rows, d, device=dev()).bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(d, device=dev())).bfloat16().requires_grad_()
+    y, h = F.rmsnorm(x, w, 1e-6, residual=r)
+    dy, dh = torch.randn_like(y), torch.randn_like(h)
+    (y * dy).sum().backward(retain_graph=True)
+    (h * dh).sum().backward()
+    xr, rr, wr = (t.detach().float().requires_grad_() for t in (x, r, w))
+    hr = (xr + rr)
+    yr = ref.rmsnorm(hr, wr, 1e-6)
+    ((yr * dy.float()).sum() + (hr * dh.float()).sum()).backward()
+    assert rel_err(y, yr) < 1e-2 and rel_err(h, hr) < 1e-2
+    assert rel_err(x.grad, xr.grad) < 2e-2
+    assert rel_err(r.grad, rr.grad) < 2e-2
+    assert rel_err(w.grad, wr.grad) < 2e-2
+    y2 = F.rmsnorm(x.detach(), w.detach(), 1e-6)
+    assert rel_err(y2, ref.rmsnorm(x.detach().float(), w.detach().float())) < 1e-2
+
+
+@pytest.mark.parametrize("rows,d", [(33, 768), (512, 64)])
+def test_layernorm(rows, d):
+    torch.manual_seed(6)
+    x = torch.randn(rows, d, device=dev()).bfloat16().requires_grad_()
+    g = (1 + 0.1 * torch.randn(d, device=dev())).bfloat16().requires_grad_()
+    b = (0.1 * torch.randn(d, device=dev())).bfloat16().requires_grad_()
+    y = F.layernorm(x, g, b)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, gr, br = (t.detach().float().requires_grad_() for t in (x, g, b))
+    yr = ref.layernorm(xr, gr, br)
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < 1e-2
+    assert rel_err(x.grad, xr.grad) < 2e-2
+    assert rel_err(g.grad, gr.grad) < 2e-2
+    assert rel_err(b.grad, br.grad) < 2e-2
+
+
+@pytest.mark.parametrize("hd,hq,hk,extra", [(128, 4, 2, 256), (64, 6, 2, 128), (128, 2, 2, 0)])
+@pytest.mark.parametrize("norm", [True, False])
+def test_qknorm_rope(hd, hq, hk, extra, norm):
+    torch.manual_seed(7)
+    n = 77
+    width = (hq + hk) * hd + extra
+    qkv = torch.randn(n, width, device=dev()).bfloat16().requires_grad_()
+    wq = (1 + 0.1 * torch.randn(hd, device=dev())).bfloat16().requires_grad_() if norm else None
+    wk = (1 + 0.1 * torch.randn(hd, device=dev())).bfloat16().requires_grad_() if norm else None
+    cos, sin = ref.rope_tables(128, hd, 1e6, device=dev())
+    pos = torch.randint(0, 128, (n,), device=dev(), dtype=torch.int32)
+    out = F.qknorm_rope(qkv, wq, wk, cos, sin, pos, hq, hk, hd)
+    do = torch.randn_like(out)
+    out.backward(do)
+    qr = qkv.detach().float().requires_grad_()
+    wqr = wq.detach().float().requires_grad_() if norm else None
+    wkr = wk.detach().float().requires_grad_() if norm else None
+    outr = ref.qknorm_rope(qr[:, :(hq + hk) * hd], wqr, wkr, cos, sin, pos.long(), hq, hk, hd)
+    outr.backward(do.float())
+    assert rel_err(out, outr) < 1e-2
+    assert rel_err(qkv.grad, qr.grad) < 2e-2
+    if norm:
+        assert rel_err(wq.grad, wqr.grad) < 2e-2
+        assert rel_err(wk.grad, wkr.grad) < 2e-2
+
+
+def test_swiglu_gelu_embedding():
+    torch.manual_seed(8)
+    gu = torch.randn(130, 2 * 96, device=dev()).bfloat16().requires_grad_()
+    h = F.swiglu(gu)
+    dh = torch.randn_like(h)
+    h.backward(dh)
+    gr = gu.detach().float().requires_grad_()
+    hr = ref.swiglu(gr)
+    hr.backward(dh.float())
+    assert rel_err(h, hr) < 1e-2 and rel_err(gu.grad, gr.grad) < 2e-2
+
+    x = torch.randn(50, 64, device=dev()).bfloat16().requires_grad_()
+    y = F.gelu(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    yr = ref.gelu_tanh(xr)
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < 1e-2 and rel_err(x.grad, xr.grad) < 2e-2
+
+    emb = torch.randn(100, 64, device=dev()).bfloat16().requires_grad_()
+    pos = torch.randn(16, 64, device=dev()).bfloat16().requires_grad_()
+    tok = torch.randint(0, 100, (3, 16), device=dev())
+    e = F.embedding(tok, emb, pos, 16)
+    de = torch.randn_like(e)
+    e.backward(de)
+    er, pr = emb.detach().float().requires_grad_(), pos.detach().float().requires_grad_()
+    want = er[tok] + pr[None]
+    want.backward(de.float())
+    assert rel_err(e, want) < 1e-2
+    assert rel_err(emb.grad, er.grad) < 1e-2 and rel_err(pos.grad, pr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("n,V", [(9, 64), (130, 50304), (64, 151936)])
+def test_cross_entropy(n, V):
+    torch.manual_seed(9)
+    logits = (3 * torch.randn(n, V, device=dev())).bfloat16().requires_grad_()
+    tgt = torch.randint(0, V, (n,), device=dev())
+    tgt[::5] = -1
+    loss = F.cross_entropy(logits, tgt)
+    loss.backward()
+    lr = logits.detach().float().requires_grad_()
+    lossr = ref.cross_entropy(lr, tgt)
+    lossr.backward()
+    assert abs(loss.item() - lossr.item()) < 2e-3 * max(1.0, abs(lossr.item()))
+    assert rel_err(logits.grad, lr.grad) < 2e-2
+
+
+def test_lm_head_ce_fused():
+    torch.manual_seed(10)
+    n, d, V = 300, 128, 1000
+    x = (0.5 * torch.randn(n, d, device=dev())).bfloat16().requires_grad_()
+    w = (0.1 * torch.randn(V, d, device=dev())).bfloat16().requires_grad_()
+    tgt = torch.randint(0, V, (n,), device=dev())
+    tgt[:7] = -1
+    loss = F.lm_head_ce(x, w, tgt, chunk_rows=128)
+    loss.backward()
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lossr = ref.cross_entropy(ref.linear(xr, wr), tgt)
+    lossr.backward()
+    assert abs(loss.item() - lossr.item()) < 1e-2 * abs(lossr.item())
+    assert rel_err(x.grad, xr.grad) < 3e-2
+    assert rel_err(w.grad, wr.grad) < 3e-2
+
+
+def test_adamw_and_gradnorm():
+    torch.manual_seed(11)
+    n = 100003
+    npad = (n + 3) // 4 * 4
+    p = torch.randn(npad, device=dev())
+    g = torch.randn(npad, device=dev())
+    m = torch.zeros(npad, device=dev())
+    v = torch.zeros(npad, device=dev())
+    w16 = torch.empty(npad, device=dev(), dtype=torch.bfloat16)
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    scratch = torch.empty(1024, device=dev())
+    ss = torch.zeros(1, device=dev())
+    coef = torch.empty(1, device=dev())
+    norm = torch.empty(1, device=dev())
+    s = _cuda.stream_ptr()
+    _cuda.call("sumsq", g, _cuda.L(n), scratch, ss, 0, s)
+    _cuda.call("clip_coef", ss, 1.0, 1.0, coef, norm, s)
+    want_norm = g[:n].norm().item()
+    assert abs(norm.item() - want_norm) < 1e-3 * want_norm
+    want_coef = min(1.0, 1.0 / (want_norm + 1e-6))
+    assert abs(coef.item() - want_coef) < 1e-5
+    for step in (1, 2, 3):
+        _cuda.call("adamw", p, m, v, g, w16, _cuda.L(n), 3e-4, 0.9, 0.95, 1e-8, 0.1, step, coef, s)
+        ref.adamw_(pr[:n], mr[:n], vr[:n], g[:n], 3e-4, 0.9, 0.95, 1e-8, 0.1, step, want_coef)
+    assert rel_err(p[:n], pr[:n]) < 1e-5
+    assert rel_err(m[:n], mr[:n]) < 1e-4 and rel_err(v[:n], vr[:n]) < 1e-4
+    assert rel_err(w16[:n], pr[:n]) < 1e-2
+
+
+@pytest.mark.parametrize("E,k", [(128, 8), (8, 2), (60, 4)])
+def test_router_topk(E, k):
+    torch.manual_seed(12)
+    n = 333
+    logits = torch.randn(n, E, device=dev())
+    logits[5, :] = 0.0  # full tie -> lowest indices win
+    counts = torch.zeros(E, device=dev(), dtype=torch.int32)
+    probs, idx, w, lse = F.router_topk(logits, k, True, 1.0, counts=counts)
+    pr, ir, wr, lr = ref.router_topk(logits, k, True, 1.0)
+    assert torch.allclose(probs, pr, atol=1e-5)
+    assert (idx == ir).all()
+    assert torch.allclose(w, wr, atol=1e-5) and torch.allclose(lse, lr, atol=1e-4)
+    assert (idx[5] == torch.arange(k, device=dev())).all()
+    assert (counts.long() == torch.bincount(ir.flatten(), minlength=E)).all()
+
+
+def test_quant_and_argmax():
+    torch.manual_seed(13)
+    x = torch.randn(100, 520, device=dev()).bfloat16()
+    q, s = F.quant_rows(x)
+    qr, sr = ref.quant_rows(x)
+    assert torch.allclose(s, sr, rtol=1e-6) and (q.int() - qr.int()).abs().max() <= 1
+    lg = torch.randn(7, 151936, device=dev()).bfloat16()
+    assert (F.argmax_rows(lg).long() == lg.float().argmax(-1)).all()
