@@ -1,0 +1,77 @@
+"""Flash attention kernels vs the materialised-scores fp32 reference."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from brain_b200.ops import _cuda, reference as ref  # noqa: E402
+from brain_b200.ops.attention import flash_attention  # noqa: E402
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _check_device_error():
+    yield
+    _cuda.check_error()
+
+
+CASES = [
+    # B, T, hq, hk, hd, causal
+    (1, 128, 2, 1, 128, True),
+    (2, 256, 4, 2, 128, True),
+    (1, 512, 4, 4, 64, True),
+    (2, 200, 2, 1, 128, True),     # ragged tail tile
+    (1, 384, 2, 2, 128, False),
+    (1, 1024, 8, 2, 128, True),
+]
+
+
+@pytest.mark.parametrize("B,T,hq,hk,hd,causal", CASES)
+def test_flash_fwd(B, T, hq, hk, hd, causal):
+    torch.manual_seed(B * T + hq)
+    dev = "cuda"
+    width = (hq + 2 * hk) * hd
+    qkv = torch.randn(B * T, width, device=dev).bfloat16()
+    q, k, v = qkv[:, :hq * hd], qkv[:, hq * hd:(hq + hk) * hd], qkv[:, (hq + hk) * hd:]
+    out = flash_attention(q, k, v, B, T, hq, hk, hd, causal)
+    want = ref.attention(q.float().reshape(B, T, hq, hd), k.float().reshape(B, T, hk, hd),
+                         v.float().reshape(B, T, hk, hd), causal).reshape(B * T, hq * hd)
+    assert rel_err(out, want) < 2e-2
+
+
+@pytest.mark.parametrize("B,T,hq,hk,hd,causal", CASES)
+def test_flash_bwd(B, T, hq, hk, hd, causal):
+    torch.manual_seed(B * T + hq + 1)
+    dev = "cuda"
+    q = torch.randn(B * T, hq * hd, device=dev).bfloat16().requires_grad_()
+    k = torch.randn(B * T, hk * hd, device=dev).bfloat16().requires_grad_()
+    v = torch.randn(B * T, hk * hd, device=dev).bfloat16().requires_grad_()
+    out = flash_attention(q, k, v, B, T, hq, hk, hd, causal)
+    do = torch.randn_like(out)
+    out.backward(do)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    want = ref.attention(qr.reshape(B, T, hq, hd), kr.reshape(B, T, hk, hd),
+                         vr.reshape(B, T, hk, hd), causal).reshape(B * T, hq * hd)
+    want.backward(do.float())
+    assert rel_err(q.grad, qr.grad) < 3e-2
+    assert rel_err(k.grad, kr.grad) < 3e-2
+    assert rel_err(v.grad, vr.grad) < 3e-2
+
+
+def test_flash_fwd_prefix_offset():
+    """Queries are the last T positions of an S-long context (chunked prefill shape)."""
+    torch.manual_seed(5)
+    B, T, S, hq, hk, hd = 1, 128, 384, 2, 1, 128
+    q = torch.randn(B * T, hq * hd, device="cuda").bfloat16()
+    k = torch.randn(B * S, hk * hd, device="cuda").bfloat16()
+    v = torch.randn(B * S, hk * hd, device="cuda").bfloat16()
+    out = flash_attention(q, k, v, B, T, hq, hk, hd, True, S=S)
+    want = ref.attention(q.float().reshape(B, T, hq, hd), k.float().reshape(B, S, hk, hd),
+                         v.float().reshape(B, S, hk, hd), True).reshape(B * T, hq * hd)
+    assert rel_err(out, want) < 2e-2
