@@ -1,11 +1,12 @@
 // Flash attention backward on tcgen05, recompute-based, deterministic (no atomics):
 //   delta = rowsum(dO * O)                                  fa_delta_kernel
 //   dQ    : one CTA per (query tile, query head, batch)     fa_bwd_dq_kernel
-//             per KV block:  S = Q K^T, dP = dO V^T  (TMEM) -> dS = P*(dP-delta)*scale (smem, bf16)
+//             per KV block:  S = Q K^T, dP = dO V^T  (TMEM) -> dS = P*(dP-delta)*scale (packed bf16,
+//                            written back over S in TMEM)
 //                            dQ += dS K               (TMEM accumulator)
 //   dK,dV : one CTA per (KV tile, KV head, batch), looping over the query heads of the GQA group
 //           and the query tiles that can see the KV tile   fa_bwd_dkv_kernel
-//             S^T = K Q^T, dP^T = V dO^T (TMEM) -> P^T, dS^T (smem, bf16)
+//             S^T = K Q^T, dP^T = V dO^T (TMEM) -> P^T, dS^T (packed bf16 over the same columns)
 //             dV += P^T dO, dK += dS^T Q             (TMEM accumulators)
 // Operands that are needed "transposed" are not copied: the same 128-byte-swizzled shared-memory
 // tile is described K-major for one MMA and MN-major for the other.
@@ -86,8 +87,7 @@ struct DqCfg {
   static constexpr int OFF_DO = OFF_Q + TILE;
   static constexpr int OFF_K = OFF_DO + TILE;
   static constexpr int OFF_V = OFF_K + 2 * TILE;
-  static constexpr int OFF_DS = OFF_V + 2 * TILE;
-  static constexpr int OFF_BAR = OFF_DS + 2 * SUB;
+  static constexpr int OFF_BAR = OFF_V + 2 * TILE;
   static constexpr int SMEM_MIN = OFF_BAR + 256 + 1024;
   static constexpr int SMEM = SMEM_MIN < 120 * 1024 ? 120 * 1024 : SMEM_MIN;
 };
@@ -106,7 +106,6 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sDO = smem + Cfg::OFF_DO;
   uint8_t* sK = smem + Cfg::OFF_K;
   uint8_t* sV = smem + Cfg::OFF_V;
-  uint8_t* sDS = smem + Cfg::OFF_DS;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* q_full = bars;        // Q and dO
   uint64_t* k_full = bars + 1;    // 2
@@ -188,7 +187,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t idesc_dq = umma_idesc(1, 1, 1, 0, 1, 128, HD);
       bool ok = mbar_wait(q_full, 0);
       if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
-      const uint32_t aq = smem_u32(sQ), ado = smem_u32(sDO), ads = smem_u32(sDS);
+      const uint32_t aq = smem_u32(sQ), ado = smem_u32(sDO);
       for (int j = 0; j < n_blocks && ok; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -215,7 +214,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_after();
 #pragma unroll
         for (int t = 0; t < 8; ++t)
-          umma_f16_ss(tDQ, desc_kmajor(ads, t), desc_mnmajor(bk, t), idesc_dq, (j | t) != 0);
+          umma_f16_ts(tDQ, tS + t * 8, desc_mnmajor(bk, t), idesc_dq, (j | t) != 0);
         umma_commit(dq_done);
         umma_commit(&k_empty[st]);
       }
@@ -236,37 +235,45 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      if (j > 0) {  // dS buffer is free once the previous dQ MMA has read it
+      if (j > 0) {  // already complete (S_j was issued after dQ_{j-1}); keeps the phase in step
         ok = mbar_wait(dq_done, (j - 1) & 1);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
       const int kv0 = j * 128;
       const bool need_mask = (kv0 + 127 > kv_limit_row);
+      // two halves of 64 kv columns; dS (packed bf16) overwrites the S columns already consumed
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rp[32];
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t rs0[32], rs1[32], rp0[32], rp1[32];
         __syncwarp();
-        tmem_ld32(tS + lane_sel + c * 32, rs);
-        tmem_ld32(tDP + lane_sel + c * 32, rp);
+        tmem_ld32(tS + lane_sel + hf * 64, rs0);
+        tmem_ld32(tS + lane_sel + hf * 64 + 32, rs1);
+        tmem_ld32(tDP + lane_sel + hf * 64, rp0);
+        tmem_ld32(tDP + lane_sel + hf * 64 + 32, rp1);
         tmem_wait_ld();
-        const int lim = kv_limit_row - (kv0 + c * 32);
-        uint32_t pk[16];
+        const int lim = kv_limit_row - (kv0 + hf * 64);
+        uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(rs[i]) * args.scale_log2 - lse2);
-          float p1 = exp2f(__uint_as_float(rs[i + 1]) * args.scale_log2 - lse2);
+          float p0 = exp2f(__uint_as_float(rs0[i]) * args.scale_log2 - lse2);
+          float p1 = exp2f(__uint_as_float(rs0[i + 1]) * args.scale_log2 - lse2);
+          float p2 = exp2f(__uint_as_float(rs1[i]) * args.scale_log2 - lse2);
+          float p3 = exp2f(__uint_as_float(rs1[i + 1]) * args.scale_log2 - lse2);
           if (need_mask) {
             if (i > lim) p0 = 0.f;
             if (i + 1 > lim) p1 = 0.f;
+            if (i + 32 > lim) p2 = 0.f;
+            if (i + 33 > lim) p3 = 0.f;
           }
-          const float d0 = p0 * (__uint_as_float(rp[i]) - dlt) * args.scale;
-          const float d1 = p1 * (__uint_as_float(rp[i + 1]) - dlt) * args.scale;
-          pk[i >> 1] = pack_bf16x2(d0, d1);
+          pk[i >> 1] = pack_bf16x2(p0 * (__uint_as_float(rp0[i]) - dlt) * args.scale,
+                                   p1 * (__uint_as_float(rp0[i + 1]) - dlt) * args.scale);
+          pk[16 + (i >> 1)] = pack_bf16x2(p2 * (__uint_as_float(rp1[i]) - dlt) * args.scale,
+                                          p3 * (__uint_as_float(rp1[i + 1]) - dlt) * args.scale);
         }
-        store_row_chunk32(sDS, row, c, pk);
+        tmem_st32(tS + lane_sel + hf * 32, pk);
       }
-      fence_proxy_async_smem();
+      tmem_wait_st();
       tc_fence_before();
       mbar_arrive(ds_ready);
     }
@@ -316,9 +323,7 @@ struct DkvCfg {
   static constexpr int OFF_V = OFF_K + TILE;
   static constexpr int OFF_Q = OFF_V + TILE;
   static constexpr int OFF_DO = OFF_Q + TILE;
-  static constexpr int OFF_PT = OFF_DO + TILE;
-  static constexpr int OFF_DST = OFF_PT + 2 * SUB;
-  static constexpr int OFF_STAT = OFF_DST + 2 * SUB;  // lse2[128], delta[128]
+  static constexpr int OFF_STAT = OFF_DO + TILE;  // lse2[128], delta[128]
   static constexpr int OFF_BAR = OFF_STAT + 1024;
   static constexpr int SMEM_MIN = OFF_BAR + 256 + 1024;
   static constexpr int SMEM = SMEM_MIN < 120 * 1024 ? 120 * 1024 : SMEM_MIN;
@@ -338,8 +343,6 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint8_t* sV = smem + Cfg::OFF_V;
   uint8_t* sQ = smem + Cfg::OFF_Q;
   uint8_t* sDO = smem + Cfg::OFF_DO;
-  uint8_t* sPT = smem + Cfg::OFF_PT;
-  uint8_t* sDST = smem + Cfg::OFF_DST;
   float* s_lse2 = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);
   float* s_delta = s_lse2 + 128;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
@@ -418,7 +421,6 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       bool ok = mbar_wait(kv_full, 0);
       if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
       const uint32_t ak = smem_u32(sK), av = smem_u32(sV), bq = smem_u32(sQ), bdo = smem_u32(sDO);
-      const uint32_t apt = smem_u32(sPT), adst = smem_u32(sDST);
       for (int it = 0; it < n_iter && ok; ++it) {
         if (!mbar_wait(qdo_full, it & 1)) {
           set_error(args.err, ERR_WAIT_MMA_FULL);
@@ -441,10 +443,10 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tc_fence_after();
 #pragma unroll
         for (int t = 0; t < 8; ++t)
-          umma_f16_ss(tDV, desc_kmajor(apt, t), desc_mnmajor(bdo, t), idesc_acc, (it | t) != 0);
+          umma_f16_ts(tDV, tST + t * 8, desc_mnmajor(bdo, t), idesc_acc, (it | t) != 0);
 #pragma unroll
         for (int t = 0; t < 8; ++t)
-          umma_f16_ss(tDK, desc_kmajor(adst, t), desc_mnmajor(bq, t), idesc_acc, (it | t) != 0);
+          umma_f16_ts(tDK, tDPT + t * 8, desc_mnmajor(bq, t), idesc_acc, (it | t) != 0);
         umma_commit(dkv_done);
         umma_commit(qdo_empty);
       }
@@ -475,7 +477,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      if (it > 0) {
+      if (it > 0) {  // already complete; keeps the barrier phase in step for the final wait
         ok = mbar_wait(dkv_done, (it - 1) & 1);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -484,32 +486,41 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const int q_min = args.causal ? (kv_idx - off) : -0x40000000;
       const bool need_mask = args.causal && (q0 < q_min);
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rp[32];
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t rs0[32], rs1[32], rp0[32], rp1[32];
         __syncwarp();
-        tmem_ld32(tST + lane_sel + c * 32, rs);
-        tmem_ld32(tDPT + lane_sel + c * 32, rp);
+        tmem_ld32(tST + lane_sel + hf * 64, rs0);
+        tmem_ld32(tST + lane_sel + hf * 64 + 32, rs1);
+        tmem_ld32(tDPT + lane_sel + hf * 64, rp0);
+        tmem_ld32(tDPT + lane_sel + hf * 64 + 32, rp1);
         tmem_wait_ld();
-        uint32_t pk[16], dk_[16];
-        const int first_ok = q_min - (q0 + c * 32);  // columns i >= first_ok are visible
+        uint32_t pk[32], dk_[32];
+        const int first_ok = q_min - (q0 + hf * 64);  // columns i >= first_ok are visible
+        const float* ls = s_lse2 + hf * 64;
+        const float* dl = s_delta + hf * 64;
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float l0 = s_lse2[c * 32 + i], l1 = s_lse2[c * 32 + i + 1];
-          float p0 = exp2f(__uint_as_float(rs[i]) * args.scale_log2 - l0);
-          float p1 = exp2f(__uint_as_float(rs[i + 1]) * args.scale_log2 - l1);
+          float p0 = exp2f(__uint_as_float(rs0[i]) * args.scale_log2 - ls[i]);
+          float p1 = exp2f(__uint_as_float(rs0[i + 1]) * args.scale_log2 - ls[i + 1]);
+          float p2 = exp2f(__uint_as_float(rs1[i]) * args.scale_log2 - ls[32 + i]);
+          float p3 = exp2f(__uint_as_float(rs1[i + 1]) * args.scale_log2 - ls[33 + i]);
           if (need_mask) {
             if (i < first_ok) p0 = 0.f;
             if (i + 1 < first_ok) p1 = 0.f;
+            if (i + 32 < first_ok) p2 = 0.f;
+            if (i + 33 < first_ok) p3 = 0.f;
           }
-          const float d0 = p0 * (__uint_as_float(rp[i]) - s_delta[c * 32 + i]) * args.scale;
-          const float d1 = p1 * (__uint_as_float(rp[i + 1]) - s_delta[c * 32 + i + 1]) * args.scale;
           pk[i >> 1] = pack_bf16x2(p0, p1);
-          dk_[i >> 1] = pack_bf16x2(d0, d1);
+          pk[16 + (i >> 1)] = pack_bf16x2(p2, p3);
+          dk_[i >> 1] = pack_bf16x2(p0 * (__uint_as_float(rp0[i]) - dl[i]) * args.scale,
+                                    p1 * (__uint_as_float(rp0[i + 1]) - dl[i + 1]) * args.scale);
+          dk_[16 + (i >> 1)] = pack_bf16x2(p2 * (__uint_as_float(rp1[i]) - dl[32 + i]) * args.scale,
+                                           p3 * (__uint_as_float(rp1[i + 1]) - dl[33 + i]) * args.scale);
         }
-        store_row_chunk32(sPT, row, c, pk);
-        store_row_chunk32(sDST, row, c, dk_);
+        tmem_st32(tST + lane_sel + hf * 32, pk);
+        tmem_st32(tDPT + lane_sel + hf * 32, dk_);
       }
-      fence_proxy_async_smem();
+      tmem_wait_st();
       tc_fence_before();
       mbar_arrive(pds_ready);
     }

@@ -1,14 +1,18 @@
 // Causal / full GQA flash attention forward on tcgen05 (no T x T materialisation).
 //
 // One CTA per (128-row query tile, query head, batch).  Per 128-row KV block j:
-//   S_j   = Q K_j^T            tcgen05.mma  (SS, fp32 accumulator in TMEM, double buffered)
-//   P_j   = exp2(S_j*c - m)    128 softmax threads, one query row each (tcgen05.ld), online max
-//                              with lazy rescale of the O accumulator (tcgen05.ld/st) and P written
-//                              to shared memory in the 128-byte-swizzled K-major operand layout
-//   O    += P_j V_j            tcgen05.mma  (A = P from smem, B = V tile read MN-major)
+//   S_j   = Q K_j^T            tcgen05.mma  (SS, fp32 accumulator in TMEM)
+//   P_j   = exp2(S_j*c - m)    128 softmax threads, one query row each: the whole row is pulled
+//                              into registers with four back-to-back tcgen05.ld and one wait,
+//                              online max with lazy rescale of the O accumulator
+//                              (tcgen05.ld/st), and P is written back as packed bf16 OVER the S
+//                              columns in TMEM (tcgen05.st) — no shared-memory round trip
+//   O    += P_j V_j            tcgen05.mma  (A = P from TMEM, B = V tile read MN-major)
 // Warp roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..5 softmax
-// and epilogue.  Q/K/V are read with 2-D TMA maps over the [tokens, heads*hd] activations (row
-// pitch free), so strided views of a fused qkv buffer work without a copy.
+// and epilogue.  A CTA uses 256 TMEM columns and < 100 KB of shared memory, so two CTAs share an
+// SM: while one runs its softmax the other keeps the tensor pipe busy.
+// Q/K/V are read with 2-D TMA maps over the [tokens, heads*hd] activations (row pitch free), so
+// strided views of a fused qkv buffer work without a copy.
 //
 // Replaces crates/kernels/wgsl/{gqa_scores,attn_softmax,gqa_apply,flash_attn_causal_gqa}.wgsl.
 #include "../common/host.hpp"
@@ -32,19 +36,18 @@ struct FaFwdCfg {
   static constexpr int NSUB = HD / 64;             // 64-column swizzled sub-tiles per row
   static constexpr int SUB_BYTES = 128 * 128;      // [128 rows][64 bf16]
   static constexpr int TILE_BYTES = NSUB * SUB_BYTES;
-  static constexpr int P_BYTES = 2 * SUB_BYTES;    // [128][128] bf16
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + TILE_BYTES;
-  static constexpr int OFF_V = OFF_K + 2 * TILE_BYTES;
-  static constexpr int OFF_P = OFF_V + 2 * TILE_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_V = OFF_K + TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_V + TILE_BYTES;
   static constexpr int SMEM_MIN = OFF_BAR + 256 + 1024;
-  // at least 120 KB so only one CTA is resident per SM (each allocates all 512 TMEM columns)
-  static constexpr int SMEM = SMEM_MIN < 120 * 1024 ? 120 * 1024 : SMEM_MIN;
+  // at least 80 KB so at most two CTAs are resident per SM (each allocates 256 TMEM columns)
+  static constexpr int SMEM = SMEM_MIN < 80 * 1024 ? 80 * 1024 : SMEM_MIN;
+  static constexpr int TMEM_COLS = 256;
 };
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 2)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const FaFwdArgs args) {
   using Cfg = FaFwdCfg<HD>;
@@ -55,17 +58,16 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint8_t* sQ = smem + Cfg::OFF_Q;
   uint8_t* sK = smem + Cfg::OFF_K;
   uint8_t* sV = smem + Cfg::OFF_V;
-  uint8_t* sP = smem + Cfg::OFF_P;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
-  uint64_t* q_full = bars;          // 1
-  uint64_t* k_full = bars + 1;      // 2
-  uint64_t* k_empty = bars + 3;     // 2
-  uint64_t* v_full = bars + 5;      // 2
-  uint64_t* v_empty = bars + 7;     // 2
-  uint64_t* s_full = bars + 9;      // 2
-  uint64_t* p_ready = bars + 11;    // 1 (128 arrivals)
-  uint64_t* pv_done = bars + 12;    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 2;
+  uint64_t* v_full = bars + 3;
+  uint64_t* v_empty = bars + 4;
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_ready = bars + 6;   // 128 arrivals
+  uint64_t* pv_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
@@ -82,26 +84,25 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-    }
+    mbar_init(k_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(s_full, 1);
     mbar_init(p_ready, 128);
     mbar_init(pv_done, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_O = tmem_base + 256;
+  const uint32_t tmem_S = tmem_base;        // fp32 scores, later packed bf16 P in its first 64 cols
+  const uint32_t tmem_O = tmem_base + 128;  // fp32 output accumulator (HD columns)
 
   if (warp == 0) {
     if (lane == 0) {
@@ -112,82 +113,64 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
       for (int c = 0; c < NSUB; ++c)
         tma_load_2d(sQ + c * Cfg::SUB_BYTES, &tmQ, q_full, h * HD + c * 64, b * T + q0);
-      bool ok = true;
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_empty[st], ph ^ 1)) {
+      for (int j = 0; j < n_blocks; ++j) {
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(k_empty, ph ^ 1)) {
           set_error(args.err, ERR_WAIT_PRODUCER);
-          ok = false;
           break;
         }
-        mbar_expect_tx(&k_full[st], Cfg::TILE_BYTES);
+        mbar_expect_tx(k_full, Cfg::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < NSUB; ++c)
-          tma_load_2d(sK + st * Cfg::TILE_BYTES + c * Cfg::SUB_BYTES, &tmK, &k_full[st],
-                      kvh * HD + c * 64, b * S + j * 128);
-        if (!mbar_wait(&v_empty[st], ph ^ 1)) {
+          tma_load_2d(sK + c * Cfg::SUB_BYTES, &tmK, k_full, kvh * HD + c * 64, b * S + j * 128);
+        if (!mbar_wait(v_empty, ph ^ 1)) {
           set_error(args.err, ERR_WAIT_PRODUCER);
-          ok = false;
           break;
         }
-        mbar_expect_tx(&v_full[st], Cfg::TILE_BYTES);
+        mbar_expect_tx(v_full, Cfg::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < NSUB; ++c)
-          tma_load_2d(sV + st * Cfg::TILE_BYTES + c * Cfg::SUB_BYTES, &tmV, &v_full[st],
-                      kvh * HD + c * 64, b * S + j * 128);
+          tma_load_2d(sV + c * Cfg::SUB_BYTES, &tmV, v_full, kvh * HD + c * 64, b * S + j * 128);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(1, 1, 1, 0, 0, 128, 128);
       constexpr uint32_t idesc_pv = umma_idesc(1, 1, 1, 0, 1, 128, HD);
-      bool ok = true;
-      auto issue_qk = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!mbar_wait(&k_full[st], (j >> 1) & 1)) return false;
-        tc_fence_after();
-        const uint32_t aq = smem_u32(sQ), bk = smem_u32(sK + st * Cfg::TILE_BYTES);
-#pragma unroll
-        for (int t = 0; t < HD / 16; ++t) {
-          const uint32_t o = (t / 4) * Cfg::SUB_BYTES + (t % 4) * 32;
-          umma_f16_ss(tmem_base + (j & 1) * 128, umma_smem_desc(aq + o, 16, 1024),
-                      umma_smem_desc(bk + o, 16, 1024), idesc_qk, t != 0);
-        }
-        umma_commit(&s_full[j & 1]);
-        umma_commit(&k_empty[st]);
-        return true;
-      };
-      if (!mbar_wait(q_full, 0)) {
-        set_error(args.err, ERR_WAIT_MMA_FULL);
-        ok = false;
-      }
-      if (ok && !issue_qk(0)) {
-        set_error(args.err, ERR_WAIT_MMA_FULL);
-        ok = false;
-      }
+      const uint32_t aq = smem_u32(sQ), bk = smem_u32(sK), bv = smem_u32(sV);
+      bool ok = mbar_wait(q_full, 0);
+      if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
       for (int j = 0; j < n_blocks && ok; ++j) {
-        if (j + 1 < n_blocks && !issue_qk(j + 1)) {
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(k_full, ph)) {
           set_error(args.err, ERR_WAIT_MMA_FULL);
           ok = false;
           break;
         }
-        if (!mbar_wait(p_ready, j & 1) || !mbar_wait(&v_full[j & 1], (j >> 1) & 1)) {
+        tc_fence_after();
+        // S = Q K^T.  Issued after PV_{j-1}, so the tensor pipe's in-order execution guarantees
+        // P_{j-1} (which aliases these columns) has been consumed.
+#pragma unroll
+        for (int t = 0; t < HD / 16; ++t) {
+          const uint32_t o = (t / 4) * Cfg::SUB_BYTES + (t % 4) * 32;
+          umma_f16_ss(tmem_S, umma_smem_desc(aq + o, 16, 1024), umma_smem_desc(bk + o, 16, 1024),
+                      idesc_qk, t != 0);
+        }
+        umma_commit(s_full);
+        umma_commit(k_empty);
+        if (!mbar_wait(p_ready, ph) || !mbar_wait(v_full, ph)) {
           set_error(args.err, ERR_WAIT_MMA_TMEM);
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t ap = smem_u32(sP), bv = smem_u32(sV + (j & 1) * Cfg::TILE_BYTES);
+        // O += P V: A = packed bf16 P in TMEM (8 columns per 16-wide k-step), B = V MN-major
 #pragma unroll
-        for (int t = 0; t < 8; ++t) {  // 128 kv rows, 16 per MMA
-          const uint32_t oa = (t / 4) * Cfg::SUB_BYTES + (t % 4) * 32;
-          umma_f16_ss(tmem_O, umma_smem_desc(ap + oa, 16, 1024),
-                      umma_smem_desc(bv + t * 2048, Cfg::SUB_BYTES, 1024), idesc_pv,
-                      (j | t) != 0);
-        }
+        for (int t = 0; t < 8; ++t)
+          umma_f16_ts(tmem_O, tmem_S + t * 8, umma_smem_desc(bv + t * 2048, Cfg::SUB_BYTES, 1024),
+                      idesc_pv, (j | t) != 0);
         umma_commit(pv_done);
-        umma_commit(&v_empty[j & 1]);
+        umma_commit(v_empty);
       }
     }
   } else {
@@ -197,28 +180,38 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int q_idx = q0 + row;
     const uint32_t lane_sel = (uint32_t)(sw * 32) << 16;
     const int kv_limit_row = args.causal ? min(q_idx + off, S - 1) : S - 1;
+    const uint32_t tS = tmem_S + lane_sel;
+    const uint32_t tO = tmem_O + lane_sel;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
-      ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1);
+      ok = mbar_wait(s_full, j & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t tS = tmem_base + lane_sel + (j & 1) * 128;
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      tmem_ld32(tS, r0);
+      tmem_ld32(tS + 32, r1);
+      tmem_ld32(tS + 64, r2);
+      tmem_ld32(tS + 96, r3);
+      tmem_wait_ld();
       const int kv0 = j * 128;
-      const bool need_mask = (kv0 + 127 > kv_limit_row);  // per-row decision, loads stay uniform
+      const bool need_mask = (kv0 + 127 > kv_limit_row);
+      const int lim = kv_limit_row - kv0;  // columns <= lim are visible
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld32(tS + c * 32, r);
-        tmem_wait_ld();
-        const int lim = kv_limit_row - (kv0 + c * 32);
+      if (!need_mask) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(r[i]);
-          if (!need_mask || i <= lim) mx = fmaxf(mx, s);
+          mx = fmaxf(mx, fmaxf(fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])),
+                               fmaxf(__uint_as_float(r2[i]), __uint_as_float(r3[i]))));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (i <= lim) mx = fmaxf(mx, __uint_as_float(r0[i]));
+          if (i + 32 <= lim) mx = fmaxf(mx, __uint_as_float(r1[i]));
+          if (i + 64 <= lim) mx = fmaxf(mx, __uint_as_float(r2[i]));
+          if (i + 96 <= lim) mx = fmaxf(mx, __uint_as_float(r3[i]));
         }
       }
       mx *= args.scale_log2;
@@ -235,47 +228,50 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll 1
           for (int c = 0; c < HD / 32; ++c) {
             uint32_t r[32];
-            tmem_ld32(tmem_O + lane_sel + c * 32, r);
+            tmem_ld32(tO + c * 32, r);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(tmem_O + lane_sel + c * 32, r);
+            tmem_st32(tO + c * 32, r);
           }
-          tmem_wait_st();
         }
       }
       l *= alpha;
       m_ref = m_new;
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld32(tS + c * 32, r);
-        tmem_wait_ld();
-        const int lim = kv_limit_row - (kv0 + c * 32);
-        uint32_t pk[16];
+      const float sc = args.scale_log2;
+      uint32_t pk0[32], pk1[32];  // 128 probabilities as 64 packed bf16x2 words
+      float ls = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(r[i]) * args.scale_log2 - m_use);
-          float p1 = exp2f(__uint_as_float(r[i + 1]) * args.scale_log2 - m_use);
-          if (need_mask) {
-            if (i > lim) p0 = 0.f;
-            if (i + 1 > lim) p1 = 0.f;
-          }
-          l += p0 + p1;
-          pk[i >> 1] = pack_bf16x2(p0, p1);
+      for (int i = 0; i < 32; i += 2) {
+        float a0 = exp2f(__uint_as_float(r0[i]) * sc - m_use);
+        float a1 = exp2f(__uint_as_float(r0[i + 1]) * sc - m_use);
+        float b0 = exp2f(__uint_as_float(r1[i]) * sc - m_use);
+        float b1 = exp2f(__uint_as_float(r1[i + 1]) * sc - m_use);
+        float c0 = exp2f(__uint_as_float(r2[i]) * sc - m_use);
+        float c1 = exp2f(__uint_as_float(r2[i + 1]) * sc - m_use);
+        float d0 = exp2f(__uint_as_float(r3[i]) * sc - m_use);
+        float d1 = exp2f(__uint_as_float(r3[i + 1]) * sc - m_use);
+        if (need_mask) {
+          if (i > lim) a0 = 0.f;
+          if (i + 1 > lim) a1 = 0.f;
+          if (i + 32 > lim) b0 = 0.f;
+          if (i + 33 > lim) b1 = 0.f;
+          if (i + 64 > lim) c0 = 0.f;
+          if (i + 65 > lim) c1 = 0.f;
+          if (i + 96 > lim) d0 = 0.f;
+          if (i + 97 > lim) d1 = 0.f;
         }
-        // 32 columns = 4 x 16-byte chunks of sub-tile c/2; chunk index XOR (row % 8) = 128B swizzle
-        uint8_t* prow = sP + (c >> 1) * Cfg::SUB_BYTES + row * 128;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = ((c & 1) * 4 + q) ^ (row & 7);
-          *reinterpret_cast<uint4*>(prow + chunk * 16) =
-              make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
-        }
+        ls += (a0 + a1) + (b0 + b1) + (c0 + c1) + (d0 + d1);
+        pk0[i >> 1] = pack_bf16x2(a0, a1);         // kv columns   0..31  -> words  0..15
+        pk0[16 + (i >> 1)] = pack_bf16x2(b0, b1);  // kv columns  32..63  -> words 16..31
+        pk1[i >> 1] = pack_bf16x2(c0, c1);         // kv columns  64..95  -> words 32..47
+        pk1[16 + (i >> 1)] = pack_bf16x2(d0, d1);  // kv columns  96..127 -> words 48..63
       }
-      fence_proxy_async_smem();
+      l += ls;
+      tmem_st32(tS, pk0);
+      tmem_st32(tS + 32, pk1);
+      tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_ready);
     }
@@ -293,7 +289,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t r[32];
         __syncwarp();
-        tmem_ld32(tmem_O + lane_sel + c * 32, r);
+        tmem_ld32(tO + c * 32, r);
         tmem_wait_ld();
         if (q_idx < T) {
 #pragma unroll
@@ -317,7 +313,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 

@@ -130,18 +130,26 @@ __global__ void qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dout, i
       dxr[HALF + lane * PER + j] = __float2bfloat16(rstd * (db[j] * wb[j] - xb[j] * dot));
     }
   }
-  if (w_q && dw_q) {
+  // block-level reduction in shared memory, then one atomic per element per block
+  __shared__ float red[2][8][HD];
+  const int wib = threadIdx.x >> 5;
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      atomicAdd(dw_q + lane * PER + j, gq_a[j]);
-      atomicAdd(dw_q + HALF + lane * PER + j, gq_b[j]);
-    }
+  for (int j = 0; j < PER; ++j) {
+    red[0][wib][lane * PER + j] = gq_a[j];
+    red[0][wib][HALF + lane * PER + j] = gq_b[j];
+    red[1][wib][lane * PER + j] = gk_a[j];
+    red[1][wib][HALF + lane * PER + j] = gk_b[j];
   }
-  if (w_k && dw_k && hk > 0) {
-#pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      atomicAdd(dw_k + lane * PER + j, gk_a[j]);
-      atomicAdd(dw_k + HALF + lane * PER + j, gk_b[j]);
+  __syncthreads();
+  const int nw = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < 2 * HD; i += blockDim.x) {
+    const int which = i / HD, c = i % HD;
+    float sum = 0.f;
+    for (int w2 = 0; w2 < nw; ++w2) sum += red[which][w2][c];
+    if (which == 0) {
+      if (w_q && dw_q) atomicAdd(dw_q + c, sum);
+    } else {
+      if (w_k && dw_k && hk > 0) atomicAdd(dw_k + c, sum);
     }
   }
 }
@@ -179,7 +187,7 @@ BB_API int bb_qknorm_rope_bwd(const void* dout, int ldo, const void* x, int ldx,
   const long total = (long)n_tok * (hq + hk);
   if (total <= 0) return BB_OK;
   long want = (total + 7) / 8;
-  const long cap = (long)sm_count() * 8;
+  const long cap = (long)sm_count() * 4;
   const int grid = (int)(want < cap ? want : cap);
   if (hd == 128)
     qknorm_rope_bwd_kernel<128><<<grid, 256, 0, (cudaStream_t)stream>>>(
