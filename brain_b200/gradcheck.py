@@ -184,8 +184,11 @@ def check_qwen_lora(n_dirs: int = 4, eps: float = 5e-3, seed: int = 0, dtype=tor
     return _model_check(m, cfg.vocab, 2, 6, n_dirs, eps, seed, dtype)
 
 
-def check_moe(n_dirs: int = 4, eps: float = 5e-3, seed: int = 0, dtype=torch.float32,
+def check_moe(n_dirs: int = 4, eps: float = 1e-5, seed: int = 0, dtype=torch.float64,
               family: str = "toymoe") -> Report:
+    """Top-k routing is piecewise: a 5e-3 step flips expert selections on a tiny model and the
+    central difference then straddles a discontinuity, so this gate differentiates in fp64 with a
+    small step (the selection is stable inside it)."""
     from .models.config import MoeConfig
     from .models.moe import MoeModel
     if family == "toymoe":
@@ -198,9 +201,13 @@ def check_moe(n_dirs: int = 4, eps: float = 5e-3, seed: int = 0, dtype=torch.flo
     return _model_check(MoeModel(cfg).init_weights(1), cfg.vocab, 2, 6, n_dirs, eps, seed, dtype)
 
 
+def check_qwen_moe(n_dirs: int = 4, eps: float = 1e-5, seed: int = 0, dtype=torch.float64) -> Report:
+    return check_moe(n_dirs, eps, seed, dtype, family="qwen3_moe")
+
+
 GATES = {
     "gpt": check_gpt, "qwen": check_qwen, "qwen2": check_qwen2, "qwen_lora": check_qwen_lora,
-    "moe": check_moe,
+    "moe": check_moe, "qwen_moe": check_qwen_moe,
 }
 
 

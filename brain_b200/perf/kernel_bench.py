@@ -1,0 +1,140 @@
+"""Kernel micro-benchmarks with roofline fractions against the measured peaks.
+
+    python -m brain_b200.perf.kernel_bench gemm  [--m 16384 --n 4096 --k 1024 --layout tn|nn|tt --bn 0]
+    python -m brain_b200.perf.kernel_bench flash [--b 4 --t 4096 --hq 16 --hk 8 --hd 128 --bwd]
+    python -m brain_b200.perf.kernel_bench i8    [--m 256 --n 4096 --k 4096]
+    python -m brain_b200.perf.kernel_bench copy  (HBM copy bandwidth probe)
+
+Timing: CUDA events on the launching stream, warm-up first, inputs rotated through a pool larger
+than the 126 MB L2 so every timed launch starts cold.  ``--iters 1 --warmup 0`` gives a run that is
+small enough to put under ``ncu``.  The roofline denominators come from ``MEASURED_PEAKS.json``
+(driver-measured cuBLAS bf16 throughput and copy bandwidth) when present, else the documented
+fallback (1.59 PFLOP/s, 6.65 TB/s)."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    try:
+        p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return p["bf16_tflops"] * 1e12, p["hbm_gbs"] * 1e9, "measured"
+    except Exception:
+        return 1.59e15, 6.65e12, "fallback"
+
+
+def timeit(fns, iters, warmup):
+    """``fns``: list of closures over distinct input sets (rotated so inputs exceed L2)."""
+    for i in range(warmup):
+        fns[i % len(fns)]()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for i in range(iters):
+        fns[i % len(fns)]()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters * 1e-3
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "flash", "i8", "copy"])
+    ap.add_argument("--m", type=int, default=16384)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--layout", default="tn", help="tn: x.W^T (fwd), nn: dy.W (dX), tt: dy^T.x (dW)")
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--b", type=int, default=4)
+    ap.add_argument("--t", type=int, default=4096)
+    ap.add_argument("--hq", type=int, default=16)
+    ap.add_argument("--hk", type=int, default=8)
+    ap.add_argument("--hd", type=int, default=128)
+    ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--library", action="store_true", help="also time the cuBLAS / SDPA baseline")
+    a = ap.parse_args(argv)
+    from brain_b200.ops import _cuda, functional as F
+    from brain_b200.ops.attention import flash_attention
+
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    pf, bw, src = peaks()
+    out = {"what": a.what, "peaks": src}
+    if a.what == "copy":
+        n = 1 << 30
+        x = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        y = torch.empty_like(x)
+        t = timeit([lambda: y.copy_(x)], a.iters, a.warmup)
+        out.update(seconds=t, gbs=2 * n * 2 / t / 1e9, frac_of_peak=2 * n * 2 / t / bw)
+    elif a.what in ("gemm", "i8"):
+        M, N, K = a.m, a.n, a.k
+        es = 1 if a.what == "i8" else 2
+        pool = max(1, min(8, int(200e6 // ((M * K + N * K) * es + M * N * 2)) + 1))
+        sets = []
+        for _ in range(pool):
+            if a.what == "i8":
+                A = torch.randint(-127, 128, (M, K), device=dev, dtype=torch.int8)
+                B = torch.randint(-127, 128, (N, K), device=dev, dtype=torch.int8)
+                sa = torch.rand(M, device=dev) + 0.5
+                sb = torch.rand(N, device=dev) + 0.5
+                C = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+                sets.append((A, B, sa, sb, C))
+            else:
+                A = torch.randn(M, K, device=dev).bfloat16()
+                B = torch.randn(N, K, device=dev).bfloat16()
+                C = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+                if a.layout == "nn":      # dX = dy[M,K] . W[K,N]: B stored [K, N]
+                    B = B.t().contiguous()
+                elif a.layout == "tt":    # dW = dy^T . x: both stored [K, rows]
+                    A, B = A.t().contiguous(), B.t().contiguous()
+                sets.append((A, B, C))
+        if a.what == "i8":
+            fns = [(lambda s=s: F.gemm_i8(s[0], s[1], s[2], s[3], out=s[4], bn=a.bn)) for s in sets]
+        else:
+            amn, bmn = a.layout == "tt", a.layout in ("nn", "tt")
+            fns = [(lambda s=s: F.gemm(s[0], s[1], a_mn=amn, b_mn=bmn, out=s[2], bn=a.bn)) for s in sets]
+        t = timeit(fns, a.iters, a.warmup)
+        fl = 2.0 * M * N * K
+        peak = pf * (2 if a.what == "i8" else 1)
+        out.update(M=M, N=N, K=K, layout=a.layout, seconds=t, tflops=fl / t / 1e12,
+                   frac_of_peak=fl / t / peak)
+        if a.library and a.what == "gemm" and a.layout == "tn":
+            A, B, C = sets[0]
+            tl = timeit([lambda: torch.matmul(A, B.t(), out=C)], a.iters, a.warmup)
+            out["library_tflops"] = fl / tl / 1e12
+    else:
+        B_, T, hq, hk, hd = a.b, a.t, a.hq, a.hk, a.hd
+        sets = []
+        for _ in range(3):
+            q = torch.randn(B_ * T, hq * hd, device=dev).bfloat16().requires_grad_(a.bwd)
+            k = torch.randn(B_ * T, hk * hd, device=dev).bfloat16().requires_grad_(a.bwd)
+            v = torch.randn(B_ * T, hk * hd, device=dev).bfloat16().requires_grad_(a.bwd)
+            sets.append((q, k, v))
+        fl = 4.0 * B_ * hq * T * T * hd / 2
+        if not a.bwd:
+            fns = [(lambda s=s: flash_attention(s[0], s[1], s[2], B_, T, hq, hk, hd, True)) for s in sets]
+        else:
+            outs = [flash_attention(s[0], s[1], s[2], B_, T, hq, hk, hd, True) for s in sets]
+            do = torch.randn_like(outs[0])
+            fns = [(lambda s=s, o=o: torch.autograd.grad(o, s, do, retain_graph=True))
+                   for s, o in zip(sets, outs)]
+            fl *= 2.5
+        t = timeit(fns, a.iters, a.warmup)
+        out.update(B=B_, T=T, hq=hq, hk=hk, hd=hd, bwd=a.bwd, seconds=t, tflops=fl / t / 1e12,
+                   frac_of_peak=fl / t / pf)
+    _cuda.check_error()
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,321 @@
+"""Paged-KV inference engine for the dense Qwen3 family (reference: crates/qwen3/src/serve.rs:
+432-530 Engine state, 1194-1304 batched decode steps, 1350-1394 greedy head, 1557-1623 chunked
+prefill with prefix-cache reuse).
+
+* KV cache: per layer K and V pools ``[num_blocks, n_kv_heads, block_size, head_dim]`` bf16.
+* ``prefill_chunk``: one chunk of one prompt; K/V rows are appended to the sequence's pages, and
+  attention runs the tcgen05 flash kernel over (pages gathered to a contiguous buffer when the chunk
+  has a past, else the chunk itself).
+* ``decode``: one batched step (or a window of k greedy steps fed back on the device) over all
+  running sequences with the split-KV paged attention kernel; greedy head = on-device argmax.
+* ``weights='int8'``: W8A8 — per-output-channel symmetric int8 weights, dynamic per-token int8
+  activations, tcgen05 ``kind::i8`` GEMM with both scales applied in the epilogue
+  (crates/model/src/int8.rs:33-59, 221-235).
+* Tensor parallel serving: with a ``tp`` group every rank holds a head-/column-slice of the
+  projections and the row-parallel outputs are summed by the one-shot peer all-reduce
+  (``parallel.tp``).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from ..models.config import QwenConfig
+from ..ops import functional as F
+from ..ops import reference as ref
+from ..ops._cuda import L, call, stream_ptr
+from ..ops.attention import flash_attention
+
+
+class _Lin:
+    """A projection held either as bf16 weights or as W8A8 int8 weights + per-channel scales."""
+
+    def __init__(self, w: torch.Tensor, bias: Optional[torch.Tensor] = None, int8: bool = False):
+        self.int8 = int8
+        self.bias = bias.float().contiguous() if bias is not None else None
+        if int8:
+            self.wq, self.sw = F.quant_rows(w.float() if not w.is_cuda else w)
+            self.wq, self.sw = self.wq.contiguous(), self.sw.contiguous()
+            self.out_features = w.shape[0]
+        else:
+            self.w = w.contiguous()
+            self.out_features = w.shape[0]
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if self.int8:
+            if x.is_cuda:
+                xq, sx = F.quant_rows(x)
+                y = F.gemm_i8(xq, self.wq, sx, self.sw)
+            else:
+                xq, sx = ref.quant_rows(x)
+                y = ((xq.float() @ self.wq.float().t()) * sx[:, None] * self.sw[None, :]).to(x.dtype)
+            if self.bias is not None:
+                y = y + self.bias.to(y.dtype)
+            return y
+        if x.is_cuda:
+            return F.gemm(x, self.w, bias=self.bias)
+        return ref.linear(x, self.w, self.bias.to(x.dtype) if self.bias is not None else None)
+
+    def nbytes(self) -> int:
+        if self.int8:
+            return self.wq.numel() + 4 * self.sw.numel()
+        return self.w.numel() * self.w.element_size()
+
+
+class QwenEngine:
+    def __init__(self, model, block_size: int = 16, num_blocks: int = 1024, max_seq_len: int = 4096,
+                 max_prefill: int = 512, weights: str = "bf16", topk: int = 64, tp=None,
+                 decode_splits: int = 0):
+        cfg: QwenConfig = model.cfg
+        self.cfg = cfg
+        self.tp = tp
+        self.tp_world = tp.world if tp is not None else 1
+        self.tp_rank = tp.rank if tp is not None else 0
+        dev = next(model.parameters()).device
+        self.device = dev
+        self.cuda = dev.type == "cuda"
+        self.dtype = torch.bfloat16 if self.cuda else torch.float32
+        self.vocab = cfg.vocab
+        self.block_size, self.num_blocks = block_size, num_blocks
+        self.max_seq_len, self.max_prefill_tokens = max_seq_len, max_prefill
+        self.topk_capacity = topk
+        self.max_blocks = (max_seq_len + block_size - 1) // block_size
+        self.int8 = weights == "int8"
+        w = self.tp_world
+        assert cfg.n_heads % w == 0 and cfg.n_kv_heads % w == 0 and cfg.d_ff % w == 0, \
+            "tensor-parallel degree must divide the head counts and d_ff"
+        self.hq, self.hk, self.hd = cfg.n_heads // w, cfg.n_kv_heads // w, cfg.head_dim
+        r = self.tp_rank
+        q, kv, ff = cfg.q_dim, cfg.kv_dim, cfg.d_ff
+        ql, kl, fl = q // w, kv // w, ff // w
+
+        def cast(t):
+            return t.detach().to(dev, self.dtype)
+
+        self.tok = cast(model.tok)
+        self.layers = []
+        for blk in model.blocks:
+            wqkv = blk.wqkv.detach()
+            rows = torch.cat([wqkv[r * ql:(r + 1) * ql], wqkv[q + r * kl:q + (r + 1) * kl],
+                              wqkv[q + kv + r * kl:q + kv + (r + 1) * kl]])
+            bias = None
+            if blk.bqkv is not None:
+                b = blk.bqkv.detach()
+                bias = torch.cat([b[r * ql:(r + 1) * ql], b[q + r * kl:q + (r + 1) * kl],
+                                  b[q + kv + r * kl:q + kv + (r + 1) * kl]]).to(dev)
+            gu = blk.gate_up.detach()
+            gu_rows = torch.cat([gu[r * fl:(r + 1) * fl], gu[ff + r * fl:ff + (r + 1) * fl]])
+            self.layers.append(dict(
+                ln1=cast(blk.ln1), ln2=cast(blk.ln2),
+                q_norm=cast(blk.q_norm) if blk.q_norm is not None else None,
+                k_norm=cast(blk.k_norm) if blk.k_norm is not None else None,
+                qkv=_Lin(cast(rows), bias, self.int8),
+                wo=_Lin(cast(blk.wo.detach()[:, r * ql:(r + 1) * ql]), None, self.int8),
+                gate_up=_Lin(cast(gu_rows), None, self.int8),
+                down=_Lin(cast(blk.down.detach()[:, r * fl:(r + 1) * fl]), None, self.int8),
+            ))
+        self.norm = cast(model.norm)
+        head = model.head_weight().detach()
+        self.head = _Lin(cast(head), None, False)  # the LM head stays bf16 (as the reference keeps it fp32)
+        self.cos, self.sin = ref.rope_tables(max_seq_len, cfg.head_dim, cfg.rope_theta, device=dev)
+        shape = (num_blocks, self.hk, block_size, self.hd)
+        self.kc = [torch.zeros(shape, device=dev, dtype=self.dtype) for _ in model.blocks]
+        self.vc = [torch.zeros(shape, device=dev, dtype=self.dtype) for _ in model.blocks]
+        self.decode_splits = decode_splits
+        self.steps = 0
+
+    # ------------------------------------------------------------------ accounting
+    def kv_pool_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.kc) * 2
+
+    def kv_pool_capacity_tokens(self) -> int:
+        return self.num_blocks * self.block_size
+
+    def weight_bytes(self) -> int:
+        n = self.tok.numel() * self.tok.element_size()
+        for l in self.layers:
+            n += sum(l[k].nbytes() for k in ("qkv", "wo", "gate_up", "down"))
+        return n
+
+    # ------------------------------------------------------------------ building blocks
+    def _allreduce(self, x):
+        if self.tp is None or self.tp_world == 1:
+            return x
+        return self.tp.all_reduce(x)
+
+    def _slots(self, block_table: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """slot = block*bs + offset for (table row, position) pairs; block_table [n, max_blocks]."""
+        bs = self.block_size
+        blk = torch.gather(block_table, 1, (positions // bs).long()[:, None]).squeeze(1)
+        return (blk * bs + positions % bs).to(torch.int32)
+
+    def _append_kv(self, li: int, k, v, slots):
+        if self.cuda:
+            call("kv_append", k, k.stride(0), v, v.stride(0), slots, self.kc[li], self.vc[li],
+                 k.shape[0], self.hk, self.hd, self.block_size, stream_ptr())
+        else:
+            s = slots.long()
+            blk, off = s // self.block_size, s % self.block_size
+            self.kc[li][blk, :, off] = k.reshape(-1, self.hk, self.hd)
+            self.vc[li][blk, :, off] = v.reshape(-1, self.hk, self.hd)
+
+    def _gather_kv(self, li: int, block_table: torch.Tensor, S: int):
+        if self.cuda:
+            ok = torch.empty(S, self.hk * self.hd, device=self.device, dtype=self.dtype)
+            ov = torch.empty_like(ok)
+            call("kv_gather", self.kc[li], self.vc[li], block_table, ok, ov, S, self.hk, self.hd,
+                 self.block_size, stream_ptr())
+            return ok, ov
+        t = torch.arange(S, device=self.device)
+        blk = block_table[(t // self.block_size).long()].long()
+        off = t % self.block_size
+        return (self.kc[li][blk, :, off].reshape(S, -1), self.vc[li][blk, :, off].reshape(S, -1))
+
+    def _paged_attention(self, li: int, q, block_tables, seqlens):
+        B = q.shape[0]
+        hq, hk, hd = self.hq, self.hk, self.hd
+        scale = 1.0 / math.sqrt(hd)
+        if self.cuda:
+            splits = self.decode_splits
+            if splits <= 0:
+                # enough CTAs to fill the machine: B * hk * splits >= ~2 per SM
+                splits = max(1, min(16, (2 * 148 + B * hk - 1) // (B * hk)))
+            out = torch.empty(B, hq * hd, device=self.device, dtype=self.dtype)
+            part_o = torch.empty(B * hq * splits * hd, device=self.device, dtype=torch.float32)
+            part_ml = torch.empty(B * hq * splits * 2, device=self.device, dtype=torch.float32)
+            call("paged_decode", q, q.stride(0), self.kc[li], self.vc[li], block_tables,
+                 block_tables.shape[1], seqlens, out, out.stride(0), part_o, part_ml, B, hq, hk, hd,
+                 self.block_size, splits, float(scale), stream_ptr())
+            return out
+        outs = []
+        for b in range(B):
+            S = int(seqlens[b])
+            kk, vv = self._gather_kv(li, block_tables[b], S)
+            o = ref.attention(q[b].reshape(1, 1, hq, hd), kk.reshape(1, S, hk, hd),
+                              vv.reshape(1, S, hk, hd), causal=False, scale=scale)
+            outs.append(o.reshape(1, hq * hd))
+        return torch.cat(outs)
+
+    def _layer(self, li: int, x, delta, pos, attn_fn):
+        l = self.layers[li]
+        eps = self.cfg.rms_eps
+        hq, hk, hd = self.hq, self.hk, self.hd
+        if delta is None:
+            h = F.rmsnorm(x, l["ln1"], eps)
+        else:
+            h, x = F.rmsnorm(delta, l["ln1"], eps, residual=x)
+        qkv = l["qkv"](h)
+        qk = F.qknorm_rope(qkv, l["q_norm"], l["k_norm"], self.cos, self.sin, pos, hq, hk, hd, eps)
+        v = qkv[:, (hq + hk) * hd:]
+        o = attn_fn(li, qk[:, : hq * hd], qk[:, hq * hd:], v)
+        a = self._allreduce(l["wo"](o))
+        h2, x = F.rmsnorm(a, l["ln2"], eps, residual=x)
+        m = self._allreduce(l["down"](F.swiglu(l["gate_up"](h2))))
+        return x, m
+
+    def _head(self, x, delta, greedy: bool):
+        h, _ = F.rmsnorm(delta, self.norm, self.cfg.rms_eps, residual=x)
+        logits = self.head(h)
+        if greedy:
+            return F.argmax_rows(logits), None
+        k = min(self.topk_capacity, logits.shape[-1])
+        vals, idx = torch.topk(logits.float(), k, dim=-1)
+        return idx[:, 0].to(torch.int32), (idx, vals)
+
+    # ------------------------------------------------------------------ PagedDecoder interface
+    @torch.no_grad()
+    def prefill_chunk(self, tokens: np.ndarray, start: int, block_table: np.ndarray, last: bool,
+                      greedy: bool = True):
+        """Process prompt positions [start, start+n) of one sequence.  Returns (first token, top-k
+        candidates) when ``last`` (else (None, None))."""
+        n = int(tokens.shape[0])
+        dev = self.device
+        tok = torch.from_numpy(np.ascontiguousarray(tokens)).to(dev)
+        bt = torch.from_numpy(np.ascontiguousarray(block_table)).to(dev)
+        pos = torch.arange(start, start + n, device=dev, dtype=torch.int32)
+        slots = self._slots(bt[None, :].expand(n, -1), pos)
+        S = start + n
+        hq, hk, hd = self.hq, self.hk, self.hd
+
+        def attn(li, q, k, v):
+            self._append_kv(li, k, v, slots)
+            if start == 0:
+                return flash_attention(q, k, v, 1, n, hq, hk, hd, causal=True)
+            kk, vv = self._gather_kv(li, bt, S)
+            return flash_attention(q, kk, vv, 1, n, hq, hk, hd, causal=True, S=S)
+
+        x = F.embedding(tok, self.tok).reshape(n, -1)
+        delta = None
+        for li in range(len(self.layers)):
+            x, delta = self._layer(li, x, delta, pos, attn)
+        self.steps += 1
+        if not last:
+            return None, None
+        t, tk = self._head(x[-1:], delta[-1:], greedy)
+        first = int(t.cpu()[0])
+        if tk is None:
+            return first, None
+        idx, vals = tk[0].cpu()[0].tolist(), tk[1].cpu()[0].tolist()
+        return first, list(zip(idx, vals))
+
+    @torch.no_grad()
+    def decode(self, tokens: np.ndarray, positions: np.ndarray, block_tables: np.ndarray,
+               window: int = 1, greedy: bool = True):
+        """One batched decode call: ``window`` on-device greedy steps (window > 1 requires greedy).
+        Returns (tokens [B][window], per-row top-k candidate lists or None)."""
+        dev = self.device
+        B = int(tokens.shape[0])
+        tok = torch.from_numpy(np.ascontiguousarray(tokens)).to(dev)
+        pos = torch.from_numpy(np.ascontiguousarray(positions)).to(dev)
+        bts = torch.from_numpy(np.ascontiguousarray(block_tables)).to(dev)
+        outs = []
+        topks = None
+        for w in range(window):
+            slots = self._slots(bts, pos)
+            seqlens = (pos + 1).to(torch.int32)
+
+            def attn(li, q, k, v):
+                self._append_kv(li, k, v, slots)
+                return self._paged_attention(li, q, bts, seqlens)
+
+            x = F.embedding(tok, self.tok).reshape(B, -1)
+            delta = None
+            for li in range(len(self.layers)):
+                x, delta = self._layer(li, x, delta, pos, attn)
+            t, tk = self._head(x, delta, greedy or window > 1)
+            outs.append(t)
+            if tk is not None:
+                topks = tk
+            tok = t
+            pos = pos + 1
+            self.steps += 1
+        out = torch.stack(outs, dim=1).cpu().numpy()
+        cand = None
+        if topks is not None:
+            idx, vals = topks[0].cpu().tolist(), topks[1].cpu().tolist()
+            cand = [list(zip(i, v)) for i, v in zip(idx, vals)]
+        return [row.tolist() for row in out], cand
+
+    # ------------------------------------------------------------------ convenience
+    @torch.no_grad()
+    def logits_all(self, tokens: List[int]) -> torch.Tensor:
+        """Contiguous (non-paged) forward over a whole prompt: [T, vocab] — the oracle the paged
+        path is checked against."""
+        n = len(tokens)
+        dev = self.device
+        tok = torch.tensor(tokens, device=dev, dtype=torch.int32)
+        pos = torch.arange(n, device=dev, dtype=torch.int32)
+        hq, hk, hd = self.hq, self.hk, self.hd
+
+        def attn(li, q, k, v):
+            return flash_attention(q, k, v, 1, n, hq, hk, hd, causal=True)
+
+        x = F.embedding(tok, self.tok).reshape(n, -1)
+        delta = None
+        for li in range(len(self.layers)):
+            x, delta = self._layer(li, x, delta, pos, attn)
+        h, _ = F.rmsnorm(delta, self.norm, self.cfg.rms_eps, residual=x)
+        return self.head(h).float()

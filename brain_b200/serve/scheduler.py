@@ -1,0 +1,256 @@
+"""Continuous-batching scheduler (native core in csrc/runtime/serving.cpp) driving a paged decoder.
+
+Per ``step``: admit waiting requests FIFO while their whole budget (prompt + max_new) fits the free
+KV blocks and the prefill-token budget (2 x max_prefill, always at least one request) remains,
+evicting LRU prefix-cache blocks first; run the planned prefill chunks (first token sampled when a
+prompt completes); run ONE batched decode over every running sequence (a window of k on-device
+greedy steps when the wait queue is empty and all are greedy); reap finished sequences (EOS is not
+appended; blocks are released, prompt blocks stay in the prefix cache).
+Reference: crates/model/src/serve.rs:374-776 (Scheduler), :262-307 (admission policies)."""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Protocol, Sequence, Tuple
+
+import numpy as np
+
+from .. import _host
+from ..data.rng import Rng
+from .sampling import SampleParams, sample_from_topk
+
+c = ctypes
+_host.register({
+    "bbh_sched_new": (c.c_void_p, [c.c_uint32] * 6 + [c.c_int64, c.c_uint32, c.c_int, c.c_double, c.c_int]),
+    "bbh_sched_free": (None, [c.c_void_p]),
+    "bbh_sched_submit": (c.c_int64, [c.c_void_p, c.c_void_p, c.c_uint32, c.c_uint32, c.c_float,
+                                     c.c_uint32, c.c_float, c.c_uint64, c.c_int]),
+    "bbh_sched_last_need": (c.c_uint64, [c.c_void_p]),
+    "bbh_sched_last_bad_token": (c.c_uint64, [c.c_void_p]),
+    "bbh_sched_cancel": (c.c_int, [c.c_void_p, c.c_int64]),
+    "bbh_sched_idle": (c.c_int, [c.c_void_p]),
+    "bbh_sched_plan": (None, [c.c_void_p, c.POINTER(c.c_uint32), c.POINTER(c.c_uint32), c.POINTER(c.c_uint32)]),
+    "bbh_sched_prefill_item": (None, [c.c_void_p, c.c_uint32, c.POINTER(c.c_int64), c.POINTER(c.c_uint32),
+                                      c.POINTER(c.c_uint32), c.POINTER(c.c_int)]),
+    "bbh_sched_decode_batch": (None, [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_uint32]),
+    "bbh_sched_commit_prefill": (None, [c.c_void_p, c.c_int64, c.c_uint32, c.c_int, c.c_uint32]),
+    "bbh_sched_commit_decode": (None, [c.c_void_p, c.c_void_p, c.c_uint32, c.c_uint32]),
+    "bbh_sched_seq_info": (c.c_int, [c.c_void_p, c.c_int64, c.POINTER(c.c_int), c.POINTER(c.c_int),
+                                     c.POINTER(c.c_uint32), c.POINTER(c.c_uint32), c.POINTER(c.c_uint32),
+                                     c.POINTER(c.c_uint32), c.POINTER(c.c_float), c.POINTER(c.c_uint32),
+                                     c.POINTER(c.c_float), c.POINTER(c.c_uint64)]),
+    "bbh_sched_seq_output": (None, [c.c_void_p, c.c_int64, c.c_void_p]),
+    "bbh_sched_seq_prompt": (None, [c.c_void_p, c.c_int64, c.c_void_p]),
+    "bbh_sched_seq_table": (c.c_uint32, [c.c_void_p, c.c_int64, c.c_void_p, c.c_uint32]),
+    "bbh_sched_forget": (None, [c.c_void_p, c.c_int64]),
+    "bbh_sched_set_service_ms": (None, [c.c_void_p, c.c_double]),
+    "bbh_sched_stats": (None, [c.c_void_p, c.c_void_p]),
+})
+
+WAITING, RUNNING, FINISHED, CANCELLED = 0, 1, 2, 3
+FINISH_NAMES = {0: None, 1: "stop", 2: "length"}
+
+
+class RejectReason(Exception):
+    """Raised by ``submit``; ``kind`` is one of exceeds_capacity / invalid_token / policy_rejected /
+    empty_prompt.  The message of ``exceeds_capacity`` carries the numbers the HTTP layer maps to
+    ``context_length_exceeded``."""
+
+    def __init__(self, kind: str, msg: str):
+        super().__init__(msg)
+        self.kind = kind
+
+
+class PagedDecoder(Protocol):
+    """What the scheduler needs from a model engine."""
+
+    vocab: int
+    block_size: int
+    num_blocks: int
+    max_prefill_tokens: int
+    max_seq_len: int
+    topk_capacity: int
+
+    def prefill_chunk(self, tokens: np.ndarray, start: int, block_table: np.ndarray, last: bool,
+                      greedy: bool): ...
+    def decode(self, tokens: np.ndarray, positions: np.ndarray, block_tables: np.ndarray,
+               window: int, greedy: bool): ...
+
+
+@dataclass
+class StepReport:
+    admitted: int = 0
+    prefill_tokens: int = 0
+    decoded: int = 0
+    window: int = 1
+    finished: List[int] = field(default_factory=list)
+    new_tokens: Dict[int, List[int]] = field(default_factory=dict)
+
+
+@dataclass
+class SeqInfo:
+    state: int
+    finish: Optional[str]
+    n_prompt: int
+    n_out: int
+    prefilled: int
+    prefix_hit: int
+    params: SampleParams
+    seed: int
+
+
+class Scheduler:
+    def __init__(self, decoder: PagedDecoder, max_batch: int = 16, eos: Optional[int] = None,
+                 window: int = 4, policy: str = "unbounded_queue", policy_arg: float = 0.0,
+                 prefix_cache: bool = True):
+        self.dec = decoder
+        pol = {"unbounded_queue": 0, "max_queue_depth": 1, "deadline_aware": 2}[policy]
+        self.max_blocks = (decoder.max_seq_len + decoder.block_size - 1) // decoder.block_size
+        self._h = _host.lib().bbh_sched_new(
+            decoder.num_blocks, decoder.block_size, max_batch, decoder.max_prefill_tokens,
+            decoder.max_seq_len, decoder.vocab, -1 if eos is None else int(eos), window, pol,
+            float(policy_arg), int(prefix_cache))
+        if not self._h:
+            raise ValueError("invalid scheduler configuration")
+        self._rngs: Dict[int, Rng] = {}
+        self.max_batch = max_batch
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            _host.lib().bbh_sched_free(self._h)
+            self._h = None
+
+    # ------------------------------------------------------------------ queue
+    def submit(self, prompt: Sequence[int], max_new: int, params: Optional[SampleParams] = None,
+               seed: int = 0, ignore_eos: bool = False) -> int:
+        params = params or SampleParams.greedy()
+        p = np.ascontiguousarray(np.asarray(prompt, dtype=np.int64))
+        if p.size and (p.min() < 0 or p.max() >= self.dec.vocab):
+            bad = int(p[(p < 0) | (p >= self.dec.vocab)][0])
+            raise RejectReason("invalid_token", f"token {bad} is outside the vocabulary of {self.dec.vocab}")
+        p = p.astype(np.uint32)
+        rid = int(_host.lib().bbh_sched_submit(self._h, p.ctypes.data, p.size, int(max_new),
+                                               float(params.temp), int(params.top_k),
+                                               float(params.top_p), int(seed), int(ignore_eos)))
+        if rid == -1:
+            need = int(_host.lib().bbh_sched_last_need(self._h))
+            raise RejectReason("exceeds_capacity",
+                               f"needs {need} tokens, engine capacity is {self.dec.max_seq_len}")
+        if rid == -2:
+            bad = int(_host.lib().bbh_sched_last_bad_token(self._h))
+            raise RejectReason("invalid_token", f"token {bad} is outside the vocabulary of {self.dec.vocab}")
+        if rid == -3:
+            raise RejectReason("policy_rejected", "admission policy rejected the request")
+        if rid == -4:
+            raise RejectReason("empty_prompt", "empty prompt")
+        self._rngs[rid] = Rng(seed)
+        return rid
+
+    def cancel(self, rid: int) -> List[int]:
+        toks = self.tokens_of(rid)
+        _host.lib().bbh_sched_cancel(self._h, rid)
+        return toks
+
+    def is_idle(self) -> bool:
+        return bool(_host.lib().bbh_sched_idle(self._h))
+
+    def info(self, rid: int) -> SeqInfo:
+        st, fin = c.c_int(), c.c_int()
+        a, b, d, e, k = (c.c_uint32() for _ in range(5))
+        t, p = c.c_float(), c.c_float()
+        s = c.c_uint64()
+        if _host.lib().bbh_sched_seq_info(self._h, rid, c.byref(st), c.byref(fin), c.byref(a), c.byref(b),
+                                          c.byref(d), c.byref(e), c.byref(t), c.byref(k), c.byref(p),
+                                          c.byref(s)) != 0:
+            raise KeyError(rid)
+        return SeqInfo(st.value, FINISH_NAMES[fin.value], a.value, b.value, d.value, e.value,
+                       SampleParams(t.value, k.value, p.value), s.value)
+
+    def tokens_of(self, rid: int) -> List[int]:
+        n = self.info(rid).n_out
+        out = np.empty(max(n, 1), dtype=np.uint32)
+        _host.lib().bbh_sched_seq_output(self._h, rid, out.ctypes.data)
+        return out[:n].tolist()
+
+    def forget(self, rid: int) -> None:
+        _host.lib().bbh_sched_forget(self._h, rid)
+        self._rngs.pop(rid, None)
+
+    def stats(self) -> Dict[str, int]:
+        out = np.zeros(12, dtype=np.uint64)
+        _host.lib().bbh_sched_stats(self._h, out.ctypes.data)
+        names = ["free_blocks", "num_blocks", "waiting", "running", "steps", "submitted", "finished",
+                 "cancelled", "generated", "kv_prefix_hit_tokens", "kv_prefix_lookup_tokens",
+                 "prefix_entries"]
+        return {n: int(v) for n, v in zip(names, out)}
+
+    # ------------------------------------------------------------------ step
+    def _pick(self, rid: int, greedy_tok, topk) -> int:
+        info = self.info(rid)
+        if info.params.is_greedy() or topk is None:
+            return int(greedy_tok)
+        return sample_from_topk(topk, info.params, self._rngs[rid])
+
+    def step(self) -> StepReport:
+        lib = _host.lib()
+        npf, nd, win = c.c_uint32(), c.c_uint32(), c.c_uint32()
+        lib.bbh_sched_plan(self._h, c.byref(npf), c.byref(nd), c.byref(win))
+        rep = StepReport(window=win.value)
+        before: Dict[int, int] = {}
+        # ---- prefill chunks
+        for i in range(npf.value):
+            rid, s, e, last = c.c_int64(), c.c_uint32(), c.c_uint32(), c.c_int()
+            lib.bbh_sched_prefill_item(self._h, i, c.byref(rid), c.byref(s), c.byref(e), c.byref(last))
+            rid_v = rid.value
+            info = self.info(rid_v)
+            prompt = np.empty(info.n_prompt, dtype=np.uint32)
+            lib.bbh_sched_seq_prompt(self._h, rid_v, prompt.ctypes.data)
+            bt = np.full(self.max_blocks, -1, dtype=np.int32)
+            lib.bbh_sched_seq_table(self._h, rid_v, bt.ctypes.data, self.max_blocks)
+            before.setdefault(rid_v, info.n_out)
+            greedy = info.params.is_greedy()
+            tok, topk = self.dec.prefill_chunk(prompt[s.value:e.value].astype(np.int32), s.value, bt,
+                                               bool(last.value), greedy)
+            if s.value == info.prefix_hit:
+                rep.admitted += 1
+            rep.prefill_tokens += e.value - s.value
+            if last.value:
+                lib.bbh_sched_commit_prefill(self._h, rid_v, e.value, 1, self._pick(rid_v, tok, topk))
+            else:
+                lib.bbh_sched_commit_prefill(self._h, rid_v, e.value, 0, 0)
+        # ---- one batched decode
+        n = nd.value
+        if n:
+            ids = np.empty(n, dtype=np.int64)
+            toks = np.empty(n, dtype=np.int32)
+            pos = np.empty(n, dtype=np.int32)
+            bts = np.empty((n, self.max_blocks), dtype=np.int32)
+            lib.bbh_sched_decode_batch(self._h, ids.ctypes.data, toks.ctypes.data, pos.ctypes.data,
+                                       bts.ctypes.data, self.max_blocks)
+            infos = [self.info(int(r)) for r in ids]
+            for r, inf in zip(ids, infos):
+                before.setdefault(int(r), inf.n_out)
+            all_greedy = all(i.params.is_greedy() for i in infos)
+            greedy_toks, topks = self.dec.decode(toks, pos, bts, win.value, all_greedy)
+            out = np.empty((n, win.value), dtype=np.uint32)
+            for i, r in enumerate(ids):
+                if all_greedy:
+                    out[i, :] = greedy_toks[i]
+                else:
+                    out[i, 0] = self._pick(int(r), greedy_toks[i][0], topks[i] if topks is not None else None)
+            lib.bbh_sched_commit_decode(self._h, out.ctypes.data, n, win.value)
+            rep.decoded = n
+        # ---- report
+        for rid_v, n0 in before.items():
+            info = self.info(rid_v)
+            if info.n_out > n0:
+                rep.new_tokens[rid_v] = self.tokens_of(rid_v)[n0:]
+            if info.state == FINISHED:
+                rep.finished.append(rid_v)
+        return rep
+
+    def run_until_idle(self, max_steps: int = 1 << 30) -> None:
+        steps = 0
+        while not self.is_idle() and steps < max_steps:
+            self.step()
+            steps += 1

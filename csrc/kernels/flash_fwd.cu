@@ -29,6 +29,7 @@ struct FaFwdArgs {
   float scale_log2;  // softmax scale * log2(e)
   int causal;
   int* err;
+  long long* timeline;  // optional [n_blocks][8] clock64 stamps of CTA (0,0,0) (profiling aid)
 };
 
 template <int HD>
@@ -70,6 +71,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  long long* tl = (args.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? args.timeline : nullptr;
   const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
   const int h = blockIdx.y, b = blockIdx.z;
   const int T = args.T, S = args.S;
@@ -148,6 +150,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           break;
         }
         tc_fence_after();
+        if (tl) tl[j * 8 + 7] = clock64();
         // S = Q K^T.  Issued after PV_{j-1}, so the tensor pipe's in-order execution guarantees
         // P_{j-1} (which aliases these columns) has been consumed.
 #pragma unroll
@@ -164,6 +167,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           break;
         }
         tc_fence_after();
+        if (tl) tl[j * 8 + 6] = clock64();
         // O += P V: A = packed bf16 P in TMEM (8 columns per 16-wide k-step), B = V MN-major
 #pragma unroll
         for (int t = 0; t < 8; ++t)
@@ -189,12 +193,15 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      const bool rec = tl && threadIdx.x == 64;
+      if (rec) tl[j * 8 + 0] = clock64();
       uint32_t r0[32], r1[32], r2[32], r3[32];
       tmem_ld32(tS, r0);
       tmem_ld32(tS + 32, r1);
       tmem_ld32(tS + 64, r2);
       tmem_ld32(tS + 96, r3);
       tmem_wait_ld();
+      if (rec) tl[j * 8 + 1] = clock64();
       const int kv0 = j * 128;
       const bool need_mask = (kv0 + 127 > kv_limit_row);
       const int lim = kv_limit_row - kv0;  // columns <= lim are visible
@@ -215,6 +222,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
       }
       mx *= args.scale_log2;
+      if (rec) tl[j * 8 + 2] = clock64();
       float m_new = m_ref;
       if (mx > m_ref + 8.f) m_new = mx;  // lazy: keep the old reference while p stays <= 2^8
       const float alpha =
@@ -236,6 +244,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           }
         }
       }
+      if (rec) tl[j * 8 + 3] = clock64();
       l *= alpha;
       m_ref = m_new;
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
@@ -269,11 +278,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         pk1[16 + (i >> 1)] = pack_bf16x2(d0, d1);  // kv columns  96..127 -> words 48..63
       }
       l += ls;
+      if (rec) tl[j * 8 + 4] = clock64();
       tmem_st32(tS, pk0);
       tmem_st32(tS + 32, pk1);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_ready);
+      if (rec) tl[j * 8 + 5] = clock64();
     }
     if (ok) {
       ok = mbar_wait(pv_done, (n_blocks - 1) & 1);
@@ -345,11 +356,25 @@ static int launch_fa_fwd(const void* q, int ldq, const void* k, int ldk, const v
 
 }  // namespace bb
 
+BB_API int bb_flash_fwd_timeline(const void*, int, const void*, int, const void*, int, void*, int,
+                                 float*, int, int, int, int, int, int, float, int, long long*, void*);
+
 // q: [B*T, ldq] (head h at columns h*hd), k/v: [B*S, ldk/ldv]; out: [B*T, ldo]; lse: [B, hq, T].
 // Requires ldo % 8 == 0 and 16-byte aligned bases.  hd in {64, 128}.
 BB_API int bb_flash_fwd(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
                         void* out, int ldo, float* lse, int B, int T, int S, int hq, int hk, int hd,
                         float scale, int causal, void* stream) {
+  return bb_flash_fwd_timeline(q, ldq, k, ldk, v, ldv, out, ldo, lse, B, T, S, hq, hk, hd, scale,
+                               causal, nullptr, stream);
+}
+
+// Same, with an optional device buffer of (T/128) x 8 clock64 stamps filled by the CTA of the last
+// query tile of head 0 / batch 0: per KV block [0] scores ready, [1] row in registers, [2] max
+// done, [3] O rescaled, [4] exponentials done, [5] P stored + signalled, [6] PV issued, [7] QK issued.
+BB_API int bb_flash_fwd_timeline(const void* q, int ldq, const void* k, int ldk, const void* v,
+                                 int ldv, void* out, int ldo, float* lse, int B, int T, int S,
+                                 int hq, int hk, int hd, float scale, int causal,
+                                 long long* timeline, void* stream) {
   using namespace bb;
   if (B <= 0 || T <= 0 || S < T || hq % hk) return BB_EARG;
   if ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) return BB_EARG;
@@ -365,6 +390,7 @@ BB_API int bb_flash_fwd(const void* q, int ldq, const void* k, int ldk, const vo
   a.scale_log2 = scale * 1.4426950408889634f;
   a.causal = causal;
   a.err = device_error_word();
+  a.timeline = timeline;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (hd == 128) return launch_fa_fwd<128>(q, ldq, k, ldk, v, ldv, a, s);
   if (hd == 64) return launch_fa_fwd<64>(q, ldq, k, ldk, v, ldv, a, s);

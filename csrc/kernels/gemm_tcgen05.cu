@@ -29,7 +29,22 @@ struct GemmArgs {
   int ldc;
   int a_mn, b_mn;
   int out_mode;  // 0 bf16 store, 1 fp32 store, 2 fp32 accumulate, 3 bf16 store of gelu(x) (tanh)
+  // Grouped (mixture-of-experts) GEMMs, one launch for all experts:
+  //  mode 1 "row-grouped": A rows are expert-sorted and padded so every 128-row tile belongs to one
+  //         expert; tile_group[tile_m] names it (-1 = unused tile, skipped); B holds the experts'
+  //         matrices stacked along its row (K-major) / k (MN-major) axis, b_group_rows apart.
+  //  mode 2 "k-grouped" (weight gradients): group g reduces over rows [group_offsets[g],
+  //         group_offsets[g+1]) (multiples of 128) of the MN-major A and B and writes
+  //         C + g * c_group_stride.  Empty groups are skipped (use with accumulate or zeroed C).
+  int group_mode;
+  const int* tile_group;
+  int b_group_rows;
+  const int* group_offsets;
+  int num_groups;
+  long c_group_stride;
   int* err;
+  long long* timeline;  // optional [tiles][8] clock64 stamps of CTA 0 (profiling aid)
+  int tma_store;        // 1: epilogue stages 128-byte-row slabs in smem and writes them with TMA
 };
 
 static constexpr int BM = 128;
@@ -42,7 +57,9 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int OUT_STAGE_BYTES = 128 * 128;  // one [128 rows][128 B] output slab
+  static constexpr int SMEM =
+      STAGES * STAGE_BYTES + 2 * OUT_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ float gelu_tanh(float x) {
@@ -53,7 +70,7 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 template <int BN, bool I8>
 __global__ void __launch_bounds__(256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const GemmArgs args) {
+            const __grid_constant__ CUtensorMap tmC, const GemmArgs args) {
   using Cfg = GemmCfg<BN>;
   constexpr int S = Cfg::STAGES;
   constexpr int BK = I8 ? 128 : 64;      // elements per k-block (128 bytes)
@@ -63,7 +80,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::STAGE_BYTES);
+  uint8_t* out_stage = smem + S * Cfg::STAGE_BYTES;  // 2 slabs, 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + 2 * Cfg::OUT_STAGE_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + S;
   uint64_t* tmem_full = bars + 2 * S;
@@ -75,8 +93,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int M = args.M, N = args.N, K = args.K;
   const int tiles_m = (M + BM - 1) / BM;
   const int tiles_n = (N + BN - 1) / BN;
-  const int ntiles = tiles_m * tiles_n;
-  const int nkb = (K + BK - 1) / BK;
+  const int ntiles = tiles_m * tiles_n * (args.group_mode == 2 ? args.num_groups : 1);
+  const int nkb_all = (K + BK - 1) / BK;
   constexpr int GROUP_M = 16;
 
   if (threadIdx.x == 0) {
@@ -103,13 +121,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto tile_coords = [&](int t, int& tm, int& tn) {
+  // tile index -> coordinates, group, and k-block range; returns false when the tile is skipped.
+  // Every role evaluates this identically, so their pipeline counters stay in step.
+  auto tile_info = [&](int t, int& tm, int& tn, int& grp, int& kb0, int& nkb) -> bool {
+    grp = 0;
+    kb0 = 0;
+    nkb = nkb_all;
+    if (args.group_mode == 2) {
+      const int per = tiles_m * tiles_n;
+      grp = t / per;
+      t -= grp * per;
+      const int r0 = args.group_offsets[grp], r1 = args.group_offsets[grp + 1];
+      kb0 = r0 / BK;
+      nkb = (r1 - r0) / BK;
+    }
     const int per_group = GROUP_M * tiles_n;
     const int g = t / per_group;
     const int first_m = g * GROUP_M;
     const int gsz = min(tiles_m - first_m, GROUP_M);
     tm = first_m + (t % per_group) % gsz;
     tn = (t % per_group) / gsz;
+    if (args.group_mode == 1) {
+      grp = args.tile_group[tm];
+      if (grp < 0) return false;
+    }
+    return nkb > 0;
   };
 
   if (warp == 0) {
@@ -121,9 +157,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t armed_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
-        int tm, tn;
-        tile_coords(t, tm, tn);
+        int tm, tn, grp, kb0, nkb;
+        if (!tile_info(t, tm, tn, grp, kb0, nkb)) continue;
         const int m0 = tm * BM, n0 = tn * BN;
+        const int b_off = args.group_mode == 1 ? grp * args.b_group_rows : 0;
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             set_error(args.err, ERR_WAIT_PRODUCER);
@@ -133,7 +170,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
           mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = (kb0 + kb) * BK;
           if (!args.a_mn) {
             tma_load_2d(sa, &tmA, &full[stage], k0, m0);
           } else {
@@ -142,11 +179,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               tma_load_2d(sa + c * (BK * 128), &tmA, &full[stage], m0 + c * 64, k0);
           }
           if (!args.b_mn) {
-            tma_load_2d(sb, &tmB, &full[stage], k0, n0);
+            tma_load_2d(sb, &tmB, &full[stage], k0, b_off + n0);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sb + c * (BK * 128), &tmB, &full[stage], n0 + c * 64, k0);
+              tma_load_2d(sb + c * (BK * 128), &tmB, &full[stage], n0 + c * 64, b_off + k0);
           }
           armed_stage = stage;
           armed_phase = phase;
@@ -175,9 +212,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x, ++it) {
+      for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+        int tm, tn, grp, kb0, nkb;
+        if (!tile_info(t, tm, tn, grp, kb0, nkb)) continue;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        ++it;
+        long long* tl = (args.timeline && blockIdx.x == 0 && it <= 16) ? args.timeline + (it - 1) * 16 : nullptr;
+        if (tl) tl[0] = clock64();
+        long long waited = 0;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
           set_error(args.err, ERR_WAIT_MMA_TMEM);
           ok = false;
@@ -186,12 +229,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < nkb; ++kb) {
+          const long long w0 = tl ? clock64() : 0;
+          if (kb == 0 && tl) tl[1] = w0;
           if (!mbar_wait(&full[stage], phase)) {
             set_error(args.err, ERR_WAIT_MMA_FULL);
             ok = false;
             break;
           }
           tc_fence_after();
+          if (tl) waited += clock64() - w0;
           const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
           const uint32_t sb = sa + Cfg::A_BYTES;
 #pragma unroll
@@ -210,15 +256,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         }
         if (ok) umma_commit(&tmem_full[acc]);
+        if (tl) {
+          tl[2] = waited;      // cycles spent waiting for TMA data in this tile
+          tl[3] = clock64();   // all MMAs of the tile issued
+        }
       }
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------ epilogue
     const int ew = warp & 3;  // TMEM lane quarter this warp may touch
     int it = 0;
-    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+    int out_slabs = 0;  // staged slabs issued so far (selects the staging buffer)
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+      int tm, tn, grp, kb0, nkb;
+      if (!tile_info(t, tm, tn, grp, kb0, nkb)) continue;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      ++it;
+      long long* tl = (args.timeline && blockIdx.x == 0 && it <= 16 && threadIdx.x == 128) ? args.timeline + (it - 1) * 16 : nullptr;
+      if (tl) tl[4] = clock64();
       bool ok = mbar_wait(&tmem_full[acc], acc_phase);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -226,13 +282,95 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         break;
       }
       tc_fence_after();
-      int tm, tn;
-      tile_coords(t, tm, tn);
+      if (tl) tl[5] = clock64();
+      const size_t c_off = args.group_mode == 2 ? (size_t)grp * args.c_group_stride : 0;
       const int row = tm * BM + ew * 32 + lane;
       const int n0 = tn * BN;
       const bool row_ok = row < M;
       const float sm = (I8 && row_ok && args.scale_m) ? args.scale_m[row] : 1.f;
       const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + acc * BN;
+      if (args.tma_store) {
+        // ---- staged epilogue: registers -> 128B-swizzled smem slab -> TMA store / reduce-add
+        const bool f32out = args.out_mode == 1 || args.out_mode == 2;
+        const int r_tile = ew * 32 + lane;  // row inside the tile
+        const int y0 = tm * BM + (args.group_mode == 2 ? grp * M : 0);
+        const bool issuer = threadIdx.x == 128;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= N) break;  // uniform across the CTA
+          uint32_t r[32];
+          __syncwarp();
+          if (tl && c == 2) tl[8] = clock64();
+          tmem_ld32(t_row + c * 32, r);
+          tmem_wait_ld();
+          if (tl && c == 2) tl[9] = clock64();
+          if (c == BN / 32 - 1 || col0 + 32 >= N) {  // last TMEM read of this tile: release it early
+            tc_fence_before();
+            mbar_arrive(&tmem_empty[acc]);
+          }
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = I8 ? (float)(int)r[j] : __uint_as_float(r[j]);
+            x *= args.alpha;
+            if (I8) {
+              x *= sm;
+              if (args.scale_n) x *= (col0 + j < N) ? args.scale_n[col0 + j] : 0.f;
+            }
+            if (args.bias && col0 + j < N) x += args.bias[col0 + j];
+            if (args.out_mode == 3) x = gelu_tanh(x);
+            v[j] = x;
+          }
+          const int slab = f32out ? c : (c >> 1);
+          const bool first_half = f32out || (c & 1) == 0;
+          const bool last_half = f32out || (c & 1) == 1 || col0 + 32 >= N;
+          uint8_t* buf = out_stage + (out_slabs & 1) * Cfg::OUT_STAGE_BYTES;
+          if (tl && c == 2) tl[10] = clock64();
+          if (first_half) {
+            // the store that last used this buffer (two slabs ago) must have finished reading it
+            if (issuer) tma_store_wait_read<1>();
+            if (tl && c == 2) tl[11] = clock64();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          }
+          if (tl && c == 2) tl[12] = clock64();
+          uint8_t* prow = buf + r_tile * 128;
+          if (f32out) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(prow + ((q ^ (r_tile & 7)) << 4)) =
+                  make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+          } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              *reinterpret_cast<uint4*>(prow + ((((c & 1) * 4 + q) ^ (r_tile & 7)) << 4)) = o;
+            }
+          }
+          if (tl && c == 3) tl[13] = clock64();
+          if (last_half) {
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (tl && c == 3) tl[14] = clock64();
+            if (issuer) {
+              const int x0 = n0 + slab * (f32out ? 32 : 64);
+              if (args.out_mode == 2)
+                tma_reduce_add_2d(&tmC, buf, x0, y0);
+              else
+                tma_store_2d(&tmC, buf, x0, y0);
+              tma_store_commit();
+            }
+            if (tl && c == 3) tl[15] = clock64();
+            ++out_slabs;
+          }
+        }
+        if (tl) tl[6] = clock64();
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -260,7 +398,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
           }
           __nv_bfloat16* crow =
-              reinterpret_cast<__nv_bfloat16*>(args.C) + (size_t)row * args.ldc + col0;
+              reinterpret_cast<__nv_bfloat16*>(args.C) + c_off + (size_t)row * args.ldc + col0;
           if (full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
             uint4* dst = reinterpret_cast<uint4*>(crow);
 #pragma unroll
@@ -276,7 +414,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int j = 0; j < 32 && col0 + j < N; ++j) crow[j] = __float2bfloat16(v[j]);
           }
         } else {
-          float* crow = reinterpret_cast<float*>(args.C) + (size_t)row * args.ldc + col0;
+          float* crow = reinterpret_cast<float*>(args.C) + c_off + (size_t)row * args.ldc + col0;
           const bool accum = args.out_mode == 2;
           if (full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
             float4* dst = reinterpret_cast<float4*>(crow);
@@ -299,9 +437,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       tc_fence_before();
       mbar_arrive(&tmem_empty[acc]);
+      if (tl) tl[6] = clock64();
     }
   }
 
+  if (args.tma_store && threadIdx.x == 128) tma_store_wait<0>();  // smem must outlive the reads
   tc_fence_before();
   __syncthreads();
   if (warp == 2) {
@@ -312,7 +452,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
 template <int BN, bool I8>
 static int launch_gemm(const void* A, const void* B, const GemmArgs& args, int lda, int ldb,
-                       cudaStream_t stream, int max_ctas) {
+                       cudaStream_t stream, int max_ctas, int b_rows_override = 0) {
   using Cfg = GemmCfg<BN>;
   constexpr int ES = I8 ? 1 : 2;
   constexpr int BK = I8 ? 128 : 64;
@@ -324,12 +464,35 @@ static int launch_gemm(const void* A, const void* B, const GemmArgs& args, int l
   else
     rc = make_tmap_2d(&tmA, dt, ES, A, args.M, args.K, (uint64_t)lda * ES, 64, BK);
   if (rc) return rc;
+  // outer extent of B's map: N rows (K-major) or K rows (MN-major); stacked experts override it
+  const uint64_t b_outer = b_rows_override > 0 ? (uint64_t)b_rows_override
+                                               : (uint64_t)(args.b_mn ? args.K : args.N);
   if (!args.b_mn)
-    rc = make_tmap_2d(&tmB, dt, ES, B, args.K, args.N, (uint64_t)ldb * ES, BK, BN);
+    rc = make_tmap_2d(&tmB, dt, ES, B, args.K, b_outer, (uint64_t)ldb * ES, BK, BN);
   else
-    rc = make_tmap_2d(&tmB, dt, ES, B, args.N, args.K, (uint64_t)ldb * ES, 64, BK);
+    rc = make_tmap_2d(&tmB, dt, ES, B, args.N, b_outer, (uint64_t)ldb * ES, 64, BK);
   if (rc) return rc;
 
+  // Output map for the staged epilogue: [rows][N] with 128-byte-wide boxes.  Needs a 16-byte
+  // aligned base and pitch; k-grouped outputs additionally need whole tiles per group.
+  CUtensorMap tmC;
+  GemmArgs largs = args;
+  {
+    const bool f32out = args.out_mode == 1 || args.out_mode == 2;
+    const int ces = f32out ? 4 : 2;
+    const bool aligned = (reinterpret_cast<uintptr_t>(args.C) & 15) == 0 &&
+                         ((uint64_t)args.ldc * ces) % 16 == 0;
+    const bool group_ok = args.group_mode != 2 || (args.M % BM == 0 &&
+                          args.c_group_stride == (long)args.M * args.ldc);
+    largs.tma_store = 0;
+    if (aligned && group_ok) {
+      const uint64_t rows = args.group_mode == 2 ? (uint64_t)args.M * args.num_groups : (uint64_t)args.M;
+      int rc2 = make_tmap_2d(&tmC, f32out ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                             ces, args.C, args.N, rows, (uint64_t)args.ldc * ces, f32out ? 32 : 64, BM);
+      if (rc2 == 0) largs.tma_store = 1;
+    }
+    if (!largs.tma_store) tmC = tmA;  // unused, but the parameter must be a valid object
+  }
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, I8>,
@@ -337,14 +500,21 @@ static int launch_gemm(const void* A, const void* B, const GemmArgs& args, int l
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  const int tiles = ((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN);
-  int grid = tiles < sm_count() ? tiles : sm_count();
+  const long tiles = (long)((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN) *
+                     (args.group_mode == 2 ? args.num_groups : 1);
+  int grid = tiles < sm_count() ? (int)tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  gemm_kernel<BN, I8><<<grid, 256, Cfg::SMEM, stream>>>(tmA, tmB, args);
+  gemm_kernel<BN, I8><<<grid, 256, Cfg::SMEM, stream>>>(tmA, tmB, tmC, largs);
   return (int)cudaGetLastError();
 }
 
 }  // namespace bb
+
+static long long* g_gemm_timeline = nullptr;
+// Profiling aid: when set, CTA 0 of the next bf16 GEMMs writes per-tile clock64 stamps
+// ([0] tile start, [1] first TMA wait, [2] cycles waiting on TMA, [3] MMAs issued, [4] epilogue
+// waits, [5] accumulator ready, [6] accumulator released) for its first 16 tiles.
+BB_API void bb_gemm_set_timeline(long long* buf) { g_gemm_timeline = buf; }
 
 // C ABI ------------------------------------------------------------------------------------------
 // bf16 GEMM.  a_mn/b_mn: 0 = operand stored [rows][K] (K contiguous), 1 = stored [K][rows].
@@ -368,6 +538,7 @@ BB_API int bb_gemm_bf16(const void* A, const void* B, void* C, const float* bias
   a.b_mn = b_mn;
   a.out_mode = out_mode;
   a.err = device_error_word();
+  a.timeline = g_gemm_timeline;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (bn == 0) {
     const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
@@ -412,6 +583,52 @@ BB_API int bb_gemm_i8(const void* A, const void* B, void* C, const float* scale_
     case 256: return launch_gemm<256, true>(A, B, a, lda, ldb, s, max_ctas);
     case 128: return launch_gemm<128, true>(A, B, a, lda, ldb, s, max_ctas);
     case 64: return launch_gemm<64, true>(A, B, a, lda, ldb, s, max_ctas);
+    default: return BB_EARG;
+  }
+}
+
+// Grouped bf16 GEMM for mixture-of-experts layers (one launch covers every expert).
+//  mode 1: C[M,N] = A[M,K] . B_g^T per 128-row tile, g = tile_group[tile] (-1 skips the tile).
+//          b_mn = 0: B is [G*b_group_rows, K] (expert g's [N,K] matrix at row g*b_group_rows);
+//          b_mn = 1: B is [G*b_group_rows, N] (expert g's [K,N] matrix at row g*b_group_rows).
+//  mode 2: for g < num_groups: C_g[M,N] (op)= A[rows_g, M]^T . B[rows_g, N] with
+//          rows_g = [group_offsets[g], group_offsets[g+1]); C_g = C + g*c_group_stride.
+//          (a_mn = b_mn = 1 implied.)  K = total rows of A/B.
+BB_API int bb_gemm_bf16_grouped(const void* A, const void* B, void* C, int M, int N, int K, int lda,
+                                int ldb, int ldc, int b_mn, int out_mode, int group_mode,
+                                const int* tile_group, int b_group_rows, int b_total_rows,
+                                const int* group_offsets, int num_groups, long c_group_stride,
+                                int bn, void* stream) {
+  using namespace bb;
+  if (M <= 0 || N <= 0 || K <= 0) return BB_EARG;
+  if (group_mode != 1 && group_mode != 2) return BB_EARG;
+  GemmArgs a{};
+  a.C = C;
+  a.alpha = 1.f;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.ldc = ldc;
+  a.a_mn = group_mode == 2 ? 1 : 0;
+  a.b_mn = group_mode == 2 ? 1 : b_mn;
+  a.out_mode = out_mode;
+  a.group_mode = group_mode;
+  a.tile_group = tile_group;
+  a.b_group_rows = b_group_rows;
+  a.group_offsets = group_offsets;
+  a.num_groups = num_groups;
+  a.c_group_stride = c_group_stride;
+  a.err = device_error_word();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn == 0) bn = (N >= 256) ? 256 : (N >= 128 ? 128 : 64);
+  // the B tensor map must span every expert: describe it with its true row count
+  GemmArgs amap = a;
+  (void)amap;
+  const void* Bp = B;
+  switch (bn) {
+    case 256: return launch_gemm<256, false>(A, Bp, a, lda, ldb, s, 0, b_total_rows);
+    case 128: return launch_gemm<128, false>(A, Bp, a, lda, ldb, s, 0, b_total_rows);
+    case 64: return launch_gemm<64, false>(A, Bp, a, lda, ldb, s, 0, b_total_rows);
     default: return BB_EARG;
   }
 }

@@ -1,0 +1,216 @@
+"""Serving stack on CPU: native paged-KV bookkeeping, scheduler semantics with a deterministic
+fake decoder, and the Qwen engine (paged == contiguous, batched == per-sequence, chunked prefill ==
+whole, warm prefix-cache prefill == cold, cancel reclaims blocks)."""
+import numpy as np
+import pytest
+import torch
+
+from brain_b200.data.rng import Rng
+from brain_b200.serve.paged import BlockAllocator, BlockTable, PrefixCache
+from brain_b200.serve.sampling import SampleParams, sample_from_topk
+from brain_b200.serve.scheduler import FINISHED, RejectReason, Scheduler
+
+
+def test_allocator_and_table():
+    a = BlockAllocator(4, 4)
+    t = BlockTable()
+    for i in range(6):
+        b, o = t.append(a)
+        assert o == i % 4
+    assert len(t) == 6 and t.blocks() == [0, 1] and a.free_blocks() == 2
+    assert t.reserve(3, a) == 6 and len(t) == 9 and len(t.blocks()) == 3
+    t.truncate(5, a)
+    assert len(t.blocks()) == 2 and a.free_blocks() == 2
+    f = t.fork(a)
+    assert a.refcount(1) == 2
+    old, new = f.unshare_tail(a)
+    assert old == 1 and new != 1 and a.refcount(1) == 1
+    t.release(a)
+    f.release(a)
+    assert a.free_blocks() == 4
+    with pytest.raises(RuntimeError):
+        a.decref(0)
+    t2 = BlockTable()
+    for _ in range(16):
+        t2.append(a)
+    with pytest.raises(MemoryError):
+        t2.append(a)
+
+
+def test_prefix_cache_lru():
+    a = BlockAllocator(8, 2)
+    pc = PrefixCache()
+    t = BlockTable()
+    prompt = [1, 2, 3, 4, 5, 6, 7]
+    t.reserve(len(prompt), a)
+    pc.insert_chain(prompt, t.blocks(), 0, a)
+    assert len(pc) == 3
+    assert pc.lookup(prompt, 2, 6) == t.blocks()[:3]
+    assert pc.lookup(prompt, 2, 4) == t.blocks()[:2]
+    assert pc.lookup([1, 2, 9, 9], 2, 4) == t.blocks()[:1]
+    assert pc.evict(2, a) == 0          # still referenced by the sequence
+    blocks = t.blocks()
+    t.release(a)
+    assert a.free_blocks() == 8 - 3      # cache keeps the three full blocks
+    pc.lookup(prompt[:2], 2, 2)          # touch the first block: most recently used
+    assert pc.evict(1, a) == 1 and a.refcount(blocks[0]) == 1
+
+
+def test_sample_from_topk():
+    cands = [(7, 3.0), (2, 2.0), (9, 0.5)]
+    assert sample_from_topk(cands, SampleParams.greedy(), Rng(0)) == 7
+    seen = {sample_from_topk(cands, SampleParams(1.0, 2, 1.0), Rng(s)) for s in range(50)}
+    assert seen == {7, 2}
+    assert {sample_from_topk(cands, SampleParams(1.0, 0, 0.1), Rng(s)) for s in range(20)} == {7}
+
+
+class FakeDecoder:
+    """Deterministic token function: next = (last + position) % vocab."""
+    vocab, block_size, num_blocks = 50, 4, 32
+    max_prefill_tokens, max_seq_len, topk_capacity = 8, 64, 8
+
+    def __init__(self):
+        self.prefill_calls = []
+        self.decode_calls = []
+
+    def prefill_chunk(self, tokens, start, block_table, last, greedy):
+        self.prefill_calls.append((len(tokens), start, last))
+        if not last:
+            return None, None
+        t = int(tokens[-1] + start + len(tokens)) % self.vocab
+        return t, [(t, 1.0), ((t + 1) % self.vocab, 0.5)]
+
+    def decode(self, tokens, positions, block_tables, window, greedy):
+        self.decode_calls.append((len(tokens), window))
+        out = []
+        for t, p in zip(tokens, positions):
+            row, cur = [], int(t)
+            for w in range(window):
+                cur = (cur + int(p) + w + 1) % self.vocab
+                row.append(cur)
+            out.append(row)
+        cand = None if greedy else [[(r[0], 1.0), ((r[0] + 1) % self.vocab, 0.1)] for r in out]
+        return out, cand
+
+
+def expected_stream(prompt, n):
+    toks, cur, pos = [], prompt[-1], len(prompt)
+    for _ in range(n):
+        cur = (cur + pos) % 50
+        toks.append(cur)
+        pos += 1
+    return toks
+
+
+def test_scheduler_continuous_batching():
+    dec = FakeDecoder()
+    s = Scheduler(dec, max_batch=4, window=4)
+    a = s.submit([1, 2, 3], 6)
+    b = s.submit(list(range(20)), 5)     # needs chunked prefill (max_prefill 8)
+    s.run_until_idle()
+    assert s.tokens_of(a) == expected_stream([1, 2, 3], 6)
+    assert s.tokens_of(b) == expected_stream(list(range(20)), 5)
+    assert s.info(a).state == FINISHED and s.info(a).finish == "length"
+    assert any(n == 8 and not last for n, _, last in dec.prefill_calls)   # a non-final chunk happened
+    assert any(w > 1 for _, w in dec.decode_calls)                        # window decode was used
+    st = s.stats()
+    assert st["free_blocks"] + st["prefix_entries"] == st["num_blocks"]
+
+
+def test_scheduler_rejects_and_cancel_and_eos():
+    dec = FakeDecoder()
+    s = Scheduler(dec, max_batch=2, eos=7, window=1)
+    with pytest.raises(RejectReason) as e:
+        s.submit([1] * 60, 10)
+    assert e.value.kind == "exceeds_capacity" and "needs 70 tokens, engine capacity is 64" in str(e.value)
+    with pytest.raises(RejectReason) as e:
+        s.submit([99], 4)
+    assert e.value.kind == "invalid_token"
+    with pytest.raises(RejectReason):
+        s.submit([], 4)
+    free0 = s.stats()["free_blocks"]
+    r = s.submit([3, 4], 30)
+    s.step()
+    s.step()
+    got = s.cancel(r)
+    assert len(got) >= 1 and s.stats()["free_blocks"] == free0
+    # EOS stops the stream and is not appended: prompt [1, 4] -> first token (4 + 2) = 6, then 6+2=8 ...
+    r2 = s.submit([2, 5], 20)            # 5+2 = 7 = EOS immediately
+    s.run_until_idle()
+    assert s.tokens_of(r2) == [] and s.info(r2).finish == "stop"
+    q = Scheduler(FakeDecoder(), max_batch=1, policy="max_queue_depth", policy_arg=1)
+    q.submit([1], 2)
+    with pytest.raises(RejectReason) as e:
+        q.submit([1], 2)
+    assert e.value.kind == "policy_rejected"
+
+
+def test_scheduler_sampling_is_seeded():
+    outs = []
+    for _ in range(2):
+        s = Scheduler(FakeDecoder(), max_batch=2, window=1)
+        r = s.submit([5, 6, 7], 8, SampleParams(1.0, 2, 1.0), seed=42)
+        s.run_until_idle()
+        outs.append(s.tokens_of(r))
+    assert outs[0] == outs[1] and len(outs[0]) == 8
+
+
+# ---------------------------------------------------------------------------------------- engine
+def _tiny_engine(weights="bf16", **kw):
+    from brain_b200.models.config import QwenConfig
+    from brain_b200.models.qwen3 import Qwen3
+    from brain_b200.serve.engine import QwenEngine
+    cfg = QwenConfig(vocab=61, block_size=64, n_layers=2, d_model=32, n_heads=4, n_kv_heads=2,
+                     head_dim=8, d_ff=48)
+    torch.manual_seed(0)
+    m = Qwen3(cfg).init_weights(3)
+    with torch.no_grad():
+        for p in m.parameters():
+            p.mul_(4.0)   # make logits well separated so greedy choices are stable
+    return QwenEngine(m, block_size=4, num_blocks=64, max_seq_len=64, max_prefill=8, weights=weights, **kw), m
+
+
+def _greedy_reference(eng, prompt, n):
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(eng.logits_all(toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+def test_engine_paged_equals_contiguous_and_batched_equals_single():
+    eng, _ = _tiny_engine()
+    prompts = [[3, 9, 27, 11, 5], list(range(1, 20)), [7]]
+    want = [_greedy_reference(eng, p, 6) for p in prompts]
+    s = Scheduler(eng, max_batch=4, window=4)
+    ids = [s.submit(p, 6) for p in prompts]
+    s.run_until_idle()
+    assert [s.tokens_of(i) for i in ids] == want
+    # one at a time gives the same streams
+    eng2, _ = _tiny_engine()
+    for p, w in zip(prompts, want):
+        s2 = Scheduler(eng2, max_batch=1, window=1)
+        r = s2.submit(p, 6)
+        s2.run_until_idle()
+        assert s2.tokens_of(r) == w
+
+
+def test_engine_prefix_cache_warm_equals_cold():
+    eng, _ = _tiny_engine()
+    s = Scheduler(eng, max_batch=2, window=1)
+    prompt = list(range(2, 19))
+    a = s.submit(prompt, 5)
+    s.run_until_idle()
+    b = s.submit(prompt, 5)           # warm: adopts the cached full blocks
+    s.run_until_idle()
+    assert s.tokens_of(a) == s.tokens_of(b)
+    assert s.info(b).prefix_hit >= 12 and s.stats()["kv_prefix_hit_tokens"] >= 12
+
+
+def test_engine_int8_tracks_full_precision():
+    eng, _ = _tiny_engine()
+    eng8, _ = _tiny_engine("int8")
+    toks = list(range(3, 23))
+    a, b = eng.logits_all(toks), eng8.logits_all(toks)
+    rel = ((a - b).norm() / a.norm()).item()
+    assert rel < 0.08
+    assert eng8.weight_bytes() < 0.6 * eng.weight_bytes()
