@@ -295,45 +295,52 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int r_tile = ew * 32 + lane;  // row inside the tile
         const int y0 = tm * BM + (args.group_mode == 2 ? grp * M : 0);
         const bool issuer = threadIdx.x == 128;
+        const float alpha = args.alpha;
+        const float* __restrict__ bias = args.bias;
+        const float* __restrict__ scale_n = args.scale_n;
+        const bool do_gelu = args.out_mode == 3;
+        const bool plain_epilogue = bias == nullptr && !do_gelu;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           const int col0 = n0 + c * 32;
           if (col0 >= N) break;  // uniform across the CTA
           uint32_t r[32];
           __syncwarp();
-          if (tl && c == 2) tl[8] = clock64();
           tmem_ld32(t_row + c * 32, r);
           tmem_wait_ld();
-          if (tl && c == 2) tl[9] = clock64();
           if (c == BN / 32 - 1 || col0 + 32 >= N) {  // last TMEM read of this tile: release it early
             tc_fence_before();
             mbar_arrive(&tmem_empty[acc]);
           }
           float v[32];
+          if (!I8 && plain_epilogue) {
+            // hot path: nothing but the scale (the general path's per-element tests cost ~30
+            // cycles per element and made the epilogue the bottleneck of K ~ 1024 GEMMs)
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = I8 ? (float)(int)r[j] : __uint_as_float(r[j]);
-            x *= args.alpha;
-            if (I8) {
-              x *= sm;
-              if (args.scale_n) x *= (col0 + j < N) ? args.scale_n[col0 + j] : 0.f;
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float x = I8 ? (float)(int)r[j] : __uint_as_float(r[j]);
+              x *= alpha;
+              if (I8) {
+                x *= sm;
+                if (scale_n) x *= (col0 + j < N) ? scale_n[col0 + j] : 0.f;
+              }
+              if (bias && col0 + j < N) x += bias[col0 + j];
+              if (do_gelu) x = gelu_tanh(x);
+              v[j] = x;
             }
-            if (args.bias && col0 + j < N) x += args.bias[col0 + j];
-            if (args.out_mode == 3) x = gelu_tanh(x);
-            v[j] = x;
           }
           const int slab = f32out ? c : (c >> 1);
           const bool first_half = f32out || (c & 1) == 0;
           const bool last_half = f32out || (c & 1) == 1 || col0 + 32 >= N;
           uint8_t* buf = out_stage + (out_slabs & 1) * Cfg::OUT_STAGE_BYTES;
-          if (tl && c == 2) tl[10] = clock64();
           if (first_half) {
             // the store that last used this buffer (two slabs ago) must have finished reading it
             if (issuer) tma_store_wait_read<1>();
-            if (tl && c == 2) tl[11] = clock64();
             asm volatile("bar.sync 1, 128;" ::: "memory");
           }
-          if (tl && c == 2) tl[12] = clock64();
           uint8_t* prow = buf + r_tile * 128;
           if (f32out) {
 #pragma unroll
@@ -351,11 +358,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               *reinterpret_cast<uint4*>(prow + ((((c & 1) * 4 + q) ^ (r_tile & 7)) << 4)) = o;
             }
           }
-          if (tl && c == 3) tl[13] = clock64();
           if (last_half) {
             fence_proxy_async_smem();
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (tl && c == 3) tl[14] = clock64();
             if (issuer) {
               const int x0 = n0 + slab * (f32out ? 32 : 64);
               if (args.out_mode == 2)
@@ -364,7 +369,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 tma_store_2d(&tmC, buf, x0, y0);
               tma_store_commit();
             }
-            if (tl && c == 3) tl[15] = clock64();
             ++out_slabs;
           }
         }
