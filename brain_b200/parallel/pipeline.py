@@ -1,0 +1,116 @@
+"""Pipeline parallelism: contiguous layer stages, micro-batched, point-to-point activations.
+
+Each rank of the pipeline group holds one stage (a model built with ``layers=range(lo, hi)``,
+``first``/``last`` flags).  ``train_step`` runs the per-stage op list of the chosen schedule
+(``1f1b`` — warm-up forwards, then one-forward-one-backward, then drain — or ``gpipe``, the
+reference's all-forward-then-all-backward): forward receives the residual stream ``[mb*T, d]`` from
+the previous stage and sends its own on; backward receives the gradient of what it sent and sends
+the gradient of what it received.  Transfers are ``torch.distributed`` p2p (NCCL on GPUs, gloo on
+CPU ranks) issued asynchronously, so a stage computes while its sends drain.  Stage inputs are kept
+for the backward (no recompute).  With tied embeddings the first and last stage both hold
+``tok.weight`` and sum its gradient before the optimiser step.
+
+Reference: crates/model/src/shard.rs:355-652 (Pipeline, GPipe with recompute, fused host AdamW and
+tied-weight sum); the 1F1B schedule is new here."""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .plan import schedule as make_schedule
+
+
+class PipelineStage:
+    def __init__(self, model, stage: int, n_stages: int, prev_rank: Optional[int], next_rank: Optional[int],
+                 group=None, tied_group=None, schedule: str = "1f1b", act_dtype=None):
+        self.model, self.stage, self.n_stages = model, stage, n_stages
+        self.prev, self.next = prev_rank, next_rank
+        self.group, self.tied_group = group, tied_group
+        self.schedule = schedule
+        p = next(model.parameters())
+        self.device = p.device
+        self.act_dtype = act_dtype or p.dtype
+        self.d_model = model.cfg.d_model
+        self._pending: List = []
+
+    @property
+    def first(self):
+        return self.stage == 0
+
+    @property
+    def last(self):
+        return self.stage == self.n_stages - 1
+
+    def _recv(self, shape, src):
+        buf = torch.empty(shape, device=self.device, dtype=self.act_dtype)
+        dist.recv(buf, src=src, group=self.group)
+        return buf
+
+    def _send(self, t, dst):
+        self._pending.append((dist.isend(t.contiguous(), dst=dst, group=self.group), t))
+
+    def _drain(self):
+        for w, _ in self._pending:
+            w.wait()
+        self._pending.clear()
+
+    def forward_backward(self, micro_tokens: List[torch.Tensor], micro_targets: List[torch.Tensor],
+                         loss_scale: float):
+        """Run this stage's schedule over the micro-batches.  ``micro_tokens`` is needed on the first
+        stage (and for shapes everywhere), ``micro_targets`` on the last.  Returns the summed loss
+        on the last stage (None elsewhere)."""
+        n_micro = len(micro_tokens)
+        ops = make_schedule(self.schedule, self.stage, self.n_stages, n_micro)
+        stash = {}
+        total = None
+        for op in ops:
+            m = abs(op) - 1
+            B, T = micro_tokens[m].shape
+            if op > 0:
+                if self.first:
+                    x_in = None
+                    out = self.model.hidden(tokens=micro_tokens[m].to(self.device))
+                else:
+                    x_in = self._recv((B * T, self.d_model), self.prev).requires_grad_()
+                    out = self.model.hidden(x_in=x_in, B=B, T=T)
+                if self.last:
+                    from ..ops import functional as F
+                    loss = F.lm_head_ce(out, self.model.head_weight(),
+                                        micro_targets[m].to(self.device).reshape(-1), loss_scale,
+                                        self.model.ce_chunk_rows)
+                    stash[m] = (x_in, loss)
+                    total = loss.detach() if total is None else total + loss.detach()
+                else:
+                    self._send(out.detach(), self.next)
+                    stash[m] = (x_in, out)
+            else:
+                x_in, out = stash.pop(m)
+                if self.last:
+                    out.backward()
+                else:
+                    dout = self._recv(tuple(out.shape), self.next)
+                    out.backward(dout)
+                if not self.first:
+                    self._send(x_in.grad, self.prev)
+        self._drain()
+        return total
+
+    def sync_tied_embeddings(self):
+        """Sum the gradient of ``tok.weight`` between the first and last stage (tied head)."""
+        if self.tied_group is None or not self.model.cfg.tie_embeddings:
+            return
+        if not (self.first or self.last) or self.model.tok is None:
+            return
+        g = getattr(self.model.tok, "main_grad", None)
+        if g is None:
+            g = self.model.tok.grad
+        if g is not None:
+            dist.all_reduce(g, group=self.tied_group)
+
+
+def build_stage_model(model_cls, cfg, stage: int, n_stages: int, bounds: List[int]):
+    """Instantiate the stage's slice: layers [bounds[stage], bounds[stage+1])."""
+    return model_cls(cfg, layers=range(bounds[stage], bounds[stage + 1]), first=stage == 0,
+                     last=stage == n_stages - 1)

@@ -18,48 +18,15 @@
 // Replaces the reference's host-staged DP step (crates/model/src/parallel.rs:152-240) and the
 // per-tensor AdamW dispatches of crates/optim/src/lib.rs:170-217.
 #include "../common/host.hpp"
+#include "../common/peer.cuh"
 #include "../common/ptx.cuh"
 
 namespace bb {
-
-static constexpr int MAX_RANKS = 16;
-
-struct PeerPtrs {
-  void* p[MAX_RANKS];
-};
 
 // Signal area layout inside each rank's symmetric buffer (uint64 slots):
 //   [0, R)      ready[r]  : rank r's gradient bucket for step `e` is complete   (value = e)
 //   [R, 2R)     norm[r]   : (e << 32) | float bits of rank r's shard sum of squares
 //   [2R, 3R)    landed[r] : rank r has stored its weight shard for step e everywhere (value = e)
-__device__ __forceinline__ uint64_t ld_acquire_sys_u64(const uint64_t* p) {
-  uint64_t v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys_u64(uint64_t* p, uint64_t v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ float4 ld_volatile_f4(const float4* p) {
-  float4 v;
-  asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-
-// Wait until (*p >> shift) >= want.  Returns false on timeout.
-__device__ __forceinline__ bool wait_epoch(const uint64_t* p, uint32_t want, int shift,
-                                           long long limit) {
-  const long long t0 = clock64();
-  while ((uint32_t)(ld_acquire_sys_u64(p) >> shift) < want) {
-    if (clock64() - t0 > limit) return false;
-    __nanosleep(64);
-  }
-  return true;
-}
-
 struct DpReduceArgs {
   PeerPtrs grads;   // fp32 gradient bucket base of every rank
   PeerPtrs sig;     // signal area base of every rank

@@ -1,0 +1,140 @@
+// Small kernels around the fused tensor-parallel GEMMs:
+//   tp_sum_slots   y = sum_r recv[r] (+ residual): the reduction half of GEMM -> reduce-scatter, run
+//                  by the owner of the rows over the `world` partial slots its peers filled
+//   tp_allreduce   one-shot all-reduce for small serving activations: every rank publishes its
+//                  [rows, d] partial in symmetric memory, signals, waits (bounded) for its peers and
+//                  sums all partials in a fixed rank order (bit-identical on every rank)
+// Peer access is plain ld/st with system-scope release/acquire flags.
+#include "../common/host.hpp"
+#include "../common/peer.cuh"
+#include "../common/ptx.cuh"
+#include "../common/vec.cuh"
+
+namespace bb {
+
+__global__ void tp_sum_slots_kernel(const __nv_bfloat16* __restrict__ recv, int world,
+                                    long slot_elems, const __nv_bfloat16* __restrict__ residual,
+                                    __nv_bfloat16* __restrict__ y) {
+  const long nv = slot_elems >> 3;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nv;
+       i += (long)gridDim.x * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < world; ++r) {
+      float f[8];
+      unpack8(reinterpret_cast<const bf16x8*>(recv + (size_t)r * slot_elems)[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    if (residual) {
+      float f[8];
+      unpack8(reinterpret_cast<const bf16x8*>(residual)[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    reinterpret_cast<bf16x8*>(y)[i] = pack8(acc);
+  }
+}
+
+struct ArArgs {
+  PeerPtrs bufs;  // every rank's symmetric [n] bf16 staging buffer
+  PeerPtrs sig;   // every rank's uint64[world] flags
+  const __nv_bfloat16* x;
+  __nv_bfloat16* y;
+  long n;
+  int rank, world;
+  uint32_t epoch;
+  long long wait_limit;
+  int* err;
+  unsigned int* counter;
+};
+
+// Phase 1 (all blocks): copy x into my staging buffer.  The last block to finish publishes the
+// flag to all peers.  Phase 2: every block waits for all peers' flags, then sums.
+__global__ void __launch_bounds__(256) tp_allreduce_kernel(const ArArgs a) {
+  __shared__ int s_ok;
+  const long nv = a.n >> 3;
+  bf16x8* mine = reinterpret_cast<bf16x8*>(a.bufs.p[a.rank]);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nv;
+       i += (long)gridDim.x * blockDim.x)
+    mine[i] = reinterpret_cast<const bf16x8*>(a.x)[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s_ok = 1;
+    const unsigned int done = atomicAdd(a.counter, 1u);
+    if (done == gridDim.x - 1) {
+      *a.counter = 0u;
+      for (int r = 0; r < a.world; ++r)
+        st_release_sys_u64(reinterpret_cast<uint64_t*>(a.sig.p[r]) + a.rank, (uint64_t)a.epoch);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < a.world) {
+    const uint64_t* f = reinterpret_cast<const uint64_t*>(a.sig.p[a.rank]) + threadIdx.x;
+    if (!wait_epoch(f, a.epoch, 0, a.wait_limit)) {
+      set_error(a.err, ERR_WAIT_PEER);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nv;
+       i += (long)gridDim.x * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < a.world; ++r) {
+      const uint4 raw = ld_volatile_u4(reinterpret_cast<const uint4*>(a.bufs.p[r]) + i);
+      float f[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(&raw), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    reinterpret_cast<bf16x8*>(a.y)[i] = pack8(acc);
+  }
+}
+
+}  // namespace bb
+
+using namespace bb;
+
+// y[slot_elems] = sum over `world` consecutive slots of recv (+ residual)
+BB_API int bb_tp_sum_slots(const void* recv, int world, long slot_elems, const void* residual,
+                           void* y, void* stream) {
+  if (slot_elems % 8) return BB_EARG;
+  long blocks = ((slot_elems >> 3) + 255) / 256;
+  const long cap = (long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  tp_sum_slots_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)recv, world, slot_elems, (const __nv_bfloat16*)residual,
+      (__nv_bfloat16*)y);
+  return (int)cudaGetLastError();
+}
+
+// One-shot all-reduce of n bf16 values (n % 8 == 0).  buf_ptrs[r]: rank r's symmetric staging
+// buffer (>= n elements; two alternating buffers must be used for back-to-back calls so a fast
+// rank cannot overwrite data a slow peer is still reading); sig_ptrs[r]: uint64[world] flags;
+// counter: zeroed uint32 in local memory.  The grid is at most one wave.
+BB_API int bb_tp_allreduce(const uint64_t* buf_ptrs, const uint64_t* sig_ptrs, const void* x,
+                           void* y, long n, int rank, int world, unsigned int epoch,
+                           unsigned int* counter, double wait_seconds, void* stream) {
+  if (world < 1 || world > MAX_RANKS || n % 8) return BB_EARG;
+  ArArgs a{};
+  for (int r = 0; r < world; ++r) {
+    a.bufs.p[r] = reinterpret_cast<void*>(buf_ptrs[r]);
+    a.sig.p[r] = reinterpret_cast<void*>(sig_ptrs[r]);
+  }
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.y = static_cast<__nv_bfloat16*>(y);
+  a.n = n;
+  a.rank = rank;
+  a.world = world;
+  a.epoch = epoch;
+  a.wait_limit = (long long)(wait_seconds * 1.9e9);
+  a.err = device_error_word();
+  a.counter = counter;
+  long blocks = ((n >> 3) + 255) / 256;
+  if (blocks > sm_count()) blocks = sm_count();  // every block waits on peers: keep them co-resident
+  if (blocks < 1) blocks = 1;
+  tp_allreduce_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}

@@ -15,6 +15,7 @@
 // warp 2 = TMEM allocator, warps 4..7 = epilogue (TMEM -> registers -> global).
 // Two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
 #include "../common/host.hpp"
+#include "../common/peer.cuh"
 #include "../common/ptx.cuh"
 
 namespace bb {
@@ -45,6 +46,28 @@ struct GemmArgs {
   int* err;
   long long* timeline;  // optional [tiles][8] clock64 stamps of CTA 0 (profiling aid)
   int tma_store;        // 1: epilogue stages 128-byte-row slabs in smem and writes them with TMA
+  // Tensor-parallel fusion (sequence-parallel Megatron layout), rows split evenly over tp ranks:
+  //  mode 1 "all-gather -> GEMM": the first tp_copy_ctas CTAs only move data: they pull every
+  //         rank's [rows_per_rank, K] shard of A over NVLink (plain peer loads) into the local
+  //         [M, K] buffer that tmA maps and publish one flag per 128-row tile; the remaining CTAs
+  //         run the GEMM, local rows first, and their TMA producer waits (bounded) on the flag of
+  //         the tile row it is about to read.  Each remote row crosses NVLink exactly once.
+  //  mode 2 "GEMM -> reduce-scatter": the epilogue TMA-stores every output tile into slot
+  //         [tp_rank] of the receive buffer of the rank that owns those rows (tp_cmaps[dest]); the
+  //         last CTA to finish exchanges "landed" flags with all peers, so when the kernel ends
+  //         every rank holds all tp partials of its rows (summed by the consumer kernel).
+  int tp_mode;
+  int tp_rank, tp_world;
+  int rows_per_rank;
+  PeerPtrs tp_src;
+  void* tp_full;
+  int* tp_row_flags;
+  int tp_copy_ctas;
+  PeerPtrs tp_sig;
+  uint32_t tp_epoch;
+  const CUtensorMap* tp_cmaps;
+  unsigned int* tp_counter;
+  long long tp_wait_limit;
 };
 
 static constexpr int BM = 128;
@@ -145,8 +168,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       grp = args.tile_group[tm];
       if (grp < 0) return false;
     }
+    if (args.tp_mode) {  // start with this rank's own rows (mode 1) / the next rank's rows (mode 2)
+      const int per_rank = args.rows_per_rank / BM;
+      tm = (tm + (args.tp_rank + (args.tp_mode == 2 ? 1 : 0)) * per_rank) % tiles_m;
+    }
     return nkb > 0;
   };
+  const int n_copy = args.tp_mode == 1 ? args.tp_copy_ctas : 0;
+  const int cta0 = (int)blockIdx.x - n_copy;
+  const int cta_stride = (int)gridDim.x - n_copy;
+
+  if (cta0 < 0) {
+    // ---------------------------------------------------------- all-gather data movers
+    __shared__ int s_ok;
+    const int per_rank = args.rows_per_rank / BM;
+    if (threadIdx.x == 0) s_ok = 1;
+    if (blockIdx.x == 0 && threadIdx.x < args.tp_world) {  // "my shard is complete"
+      __threadfence_system();
+      st_release_sys_u64(reinterpret_cast<uint64_t*>(args.tp_sig.p[threadIdx.x]) + args.tp_rank,
+                         (uint64_t)args.tp_epoch);
+    }
+    __syncthreads();
+    const size_t row_vecs = (size_t)K * (I8 ? 1 : 2) / 16;  // 16-byte vectors per row
+    // tile rows in the order the GEMM consumes them, dealt round-robin to the copy CTAs
+    for (int i = blockIdx.x; i < tiles_m && s_ok; i += n_copy) {
+      const int tmr = (i + args.tp_rank * per_rank) % tiles_m;
+      const int src_rank = tmr / per_rank;
+      if (threadIdx.x == 0) {
+        const uint64_t* flag =
+            reinterpret_cast<const uint64_t*>(args.tp_sig.p[args.tp_rank]) + src_rank;
+        if (!wait_epoch(flag, args.tp_epoch, 0, args.tp_wait_limit)) {
+          set_error(args.err, ERR_WAIT_PEER);
+          s_ok = 0;
+        }
+      }
+      __syncthreads();
+      if (!s_ok) break;
+      const int rows = min(BM, M - tmr * BM);
+      const uint4* src = reinterpret_cast<const uint4*>(args.tp_src.p[src_rank]) +
+                         (size_t)(tmr - src_rank * per_rank) * BM * row_vecs;
+      uint4* dst = reinterpret_cast<uint4*>(args.tp_full) + (size_t)tmr * BM * row_vecs;
+      const size_t nvec = (size_t)rows * row_vecs;
+      for (size_t v = threadIdx.x; v < nvec; v += blockDim.x) dst[v] = ld_volatile_u4(src + v);
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) st_release_gpu_s32(args.tp_row_flags + tmr, (int)args.tp_epoch);
+    }
+  } else
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -156,11 +224,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int armed_stage = -1;
       uint32_t armed_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+      for (int t = cta0; t < ntiles && ok; t += cta_stride) {
         int tm, tn, grp, kb0, nkb;
         if (!tile_info(t, tm, tn, grp, kb0, nkb)) continue;
         const int m0 = tm * BM, n0 = tn * BN;
         const int b_off = args.group_mode == 1 ? grp * args.b_group_rows : 0;
+        if (args.tp_mode == 1) {
+          if (!wait_flag_ge(args.tp_row_flags + tm, (int)args.tp_epoch, args.tp_wait_limit)) {
+            set_error(args.err, ERR_WAIT_PEER);
+            ok = false;
+            break;
+          }
+          // rows were written by ordinary stores of another CTA; TMA reads them via the async proxy
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             set_error(args.err, ERR_WAIT_PRODUCER);
@@ -212,7 +289,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+      for (int t = cta0; t < ntiles && ok; t += cta_stride) {
         int tm, tn, grp, kb0, nkb;
         if (!tile_info(t, tm, tn, grp, kb0, nkb)) continue;
         const int acc = it & 1;
@@ -267,7 +344,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int ew = warp & 3;  // TMEM lane quarter this warp may touch
     int it = 0;
     int out_slabs = 0;  // staged slabs issued so far (selects the staging buffer)
-    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    for (int t = cta0; t < ntiles; t += cta_stride) {
       int tm, tn, grp, kb0, nkb;
       if (!tile_info(t, tm, tn, grp, kb0, nkb)) continue;
       const int acc = it & 1;
@@ -363,10 +440,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (issuer) {
               const int x0 = n0 + slab * (f32out ? 32 : 64);
-              if (args.out_mode == 2)
+              if (args.tp_mode == 2) {
+                const int per_rank = args.rows_per_rank / BM;
+                const int dest = tm / per_rank;
+                const int yd = (tm - dest * per_rank) * BM + args.tp_rank * args.rows_per_rank;
+                tma_store_2d(args.tp_cmaps + dest, buf, x0, yd);
+              } else if (args.out_mode == 2) {
                 tma_reduce_add_2d(&tmC, buf, x0, y0);
-              else
+              } else {
                 tma_store_2d(&tmC, buf, x0, y0);
+              }
               tma_store_commit();
             }
             ++out_slabs;
@@ -446,6 +529,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 
   if (args.tma_store && threadIdx.x == 128) tma_store_wait<0>();  // smem must outlive the reads
+  if (args.tp_mode == 2) {
+    // all of this CTA's tiles are written; the last CTA of the grid tells every peer and waits
+    // until every peer has told us, so the kernel's end means "all partials of my rows landed"
+    __shared__ bool s_last;
+    if (threadIdx.x == 128) {
+      asm volatile("fence.proxy.async;" ::: "memory");
+      __threadfence_system();
+      s_last = atomicAdd(args.tp_counter, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x < args.tp_world) {
+      st_release_sys_u64(reinterpret_cast<uint64_t*>(args.tp_sig.p[threadIdx.x]) + args.tp_world +
+                             args.tp_rank,
+                         (uint64_t)args.tp_epoch);
+      const uint64_t* flag = reinterpret_cast<const uint64_t*>(args.tp_sig.p[args.tp_rank]) +
+                             args.tp_world + threadIdx.x;
+      if (!wait_epoch(flag, args.tp_epoch, 0, args.tp_wait_limit)) set_error(args.err, ERR_WAIT_PEER);
+      if (threadIdx.x == 0) *args.tp_counter = 0u;
+    }
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 2) {
@@ -456,7 +559,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
 template <int BN, bool I8>
 static int launch_gemm(const void* A, const void* B, const GemmArgs& args, int lda, int ldb,
-                       cudaStream_t stream, int max_ctas, int b_rows_override = 0) {
+                       cudaStream_t stream, int max_ctas, int b_rows_override = 0, int force_grid = 0) {
   using Cfg = GemmCfg<BN>;
   constexpr int ES = I8 ? 1 : 2;
   constexpr int BK = I8 ? 128 : 64;
@@ -489,7 +592,10 @@ static int launch_gemm(const void* A, const void* B, const GemmArgs& args, int l
     const bool group_ok = args.group_mode != 2 || (args.M % BM == 0 &&
                           args.c_group_stride == (long)args.M * args.ldc);
     largs.tma_store = 0;
-    if (aligned && group_ok) {
+    if (args.tp_mode == 2) {
+      largs.tma_store = 1;
+      tmC = tmA;
+    } else if (aligned && group_ok) {
       const uint64_t rows = args.group_mode == 2 ? (uint64_t)args.M * args.num_groups : (uint64_t)args.M;
       int rc2 = make_tmap_2d(&tmC, f32out ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                              ces, args.C, args.N, rows, (uint64_t)args.ldc * ces, f32out ? 32 : 64, BM);
@@ -508,6 +614,7 @@ static int launch_gemm(const void* A, const void* B, const GemmArgs& args, int l
                      (args.group_mode == 2 ? args.num_groups : 1);
   int grid = tiles < sm_count() ? (int)tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  if (force_grid > 0) grid = force_grid;
   gemm_kernel<BN, I8><<<grid, 256, Cfg::SMEM, stream>>>(tmA, tmB, tmC, largs);
   return (int)cudaGetLastError();
 }
@@ -635,4 +742,78 @@ BB_API int bb_gemm_bf16_grouped(const void* A, const void* B, void* C, int M, in
     case 64: return launch_gemm<64, false>(A, Bp, a, lda, ldb, s, 0, b_total_rows);
     default: return BB_EARG;
   }
+}
+
+// Tensor-parallel fused GEMMs (bf16, x.W^T layout: A [M,K] K-major, B [N,K] K-major).
+//  mode 1 (all-gather -> GEMM): `a_full` is this rank's [M, K] landing buffer; `a_src_ptrs[r]`
+//    is rank r's [rows_per_rank, K] shard; `row_flags` int32[M/128] local (persistent, compared
+//    against the monotonically increasing `epoch`); C [M, N] local.
+//  mode 2 (GEMM -> reduce-scatter): A [M, K] local; `cmaps` = device array of `world` tensor maps
+//    made by bb_tp_make_cmaps over every rank's receive buffer [world*rows_per_rank, N];
+//    `counter` = one zeroed uint32 of local device memory.
+//  `sig_ptrs[r]`: rank r's signal words (uint64[2*world], zeroed once).  M = world*rows_per_rank,
+//  rows_per_rank % 128 == 0.
+BB_API int bb_gemm_bf16_tp(int mode, const void* A, const void* B, void* C, int M, int N, int K,
+                           int lda, int ldb, int ldc, int rank, int world, int rows_per_rank,
+                           const uint64_t* a_src_ptrs, int* row_flags, int copy_ctas,
+                           const uint64_t* sig_ptrs, unsigned int epoch, const void* cmaps,
+                           unsigned int* counter, double wait_seconds, void* stream) {
+  using namespace bb;
+  if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > MAX_RANKS) return BB_EARG;
+  if (rows_per_rank % BM || (long)rows_per_rank * world != M) return BB_EARG;
+  if (mode != 1 && mode != 2) return BB_EARG;
+  GemmArgs a{};
+  a.C = C;
+  a.alpha = 1.f;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.ldc = ldc;
+  a.out_mode = 0;
+  a.err = device_error_word();
+  a.tp_mode = mode;
+  a.tp_rank = rank;
+  a.tp_world = world;
+  a.rows_per_rank = rows_per_rank;
+  a.tp_epoch = epoch;
+  a.tp_wait_limit = (long long)(wait_seconds * 1.9e9);
+  for (int r = 0; r < world; ++r) a.tp_sig.p[r] = reinterpret_cast<void*>(sig_ptrs[r]);
+  if (mode == 1) {
+    if (lda != K) return BB_EARG;  // the landing buffer is dense
+    for (int r = 0; r < world; ++r) a.tp_src.p[r] = reinterpret_cast<void*>(a_src_ptrs[r]);
+    a.tp_full = const_cast<void*>(A);
+    a.tp_row_flags = row_flags;
+    a.tp_copy_ctas = copy_ctas > 0 ? copy_ctas : 16;
+    if (a.tp_copy_ctas > sm_count() / 2) a.tp_copy_ctas = sm_count() / 2;
+  } else {
+    a.tp_cmaps = static_cast<const CUtensorMap*>(cmaps);
+    a.tp_counter = counter;
+  }
+  const int bn = N >= 256 ? 256 : (N >= 128 ? 128 : 64);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the persistent grid must be fully co-resident (one CTA per SM): movers and consumers wait
+  // on each other only in the mover -> consumer direction, and movers have the lowest block ids
+  const int force_grid = sm_count();
+  switch (bn) {
+    case 256: return launch_gemm<256, false>(A, B, a, lda, ldb, s, 0, 0, force_grid);
+    case 128: return launch_gemm<128, false>(A, B, a, lda, ldb, s, 0, 0, force_grid);
+    default: return launch_gemm<64, false>(A, B, a, lda, ldb, s, 0, 0, force_grid);
+  }
+}
+
+// Encode, for every destination rank, a bf16 output map over its receive buffer
+// [world*rows_per_rank rows][N] (pitch ldc elements), 128x64 boxes, and copy the `world` maps to
+// `dst_dev` (device memory, 64-byte aligned, world*128 bytes).
+BB_API int bb_tp_make_cmaps(void* dst_dev, const uint64_t* recv_ptrs, int world, int rows_total,
+                            int N, int ldc) {
+  using namespace bb;
+  if (world < 1 || world > MAX_RANKS) return BB_EARG;
+  CUtensorMap maps[MAX_RANKS];
+  for (int r = 0; r < world; ++r) {
+    int rc = make_tmap_2d(&maps[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                          reinterpret_cast<void*>(recv_ptrs[r]), (uint64_t)N, (uint64_t)rows_total,
+                          (uint64_t)ldc * 2, 64, BM);
+    if (rc) return rc;
+  }
+  return (int)cudaMemcpy(dst_dev, maps, sizeof(CUtensorMap) * world, cudaMemcpyHostToDevice);
 }

@@ -1,0 +1,219 @@
+"""Distributed logic on CPU ranks (gloo processes and native host collectives): grid, planners,
+collectives, thread data parallelism, ZeRO baseline, tensor-parallel primitives and the pipeline
+schedules — N-rank result == 1-rank result."""
+import threading
+
+import pytest
+import torch
+
+from brain_b200.parallel.collective import CollectiveError, HostCollective, NetworkCollective
+from brain_b200.parallel.grid import Grid
+from brain_b200.parallel.plan import (Hardware, ModelShape, ShardCost, plan_balanced, plan_by_capacity,
+                                      plan_tp, schedule, tp_step_secs)
+from tests.mp_util import run_ranks
+
+
+def test_grid_rank_formula_and_groups():
+    g = Grid(tp=2, pp=2, dp=2)
+    assert g.world == 8
+    for r in range(8):
+        assert g.rank_of(*g.coord_of(r)) == r
+    assert g.tp_group(5) == [4, 5] and g.pp_group(5) == [5, 7] and g.dp_group(5) == [1, 5]
+    assert len(g.all_groups("dp")) == 4 and sorted(sum(g.all_groups("pp"), [])) == list(range(8))
+
+
+def test_planners():
+    p = plan_balanced(ShardCost(12, 1.0, 0.0, 0.0), [0, 1, 2])
+    assert [(s.start, s.end) for s in p] == [(0, 4), (4, 8), (8, 12)] and p[0].embed and p[-1].head
+    p = plan_balanced(ShardCost(10, 1.0, 0.0, 4.0), [0, 1])       # heavy head pulls the cut right
+    assert p[0].end > 5
+    assert plan_by_capacity(8, 10.0, 5.0, 5.0, [30.0, 30.0]) is None
+    q = plan_by_capacity(8, 10.0, 5.0, 5.0, [40.0, 40.0, 40.0])
+    assert q is not None and q[-1].end == 8
+    hw = Hardware(n_gpus=8, mem_bytes=100.0)
+    assert plan_tp(hw, ModelShape(1024, 1024, 4096, 4, 50.0, 10.0)).degree == 1
+    t = plan_tp(hw, ModelShape(1024, 1024, 4096, 4, 300.0, 10.0))
+    assert t.degree == 4 and t.fits
+    assert not plan_tp(hw, ModelShape(1024, 1024, 4096, 4, 1e6, 10.0)).fits
+    assert tp_step_secs(Hardware(), ModelShape(4096, 4096, 16384, 32, 0, 0), 2) > 0
+    assert schedule("1f1b", 0, 4, 6) == [1, 2, 3, 4, -1, 5, -2, 6, -3, -4, -5, -6]
+    assert schedule("1f1b", 3, 4, 6) == [1, -1, 2, -2, 3, -3, 4, -4, 5, -5, 6, -6]
+    assert schedule("gpipe", 1, 2, 3) == [1, 2, 3, -3, -2, -1]
+
+
+def test_host_collective_threads_and_abort():
+    g = HostCollective.group(3)
+    res = [None] * 3
+
+    def work(r):
+        t = torch.full((5,), float(r + 1))
+        g[r].all_reduce(t)
+        rs = g[r].reduce_scatter(torch.arange(6, dtype=torch.float32) * (r + 1))
+        ag = g[r].all_gather(torch.tensor([float(r)]))
+        b = torch.full((2,), float(r))
+        g[r].broadcast(b, root=2)
+        res[r] = (t.tolist(), rs.tolist(), ag.tolist(), b.tolist())
+
+    ths = [threading.Thread(target=work, args=(r,)) for r in range(3)]
+    [t.start() for t in ths]
+    [t.join() for t in ths]
+    assert all(r[0] == [6.0] * 5 and r[2] == [0.0, 1.0, 2.0] and r[3] == [2.0, 2.0] for r in res)
+    assert res[1][1] == [12.0, 18.0]
+    # a rank that never joins: the waiting rank times out with an error instead of hanging
+    g2 = HostCollective.group(2, timeout_s=0.3)
+    with pytest.raises(CollectiveError):
+        g2[0].all_reduce(torch.ones(3))
+
+
+def test_network_collective_loopback_and_dropped_peer():
+    co = NetworkCollective.coordinator(2)
+    out = {}
+
+    def w():
+        n = NetworkCollective.worker(1, 2, co.port)
+        t = torch.ones(4) * 2
+        n.all_reduce(t)
+        out["w"] = t.tolist()
+        out["g"] = n.all_gather(torch.tensor([5.0])).tolist()
+        n.close()   # leaves between steps
+
+    th = threading.Thread(target=w)
+    th.start()
+    co.accept()
+    t = torch.ones(4)
+    co.all_reduce(t)
+    g = co.all_gather(torch.tensor([3.0])).tolist()
+    th.join()
+    assert t.tolist() == [3.0] * 4 == out["w"] and g == [3.0, 5.0] == out["g"]
+    with pytest.raises(CollectiveError) as e:     # the worker is gone: named, not ignored
+        co.all_reduce(torch.ones(4))
+    assert "rank 1" in str(e.value)
+
+
+def test_thread_data_parallel_matches_single_replica():
+    from brain_b200.engine import Trainer
+    from brain_b200.models.config import GptConfig
+    from brain_b200.models.gpt2 import Gpt2
+    from brain_b200.parallel.dp import DataParallel
+    cfg = GptConfig(vocab=50, block_size=16, n_layers=2, d_model=32, n_heads=2, d_ff=64)
+    mk = lambda: Gpt2(cfg).init_weights(0)
+    dp = DataParallel(mk, 2, betas=(0.9, 0.95))
+    g = torch.Generator().manual_seed(0)
+    mbs = [(torch.randint(0, 50, (4, 16), generator=g), torch.randint(0, 50, (4, 16), generator=g))
+           for _ in range(2)]
+    single = Trainer(mk(), device="cpu", betas=(0.9, 0.95), weight_decay=0.1, grad_clip=1.0)
+    tok, tgt = torch.cat([m[0] for m in mbs]), torch.cat([m[1] for m in mbs])
+    for _ in range(2):
+        l = dp.train_step(mbs, 3e-3, 0.1, 1.0)
+        l1 = float(single.train_step(tok, tgt, 3e-3, 4))
+        assert abs(l - l1) < 1e-3 * abs(l1)
+    assert torch.equal(dp.stores[0].weights, dp.stores[1].weights)
+
+
+# ------------------------------------------------------------------ gloo process ranks
+def _zero_rank(rank, world):
+    from brain_b200.engine import Trainer
+    from brain_b200.models.config import QwenConfig
+    from brain_b200.models.qwen3 import Qwen3
+    from brain_b200.parallel.zero import ZeroDP
+    cfg = QwenConfig.tiny()
+    tr = Trainer(Qwen3(cfg).init_weights(0), device="cpu", dp=ZeroDP())
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab, (4, 13), generator=g)
+    mine = ids[rank * 2:(rank + 1) * 2]
+    losses = [float(tr.train_step(mine[:, :-1].contiguous(), mine[:, 1:].contiguous(), 1e-2, 1, 4 * 12))
+              for _ in range(3)]
+    return tr.store.weights.clone(), losses
+
+
+def test_zero_dp_two_gloo_ranks_match_single():
+    from brain_b200.engine import Trainer
+    from brain_b200.models.config import QwenConfig
+    from brain_b200.models.qwen3 import Qwen3
+    outs = run_ranks(_zero_rank, 2)
+    assert torch.equal(outs[0][0], outs[1][0])
+    cfg = QwenConfig.tiny()
+    tr = Trainer(Qwen3(cfg).init_weights(0), device="cpu")
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab, (4, 13), generator=g)
+    for _ in range(3):
+        tr.train_step(ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), 1e-2, 2, 4 * 12)
+    n = tr.store.n_train
+    rel = ((outs[0][0][:n] - tr.store.weights[:n]).norm() / tr.store.weights[:n].norm()).item()
+    assert rel < 1e-3
+
+
+def _tp_rank(rank, world):
+    from brain_b200.parallel.tp import TensorParallel, column_parallel_linear, row_parallel_linear
+    torch.manual_seed(0)
+    S, d, ff = 8, 16, 32
+    x = torch.randn(S, d)
+    w1, w2 = torch.randn(ff, d) * 0.2, torch.randn(d, ff) * 0.2
+    tp = TensorParallel()
+    rows, cols = S // world, ff // world
+    xs = x[rank * rows:(rank + 1) * rows].clone().requires_grad_()
+    w1s = w1[rank * cols:(rank + 1) * cols].clone().requires_grad_()
+    w2s = w2[:, rank * cols:(rank + 1) * cols].clone().requires_grad_()
+    h = torch.relu(column_parallel_linear(xs, w1s, tp))
+    y = row_parallel_linear(h, w2s, tp)
+    dy = torch.arange(S * d, dtype=torch.float32).reshape(S, d) / 100
+    y.backward(dy[rank * rows:(rank + 1) * rows])
+    return y.detach(), xs.grad, w1s.grad, w2s.grad
+
+
+def test_tensor_parallel_mlp_matches_unsharded():
+    outs = run_ranks(_tp_rank, 2)
+    torch.manual_seed(0)
+    S, d, ff = 8, 16, 32
+    x = torch.randn(S, d).requires_grad_()
+    w1, w2 = (torch.randn(ff, d) * 0.2).requires_grad_(), (torch.randn(d, ff) * 0.2).requires_grad_()
+    y = torch.relu(x @ w1.t()) @ w2.t()
+    dy = torch.arange(S * d, dtype=torch.float32).reshape(S, d) / 100
+    y.backward(dy)
+    assert torch.allclose(torch.cat([o[0] for o in outs]), y.detach(), atol=1e-5)
+    assert torch.allclose(torch.cat([o[1] for o in outs]), x.grad, atol=1e-5)
+    assert torch.allclose(torch.cat([o[2] for o in outs]), w1.grad, atol=1e-5)
+    assert torch.allclose(torch.cat([o[3] for o in outs], dim=1), w2.grad, atol=1e-5)
+
+
+def _pp_rank(rank, world, sched):
+    from brain_b200.models.config import QwenConfig
+    from brain_b200.models.qwen3 import Qwen3
+    from brain_b200.parallel.pipeline import PipelineStage
+    cfg = QwenConfig.tiny()
+    cfg.n_layers = 4
+    full = Qwen3(cfg).init_weights(0)
+    bounds = [0, 2, 4]
+    stage = Qwen3(cfg, layers=range(bounds[rank], bounds[rank + 1]), first=rank == 0, last=rank == world - 1)
+    stage.load_reference_state(full.reference_state(), strict=True)
+    import torch.distributed as dist
+    tied = dist.new_group([0, world - 1])
+    pp = PipelineStage(stage, rank, world, rank - 1 if rank > 0 else None,
+                       rank + 1 if rank < world - 1 else None, tied_group=tied, schedule=sched)
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, cfg.vocab, (4, 13), generator=g)
+    toks = [ids[i:i + 1, :-1].contiguous() for i in range(4)]
+    tgts = [ids[i:i + 1, 1:].contiguous() for i in range(4)]
+    loss = pp.forward_backward(toks, tgts, 1.0 / (4 * 12))
+    pp.sync_tied_embeddings()
+    grads = {n: p.grad.clone() for n, p in stage.reference_state().items() if p.grad is not None}
+    return (None if loss is None else float(loss)), grads
+
+
+@pytest.mark.parametrize("sched", ["1f1b", "gpipe"])
+def test_pipeline_two_stages_match_single(sched):
+    from brain_b200.models.config import QwenConfig
+    from brain_b200.models.qwen3 import Qwen3
+    outs = run_ranks(_pp_rank, 2, sched)
+    cfg = QwenConfig.tiny()
+    cfg.n_layers = 4
+    full = Qwen3(cfg).init_weights(0)
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, cfg.vocab, (4, 13), generator=g)
+    loss = full.loss(ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), 1.0 / (4 * 12))
+    loss.backward()
+    assert abs(outs[1][0] - float(loss)) < 1e-4
+    want = {n: p.grad for n, p in full.reference_state().items()}
+    for r in range(2):
+        for n, gr in outs[r][1].items():
+            assert torch.allclose(gr, want[n], atol=2e-5), (sched, r, n)
