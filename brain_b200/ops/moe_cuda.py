@@ -146,8 +146,8 @@ class _Experts(torch.autograd.Function):
         yp = grouped_gemm_rows(h, w_down.view(E * d, ff), tile_group, d, d)
         y = torch.empty(n, d, device=dev, dtype=x.dtype)
         wc = w.contiguous()
-        call("moe_combine", _u64([yp.data_ptr()]), 1, idx, pos_of_pair, wc, k, E, y, n, d,
-             stream_ptr())
+        call("moe_combine", _u64([yp.data_ptr()]), _u64([pos_of_pair.data_ptr()]), 1, idx, L(0), wc,
+             k, E, y, n, d, stream_ptr())
         ctx.save_for_backward(xp, gu, h, yp, wc, idx, offsets, tile_group, pos_of_pair, pair_of_pos)
         ctx.w_refs = (w_gate_up, w_down)
         ctx.dims = (n, d, k, E, ff, max_rows)
@@ -162,7 +162,8 @@ class _Experts(torch.autograd.Function):
         dy = dy.contiguous()
         s = stream_ptr()
         d_w = torch.empty(n, k, device=dev, dtype=torch.float32)
-        call("moe_rowdot", dy, _u64([yp.data_ptr()]), 1, idx, pos_of_pair, k, E, d_w, L(n * k), d, s)
+        call("moe_rowdot", dy, _u64([yp.data_ptr()]), _u64([pos_of_pair.data_ptr()]), 1, idx, L(0),
+             k, E, d_w, L(n * k), d, s)
         dyp = torch.empty(max_rows, d, device=dev, dtype=dy.dtype)
         call("moe_gather", _u64([dy.data_ptr()]), 1, n, pair_of_pos, wc, k, dyp, offsets, E, d,
              max_rows, s)
@@ -171,7 +172,8 @@ class _Experts(torch.autograd.Function):
         call("swiglu_bwd", dh, gu, dgu, L(max_rows), ff, s)
         dxp = grouped_gemm_rows(dgu, w_gate_up.view(E * 2 * ff, d), tile_group, 2 * ff, d, b_mn=True)
         dx = torch.empty(n, d, device=dev, dtype=dy.dtype)
-        call("moe_combine", _u64([dxp.data_ptr()]), 1, idx, pos_of_pair, None, k, E, dx, n, d, s)
+        call("moe_combine", _u64([dxp.data_ptr()]), _u64([pos_of_pair.data_ptr()]), 1, idx, L(0),
+             None, k, E, dx, n, d, s)
         grads = []
         for wp, a_rows, b_rows in ((w_down, dyp, h), (w_gate_up, dgu, xp)):
             mg = getattr(wp, "main_grad", None)

@@ -1,0 +1,295 @@
+"""Expert parallelism: every rank of the group stores ``E / world`` experts of each MoE layer and
+runs their grouped tcgen05 GEMMs over the rows that ALL ranks route to them.
+
+The all-to-all dispatch and combine are not separate collectives: the row movement is the MoE
+kernels' own NVLink peer loads.  Per layer and direction:
+
+  dispatch   the expert owner's gather kernel pulls the routed token rows straight out of every
+             source rank's symmetric activation buffer into its expert-sorted, 128-row-padded
+             operand buffer (the grouped GEMM then TMA-loads it locally — a remote row crosses
+             NVLink once);
+  combine    the token owner's combine kernel pulls each of its tokens' top-k expert outputs from
+             the owners' symmetric output buffers and applies the routing weights while summing.
+
+Only routing metadata (top-k ids and weights, a few bytes per token) goes through
+``torch.distributed``.  Ranks meet at bounded in-stream flag barriers (``bb_symm_barrier``) before
+reading each other's buffers.  ``impl='nccl'`` is the baseline: ``all_to_all_single`` of the rows
+plus the single-rank kernels.  CPU (gloo) ranks use a reference restatement for tests.
+
+The reference has no distributed expert parallelism (closest: checkpoint-level expert shards,
+crates/federated/src/shard.rs:1-36); the layer math follows crates/model/src/moe.rs:256-286."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as F
+from ..ops import reference as ref
+
+
+class ExpertParallel:
+    def __init__(self, group=None, impl: str = "fused", device=None, arena_mb: int = 1024,
+                 wait_seconds: float = 20.0):
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.impl = impl
+        self.wait_seconds = wait_seconds
+        self.epoch = 0
+        self._slots = {}
+        if self.world > 1 and impl == "fused":
+            from .symm import SymmArena
+            self.device = torch.device(device if device is not None else torch.cuda.current_device())
+            self.arena = SymmArena(arena_mb << 20, self.device, group)
+            self.sig = self.arena.alloc(self.world, torch.int64)
+            self._U64 = ctypes.c_uint64 * self.world
+            self.sig_ptrs = self._U64(*self.arena.peer_ptrs(self.sig))
+
+    # ------------------------------------------------------------------ helpers
+    def _slot(self, kind, numel, dtype, parity):
+        key = (kind, numel, dtype, parity)
+        t = self._slots.get(key)
+        if t is None:
+            t = self.arena.alloc(numel, dtype)
+            self._slots[key] = t
+        return t
+
+    def _barrier(self):
+        from ..ops._cuda import call, stream_ptr
+        self.epoch += 1
+        call("symm_barrier", self.sig_ptrs, self.rank, self.world, ctypes.c_uint(self.epoch),
+             ctypes.c_double(self.wait_seconds), stream_ptr())
+
+    def _ptrs(self, t):
+        return self._U64(*self.arena.peer_ptrs(t))
+
+    def _gather_meta(self, t):
+        out = torch.empty(self.world * t.shape[0], *t.shape[1:], device=t.device, dtype=t.dtype)
+        dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
+        return out
+
+    # ------------------------------------------------------------------ CUDA path
+    def experts(self, x, w, w_gate_up, w_down, idx, counts):
+        if self.impl != "fused":
+            return _ExpertsA2A.apply(x, w, w_gate_up, w_down, idx, self)
+        return _ExpertsEP.apply(x, w, w_gate_up, w_down, idx, counts, self)
+
+    # ------------------------------------------------------------------ CPU reference (gloo)
+    def forward_reference(self, x, router, w_gate_up, w_down, top_k, norm, scale, aux_coef, z_coef):
+        """Differentiable restatement for CPU ranks: all-gather tokens and routing, apply the local
+        experts to every rank's rows, reduce-scatter the partial outputs."""
+        from ..ops.moe import _aux_losses
+        n, d = x.shape
+        E = router.shape[0]
+        e_local = w_gate_up.shape[0]
+        e_first = self.rank * e_local
+        logits = ref.linear(x, router)
+        probs, idx, w, lse = ref.router_topk(logits, top_k, norm, scale)
+        aux, counts = _aux_losses(probs, idx, lse, E, top_k, aux_coef, z_coef)
+        xa = _AllGatherRows.apply(x, self)
+        ia = self._gather_cpu(idx)
+        wa = _AllGatherRows.apply(w, self)
+        y = torch.zeros_like(xa)
+        for j in range(e_local):
+            sel = ia == (e_first + j)
+            rows = sel.any(dim=-1).nonzero(as_tuple=True)[0]
+            if rows.numel() == 0:
+                continue
+            h = ref.swiglu(ref.linear(xa[rows], w_gate_up[j]))
+            o = ref.linear(h, w_down[j])
+            gate = (wa * sel).sum(dim=-1)[rows].to(o.dtype)
+            y = y.index_add(0, rows, o * gate[:, None])
+        y = _ReduceScatterRows.apply(y, self)
+        return y, aux, counts
+
+    def _gather_cpu(self, t):
+        parts = [torch.empty_like(t) for _ in range(self.world)]
+        dist.all_gather(parts, t.contiguous(), group=self.group)
+        return torch.cat(parts)
+
+
+class _AllGatherRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, ep):
+        ctx.ep = ep
+        parts = [torch.empty_like(x) for _ in range(ep.world)]
+        dist.all_gather(parts, x.contiguous(), group=ep.group)
+        return torch.cat(parts)
+
+    @staticmethod
+    def backward(ctx, g):
+        ep = ctx.ep
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ep.group)
+        n = g.shape[0] // ep.world
+        return g[ep.rank * n:(ep.rank + 1) * n], None
+
+
+class _ReduceScatterRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, ep):
+        ctx.ep = ep
+        y = y.contiguous().clone()
+        dist.all_reduce(y, group=ep.group)
+        n = y.shape[0] // ep.world
+        return y[ep.rank * n:(ep.rank + 1) * n].clone()
+
+    @staticmethod
+    def backward(ctx, g):
+        ep = ctx.ep
+        parts = [torch.empty_like(g) for _ in range(ep.world)]
+        dist.all_gather(parts, g.contiguous(), group=ep.group)
+        return torch.cat(parts), None
+
+
+class _ExpertsEP(torch.autograd.Function):
+    """Fused expert-parallel experts: peer-load dispatch, local grouped GEMMs, peer-load combine."""
+
+    @staticmethod
+    def forward(ctx, x, w, w_gate_up, w_down, idx, counts, ep):
+        from ..ops._cuda import L, call, stream_ptr
+        from ..ops.moe_cuda import grouped_gemm_rows
+        n, d = x.shape
+        k = idx.shape[1]
+        El, ff2, _ = w_gate_up.shape
+        ff = ff2 // 2
+        W = ep.world
+        E = El * W
+        dev = x.device
+        s = stream_ptr()
+        par = (ep.epoch // 2) & 1   # two barriers per call: slots alternate per call
+        # routing metadata of every rank (ids, weights) and the global load of my experts
+        idx_all = ep._gather_meta(idx)                      # [W*n, k] int32
+        w_all = ep._gather_meta(w.contiguous())             # [W*n, k] fp32
+        cnt = counts.clone()
+        dist.all_reduce(cnt, group=ep.group)
+        cnt_local = cnt[ep.rank * El:(ep.rank + 1) * El].contiguous()
+        n_pairs_all = W * n * k
+        max_rows = (n_pairs_all + El * 127 + 127) // 128 * 128
+        max_tiles = max_rows // 128
+        offsets = torch.empty(El + 1, device=dev, dtype=torch.int32)
+        tile_group = torch.empty(max_tiles, device=dev, dtype=torch.int32)
+        call("moe_plan", cnt_local, El, offsets, tile_group, max_tiles, s)
+        pos_tab = ep._slot("pos", n_pairs_all, torch.int32, par)
+        pos_tab.fill_(-1)
+        pair_of_pos = torch.full((max_rows,), -1, device=dev, dtype=torch.int32)
+        call("moe_positions", idx_all, L(n_pairs_all), ep.rank * El, El, offsets, pos_tab, pair_of_pos, s)
+        xs = ep._slot("x", n * d, x.dtype, par).view(n, d)
+        xs.copy_(x)
+        ep._barrier()                                       # every rank's x and pos table are in place
+        xp = torch.empty(max_rows, d, device=dev, dtype=x.dtype)
+        call("moe_gather", ep._ptrs(xs), W, n, pair_of_pos, None, k, xp, offsets, El, d, max_rows, s)
+        gu = grouped_gemm_rows(xp, w_gate_up.view(El * ff2, d), tile_group, ff2, ff2)
+        h = torch.empty(max_rows, ff, device=dev, dtype=x.dtype)
+        call("swiglu_fwd", gu, h, L(max_rows), ff, s)
+        yp = ep._slot("yp", max_rows * d, x.dtype, par).view(max_rows, d)
+        grouped_gemm_rows(h, w_down.view(El * d, ff), tile_group, d, d, out=yp)
+        ep._barrier()                                       # every rank's expert outputs are in place
+        y = torch.empty(n, d, device=dev, dtype=x.dtype)
+        wc = w.contiguous()
+        call("moe_combine", ep._ptrs(yp), ep._ptrs(pos_tab), W, idx, L(ep.rank * n * k), wc, k, El,
+             y, n, d, s)
+        yp_keep = yp.clone()   # the symmetric slot is recycled two calls later
+        ctx.save_for_backward(xp, gu, h, yp_keep, wc, w_all, idx, idx_all, offsets, tile_group,
+                              pos_tab.clone(), pair_of_pos)
+        ctx.ep, ctx.w_refs = ep, (w_gate_up, w_down)
+        ctx.dims = (n, d, k, El, ff, max_rows, W)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops._cuda import L, call, stream_ptr
+        from ..ops.moe_cuda import grouped_gemm_dw, grouped_gemm_rows
+        (xp, gu, h, yp, wc, w_all, idx, idx_all, offsets, tile_group, pos_keep,
+         pair_of_pos) = ctx.saved_tensors
+        ep = ctx.ep
+        w_gate_up, w_down = ctx.w_refs
+        n, d, k, El, ff, max_rows, W = ctx.dims
+        dev = dy.device
+        s = stream_ptr()
+        par = (ep.epoch // 2) & 1
+        n_pairs_all = W * n * k
+        # republish what peers need: my dy, my pos table and my yp (for their d_w)
+        dys = ep._slot("x", n * d, dy.dtype, par).view(n, d)
+        dys.copy_(dy)
+        pos_tab = ep._slot("pos", n_pairs_all, torch.int32, par)
+        pos_tab.copy_(pos_keep)
+        yps = ep._slot("yp", max_rows * d, dy.dtype, par).view(max_rows, d)
+        yps.copy_(yp)
+        ep._barrier()
+        d_w = torch.empty(n, k, device=dev, dtype=torch.float32)
+        call("moe_rowdot", dys, ep._ptrs(yps), ep._ptrs(pos_tab), W, idx, L(ep.rank * n * k), k, El,
+             d_w, L(n * k), d, s)
+        dyp = torch.empty(max_rows, d, device=dev, dtype=dy.dtype)
+        call("moe_gather", ep._ptrs(dys), W, n, pair_of_pos, w_all.reshape(-1), k, dyp, offsets, El, d,
+             max_rows, s)
+        dh = grouped_gemm_rows(dyp, w_down.view(El * d, ff), tile_group, d, ff, b_mn=True)
+        dgu = torch.empty_like(gu)
+        call("swiglu_bwd", dh, gu, dgu, L(max_rows), ff, s)
+        dxp = ep._slot("dxp", max_rows * d, dy.dtype, par).view(max_rows, d)
+        dxp.zero_()
+        grouped_gemm_rows(dgu, w_gate_up.view(El * 2 * ff, d), tile_group, 2 * ff, d, b_mn=True, out=dxp)
+        ep._barrier()
+        dx = torch.empty(n, d, device=dev, dtype=dy.dtype)
+        call("moe_combine", ep._ptrs(dxp), ep._ptrs(pos_tab), W, idx, L(ep.rank * n * k), None, k, El,
+             dx, n, d, s)
+        grads = []
+        for wp, a_rows, b_rows in ((w_down, dyp, h), (w_gate_up, dgu, xp)):
+            mg = getattr(wp, "main_grad", None)
+            if mg is not None:
+                grouped_gemm_dw(a_rows, b_rows, offsets, El, mg, accumulate=True)
+                F._notify(wp)
+                grads.append(None)
+            else:
+                g = torch.zeros(wp.shape, device=dev, dtype=torch.float32)
+                grouped_gemm_dw(a_rows, b_rows, offsets, El, g, accumulate=True)
+                grads.append(g.to(wp.dtype))
+        return dx, d_w, grads[1], grads[0], None, None, None
+
+
+class _ExpertsA2A(torch.autograd.Function):
+    """Baseline: rows travel with ``all_gather`` / ``reduce_scatter`` collectives and every rank
+    applies its local experts with the single-rank kernels (what the fused path is measured against)."""
+
+    @staticmethod
+    def forward(ctx, x, w, w_gate_up, w_down, idx, ep):
+        from ..ops.moe_cuda import _Experts
+        El = w_gate_up.shape[0]
+        xa = ep._gather_meta(x.contiguous())
+        ia = ep._gather_meta(idx)
+        wa = ep._gather_meta(w.contiguous())
+        # keep only pairs routed to my experts: remap ids to local, others to a dead slot
+        local = ia - ep.rank * El
+        mine = (local >= 0) & (local < El)
+        li = torch.where(mine, local, torch.zeros_like(local)).to(torch.int32)
+        wl = torch.where(mine, wa, torch.zeros_like(wa))
+        counts = torch.bincount(li[mine].long(), minlength=El).to(torch.int32)
+        # pairs that are not mine point at local expert 0 with weight 0: add their count
+        counts[0] += int((~mine).sum())
+        with torch.enable_grad():
+            xa_g = xa.detach().requires_grad_()
+            wl_g = wl.detach().requires_grad_()
+            part = _Experts.apply(xa_g, wl_g, w_gate_up, w_down, li.contiguous(), counts)
+        y = torch.empty_like(x)
+        dist.reduce_scatter_tensor(y, part.detach().contiguous(), group=ep.group)
+        ctx.save_for_backward(xa_g, wl_g, part, mine)
+        ctx.ep = ep
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xa_g, wl_g, part, mine = ctx.saved_tensors
+        ep = ctx.ep
+        dya = ep._gather_meta(dy.contiguous())
+        part.backward(dya)
+        n = dy.shape[0]
+        dxa = xa_g.grad.contiguous()
+        dx = torch.empty_like(dy)
+        dist.reduce_scatter_tensor(dx, dxa, group=ep.group)
+        dwa = torch.where(mine, wl_g.grad, torch.zeros_like(wl_g.grad)).contiguous()
+        dw = torch.empty(n, dwa.shape[1], device=dy.device, dtype=dwa.dtype)
+        dist.reduce_scatter_tensor(dw, dwa, group=ep.group)
+        return dx, dw, None, None, None, None

@@ -92,9 +92,33 @@ __global__ void __launch_bounds__(256) tp_allreduce_kernel(const ArArgs a) {
   }
 }
 
+// All ranks meet: publish `epoch` to every peer, then wait (bounded) until every peer published it.
+// Orders "my earlier kernels' writes to symmetric memory" before "peers' later reads" without NCCL.
+__global__ void symm_barrier_kernel(PeerPtrs sig, int rank, int world, uint32_t epoch,
+                                    long long wait_limit, int* err) {
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys_u64(reinterpret_cast<uint64_t*>(sig.p[threadIdx.x]) + rank, (uint64_t)epoch);
+    if (!wait_epoch(reinterpret_cast<const uint64_t*>(sig.p[rank]) + threadIdx.x, epoch, 0, wait_limit))
+      set_error(err, ERR_WAIT_PEER);
+  }
+}
+
 }  // namespace bb
 
 using namespace bb;
+
+// sig_ptrs[r]: rank r's uint64[world] flag words (zeroed once); epoch must increase on every call.
+BB_API int bb_symm_barrier(const uint64_t* sig_ptrs, int rank, int world, unsigned int epoch,
+                           double wait_seconds, void* stream) {
+  if (world < 1 || world > MAX_RANKS) return BB_EARG;
+  PeerPtrs s{};
+  for (int r = 0; r < world; ++r) s.p[r] = reinterpret_cast<void*>(sig_ptrs[r]);
+  symm_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, rank, world, epoch,
+                                                          (long long)(wait_seconds * 1.9e9),
+                                                          device_error_word());
+  return (int)cudaGetLastError();
+}
 
 // y[slot_elems] = sum over `world` consecutive slots of recv (+ residual)
 BB_API int bb_tp_sum_slots(const void* recv, int world, long slot_elems, const void* residual,

@@ -125,10 +125,9 @@ __global__ void moe_gather_kernel(MoePeers src, int n_per_rank, const int* __res
 
 // y[token, :] = sum_s (w ? w[token,s] : 1) * yp_rank(s)[pos, :].  pos_of_pair gives, per pair,
 // the row inside the buffer of the rank that owns the pair's expert (rank = expert / e_per_rank).
-__global__ void moe_combine_kernel(MoePeers yp, const int* __restrict__ idx,
-                                   const int* __restrict__ pos_of_pair, const float* __restrict__ w,
-                                   int k, int e_per_rank, __nv_bfloat16* __restrict__ y, int n_tok,
-                                   int dv) {
+__global__ void moe_combine_kernel(MoePeers yp, const int* __restrict__ idx, MoePeers pos_tabs,
+                                   long pair_offset, const float* __restrict__ w, int k,
+                                   int e_per_rank, __nv_bfloat16* __restrict__ y, int n_tok, int dv) {
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
   for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < n_tok; t += warps) {
@@ -136,9 +135,10 @@ __global__ void moe_combine_kernel(MoePeers yp, const int* __restrict__ idx,
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       for (int s = 0; s < k; ++s) {
         const int pair = t * k + s;
-        const int pos = pos_of_pair[pair];
-        if (pos < 0) continue;
         const int rank = idx[pair] / e_per_rank;
+        // the row's position is known to the rank that owns the expert: read it from that rank's table
+        const int pos = reinterpret_cast<const int*>(pos_tabs.p[rank])[pair_offset + pair];
+        if (pos < 0) continue;
         float f[8];
         unpack8(reinterpret_cast<const bf16x8*>(yp.p[rank])[(size_t)pos * dv + c], f);
         const float g = w ? w[pair] : 1.f;
@@ -152,18 +152,18 @@ __global__ void moe_combine_kernel(MoePeers yp, const int* __restrict__ idx,
 
 // dw[pair] = <dy[token, :], yp[pos(pair), :]>
 __global__ void moe_rowdot_kernel(const __nv_bfloat16* __restrict__ dy, MoePeers yp,
-                                  const int* __restrict__ idx, const int* __restrict__ pos_of_pair,
+                                  const int* __restrict__ idx, MoePeers pos_tabs, long pair_offset,
                                   int k, int e_per_rank, float* __restrict__ dw, long n_pairs,
                                   int dv) {
   const long warps = ((long)gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
   for (long pair = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; pair < n_pairs;
        pair += warps) {
-    const int pos = pos_of_pair[pair];
+    const int rank = idx[pair] / e_per_rank;
+    const int pos = reinterpret_cast<const int*>(pos_tabs.p[rank])[pair_offset + pair];
     float acc = 0.f;
     if (pos >= 0) {
       const long t = pair / k;
-      const int rank = idx[pair] / e_per_rank;
       const bf16x8* a = reinterpret_cast<const bf16x8*>(dy) + (size_t)t * dv;
       const bf16x8* b = reinterpret_cast<const bf16x8*>(yp.p[rank]) + (size_t)pos * dv;
       for (int c = lane; c < dv; c += 32) {
@@ -220,33 +220,37 @@ BB_API int bb_moe_gather(const uint64_t* src_ptrs, int world, int n_per_rank,
   return (int)cudaGetLastError();
 }
 
-BB_API int bb_moe_combine(const uint64_t* yp_ptrs, int world, const int* idx,
-                          const int* pos_of_pair, const float* w, int k, int e_per_rank, void* y,
-                          int n_tok, int d, void* stream) {
-  MoePeers p{};
+// pos_ptrs[r]: rank r's pos_of_pair table over ALL ranks' pairs; pair_offset = first pair of this
+// rank's tokens in that global numbering (0 on a single rank).
+BB_API int bb_moe_combine(const uint64_t* yp_ptrs, const uint64_t* pos_ptrs, int world,
+                          const int* idx, long pair_offset, const float* w, int k, int e_per_rank,
+                          void* y, int n_tok, int d, void* stream) {
+  MoePeers p{}, pt{};
   if (int rc = fill_peers(p, yp_ptrs, world)) return rc;
+  if (int rc = fill_peers(pt, pos_ptrs, world)) return rc;
   if (d % 8) return BB_EARG;
   int blocks = (n_tok + 7) / 8;
   const int cap = sm_count() * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  moe_combine_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, idx, pos_of_pair, w, k,
+  moe_combine_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, idx, pt, pair_offset, w, k,
                                                               e_per_rank, (__nv_bfloat16*)y, n_tok,
                                                               d / 8);
   return (int)cudaGetLastError();
 }
 
-BB_API int bb_moe_rowdot(const void* dy, const uint64_t* yp_ptrs, int world, const int* idx,
-                         const int* pos_of_pair, int k, int e_per_rank, float* dw, long n_pairs,
-                         int d, void* stream) {
-  MoePeers p{};
+BB_API int bb_moe_rowdot(const void* dy, const uint64_t* yp_ptrs, const uint64_t* pos_ptrs,
+                         int world, const int* idx, long pair_offset, int k, int e_per_rank,
+                         float* dw, long n_pairs, int d, void* stream) {
+  MoePeers p{}, pt{};
   if (int rc = fill_peers(p, yp_ptrs, world)) return rc;
+  if (int rc = fill_peers(pt, pos_ptrs, world)) return rc;
   if (d % 8) return BB_EARG;
   long blocks = (n_pairs + 7) / 8;
   const long cap = (long)sm_count() * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   moe_rowdot_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)dy, p, idx, pos_of_pair, k, e_per_rank, dw, n_pairs, d / 8);
+      (const __nv_bfloat16*)dy, p, idx, pt, pair_offset, k, e_per_rank, dw, n_pairs, d / 8);
   return (int)cudaGetLastError();
 }
