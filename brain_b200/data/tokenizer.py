@@ -1,0 +1,179 @@
+"""Tokenizers: character-level (the ``meta.json`` ``itos`` table of the synthetic datasets) and
+byte-level BPE in the GPT-2 / Qwen family (regex pre-tokenisation + byte-to-unicode mapping here,
+merge loop native in csrc/runtime/bpe.cpp).  A BPE tokenizer is loaded from a HuggingFace
+``tokenizer.json`` (``model.vocab``, ``model.merges``, ``added_tokens``) or built in memory.
+Reference: crates/data/src/{tokenizer,bpe,qwen_tokenizer}.rs."""
+from __future__ import annotations
+
+import ctypes
+import json
+from typing import Dict, Iterable, List, Optional, Sequence
+
+import numpy as np
+
+from .. import _host
+
+c = ctypes
+_host.register({
+    "bbh_bpe_new": (c.c_void_p, []),
+    "bbh_bpe_free": (None, [c.c_void_p]),
+    "bbh_bpe_add_token": (None, [c.c_void_p, c.c_char_p, c.c_int32, c.c_int32]),
+    "bbh_bpe_add_merge": (c.c_int, [c.c_void_p, c.c_char_p, c.c_int32, c.c_char_p, c.c_int32, c.c_int32]),
+    "bbh_bpe_encode_word": (c.c_int32, [c.c_void_p, c.c_char_p, c.c_int32, c.c_void_p, c.c_int32]),
+    "bbh_bpe_token": (c.c_int32, [c.c_void_p, c.c_int32, c.c_char_p, c.c_int32]),
+    "bbh_bpe_vocab_size": (c.c_int32, [c.c_void_p]),
+})
+
+GPT2_SPLIT = r"""'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
+QWEN_SPLIT = (r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*"""
+              r"""|\s*[\r\n]+|\s+(?!\S)|\s+""")
+
+
+def bytes_to_unicode() -> Dict[int, str]:
+    """The GPT-2 reversible byte -> printable-unicode table."""
+    bs = list(range(ord("!"), ord("~") + 1)) + list(range(ord("¡"), ord("¬") + 1)) + \
+        list(range(ord("®"), ord("ÿ") + 1))
+    cs = bs[:]
+    n = 0
+    for b in range(256):
+        if b not in bs:
+            bs.append(b)
+            cs.append(256 + n)
+            n += 1
+    return {b: chr(ch) for b, ch in zip(bs, cs)}
+
+
+class CharTokenizer:
+    def __init__(self, itos: Sequence[str]):
+        self.itos = list(itos)
+        self.stoi = {ch: i for i, ch in enumerate(self.itos)}
+        self.vocab_size = len(self.itos)
+        self.eos_id = None
+
+    @staticmethod
+    def from_text(text: str) -> "CharTokenizer":
+        return CharTokenizer(sorted(set(text)))
+
+    def encode(self, text: str) -> List[int]:
+        try:
+            return [self.stoi[ch] for ch in text]
+        except KeyError as e:
+            raise ValueError(f"character {e.args[0]!r} is not in the vocabulary") from None
+
+    def decode(self, ids: Iterable[int]) -> str:
+        return "".join(self.itos[i] for i in ids if 0 <= i < self.vocab_size)
+
+
+class BpeTokenizer:
+    def __init__(self, vocab: Dict[str, int], merges: Sequence, special: Optional[Dict[str, int]] = None,
+                 pattern: str = QWEN_SPLIT, eos: Optional[str] = None):
+        import regex
+        self._re = regex.compile(pattern)
+        self._b2u = bytes_to_unicode()
+        self._u2b = {v: k for k, v in self._b2u.items()}
+        self.special = dict(special or {})
+        self._special_re = None
+        if self.special:
+            self._special_re = regex.compile("(" + "|".join(regex.escape(s) for s in
+                                                            sorted(self.special, key=len, reverse=True)) + ")")
+        self._id2special = {v: k for k, v in self.special.items()}
+        lib = _host.lib()
+        self._h = lib.bbh_bpe_new()
+        for tok, i in vocab.items():
+            b = tok.encode("utf-8")
+            lib.bbh_bpe_add_token(self._h, b, len(b), i)
+        for rank, m in enumerate(merges):
+            l, r = m.split(" ", 1) if isinstance(m, str) else m
+            lb, rb = l.encode("utf-8"), r.encode("utf-8")
+            lib.bbh_bpe_add_merge(self._h, lb, len(lb), rb, len(rb), rank)
+        self.vocab_size = max([lib.bbh_bpe_vocab_size(self._h)] + [i + 1 for i in self.special.values()])
+        self.eos_id = self.special.get(eos) if eos else None
+        self._buf = np.empty(4096, dtype=np.int32)
+
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                _host.lib().bbh_bpe_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    @staticmethod
+    def from_file(path: str) -> "BpeTokenizer":
+        """Load a HuggingFace ``tokenizer.json``."""
+        d = json.loads(open(path, encoding="utf-8").read())
+        model = d["model"]
+        special = {t["content"]: t["id"] for t in d.get("added_tokens", [])}
+        eos = next((s for s in ("<|im_end|>", "<|endoftext|>") if s in special), None)
+        pat = QWEN_SPLIT if "<|im_end|>" in special or len(model["vocab"]) > 60000 else GPT2_SPLIT
+        return BpeTokenizer(model["vocab"], model["merges"], special, pat, eos)
+
+    @staticmethod
+    def byte_level(merges: Sequence = (), special: Optional[Dict[str, int]] = None) -> "BpeTokenizer":
+        """A 256-symbol byte vocabulary plus the given merges (used by tests and synthetic data)."""
+        b2u = bytes_to_unicode()
+        vocab = {b2u[b]: b for b in range(256)}
+        nxt = 256
+        for m in merges:
+            l, r = m.split(" ", 1)
+            vocab[l + r] = nxt
+            nxt += 1
+        sp = {s: nxt + i for i, s in enumerate(special or [])} if not isinstance(special, dict) else special
+        return BpeTokenizer(vocab, merges, sp, GPT2_SPLIT, eos=next(iter(sp), None) if sp else None)
+
+    def _encode_plain(self, text: str, out: List[int]):
+        lib = _host.lib()
+        for piece in self._re.findall(text):
+            mapped = "".join(self._b2u[b] for b in piece.encode("utf-8")).encode("utf-8")
+            if len(mapped) > self._buf.size:
+                self._buf = np.empty(len(mapped), dtype=np.int32)
+            n = lib.bbh_bpe_encode_word(self._h, mapped, len(mapped), self._buf.ctypes.data, self._buf.size)
+            if n < 0:
+                raise ValueError(f"cannot encode {piece!r}")
+            out.extend(self._buf[:n].tolist())
+
+    def encode(self, text: str, allow_special: bool = True) -> List[int]:
+        out: List[int] = []
+        if self._special_re is None or not allow_special:
+            self._encode_plain(text, out)
+            return out
+        for part in self._special_re.split(text):
+            if not part:
+                continue
+            if part in self.special:
+                out.append(self.special[part])
+            else:
+                self._encode_plain(part, out)
+        return out
+
+    def decode(self, ids: Iterable[int], skip_special: bool = False) -> str:
+        lib = _host.lib()
+        buf = ctypes.create_string_buffer(256)
+        chunks: List[bytes] = []
+        for i in ids:
+            i = int(i)
+            if i in self._id2special:
+                if not skip_special:
+                    chunks.append(self._id2special[i].encode("utf-8"))
+                continue
+            n = lib.bbh_bpe_token(self._h, i, buf, 256)
+            if n <= 0 or n > 256:
+                continue
+            mapped = buf.raw[:n].decode("utf-8", errors="ignore")
+            chunks.append(bytes(self._u2b.get(ch, ord("?")) for ch in mapped))
+        return b"".join(chunks).decode("utf-8", errors="replace")
+
+
+def load_tokenizer(path_or_dir: str):
+    """tokenizer.json (BPE) or a dataset directory with meta.json (character level)."""
+    import os
+    if os.path.isdir(path_or_dir):
+        tj = os.path.join(path_or_dir, "tokenizer.json")
+        if os.path.exists(tj):
+            return BpeTokenizer.from_file(tj)
+        from .binio import read_meta
+        meta = read_meta(path_or_dir)
+        if meta.get("itos"):
+            return CharTokenizer(meta["itos"])
+        raise FileNotFoundError(f"{path_or_dir}: no tokenizer.json or meta.json with itos")
+    return BpeTokenizer.from_file(path_or_dir)
