@@ -163,6 +163,14 @@ class BpeTokenizer:
             chunks.append(bytes(self._u2b.get(ch, ord("?")) for ch in mapped))
         return b"".join(chunks).decode("utf-8", errors="replace")
 
+    def apply_chat_template(self, messages, add_generation_prompt: bool = True,
+                            enable_thinking: bool = True, tools=None) -> str:
+        """ChatML rendering used by the Qwen family (reference: crates/data/src/qwen_tokenizer.rs
+        ``apply_chat_template``): ``<|im_start|>role\ncontent<|im_end|>\n`` per message, an open
+        assistant turn when generating, and an empty think block when thinking is disabled.
+        ``messages`` is a sequence of (role, content) pairs or {"role", "content"} dicts."""
+        return render_chatml(messages, add_generation_prompt, enable_thinking, tools)
+
 
 def load_tokenizer(path_or_dir: str):
     """tokenizer.json (BPE) or a dataset directory with meta.json (character level)."""
@@ -177,3 +185,29 @@ def load_tokenizer(path_or_dir: str):
             return CharTokenizer(meta["itos"])
         raise FileNotFoundError(f"{path_or_dir}: no tokenizer.json or meta.json with itos")
     return BpeTokenizer.from_file(path_or_dir)
+
+
+def render_chatml(messages, add_generation_prompt: bool = True, enable_thinking: bool = True,
+                  tools=None) -> str:
+    out = []
+    msgs = [(m["role"], m.get("content") or "") if isinstance(m, dict) else (m[0], m[1]) for m in messages]
+    if tools:
+        sys_txt = msgs[0][1] + "\n\n" if msgs and msgs[0][0] == "system" else ""
+        if msgs and msgs[0][0] == "system":
+            msgs = msgs[1:]
+        decl = "\n".join(json.dumps(t, separators=(",", ":"), ensure_ascii=False) for t in tools)
+        out.append("<|im_start|>system\n" + sys_txt + "# Tools\n\nYou may call one or more functions to assist "
+                   "with the user query.\n\nYou are provided with function signatures within <tools></tools> "
+                   "XML tags:\n<tools>\n" + decl + "\n</tools>\n\nFor each function call, return a json object "
+                   "with function name and arguments within <tool_call></tool_call> XML tags:\n<tool_call>\n"
+                   "{\"name\": <function-name>, \"arguments\": <args-json-object>}\n</tool_call><|im_end|>\n")
+    for role, content in msgs:
+        if role == "tool":
+            out.append(f"<|im_start|>user\n<tool_response>\n{content}\n</tool_response><|im_end|>\n")
+        else:
+            out.append(f"<|im_start|>{role}\n{content}<|im_end|>\n")
+    if add_generation_prompt:
+        out.append("<|im_start|>assistant\n")
+        if not enable_thinking:
+            out.append("<think>\n\n</think>\n\n")
+    return "".join(out)

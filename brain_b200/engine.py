@@ -22,16 +22,24 @@ from .paramstore import ParamStore
 class Trainer:
     def __init__(self, model: nn.Module, device=None, betas=(0.9, 0.999), eps=1e-8,
                  weight_decay=0.1, grad_clip: Optional[float] = 1.0, dp=None, decay_fn=None,
-                 dtype: Optional[torch.dtype] = None):
-        """``dp``: a ``parallel.zero.ZeroDP`` (or None for a single replica)."""
+                 dtype: Optional[torch.dtype] = None, offload_adam: Optional[bool] = None):
+        """``dp``: a ``parallel.zero.ZeroDP`` (or None for a single replica).  ``offload_adam``
+        keeps fp32 master weights and moments in host memory (default: env ``BRAIN_OFFLOAD_ADAM=1``)."""
         self.model = model
         self.dp = dp
         world = dp.world if dp is not None else 1
         self.store = ParamStore(model, device=device, dtype=dtype, pad_to=world, decay_fn=decay_fn)
         self.device = self.store.device
         shard = (dp.rank, world) if dp is not None else None
-        self.opt = AdamW(self.store, betas=betas, eps=eps, shard=shard,
-                         group=dp.group if dp is not None else None)
+        if offload_adam is None:
+            import os
+            offload_adam = os.environ.get("BRAIN_OFFLOAD_ADAM") == "1"
+        if offload_adam and dp is None:
+            from .optim.offload import OffloadAdam
+            self.opt = OffloadAdam(self.store, betas=betas, eps=eps)
+        else:
+            self.opt = AdamW(self.store, betas=betas, eps=eps, shard=shard,
+                             group=dp.group if dp is not None else None)
         if dp is not None:
             dp.attach(self.store, self.opt)
         self.wd = weight_decay
