@@ -1,0 +1,90 @@
+"""``brain serve`` (reference: crates/cli/src/run_cli.rs:186-263 flag set: ``--stdio --gpt --yolo
+--max-new --temp --top-k --seed --conf --dbus --dbus-system --dbus-name --reserve-gb --models-dir
+--anthropic [8787] --openai [8788] --openrouter [8789] --api-keys-out FILE --ready-file PATH
+-v/--verbose [0-3]``; HTTP binds localhost only, there is no ``--listen``)."""
+from __future__ import annotations
+
+import json
+import sys
+import time
+from typing import List
+
+from ..cli.args import Args
+from ..utils import shutdown, trace
+from . import auth
+from .executor import Executor
+from .resident import registry_from_env
+from .server import DEFAULT_PORTS, Server
+
+
+def _port_flag(args: List[str], name: str):
+    """``--openai`` alone selects the default port; ``--openai 9000`` a specific one."""
+    if name not in args:
+        return None
+    i = args.index(name)
+    if i + 1 < len(args) and args[i + 1].isdigit():
+        port = int(args[i + 1])
+        del args[i:i + 2]
+        return port
+    del args[i]
+    return DEFAULT_PORTS[name[2:]]
+
+
+def run_serve(argv: List[str], device: str = "auto") -> int:
+    args = list(argv)
+    ports = {p: _port_flag(args, "--" + p) for p in ("anthropic", "openai", "openrouter")}
+    ports = {k: v for k, v in ports.items() if v is not None}
+    a = Args(args)
+    stdio = a.take_flag("--stdio")
+    keys_out = a.take_str("--api-keys-out")
+    ready = a.take_str("--ready-file")
+    verbose = a.int_or("--verbose", a.int_or("-v", 1))
+    defaults = {}
+    for flag, key, conv in (("--max-new", "max_new", int), ("--temp", "temp", float), ("--top-k", "top_k", int),
+                            ("--seed", "seed", int)):
+        v = a.take_str(flag)
+        if v is not None:
+            defaults[key] = conv(v)
+    for f in ("--dbus", "--dbus-system", "--yolo", "--gpt"):
+        if a.take_flag(f):
+            print(f"serve: {f} is not available in this build (no D-Bus / vision stack); ignoring", file=sys.stderr)
+    for f in ("--dbus-name", "--reserve-gb", "--models-dir", "--conf"):
+        a.take_str(f)
+    a.finish()
+    if not stdio and not ports:
+        print("usage: brain serve [--stdio | --openai [PORT] --anthropic [PORT] --openrouter [PORT]] "
+              "[--api-keys-out FILE --ready-file PATH -v N]   (models: BRAIN_MOCK=1, BRAIN_QWEN_WEIGHTS=…)",
+              file=sys.stderr)
+        return 2
+    models = registry_from_env(load=True, device=device)
+    if not models:
+        print("serve: no model selected — set BRAIN_QWEN_WEIGHTS (and BRAIN_QWEN_TOKENIZER) or BRAIN_MOCK=1",
+              file=sys.stderr)
+        return 1
+    ex = Executor(models)
+    shutdown.install()
+    server = None
+    try:
+        if ports:
+            server = Server(ex, ports).start_background()
+            server.announce(lambda s: print(s, flush=True))
+            if keys_out:
+                auth.write_keys(keys_out, server.keys)
+        if ready:
+            shutdown.write_ready_file(ready, json.dumps({"ports": server.bound if server else {},
+                                                         "models": list(models)}) + "\n")
+        if stdio:
+            from .stdio import StdioServer
+            StdioServer(ex, defaults=defaults).serve()
+        else:
+            last = time.time()
+            while not shutdown.wait(0.5):
+                if verbose >= 2 and time.time() - last > 10:
+                    from ..utils.stats import snapshot
+                    print("stats " + json.dumps(snapshot(ex)["executor"]), file=sys.stderr)
+                    last = time.time()
+    finally:
+        if server is not None:
+            server.shutdown()
+        ex.close()
+    return 0

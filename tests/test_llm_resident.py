@@ -1,0 +1,136 @@
+"""The language-model resident on the CPU backend: continuous batching through one long-lived
+scheduler gives the same greedy text as serial generation, stop sequences and cancellation work,
+capacity errors map to ``context_length_exceeded``, and the HTTP layer serves it."""
+import json
+import os
+import sys
+import threading
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from brain_b200.api.capability import ActionError, CancelToken, Invocation  # noqa: E402
+from brain_b200.api.errors import from_exception  # noqa: E402
+from brain_b200.api.executor import Executor  # noqa: E402
+from brain_b200.api.resident import LlmResident  # noqa: E402
+from brain_b200.data.tokenizer import BpeTokenizer  # noqa: E402
+from brain_b200.models.config import QwenConfig  # noqa: E402
+from brain_b200.models.qwen3 import Qwen3  # noqa: E402
+from brain_b200.train import generate  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def llm():
+    tok = BpeTokenizer.byte_level(["t h", "th e"], {"<|im_start|>": 258, "<|im_end|>": 259, "<|endoftext|>": 260})
+    cfg = QwenConfig(vocab=264, block_size=256, n_layers=2, d_model=32, n_heads=4, n_kv_heads=2, head_dim=8, d_ff=64)
+    m = Qwen3(cfg).init_weights(7).eval()
+    r = LlmResident(m, tok, "brain/tiny", ctx=256, max_batch=4)
+    yield r, m, tok
+    r.close()
+
+
+def run(r, **params):
+    inv = Invocation(r.manifest().action("generate").validate(params))
+    pieces = []
+    out = r.run("generate", inv, lambda p: pieces.append(p.text))
+    return out, pieces
+
+
+def test_matches_serial_greedy_and_streams(llm):
+    r, m, tok = llm
+    prompt = "the quick brown fox"
+    out, pieces = run(r, prompt=prompt, chat=False, max_new=12, temp=0.0, ignore_eos=True)
+    ids = tok.encode(prompt)
+    want = generate(m, ids, 12, temp=0.0)
+    assert out.outputs["completion_tokens"] == 12 and out.outputs["finish_reason"] == "length"
+    assert out.outputs["prompt_tokens"] == len(ids)
+    assert out.text() == tok.decode(want, skip_special=True)
+    assert "".join(pieces) == out.text()
+
+
+def test_concurrent_equals_serial(llm):
+    r, m, tok = llm
+    prompts = [f"prompt number {i} says" for i in range(6)]
+    serial = [run(r, prompt=p, chat=False, max_new=10, temp=0.0, ignore_eos=True)[0].text() for p in prompts]
+    got = [None] * len(prompts)
+
+    def work(i):
+        got[i] = run(r, prompt=prompts[i], chat=False, max_new=10, temp=0.0, ignore_eos=True)[0].text()
+    ts = [threading.Thread(target=work, args=(i,)) for i in range(len(prompts))]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert got == serial
+    assert r.stats()["finished"] >= 12
+
+
+def test_chat_template_and_sampling_seed(llm):
+    r, m, tok = llm
+    a, _ = run(r, messages=json.dumps([{"role": "user", "content": "hi"}]), max_new=8, temp=0.9, top_k=20, seed=3, ignore_eos=True)
+    b, _ = run(r, messages=json.dumps([{"role": "user", "content": "hi"}]), max_new=8, temp=0.9, top_k=20, seed=3, ignore_eos=True)
+    assert a.text() == b.text()
+    want = len(tok.encode(tok.apply_chat_template([("user", "hi")], True)))
+    assert a.outputs["prompt_tokens"] == want
+
+
+def test_stop_sequence_truncates(llm):
+    r, m, tok = llm
+    full, _ = run(r, prompt="abc abc abc", chat=False, max_new=24, temp=0.0, ignore_eos=True)
+    text = full.text()
+    visible = [c for c in text[3:] if c.isprintable() and c != "�"]
+    if not visible:
+        pytest.skip("tiny random model produced no printable text to stop on")
+    stop = visible[0]
+    out, pieces = run(r, prompt="abc abc abc", chat=False, max_new=24, temp=0.0, ignore_eos=True, stop=json.dumps([stop]))
+    assert out.outputs["finish_reason"] == "stop_sequence"
+    assert out.text() == text[:text.index(stop)] and stop not in "".join(pieces)
+
+
+def test_capacity_error_maps_to_context_length(llm):
+    r, _, _ = llm
+    with pytest.raises(ActionError) as e:
+        run(r, prompt="x" * 300, chat=False, max_new=8)
+    err = from_exception(e.value)
+    assert err.code == "context_length_exceeded" and err.status == 400 and "256" in err.message
+
+
+def test_cancel_frees_blocks(llm):
+    r, _, _ = llm
+    free0 = r.stats()["free_blocks"]
+    tok = CancelToken()
+    inv = Invocation(r.manifest().action("generate").validate(dict(prompt="go on", chat=False, max_new=200, temp=0.0, ignore_eos=True)), cancel=tok)
+    n = [0]
+
+    def prog(p):
+        n[0] += 1
+        if n[0] == 3:
+            tok.cancel()
+    with pytest.raises(ActionError) as e:
+        r.run("generate", inv, prog)
+    assert e.value.kind == "cancelled" and n[0] < 200
+    out, _ = run(r, prompt="after", chat=False, max_new=4, temp=0.0, ignore_eos=True)
+    assert out.outputs["completion_tokens"] == 4
+    assert r.stats()["free_blocks"] >= free0 - 2       # only prefix-cache blocks may stay resident
+
+
+def test_http_serves_the_model(llm):
+    from brain_b200.api.server import Server
+    import urllib.request
+    r, _, _ = llm
+    ex = Executor({r.id: r})
+    s = Server(ex, {"openai": 0}).start_background()
+    try:
+        body = json.dumps({"model": "brain/tiny", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 6,
+                           "temperature": 0}).encode()
+        req = urllib.request.Request(f"http://127.0.0.1:{s.bound['openai']}/v1/chat/completions", data=body,
+                                     headers={"Authorization": "Bearer " + s.keys["openai"], "Content-Type": "application/json"})
+        d = json.load(urllib.request.urlopen(req, timeout=60))
+        assert d["usage"]["completion_tokens"] <= 6 and d["choices"][0]["finish_reason"] in ("stop", "length")
+        req = urllib.request.Request(f"http://127.0.0.1:{s.bound['openai']}/v1/models",
+                                     headers={"Authorization": "Bearer " + s.keys["openai"]})
+        d = json.load(urllib.request.urlopen(req, timeout=60))
+        assert d["data"][0]["context_length"] == 256
+    finally:
+        s.shutdown()
+        ex.pool.shutdown(wait=False)
