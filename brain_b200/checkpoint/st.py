@@ -118,16 +118,20 @@ class StWriter:
                  dtype: str = "F32"):
         self.path = str(path)
         self.dtype = dtype
-        self.specs = [(n, tuple(int(x) for x in (s if isinstance(s, (tuple, list)) else (s,))))
-                      for n, s in specs]
+        self.specs = []
+        self.dtypes = {}
+        for spec in specs:
+            n, s = spec[0], spec[1]
+            self.specs.append((n, tuple(int(x) for x in (s if isinstance(s, (tuple, list)) else (s,)))))
+            self.dtypes[n] = spec[2] if len(spec) > 2 else dtype      # optional per-tensor dtype
         hdr = {"__metadata__": {k: str(v) for k, v in metadata.items()}}
         off = 0
         for n, shape in self.specs:
             numel = 1
             for s in shape:
                 numel *= s
-            nb = numel * _ES[dtype]
-            hdr[n] = {"dtype": dtype, "shape": list(shape), "data_offsets": [off, off + nb]}
+            nb = numel * _ES[self.dtypes[n]]
+            hdr[n] = {"dtype": self.dtypes[n], "shape": list(shape), "data_offsets": [off, off + nb]}
             off += nb
         raw = json.dumps(hdr, separators=(",", ":")).encode("utf-8")
         raw += b" " * ((8 - len(raw) % 8) % 8)
@@ -140,13 +144,18 @@ class StWriter:
         exp, shape = self.specs[self._i]
         if exp != name:
             raise ValueError(f"tensors must be written in declared order: expected {exp}, got {name}")
-        flat = t.detach().reshape(-1).to(device="cpu", dtype=torch.float32).contiguous()
+        dt = self.dtypes[name]
         numel = 1
         for s in shape:
             numel *= s
-        if flat.numel() != numel:
-            raise ValueError(f"{name}: got {flat.numel()} elements, declared {numel}")
-        rc = _host.lib().bbh_stw_append_f32(self._h, flat.data_ptr(), numel, _DT[self.dtype])
+        if t.numel() != numel:
+            raise ValueError(f"{name}: got {t.numel()} elements, declared {numel}")
+        if dt in _DT:
+            flat = t.detach().reshape(-1).to(device="cpu", dtype=torch.float32).contiguous()
+            rc = _host.lib().bbh_stw_append_f32(self._h, flat.data_ptr(), numel, _DT[dt])
+        else:
+            flat = t.detach().reshape(-1).to(device="cpu", dtype=_TORCH[dt]).contiguous()
+            rc = _host.lib().bbh_stw_append_raw(self._h, flat.data_ptr(), numel * _ES[dt])
         if rc != 0:
             raise IOError(f"write of {name} failed ({rc})")
         self._i += 1

@@ -99,9 +99,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     if r.kind == "arch":
         return _dispatch_arch(r.arch, r.rest, device)
     if r.kind == "import":
-        return _import_file(r.rest, device)
+        return _import_file(r.rest, device) or 0
     if r.kind == "quantize":
-        return _quantize(r.rest, device)
+        return _quantize(r.rest, device) or 0
     print(f"unknown command {r.word!r}; try `brain help`", file=sys.stderr)
     return 2
 
@@ -122,7 +122,11 @@ def _dispatch_arch(arch_id: str, rest: List[str], device: str) -> int:
         from .toymoe_cli import run_toymoe
         return run_toymoe(rest, device)
     if a.id == "splat":
-        from .splat_cli import run_splat
+        try:
+            from .splat_cli import run_splat
+        except ImportError:
+            print("brain splat: the rasteriser is not part of this build", file=sys.stderr)
+            return 3
         return run_splat(rest, device)
     return 2
 

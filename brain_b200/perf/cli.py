@@ -1,0 +1,120 @@
+"""``brain perf {list,run,compare,gate}`` (reference: crates/cli/src/perf_cli.rs — workloads and
+targets by name, one JSON row per run, compare/gate between saved rows)."""
+from __future__ import annotations
+
+import json
+import sys
+import time
+from typing import List
+
+from ..cli.args import Args
+from . import fidelity, gate
+from .driver import drive
+from .metrics import Summary
+from .targets import FakeTarget, HttpTarget, SchedulerTarget, synth_qwen
+from .workload import Arrival, standard, standard_names
+
+
+def _arrival(a: Args) -> Arrival:
+    rate = a.float_or("--rate", 0.0)
+    if a.take_flag("--saturated"):
+        return Arrival.saturated()
+    if rate > 0:
+        return Arrival.rate(rate, a.float_or("--burstiness", 1.0))
+    return Arrival.closed_loop(a.int_or("--concurrency", 8))
+
+
+def _make_target(spec: str, device: str, a_conc: int, ctx: int, weights: str):
+    if spec == "fake":
+        return (lambda: FakeTarget(max(a_conc, 1), 2)), 32000
+    if spec.startswith("qwen-synth:"):
+        from ..train import pick_device
+        dev = pick_device(device)
+        model = synth_qwen(spec.split(":", 1)[1], dev)
+        return (lambda: SchedulerTarget(model, max_batch=max(a_conc, 1), ctx=ctx, weights=weights, name=spec)), model.cfg.vocab
+    if spec.startswith("weights:"):
+        import torch
+        from ..checkpoint import st
+        from ..train import pick_device
+        dev = pick_device(device)
+        model, _, _ = st.load_model(spec.split(":", 1)[1], device=dev,
+                                    dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32)
+        model.eval()
+        return (lambda: SchedulerTarget(model, max_batch=max(a_conc, 1), ctx=ctx, weights=weights, name=spec)), model.cfg.vocab
+    if spec.startswith("http:"):
+        # http:<base_url>|<api_key>|<model>
+        base, key, model = spec[5:].split("|")
+        return (lambda: HttpTarget(base, key, model)), 32000
+    raise ValueError(f"unknown target {spec!r}: fake | qwen-synth:LxDxH[xV] | weights:FILE | http:URL|KEY|MODEL")
+
+
+def run_perf(argv: List[str], device: str = "auto") -> int:
+    sub = argv[0] if argv else None
+    if sub == "list":
+        print("workloads: " + " ".join(standard_names()))
+        print("targets:   fake | qwen-synth:LxDxH[xV] | weights:FILE | http:URL|KEY|MODEL")
+        print("arrivals:  --concurrency N (closed loop) | --saturated | --rate R [--burstiness K]")
+        return 0
+    if sub == "run":
+        a = Args(argv[1:])
+        name = a.positional() or "interactive"
+        target = a.str_or("--target", "fake")
+        n = a.int_or("--requests", 32)
+        seed = a.int_or("--seed", 0)
+        ctx = a.int_or("--ctx", 4096)
+        weights = a.str_or("--weights-dtype", "bf16")
+        out = a.take_str("--out")
+        skip_fid = a.take_flag("--no-fidelity")
+        arrival = _arrival(a)
+        a.finish()
+        wl = standard(name, arrival, n, seed)
+        if wl is None:
+            print(f"unknown workload {name!r}; have: {' '.join(standard_names())}", file=sys.stderr)
+            return 2
+        try:
+            make, vocab = _make_target(target, device, arrival.concurrency if arrival.kind == "closed_loop" else 256, ctx, weights)
+            wl.vocab = vocab
+        except ValueError as e:
+            print(str(e), file=sys.stderr)
+            return 2
+        fid = None
+        if not skip_fid and not target.startswith("http:"):
+            fid = fidelity.serial_vs_concurrent(make, wl, n=min(4, n))
+            if not fid.passed:
+                print(f"fidelity FAILED: serial and concurrent outputs differ ({fid.matching}/{fid.compared} exact)",
+                      file=sys.stderr)
+        t = make()
+        try:
+            run = drive(t, wl)
+        finally:
+            t.close()
+        s = Summary.build(run.records, run.wall_s, wl.classes[0].slo)
+        row = {"workload": wl.to_json(), "target": dict(t.info, spec=target), "summary": s.to_json(),
+               "fidelity": fid.to_json() if fid else None, "when": time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())}
+        text = json.dumps(row)
+        if out:
+            open(out, "w").write(text + "\n")
+        j = s.to_json()
+        print(f"{name} on {target}: {s.completed}/{s.requests} done in {s.wall_s:.2f}s  out {s.output_per_s:.1f}/s  "
+              f"goodput {s.goodput_per_s:.1f}/s  TTFA p50 {j['ttfa_ms'].get('p50', 0) or 0:.1f} ms p99 "
+              f"{j['ttfa_ms'].get('p99', 0) or 0:.1f} ms  TPOA p50 {j['tpoa_ms'].get('p50', 0) or 0:.2f} ms  "
+              f"SLO {100 * s.slo_attainment:.0f}%")
+        if not out:
+            print(text)
+        return 0 if (fid is None or fid.passed) else 1
+    if sub in ("compare", "gate"):
+        a = Args(argv[1:])
+        ca, ba = a.positional(), a.positional()
+        floor = 1.0 - a.float_or("--tolerance", 0.1)
+        a.finish()
+        if not ca or not ba:
+            print(f"usage: brain perf {sub} CANDIDATE.json BASELINE.json [--tolerance 0.1]", file=sys.stderr)
+            return 2
+        c = json.loads(open(ca).read())["summary"]
+        b = json.loads(open(ba).read())["summary"]
+        checks = gate.compare(c, b, floor)
+        print(gate.render(checks, floor))
+        return 0 if (sub == "compare" or gate.passed(checks)) else 1
+    print("usage: brain perf list | run <workload> [--target T --requests N --concurrency C --out F] | "
+          "compare A B | gate A B [--tolerance X]", file=sys.stderr)
+    return 2
