@@ -15,7 +15,7 @@ import torch.nn as nn
 
 from ..ops import functional as F
 from ..ops import reference as ref
-from ..ops.attention import flash_attention
+from ..ops.attention import attention_qkv, flash_attention
 from .config import QwenConfig
 
 
@@ -44,9 +44,7 @@ class QwenBlock(nn.Module):
         qkv = F.linear(h, self.wqkv, self.bqkv)
         if self.lora is not None:
             qkv = self.lora.add(self, "qkv", h, qkv)
-        qk = F.qknorm_rope(qkv, self.q_norm, self.k_norm, cos, sin, pos, hq, hk, hd, cfg.rms_eps)
-        v = qkv[:, (hq + hk) * hd:]
-        o = flash_attention(qk[:, : hq * hd], qk[:, hq * hd:], v, B, T, hq, hk, hd, causal=True)
+        o = attention_qkv(qkv, self.q_norm, self.k_norm, cos, sin, pos, B, T, hq, hk, hd, cfg.rms_eps)
         y = F.linear(o, self.wo)
         if self.lora is not None:
             y = self.lora.add(self, "wo", o, y)

@@ -267,6 +267,14 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// bf16x2 pack on the integer pipe: round-half-up (add 0x8000, keep the upper halves) with one PRMT.
+// The cvt.rn.bf16x2.f32 form shares the quarter-rate unit with ex2, which is the scarce resource
+// in the attention softmax loops; this form differs from round-to-nearest-even only on exact ties.
+// Inputs must be finite.
+__device__ __forceinline__ uint32_t pack_bf16x2_alu(float lo, float hi) {
+  const uint32_t a = __float_as_uint(lo) + 0x8000u, b = __float_as_uint(hi) + 0x8000u;
+  return __byte_perm(a, b, 0x7632);
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

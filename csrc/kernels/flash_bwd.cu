@@ -10,7 +10,8 @@
 //             dV += P^T dO, dK += dS^T Q             (TMEM accumulators)
 // Operands that are needed "transposed" are not copied: the same 128-byte-swizzled shared-memory
 // tile is described K-major for one MMA and MN-major for the other.
-// Roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..5 softmax.
+// Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9 softmax
+// (two warpgroups that alternate 64-wide units so the tensor core never waits for the exponentials).
 // Replaces crates/kernels/wgsl/gqa_bwd_{dscores,dv,dq,dk}.wgsl (which read a saved T x T probs buffer).
 #include "../common/host.hpp"
 #include "../common/ptx.cuh"
@@ -28,6 +29,7 @@ struct FaBwdArgs {
   float scale, scale_log2;
   int causal;
   int* err;
+  long long* tl;  // optional clock64 stamps of CTA (0,0,0): [0,4096) MMA, then one 4096 block per warpgroup
 };
 
 static constexpr int SUB = 128 * 128;  // bytes of a [128 rows][64 bf16] swizzled sub-tile
@@ -52,6 +54,21 @@ __device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int t) {
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int t) {
   return umma_smem_desc(base + t * 2048, SUB, 1024);
 }
+
+// Hoisted descriptor arithmetic for the single MMA-issuing thread: the upper descriptor word is a
+// constant, the lower word is (address >> 4) | (lbo >> 4) << 16, so stepping through a tile is one
+// 32-bit add per operand instead of rebuilding the 64-bit descriptor.
+static constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t base) {
+  return ((base & 0x3FFFF) >> 4) | (1u << 16);
+}
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t base) {
+  return ((base & 0x3FFFF) >> 4) | ((uint32_t)(SUB >> 4) << 16);
+}
+__device__ __forceinline__ uint64_t desc_of(uint32_t lo) { return ((uint64_t)DESC_HI << 32) | lo; }
+// offsets, in 16-byte units, of k-step t inside a tile
+__device__ __forceinline__ constexpr uint32_t kstep_kmajor(int t) { return (t / 4) * (SUB >> 4) + (t % 4) * 2; }
+__device__ __forceinline__ constexpr uint32_t kstep_mnmajor(int t) { return t * 128; }
 
 // ------------------------------------------------------------------------------------ delta
 __global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ o, int ldo,
@@ -79,6 +96,15 @@ __global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ o, int ldo,
 }
 
 // ------------------------------------------------------------------------------------ dQ
+// Work is cut into UNITS of 64 key columns.  Two softmax warpgroups alternate units (warpgroup g
+// owns half g of every 128-row K/V tile and TMEM buffer g), so while one warpgroup turns S/dP of
+// its unit into dS, the tensor core already runs S/dP of the other unit and the dQ MMA of the unit
+// before: tensor-core order is  SdP(0,0) SdP(0,1) dQ(0,0) SdP(1,0) dQ(0,1) SdP(1,1) dQ(1,0) ...
+// MMAs execute in issue order, so S of unit (j+1,g) may be issued straight after dQ of unit (j,g)
+// although it overwrites the TMEM columns that dQ reads its dS operand from.
+// Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9 softmax.
+// TMEM columns: S[g] at g*64, dP[g] at 128 + g*64 (64 fp32 columns each; the packed bf16 dS of a
+// unit overwrites the first 32 columns of its S buffer), dQ at 256.
 template <int HD>
 struct DqCfg {
   static constexpr int NSUB = HD / 64;
@@ -92,8 +118,18 @@ struct DqCfg {
   static constexpr int SMEM = SMEM_MIN < 120 * 1024 ? 120 * 1024 : SMEM_MIN;
 };
 
+static constexpr int BWD_THREADS = 320;
+
+#define BWD_STAMP(slot) do { if (tl) tl[(slot)] = clock64(); } while (0)
+
+// Named barrier over the 128 threads of softmax warpgroup g (barrier 0 is __syncthreads).
+__device__ __forceinline__ void wg_sync(int g) {
+  if (g == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+  else asm volatile("bar.sync 2, 128;" ::: "memory");
+}
+
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const FaBwdArgs args) {
@@ -107,15 +143,15 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sK = smem + Cfg::OFF_K;
   uint8_t* sV = smem + Cfg::OFF_V;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
-  uint64_t* q_full = bars;        // Q and dO
-  uint64_t* k_full = bars + 1;    // 2
-  uint64_t* k_empty = bars + 3;   // 2
-  uint64_t* v_full = bars + 5;    // 2
-  uint64_t* v_empty = bars + 7;   // 2
-  uint64_t* sdp_full = bars + 9;  // 1
-  uint64_t* ds_ready = bars + 10; // 1 (128 arrivals)
-  uint64_t* dq_done = bars + 11;  // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* q_full = bars;         // Q and dO
+  uint64_t* k_full = bars + 1;     // 2 stages
+  uint64_t* k_empty = bars + 3;    // 2
+  uint64_t* v_full = bars + 5;     // 2
+  uint64_t* v_empty = bars + 7;    // 2
+  uint64_t* sdp_full = bars + 9;   // 2 (one per TMEM buffer / warpgroup)
+  uint64_t* ds_ready = bars + 11;  // 2 (128 arrivals each)
+  uint64_t* dq_done = bars + 13;   // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = gridDim.x - 1 - blockIdx.x;
@@ -137,9 +173,9 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
+      mbar_init(&sdp_full[i], 1);
+      mbar_init(&ds_ready[i], 128);
     }
-    mbar_init(sdp_full, 1);
-    mbar_init(ds_ready, 128);
     mbar_init(dq_done, 1);
     mbar_fence_init();
   }
@@ -151,7 +187,8 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 256;
+  const uint32_t tDQ = tmem_base + 256;
+  long long* tl = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 ? args.tl : nullptr;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -183,43 +220,73 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc(1, 1, 1, 0, 0, 128, 128);
+      constexpr uint32_t idesc_s = umma_idesc(1, 1, 1, 0, 0, 128, 64);
       constexpr uint32_t idesc_dq = umma_idesc(1, 1, 1, 0, 1, 128, HD);
       bool ok = mbar_wait(q_full, 0);
       if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
       const uint32_t aq = smem_u32(sQ), ado = smem_u32(sDO);
-      for (int j = 0; j < n_blocks && ok; ++j) {
+      // S and dP of half g of block j into TMEM buffer g
+      const uint32_t lq = desc_lo_kmajor(smem_u32(sQ)), ldo = desc_lo_kmajor(smem_u32(sDO));
+      auto issue_sdp = [&](int j, int g) {
         const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_full[st], ph) || !mbar_wait(&v_full[st], ph)) {
+        const uint32_t lk = desc_lo_kmajor(smem_u32(sK + st * Cfg::TILE) + g * 8192);
+        const uint32_t lv = desc_lo_kmajor(smem_u32(sV + st * Cfg::TILE) + g * 8192);
+        const uint32_t tS = tmem_base + g * 64, tDP = tmem_base + 128 + g * 64;
+#pragma unroll
+        for (int t = 0; t < HD / 16; ++t)
+          umma_f16_ss(tS, desc_of(lq + kstep_kmajor(t)), desc_of(lk + kstep_kmajor(t)), idesc_s, t != 0);
+#pragma unroll
+        for (int t = 0; t < HD / 16; ++t)
+          umma_f16_ss(tDP, desc_of(ldo + kstep_kmajor(t)), desc_of(lv + kstep_kmajor(t)), idesc_s, t != 0);
+        umma_commit(&sdp_full[g]);
+        if (g == 1) umma_commit(&v_empty[st]);
+      };
+      if (ok && n_blocks > 0) {
+        if (!mbar_wait(&k_full[0], 0) || !mbar_wait(&v_full[0], 0)) {
           set_error(args.err, ERR_WAIT_MMA_FULL);
           ok = false;
-          break;
+        } else {
+          tc_fence_after();
+          issue_sdp(0, 0);
+          issue_sdp(0, 1);
         }
-        tc_fence_after();
-        const uint32_t bk = smem_u32(sK + st * Cfg::TILE), bv = smem_u32(sV + st * Cfg::TILE);
-#pragma unroll
-        for (int t = 0; t < HD / 16; ++t)
-          umma_f16_ss(tS, desc_kmajor(aq, t), desc_kmajor(bk, t), idesc_s, t != 0);
-#pragma unroll
-        for (int t = 0; t < HD / 16; ++t)
-          umma_f16_ss(tDP, desc_kmajor(ado, t), desc_kmajor(bv, t), idesc_s, t != 0);
-        umma_commit(sdp_full);
-        umma_commit(&v_empty[st]);
-        if (!mbar_wait(ds_ready, j & 1)) {
-          set_error(args.err, ERR_WAIT_MMA_TMEM);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-#pragma unroll
-        for (int t = 0; t < 8; ++t)
-          umma_f16_ts(tDQ, tS + t * 8, desc_mnmajor(bk, t), idesc_dq, (j | t) != 0);
-        umma_commit(dq_done);
-        umma_commit(&k_empty[st]);
       }
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t lkm = desc_lo_mnmajor(smem_u32(sK + st * Cfg::TILE));
+        for (int g = 0; g < 2 && ok; ++g) {
+          if (!mbar_wait(&ds_ready[g], j & 1)) {
+            set_error(args.err, ERR_WAIT_MMA_TMEM);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (2 * j + g < 1024) BWD_STAMP(4 * j + 2 * g);
+          const uint32_t tS = tmem_base + g * 64;
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            umma_f16_ts(tDQ, tS + t * 8, desc_of(lkm + g * 512 + kstep_mnmajor(t)), idesc_dq,
+                        (j | g | t) != 0);
+          if (g == 1) umma_commit(&k_empty[st]);
+          if (j + 1 < n_blocks) {
+            if (g == 0) {
+              const uint32_t ph = ((j + 1) >> 1) & 1;
+              if (!mbar_wait(&k_full[st ^ 1], ph) || !mbar_wait(&v_full[st ^ 1], ph)) {
+                set_error(args.err, ERR_WAIT_MMA_FULL);
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+            }
+            issue_sdp(j + 1, g);
+          }
+          if (2 * j + g < 1024) BWD_STAMP(4 * j + 2 * g + 1);
+        }
+      }
+      if (ok) umma_commit(dq_done);
     }
   } else {
+    const int g = (warp - 2) >> 2;  // warpgroup = half of every K/V tile = TMEM buffer
     const int sw = warp & 3;
     const int row = sw * 32 + lane;
     const int q_idx = q0 + row;
@@ -228,66 +295,57 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const bool row_ok = q_idx < T;
     const size_t stat = ((size_t)b * args.hq + h) * T + (row_ok ? q_idx : 0);
     const float lse2 = row_ok ? args.lse[stat] * 1.4426950408889634f : INFINITY;
-    const float dlt = row_ok ? args.delta[stat] : 0.f;
+    const float dlt = row_ok ? -args.delta[stat] * args.scale : 0.f;  // -delta * scale
+    const uint32_t tS = tmem_base + g * 64 + lane_sel, tDP = tmem_base + 128 + g * 64 + lane_sel;
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
-      ok = mbar_wait(sdp_full, j & 1);
+      ok = mbar_wait(&sdp_full[g], j & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      if (j > 0) {  // already complete (S_j was issued after dQ_{j-1}); keeps the phase in step
-        ok = mbar_wait(dq_done, (j - 1) & 1);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
-      const int kv0 = j * 128;
-      const bool need_mask = (kv0 + 127 > kv_limit_row);
-      // two halves of 64 kv columns; dS (packed bf16) overwrites the S columns already consumed
-#pragma unroll 1
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t rs0[32], rs1[32], rp0[32], rp1[32];
+      if ((warp & 3) == 2 && lane == 0 && j < 1024) BWD_STAMP(4096 * (1 + g) + 2 * j);
+      const int kv0 = j * 128 + g * 64;
+      const bool need_mask = (kv0 + 63 > kv_limit_row);
+      uint32_t pk[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rp[32];
         __syncwarp();
-        tmem_ld32(tS + lane_sel + hf * 64, rs0);
-        tmem_ld32(tS + lane_sel + hf * 64 + 32, rs1);
-        tmem_ld32(tDP + lane_sel + hf * 64, rp0);
-        tmem_ld32(tDP + lane_sel + hf * 64 + 32, rp1);
+        tmem_ld32(tS + c * 32, rs);
+        tmem_ld32(tDP + c * 32, rp);
         tmem_wait_ld();
-        const int lim = kv_limit_row - (kv0 + hf * 64);
-        uint32_t pk[32];
+        const int lim = kv_limit_row - (kv0 + c * 32);
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(rs0[i]) * args.scale_log2 - lse2);
-          float p1 = exp2f(__uint_as_float(rs0[i + 1]) * args.scale_log2 - lse2);
-          float p2 = exp2f(__uint_as_float(rs1[i]) * args.scale_log2 - lse2);
-          float p3 = exp2f(__uint_as_float(rs1[i + 1]) * args.scale_log2 - lse2);
+          float p0 = exp2f(__uint_as_float(rs[i]) * args.scale_log2 - lse2);
+          float p1 = exp2f(__uint_as_float(rs[i + 1]) * args.scale_log2 - lse2);
           if (need_mask) {
             if (i > lim) p0 = 0.f;
             if (i + 1 > lim) p1 = 0.f;
-            if (i + 32 > lim) p2 = 0.f;
-            if (i + 33 > lim) p3 = 0.f;
           }
-          pk[i >> 1] = pack_bf16x2(p0 * (__uint_as_float(rp0[i]) - dlt) * args.scale,
-                                   p1 * (__uint_as_float(rp0[i + 1]) - dlt) * args.scale);
-          pk[16 + (i >> 1)] = pack_bf16x2(p2 * (__uint_as_float(rp1[i]) - dlt) * args.scale,
-                                          p3 * (__uint_as_float(rp1[i + 1]) - dlt) * args.scale);
+          pk[c * 16 + (i >> 1)] = pack_bf16x2_alu(p0 * fmaf(__uint_as_float(rp[i]), args.scale, dlt),
+                                              p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, dlt));
         }
-        tmem_st32(tS + lane_sel + hf * 32, pk);
       }
+      // all 64 S columns of this unit are in registers: the packed dS may overwrite them
+      tmem_st32(tS, pk);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(ds_ready);
+      mbar_arrive(&ds_ready[g]);
+      if ((warp & 3) == 2 && lane == 0 && j < 1024) BWD_STAMP(4096 * (1 + g) + 2 * j + 1);
     }
     if (ok) {
-      ok = mbar_wait(dq_done, (n_blocks - 1) & 1);
+      ok = mbar_wait(dq_done, 0);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (!ok) {
       if (lane == 0) set_error(args.err, ERR_WAIT_SOFTMAX);
     } else {
       tc_fence_after();
+      // warpgroup g writes columns [g*HD/2, (g+1)*HD/2) of dQ
       __nv_bfloat16* orow = args.dQ + (size_t)(b * T + q_idx) * args.lddq + h * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = g * (HD / 64); c < (g + 1) * (HD / 64); ++c) {
         uint32_t r[32];
         __syncwarp();
         tmem_ld32(tDQ + lane_sel + c * 32, r);
@@ -315,22 +373,26 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------ dK, dV
+// Same unit pipeline with the roles of rows and columns swapped: a unit is 64 QUERY rows of the
+// current (head, query tile) iteration; warpgroup g owns half g of every 128-row Q/dO tile.
+// TMEM columns: S^T[g] at g*64, dP^T[g] at 128 + g*64, dV at 256, dK at 384.  P^T (packed bf16)
+// overwrites the first 32 columns of its S^T buffer, dS^T those of its dP^T buffer.
 template <int HD>
 struct DkvCfg {
   static constexpr int NSUB = HD / 64;
   static constexpr int TILE = NSUB * SUB;
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + TILE;
-  static constexpr int OFF_Q = OFF_V + TILE;
-  static constexpr int OFF_DO = OFF_Q + TILE;
-  static constexpr int OFF_STAT = OFF_DO + TILE;  // lse2[128], delta[128]
+  static constexpr int OFF_Q = OFF_V + TILE;        // 2 stages
+  static constexpr int OFF_DO = OFF_Q + 2 * TILE;   // 2 stages
+  static constexpr int OFF_STAT = OFF_DO + 2 * TILE;  // per warpgroup: lse2[64], delta[64]
   static constexpr int OFF_BAR = OFF_STAT + 1024;
   static constexpr int SMEM_MIN = OFF_BAR + 256 + 1024;
   static constexpr int SMEM = SMEM_MIN < 120 * 1024 ? 120 * 1024 : SMEM_MIN;
 };
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                   const FaBwdArgs args) {
@@ -343,16 +405,15 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint8_t* sV = smem + Cfg::OFF_V;
   uint8_t* sQ = smem + Cfg::OFF_Q;
   uint8_t* sDO = smem + Cfg::OFF_DO;
-  float* s_lse2 = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);
-  float* s_delta = s_lse2 + 128;
+  float* s_stat = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
-  uint64_t* kv_full = bars;        // K and V tiles (once)
-  uint64_t* qdo_full = bars + 1;   // Q and dO of the current iteration
-  uint64_t* qdo_empty = bars + 2;
-  uint64_t* st_full = bars + 3;    // S^T and dP^T ready in TMEM
-  uint64_t* pds_ready = bars + 4;  // P^T, dS^T written (128 arrivals)
-  uint64_t* dkv_done = bars + 5;   // dV/dK MMAs of the iteration finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* kv_full = bars;         // K and V tiles (once)
+  uint64_t* qdo_full = bars + 1;    // 2 stages: Q and dO of an iteration
+  uint64_t* qdo_empty = bars + 3;   // 2
+  uint64_t* st_full = bars + 5;     // 2: S^T and dP^T of a unit ready in TMEM buffer g
+  uint64_t* pds_ready = bars + 7;   // 2: P^T, dS^T written (128 arrivals each)
+  uint64_t* dkv_done = bars + 9;    // all dV/dK MMAs finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kt = blockIdx.x;
@@ -373,10 +434,12 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    mbar_init(qdo_full, 1);
-    mbar_init(qdo_empty, 1);
-    mbar_init(st_full, 1);
-    mbar_init(pds_ready, 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qdo_full[i], 1);
+      mbar_init(&qdo_empty[i], 1);
+      mbar_init(&st_full[i], 1);
+      mbar_init(&pds_ready[i], 128);
+    }
     mbar_init(dkv_done, 1);
     mbar_fence_init();
   }
@@ -388,8 +451,8 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tST = tmem_base, tDPT = tmem_base + 128, tDV = tmem_base + 256,
-                 tDK = tmem_base + 384;
+  const uint32_t tDV = tmem_base + 256, tDK = tmem_base + 384;
+  long long* tl = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && args.tl ? args.tl + 3 * 4096 : nullptr;
 
   if (warp == 0) {
     if (lane == 0 && n_iter > 0) {
@@ -402,154 +465,192 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       for (int it = 0; it < n_iter; ++it) {
         const int h = kvh * group + it / per_head;
         const int qt = qt_first + it % per_head;
-        if (!mbar_wait(qdo_empty, (it & 1) ^ 1)) {
+        const int st = it & 1;
+        if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1)) {
           set_error(args.err, ERR_WAIT_PRODUCER);
           break;
         }
-        mbar_expect_tx(qdo_full, 2 * Cfg::TILE);
+        mbar_expect_tx(&qdo_full[st], 2 * Cfg::TILE);
 #pragma unroll
         for (int c = 0; c < NSUB; ++c) {
-          tma_load_2d(sQ + c * SUB, &tmQ, qdo_full, h * HD + c * 64, b * T + qt * 128);
-          tma_load_2d(sDO + c * SUB, &tmDO, qdo_full, h * HD + c * 64, b * T + qt * 128);
+          tma_load_2d(sQ + st * Cfg::TILE + c * SUB, &tmQ, &qdo_full[st], h * HD + c * 64,
+                      b * T + qt * 128);
+          tma_load_2d(sDO + st * Cfg::TILE + c * SUB, &tmDO, &qdo_full[st], h * HD + c * 64,
+                      b * T + qt * 128);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && n_iter > 0) {
-      constexpr uint32_t idesc_st = umma_idesc(1, 1, 1, 0, 0, 128, 128);
+      constexpr uint32_t idesc_st = umma_idesc(1, 1, 1, 0, 0, 128, 64);
       constexpr uint32_t idesc_acc = umma_idesc(1, 1, 1, 0, 1, 128, HD);
       bool ok = mbar_wait(kv_full, 0);
       if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
-      const uint32_t ak = smem_u32(sK), av = smem_u32(sV), bq = smem_u32(sQ), bdo = smem_u32(sDO);
-      for (int it = 0; it < n_iter && ok; ++it) {
-        if (!mbar_wait(qdo_full, it & 1)) {
+      const uint32_t ak = smem_u32(sK), av = smem_u32(sV);
+      const uint32_t lkk = desc_lo_kmajor(ak), lvv = desc_lo_kmajor(av);
+      auto issue_st = [&](int it, int g) {
+        const int st = it & 1;
+        const uint32_t lq = desc_lo_kmajor(smem_u32(sQ + st * Cfg::TILE) + g * 8192);
+        const uint32_t ldo = desc_lo_kmajor(smem_u32(sDO + st * Cfg::TILE) + g * 8192);
+        const uint32_t tST = tmem_base + g * 64, tDPT = tmem_base + 128 + g * 64;
+#pragma unroll
+        for (int t = 0; t < HD / 16; ++t)
+          umma_f16_ss(tST, desc_of(lkk + kstep_kmajor(t)), desc_of(lq + kstep_kmajor(t)), idesc_st, t != 0);
+#pragma unroll
+        for (int t = 0; t < HD / 16; ++t)
+          umma_f16_ss(tDPT, desc_of(lvv + kstep_kmajor(t)), desc_of(ldo + kstep_kmajor(t)), idesc_st, t != 0);
+        umma_commit(&st_full[g]);
+      };
+      if (ok) {
+        if (!mbar_wait(&qdo_full[0], 0)) {
           set_error(args.err, ERR_WAIT_MMA_FULL);
           ok = false;
-          break;
+        } else {
+          tc_fence_after();
+          issue_st(0, 0);
+          issue_st(0, 1);
         }
-        tc_fence_after();
-#pragma unroll
-        for (int t = 0; t < HD / 16; ++t)
-          umma_f16_ss(tST, desc_kmajor(ak, t), desc_kmajor(bq, t), idesc_st, t != 0);
-#pragma unroll
-        for (int t = 0; t < HD / 16; ++t)
-          umma_f16_ss(tDPT, desc_kmajor(av, t), desc_kmajor(bdo, t), idesc_st, t != 0);
-        umma_commit(st_full);
-        if (!mbar_wait(pds_ready, it & 1)) {
-          set_error(args.err, ERR_WAIT_MMA_TMEM);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-#pragma unroll
-        for (int t = 0; t < 8; ++t)
-          umma_f16_ts(tDV, tST + t * 8, desc_mnmajor(bdo, t), idesc_acc, (it | t) != 0);
-#pragma unroll
-        for (int t = 0; t < 8; ++t)
-          umma_f16_ts(tDK, tDPT + t * 8, desc_mnmajor(bq, t), idesc_acc, (it | t) != 0);
-        umma_commit(dkv_done);
-        umma_commit(qdo_empty);
       }
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t lqm = desc_lo_mnmajor(smem_u32(sQ + st * Cfg::TILE));
+        const uint32_t ldom = desc_lo_mnmajor(smem_u32(sDO + st * Cfg::TILE));
+        for (int g = 0; g < 2 && ok; ++g) {
+          if (!mbar_wait(&pds_ready[g], it & 1)) {
+            set_error(args.err, ERR_WAIT_MMA_TMEM);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (2 * it + g < 1024) BWD_STAMP(4 * it + 2 * g);
+          const uint32_t tST = tmem_base + g * 64, tDPT = tmem_base + 128 + g * 64;
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            umma_f16_ts(tDV, tST + t * 8, desc_of(ldom + g * 512 + kstep_mnmajor(t)), idesc_acc,
+                        (it | g | t) != 0);
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            umma_f16_ts(tDK, tDPT + t * 8, desc_of(lqm + g * 512 + kstep_mnmajor(t)), idesc_acc,
+                        (it | g | t) != 0);
+          if (g == 1) umma_commit(&qdo_empty[st]);
+          if (it + 1 < n_iter) {
+            if (g == 0) {
+              if (!mbar_wait(&qdo_full[st ^ 1], ((it + 1) >> 1) & 1)) {
+                set_error(args.err, ERR_WAIT_MMA_FULL);
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+            }
+            issue_st(it + 1, g);
+          }
+          if (2 * it + g < 1024) BWD_STAMP(4 * it + 2 * g + 1);
+        }
+      }
+      if (ok) umma_commit(dkv_done);
     }
   } else {
+    const int g = (warp - 2) >> 2;
     const int sw = warp & 3;
     const int row = sw * 32 + lane;   // kv row inside the tile
     const int kv_idx = kv0 + row;
     const uint32_t lane_sel = (uint32_t)(sw * 32) << 16;
-    const int st_tid = threadIdx.x - 64;  // 0..127
+    const int wt = threadIdx.x - 64 - g * 128;  // 0..127 inside the warpgroup
+    float* ls = s_stat + g * 128;               // lse2 of the unit's 64 query rows
+    float* dl = ls + 64;                        // -delta * scale of the same rows
+    const uint32_t tST = tmem_base + g * 64 + lane_sel, tDPT = tmem_base + 128 + g * 64 + lane_sel;
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int h = kvh * group + it / per_head;
       const int qt = qt_first + it % per_head;
-      const int q0 = qt * 128;
-      // stage per-query statistics of this tile (each softmax thread loads one)
+      const int q0 = qt * 128 + g * 64;
       {
-        const int qi = q0 + st_tid;
+        // stage the unit's per-query statistics; named barrier 1+g = this warpgroup's 128 threads
+        const int qi = q0 + (wt & 63);
         const bool qok = qi < T;
         const size_t stat = ((size_t)b * args.hq + h) * T + (qok ? qi : 0);
-        // named barrier 1: all 128 softmax threads finished reading the previous statistics
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        s_lse2[st_tid] = qok ? args.lse[stat] * 1.4426950408889634f : INFINITY;
-        s_delta[st_tid] = qok ? args.delta[stat] : 0.f;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        float val;
+        if (wt < 64) val = qok ? args.lse[stat] * 1.4426950408889634f : INFINITY;
+        else val = qok ? -args.delta[stat] * args.scale : 0.f;  // -delta * scale: one FMA per element below
+        wg_sync(g);    // previous unit's reads done
+        ls[wt] = val;  // wt >= 64 lands in dl[]
+        wg_sync(g);
       }
-      ok = mbar_wait(st_full, it & 1);
+      ok = mbar_wait(&st_full[g], it & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      if (it > 0) {  // already complete; keeps the barrier phase in step for the final wait
-        ok = mbar_wait(dkv_done, (it - 1) & 1);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
+      if ((warp & 3) == 2 && lane == 0 && it < 1024) BWD_STAMP(4096 * (1 + g) + 2 * it);
       // column (query) c is visible from this kv row iff kv_idx <= q + off  <=>  q >= kv_idx - off
       const int q_min = args.causal ? (kv_idx - off) : -0x40000000;
       const bool need_mask = args.causal && (q0 < q_min);
-#pragma unroll 1
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t rs0[32], rs1[32], rp0[32], rp1[32];
-        __syncwarp();
-        tmem_ld32(tST + lane_sel + hf * 64, rs0);
-        tmem_ld32(tST + lane_sel + hf * 64 + 32, rs1);
-        tmem_ld32(tDPT + lane_sel + hf * 64, rp0);
-        tmem_ld32(tDPT + lane_sel + hf * 64 + 32, rp1);
-        tmem_wait_ld();
-        uint32_t pk[32], dk_[32];
-        const int first_ok = q_min - (q0 + hf * 64);  // columns i >= first_ok are visible
-        const float* ls = s_lse2 + hf * 64;
-        const float* dl = s_delta + hf * 64;
+      uint32_t pk[32], dk_[32];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(rs0[i]) * args.scale_log2 - ls[i]);
-          float p1 = exp2f(__uint_as_float(rs0[i + 1]) * args.scale_log2 - ls[i + 1]);
-          float p2 = exp2f(__uint_as_float(rs1[i]) * args.scale_log2 - ls[32 + i]);
-          float p3 = exp2f(__uint_as_float(rs1[i + 1]) * args.scale_log2 - ls[33 + i]);
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rp[32];
+        __syncwarp();
+        tmem_ld32(tST + c * 32, rs);
+        tmem_ld32(tDPT + c * 32, rp);
+        tmem_wait_ld();
+        const int first_ok = q_min - (q0 + c * 32);  // columns i >= first_ok are visible
+        // the per-query statistics are the same for every thread: fetch them four at a time
+        const float4* ls4 = reinterpret_cast<const float4*>(ls + c * 32);
+        const float4* dl4 = reinterpret_cast<const float4*>(dl + c * 32);
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 l = ls4[i >> 2], d = dl4[i >> 2];
+          float p0 = exp2f(__uint_as_float(rs[i]) * args.scale_log2 - l.x);
+          float p1 = exp2f(__uint_as_float(rs[i + 1]) * args.scale_log2 - l.y);
+          float p2 = exp2f(__uint_as_float(rs[i + 2]) * args.scale_log2 - l.z);
+          float p3 = exp2f(__uint_as_float(rs[i + 3]) * args.scale_log2 - l.w);
           if (need_mask) {
             if (i < first_ok) p0 = 0.f;
             if (i + 1 < first_ok) p1 = 0.f;
-            if (i + 32 < first_ok) p2 = 0.f;
-            if (i + 33 < first_ok) p3 = 0.f;
+            if (i + 2 < first_ok) p2 = 0.f;
+            if (i + 3 < first_ok) p3 = 0.f;
           }
-          pk[i >> 1] = pack_bf16x2(p0, p1);
-          pk[16 + (i >> 1)] = pack_bf16x2(p2, p3);
-          dk_[i >> 1] = pack_bf16x2(p0 * (__uint_as_float(rp0[i]) - dl[i]) * args.scale,
-                                    p1 * (__uint_as_float(rp0[i + 1]) - dl[i + 1]) * args.scale);
-          dk_[16 + (i >> 1)] = pack_bf16x2(p2 * (__uint_as_float(rp1[i]) - dl[32 + i]) * args.scale,
-                                           p3 * (__uint_as_float(rp1[i + 1]) - dl[33 + i]) * args.scale);
+          pk[c * 16 + (i >> 1)] = pack_bf16x2_alu(p0, p1);
+          pk[c * 16 + (i >> 1) + 1] = pack_bf16x2_alu(p2, p3);
+          // dS^T = P^T * (dP^T * scale - delta * scale)
+          dk_[c * 16 + (i >> 1)] = pack_bf16x2_alu(p0 * fmaf(__uint_as_float(rp[i]), args.scale, d.x),
+                                               p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, d.y));
+          dk_[c * 16 + (i >> 1) + 1] = pack_bf16x2_alu(p2 * fmaf(__uint_as_float(rp[i + 2]), args.scale, d.z),
+                                                   p3 * fmaf(__uint_as_float(rp[i + 3]), args.scale, d.w));
         }
-        tmem_st32(tST + lane_sel + hf * 32, pk);
-        tmem_st32(tDPT + lane_sel + hf * 32, dk_);
       }
+      tmem_st32(tST, pk);
+      tmem_st32(tDPT, dk_);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(pds_ready);
+      mbar_arrive(&pds_ready[g]);
+      if ((warp & 3) == 2 && lane == 0 && it < 1024) BWD_STAMP(4096 * (1 + g) + 2 * it + 1);
     }
     if (ok && n_iter > 0) {
-      ok = mbar_wait(dkv_done, (n_iter - 1) & 1);
+      ok = mbar_wait(dkv_done, 0);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (!ok) {
       if (lane == 0) set_error(args.err, ERR_WAIT_SOFTMAX);
     } else {
       tc_fence_after();
+      // warpgroup 0 writes dV, warpgroup 1 writes dK
       const bool row_ok = kv_idx < S;
-      __nv_bfloat16* vrow = args.dV + (size_t)(b * S + kv_idx) * args.lddv + kvh * HD;
-      __nv_bfloat16* krow = args.dK + (size_t)(b * S + kv_idx) * args.lddk + kvh * HD;
+      const bool is_k = g == 1;
+      __nv_bfloat16* drow = (is_k ? args.dK + (size_t)(b * S + kv_idx) * args.lddk
+                                  : args.dV + (size_t)(b * S + kv_idx) * args.lddv) + kvh * HD;
 #pragma unroll 1
-      for (int c = 0; c < 2 * (HD / 32); ++c) {
-        const bool is_k = c >= HD / 32;
-        const int cc = is_k ? c - HD / 32 : c;
+      for (int c = 0; c < HD / 32; ++c) {
         uint32_t r[32];
         __syncwarp();
         if (n_iter > 0) {
-          tmem_ld32((is_k ? tDK : tDV) + lane_sel + cc * 32, r);
+          tmem_ld32((is_k ? tDK : tDV) + lane_sel + c * 32, r);
           tmem_wait_ld();
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0u;
         }
         if (row_ok) {
-          __nv_bfloat16* dst = (is_k ? krow : vrow) + cc * 32;
+          __nv_bfloat16* dst = drow + c * 32;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint4 o;
@@ -600,15 +701,25 @@ static int launch_fa_bwd(const void* q, int ldq, const void* k, int ldk, const v
     attr_set = true;
   }
   dim3 gq((a.T + 127) / 128, a.hq, a.B);
-  fa_bwd_dq_kernel<HD><<<gq, 192, DqCfg<HD>::SMEM, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  fa_bwd_dq_kernel<HD><<<gq, BWD_THREADS, DqCfg<HD>::SMEM, stream>>>(tmQ, tmK, tmV, tmDO, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   dim3 gk((a.S + 127) / 128, a.hk, a.B);
-  fa_bwd_dkv_kernel<HD><<<gk, 192, DkvCfg<HD>::SMEM, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  fa_bwd_dkv_kernel<HD><<<gk, BWD_THREADS, DkvCfg<HD>::SMEM, stream>>>(tmQ, tmK, tmV, tmDO, a);
   return (int)cudaGetLastError();
 }
 
 }  // namespace bb
+
+static long long* g_bwd_timeline = nullptr;
+
+// Profiling aid: when set to a device buffer of 6*4096 int64, CTA (0,0,0) of the dQ kernel (first
+// 3*4096 slots) and of the dK/dV kernel (next 3*4096) record clock64 stamps: per unit the MMA
+// issuer's [after the dS wait, after issuing], and per warpgroup [S/dP ready, dS handed over].
+BB_API int bb_flash_bwd_timeline(long long* buf) {
+  g_bwd_timeline = buf;
+  return 0;
+}
 
 // Backward of bb_flash_fwd.  `out`/`dout`: [B*T, ld]; lse from the forward; delta: scratch
 // [B, hq, T] fp32 written here; dq/dk/dv: [B*T or B*S, ld] bf16, fully overwritten.
@@ -644,6 +755,7 @@ BB_API int bb_flash_bwd(const void* q, int ldq, const void* k, int ldk, const vo
   a.scale_log2 = scale * 1.4426950408889634f;
   a.causal = causal;
   a.err = device_error_word();
+  a.tl = g_bwd_timeline;
   if (hd == 128) return launch_fa_bwd<128>(q, ldq, k, ldk, v, ldv, dout, lddo, a, s);
   if (hd == 64) return launch_fa_bwd<64>(q, ldq, k, ldk, v, ldv, dout, lddo, a, s);
   return BB_EARG;

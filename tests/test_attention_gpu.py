@@ -75,3 +75,36 @@ def test_flash_fwd_prefix_offset():
     want = ref.attention(q.float().reshape(B, T, hq, hd), k.float().reshape(B, S, hk, hd),
                          v.float().reshape(B, S, hk, hd), True).reshape(B * T, hq * hd)
     assert rel_err(out, want) < 2e-2
+
+
+@pytest.mark.parametrize("B,T,hq,hk,hd,norm", [(2, 256, 4, 2, 128, True), (1, 384, 4, 4, 64, False),
+                                                (1, 200, 2, 1, 128, True)])
+def test_attention_from_fused_qkv(B, T, hq, hk, hd, norm):
+    """The single-node qk-norm + rope + attention op against the fp32 CPU composition, including
+    the gradient of the whole qkv buffer (q|k through the rope backward, v written in place)."""
+    from brain_b200.ops.attention import attention_qkv
+    torch.manual_seed(7 * T + hd)
+    width = (hq + 2 * hk) * hd
+    qkv = (torch.randn(B * T, width) * 0.7)
+    wq = (1.0 + 0.1 * torch.randn(hd)) if norm else None
+    wk = (1.0 + 0.1 * torch.randn(hd)) if norm else None
+    cos, sin = ref.rope_tables(T, hd, 1e6)
+    pos = torch.arange(T, dtype=torch.int32).repeat(B)
+    do = torch.randn(B * T, hq * hd)
+
+    def run(dev, dt):
+        x = qkv.to(dev, dt).requires_grad_()
+        gq = wq.to(dev, dt).requires_grad_() if norm else None
+        gk = wk.to(dev, dt).requires_grad_() if norm else None
+        o = attention_qkv(x, gq, gk, cos.to(dev), sin.to(dev), pos.to(dev), B, T, hq, hk, hd, 1e-6)
+        o.backward(do.to(dev, dt))
+        return o.detach(), x.grad, (gq.grad if norm else None), (gk.grad if norm else None)
+
+    o1, dx1, dq1, dk1 = run("cuda", torch.bfloat16)
+    o0, dx0, dq0, dk0 = run("cpu", torch.float32)
+    assert rel_err(o1.cpu(), o0) < 2e-2
+    qkw = (hq + hk) * hd
+    assert rel_err(dx1.cpu()[:, :qkw], dx0[:, :qkw]) < 4e-2
+    assert rel_err(dx1.cpu()[:, qkw:], dx0[:, qkw:]) < 3e-2
+    if norm:
+        assert rel_err(dq1.cpu(), dq0) < 5e-2 and rel_err(dk1.cpu(), dk0) < 5e-2
