@@ -175,7 +175,10 @@ def main():
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
     ms_per_step = float(t_ms.item()) / args.steps
     tok_per_s = global_count / (ms_per_step / 1e3)
-    final_loss = float(loss.item())
+    loss_t = loss.detach().clone().reshape(1)
+    if world > 1:
+        dist.all_reduce(loss_t)        # each rank holds its rows' share of the global mean
+    final_loss = float(loss_t.item())
     _cuda.check_error()
     del dev_tok, dev_tgt
 

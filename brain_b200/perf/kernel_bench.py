@@ -44,9 +44,57 @@ def timeit(fns, iters, warmup):
     return s.elapsed_time(e) / iters * 1e-3
 
 
+def elementwise_suite(a, dev, bw):
+    """Bandwidth-bound kernels at the training shapes (rows = b*t): algorithmic bytes / device time
+    as a fraction of the measured copy bandwidth.  Inputs total > 126 MB per call, so L2 does not
+    hold them between iterations."""
+    from brain_b200.ops import functional as F
+    from brain_b200.ops import reference as ref
+    from brain_b200.ops._cuda import L, call, stream_ptr
+    rows, d, ff, hq, hk, hd = a.b * a.t, a.k, 3 * a.k, a.hq, a.hk, a.hd
+    bf = torch.bfloat16
+    res = {}
+
+    def rec(name, fn, nbytes):
+        t = timeit([fn], a.iters, a.warmup)
+        res[name] = {"us": round(t * 1e6, 1), "gbs": round(nbytes / t / 1e9), "frac_of_copy": round(nbytes / t / bw, 3)}
+    x = torch.randn(rows, d, device=dev, dtype=bf)
+    r = torch.randn(rows, d, device=dev, dtype=bf)
+    w = torch.ones(d, device=dev, dtype=bf)
+    y, h, dx = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+    rstd = torch.empty(rows, device=dev, dtype=torch.float32)
+    rec("rmsnorm_fwd(+residual)", lambda: call("rmsnorm_fwd", x, r, w, y, h, rstd, rows, d, 1e-6, stream_ptr()), 4 * rows * d * 2)
+    rec("rmsnorm_bwd_dx(+dres)", lambda: call("rmsnorm_bwd_dx", y, x, w, rstd, r, dx, rows, d, stream_ptr()), 4 * rows * d * 2)
+    gu = torch.randn(rows, 2 * ff, device=dev, dtype=bf)
+    hh = torch.empty(rows, ff, device=dev, dtype=bf)
+    dgu = torch.empty_like(gu)
+    rec("swiglu_fwd", lambda: call("swiglu_fwd", gu, hh, L(rows), ff, stream_ptr()), 3 * rows * ff * 2)
+    rec("swiglu_bwd", lambda: call("swiglu_bwd", hh, gu, dgu, L(rows), ff, stream_ptr()), 5 * rows * ff * 2)
+    width = (hq + 2 * hk) * hd
+    qkw = (hq + hk) * hd
+    qkv = torch.randn(rows, width, device=dev, dtype=bf)
+    qk = torch.empty(rows, qkw, device=dev, dtype=bf)
+    dqkv = torch.empty_like(qkv)
+    rs2 = torch.empty(rows * (hq + hk), device=dev, dtype=torch.float32)
+    gq = torch.ones(hd, device=dev, dtype=bf)
+    cos, sin = ref.rope_tables(a.t, hd, 1e6, device=dev)
+    pos = torch.arange(a.t, device=dev, dtype=torch.int32).repeat(a.b)
+    tq, tk = torch.zeros(hd, device=dev), torch.zeros(hd, device=dev)
+    rec("qknorm_rope_fwd", lambda: call("qknorm_rope_fwd", qkv, width, gq, gq, cos, sin, pos, qk, qkw, rs2, rows, hq, hk, hd,
+                                        1e-6, stream_ptr()), 2 * rows * qkw * 2)
+    rec("qknorm_rope_bwd", lambda: call("qknorm_rope_bwd", qk, qkw, qkv, width, gq, gq, rs2, cos, sin, pos, dqkv, width, tq, tk,
+                                        rows, hq, hk, hd, stream_ptr()), 3 * rows * qkw * 2)
+    n = rows * d * 8
+    m_, v_, ms, g = (torch.zeros(n, device=dev) for _ in range(4))
+    w16 = torch.zeros(n, device=dev, dtype=bf)
+    coef = torch.ones(1, device=dev)
+    rec("adamw", lambda: call("adamw", ms, m_, v_, g, w16, L(n), 1e-4, 0.9, 0.999, 1e-8, 0.1, 3, coef, stream_ptr()), n * 30)
+    return res
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "flash", "i8", "copy"])
+    ap.add_argument("what", choices=["gemm", "flash", "i8", "copy", "elementwise"])
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
@@ -75,6 +123,8 @@ def main(argv=None):
         y = torch.empty_like(x)
         t = timeit([lambda: y.copy_(x)], a.iters, a.warmup)
         out.update(seconds=t, gbs=2 * n * 2 / t / 1e9, frac_of_peak=2 * n * 2 / t / bw)
+    elif a.what == "elementwise":
+        out["kernels"] = elementwise_suite(a, dev, bw)
     elif a.what in ("gemm", "i8"):
         M, N, K = a.m, a.n, a.k
         es = 1 if a.what == "i8" else 2
@@ -94,14 +144,16 @@ def main(argv=None):
                 C = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
                 if a.layout == "nn":      # dX = dy[M,K] . W[K,N]: B stored [K, N]
                     B = B.t().contiguous()
-                elif a.layout == "tt":    # dW = dy^T . x: both stored [K, rows]
+                elif a.layout == "tt":    # dW += dy^T . x: both stored [K, rows], fp32 accumulate
                     A, B = A.t().contiguous(), B.t().contiguous()
+                    C = torch.zeros(M, N, device=dev, dtype=torch.float32)
                 sets.append((A, B, C))
         if a.what == "i8":
             fns = [(lambda s=s: F.gemm_i8(s[0], s[1], s[2], s[3], out=s[4], bn=a.bn)) for s in sets]
         else:
             amn, bmn = a.layout == "tt", a.layout in ("nn", "tt")
-            fns = [(lambda s=s: F.gemm(s[0], s[1], a_mn=amn, b_mn=bmn, out=s[2], bn=a.bn)) for s in sets]
+            fns = [(lambda s=s: F.gemm(s[0], s[1], a_mn=amn, b_mn=bmn, out=s[2], bn=a.bn,
+                                       accumulate=a.layout == "tt")) for s in sets]
         t = timeit(fns, a.iters, a.warmup)
         fl = 2.0 * M * N * K
         peak = pf * (2 if a.what == "i8" else 1)

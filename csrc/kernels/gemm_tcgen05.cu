@@ -30,6 +30,8 @@ struct GemmArgs {
   int ldc;
   int a_mn, b_mn;
   int out_mode;  // 0 bf16 store, 1 fp32 store, 2 fp32 accumulate, 3 bf16 store of gelu(x) (tanh)
+  int split_k;   // >1 (accumulate mode only): the k-blocks are cut into this many slices, each slice is a
+                 // tile of its own and adds its partial product into C
   // Grouped (mixture-of-experts) GEMMs, one launch for all experts:
   //  mode 1 "row-grouped": A rows are expert-sorted and padded so every 128-row tile belongs to one
   //         expert; tile_group[tile_m] names it (-1 = unused tile, skipped); B holds the experts'
@@ -116,8 +118,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int M = args.M, N = args.N, K = args.K;
   const int tiles_m = (M + BM - 1) / BM;
   const int tiles_n = (N + BN - 1) / BN;
-  const int ntiles = tiles_m * tiles_n * (args.group_mode == 2 ? args.num_groups : 1);
+  const int split_k = args.split_k > 1 ? args.split_k : 1;
+  const int ntiles = tiles_m * tiles_n * (args.group_mode == 2 ? args.num_groups : split_k);
   const int nkb_all = (K + BK - 1) / BK;
+  const int kb_per_split = (nkb_all + split_k - 1) / split_k;
   constexpr int GROUP_M = 16;
 
   if (threadIdx.x == 0) {
@@ -157,6 +161,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int r0 = args.group_offsets[grp], r1 = args.group_offsets[grp + 1];
       kb0 = r0 / BK;
       nkb = (r1 - r0) / BK;
+    } else if (split_k > 1) {  // slice index outermost: neighbouring tiles share the slice's A/B panels in L2
+      const int per = tiles_m * tiles_n;
+      const int ks = t / per;
+      t -= ks * per;
+      kb0 = ks * kb_per_split;
+      nkb = min(kb_per_split, nkb_all - kb0);
     }
     const int per_group = GROUP_M * tiles_n;
     const int g = t / per_group;
@@ -602,6 +612,8 @@ static int launch_gemm(const void* A, const void* B, const GemmArgs& args, int l
       if (rc2 == 0) largs.tma_store = 1;
     }
     if (!largs.tma_store) tmC = tmA;  // unused, but the parameter must be a valid object
+    // K slices add into C concurrently: only the TMA reduce-add epilogue does that atomically
+    if (!largs.tma_store || args.tp_mode || args.out_mode != 2) largs.split_k = 1;
   }
   static bool attr_set = false;
   if (!attr_set) {
@@ -611,7 +623,7 @@ static int launch_gemm(const void* A, const void* B, const GemmArgs& args, int l
     attr_set = true;
   }
   const long tiles = (long)((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN) *
-                     (args.group_mode == 2 ? args.num_groups : 1);
+                     (args.group_mode == 2 ? args.num_groups : (largs.split_k > 1 ? largs.split_k : 1));
   int grid = tiles < sm_count() ? (int)tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (force_grid > 0) grid = force_grid;
@@ -657,6 +669,25 @@ BB_API int bb_gemm_bf16(const void* A, const void* B, void* C, const float* bias
     const int sms = sm_count();
     bn = (tiles256 >= sms) ? 256 : (tiles128 >= sms / 2 ? 128 : 64);
     if (N <= 64) bn = 64;
+    if (out_mode == 2 && K >= 4096) bn = 256 <= N ? 256 : (N >= 128 ? 128 : 64);  // split-K fills the SMs instead
+  }
+  if (out_mode == 2 && K >= 4096 && max_ctas == 0) {
+    // Accumulating GEMMs (weight gradients: small M x N, long K) rarely give a whole number of
+    // waves.  Cut K into the slice count (<= 8, >= 16 k-blocks each) with the best wave efficiency;
+    // every slice adds into C, which this mode does anyway.
+    const long tiles = (long)((M + 127) / 128) * ((N + bn - 1) / bn);
+    const int sms = sm_count(), nkb = (K + 63) / 64;
+    double best = 0.0;
+    int pick = 1;
+    for (int sk = 1; sk <= 8 && nkb / sk >= 16; ++sk) {
+      const long t = tiles * sk;
+      const double eff = (double)t / (double)(((t + sms - 1) / sms) * sms) - 0.01 * (sk - 1);
+      if (eff > best + 1e-9) {
+        best = eff;
+        pick = sk;
+      }
+    }
+    a.split_k = pick;
   }
   switch (bn) {
     case 256: return launch_gemm<256, false>(A, B, a, lda, ldb, s, max_ctas);

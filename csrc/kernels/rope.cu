@@ -8,129 +8,207 @@
 #include "../common/host.hpp"
 #include "../common/ptx.cuh"
 
+#include <type_traits>
+
 namespace bb {
 
+// One warp per TOKEN (grid-stride): position, cos and sin are fetched once per token and reused
+// for all of its heads; heads are processed ROPE_UNR at a time with every load of the group issued
+// before the first dependent instruction.  No integer division anywhere on the hot path (an
+// earlier (token, head)-per-warp form spent more instructions on 64-bit div/mod than on the math).
+static constexpr int ROPE_UNR = 4;
+
 template <int HD>
-__global__ void qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
-                                       const __nv_bfloat16* __restrict__ w_q,
-                                       const __nv_bfloat16* __restrict__ w_k,
-                                       const float* __restrict__ cos_t,
-                                       const float* __restrict__ sin_t,
-                                       const int* __restrict__ pos, __nv_bfloat16* __restrict__ out,
-                                       int ldo, float* __restrict__ rstd_out, int n_tok, int hq,
-                                       int hk, float eps) {
+__global__ void __launch_bounds__(256)
+qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
+                       const __nv_bfloat16* __restrict__ w_q, const __nv_bfloat16* __restrict__ w_k,
+                       const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                       const int* __restrict__ pos, __nv_bfloat16* __restrict__ out, int ldo,
+                       float* __restrict__ rstd_out, int n_tok, int hq, int hk, float eps) {
   constexpr int HALF = HD / 2;
   constexpr int PER = HALF / 32;  // elements per lane per half: 1 (hd 64) or 2 (hd 128)
+  constexpr int U = ROPE_UNR;
+  using Vec = typename std::conditional<PER == 2, __nv_bfloat162, __nv_bfloat16>::type;
   const int heads = hq + hk;
-  const long gw = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (gw >= (long)n_tok * heads) return;
-  const int tok = (int)(gw / heads), head = (int)(gw % heads);
-  const __nv_bfloat16* xr = x + (size_t)tok * ldx + head * HD;
-  const __nv_bfloat16* w = head < hq ? w_q : w_k;
-  float a[PER], b[PER];
-#pragma unroll
-  for (int j = 0; j < PER; ++j) {
-    a[j] = __bfloat162float(xr[lane * PER + j]);
-    b[j] = __bfloat162float(xr[HALF + lane * PER + j]);
-  }
-  float rstd = 1.f;
-  if (w) {
-    float ss = 0.f;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) ss += a[j] * a[j] + b[j] * b[j];
-    ss = warp_sum(ss);
-    rstd = rsqrtf(ss / (float)HD + eps);
-    if (lane == 0 && rstd_out) rstd_out[gw] = rstd;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const bool norm = w_q != nullptr;
+  float wqa[PER], wqb[PER], wka[PER], wkb[PER];
+  if (norm) {
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
-      a[j] *= rstd * __bfloat162float(w[lane * PER + j]);
-      b[j] *= rstd * __bfloat162float(w[HALF + lane * PER + j]);
+      wqa[j] = __bfloat162float(w_q[lane * PER + j]);
+      wqb[j] = __bfloat162float(w_q[HALF + lane * PER + j]);
+      wka[j] = __bfloat162float(w_k[lane * PER + j]);
+      wkb[j] = __bfloat162float(w_k[HALF + lane * PER + j]);
     }
   }
-  const int p = pos[tok];
-  __nv_bfloat16* orow = out + (size_t)tok * ldo + head * HD;
+  auto unpack = [](const Vec v, float (&o)[PER]) {
+    if constexpr (PER == 2) { o[0] = __low2float(v); o[1] = __high2float(v); }
+    else { o[0] = __bfloat162float(v); }
+  };
+  for (int tok = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; tok < n_tok; tok += nwarps) {
+    const int p = pos[tok];
+    float c[PER], sn[PER];
 #pragma unroll
-  for (int j = 0; j < PER; ++j) {
-    const int m = lane * PER + j;
-    const float c = cos_t[(size_t)p * HALF + m], s = sin_t[(size_t)p * HALF + m];
-    orow[m] = __float2bfloat16(a[j] * c - b[j] * s);
-    orow[HALF + m] = __float2bfloat16(b[j] * c + a[j] * s);
+    for (int j = 0; j < PER; ++j) {
+      c[j] = cos_t[(size_t)p * HALF + lane * PER + j];
+      sn[j] = sin_t[(size_t)p * HALF + lane * PER + j];
+    }
+    const __nv_bfloat16* xt = x + (size_t)tok * ldx;
+    __nv_bfloat16* ot = out + (size_t)tok * ldo;
+    for (int h0 = 0; h0 < heads; h0 += U) {
+      float a[U][PER], b[U][PER];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int h = min(h0 + u, heads - 1);
+        unpack(*reinterpret_cast<const Vec*>(xt + h * HD + lane * PER), a[u]);
+        unpack(*reinterpret_cast<const Vec*>(xt + h * HD + HALF + lane * PER), b[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int h = h0 + u;
+        if (norm) {
+          float ss = 0.f;
+#pragma unroll
+          for (int j = 0; j < PER; ++j) ss += a[u][j] * a[u][j] + b[u][j] * b[u][j];
+          ss = warp_sum(ss);
+          const float rstd = rsqrtf(ss / (float)HD + eps);
+          if (lane == 0 && rstd_out && h < heads) rstd_out[(size_t)tok * heads + h] = rstd;
+          const bool is_q = h < hq;
+#pragma unroll
+          for (int j = 0; j < PER; ++j) {
+            a[u][j] *= rstd * (is_q ? wqa[j] : wka[j]);
+            b[u][j] *= rstd * (is_q ? wqb[j] : wkb[j]);
+          }
+        }
+        if (h >= heads) continue;
+        float o0[PER], o1[PER];
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          o0[j] = a[u][j] * c[j] - b[u][j] * sn[j];
+          o1[j] = b[u][j] * c[j] + a[u][j] * sn[j];
+        }
+        __nv_bfloat16* orow = ot + h * HD;
+        if constexpr (PER == 2) {
+          *reinterpret_cast<__nv_bfloat162*>(orow + lane * 2) = __floats2bfloat162_rn(o0[0], o0[1]);
+          *reinterpret_cast<__nv_bfloat162*>(orow + HALF + lane * 2) = __floats2bfloat162_rn(o1[0], o1[1]);
+        } else {
+          orow[lane] = __float2bfloat16(o0[0]);
+          orow[HALF + lane] = __float2bfloat16(o1[0]);
+        }
+      }
+    }
   }
 }
 
-// Backward: given d(out), produce d(x) and accumulate d(w_q), d(w_k) (fp32, [HD] each).
-// Persistent grid-stride over (token, head) pairs so the gain gradient is reduced in registers and
-// hits global memory with one atomic per lane per block-warp.
+// Backward: given d(out), produce d(x) and accumulate d(w_q), d(w_k) (fp32, [HD] each).  The gain
+// gradient is reduced in registers over the warp's tokens, then across the block in shared memory,
+// and reaches global memory with one atomic per element per block.
 template <int HD>
-__global__ void qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dout, int ldo,
-                                       const __nv_bfloat16* __restrict__ x, int ldx,
-                                       const __nv_bfloat16* __restrict__ w_q,
-                                       const __nv_bfloat16* __restrict__ w_k,
-                                       const float* __restrict__ rstd_in,
-                                       const float* __restrict__ cos_t,
-                                       const float* __restrict__ sin_t,
-                                       const int* __restrict__ pos, __nv_bfloat16* __restrict__ dx,
-                                       int ldd, float* __restrict__ dw_q, float* __restrict__ dw_k,
-                                       int n_tok, int hq, int hk) {
+__global__ void __launch_bounds__(256)
+qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dout, int ldo,
+                       const __nv_bfloat16* __restrict__ x, int ldx,
+                       const __nv_bfloat16* __restrict__ w_q, const __nv_bfloat16* __restrict__ w_k,
+                       const float* __restrict__ rstd_in, const float* __restrict__ cos_t,
+                       const float* __restrict__ sin_t, const int* __restrict__ pos,
+                       __nv_bfloat16* __restrict__ dx, int ldd, float* __restrict__ dw_q,
+                       float* __restrict__ dw_k, int n_tok, int hq, int hk) {
   constexpr int HALF = HD / 2;
   constexpr int PER = HALF / 32;
+  constexpr int U = ROPE_UNR;
+  using Vec = typename std::conditional<PER == 2, __nv_bfloat162, __nv_bfloat16>::type;
   const int heads = hq + hk;
   const int lane = threadIdx.x & 31;
-  const long nwarps = ((long)gridDim.x * blockDim.x) >> 5;
-  const long total = (long)n_tok * heads;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const bool norm = w_q != nullptr;
   float gq_a[PER] = {0}, gq_b[PER] = {0}, gk_a[PER] = {0}, gk_b[PER] = {0};
-  for (long gw = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; gw < total; gw += nwarps) {
-    const int tok = (int)(gw / heads), head = (int)(gw % heads);
-    const bool is_q = head < hq;
-    const __nv_bfloat16* w = is_q ? w_q : w_k;
-    const __nv_bfloat16* dor = dout + (size_t)tok * ldo + head * HD;
-    const int p = pos[tok];
-    float da[PER], db[PER];
+  float wqa[PER], wqb[PER], wka[PER], wkb[PER];
+  if (norm) {
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
-      const int m = lane * PER + j;
-      const float c = cos_t[(size_t)p * HALF + m], s = sin_t[(size_t)p * HALF + m];
-      const float g0 = __bfloat162float(dor[m]), g1 = __bfloat162float(dor[HALF + m]);
-      da[j] = g0 * c + g1 * s;   // d xn[m]
-      db[j] = g1 * c - g0 * s;   // d xn[m+half]
-    }
-    __nv_bfloat16* dxr = dx + (size_t)tok * ldd + head * HD;
-    if (!w) {
-#pragma unroll
-      for (int j = 0; j < PER; ++j) {
-        dxr[lane * PER + j] = __float2bfloat16(da[j]);
-        dxr[HALF + lane * PER + j] = __float2bfloat16(db[j]);
-      }
-      continue;
-    }
-    const __nv_bfloat16* xr = x + (size_t)tok * ldx + head * HD;
-    const float rstd = rstd_in[gw];
-    float xa[PER], xb[PER], wa[PER], wb[PER];
-    float dot = 0.f;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      xa[j] = __bfloat162float(xr[lane * PER + j]) * rstd;
-      xb[j] = __bfloat162float(xr[HALF + lane * PER + j]) * rstd;
-      wa[j] = __bfloat162float(w[lane * PER + j]);
-      wb[j] = __bfloat162float(w[HALF + lane * PER + j]);
-      if (is_q) {
-        gq_a[j] += da[j] * xa[j];
-        gq_b[j] += db[j] * xb[j];
-      } else {
-        gk_a[j] += da[j] * xa[j];
-        gk_b[j] += db[j] * xb[j];
-      }
-      dot += da[j] * wa[j] * xa[j] + db[j] * wb[j] * xb[j];
-    }
-    dot = warp_sum(dot) / (float)HD;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      dxr[lane * PER + j] = __float2bfloat16(rstd * (da[j] * wa[j] - xa[j] * dot));
-      dxr[HALF + lane * PER + j] = __float2bfloat16(rstd * (db[j] * wb[j] - xb[j] * dot));
+      wqa[j] = __bfloat162float(w_q[lane * PER + j]);
+      wqb[j] = __bfloat162float(w_q[HALF + lane * PER + j]);
+      wka[j] = __bfloat162float(w_k[lane * PER + j]);
+      wkb[j] = __bfloat162float(w_k[HALF + lane * PER + j]);
     }
   }
-  // block-level reduction in shared memory, then one atomic per element per block
+  auto unpack = [](const Vec v, float (&o)[PER]) {
+    if constexpr (PER == 2) { o[0] = __low2float(v); o[1] = __high2float(v); }
+    else { o[0] = __bfloat162float(v); }
+  };
+  for (int tok = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; tok < n_tok; tok += nwarps) {
+    const int p = pos[tok];
+    float c[PER], sn[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      c[j] = cos_t[(size_t)p * HALF + lane * PER + j];
+      sn[j] = sin_t[(size_t)p * HALF + lane * PER + j];
+    }
+    const __nv_bfloat16* dot_ = dout + (size_t)tok * ldo;
+    const __nv_bfloat16* xt = x + (size_t)tok * ldx;
+    __nv_bfloat16* dxt = dx + (size_t)tok * ldd;
+    for (int h0 = 0; h0 < heads; h0 += U) {
+      float g0[U][PER], g1[U][PER], xa[U][PER], xb[U][PER], rstd[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int h = min(h0 + u, heads - 1);
+        unpack(*reinterpret_cast<const Vec*>(dot_ + h * HD + lane * PER), g0[u]);
+        unpack(*reinterpret_cast<const Vec*>(dot_ + h * HD + HALF + lane * PER), g1[u]);
+        if (norm) {
+          unpack(*reinterpret_cast<const Vec*>(xt + h * HD + lane * PER), xa[u]);
+          unpack(*reinterpret_cast<const Vec*>(xt + h * HD + HALF + lane * PER), xb[u]);
+          rstd[u] = rstd_in[(size_t)tok * heads + h];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int h = h0 + u;
+        const bool live = h < heads;
+        float da[PER], db[PER], ra[PER], rb[PER];
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          da[j] = g0[u][j] * c[j] + g1[u][j] * sn[j];   // d xn[m]
+          db[j] = g1[u][j] * c[j] - g0[u][j] * sn[j];   // d xn[m+half]
+        }
+        if (!norm) {
+#pragma unroll
+          for (int j = 0; j < PER; ++j) { ra[j] = da[j]; rb[j] = db[j]; }
+        } else {
+          const bool is_q = h < hq;
+          float dot = 0.f;
+          float wa[PER], wb[PER];
+#pragma unroll
+          for (int j = 0; j < PER; ++j) {
+            xa[u][j] *= rstd[u];
+            xb[u][j] *= rstd[u];
+            wa[j] = is_q ? wqa[j] : wka[j];
+            wb[j] = is_q ? wqb[j] : wkb[j];
+            const float pa = live ? da[j] * xa[u][j] : 0.f, pb = live ? db[j] * xb[u][j] : 0.f;
+            if (is_q) { gq_a[j] += pa; gq_b[j] += pb; }
+            else { gk_a[j] += pa; gk_b[j] += pb; }
+            dot += da[j] * wa[j] * xa[u][j] + db[j] * wb[j] * xb[u][j];
+          }
+          dot = warp_sum(dot) / (float)HD;
+#pragma unroll
+          for (int j = 0; j < PER; ++j) {
+            ra[j] = rstd[u] * (da[j] * wa[j] - xa[u][j] * dot);
+            rb[j] = rstd[u] * (db[j] * wb[j] - xb[u][j] * dot);
+          }
+        }
+        if (!live) continue;
+        __nv_bfloat16* dxr = dxt + h * HD;
+        if constexpr (PER == 2) {
+          *reinterpret_cast<__nv_bfloat162*>(dxr + lane * 2) = __floats2bfloat162_rn(ra[0], ra[1]);
+          *reinterpret_cast<__nv_bfloat162*>(dxr + HALF + lane * 2) = __floats2bfloat162_rn(rb[0], rb[1]);
+        } else {
+          dxr[lane] = __float2bfloat16(ra[0]);
+          dxr[HALF + lane] = __float2bfloat16(rb[0]);
+        }
+      }
+    }
+  }
+  if (!norm) return;
   __shared__ float red[2][8][HD];
   const int wib = threadIdx.x >> 5;
 #pragma unroll
@@ -143,13 +221,13 @@ __global__ void qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dout, i
   __syncthreads();
   const int nw = blockDim.x >> 5;
   for (int i = threadIdx.x; i < 2 * HD; i += blockDim.x) {
-    const int which = i / HD, c = i % HD;
+    const int which = i / HD, cc = i % HD;
     float sum = 0.f;
-    for (int w2 = 0; w2 < nw; ++w2) sum += red[which][w2][c];
+    for (int w2 = 0; w2 < nw; ++w2) sum += red[which][w2][cc];
     if (which == 0) {
-      if (w_q && dw_q) atomicAdd(dw_q + c, sum);
+      if (dw_q) atomicAdd(dw_q + cc, sum);
     } else {
-      if (w_k && dw_k && hk > 0) atomicAdd(dw_k + c, sum);
+      if (dw_k && hk > 0) atomicAdd(dw_k + cc, sum);
     }
   }
 }
@@ -166,7 +244,9 @@ BB_API int bb_qknorm_rope_fwd(const void* x, int ldx, const void* w_q, const voi
                               void* stream) {
   const long total = (long)n_tok * (hq + hk);
   if (total <= 0) return BB_OK;
-  const int grid = (int)((total + 7) / 8);
+  long want = ((long)n_tok + 7) / 8;
+  const long cap = (long)sm_count() * 8;
+  const int grid = (int)(want < cap ? want : cap);
   if (hd == 128)
     qknorm_rope_fwd_kernel<128><<<grid, 256, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w_q, (const __nv_bfloat16*)w_k, cos_t,
@@ -186,7 +266,7 @@ BB_API int bb_qknorm_rope_bwd(const void* dout, int ldo, const void* x, int ldx,
                               float* dw_k, int n_tok, int hq, int hk, int hd, void* stream) {
   const long total = (long)n_tok * (hq + hk);
   if (total <= 0) return BB_OK;
-  long want = (total + 7) / 8;
+  long want = ((long)n_tok + 7) / 8;
   const long cap = (long)sm_count() * 4;
   const int grid = (int)(want < cap ? want : cap);
   if (hd == 128)
