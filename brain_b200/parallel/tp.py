@@ -50,6 +50,12 @@ class TensorParallel:
             self.row_flags = torch.zeros(1 << 16, device=self.device, dtype=torch.int32)
             self.ar_epoch = 0
             self._cmaps = {}
+            # two-shot all-reduce state: device-resident epoch (graph capture safe), own flags
+            self.ar2_sig = self.arena.alloc(self.world, torch.int64)
+            self.ar2_sig_ptrs = self._U64(*self.arena.peer_ptrs(self.ar2_sig))
+            self.ar2_state = torch.zeros(4, device=self.device, dtype=torch.int32)   # [0] epoch, [1..3] counters
+            self._ar2 = None
+            self.ar2_calls = 0
 
     # ------------------------------------------------------------------ symmetric slots
     def _slot(self, kind: str, numel: int, dtype, parity: int) -> torch.Tensor:
@@ -89,6 +95,9 @@ class TensorParallel:
         """Sum over the TP group (serving: small activations -> one-shot peer kernel when fused)."""
         if self.world == 1:
             return x
+        if self.impl == "fused" and x.is_cuda and x.dtype == torch.bfloat16 and \
+                x.numel() % (8 * self.world) == 0:
+            return self._all_reduce2(x)
         if self.impl == "fused" and x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % 8 == 0:
             from ..ops._cuda import L, call, stream_ptr
             self.ar_epoch += 1
@@ -103,6 +112,28 @@ class TensorParallel:
         y = x.clone()
         dist.all_reduce(y, group=self.group)
         return y
+
+    def _all_reduce2(self, x):
+        """Two-shot peer-memory all-reduce; the result is a view of this rank's symmetric result
+        buffer (two alternate, so a result stays valid across ONE later all-reduce)."""
+        from ..ops._cuda import L, call, stream_ptr
+        n = x.numel()
+        if self._ar2 is None or self._ar2["cap"] < n:
+            cap = max(n, 1 << 22)
+            stage = self.arena.alloc(cap, torch.bfloat16)
+            res = [self.arena.alloc(cap, torch.bfloat16) for _ in range(2)]
+            self._ar2 = {"cap": cap, "stage": stage, "res": res,
+                         "stage_ptrs": self._U64(*self.arena.peer_ptrs(stage)),
+                         "res_ptrs": [self._U64(*self.arena.peer_ptrs(r)) for r in res]}
+            if dist.is_initialized():
+                dist.barrier(group=self.group)      # nobody signals into buffers that do not exist yet
+        st = self._ar2
+        which = self.ar2_calls & 1
+        self.ar2_calls += 1
+        xc = x.contiguous()
+        call("tp_allreduce2", st["stage_ptrs"], st["res_ptrs"][which], self.ar2_sig_ptrs, xc, L(n), self.rank,
+             self.world, self.ar2_state, self.ar2_state[1:], ctypes.c_double(self.wait_seconds), stream_ptr())
+        return st["res"][which][:n].view(x.shape)
 
     # ------------------------------------------------------------------ fused GEMM + collective
     def ag_gemm(self, x_shard, w):

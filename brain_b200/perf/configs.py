@@ -35,11 +35,11 @@ def cpu_dp(args) -> dict:
     build_s = time.perf_counter() - t0
     rng = Rng(0)
     losses, times = [], []
+    mbs = []          # one fixed batch per worker, drawn once with seed 0
+    for _ in range(workers):
+        toks = torch.from_numpy(rng.tokens(B * (T + 1), cfg.vocab).astype("int64")).view(B, T + 1)
+        mbs.append((toks[:, :-1].to(torch.int32).contiguous(), toks[:, 1:].contiguous()))
     for step in range(args.steps):
-        mbs = []
-        for _ in range(workers):
-            toks = torch.from_numpy(rng.tokens(B * (T + 1), cfg.vocab).astype("int64")).view(B, T + 1)
-            mbs.append((toks[:, :-1].to(torch.int32).contiguous(), toks[:, 1:].contiguous()))
         t1 = time.perf_counter()
         losses.append(dp.train_step(mbs, 3e-4, wd=0.1, clip=1.0))
         times.append(time.perf_counter() - t1)
@@ -57,14 +57,120 @@ def cpu_dp(args) -> dict:
             "dtype": "fp32", "data": "synthetic"}
 
 
+def _dist_init():
+    import os
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, torch.device("cuda", local)
+
+
+def _random_qwen(cfg, dev, seed=1234):
+    """Random-init model built directly on the device in bf16 (normal std 0.02, gains 1); every
+    rank draws the same values from the same seed."""
+    from ..models.qwen3 import Qwen3
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            m = Qwen3(cfg)
+    finally:
+        torch.set_default_dtype(prev)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    with torch.no_grad():
+        for name, p in m.named_parameters():
+            if p.dim() == 1:
+                p.fill_(1.0)
+            else:
+                p.normal_(0.0, 0.02, generator=g)
+    return m.eval()
+
+
+def serve_tp(args) -> dict:
+    """Qwen3-8B-architecture serving, tensor parallel over all ranks, W8A8 int8, paged KV with
+    16-token blocks, continuous batching: 512 requests at 256 concurrent (closed loop), prompts
+    uniform 128..2048 random token ids, 256 greedy output tokens each (stop ignored)."""
+    import torch.distributed as dist
+    from ..models.config import QwenConfig
+    from ..ops import _cuda
+    from ..parallel.tp import TensorParallel
+    from ..serve.engine import QwenEngine
+    from .driver import drive
+    from .metrics import Summary
+    from .targets import SchedulerTarget
+    from .workload import Arrival, standard
+    rank, world, dev = _dist_init()
+    tp = TensorParallel(impl=args.impl, device=dev, arena_mb=1024) if world > 1 else None
+    cfg = QwenConfig.preset(args.model, 4096)
+    if args.layers:
+        cfg.n_layers = args.layers
+    ctx = 2048 + args.out_tokens + 16
+    conc, nreq = args.concurrency, args.requests
+    t0 = time.perf_counter()
+    model = _random_qwen(cfg, dev)
+    per_seq = -(-ctx // 16)
+    eng = QwenEngine(model, block_size=16, num_blocks=per_seq * conc + conc, max_seq_len=per_seq * 16,
+                     max_prefill=2048, weights=args.weights, tp=tp, cuda_graphs=not args.no_graphs)
+    del model
+    torch.cuda.empty_cache()
+    build_s = time.perf_counter() - t0
+    wl = standard("serving_mix", Arrival.closed_loop(conc), nreq, seed=0, vocab=cfg.vocab)
+    wl.classes[0].output.n = args.out_tokens
+    # warm-up: a few short requests so graphs for small buckets and all lazy setup exist
+    warm = standard("serving_mix", Arrival.closed_loop(min(conc, 8)), 8, seed=1, vocab=cfg.vocab)
+    warm.classes[0].output.n = 8
+    target = SchedulerTarget(None, max_batch=conc, ctx=per_seq * 16, engine=eng, name=f"qwen3-{args.model}")
+    drive(target, warm)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches0 = _cuda.launch_count
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    run = drive(target, wl)
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    _cuda.check_error()
+    s = Summary.build(run.records, float(ms.item()) / 1e3, wl.classes[0].slo)
+    j = s.to_json()
+    return {"config": "serve-tp", "metric": f"serve out tok/s + p50 TTFT (Qwen3-{args.model} TP{world} {args.weights})",
+            "value": s.output_per_s, "unit": "output tokens/s", "n_gpus": world, "ttft_ms_p50": j["ttfa_ms"].get("p50"),
+            "ttft_ms_p99": j["ttfa_ms"].get("p99"), "tpot_ms_p50": j["tpoa_ms"].get("p50"),
+            "e2e_ms_p50": j["e2e_ms"].get("p50"), "requests": s.requests, "completed": s.completed,
+            "input_tokens": s.input_artifacts, "output_tokens": s.output_artifacts, "wall_s": s.wall_s,
+            "concurrency": conc, "weights": args.weights, "impl": args.impl, "layers": cfg.n_layers,
+            "kv_pool_gb": eng.kv_pool_bytes() / 2**30, "weight_gb_per_rank": eng.weight_bytes() / 2**30,
+            "cuda_graph_replays": eng.graph_replays, "engine_steps": eng.steps, "build_s": build_s,
+            "gpu_launches": _cuda.launch_count - launches0, "dtype": "int8 weights+activations, bf16 KV" if args.weights == "int8" else "bf16",
+            "data": "synthetic", "timing": "CUDA events around the whole run, max over ranks"}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", choices=["cpu-dp"])
+    ap.add_argument("which", choices=["cpu-dp", "serve-tp"])
     ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--layers", type=int, default=12)
+    ap.add_argument("--layers", type=int, default=0, help="override depth (debug; invalidates the number)")
+    ap.add_argument("--model", default="8b")
+    ap.add_argument("--weights", default="int8", choices=["int8", "bf16"])
+    ap.add_argument("--impl", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--requests", type=int, default=512)
+    ap.add_argument("--concurrency", type=int, default=256)
+    ap.add_argument("--out-tokens", type=int, default=256)
+    ap.add_argument("--no-graphs", action="store_true")
     a = ap.parse_args(argv)
-    out = {"cpu-dp": cpu_dp}[a.which](a)
-    print(json.dumps(out))
+    if a.which == "cpu-dp" and not a.layers:
+        a.layers = 12
+    out = {"cpu-dp": cpu_dp, "serve-tp": serve_tp}[a.which](a)
+    import os
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(out))
     return 0
 
 

@@ -68,7 +68,7 @@ class _Lin:
 class QwenEngine:
     def __init__(self, model, block_size: int = 16, num_blocks: int = 1024, max_seq_len: int = 4096,
                  max_prefill: int = 512, weights: str = "bf16", topk: int = 64, tp=None,
-                 decode_splits: int = 0):
+                 decode_splits: int = 0, cuda_graphs: bool = True):
         cfg: QwenConfig = model.cfg
         self.cfg = cfg
         self.tp = tp
@@ -121,11 +121,17 @@ class QwenEngine:
         head = model.head_weight().detach()
         self.head = _Lin(cast(head), None, False)  # the LM head stays bf16 (as the reference keeps it fp32)
         self.cos, self.sin = ref.rope_tables(max_seq_len, cfg.head_dim, cfg.rope_theta, device=dev)
-        shape = (num_blocks, self.hk, block_size, self.hd)
+        # one extra physical block past the allocator's range: padded rows of a bucketed decode batch
+        # write their K/V there
+        self.dummy_block = num_blocks
+        shape = (num_blocks + 1, self.hk, block_size, self.hd)
         self.kc = [torch.zeros(shape, device=dev, dtype=self.dtype) for _ in model.blocks]
         self.vc = [torch.zeros(shape, device=dev, dtype=self.dtype) for _ in model.blocks]
         self.decode_splits = decode_splits
         self.steps = 0
+        self.cuda_graphs = bool(cuda_graphs) and self.cuda
+        self._graphs = {}
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ accounting
     def kv_pool_bytes(self) -> int:
@@ -268,9 +274,23 @@ class QwenEngine:
         Returns (tokens [B][window], per-row top-k candidate lists or None)."""
         dev = self.device
         B = int(tokens.shape[0])
+        if self.cuda_graphs and (greedy or window > 1):
+            out = self._decode_graphed(tokens, positions, block_tables, window)
+            return [row.tolist() for row in out], None
         tok = torch.from_numpy(np.ascontiguousarray(tokens)).to(dev)
         pos = torch.from_numpy(np.ascontiguousarray(positions)).to(dev)
         bts = torch.from_numpy(np.ascontiguousarray(block_tables)).to(dev)
+        out_t, topks = self._decode_steps(tok, pos, bts, window, greedy or window > 1)
+        out = out_t.cpu().numpy()
+        cand = None
+        if topks is not None:
+            idx, vals = topks[0].cpu().tolist(), topks[1].cpu().tolist()
+            cand = [list(zip(i, v)) for i, v in zip(idx, vals)]
+        return [row.tolist() for row in out], cand
+
+    def _decode_steps(self, tok, pos, bts, window: int, greedy: bool):
+        """``window`` decode steps on device tensors -> (tokens [B, window], last top-k or None)."""
+        B = tok.shape[0]
         outs = []
         topks = None
         for w in range(window):
@@ -285,19 +305,77 @@ class QwenEngine:
             delta = None
             for li in range(len(self.layers)):
                 x, delta = self._layer(li, x, delta, pos, attn)
-            t, tk = self._head(x, delta, greedy or window > 1)
+            t, tk = self._head(x, delta, greedy)
             outs.append(t)
             if tk is not None:
                 topks = tk
             tok = t
             pos = pos + 1
             self.steps += 1
-        out = torch.stack(outs, dim=1).cpu().numpy()
-        cand = None
-        if topks is not None:
-            idx, vals = topks[0].cpu().tolist(), topks[1].cpu().tolist()
-            cand = [list(zip(i, v)) for i, v in zip(idx, vals)]
-        return [row.tolist() for row in out], cand
+        return torch.stack(outs, dim=1), topks
+
+    # ---- CUDA-graph decode: one captured graph per (padded batch, window)
+    @staticmethod
+    def _bucket(b: int) -> int:
+        for cap in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 160, 192, 224, 256):
+            if b <= cap:
+                return cap
+        return -(-b // 64) * 64
+
+    def _decode_graphed(self, tokens, positions, block_tables, window: int):
+        """Greedy decode through a replayed CUDA graph.  The batch is padded to a bucket size with
+        rows that sit at position 0 of the dummy block; inputs travel through pinned staging."""
+        B = int(tokens.shape[0])
+        Bp = self._bucket(B)
+        key = (Bp, window)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._capture(Bp, window)
+            self._graphs[key] = g
+        h_tok, h_pos, h_bts = g["h_tok"], g["h_pos"], g["h_bts"]
+        h_tok[:B] = torch.from_numpy(np.ascontiguousarray(tokens, dtype=np.int32))
+        h_pos[:B] = torch.from_numpy(np.ascontiguousarray(positions, dtype=np.int32))
+        h_bts[:B] = torch.from_numpy(np.ascontiguousarray(block_tables, dtype=np.int32))
+        if Bp > B:
+            h_tok[B:] = 0
+            h_pos[B:] = 0
+            h_bts[B:] = self.dummy_block
+        g["tok"].copy_(h_tok, non_blocking=True)
+        g["pos"].copy_(h_pos, non_blocking=True)
+        g["bts"].copy_(h_bts, non_blocking=True)
+        g["graph"].replay()
+        self.graph_replays += 1
+        self.steps += window
+        g["h_out"].copy_(g["out"], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return g["h_out"][:B].numpy().copy()
+
+    def _capture(self, Bp: int, window: int):
+        dev = self.device
+        mb = self.max_blocks
+        g = {"tok": torch.zeros(Bp, device=dev, dtype=torch.int32),
+             "pos": torch.zeros(Bp, device=dev, dtype=torch.int32),
+             "bts": torch.full((Bp, mb), self.dummy_block, device=dev, dtype=torch.int32),
+             "h_tok": torch.zeros(Bp, dtype=torch.int32).pin_memory(),
+             "h_pos": torch.zeros(Bp, dtype=torch.int32).pin_memory(),
+             "h_bts": torch.zeros(Bp, mb, dtype=torch.int32).pin_memory(),
+             "h_out": torch.zeros(Bp, window, dtype=torch.int32).pin_memory()}
+        steps0 = self.steps
+        # warm-up on a side stream (lazy one-time setup such as kernel attributes and symmetric
+        # buffers must not happen during capture), then capture the same work
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._decode_steps(g["tok"], g["pos"], g["bts"], window, True)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out, _ = self._decode_steps(g["tok"], g["pos"], g["bts"], window, True)
+        g["graph"], g["out"] = graph, out
+        self.steps = steps0
+        return g
 
     # ------------------------------------------------------------------ convenience
     @torch.no_grad()

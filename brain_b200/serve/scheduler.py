@@ -43,6 +43,10 @@ _host.register({
     "bbh_sched_seq_prompt": (None, [c.c_void_p, c.c_int64, c.c_void_p]),
     "bbh_sched_seq_table": (c.c_uint32, [c.c_void_p, c.c_int64, c.c_void_p, c.c_uint32]),
     "bbh_sched_forget": (None, [c.c_void_p, c.c_int64]),
+    "bbh_sched_decode_all_greedy": (c.c_int, [c.c_void_p]),
+    "bbh_sched_step_report": (c.c_uint32, [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_uint32, c.c_void_p,
+                                           c.c_uint32]),
+    "bbh_sched_step_tokens": (c.c_uint32, [c.c_void_p]),
     "bbh_sched_set_service_ms": (None, [c.c_void_p, c.c_double]),
     "bbh_sched_stats": (None, [c.c_void_p, c.c_void_p]),
 })
@@ -196,7 +200,6 @@ class Scheduler:
         npf, nd, win = c.c_uint32(), c.c_uint32(), c.c_uint32()
         lib.bbh_sched_plan(self._h, c.byref(npf), c.byref(nd), c.byref(win))
         rep = StepReport(window=win.value)
-        before: Dict[int, int] = {}
         # ---- prefill chunks
         for i in range(npf.value):
             rid, s, e, last = c.c_int64(), c.c_uint32(), c.c_uint32(), c.c_int()
@@ -207,7 +210,6 @@ class Scheduler:
             lib.bbh_sched_seq_prompt(self._h, rid_v, prompt.ctypes.data)
             bt = np.full(self.max_blocks, -1, dtype=np.int32)
             lib.bbh_sched_seq_table(self._h, rid_v, bt.ctypes.data, self.max_blocks)
-            before.setdefault(rid_v, info.n_out)
             greedy = info.params.is_greedy()
             tok, topk = self.dec.prefill_chunk(prompt[s.value:e.value].astype(np.int32), s.value, bt,
                                                bool(last.value), greedy)
@@ -227,26 +229,35 @@ class Scheduler:
             bts = np.empty((n, self.max_blocks), dtype=np.int32)
             lib.bbh_sched_decode_batch(self._h, ids.ctypes.data, toks.ctypes.data, pos.ctypes.data,
                                        bts.ctypes.data, self.max_blocks)
-            infos = [self.info(int(r)) for r in ids]
-            for r, inf in zip(ids, infos):
-                before.setdefault(int(r), inf.n_out)
-            all_greedy = all(i.params.is_greedy() for i in infos)
+            all_greedy = bool(lib.bbh_sched_decode_all_greedy(self._h))
             greedy_toks, topks = self.dec.decode(toks, pos, bts, win.value, all_greedy)
-            out = np.empty((n, win.value), dtype=np.uint32)
-            for i, r in enumerate(ids):
-                if all_greedy:
-                    out[i, :] = greedy_toks[i]
-                else:
+            if all_greedy:
+                out = np.ascontiguousarray(np.asarray(greedy_toks, dtype=np.uint32).reshape(n, win.value))
+            else:
+                out = np.empty((n, win.value), dtype=np.uint32)
+                for i, r in enumerate(ids):
                     out[i, 0] = self._pick(int(r), greedy_toks[i][0], topks[i] if topks is not None else None)
             lib.bbh_sched_commit_decode(self._h, out.ctypes.data, n, win.value)
             rep.decoded = n
-        # ---- report
-        for rid_v, n0 in before.items():
-            info = self.info(rid_v)
-            if info.n_out > n0:
-                rep.new_tokens[rid_v] = self.tokens_of(rid_v)[n0:]
-            if info.state == FINISHED:
-                rep.finished.append(rid_v)
+        # ---- report: what this step's commits produced, fetched in one native call
+        ne = int(lib.bbh_sched_step_report(self._h, None, None, None, 0, None, 0))
+        if ne:
+            nt = max(int(lib.bbh_sched_step_tokens(self._h)), 1)
+            e_ids = np.empty(ne, dtype=np.int64)
+            e_new = np.empty(ne, dtype=np.uint32)
+            e_fin = np.empty(ne, dtype=np.int32)
+            e_tok = np.empty(nt, dtype=np.uint32)
+            lib.bbh_sched_step_report(self._h, e_ids.ctypes.data, e_new.ctypes.data, e_fin.ctypes.data, ne,
+                                      e_tok.ctypes.data, nt)
+            t = 0
+            tok_list = e_tok.tolist()
+            for rid_v, k, fin in zip(e_ids.tolist(), e_new.tolist(), e_fin.tolist()):
+                if k:
+                    prev = rep.new_tokens.get(rid_v)
+                    rep.new_tokens[rid_v] = (prev + tok_list[t:t + k]) if prev else tok_list[t:t + k]
+                    t += k
+                if fin and rid_v not in rep.finished:
+                    rep.finished.append(rid_v)
         return rep
 
     def run_until_idle(self, max_steps: int = 1 << 30) -> None:

@@ -92,6 +92,100 @@ __global__ void __launch_bounds__(256) tp_allreduce_kernel(const ArArgs a) {
   }
 }
 
+// Two-shot all-reduce whose epoch lives in device memory, so the launch parameters never change
+// and the call can sit inside a captured CUDA graph (decode steps replay one graph).
+//   phase 1  copy x into my staging buffer; the last block publishes flag 2e-1 to every peer
+//   phase 2  wait for every peer's 2e-1; reduce MY 1/world slice over all staging buffers in rank
+//            order (bit-identical everywhere) and store it into every rank's result buffer; the
+//            last block publishes flag 2e
+//   phase 3  wait for every peer's 2e: my result buffer is complete, and every peer has finished
+//            reading my staging buffer, so ONE staging buffer is enough for back-to-back calls.
+// A peer writes into my result buffer only after it saw my flag 2(e+1)-1, which my next call
+// publishes after everything I launched before it on the stream has consumed the result.
+// Each value crosses NVLink (world-1)/world times in each direction instead of world-1 times.
+struct Ar2Args {
+  PeerPtrs stage, result, sig;
+  const __nv_bfloat16* x;
+  long n;
+  int rank, world;
+  unsigned int* epoch_dev;   // [0] epoch of the last finished call
+  unsigned int* counters;    // [0..2] zeroed block counters
+  long long wait_limit;
+  int* err;
+};
+
+__global__ void __launch_bounds__(256) tp_allreduce2_kernel(const Ar2Args a) {
+  __shared__ unsigned int s_e;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_e = *reinterpret_cast<volatile unsigned int*>(a.epoch_dev) + 1u;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const unsigned int e = s_e;
+  const long nv = a.n >> 3;
+  const long stride = (long)gridDim.x * blockDim.x;
+  const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  bf16x8* mine = reinterpret_cast<bf16x8*>(a.stage.p[a.rank]);
+  for (long i = tid; i < nv; i += stride) mine[i] = reinterpret_cast<const bf16x8*>(a.x)[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(a.counters, 1u) == gridDim.x - 1) {
+      a.counters[0] = 0u;
+      for (int r = 0; r < a.world; ++r)
+        st_release_sys_u64(reinterpret_cast<uint64_t*>(a.sig.p[r]) + a.rank, (uint64_t)(2u * e - 1u));
+    }
+  }
+  if (threadIdx.x < a.world) {
+    const uint64_t* f = reinterpret_cast<const uint64_t*>(a.sig.p[a.rank]) + threadIdx.x;
+    if (!wait_epoch(f, 2u * e - 1u, 0, a.wait_limit)) {
+      set_error(a.err, ERR_WAIT_PEER);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  if (s_ok) {
+    const long per = nv / a.world;  // host guarantees divisibility
+    const long lo = (long)a.rank * per;
+    for (long j = tid; j < per; j += stride) {
+      const long i = lo + j;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int r = 0; r < a.world; ++r) {
+        const uint4 raw = ld_volatile_u4(reinterpret_cast<const uint4*>(a.stage.p[r]) + i);
+        float f[8];
+        unpack8(*reinterpret_cast<const bf16x8*>(&raw), f);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] += f[q];
+      }
+      const bf16x8 out = pack8(acc);
+      for (int r = 0; r < a.world; ++r) reinterpret_cast<bf16x8*>(a.result.p[r])[i] = out;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(a.counters + 1, 1u) == gridDim.x - 1) {
+      a.counters[1] = 0u;
+      for (int r = 0; r < a.world; ++r)
+        st_release_sys_u64(reinterpret_cast<uint64_t*>(a.sig.p[r]) + a.rank, (uint64_t)(2u * e));
+    }
+  }
+  if (threadIdx.x < a.world && s_ok) {
+    const uint64_t* f = reinterpret_cast<const uint64_t*>(a.sig.p[a.rank]) + threadIdx.x;
+    if (!wait_epoch(f, 2u * e, 0, a.wait_limit)) set_error(a.err, ERR_WAIT_PEER);
+  }
+  __syncthreads();
+  // the epoch advances even after a timeout, so the ranks stay in step for the next call
+  if (threadIdx.x == 0) {
+    if (atomicAdd(a.counters + 2, 1u) == gridDim.x - 1) {
+      a.counters[2] = 0u;
+      *reinterpret_cast<volatile unsigned int*>(a.epoch_dev) = e;
+      __threadfence();
+    }
+  }
+}
+
 // All ranks meet: publish `epoch` to every peer, then wait (bounded) until every peer published it.
 // Orders "my earlier kernels' writes to symmetric memory" before "peers' later reads" without NCCL.
 __global__ void symm_barrier_kernel(PeerPtrs sig, int rank, int world, uint32_t epoch,
@@ -160,5 +254,35 @@ BB_API int bb_tp_allreduce(const uint64_t* buf_ptrs, const uint64_t* sig_ptrs, c
   if (blocks > sm_count()) blocks = sm_count();  // every block waits on peers: keep them co-resident
   if (blocks < 1) blocks = 1;
   tp_allreduce_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+// Graph-safe two-shot all-reduce of n bf16 values (n % (8*world) == 0) into this rank's symmetric
+// result buffer.  stage/result/sig_ptrs[r]: rank r's buffers (>= n elements; uint64[world] flags
+// used by no other protocol); epoch_dev: one zeroed uint32; counters: three zeroed uint32.
+BB_API int bb_tp_allreduce2(const uint64_t* stage_ptrs, const uint64_t* result_ptrs,
+                            const uint64_t* sig_ptrs, const void* x, long n, int rank, int world,
+                            unsigned int* epoch_dev, unsigned int* counters, double wait_seconds,
+                            void* stream) {
+  using namespace bb;
+  if (world < 1 || world > MAX_RANKS || n <= 0 || n % (8L * world)) return BB_EARG;
+  Ar2Args a{};
+  for (int r = 0; r < world; ++r) {
+    a.stage.p[r] = reinterpret_cast<void*>(stage_ptrs[r]);
+    a.result.p[r] = reinterpret_cast<void*>(result_ptrs[r]);
+    a.sig.p[r] = reinterpret_cast<void*>(sig_ptrs[r]);
+  }
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.n = n;
+  a.rank = rank;
+  a.world = world;
+  a.epoch_dev = epoch_dev;
+  a.counters = counters;
+  a.wait_limit = (long long)(wait_seconds * 1.9e9);
+  a.err = device_error_word();
+  long blocks = ((n >> 3) + 255) / 256;
+  if (blocks > sm_count()) blocks = sm_count();  // every block waits on peers: keep them co-resident
+  if (blocks < 1) blocks = 1;
+  tp_allreduce2_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }

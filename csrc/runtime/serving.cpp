@@ -297,10 +297,22 @@ class Scheduler {
   std::vector<PrefillItem> prefill_plan;
   std::vector<int64_t> decode_plan;
   uint32_t decode_window = 1;
+  bool decode_all_greedy = true;
+  // what the commits of the current step produced: one entry per sequence that gained tokens or
+  // finished, with its new tokens in step_tokens[first, first + n_new)
+  struct StepOut {
+    int64_t id;
+    uint32_t n_new, first;
+    int finished;
+  };
+  std::vector<StepOut> step_out;
+  std::vector<uint32_t> step_tokens;
 
   void plan() {
     prefill_plan.clear();
     decode_plan.clear();
+    step_out.clear();
+    step_tokens.clear();
     // (1) continue partially prefilled sequences, then admit new ones, under the token budget
     uint32_t budget = 2 * cfg_.max_prefill;
     bool any = false;
@@ -356,6 +368,7 @@ class Scheduler {
         all_greedy = all_greedy && s.greedy();
       }
     }
+    decode_all_greedy = all_greedy;
     decode_window = 1;
     if (cfg_.window > 1 && waiting_.empty() && prefill_plan.empty() && all_greedy && !decode_plan.empty() &&
         alloc_.free_blocks() >= decode_plan.size() * cfg_.window) {
@@ -389,7 +402,11 @@ class Scheduler {
       if (cfg_.prefix_cache)
         prefix_.insert_chain(s.prompt.data(), s.prompt.size(), s.table.blocks,
                              s.prefix_hit / cfg_.block_size, alloc_);
-      if (has_token) push_token(s, token);
+      if (has_token) {
+        const size_t before = s.out.size();
+        push_token(s, token);
+        record(s, before);
+      }
     }
   }
 
@@ -399,11 +416,13 @@ class Scheduler {
     for (uint32_t i = 0; i < n && i < ids.size(); ++i) {
       Seq& s = *seqs_.at(ids[i]);
       uint32_t used = 0;
+      const size_t before = s.out.size();
       for (uint32_t w = 0; w < window && s.state == RUNNING; ++w) {
         push_token(s, tokens[i * window + w]);
         ++used;
       }
       if (s.state == RUNNING && used < window) s.table.truncate(s.table.len - (window - used), alloc_);
+      record(s, before);
     }
   }
 
@@ -424,6 +443,12 @@ class Scheduler {
   double mean_service_ms_ = 0;
 
  private:
+  void record(const Seq& s, size_t before) {
+    const uint32_t n_new = static_cast<uint32_t>(s.out.size() - before);
+    if (n_new == 0 && s.state != FINISHED) return;
+    step_out.push_back({s.id, n_new, static_cast<uint32_t>(step_tokens.size()), s.state == FINISHED ? 1 : 0});
+    step_tokens.insert(step_tokens.end(), s.out.begin() + static_cast<long>(before), s.out.end());
+  }
   void finish(Seq& s, Finish why) {
     s.state = FINISHED;
     s.finish = why;
@@ -602,6 +627,25 @@ BBH_API uint32_t bbh_sched_seq_table(void* s, int64_t id, int32_t* blocks, uint3
   for (uint32_t i = 0; i < n; ++i) blocks[i] = static_cast<int32_t>(q->table.blocks[i]);
   return static_cast<uint32_t>(q->table.blocks.size());
 }
+BBH_API int bbh_sched_decode_all_greedy(void* s) { return static_cast<Scheduler*>(s)->decode_all_greedy ? 1 : 0; }
+// The current step's results in one call: returns the entry count; fills ids / n_new / finished per
+// entry and the new tokens flattened in entry order (`tokens` holds at least `cap_tokens`).
+BBH_API uint32_t bbh_sched_step_report(void* s, int64_t* ids, uint32_t* n_new, int32_t* finished,
+                                       uint32_t cap_entries, uint32_t* tokens, uint32_t cap_tokens) {
+  auto* sc = static_cast<Scheduler*>(s);
+  const uint32_t n = static_cast<uint32_t>(sc->step_out.size());
+  if (!ids) return n;
+  uint32_t t = 0;
+  for (uint32_t i = 0; i < n && i < cap_entries; ++i) {
+    const auto& e = sc->step_out[i];
+    ids[i] = e.id;
+    n_new[i] = e.n_new;
+    finished[i] = e.finished;
+    for (uint32_t k = 0; k < e.n_new && t < cap_tokens; ++k) tokens[t++] = sc->step_tokens[e.first + k];
+  }
+  return n;
+}
+BBH_API uint32_t bbh_sched_step_tokens(void* s) { return static_cast<uint32_t>(static_cast<Scheduler*>(s)->step_tokens.size()); }
 BBH_API void bbh_sched_forget(void* s, int64_t id) { static_cast<Scheduler*>(s)->forget(id); }
 BBH_API void bbh_sched_set_service_ms(void* s, double ms) { static_cast<Scheduler*>(s)->mean_service_ms_ = ms; }
 // stats: [free_blocks, num_blocks, waiting, running, steps, submitted, finished, cancelled,
