@@ -24,7 +24,7 @@ from .plan import schedule as make_schedule
 
 class PipelineStage:
     def __init__(self, model, stage: int, n_stages: int, prev_rank: Optional[int], next_rank: Optional[int],
-                 group=None, tied_group=None, schedule: str = "1f1b", act_dtype=None):
+                 group=None, tied_group=None, schedule: str = "1f1b", act_dtype=None, row_div: int = 1):
         self.model, self.stage, self.n_stages = model, stage, n_stages
         self.prev, self.next = prev_rank, next_rank
         self.group, self.tied_group = group, tied_group
@@ -33,6 +33,7 @@ class PipelineStage:
         self.device = p.device
         self.act_dtype = act_dtype or p.dtype
         self.d_model = model.cfg.d_model
+        self.row_div = row_div      # tensor-parallel degree: stages exchange [B*T/row_div, d] row shards
         self._pending: List = []
 
     @property
@@ -73,12 +74,14 @@ class PipelineStage:
                     x_in = None
                     out = self.model.hidden(tokens=micro_tokens[m].to(self.device))
                 else:
-                    x_in = self._recv((B * T, self.d_model), self.prev).requires_grad_()
+                    x_in = self._recv((B * T // self.row_div, self.d_model), self.prev).requires_grad_()
                     out = self.model.hidden(x_in=x_in, B=B, T=T)
                 if self.last:
                     from ..ops import functional as F
-                    loss = F.lm_head_ce(out, self.model.head_weight(),
-                                        micro_targets[m].to(self.device).reshape(-1), loss_scale,
+                    tgt = micro_targets[m].to(self.device).reshape(-1)
+                    if self.row_div > 1:
+                        tgt = self.model.local_rows(tgt)
+                    loss = F.lm_head_ce(out, self.model.head_weight(), tgt, loss_scale,
                                         self.model.ce_chunk_rows)
                     stash[m] = (x_in, loss)
                     total = loss.detach() if total is None else total + loss.detach()

@@ -40,8 +40,11 @@ def _round_up(x: int, a: int) -> int:
 
 class ParamStore:
     def __init__(self, module: nn.Module, device=None, dtype: Optional[torch.dtype] = None,
-                 pad_to: int = 1, decay_fn=None, roles: Optional[Dict[str, Role]] = None):
-        params = [(n, p) for n, p in module.named_parameters()]
+                 pad_to: int = 1, decay_fn=None, roles: Optional[Dict[str, Role]] = None, select=None):
+        """``select(name) -> bool`` restricts the store to a subset of the module's parameters (a
+        model may keep e.g. its replicated and its expert-parallel tensors in two stores with two
+        different optimiser/collective treatments)."""
+        params = [(n, p) for n, p in module.named_parameters() if select is None or select(n)]
         if device is None:
             device = params[0][1].device
         device = torch.device(device)

@@ -104,7 +104,9 @@ def serve_tp(args) -> dict:
     from .targets import SchedulerTarget
     from .workload import Arrival, standard
     rank, world, dev = _dist_init()
-    tp = TensorParallel(impl=args.impl, device=dev, arena_mb=1024) if world > 1 else None
+    import faulthandler
+    faulthandler.dump_traceback_later(args.stuck_after, exit=True)     # a stuck rank prints its stack and exits
+    tp = TensorParallel(impl=args.impl, device=dev, arena_mb=1024, wait_seconds=5.0) if world > 1 else None
     cfg = QwenConfig.preset(args.model, 4096)
     if args.layers:
         cfg.n_layers = args.layers
@@ -138,6 +140,7 @@ def serve_tp(args) -> dict:
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     _cuda.check_error()
+    faulthandler.cancel_dump_traceback_later()
     s = Summary.build(run.records, float(ms.item()) / 1e3, wl.classes[0].slo)
     j = s.to_json()
     return {"config": "serve-tp", "metric": f"serve out tok/s + p50 TTFT (Qwen3-{args.model} TP{world} {args.weights})",
@@ -152,9 +155,126 @@ def serve_tp(args) -> dict:
             "data": "synthetic", "timing": "CUDA events around the whole run, max over ranks"}
 
 
+def _timed_steps(step_fn, steps, warmup, dev, world):
+    import torch.distributed as dist
+    for _ in range(warmup):
+        step_fn()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    loss = None
+    for _ in range(steps):
+        loss = step_fn()
+    ev1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item()) / steps, loss
+
+
+def train_3d(args) -> dict:
+    """Qwen3-14B architecture, bf16, tensor parallel x pipeline parallel (default TP4 x PP2 on 8
+    GPUs), 1F1B over 16 micro-batches of 1 x 4096 uniform-random tokens; fused all-gather->GEMM and
+    GEMM->reduce-scatter inside every block, pipeline send/recv on NCCL p2p."""
+    from ..models.config import QwenConfig
+    from ..ops import _cuda
+    from ..parallel.grid import Grid
+    from ..parallel.trainer3d import Trainer3D
+    rank, world, dev = _dist_init()
+    tp = args.tp or (4 if world >= 8 else max(world // 2, 1))
+    pp = world // tp
+    cfg = QwenConfig.preset(args.model, args.seq)
+    if args.layers:
+        cfg.n_layers = args.layers
+    tr = Trainer3D(cfg, Grid(tp=tp, pp=pp, dp=1), dev, impl=args.impl, schedule=args.schedule, seed=1234)
+    g = torch.Generator().manual_seed(0)
+    n_micro, T = args.micro, args.seq
+    toks = [torch.randint(0, cfg.vocab, (1, T), generator=g, dtype=torch.int32).to(dev) for _ in range(n_micro)]
+    tgts = [torch.randint(0, cfg.vocab, (1, T), generator=g).to(dev) for _ in range(n_micro)]
+    count = n_micro * T
+    launches0 = _cuda.launch_count
+    ms, loss = _timed_steps(lambda: tr.train_step(toks, tgts, 1e-4, count), args.steps, args.warmup, dev, world)
+    _cuda.check_error()
+    flops = tr.model.flops_per_token(T) if hasattr(tr.model, "flops_per_token") else 0.0
+    return {"config": "train-3d", "metric": f"train tok/s (Qwen3-{args.model} bf16 TP{tp}xPP{pp} {args.schedule})",
+            "value": count / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "ms_per_step": ms, "steps": args.steps,
+            "warmup": args.warmup, "micro_batches": n_micro, "seq_len": T, "impl": args.impl, "layers": cfg.n_layers,
+            "final_loss": float(loss), "params_per_rank_b": tr.store.n_train / 1e9,
+            "mem_gb": torch.cuda.max_memory_allocated() / 2**30, "gpu_launches": _cuda.launch_count - launches0,
+            "dtype": "bf16", "data": "synthetic", "timing": "CUDA events, max over ranks"}
+
+
+def train_ep(args) -> dict:
+    """Qwen3-30B-A3B-style MoE (48 layers, hidden 2048, 32 Q / 4 KV heads, 128 experts of FFN 768,
+    softmax router top-8, aux loss 0.001), bf16, expert parallel over all ranks, 8 sequences of
+    4096 uniform-random tokens per GPU; fused peer-memory dispatch/combine + grouped tcgen05 GEMM."""
+    from ..models.config import MoeConfig
+    from ..models.moe import MoeModel
+    from ..ops import _cuda
+    from ..parallel.ep import ExpertParallel
+    from ..parallel.trainer_ep import TrainerEP
+    rank, world, dev = _dist_init()
+    cfg = MoeConfig.qwen3_30b_a3b(args.seq)
+    if args.layers:
+        cfg.n_layers = args.layers
+    if args.experts:
+        cfg.n_experts = args.experts
+    ep = ExpertParallel(impl=args.impl, device=dev, arena_mb=args.arena_mb) if world > 1 else None
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            model = MoeModel(cfg, ep=ep)
+    finally:
+        torch.set_default_dtype(prev)
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    gen_local = torch.Generator(device=dev).manual_seed(99 + rank)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() == 1:
+                p.fill_(1.0)
+            else:
+                p.normal_(0.0, 0.02, generator=gen_local if ".moe.w_" in name else gen)
+    tr = TrainerEP(model, dev, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(rank)
+    B, T = args.seqs_per_gpu, args.seq
+    toks = torch.randint(0, cfg.vocab, (B, T), generator=g, dtype=torch.int32).pin_memory()
+    tgts = torch.randint(0, cfg.vocab, (B, T), generator=g).pin_memory()
+    count = B * T * world
+    launches0 = _cuda.launch_count
+    ms, loss = _timed_steps(lambda: tr.train_step(toks, tgts, 1e-4, args.micro_batch, count), args.steps, args.warmup,
+                            dev, world)
+    _cuda.check_error()
+    loss_t = loss.detach().float().reshape(1).clone()
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(loss_t)
+    return {"config": "train-ep", "metric": f"train tok/s (Qwen3-MoE {cfg.n_experts} experts top-{cfg.top_k} bf16 EP{world})",
+            "value": count / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "ms_per_step": ms, "steps": args.steps,
+            "warmup": args.warmup, "seqs_per_gpu": B, "seq_len": T, "micro_batch": args.micro_batch, "impl": args.impl,
+            "layers": cfg.n_layers, "experts": cfg.n_experts, "final_loss": float(loss_t),
+            "shared_params_b": tr.shared.n_train / 1e9, "expert_params_per_rank_b": tr.expert.n_train / 1e9,
+            "mem_gb": torch.cuda.max_memory_allocated() / 2**30, "gpu_launches": _cuda.launch_count - launches0,
+            "dtype": "bf16", "data": "synthetic", "timing": "CUDA events, max over ranks"}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", choices=["cpu-dp", "serve-tp"])
+    ap.add_argument("which", choices=["cpu-dp", "serve-tp", "train-3d", "train-ep"])
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--tp", type=int, default=0)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--micro", type=int, default=16, help="train-3d: micro-batches per step")
+    ap.add_argument("--schedule", default="1f1b", choices=["1f1b", "gpipe"])
+    ap.add_argument("--seqs-per-gpu", type=int, default=8)
+    ap.add_argument("--micro-batch", type=int, default=1, help="train-ep: sequences per forward/backward")
+    ap.add_argument("--experts", type=int, default=0)
+    ap.add_argument("--arena-mb", type=int, default=4096)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--layers", type=int, default=0, help="override depth (debug; invalidates the number)")
     ap.add_argument("--model", default="8b")
@@ -164,10 +284,15 @@ def main(argv=None):
     ap.add_argument("--concurrency", type=int, default=256)
     ap.add_argument("--out-tokens", type=int, default=256)
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--stuck-after", type=int, default=600, help="seconds before a stuck rank dumps its stack and exits")
     a = ap.parse_args(argv)
     if a.which == "cpu-dp" and not a.layers:
         a.layers = 12
-    out = {"cpu-dp": cpu_dp, "serve-tp": serve_tp}[a.which](a)
+    if a.which in ("train-3d", "train-ep") and a.steps == 20:
+        a.steps = 3
+    if a.which == "train-3d" and a.model == "8b":
+        a.model = "14b"
+    out = {"cpu-dp": cpu_dp, "serve-tp": serve_tp, "train-3d": train_3d, "train-ep": train_ep}[a.which](a)
     import os
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(out))

@@ -371,7 +371,9 @@ class QwenEngine:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        # thread-local capture mode: other threads of the process (e.g. a process group's watchdog)
+        # keep making CUDA calls of their own while this thread captures
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             out, _ = self._decode_steps(g["tok"], g["pos"], g["bts"], window, True)
         g["graph"], g["out"] = graph, out
         self.steps = steps0

@@ -120,9 +120,12 @@ class Scheduler:
         self.max_batch = max_batch
 
     def __del__(self):
-        if getattr(self, "_h", None):
-            _host.lib().bbh_sched_free(self._h)
-            self._h = None
+        try:
+            if getattr(self, "_h", None):
+                _host.lib().bbh_sched_free(self._h)
+                self._h = None
+        except Exception:      # interpreter shutdown: the library handle may already be gone
+            pass
 
     # ------------------------------------------------------------------ queue
     def submit(self, prompt: Sequence[int], max_new: int, params: Optional[SampleParams] = None,

@@ -321,11 +321,20 @@ class Scheduler {
       if (s.prefilled < s.prompt.size()) {
         const uint32_t n = std::min<uint32_t>(cfg_.max_prefill, static_cast<uint32_t>(s.prompt.size()) - s.prefilled);
         if (any && n > budget) break;
-        if (s.table.reserve(n, alloc_) < 0) break;
+        if (!reserve_or_evict(s, n)) break;
         prefill_plan.push_back({id, s.prefilled, s.prefilled + n, s.prefilled + n == s.prompt.size()});
         budget = budget > n ? budget - n : 0;
         any = true;
       }
+    }
+    // blocks the running sequences may still claim (prompt + max_new each): admission keeps them
+    // free, so a sequence that was admitted can always run to its full length
+    uint64_t outstanding = 0;
+    for (int64_t id : running_) {
+      const Seq& r = *seqs_[id];
+      const uint32_t full = blocks_for(static_cast<uint32_t>(r.prompt.size()) + r.max_new);
+      const uint32_t have = static_cast<uint32_t>(r.table.blocks.size());
+      if (full > have) outstanding += full - have;
     }
     while (!waiting_.empty() && running_.size() < cfg_.max_batch) {
       Seq& s = *seqs_[waiting_.front()];
@@ -336,13 +345,14 @@ class Scheduler {
       if (cfg_.prefix_cache)
         hit = prefix_.lookup(s.prompt.data(), s.prompt.size(), cfg_.block_size, s.prompt.size() - 1);
       const uint32_t need_blocks = blocks_for(total) - static_cast<uint32_t>(hit.size());
-      if (alloc_.free_blocks() < need_blocks && cfg_.prefix_cache) {
+      const uint64_t want_free = need_blocks + outstanding;
+      if (alloc_.free_blocks() < want_free && cfg_.prefix_cache) {
         // pin the hit while evicting so the eviction cannot take it
         for (uint32_t b : hit) alloc_.incref(b);
-        prefix_.evict(need_blocks - alloc_.free_blocks(), alloc_);
+        prefix_.evict(static_cast<uint32_t>(want_free - alloc_.free_blocks()), alloc_);
         for (uint32_t b : hit) alloc_.decref(b);
       }
-      if (alloc_.free_blocks() < need_blocks) break;  // FIFO: do not skip ahead
+      if (alloc_.free_blocks() < want_free) break;  // FIFO: do not skip ahead
       const uint32_t remaining = static_cast<uint32_t>(s.prompt.size()) - static_cast<uint32_t>(hit.size()) * cfg_.block_size;
       const uint32_t n = std::min(cfg_.max_prefill, remaining);
       if (any && n > budget) break;
@@ -353,6 +363,7 @@ class Scheduler {
       prefix_hit_tokens_ += s.prefix_hit;
       prefix_lookup_tokens_ += s.prompt.size();
       s.table.reserve(n, alloc_);
+      outstanding += blocks_for(total) - static_cast<uint32_t>(s.table.blocks.size());
       s.state = RUNNING;
       running_.push_back(s.id);
       prefill_plan.push_back({s.id, s.prefilled, s.prefilled + n, s.prefilled + n == s.prompt.size()});
@@ -383,9 +394,11 @@ class Scheduler {
     std::vector<int64_t> ok;
     for (int64_t id : decode_plan) {
       Seq& s = *seqs_[id];
-      if (s.table.reserve(decode_window, alloc_) < 0) {
-        // pool exhausted mid-flight: finish the sequence at its current length
+      if (!reserve_or_evict(s, decode_window)) {
+        // pool exhausted mid-flight even after dropping cached prefixes: finish the sequence at
+        // its current length (and say so in this step's report)
         finish(s, LENGTH);
+        record(s, s.out.size());
         continue;
       }
       ok.push_back(id);
@@ -443,6 +456,15 @@ class Scheduler {
   double mean_service_ms_ = 0;
 
  private:
+  // Back `n` more positions of `s`; when the pool is short, evict least-recently-used prefix-cache
+  // blocks (they only hold a cache reference) and try once more.
+  bool reserve_or_evict(Seq& s, uint32_t n) {
+    if (s.table.reserve(n, alloc_) >= 0) return true;
+    if (!cfg_.prefix_cache) return false;
+    const uint32_t need = blocks_for(s.table.len + n), have = static_cast<uint32_t>(s.table.blocks.size());
+    prefix_.evict(need > have ? need - have : 1, alloc_);
+    return s.table.reserve(n, alloc_) >= 0;
+  }
   void record(const Seq& s, size_t before) {
     const uint32_t n_new = static_cast<uint32_t>(s.out.size() - before);
     if (n_new == 0 && s.state != FINISHED) return;

@@ -217,3 +217,50 @@ def test_pipeline_two_stages_match_single(sched):
     for r in range(2):
         for n, gr in outs[r][1].items():
             assert torch.allclose(gr, want[n], atol=2e-5), (sched, r, n)
+
+
+def _trainer3d_worker(rank, world, tp, pp, sched):
+    from brain_b200.models.config import QwenConfig
+    from brain_b200.models.qwen3 import Qwen3
+    from brain_b200.parallel.grid import Grid
+    from brain_b200.parallel.trainer3d import Trainer3D, gather_state
+    cfg = QwenConfig(vocab=96, block_size=128, n_layers=4, d_model=32, n_heads=4, n_kv_heads=2, head_dim=8, d_ff=64,
+                     tie_embeddings=True)
+    full = Qwen3(cfg).init_weights(5)
+    state = {k: v.detach().clone() for k, v in full.reference_state().items()}
+    tr = Trainer3D(cfg, Grid(tp=tp, pp=pp, dp=1), "cpu", schedule=sched, full_state=state, grad_clip=1.0,
+                   weight_decay=0.1)
+    g = torch.Generator().manual_seed(3)
+    toks = [torch.randint(0, 96, (2, 128), generator=g, dtype=torch.int32) for _ in range(4)]
+    tgts = [torch.randint(0, 96, (2, 128), generator=g) for _ in range(4)]
+    losses = [float(tr.train_step(toks, tgts, 1e-2)) for _ in range(2)]
+    out = gather_state(tr)
+    return {"losses": losses, "state": out, "norm": float(tr.last_grad_norm)}
+
+
+@pytest.mark.parametrize("tp,pp,sched", [(2, 2, "1f1b"), (2, 1, "1f1b"), (1, 2, "gpipe")])
+def test_trainer3d_matches_single_process(tp, pp, sched):
+    """Tensor x pipeline parallel training on gloo CPU ranks reproduces the single-process step:
+    same losses, same global gradient norm, same weights after two optimiser steps."""
+    from brain_b200.engine import Trainer
+    from brain_b200.models.config import QwenConfig
+    from brain_b200.models.qwen3 import Qwen3
+    res = run_ranks(_trainer3d_worker, tp * pp, tp, pp, sched)
+    cfg = QwenConfig(vocab=96, block_size=128, n_layers=4, d_model=32, n_heads=4, n_kv_heads=2, head_dim=8, d_ff=64,
+                     tie_embeddings=True)
+    full = Qwen3(cfg).init_weights(5)
+    tr = Trainer(full, device="cpu", weight_decay=0.1, grad_clip=1.0)
+    g = torch.Generator().manual_seed(3)
+    toks = [torch.randint(0, 96, (2, 128), generator=g, dtype=torch.int32) for _ in range(4)]
+    tgts = [torch.randint(0, 96, (2, 128), generator=g) for _ in range(4)]
+    want = []
+    for _ in range(2):
+        want.append(float(tr.train_step(torch.cat(toks), torch.cat(tgts), 1e-2, micro_batch=2)))
+    for r in res:
+        assert r["losses"] == pytest.approx(want, rel=2e-4)
+    assert res[0]["norm"] == pytest.approx(float(tr.opt.last_grad_norm), rel=2e-3)
+    ref_state = full.reference_state()
+    got = res[0]["state"]
+    assert set(got) == set(ref_state)
+    for k, v in ref_state.items():
+        assert torch.allclose(got[k], v.detach().reshape(-1), atol=2e-4), k

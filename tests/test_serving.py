@@ -214,3 +214,30 @@ def test_engine_int8_tracks_full_precision():
     rel = ((a - b).norm() / a.norm()).item()
     assert rel < 0.08
     assert eng8.weight_bytes() < 0.6 * eng.weight_bytes()
+
+
+def test_full_pool_with_prefix_cache_still_completes_every_request():
+    """A pool sized for exactly `concurrency` full-length sequences fills up with cached prompt
+    blocks of finished requests; admission must evict them (and keep room for what running
+    sequences may still claim) so that every request runs to its full length and every finish is
+    reported — a closed-loop driver would otherwise wait forever."""
+    from brain_b200.perf.driver import drive
+    from brain_b200.perf.metrics import Summary
+    from brain_b200.perf.targets import SchedulerTarget, synth_qwen
+    from brain_b200.perf.workload import Arrival, standard
+    from brain_b200.serve.engine import QwenEngine
+    m = synth_qwen("1x32x4x300", "cpu")
+    conc, out = 6, 12
+    ctx = 512 + out + 16
+    per_seq = -(-ctx // 16)
+    eng = QwenEngine(m, block_size=16, num_blocks=per_seq * conc + conc, max_seq_len=per_seq * 16, max_prefill=512)
+    wl = standard("serving_mix", Arrival.closed_loop(conc), 30, seed=0, vocab=300)
+    wl.classes[0].input.lo, wl.classes[0].input.hi = 64, 512
+    wl.classes[0].output.n = out
+    t = SchedulerTarget(None, max_batch=conc, ctx=per_seq * 16, engine=eng)
+    run = drive(t, wl, max_seconds=120)
+    s = Summary.build(run.records, run.wall_s, wl.classes[0].slo)
+    assert s.completed == 30 and s.failed == 0 and s.rejected == 0
+    assert all(r.output_artifacts() == out for r in run.records)
+    st = t.sched.stats()
+    assert st["running"] == 0 and st["waiting"] == 0 and st["finished"] == 30
