@@ -268,6 +268,59 @@ class QwenEngine:
         return first, list(zip(idx, vals))
 
     @torch.no_grad()
+    def prefill_batch(self, items):
+        """Several prefill chunks in ONE packed forward: ``items`` is a list of (tokens, start,
+        block_table, last, greedy).  Norms, projections, RoPE, KV append and the MLP run once over
+        the concatenated rows; only attention runs per sequence (on its row slice).  Returns one
+        (first token, top-k candidates) pair per item (``(None, None)`` for non-final chunks)."""
+        if len(items) == 1:
+            t, st, bt, last, greedy = items[0]
+            return [self.prefill_chunk(t, st, bt, last, greedy)]
+        dev = self.device
+        lens = [int(it[0].shape[0]) for it in items]
+        offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        n = int(offs[-1])
+        tok = torch.from_numpy(np.ascontiguousarray(np.concatenate([np.asarray(it[0], dtype=np.int32) for it in items]))).to(dev)
+        pos_np = np.concatenate([np.arange(it[1], it[1] + l, dtype=np.int32) for it, l in zip(items, lens)])
+        pos = torch.from_numpy(pos_np).to(dev)
+        bts = [torch.from_numpy(np.ascontiguousarray(it[2])).to(dev) for it in items]
+        slots = torch.cat([self._slots(bt[None, :].expand(l, -1), pos[o:o + l])
+                           for bt, l, o in zip(bts, lens, offs[:-1].tolist())])
+        hq, hk, hd = self.hq, self.hk, self.hd
+
+        def attn(li, q, k, v):
+            self._append_kv(li, k, v, slots)
+            outs = []
+            for (t_, start, _, _, _), bt, l, o in zip(items, bts, lens, offs[:-1].tolist()):
+                qs = q[o:o + l]
+                if start == 0:
+                    outs.append(flash_attention(qs, k[o:o + l], v[o:o + l], 1, l, hq, hk, hd, causal=True))
+                else:
+                    kk, vv = self._gather_kv(li, bt, start + l)
+                    outs.append(flash_attention(qs, kk, vv, 1, l, hq, hk, hd, causal=True, S=start + l))
+            return torch.cat(outs)
+
+        x = F.embedding(tok, self.tok).reshape(n, -1)
+        delta = None
+        for li in range(len(self.layers)):
+            x, delta = self._layer(li, x, delta, pos, attn)
+        self.steps += 1
+        final = [i for i, it in enumerate(items) if it[3]]
+        results = [(None, None)] * len(items)
+        if not final:
+            return results
+        rows = torch.tensor([int(offs[i + 1]) - 1 for i in final], device=dev, dtype=torch.long)
+        all_greedy = all(items[i][4] for i in final)
+        t, tk = self._head(x[rows], delta[rows], all_greedy)
+        firsts = t.cpu().tolist()
+        if tk is not None:
+            idx, vals = tk[0].cpu().tolist(), tk[1].cpu().tolist()
+        for j, i in enumerate(final):
+            cand = list(zip(idx[j], vals[j])) if tk is not None else None
+            results[i] = (int(firsts[j]), cand)
+        return results
+
+    @torch.no_grad()
     def decode(self, tokens: np.ndarray, positions: np.ndarray, block_tables: np.ndarray,
                window: int = 1, greedy: bool = True):
         """One batched decode call: ``window`` on-device greedy steps (window > 1 requires greedy).

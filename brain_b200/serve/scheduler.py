@@ -203,7 +203,8 @@ class Scheduler:
         npf, nd, win = c.c_uint32(), c.c_uint32(), c.c_uint32()
         lib.bbh_sched_plan(self._h, c.byref(npf), c.byref(nd), c.byref(win))
         rep = StepReport(window=win.value)
-        # ---- prefill chunks
+        # ---- prefill chunks (packed into one forward when the decoder can)
+        plan = []
         for i in range(npf.value):
             rid, s, e, last = c.c_int64(), c.c_uint32(), c.c_uint32(), c.c_int()
             lib.bbh_sched_prefill_item(self._h, i, c.byref(rid), c.byref(s), c.byref(e), c.byref(last))
@@ -213,16 +214,22 @@ class Scheduler:
             lib.bbh_sched_seq_prompt(self._h, rid_v, prompt.ctypes.data)
             bt = np.full(self.max_blocks, -1, dtype=np.int32)
             lib.bbh_sched_seq_table(self._h, rid_v, bt.ctypes.data, self.max_blocks)
-            greedy = info.params.is_greedy()
-            tok, topk = self.dec.prefill_chunk(prompt[s.value:e.value].astype(np.int32), s.value, bt,
-                                               bool(last.value), greedy)
+            plan.append((rid_v, s.value, e.value, bool(last.value), info.params.is_greedy(),
+                         prompt[s.value:e.value].astype(np.int32), bt))
             if s.value == info.prefix_hit:
                 rep.admitted += 1
             rep.prefill_tokens += e.value - s.value
-            if last.value:
-                lib.bbh_sched_commit_prefill(self._h, rid_v, e.value, 1, self._pick(rid_v, tok, topk))
+        if plan:
+            batch = getattr(self.dec, "prefill_batch", None)
+            if batch is not None and len(plan) > 1:
+                outs = batch([(p[5], p[1], p[6], p[3], p[4]) for p in plan])
             else:
-                lib.bbh_sched_commit_prefill(self._h, rid_v, e.value, 0, 0)
+                outs = [self.dec.prefill_chunk(p[5], p[1], p[6], p[3], p[4]) for p in plan]
+            for p, (tok, topk) in zip(plan, outs):
+                if p[3]:
+                    lib.bbh_sched_commit_prefill(self._h, p[0], p[2], 1, self._pick(p[0], tok, topk))
+                else:
+                    lib.bbh_sched_commit_prefill(self._h, p[0], p[2], 0, 0)
         # ---- one batched decode
         n = nd.value
         if n:

@@ -241,3 +241,42 @@ def test_full_pool_with_prefix_cache_still_completes_every_request():
     assert all(r.output_artifacts() == out for r in run.records)
     st = t.sched.stats()
     assert st["running"] == 0 and st["waiting"] == 0 and st["finished"] == 30
+
+
+def test_packed_prefill_equals_one_by_one():
+    """Several prompts (and a continuation chunk) prefilled in one packed forward leave the same
+    paged KV and pick the same first tokens as prefilling them one at a time."""
+    import torch
+    from brain_b200.perf.targets import synth_qwen
+    from brain_b200.serve.engine import QwenEngine
+    m = synth_qwen("2x32x4x200", "cpu")
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, 200, n).astype(np.int32) for n in (37, 64, 21)]
+
+    def tables(eng):
+        out, nxt = [], 0
+        for p in prompts:
+            nb = -(-(len(p) + 8) // eng.block_size)
+            bt = np.full(eng.max_blocks, -1, dtype=np.int32)
+            bt[:nb] = np.arange(nxt, nxt + nb)
+            nxt += nb
+            out.append(bt)
+        return out
+    a = QwenEngine(m, block_size=16, num_blocks=64, max_seq_len=128, max_prefill=64)
+    b = QwenEngine(m, block_size=16, num_blocks=64, max_seq_len=128, max_prefill=64)
+    ta, tb = tables(a), tables(b)
+    # engine a: one by one; the second prompt in two chunks (32 + 32)
+    ra = [a.prefill_chunk(prompts[0], 0, ta[0], True)]
+    a.prefill_chunk(prompts[1][:32], 0, ta[1], False)
+    ra.append(a.prefill_chunk(prompts[1][32:], 32, ta[1], True))
+    ra.append(a.prefill_chunk(prompts[2], 0, ta[2], True, greedy=False))
+    # engine b: first chunk of prompt 1 alone, then everything else packed (incl. the continuation)
+    b.prefill_chunk(prompts[1][:32], 0, tb[1], False)
+    rb = b.prefill_batch([(prompts[0], 0, tb[0], True, True), (prompts[1][32:], 32, tb[1], True, True),
+                          (prompts[2], 0, tb[2], True, False)])
+    assert [r[0] for r in ra] == [r[0] for r in rb]
+    assert rb[0][1] is None or len(rb[0][1]) > 0
+    assert [c[0] for c in ra[2][1][:5]] == [c[0] for c in rb[2][1][:5]]
+    for li in range(2):
+        assert torch.allclose(a.kc[li][:12], b.kc[li][:12], atol=1e-5)
+        assert torch.allclose(a.vc[li][:12], b.vc[li][:12], atol=1e-5)
