@@ -144,8 +144,15 @@ class MoeModel(nn.Module):
         cos, sin = self.rope_tables(x.device, T)
         pos = torch.arange(T, device=x.device, dtype=torch.int32).repeat(B)
         aux_total = None
+        recompute = getattr(self, "recompute_blocks", False) and torch.is_grad_enabled()
         for blk in self.blocks:
-            x, aux = blk(x, B, T, cos, sin, pos)
+            if recompute:
+                # activation recomputation: keep only the block input, re-run the block (including
+                # its expert dispatch/combine, on every rank alike) inside backward
+                from torch.utils.checkpoint import checkpoint
+                x, aux = checkpoint(blk, x, B, T, cos, sin, pos, use_reentrant=False)
+            else:
+                x, aux = blk(x, B, T, cos, sin, pos)
             aux_total = aux if aux_total is None else aux_total + aux
         return F.rmsnorm(x, self.norm, self.cfg.rms_eps), aux_total
 

@@ -105,7 +105,6 @@ def serve_tp(args) -> dict:
     from .workload import Arrival, standard
     rank, world, dev = _dist_init()
     import faulthandler
-    faulthandler.dump_traceback_later(args.stuck_after, exit=True)     # a stuck rank prints its stack and exits
     tp = TensorParallel(impl=args.impl, device=dev, arena_mb=1024, wait_seconds=5.0) if world > 1 else None
     cfg = QwenConfig.preset(args.model, 4096)
     if args.layers:
@@ -125,7 +124,8 @@ def serve_tp(args) -> dict:
     # warm-up: a few short requests so graphs for small buckets and all lazy setup exist
     warm = standard("serving_mix", Arrival.closed_loop(min(conc, 8)), 8, seed=1, vocab=cfg.vocab)
     warm.classes[0].output.n = 8
-    target = SchedulerTarget(None, max_batch=conc, ctx=per_seq * 16, engine=eng, name=f"qwen3-{args.model}")
+    target = SchedulerTarget(None, max_batch=conc, ctx=per_seq * 16, engine=eng, name=f"qwen3-{args.model}",
+                             admit_batch=args.admit_batch, prefix_cache=False)   # random prompts share no prefix
     drive(target, warm)
     if world > 1:
         dist.barrier()
@@ -148,7 +148,7 @@ def serve_tp(args) -> dict:
             "ttft_ms_p99": j["ttfa_ms"].get("p99"), "tpot_ms_p50": j["tpoa_ms"].get("p50"),
             "e2e_ms_p50": j["e2e_ms"].get("p50"), "requests": s.requests, "completed": s.completed,
             "input_tokens": s.input_artifacts, "output_tokens": s.output_artifacts, "wall_s": s.wall_s,
-            "concurrency": conc, "weights": args.weights, "impl": args.impl, "layers": cfg.n_layers,
+            "concurrency": conc, "admit_batch": args.admit_batch, "weights": args.weights, "impl": args.impl, "layers": cfg.n_layers,
             "kv_pool_gb": eng.kv_pool_bytes() / 2**30, "weight_gb_per_rank": eng.weight_bytes() / 2**30,
             "cuda_graph_replays": eng.graph_replays, "engine_steps": eng.steps, "build_s": build_s,
             "gpu_launches": _cuda.launch_count - launches0, "dtype": "int8 weights+activations, bf16 KV" if args.weights == "int8" else "bf16",
@@ -192,13 +192,17 @@ def train_3d(args) -> dict:
     if args.layers:
         cfg.n_layers = args.layers
     tr = Trainer3D(cfg, Grid(tp=tp, pp=pp, dp=1), dev, impl=args.impl, schedule=args.schedule, seed=1234)
-    g = torch.Generator().manual_seed(0)
+    gd = torch.Generator(device=dev).manual_seed(0)     # same seed on every rank: same batches
     n_micro, T = args.micro, args.seq
-    toks = [torch.randint(0, cfg.vocab, (1, T), generator=g, dtype=torch.int32).to(dev) for _ in range(n_micro)]
-    tgts = [torch.randint(0, cfg.vocab, (1, T), generator=g).to(dev) for _ in range(n_micro)]
     count = n_micro * T
+
+    def step():
+        # fresh uniform-random tokens every step (drawn on the device, no host traffic)
+        toks = [torch.randint(0, cfg.vocab, (1, T), generator=gd, device=dev, dtype=torch.int32) for _ in range(n_micro)]
+        tgts = [torch.randint(0, cfg.vocab, (1, T), generator=gd, device=dev) for _ in range(n_micro)]
+        return tr.train_step(toks, tgts, 1e-4, count)
     launches0 = _cuda.launch_count
-    ms, loss = _timed_steps(lambda: tr.train_step(toks, tgts, 1e-4, count), args.steps, args.warmup, dev, world)
+    ms, loss = _timed_steps(step, args.steps, args.warmup, dev, world)
     _cuda.check_error()
     flops = tr.model.flops_per_token(T) if hasattr(tr.model, "flops_per_token") else 0.0
     return {"config": "train-3d", "metric": f"train tok/s (Qwen3-{args.model} bf16 TP{tp}xPP{pp} {args.schedule})",
@@ -240,6 +244,7 @@ def train_ep(args) -> dict:
                 p.fill_(1.0)
             else:
                 p.normal_(0.0, 0.02, generator=gen_local if ".moe.w_" in name else gen)
+    model.recompute_blocks = not args.no_recompute
     tr = TrainerEP(model, dev, dtype=torch.bfloat16)
     g = torch.Generator().manual_seed(rank)
     B, T = args.seqs_per_gpu, args.seq
@@ -258,7 +263,7 @@ def train_ep(args) -> dict:
             "value": count / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "ms_per_step": ms, "steps": args.steps,
             "warmup": args.warmup, "seqs_per_gpu": B, "seq_len": T, "micro_batch": args.micro_batch, "impl": args.impl,
             "layers": cfg.n_layers, "experts": cfg.n_experts, "final_loss": float(loss_t),
-            "shared_params_b": tr.shared.n_train / 1e9, "expert_params_per_rank_b": tr.expert.n_train / 1e9,
+            "recompute_blocks": bool(model.recompute_blocks), "shared_params_b": tr.shared.n_train / 1e9, "expert_params_per_rank_b": tr.expert.n_train / 1e9,
             "mem_gb": torch.cuda.max_memory_allocated() / 2**30, "gpu_launches": _cuda.launch_count - launches0,
             "dtype": "bf16", "data": "synthetic", "timing": "CUDA events, max over ranks"}
 
@@ -275,6 +280,7 @@ def main(argv=None):
     ap.add_argument("--micro-batch", type=int, default=1, help="train-ep: sequences per forward/backward")
     ap.add_argument("--experts", type=int, default=0)
     ap.add_argument("--arena-mb", type=int, default=4096)
+    ap.add_argument("--no-recompute", action="store_true", help="train-ep: keep all block activations (more memory)")
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--layers", type=int, default=0, help="override depth (debug; invalidates the number)")
     ap.add_argument("--model", default="8b")
@@ -284,6 +290,7 @@ def main(argv=None):
     ap.add_argument("--concurrency", type=int, default=256)
     ap.add_argument("--out-tokens", type=int, default=256)
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--admit-batch", type=int, default=16, help="serve-tp: admit new requests in groups of this many")
     ap.add_argument("--stuck-after", type=int, default=600, help="seconds before a stuck rank dumps its stack and exits")
     a = ap.parse_args(argv)
     if a.which == "cpu-dp" and not a.layers:
@@ -292,6 +299,9 @@ def main(argv=None):
         a.steps = 3
     if a.which == "train-3d" and a.model == "8b":
         a.model = "14b"
+    if a.which != "cpu-dp":
+        import faulthandler
+        faulthandler.dump_traceback_later(a.stuck_after, exit=True)   # a stuck rank prints its stack and exits
     out = {"cpu-dp": cpu_dp, "serve-tp": serve_tp, "train-3d": train_3d, "train-ep": train_ep}[a.which](a)
     import os
     if int(os.environ.get("RANK", "0")) == 0:

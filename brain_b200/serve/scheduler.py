@@ -44,6 +44,7 @@ _host.register({
     "bbh_sched_seq_table": (c.c_uint32, [c.c_void_p, c.c_int64, c.c_void_p, c.c_uint32]),
     "bbh_sched_forget": (None, [c.c_void_p, c.c_int64]),
     "bbh_sched_decode_all_greedy": (c.c_int, [c.c_void_p]),
+    "bbh_sched_set_admit": (None, [c.c_void_p, c.c_uint32, c.c_uint32]),
     "bbh_sched_step_report": (c.c_uint32, [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_uint32, c.c_void_p,
                                            c.c_uint32]),
     "bbh_sched_step_tokens": (c.c_uint32, [c.c_void_p]),
@@ -106,7 +107,10 @@ class SeqInfo:
 class Scheduler:
     def __init__(self, decoder: PagedDecoder, max_batch: int = 16, eos: Optional[int] = None,
                  window: int = 4, policy: str = "unbounded_queue", policy_arg: float = 0.0,
-                 prefix_cache: bool = True):
+                 prefix_cache: bool = True, admit_batch: int = 1, admit_max_wait: int = 64):
+        """``admit_batch`` > 1 batches admissions: new requests join only once that many slots are
+        free (or ``admit_max_wait`` steps passed), trading a little queueing delay for far fewer
+        prefill-carrying steps under a saturated closed loop."""
         self.dec = decoder
         pol = {"unbounded_queue": 0, "max_queue_depth": 1, "deadline_aware": 2}[policy]
         self.max_blocks = (decoder.max_seq_len + decoder.block_size - 1) // decoder.block_size
@@ -116,6 +120,8 @@ class Scheduler:
             float(policy_arg), int(prefix_cache))
         if not self._h:
             raise ValueError("invalid scheduler configuration")
+        if admit_batch > 1:
+            _host.lib().bbh_sched_set_admit(self._h, int(admit_batch), int(admit_max_wait))
         self._rngs: Dict[int, Rng] = {}
         self.max_batch = max_batch
 

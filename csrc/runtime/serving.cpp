@@ -336,7 +336,17 @@ class Scheduler {
       const uint32_t have = static_cast<uint32_t>(r.table.blocks.size());
       if (full > have) outstanding += full - have;
     }
-    while (!waiting_.empty() && running_.size() < cfg_.max_batch) {
+    // Admission batching: with `admit_batch` > 1 new requests are taken in only once that many
+    // slots are free (or nothing runs, or the head of the queue has waited `admit_max_wait`
+    // steps), so prefill work arrives in a few large chunks instead of one small one per step.
+    ++steps_since_admit_;
+    bool admit_now = true;
+    if (admit_batch_ > 1 && !running_.empty() && !waiting_.empty()) {
+      const size_t free_slots = cfg_.max_batch > running_.size() ? cfg_.max_batch - running_.size() : 0;
+      const size_t want = std::min<size_t>(admit_batch_, waiting_.size());
+      admit_now = free_slots >= want || steps_since_admit_ >= admit_max_wait_;
+    }
+    while (admit_now && !waiting_.empty() && running_.size() < cfg_.max_batch) {
       Seq& s = *seqs_[waiting_.front()];
       const uint32_t total = static_cast<uint32_t>(s.prompt.size()) + s.max_new;
       // prefix-cache hit: adopt shared full blocks (never the whole prompt: the last token must
@@ -366,6 +376,7 @@ class Scheduler {
       outstanding += blocks_for(total) - static_cast<uint32_t>(s.table.blocks.size());
       s.state = RUNNING;
       running_.push_back(s.id);
+      steps_since_admit_ = 0;
       prefill_plan.push_back({s.id, s.prefilled, s.prefilled + n, s.prefilled + n == s.prompt.size()});
       budget = budget > n ? budget - n : 0;
       any = true;
@@ -450,6 +461,7 @@ class Scheduler {
   PrefixCache& prefix() { return prefix_; }
   size_t n_waiting() const { return waiting_.size(); }
   size_t n_running() const { return running_.size(); }
+  uint32_t admit_batch_ = 1, admit_max_wait_ = 64, steps_since_admit_ = 0;
   uint64_t last_need_ = 0, last_bad_token_ = 0;
   uint64_t prefix_hit_tokens_ = 0, prefix_lookup_tokens_ = 0, steps_ = 0, submitted_ = 0, finished_ = 0,
            cancelled_ = 0, generated_ = 0;
@@ -648,6 +660,11 @@ BBH_API uint32_t bbh_sched_seq_table(void* s, int64_t id, int32_t* blocks, uint3
   const uint32_t n = std::min<uint32_t>(max_blocks, static_cast<uint32_t>(q->table.blocks.size()));
   for (uint32_t i = 0; i < n; ++i) blocks[i] = static_cast<int32_t>(q->table.blocks[i]);
   return static_cast<uint32_t>(q->table.blocks.size());
+}
+BBH_API void bbh_sched_set_admit(void* s, uint32_t batch, uint32_t max_wait_steps) {
+  auto* sc = static_cast<Scheduler*>(s);
+  sc->admit_batch_ = batch < 1 ? 1 : batch;
+  sc->admit_max_wait_ = max_wait_steps < 1 ? 1 : max_wait_steps;
 }
 BBH_API int bbh_sched_decode_all_greedy(void* s) { return static_cast<Scheduler*>(s)->decode_all_greedy ? 1 : 0; }
 // The current step's results in one call: returns the entry count; fills ids / n_new / finished per

@@ -280,3 +280,24 @@ def test_packed_prefill_equals_one_by_one():
     for li in range(2):
         assert torch.allclose(a.kc[li][:12], b.kc[li][:12], atol=1e-5)
         assert torch.allclose(a.vc[li][:12], b.vc[li][:12], atol=1e-5)
+
+
+def test_admission_batching_takes_requests_in_groups():
+    from brain_b200.perf.driver import drive
+    from brain_b200.perf.metrics import Summary
+    from brain_b200.perf.targets import SchedulerTarget, synth_qwen
+    from brain_b200.perf.workload import Arrival, standard
+    m = synth_qwen("1x32x4x300", "cpu")
+
+    def run(admit):
+        wl = standard("serving_mix", Arrival.closed_loop(8), 32, seed=0, vocab=300)
+        wl.classes[0].input.lo, wl.classes[0].input.hi = 16, 64
+        wl.classes[0].output = type(wl.classes[0].output).uniform(4, 24)
+        t = SchedulerTarget(m, max_batch=8, ctx=256, admit_batch=admit)
+        r = drive(t, wl, max_seconds=120)
+        s = Summary.build(r.records, r.wall_s, wl.classes[0].slo)
+        return s, t.sched.stats(), [t.outputs(i) for i in r.ids]
+    s1, st1, o1 = run(1)
+    s4, st4, o4 = run(4)
+    assert s1.completed == s4.completed == 32 and s4.output_artifacts == s1.output_artifacts
+    assert o1 == o4                                  # batching admissions never changes greedy outputs
