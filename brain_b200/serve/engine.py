@@ -187,8 +187,8 @@ class QwenEngine:
         if self.cuda:
             splits = self.decode_splits
             if splits <= 0:
-                # enough CTAs to fill the machine: B * hk * splits >= ~2 per SM
-                splits = max(1, min(16, (2 * 148 + B * hk - 1) // (B * hk)))
+                # enough CTAs to fill the machine: B * hk * splits >= ~4 per SM
+                splits = max(1, min(16, (4 * 148 + B * hk - 1) // (B * hk)))
             out = torch.empty(B, hq * hd, device=self.device, dtype=self.dtype)
             part_o = torch.empty(B * hq * splits * hd, device=self.device, dtype=torch.float32)
             part_ml = torch.empty(B * hq * splits * 2, device=self.device, dtype=torch.float32)

@@ -61,6 +61,15 @@ __global__ void kv_gather_kernel(const __nv_bfloat16* __restrict__ kc,
 // One CTA (4 warps) per (sequence b, kv head, split).  G = query heads per kv head (<= 8).
 // q: [B, hq*hd]; block_tables: int32 [B, max_blocks]; seqlens: int32[B] (keys visible to the query).
 // part_o: fp32 [B, hq, splits, hd], part_ml: fp32 [B, hq, splits, 2] (running max in log2 domain, sum).
+//
+// Work layout: the head dimension is split over 8 lanes (HD/8 contiguous dims each), so a warp holds
+// four 8-lane groups and each group owns one key per step; the CTA's 4 warps x 4 groups take the 16
+// keys of one KV block per step (one block-table lookup per warp and step).  The query slice and the
+// output accumulators of all G heads stay in registers; a key's dot products are finished by a
+// 3-step butterfly inside its group, which leaves the score in all 8 lanes, so P.V needs no further
+// exchange.  Every group keeps its own running (max, sum, output) and the 16 partial states are
+// merged once at the end.  An earlier form (one lane per key, query read from shared memory for
+// every multiply) spent ~300 us per layer at batch 256 and was the largest item of a decode step.
 template <int HD, int G>
 __global__ void __launch_bounds__(128)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
@@ -69,97 +78,131 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
                     const int* __restrict__ seqlens, float* __restrict__ part_o,
                     float* __restrict__ part_ml, int hq, int hk, int bs, int splits,
                     float scale_log2) {
-  constexpr int PER = HD / 32;  // output columns per lane
+  constexpr int DPL = HD / 8;   // dims per lane: 16 (hd 128) or 8 (hd 64)
+  constexpr int NV = DPL / 8;   // 16-byte vectors per lane per row
   const int b = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = lane >> 3, sub = lane & 7;
   const int S = seqlens[b];
   const int per_split = ((S + splits - 1) / splits + 31) / 32 * 32;
   const int k_begin = sp * per_split;
   const int k_end = min(S, k_begin + per_split);
-  __shared__ float sq[G][HD];
   __shared__ float s_o[4][G][HD];
   __shared__ float s_m[4][G], s_l[4][G];
-  for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
-    const int g = i / HD, c = i % HD;
-    sq[g][c] = __bfloat162float(q[(size_t)b * ldq + (kvh * G + g) * HD + c]) * scale_log2;
+
+  float qr[G][DPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const bf16x8* qp = reinterpret_cast<const bf16x8*>(q + (size_t)b * ldq + (kvh * G + g) * HD + sub * DPL);
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      float f[8];
+      unpack8(qp[v], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qr[g][v * 8 + j] = f[j] * scale_log2;
+    }
   }
-  __syncthreads();
-  float m[G], l[G], o[G][PER];
+  float m[G], l[G], o[G][DPL];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     m[g] = -INFINITY;
     l[g] = 0.f;
 #pragma unroll
-    for (int j = 0; j < PER; ++j) o[g][j] = 0.f;
+    for (int j = 0; j < DPL; ++j) o[g][j] = 0.f;
   }
   const int* bt = block_tables + (size_t)b * max_blocks;
-  for (int k0 = k_begin + warp * 32; k0 < k_end; k0 += 4 * 32) {
-    const int key = k0 + lane;
-    const bool valid = key < k_end;
-    float s[G];
+  // 16 keys per CTA step: warp w takes keys [k0 + 4w, k0 + 4w + 4), group g one of them.  The rows of
+  // the NEXT step are fetched before the current ones are used, so two steps of loads are in flight.
+  bf16x8 kraw[NV], vraw[NV], knext[NV], vnext[NV];
+  auto fetch = [&](int k0, bf16x8 (&kk)[NV], bf16x8 (&vv)[NV]) -> bool {
+    const int key = k0 + warp * 4 + grp;
+    if (key >= k_end) return false;
+    const int blk = bt[key / bs], off = key % bs;
+    const size_t row = (((size_t)blk * hk + kvh) * bs + off) * HD + sub * DPL;
+    const bf16x8* kr = reinterpret_cast<const bf16x8*>(kc + row);
+    const bf16x8* vr = reinterpret_cast<const bf16x8*>(vc + row);
 #pragma unroll
-    for (int g = 0; g < G; ++g) s[g] = 0.f;
+    for (int v = 0; v < NV; ++v) {
+      kk[v] = kr[v];
+      vv[v] = vr[v];
+    }
+    return true;
+  };
+  bool valid = fetch(k_begin, kraw, vraw);
+  for (int k0 = k_begin; k0 < k_end; k0 += 16) {
+    const bool valid_next = (k0 + 16 < k_end) ? fetch(k0 + 16, knext, vnext) : false;
     if (valid) {
-      const int blk = bt[key / bs], off = key % bs;
-      const bf16x8* kr = reinterpret_cast<const bf16x8*>(
-          kc + (((size_t)blk * hk + kvh) * bs + off) * HD);
+      float kf[DPL], vf[DPL];
 #pragma unroll
-      for (int c = 0; c < HD / 8; ++c) {
-        float f[8];
-        unpack8(kr[c], f);
+      for (int v = 0; v < NV; ++v) {
+        float t[8];
+        unpack8(kraw[v], t);
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
+        for (int j = 0; j < 8; ++j) kf[v * 8 + j] = t[j];
+        unpack8(vraw[v], t);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) s[g] += f[j] * sq[g][c * 8 + j];
-        }
-      }
-    }
-    float p[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float sv = valid ? s[g] : -INFINITY;
-      const float mx = warp_max(sv);
-      const float m_new = fmaxf(m[g], mx);
-      const float alpha = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - m_new);
-      p[g] = valid ? exp2f(sv - m_new) : 0.f;
-      l[g] = l[g] * alpha + warp_sum(p[g]);
-#pragma unroll
-      for (int j = 0; j < PER; ++j) o[g][j] *= alpha;
-      m[g] = m_new;
-    }
-    // P.V: every lane owns PER output columns; walk the 32 keys of this group
-    const int nk = min(32, k_end - k0);
-    for (int t = 0; t < nk; ++t) {
-      const int kk = k0 + t;
-      const int blk = bt[kk / bs], off = kk % bs;
-      const __nv_bfloat16* vr = vc + (((size_t)blk * hk + kvh) * bs + off) * HD + lane * PER;
-      float vv[PER];
-      if (PER == 4) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(vr);
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-        const float2 c2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-        vv[0] = a.x; vv[1] = a.y; vv[PER - 2] = c2.x; vv[PER - 1] = c2.y;
-      } else {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vr));
-        vv[0] = a.x; vv[1] = a.y;
+        for (int j = 0; j < 8; ++j) vf[v * 8 + j] = t[j];
       }
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        const float pg = __shfl_sync(0xffffffffu, p[g], t);
+        float sc = 0.f;
 #pragma unroll
-        for (int j = 0; j < PER; ++j) o[g][j] += pg * vv[j];
+        for (int j = 0; j < DPL; ++j) sc += kf[j] * qr[g][j];
+        // the 8 lanes of a group are all valid or all invalid, so they shuffle among themselves
+        const unsigned int gm = 0xffu << (grp * 8);
+        sc += __shfl_xor_sync(gm, sc, 1);
+        sc += __shfl_xor_sync(gm, sc, 2);
+        sc += __shfl_xor_sync(gm, sc, 4);
+        if (sc > m[g]) {   // new running maximum: rescale what this group accumulated so far
+          const float alpha = exp2f(m[g] - sc);   // exp2(-inf) = 0 on the first key
+          l[g] *= alpha;
+#pragma unroll
+          for (int j = 0; j < DPL; ++j) o[g][j] *= alpha;
+          m[g] = sc;
+        }
+        const float pg = exp2f(sc - m[g]);
+        l[g] += pg;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) o[g][j] += pg * vf[j];
       }
+    }
+    valid = valid_next;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      kraw[v] = knext[v];
+      vraw[v] = vnext[v];
+    }
+  }
+  // merge the 4 groups of the warp (lanes sub, sub+8, sub+16, sub+24 hold the same dims)
+#pragma unroll
+  for (int step = 8; step <= 16; step <<= 1) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m[g], step);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l[g], step);
+      const float mm = fmaxf(m[g], m2);
+      const float a1 = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mm);
+      const float a2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - mm);
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) {
+        const float o2 = __shfl_xor_sync(0xffffffffu, o[g][j], step);
+        o[g][j] = o[g][j] * a1 + o2 * a2;
+      }
+      l[g] = l[g] * a1 + l2 * a2;
+      m[g] = mm;
     }
   }
   // merge the 4 warps of the CTA
+  if (grp == 0) {
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    if (lane == 0) {
-      s_m[warp][g] = m[g];
-      s_l[warp][g] = l[g];
+    for (int g = 0; g < G; ++g) {
+      if (sub == 0) {
+        s_m[warp][g] = m[g];
+        s_l[warp][g] = l[g];
+      }
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) s_o[warp][g][sub * DPL + j] = o[g][j];
     }
-#pragma unroll
-    for (int j = 0; j < PER; ++j) s_o[warp][g][lane * PER + j] = o[g][j];
   }
   __syncthreads();
   for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {

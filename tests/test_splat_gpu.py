@@ -58,33 +58,73 @@ def test_render_matches_cpu_oracle(n, wh, depth, aa):
     assert float(err.mean()) < 2e-4 and float((err > 2e-2).float().mean()) < 2e-3
 
 
-def test_render_diff_gradients_match_finite_differences():
+def _composite_dense(xy, conic_op, colors, depth, rad, H, W, bg):
+    """Dense PyTorch restatement of the compositing (every Gaussian against every pixel, sorted by
+    depth), differentiable by autograd; the skip tests are masks, exactly like the kernel."""
+    order = torch.argsort(depth)
+    xy, conic_op, colors, rad = xy[order], conic_op[order], colors[order], rad[order]
+    ys, xs = torch.meshgrid(torch.arange(H, device=xy.device) + 0.5, torch.arange(W, device=xy.device) + 0.5, indexing="ij")
+    dx = xy[:, 0, None, None] - xs[None]
+    dy = xy[:, 1, None, None] - ys[None]
+    sigma = 0.5 * (conic_op[:, 0, None, None] * dx * dx + conic_op[:, 2, None, None] * dy * dy) + conic_op[:, 1, None, None] * dx * dy
+    alpha = torch.clamp(conic_op[:, 3, None, None] * torch.exp(-sigma), max=0.99)
+    keep = (dx.abs() <= rad[:, 0, None, None]) & (dy.abs() <= rad[:, 1, None, None]) & (sigma >= 0) & (alpha >= 1.0 / 255.0)
+    alpha = torch.where(keep, alpha, torch.zeros_like(alpha))
+    T = torch.ones(H, W, device=xy.device)
+    C = torch.zeros(H, W, 3, device=xy.device)
+    alive = torch.ones(H, W, dtype=torch.bool, device=xy.device)
+    for k in range(xy.shape[0]):
+        nt = T * (1 - alpha[k])
+        alive = alive & ~((nt <= 1e-4) & (alpha[k] > 0))
+        a_k = torch.where(alive, alpha[k], torch.zeros_like(alpha[k]))
+        C = C + (a_k * T)[..., None] * colors[k]
+        T = T * (1 - a_k)
+    return torch.cat([C + T[..., None] * torch.tensor(bg, device=xy.device), (1 - T)[..., None]], dim=-1)
+
+
+def test_render_diff_gradients_match_autograd_reference_and_finite_differences():
+    """Analytic gradients of the CUDA rasteriser against autograd through a dense PyTorch
+    restatement (both treat the contribution tests as fixed masks), then a finite-difference check
+    on the fields whose loss is smooth (colours exactly linear; means, where the moving cut-off
+    boundary gains on one side what it loses on the other)."""
+    from brain_b200.splat.render import _Binned, project_torch
     torch.manual_seed(0)
     s = Splats.random(60, seed=3)
     s.scales = s.scales * 3.0
-    cam = Camera.look_at([0, 0, -3.0], [0, 0, 0], [0, 1, 0], 50.0, 48, 48)
-    opts = RenderOpts(bg=(0.05, 0.05, 0.05))
+    H = W = 48
+    cam = Camera.look_at([0, 0, -3.0], [0, 0, 0], [0, 1, 0], 50.0, W, H)
+    opts = RenderOpts(bg=(0.05, 0.1, 0.15))
     dev = "cuda"
-    fields = {k: getattr(s, k).to(dev).double().float().requires_grad_() for k in ("means", "quats", "scales", "opacities", "colors")}
-    wimg = torch.rand(48, 48, 4, device=dev)
+    names = ("means", "quats", "scales", "opacities", "colors")
+    wimg = torch.rand(H, W, 4, device=dev)
+
+    def leaves():
+        return {k: getattr(s, k).to(dev).clone().requires_grad_() for k in names}
+    f1 = leaves()
+    img = render_diff(Splats(*(f1[k] for k in names)), cam, opts)
+    (img * wimg).sum().backward()
+    f2 = leaves()
+    b = _Binned(Splats(*(f2[k].detach() for k in names)), cam, opts)
+    xy, conic_op = project_torch(f2["means"], f2["quats"], f2["scales"], f2["opacities"], cam, opts)
+    live = b.touched > 0
+    ref_img = _composite_dense(xy[live], conic_op[live], f2["colors"][live], b.depth[live], b.rad[live], H, W, opts.bg)
+    assert float((ref_img - img.detach()).abs().max()) < 2e-3
+    (ref_img * wimg).sum().backward()
+    for k in names:
+        ga, gr = f1[k].grad, f2[k].grad
+        assert float((ga - gr).norm() / gr.norm().clamp_min(1e-6)) < 2e-3, k
 
     def loss_of(f):
-        img = render_diff(Splats(f["means"], f["quats"], f["scales"], f["opacities"], f["colors"]), cam, opts)
-        return (img * wimg).sum()
-
-    loss = loss_of(fields)
-    loss.backward()
-    base = render(Splats(*(fields[k].detach() for k in ("means", "quats", "scales", "opacities", "colors"))), cam, opts)
-    assert float((render_diff(Splats(*(fields[k].detach() for k in ("means", "quats", "scales", "opacities", "colors"))), cam, opts) - base).abs().max()) < 1e-3
+        return float((render_diff(Splats(*(f[k] for k in names)), cam, opts) * wimg).sum())
     g = torch.Generator().manual_seed(1)
-    for name, eps in (("colors", 1e-2), ("opacities", 2e-3), ("means", 2e-3), ("scales", 1e-3), ("quats", 2e-3)):
-        p = fields[name]
+    for name, eps, tol in (("colors", 1e-2, 0.01), ("means", 2e-3, 0.15)):
+        p = f1[name]
         v = (torch.randint(0, 2, p.shape, generator=g).float() * 2 - 1).to(dev)
         analytic = float((p.grad * v).sum())
         with torch.no_grad():
-            plus = dict(fields); plus[name] = p.detach() + eps * v
-            minus = dict(fields); minus[name] = p.detach() - eps * v
-            plus = {k: t.detach() for k, t in plus.items()}
-            minus = {k: t.detach() for k, t in minus.items()}
-            numeric = float((loss_of(plus) - loss_of(minus)) / (2 * eps))
-        assert abs(analytic - numeric) <= 0.02 * max(abs(analytic), abs(numeric)) + 0.05, (name, analytic, numeric)
+            plus = {k: t.detach() for k, t in f1.items()}
+            minus = dict(plus)
+            plus[name] = p.detach() + eps * v
+            minus[name] = p.detach() - eps * v
+            numeric = (loss_of(plus) - loss_of(minus)) / (2 * eps)
+        assert abs(analytic - numeric) <= tol * max(abs(analytic), abs(numeric)) + 0.05, (name, analytic, numeric)
