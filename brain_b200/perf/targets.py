@@ -94,7 +94,7 @@ class SchedulerTarget(PerfTarget):
 
     def __init__(self, model, max_batch: int = 256, ctx: int = 4096, block_size: int = 16, weights: str = "bf16",
                  num_blocks: Optional[int] = None, tp=None, name: str = "qwen", engine=None, admit_batch: int = 1,
-                 prefix_cache: bool = True):
+                 prefix_cache: bool = True, prefill_budget: int = 0):
         from ..serve.engine import QwenEngine
         from ..serve.scheduler import Scheduler
         per_seq = -(-ctx // block_size)
@@ -102,7 +102,7 @@ class SchedulerTarget(PerfTarget):
         self.engine = engine or QwenEngine(model, block_size=block_size, num_blocks=nb, max_seq_len=ctx,
                                            max_prefill=min(ctx, 2048), weights=weights, tp=tp)
         self.sched = Scheduler(self.engine, max_batch=max_batch, eos=None, admit_batch=admit_batch,
-                               prefix_cache=prefix_cache)
+                               prefix_cache=prefix_cache, prefill_budget=prefill_budget)
         self.live: Dict[int, bool] = {}
         self.admitted: Dict[int, bool] = {}
         self.info = {"model": name, "artifact_unit": "token", "max_batch": max_batch, "ctx": ctx,

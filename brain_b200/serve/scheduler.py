@@ -45,6 +45,7 @@ _host.register({
     "bbh_sched_forget": (None, [c.c_void_p, c.c_int64]),
     "bbh_sched_decode_all_greedy": (c.c_int, [c.c_void_p]),
     "bbh_sched_set_admit": (None, [c.c_void_p, c.c_uint32, c.c_uint32]),
+    "bbh_sched_set_prefill_budget": (None, [c.c_void_p, c.c_uint32]),
     "bbh_sched_step_report": (c.c_uint32, [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_uint32, c.c_void_p,
                                            c.c_uint32]),
     "bbh_sched_step_tokens": (c.c_uint32, [c.c_void_p]),
@@ -107,7 +108,8 @@ class SeqInfo:
 class Scheduler:
     def __init__(self, decoder: PagedDecoder, max_batch: int = 16, eos: Optional[int] = None,
                  window: int = 4, policy: str = "unbounded_queue", policy_arg: float = 0.0,
-                 prefix_cache: bool = True, admit_batch: int = 1, admit_max_wait: int = 64):
+                 prefix_cache: bool = True, admit_batch: int = 1, admit_max_wait: int = 64,
+                 prefill_budget: int = 0):
         """``admit_batch`` > 1 batches admissions: new requests join only once that many slots are
         free (or ``admit_max_wait`` steps passed), trading a little queueing delay for far fewer
         prefill-carrying steps under a saturated closed loop."""
@@ -122,6 +124,8 @@ class Scheduler:
             raise ValueError("invalid scheduler configuration")
         if admit_batch > 1:
             _host.lib().bbh_sched_set_admit(self._h, int(admit_batch), int(admit_max_wait))
+        if prefill_budget > 0:      # prompt tokens per step (default 2 x max_prefill)
+            _host.lib().bbh_sched_set_prefill_budget(self._h, int(prefill_budget))
         self._rngs: Dict[int, Rng] = {}
         self.max_batch = max_batch
 

@@ -314,7 +314,7 @@ class Scheduler {
     step_out.clear();
     step_tokens.clear();
     // (1) continue partially prefilled sequences, then admit new ones, under the token budget
-    uint32_t budget = 2 * cfg_.max_prefill;
+    uint32_t budget = prefill_budget_ ? prefill_budget_ : 2 * cfg_.max_prefill;
     bool any = false;
     for (int64_t id : running_) {
       Seq& s = *seqs_[id];
@@ -342,9 +342,10 @@ class Scheduler {
     ++steps_since_admit_;
     bool admit_now = true;
     if (admit_batch_ > 1 && !running_.empty() && !waiting_.empty()) {
+      // a closed-loop client hands over one new request per finished one, so the queue length says
+      // nothing: wait until a whole group of slots is free (or the head waited long enough)
       const size_t free_slots = cfg_.max_batch > running_.size() ? cfg_.max_batch - running_.size() : 0;
-      const size_t want = std::min<size_t>(admit_batch_, waiting_.size());
-      admit_now = free_slots >= want || steps_since_admit_ >= admit_max_wait_;
+      admit_now = free_slots >= admit_batch_ || steps_since_admit_ >= admit_max_wait_;
     }
     while (admit_now && !waiting_.empty() && running_.size() < cfg_.max_batch) {
       Seq& s = *seqs_[waiting_.front()];
@@ -461,7 +462,7 @@ class Scheduler {
   PrefixCache& prefix() { return prefix_; }
   size_t n_waiting() const { return waiting_.size(); }
   size_t n_running() const { return running_.size(); }
-  uint32_t admit_batch_ = 1, admit_max_wait_ = 64, steps_since_admit_ = 0;
+  uint32_t admit_batch_ = 1, admit_max_wait_ = 64, steps_since_admit_ = 0, prefill_budget_ = 0;
   uint64_t last_need_ = 0, last_bad_token_ = 0;
   uint64_t prefix_hit_tokens_ = 0, prefix_lookup_tokens_ = 0, steps_ = 0, submitted_ = 0, finished_ = 0,
            cancelled_ = 0, generated_ = 0;
@@ -666,6 +667,7 @@ BBH_API void bbh_sched_set_admit(void* s, uint32_t batch, uint32_t max_wait_step
   sc->admit_batch_ = batch < 1 ? 1 : batch;
   sc->admit_max_wait_ = max_wait_steps < 1 ? 1 : max_wait_steps;
 }
+BBH_API void bbh_sched_set_prefill_budget(void* s, uint32_t tokens) { static_cast<Scheduler*>(s)->prefill_budget_ = tokens; }
 BBH_API int bbh_sched_decode_all_greedy(void* s) { return static_cast<Scheduler*>(s)->decode_all_greedy ? 1 : 0; }
 // The current step's results in one call: returns the entry count; fills ids / n_new / finished per
 // entry and the new tokens flattened in entry order (`tokens` holds at least `cap_tokens`).
