@@ -115,6 +115,18 @@ def run_perf(argv: List[str], device: str = "auto") -> int:
         checks = gate.compare(c, b, floor)
         print(gate.render(checks, floor))
         return 0 if (sub == "compare" or gate.passed(checks)) else 1
+    if sub == "faults":
+        from . import faults
+        names = [n for n in argv[1:] if not n.startswith("-")] or None
+        bad = [n for n in (names or []) if n not in faults.SCENARIOS]
+        if bad:
+            print(f"unknown fault {bad[0]!r}; one of: {' '.join(faults.SCENARIOS)}", file=sys.stderr)
+            return 2
+        res = faults.run_all(names)
+        for r in res:
+            print(f"{r.fault:<22} reported {str(r.reported):<5} clean {str(r.clean):<5} survived "
+                  f"{str(r.survived):<5} {'PASS' if r.passed else 'FAIL'}  {r.detail}")
+        return 0 if all(r.passed for r in res) else 1
     print("usage: brain perf list | run <workload> [--target T --requests N --concurrency C --out F] | "
-          "compare A B | gate A B [--tolerance X]", file=sys.stderr)
+          "compare A B | gate A B [--tolerance X] | faults [NAME…]", file=sys.stderr)
     return 2

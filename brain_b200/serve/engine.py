@@ -130,6 +130,9 @@ class QwenEngine:
         self.decode_splits = decode_splits
         self.steps = 0
         self.cuda_graphs = bool(cuda_graphs) and self.cuda
+        #: host-side fault-injection point: called with "prefill" / "decode" before the device work
+        #: of that call is issued; raising from it models a failed launch without touching the GPU
+        self.fault_hook = None
         self._graphs = {}
         self.graph_replays = 0
 
@@ -237,6 +240,8 @@ class QwenEngine:
                       greedy: bool = True):
         """Process prompt positions [start, start+n) of one sequence.  Returns (first token, top-k
         candidates) when ``last`` (else (None, None))."""
+        if self.fault_hook is not None:
+            self.fault_hook("prefill")
         n = int(tokens.shape[0])
         dev = self.device
         tok = torch.from_numpy(np.ascontiguousarray(tokens)).to(dev)
@@ -276,6 +281,8 @@ class QwenEngine:
         if len(items) == 1:
             t, st, bt, last, greedy = items[0]
             return [self.prefill_chunk(t, st, bt, last, greedy)]
+        if self.fault_hook is not None:
+            self.fault_hook("prefill")
         dev = self.device
         lens = [int(it[0].shape[0]) for it in items]
         offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
@@ -325,6 +332,8 @@ class QwenEngine:
                window: int = 1, greedy: bool = True):
         """One batched decode call: ``window`` on-device greedy steps (window > 1 requires greedy).
         Returns (tokens [B][window], per-row top-k candidate lists or None)."""
+        if self.fault_hook is not None:
+            self.fault_hook("decode")
         dev = self.device
         B = int(tokens.shape[0])
         if self.cuda_graphs and (greedy or window > 1):
