@@ -2,7 +2,10 @@
 432-530 Engine state, 1194-1304 batched decode steps, 1350-1394 greedy head, 1557-1623 chunked
 prefill with prefix-cache reuse).
 
-* KV cache: per layer K and V pools ``[num_blocks, n_kv_heads, block_size, head_dim]`` bf16.
+* KV cache: per layer K and V pools ``[num_blocks, n_kv_heads, block_size, head_dim]`` bf16, or
+  with ``kv_dtype='int8'`` int8 rows plus one fp32 scale per stored row (``min(absmax, ceiling)/127``
+  with the per-head ceilings of ``brain qwen3 calib``); the first chunk of a prompt attends over its
+  own unquantised K/V, everything later reads the quantised pool.
 * ``prefill_chunk``: one chunk of one prompt; K/V rows are appended to the sequence's pages, and
   attention runs the tcgen05 flash kernel over (pages gathered to a contiguous buffer when the chunk
   has a past, else the chunk itself).
@@ -68,7 +71,8 @@ class _Lin:
 class QwenEngine:
     def __init__(self, model, block_size: int = 16, num_blocks: int = 1024, max_seq_len: int = 4096,
                  max_prefill: int = 512, weights: str = "bf16", topk: int = 64, tp=None,
-                 decode_splits: int = 0, cuda_graphs: bool = True):
+                 decode_splits: int = 0, cuda_graphs: bool = True, kv_dtype: str = "bf16",
+                 kv_clip=None):
         cfg: QwenConfig = model.cfg
         self.cfg = cfg
         self.tp = tp
@@ -125,8 +129,21 @@ class QwenEngine:
         # write their K/V there
         self.dummy_block = num_blocks
         shape = (num_blocks + 1, self.hk, block_size, self.hd)
-        self.kc = [torch.zeros(shape, device=dev, dtype=self.dtype) for _ in model.blocks]
-        self.vc = [torch.zeros(shape, device=dev, dtype=self.dtype) for _ in model.blocks]
+        assert kv_dtype in ("bf16", "int8"), kv_dtype
+        self.kv_int8 = kv_dtype == "int8"
+        pool_dtype = torch.int8 if self.kv_int8 else self.dtype
+        self.kc = [torch.zeros(shape, device=dev, dtype=pool_dtype) for _ in model.blocks]
+        self.vc = [torch.zeros(shape, device=dev, dtype=pool_dtype) for _ in model.blocks]
+        if self.kv_int8:
+            # one fp32 scale per stored row; ceilings on the row absmax per (layer, K|V, kv head)
+            self.ks = [torch.zeros(shape[:3], device=dev, dtype=torch.float32) for _ in model.blocks]
+            self.vs = [torch.zeros(shape[:3], device=dev, dtype=torch.float32) for _ in model.blocks]
+            self.kv_clip = None
+            if kv_clip is not None:
+                kc_, vc_ = torch.as_tensor(kv_clip["k_clip"]), torch.as_tensor(kv_clip["v_clip"])
+                lo, hi = self.tp_rank * self.hk, (self.tp_rank + 1) * self.hk
+                self.kv_clip = [torch.stack([kc_[li, lo:hi], vc_[li, lo:hi]]).float().contiguous().to(dev)
+                                for li in range(len(model.blocks))]
         self.decode_splits = decode_splits
         self.steps = 0
         self.cuda_graphs = bool(cuda_graphs) and self.cuda
@@ -138,7 +155,10 @@ class QwenEngine:
 
     # ------------------------------------------------------------------ accounting
     def kv_pool_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.kc) * 2
+        n = sum(t.numel() * t.element_size() for t in self.kc) * 2
+        if self.kv_int8:
+            n += sum(t.numel() * 4 for t in self.ks) * 2
+        return n
 
     def kv_pool_capacity_tokens(self) -> int:
         return self.num_blocks * self.block_size
@@ -162,6 +182,8 @@ class QwenEngine:
         return (blk * bs + positions % bs).to(torch.int32)
 
     def _append_kv(self, li: int, k, v, slots):
+        if self.kv_int8:
+            return self._append_kv_i8(li, k, v, slots)
         if self.cuda:
             call("kv_append", k, k.stride(0), v, v.stride(0), slots, self.kc[li], self.vc[li],
                  k.shape[0], self.hk, self.hd, self.block_size, stream_ptr())
@@ -171,7 +193,40 @@ class QwenEngine:
             self.kc[li][blk, :, off] = k.reshape(-1, self.hk, self.hd)
             self.vc[li][blk, :, off] = v.reshape(-1, self.hk, self.hd)
 
+    def _append_kv_i8(self, li: int, k, v, slots):
+        """Row scale = min(absmax(row), ceiling) / 127 (crates/model/src/kvcalib.rs:42-160 gives the
+        ceilings; crates/qwen3/src/serve.rs:1262-1288 the append)."""
+        clip = self.kv_clip[li] if self.kv_clip is not None else None
+        if self.cuda:
+            call("kv_append_i8", k, k.stride(0), v, v.stride(0), slots, self.kc[li], self.vc[li],
+                 self.ks[li], self.vs[li], clip, k.shape[0], self.hk, self.hd, self.block_size, stream_ptr())
+            return
+        s = slots.long()
+        blk, off = s // self.block_size, s % self.block_size
+        for which, (x, pool, sc) in enumerate(((k, self.kc[li], self.ks[li]), (v, self.vc[li], self.vs[li]))):
+            x = x.reshape(-1, self.hk, self.hd).float()
+            amax = x.abs().amax(-1)
+            if clip is not None:
+                amax = torch.minimum(amax, clip[which][None, :])
+            scale = amax / 127.0
+            inv = torch.where(scale > 0, 1.0 / scale, torch.zeros_like(scale))
+            pool[blk, :, off] = torch.clamp(torch.round(x * inv[..., None]), -127, 127).to(torch.int8)
+            sc[blk, :, off] = scale
+
     def _gather_kv(self, li: int, block_table: torch.Tensor, S: int):
+        if self.kv_int8:
+            if self.cuda:
+                ok = torch.empty(S, self.hk * self.hd, device=self.device, dtype=self.dtype)
+                ov = torch.empty_like(ok)
+                call("kv_gather_i8", self.kc[li], self.vc[li], self.ks[li], self.vs[li], block_table, ok, ov,
+                     S, self.hk, self.hd, self.block_size, stream_ptr())
+                return ok, ov
+            t = torch.arange(S, device=self.device)
+            blk = block_table[(t // self.block_size).long()].long()
+            off = t % self.block_size
+            kk = self.kc[li][blk, :, off].float() * self.ks[li][blk, :, off][..., None]
+            vv = self.vc[li][blk, :, off].float() * self.vs[li][blk, :, off][..., None]
+            return kk.reshape(S, -1).to(self.dtype), vv.reshape(S, -1).to(self.dtype)
         if self.cuda:
             ok = torch.empty(S, self.hk * self.hd, device=self.device, dtype=self.dtype)
             ov = torch.empty_like(ok)
@@ -195,9 +250,14 @@ class QwenEngine:
             out = torch.empty(B, hq * hd, device=self.device, dtype=self.dtype)
             part_o = torch.empty(B * hq * splits * hd, device=self.device, dtype=torch.float32)
             part_ml = torch.empty(B * hq * splits * 2, device=self.device, dtype=torch.float32)
-            call("paged_decode", q, q.stride(0), self.kc[li], self.vc[li], block_tables,
-                 block_tables.shape[1], seqlens, out, out.stride(0), part_o, part_ml, B, hq, hk, hd,
-                 self.block_size, splits, float(scale), stream_ptr())
+            if self.kv_int8:
+                call("paged_decode_i8", q, q.stride(0), self.kc[li], self.vc[li], self.ks[li], self.vs[li],
+                     block_tables, block_tables.shape[1], seqlens, out, out.stride(0), part_o, part_ml,
+                     B, hq, hk, hd, self.block_size, splits, float(scale), stream_ptr())
+            else:
+                call("paged_decode", q, q.stride(0), self.kc[li], self.vc[li], block_tables,
+                     block_tables.shape[1], seqlens, out, out.stride(0), part_o, part_ml, B, hq, hk, hd,
+                     self.block_size, splits, float(scale), stream_ptr())
             return out
         outs = []
         for b in range(B):
@@ -234,12 +294,9 @@ class QwenEngine:
         vals, idx = torch.topk(logits.float(), k, dim=-1)
         return idx[:, 0].to(torch.int32), (idx, vals)
 
-    # ------------------------------------------------------------------ PagedDecoder interface
-    @torch.no_grad()
-    def prefill_chunk(self, tokens: np.ndarray, start: int, block_table: np.ndarray, last: bool,
-                      greedy: bool = True):
-        """Process prompt positions [start, start+n) of one sequence.  Returns (first token, top-k
-        candidates) when ``last`` (else (None, None))."""
+    def _prefill_forward(self, tokens: np.ndarray, start: int, block_table: np.ndarray):
+        """Positions [start, start+n) of one sequence through every layer (K/V appended to its pages);
+        returns the residual stream and the last layer's MLP output, both [n, d]."""
         if self.fault_hook is not None:
             self.fault_hook("prefill")
         n = int(tokens.shape[0])
@@ -263,6 +320,24 @@ class QwenEngine:
         for li in range(len(self.layers)):
             x, delta = self._layer(li, x, delta, pos, attn)
         self.steps += 1
+        return x, delta
+
+    @torch.no_grad()
+    def verify_chunk(self, tokens: np.ndarray, start: int, block_table: np.ndarray) -> np.ndarray:
+        """Greedy next-token prediction after EVERY row of a chunk (the verification forward of
+        speculative decoding, crates/qwen3/src/serve.rs:1899-1975): row i sees positions
+        [0, start+i] and the chunk's K/V are appended to the pages."""
+        x, delta = self._prefill_forward(np.asarray(tokens, dtype=np.int32), start, block_table)
+        t, _ = self._head(x, delta, True)
+        return t.cpu().numpy().astype(np.int64)
+
+    # ------------------------------------------------------------------ PagedDecoder interface
+    @torch.no_grad()
+    def prefill_chunk(self, tokens: np.ndarray, start: int, block_table: np.ndarray, last: bool,
+                      greedy: bool = True):
+        """Process prompt positions [start, start+n) of one sequence.  Returns (first token, top-k
+        candidates) when ``last`` (else (None, None))."""
+        x, delta = self._prefill_forward(tokens, start, block_table)
         if not last:
             return None, None
         t, tk = self._head(x[-1:], delta[-1:], greedy)

@@ -7,11 +7,16 @@
 //                (CTA, 32-key group): lane-per-key dot products against the GQA group's query
 //                vectors, online softmax, lane-per-column P.V; partial (m, l, o) merged by
 //                paged_decode_merge.  Memory-bound by design: K and V are read exactly once.
+// int8 cache (kv_append_i8 / kv_gather_i8 / paged_decode with I8): the pools hold int8 rows of the
+// same layout plus one fp32 scale per (block, head, slot); a row's scale is
+// min(absmax(row), clip[head]) / 127 (crates/kernels/wgsl/paged_kv_append_i8_clipped_batched.wgsl).
+// Decode multiplies the integer dot product by the key's scale and the probability by the value's.
 // Reference contracts: crates/kernels/wgsl/{paged_kv_append_batched,paged_decode_scores_batched,
 // decode_softmax_batched,paged_decode_apply_batched}.wgsl, crates/qwen3/src/serve.rs:1262-1288.
 #include "../common/host.hpp"
 #include "../common/ptx.cuh"
 #include "../common/vec.cuh"
+#include <type_traits>
 
 namespace bb {
 
@@ -58,6 +63,81 @@ __global__ void kv_gather_kernel(const __nv_bfloat16* __restrict__ kc,
   }
 }
 
+// One warp per (token, kv head, K|V): absmax over the row, scale = min(absmax, clip) / 127, int8 row
+// and its scale written to the slot.  clip: fp32 [2][hk] (K then V) or null for no ceiling.
+__global__ void kv_append_i8_kernel(const __nv_bfloat16* __restrict__ k, int ldk,
+                                    const __nv_bfloat16* __restrict__ v, int ldv,
+                                    const int* __restrict__ slots, int8_t* __restrict__ kc,
+                                    int8_t* __restrict__ vc, float* __restrict__ ks,
+                                    float* __restrict__ vs, const float* __restrict__ clip, int n,
+                                    int hk, int hd, int bs) {
+  const int lane = threadIdx.x & 31;
+  const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long nwarps = ((long)gridDim.x * blockDim.x) >> 5;
+  for (long w = warp; w < (long)n * hk * 2; w += nwarps) {
+    const int which = (int)(w & 1);
+    const int h = (int)((w >> 1) % hk);
+    const int t = (int)((w >> 1) / hk);
+    const int slot = slots[t];
+    if (slot < 0) continue;
+    const __nv_bfloat16* src = which ? v + (size_t)t * ldv + h * hd : k + (size_t)t * ldk + h * hd;
+    float x[4];  // hd <= 128: up to 4 elements per lane
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = lane + 32 * j;
+      x[j] = c < hd ? __bfloat162float(src[c]) : 0.f;
+      amax = fmaxf(amax, fabsf(x[j]));
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (clip) amax = fminf(amax, clip[which * hk + h]);
+    const float sc = amax / 127.f;
+    const float inv = sc > 0.f ? 1.f / sc : 0.f;
+    const int blk = slot / bs, off = slot - blk * bs;
+    const size_t row = ((size_t)blk * hk + h) * bs + off;
+    int8_t* dst = (which ? vc : kc) + row * hd;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = lane + 32 * j;
+      if (c < hd) dst[c] = (int8_t)max(-127, min(127, __float2int_rn(x[j] * inv)));
+    }
+    if (lane == 0) (which ? vs : ks)[row] = sc;
+  }
+}
+
+// Dequantising gather: out_k/out_v [S, hk*hd] bf16 from the int8 pools of one sequence.
+__global__ void kv_gather_i8_kernel(const int8_t* __restrict__ kc, const int8_t* __restrict__ vc,
+                                    const float* __restrict__ ks, const float* __restrict__ vs,
+                                    const int* __restrict__ block_table,
+                                    __nv_bfloat16* __restrict__ ok, __nv_bfloat16* __restrict__ ov,
+                                    int S, int hk, int hd, int bs) {
+  const int hv = hd >> 3;  // 8 elements (8 bytes in, 16 bytes out) per thread
+  const long total = (long)S * hk * hv;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % hv);
+    const int h = (int)((i / hv) % hk);
+    const int t = (int)(i / ((long)hv * hk));
+    const int blk = block_table[t / bs], off = t % bs;
+    const size_t row = ((size_t)blk * hk + h) * bs + off;
+    const size_t dst = (size_t)t * hk * hd + h * hd + c * 8;
+    const float sk = ks[row], sv = vs[row];
+    const char4* pk = reinterpret_cast<const char4*>(kc + row * hd + c * 8);
+    const char4* pv = reinterpret_cast<const char4*>(vc + row * hd + c * 8);
+    const char4 k0 = pk[0], k1 = pk[1], v0 = pv[0], v1 = pv[1];
+    const float fk[8] = {k0.x * sk, k0.y * sk, k0.z * sk, k0.w * sk, k1.x * sk, k1.y * sk, k1.z * sk, k1.w * sk};
+    const float fv[8] = {v0.x * sv, v0.y * sv, v0.z * sv, v0.w * sv, v1.x * sv, v1.y * sv, v1.z * sv, v1.w * sv};
+    *reinterpret_cast<bf16x8*>(ok + dst) = pack8(fk);
+    *reinterpret_cast<bf16x8*>(ov + dst) = pack8(fv);
+  }
+}
+
+template <int N>
+struct alignas(N) i8vec {
+  uint32_t w[N / 4];
+};
+
 // One CTA (4 warps) per (sequence b, kv head, split).  G = query heads per kv head (<= 8).
 // q: [B, hq*hd]; block_tables: int32 [B, max_blocks]; seqlens: int32[B] (keys visible to the query).
 // part_o: fp32 [B, hq, splits, hd], part_ml: fp32 [B, hq, splits, 2] (running max in log2 domain, sum).
@@ -70,16 +150,25 @@ __global__ void kv_gather_kernel(const __nv_bfloat16* __restrict__ kc,
 // exchange.  Every group keeps its own running (max, sum, output) and the 16 partial states are
 // merged once at the end.  An earlier form (one lane per key, query read from shared memory for
 // every multiply) spent ~300 us per layer at batch 256 and was the largest item of a decode step.
-template <int HD, int G>
+//
+// I8: kc/vc point at int8 pools and ks/vs at their per-row scales; a lane's slice of a row is DPL
+// bytes, the dot product runs on the integer values and the key's scale multiplies the score, the
+// value's scale multiplies the probability.
+template <int HD, int G, bool I8>
 __global__ void __launch_bounds__(128)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
-                    const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
+                    const void* __restrict__ kc_, const void* __restrict__ vc_,
+                    const float* __restrict__ ks, const float* __restrict__ vs,
                     const int* __restrict__ block_tables, int max_blocks,
                     const int* __restrict__ seqlens, float* __restrict__ part_o,
                     float* __restrict__ part_ml, int hq, int hk, int bs, int splits,
                     float scale_log2) {
   constexpr int DPL = HD / 8;   // dims per lane: 16 (hd 128) or 8 (hd 64)
-  constexpr int NV = DPL / 8;   // 16-byte vectors per lane per row
+  constexpr int NV = I8 ? 1 : DPL / 8;   // raw vectors per lane per row: one DPL-byte (int8) / 16-byte (bf16)
+  using Raw = typename std::conditional<I8, i8vec<DPL>, bf16x8>::type;
+  using Elem = typename std::conditional<I8, int8_t, __nv_bfloat16>::type;
+  const Elem* __restrict__ kc = static_cast<const Elem*>(kc_);
+  const Elem* __restrict__ vc = static_cast<const Elem*>(vc_);
   const int b = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grp = lane >> 3, sub = lane & 7;
@@ -95,7 +184,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
   for (int g = 0; g < G; ++g) {
     const bf16x8* qp = reinterpret_cast<const bf16x8*>(q + (size_t)b * ldq + (kvh * G + g) * HD + sub * DPL);
 #pragma unroll
-    for (int v = 0; v < NV; ++v) {
+    for (int v = 0; v < DPL / 8; ++v) {
       float f[8];
       unpack8(qp[v], f);
 #pragma unroll
@@ -113,41 +202,59 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
   const int* bt = block_tables + (size_t)b * max_blocks;
   // 16 keys per CTA step: warp w takes keys [k0 + 4w, k0 + 4w + 4), group g one of them.  The rows of
   // the NEXT step are fetched before the current ones are used, so two steps of loads are in flight.
-  bf16x8 kraw[NV], vraw[NV], knext[NV], vnext[NV];
-  auto fetch = [&](int k0, bf16x8 (&kk)[NV], bf16x8 (&vv)[NV]) -> bool {
+  Raw kraw[NV], vraw[NV], knext[NV], vnext[NV];
+  float ksc = 1.f, vsc = 1.f, ksc_next = 1.f, vsc_next = 1.f;
+  auto fetch = [&](int k0, Raw (&kk)[NV], Raw (&vv)[NV], float& sk, float& sv) -> bool {
     const int key = k0 + warp * 4 + grp;
     if (key >= k_end) return false;
     const int blk = bt[key / bs], off = key % bs;
-    const size_t row = (((size_t)blk * hk + kvh) * bs + off) * HD + sub * DPL;
-    const bf16x8* kr = reinterpret_cast<const bf16x8*>(kc + row);
-    const bf16x8* vr = reinterpret_cast<const bf16x8*>(vc + row);
+    const size_t r = ((size_t)blk * hk + kvh) * bs + off;
+    const size_t row = r * HD + sub * DPL;
+    const Raw* kr = reinterpret_cast<const Raw*>(kc + row);
+    const Raw* vr = reinterpret_cast<const Raw*>(vc + row);
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       kk[v] = kr[v];
       vv[v] = vr[v];
     }
+    if constexpr (I8) {
+      sk = ks[r];
+      sv = vs[r];
+    }
     return true;
   };
-  bool valid = fetch(k_begin, kraw, vraw);
+  bool valid = fetch(k_begin, kraw, vraw, ksc, vsc);
   for (int k0 = k_begin; k0 < k_end; k0 += 16) {
-    const bool valid_next = (k0 + 16 < k_end) ? fetch(k0 + 16, knext, vnext) : false;
+    const bool valid_next = (k0 + 16 < k_end) ? fetch(k0 + 16, knext, vnext, ksc_next, vsc_next) : false;
     if (valid) {
       float kf[DPL], vf[DPL];
+      if constexpr (I8) {
 #pragma unroll
-      for (int v = 0; v < NV; ++v) {
-        float t[8];
-        unpack8(kraw[v], t);
+        for (int v = 0; v < DPL / 4; ++v) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) kf[v * 8 + j] = t[j];
-        unpack8(vraw[v], t);
+          for (int j = 0; j < 4; ++j) {
+            kf[v * 4 + j] = (float)(int8_t)(kraw[0].w[v] >> (8 * j));
+            vf[v * 4 + j] = (float)(int8_t)(vraw[0].w[v] >> (8 * j));
+          }
+        }
+      } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) vf[v * 8 + j] = t[j];
+        for (int v = 0; v < NV; ++v) {
+          float t[8];
+          unpack8(kraw[v], t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) kf[v * 8 + j] = t[j];
+          unpack8(vraw[v], t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vf[v * 8 + j] = t[j];
+        }
       }
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         float sc = 0.f;
 #pragma unroll
         for (int j = 0; j < DPL; ++j) sc += kf[j] * qr[g][j];
+        if constexpr (I8) sc *= ksc;
         // the 8 lanes of a group are all valid or all invalid, so they shuffle among themselves
         const unsigned int gm = 0xffu << (grp * 8);
         sc += __shfl_xor_sync(gm, sc, 1);
@@ -162,11 +269,14 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
         }
         const float pg = exp2f(sc - m[g]);
         l[g] += pg;
+        const float pv = I8 ? pg * vsc : pg;
 #pragma unroll
-        for (int j = 0; j < DPL; ++j) o[g][j] += pg * vf[j];
+        for (int j = 0; j < DPL; ++j) o[g][j] += pv * vf[j];
       }
     }
     valid = valid_next;
+    ksc = ksc_next;
+    vsc = vsc_next;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       kraw[v] = knext[v];
@@ -281,11 +391,11 @@ BB_API int bb_kv_gather(const void* kc, const void* vc, const int* block_table, 
   return (int)cudaGetLastError();
 }
 
-// part_o: fp32 [B*hq*splits*hd], part_ml: fp32 [B*hq*splits*2] scratch provided by the caller.
-BB_API int bb_paged_decode(const void* q, int ldq, const void* kc, const void* vc,
-                           const int* block_tables, int max_blocks, const int* seqlens, void* out,
-                           int ldo, float* part_o, float* part_ml, int B, int hq, int hk, int hd,
-                           int bs, int splits, float scale, void* stream) {
+static int launch_paged_decode(bool i8, const void* q, int ldq, const void* kc, const void* vc,
+                               const float* ks, const float* vs, const int* block_tables,
+                               int max_blocks, const int* seqlens, void* out, int ldo, float* part_o,
+                               float* part_ml, int B, int hq, int hk, int hd, int bs, int splits,
+                               float scale, void* stream) {
   if (B <= 0) return BB_OK;
   if (hq % hk || splits < 1) return BB_EARG;
   const int G = hq / hk;
@@ -293,9 +403,16 @@ BB_API int bb_paged_decode(const void* q, int ldq, const void* kc, const void* v
   const float sl2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
 #define BB_LAUNCH_PD(HD_, G_)                                                                     \
-  paged_decode_kernel<HD_, G_><<<grid, 128, 0, s>>>(                                              \
-      (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,           \
-      block_tables, max_blocks, seqlens, part_o, part_ml, hq, hk, bs, splits, sl2)
+  do {                                                                                            \
+    if (i8)                                                                                       \
+      paged_decode_kernel<HD_, G_, true><<<grid, 128, 0, s>>>(                                    \
+          (const __nv_bfloat16*)q, ldq, kc, vc, ks, vs, block_tables, max_blocks, seqlens,        \
+          part_o, part_ml, hq, hk, bs, splits, sl2);                                              \
+    else                                                                                          \
+      paged_decode_kernel<HD_, G_, false><<<grid, 128, 0, s>>>(                                   \
+          (const __nv_bfloat16*)q, ldq, kc, vc, nullptr, nullptr, block_tables, max_blocks,       \
+          seqlens, part_o, part_ml, hq, hk, bs, splits, sl2);                                     \
+  } while (0)
   if (hd == 128) {
     switch (G) {
       case 1: BB_LAUNCH_PD(128, 1); break;
@@ -320,5 +437,56 @@ BB_API int bb_paged_decode(const void* q, int ldq, const void* kc, const void* v
   if (e != cudaSuccess) return (int)e;
   paged_decode_merge_kernel<<<dim3(B, hq), 128, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, ldo,
                                                         hq, hd, splits);
+  return (int)cudaGetLastError();
+}
+
+// part_o: fp32 [B*hq*splits*hd], part_ml: fp32 [B*hq*splits*2] scratch provided by the caller.
+BB_API int bb_paged_decode(const void* q, int ldq, const void* kc, const void* vc,
+                           const int* block_tables, int max_blocks, const int* seqlens, void* out,
+                           int ldo, float* part_o, float* part_ml, int B, int hq, int hk, int hd,
+                           int bs, int splits, float scale, void* stream) {
+  return launch_paged_decode(false, q, ldq, kc, vc, nullptr, nullptr, block_tables, max_blocks,
+                             seqlens, out, ldo, part_o, part_ml, B, hq, hk, hd, bs, splits, scale,
+                             stream);
+}
+
+// int8 pools kc/vc with per-row scales ks/vs: fp32 [num_blocks, hk, bs].
+BB_API int bb_paged_decode_i8(const void* q, int ldq, const void* kc, const void* vc,
+                              const float* ks, const float* vs, const int* block_tables,
+                              int max_blocks, const int* seqlens, void* out, int ldo,
+                              float* part_o, float* part_ml, int B, int hq, int hk, int hd, int bs,
+                              int splits, float scale, void* stream) {
+  return launch_paged_decode(true, q, ldq, kc, vc, ks, vs, block_tables, max_blocks, seqlens, out,
+                             ldo, part_o, part_ml, B, hq, hk, hd, bs, splits, scale, stream);
+}
+
+// clip: fp32 [2, hk] ceilings on the row absmax (K heads then V heads), or null.
+BB_API int bb_kv_append_i8(const void* k, int ldk, const void* v, int ldv, const int* slots,
+                           void* kc, void* vc, float* ks, float* vs, const float* clip, int n,
+                           int hk, int hd, int bs, void* stream) {
+  if (n <= 0) return BB_OK;
+  if (hd > 128 || hd % 8) return BB_EARG;
+  const long warps = (long)n * hk * 2;
+  long blocks = (warps + 7) / 8;
+  const long cap = (long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  kv_append_i8_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv, slots, (int8_t*)kc, (int8_t*)vc,
+      ks, vs, clip, n, hk, hd, bs);
+  return (int)cudaGetLastError();
+}
+
+BB_API int bb_kv_gather_i8(const void* kc, const void* vc, const float* ks, const float* vs,
+                           const int* block_table, void* ok, void* ov, int S, int hk, int hd,
+                           int bs, void* stream) {
+  if (S <= 0) return BB_OK;
+  if (hd % 8) return BB_EARG;
+  const long total = (long)S * hk * (hd / 8);
+  long blocks = (total + 255) / 256;
+  const long cap = (long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  kv_gather_i8_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const int8_t*)kc, (const int8_t*)vc, ks, vs, block_table, (__nv_bfloat16*)ok,
+      (__nv_bfloat16*)ov, S, hk, hd, bs);
   return (int)cudaGetLastError();
 }

@@ -6,7 +6,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _engine(weights="bf16"):
+def _engine(weights="bf16", kv="bf16"):
     from brain_b200.models.config import QwenConfig
     from brain_b200.models.qwen3 import Qwen3
     from brain_b200.serve.engine import QwenEngine
@@ -17,7 +17,7 @@ def _engine(weights="bf16"):
         for p in m.parameters():
             p.mul_(3.0)
     m = m.to("cuda", torch.bfloat16)
-    return QwenEngine(m, block_size=16, num_blocks=256, max_seq_len=512, max_prefill=128, weights=weights)
+    return QwenEngine(m, block_size=16, num_blocks=256, max_seq_len=512, max_prefill=128, weights=weights, kv_dtype=kv)
 
 
 def test_paged_kv_kernels_roundtrip():
@@ -98,3 +98,78 @@ def test_engine_int8_tracks_bf16():
     rel = ((a - b).norm() / a.norm()).item()
     assert rel < 0.2, rel
     assert eng8.weight_bytes() < 0.7 * eng.weight_bytes()
+
+
+@pytest.mark.parametrize("hd,hq,hk", [(128, 8, 2), (64, 6, 2)])
+def test_int8_kv_kernels_match_reference(hd, hq, hk):
+    """kv_append_i8 == torch quantisation (row scale min(absmax, ceiling)/127); kv_gather_i8 returns
+    the dequantised rows; paged_decode_i8 == fp32 attention over the dequantised cache."""
+    from brain_b200.ops import reference as ref
+    from brain_b200.ops._cuda import call, stream_ptr, check_error
+    torch.manual_seed(2)
+    bs, nb, n = 16, 40, 300
+    k = torch.randn(n, hk * hd, device="cuda").bfloat16()
+    v = (torch.randn(n, hk * hd, device="cuda") * 3).bfloat16()
+    clip = torch.tensor([[2.5] * hk, [1e30] * hk], device="cuda")
+    table = torch.randperm(nb)[:20].to("cuda", torch.int32)
+    t = torch.arange(n, device="cuda")
+    slots = (table[(t // bs).long()] * bs + (t % bs).int()).to(torch.int32)
+    kc = torch.zeros(nb, hk, bs, hd, device="cuda", dtype=torch.int8)
+    vc = torch.zeros_like(kc)
+    ks = torch.zeros(nb, hk, bs, device="cuda")
+    vs = torch.zeros_like(ks)
+    call("kv_append_i8", k, k.stride(0), v, v.stride(0), slots, kc, vc, ks, vs, clip, n, hk, hd, bs, stream_ptr())
+    check_error()
+    blk, off = (slots // bs).long(), (slots % bs).long()
+    for x, pool, sc, ceil in ((k, kc, ks, 2.5), (v, vc, vs, 1e30)):
+        xf = x.float().reshape(n, hk, hd)
+        scale = xf.abs().amax(-1).clamp(max=ceil) / 127
+        want = torch.clamp(torch.round(xf / scale[..., None]), -127, 127)
+        got = pool[blk, :, off].float()
+        assert torch.allclose(sc[blk, :, off], scale, rtol=1e-6, atol=0)
+        assert (got - want).abs().max().item() <= 1.0     # round-half ties may differ by one step
+        assert ((got - want).abs() > 0).float().mean().item() < 1e-3
+    ok = torch.empty(n, hk * hd, device="cuda", dtype=torch.bfloat16)
+    ov = torch.empty_like(ok)
+    call("kv_gather_i8", kc, vc, ks, vs, table, ok, ov, n, hk, hd, bs, stream_ptr())
+    check_error()
+    dk = (kc[blk, :, off].float() * ks[blk, :, off][..., None]).reshape(n, -1)
+    dv = (vc[blk, :, off].float() * vs[blk, :, off][..., None]).reshape(n, -1)
+    assert torch.allclose(ok.float(), dk, rtol=1e-2, atol=1e-3) and torch.allclose(ov.float(), dv, rtol=1e-2, atol=1e-3)
+
+    B = 3
+    lens = [7, 129, 300]
+    q = torch.randn(B, hq * hd, device="cuda").bfloat16()
+    bts = table[None, :].expand(B, -1).contiguous()
+    seqlens = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    for splits in (1, 3):
+        out = torch.empty(B, hq * hd, device="cuda", dtype=torch.bfloat16)
+        po = torch.empty(B * hq * splits * hd, device="cuda")
+        pm = torch.empty(B * hq * splits * 2, device="cuda")
+        call("paged_decode_i8", q, q.stride(0), kc, vc, ks, vs, bts, bts.shape[1], seqlens, out, out.stride(0),
+             po, pm, B, hq, hk, hd, bs, splits, float(hd ** -0.5), stream_ptr())
+        check_error()
+        for b in range(B):
+            S = lens[b]
+            want = ref.attention(q[b].float().reshape(1, 1, hq, hd), dk[:S].reshape(1, S, hk, hd),
+                                 dv[:S].reshape(1, S, hk, hd), causal=False)
+            err = ((out[b].float() - want.reshape(-1)).norm() / want.norm()).item()
+            assert err < 1e-2, (splits, b, err)
+
+
+def test_engine_int8_kv_tracks_bf16_kv():
+    from brain_b200.ops import _cuda
+    base, e8 = _engine(), _engine(kv="int8")
+    toks = np.arange(5, 205, dtype=np.int32)
+    bt = np.arange(base.max_blocks, dtype=np.int32)
+    outs = []
+    for e in (base, e8):
+        e.prefill_chunk(toks[:128], 0, bt, False)
+        e.prefill_chunk(toks[128:], 128, bt, True)
+        _, c = e.decode(np.array([7], dtype=np.int32), np.array([200], dtype=np.int32), bt[None, :], greedy=False)
+        outs.append(dict(c[0]))
+    _cuda.check_error()
+    common = set(outs[0]) & set(outs[1])
+    assert len(common) >= 32
+    spread = max(outs[0].values()) - min(outs[0].values())
+    assert max(abs(outs[0][t] - outs[1][t]) for t in common) < 0.1 * spread
