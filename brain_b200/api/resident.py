@@ -172,7 +172,8 @@ class LlmResident(ResidentModel):
     """A Qwen-family checkpoint behind a paged-KV engine and one continuous-batching scheduler."""
 
     def __init__(self, model, tokenizer, model_id: str = "brain/qwen3", ctx: Optional[int] = None,
-                 max_batch: Optional[int] = None, weights: str = "bf16", block_size: int = 16, tp=None):
+                 max_batch: Optional[int] = None, weights: str = "bf16", block_size: int = 16, tp=None,
+                 kv_dtype: str = "bf16", kv_clip=None):
         from ..serve.engine import QwenEngine
         from ..serve.scheduler import Scheduler
         self.id = model_id
@@ -183,7 +184,8 @@ class LlmResident(ResidentModel):
         blocks_per_ctx = -(-self.ctx // block_size)
         pool = int(os.environ.get("BRAIN_SCHED_NUM_BLOCKS", "0")) or 2 * blocks_per_ctx + self.max_batch
         self.engine = QwenEngine(model, block_size=block_size, num_blocks=pool, max_seq_len=self.ctx,
-                                 max_prefill=min(self.ctx, 512), weights=weights, tp=tp)
+                                 max_prefill=min(self.ctx, 512), weights=weights, tp=tp,
+                                 kv_dtype=kv_dtype, kv_clip=kv_clip)
         ids = tokenizer.encode("<|im_end|>") if hasattr(tokenizer, "special") else []
         self.eos = ids[0] if len(ids) == 1 else getattr(tokenizer, "eos_id", None)
         self.sched = Scheduler(self.engine, max_batch=self.max_batch, eos=self.eos)
@@ -384,8 +386,13 @@ def load_llm_from_env(device: str = "auto") -> Optional[LlmResident]:
     model, _, card = st.load_model(w, device=dev, dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32)
     model.eval()
     mode = "int8" if os.environ.get("BRAIN_QWEN_INT8") == "1" and dev.type == "cuda" else "bf16"
+    kv8 = os.environ.get("BRAIN_QWEN_KV_INT8") == "1"
+    clip = None
+    if kv8 and os.environ.get("BRAIN_QWEN_KV_CALIB") == "1":
+        from ..serve.calib import load_kv_clip
+        clip = load_kv_clip(w)
     return LlmResident(model, load_tokenizer(t), card.id if card is not None and card.id else "brain/qwen3",
-                       weights=mode)
+                       weights=mode, kv_dtype="int8" if kv8 else "bf16", kv_clip=clip)
 
 
 def registry_from_env(load: bool = True, device: str = "auto") -> Dict[str, ResidentModel]:

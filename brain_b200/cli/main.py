@@ -27,9 +27,10 @@ model commands
                  --seed 1234 --mask C --align --save-secs 600 --preset 0.6b --dp N]
            finetune <data_dir> --weights BASE --out F [...]        (full-parameter, moments offloaded)
            finetune --lora R --weights BASE --adapter OWNER/NAME[:TAG] --dataset DIR [--alpha A ...]
-           infer --weights F --tokenizer T --prompt "..." [--max-new N --temp X --top-k K --seed S --chat]
+           infer --weights F --tokenizer T --prompt "..." [--max-new N --temp X --top-k K --seed S --chat
+                 --spec K]
            serve --weights F --tokenizer T --prompt "..." [--prompt "..."]... [--max-new 64
-                 --block-size 16 --weights-int8 --tp N]
+                 --block-size 16 --weights-int8 --int8|--kv-fp32 --kv-calib --tp N]
            export --weights F --out DIR     eval --weights F --jsonl FILE [--adapter ...]
            toolcall gen|eval ...            calib --weights F --jsonl FILE [--report --clip-out F]
            precompile

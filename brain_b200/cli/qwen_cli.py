@@ -44,16 +44,19 @@ def _load(weights: str, device: str, dtype=None):
 
 
 def _tok(path: str):
-    from ..data.tokenizer import BpeTokenizer
+    from ..data.tokenizer import load_tokenizer
     try:
-        return BpeTokenizer.from_file(path)
+        return load_tokenizer(path)   # tokenizer.json, or a dataset directory (character level)
     except Exception as e:  # noqa: BLE001
         print(f"tokenizer load failed: {e}", file=sys.stderr)
         return None
 
 
 def _eos(tok) -> Optional[int]:
-    ids = tok.encode("<|im_end|>")
+    try:
+        ids = tok.encode("<|im_end|>")
+    except ValueError:   # a character-level vocabulary without the marker's characters
+        ids = []
     return ids[0] if len(ids) == 1 else tok.eos_id
 
 
@@ -116,15 +119,16 @@ def _serve(args, device):
     prompts = a.take_all("--prompt")
     max_new = a.int_or("--max-new", 64)
     block_size = a.int_or("--block-size", 16)
-    a.take_flag("--int8")
-    a.take_flag("--kv-fp32")
+    kv_int8 = a.take_flag("--int8")
+    if a.take_flag("--kv-fp32"):
+        kv_int8 = False
     weights_int8 = a.take_flag("--weights-int8")
-    a.take_flag("--kv-calib")
+    kv_calib = a.take_flag("--kv-calib")
     tp_n = a.int_or("--tp", 1)
     a.finish()
     if not weights or not tokenizer or not prompts:
         print('usage: brain qwen3 serve --weights F --tokenizer T --prompt "..." [--prompt "..."]... '
-              "[--max-new N --block-size B --weights-int8 --tp N]", file=sys.stderr)
+              "[--max-new N --block-size B --weights-int8 --int8 | --kv-fp32  --kv-calib  --tp N]", file=sys.stderr)
         return 2
     tok = _tok(tokenizer)
     if tok is None:
@@ -133,14 +137,23 @@ def _serve(args, device):
         return _relaunch(tp_n, ["qwen3", "serve"] + args)
     tp = _tp_from_env(device)
     model, cfg, _, dev = _load(weights, device)
-    toks = [tok.encode(tok.apply_chat_template([("user", p)], True)) for p in prompts]
+    chatml = hasattr(tok, "apply_chat_template")
+    toks = [tok.encode(tok.apply_chat_template([("user", p)], True) if chatml else p) for p in prompts]
     mode = "int8" if weights_int8 and dev.type == "cuda" else "bf16"
-    r = serve_prompts(model, toks, max_new, block_size, mode, _eos(tok), tp=tp)
+    clip = None
+    if kv_int8 and kv_calib:
+        from ..serve.calib import load_kv_clip
+        clip = load_kv_clip(weights)
+        if clip is None:
+            print("note: --kv-calib given but no kv_calib.json beside the weights; using uncapped row scales",
+                  file=sys.stderr)
+    r = serve_prompts(model, toks, max_new, block_size, mode, _eos(tok), tp=tp,
+                      kv_dtype="int8" if kv_int8 else "bf16", kv_clip=clip)
     if tp is None or tp.rank == 0:
         for i, out in enumerate(r["outputs"]):
             print(f"=== prompt {i}: {prompts[i]!r}")
             print(tok.decode(out) + "\n")
-        kv = "bf16 KV" if dev.type == "cuda" else "fp32 KV"
+        kv = "int8 KV" if kv_int8 else ("bf16 KV" if dev.type == "cuda" else "fp32 KV")
         print(f"served {len(prompts)} prompts, {r['tokens']} tokens in {r['secs']:.2f}s "
               f"({r['tok_s']:.1f} tok/s aggregate) [{kv}]" + (" [int8 weights]" if mode == "int8" else ""),
               file=sys.stderr)
@@ -184,18 +197,19 @@ def _infer(args, device):
     top_k = a.int_or("--top-k", 0)
     seed = a.int_or("--seed", 0)
     chat = a.take_flag("--chat")
+    spec_k = a.int_or("--spec", 0)
     for f in ("--npu-cache", "--seq"):
         a.take_str(f)
     a.take_flag("--allow-fallback")
     a.finish()
     if not weights or not tokenizer:
         print('usage: brain qwen3 infer --weights F --tokenizer tokenizer.json --prompt "..." '
-              "[--max-new N --temp X --top-k K --chat]", file=sys.stderr)
+              "[--max-new N --temp X --top-k K --chat --spec K]", file=sys.stderr)
         return 2
     tok = _tok(tokenizer)
     if tok is None:
         return 1
-    text = tok.apply_chat_template([("user", prompt)], True) if chat else prompt
+    text = tok.apply_chat_template([("user", prompt)], True) if chat and hasattr(tok, "apply_chat_template") else prompt
     ids = tok.encode(text)
     if not ids:
         print("empty prompt", file=sys.stderr)
@@ -204,8 +218,21 @@ def _infer(args, device):
     model, _, _, _ = _load(weights, device)
     load_ms = (time.time() - t0) * 1e3
     t1 = time.time()
-    r = serve_prompts(model, [ids], max_new, 16, "bf16", _eos(tok), SampleParams(temp, top_k, 1.0), seed)
-    gen = r["outputs"][0]
+    if spec_k > 0 and temp == 0.0:
+        # greedy speculative decoding with a prompt-lookup draft: same text, fewer target forwards
+        from ..serve.engine import QwenEngine
+        from ..serve.spec import ngram_draft, spec_decode
+        ctx = -(-(len(ids) + max_new + 8) // 16) * 16
+        eng = QwenEngine(model, block_size=16, num_blocks=ctx // 16 + 1, max_seq_len=ctx,
+                         max_prefill=max(len(ids), 1), cuda_graphs=False)
+        gen, fwd = spec_decode(eng, ids, max_new, spec_k, ngram_draft(3))
+        eos = _eos(tok)
+        if eos is not None and eos in gen:
+            gen = gen[:gen.index(eos)]
+        print(f"qwen-spec k={spec_k} target_forwards={fwd} tokens={len(gen)}", file=sys.stderr)
+    else:
+        r = serve_prompts(model, [ids], max_new, 16, "bf16", _eos(tok), SampleParams(temp, top_k, 1.0), seed)
+        gen = r["outputs"][0]
     print(f"qwen-timing load_ms={load_ms:.1f} gen_ms={(time.time() - t1) * 1e3:.1f} tokens={len(gen)}",
           file=sys.stderr)
     print(prompt + tok.decode(gen))

@@ -58,3 +58,16 @@ def collect_kv_stats(model, seqs: Sequence[Sequence[int]], percentile: float = 0
         out["k_clip"].append([q for _, q in ks])
         out["v_clip"].append([q for _, q in vs])
     return out
+
+
+def load_kv_clip(weights_path: str):
+    """The ``kv_calib.json`` written beside a checkpoint by ``brain qwen3 calib`` ->
+    ``{"k_clip": [[…per kv head] per layer], "v_clip": …}`` for ``QwenEngine(kv_clip=…)``; None when
+    the file is absent."""
+    import json
+    import os
+    path = os.path.join(os.path.dirname(weights_path) or ".", "kv_calib.json")
+    if not os.path.exists(path):
+        return None
+    d = json.loads(open(path).read())
+    return {"k_clip": d["k"], "v_clip": d["v"]}

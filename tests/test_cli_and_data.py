@@ -316,6 +316,15 @@ def test_cli_end_to_end(tmp_path, capsys):
     q = os.path.join(o, "q.safetensors")
     assert main(["qwen3", "train", d, "--out", q, "--steps", "3", "--batch", "2", "--block", "16", "--device", "cpu"]) == 0
     assert f"; saved {q}" in capsys.readouterr().out
+    assert main(["qwen3", "infer", "--weights", q, "--tokenizer", d, "--prompt", "1+1=", "--max-new", "8", "--device", "cpu"]) == 0
+    plain = capsys.readouterr()
+    assert main(["qwen3", "infer", "--weights", q, "--tokenizer", d, "--prompt", "1+1=", "--max-new", "8", "--spec", "3",
+                 "--device", "cpu"]) == 0
+    spec = capsys.readouterr()
+    assert spec.out == plain.out and "qwen-spec k=3 target_forwards=" in spec.err
+    assert main(["qwen3", "serve", "--weights", q, "--tokenizer", d, "--prompt", "1+1=", "--prompt", "2+2=", "--max-new", "4",
+                 "--int8", "--device", "cpu"]) == 0
+    assert "[int8 KV]" in capsys.readouterr().err
     q2 = os.path.join(o, "q_ft.safetensors")
     assert main(["finetune", "qwen3", d, "--weights", q, "--out", q2, "--steps", "2", "--batch", "2", "--block", "16", "--device", "cpu"]) == 0
     assert "resuming from existing checkpoint" in capsys.readouterr().out and os.path.exists(q2)
