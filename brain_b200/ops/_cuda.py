@@ -65,15 +65,48 @@ def _conv(a):
 
 
 def stream_ptr() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
+
+
+_Tensor = torch.Tensor
+#: per-launcher (function, argument count); the argument types are declared on the first call so
+#: that later calls hand plain ints / floats / addresses to ctypes instead of building one ctypes
+#: object per argument (that conversion was two thirds of the host cost of a launch)
+_FN: dict = {}
+
+
+def _argtype(a):
+    if a is None or isinstance(a, _Tensor):
+        return ctypes.c_void_p
+    if isinstance(a, (bool, int)):
+        return ctypes.c_int
+    if isinstance(a, float):
+        return ctypes.c_float
+    if isinstance(a, ctypes.Array):
+        return ctypes.c_void_p
+    return type(a)      # an explicit ctypes scalar: c_long, c_uint, c_double, c_void_p
+
+
+def _bind(name: str, args):
+    fn = getattr(lib(), "bb_" + name)
+    fn.restype = ctypes.c_int
+    fn.argtypes = [_argtype(a) for a in args]
+    _FN[name] = (fn, len(args))
+    return _FN[name]
 
 
 def call(name: str, *args) -> None:
     """Launch ``bb_<name>``; tensors become device pointers, ints c_int, floats c_float.
-    Pass ``ctypes.c_long(x)`` explicitly for 64-bit parameters."""
+    Pass ``ctypes.c_long(x)`` explicitly for 64-bit parameters (and always the same kind of value
+    for a given parameter: the C types are fixed by the first call)."""
     global launch_count
-    fn = getattr(lib(), "bb_" + name)
-    rc = fn(*[_conv(a) for a in args])
+    ent = _FN.get(name)
+    if ent is None:
+        ent = _bind(name, args)
+    fn, n = ent
+    if n != len(args):
+        raise NativeError(f"bb_{name}: {len(args)} arguments, first call had {n}")
+    rc = fn(*[a.data_ptr() if isinstance(a, _Tensor) else a for a in args])
     launch_count += 1
     if rc != 0:
         raise NativeError(f"bb_{name} failed with code {rc}")

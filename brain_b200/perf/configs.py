@@ -134,6 +134,8 @@ def serve_tp(args) -> dict:
     launches0 = _cuda.launch_count
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
+    for k in eng.acct:
+        eng.acct[k] = type(eng.acct[k])(0)
     run = drive(target, wl)
     ev1.record()
     torch.cuda.synchronize()
@@ -152,6 +154,7 @@ def serve_tp(args) -> dict:
             "concurrency": conc, "admit_batch": args.admit_batch, "prefill_budget": args.prefill_budget, "weights": args.weights, "impl": args.impl, "layers": cfg.n_layers,
             "kv_pool_gb": eng.kv_pool_bytes() / 2**30, "weight_gb_per_rank": eng.weight_bytes() / 2**30,
             "cuda_graph_replays": eng.graph_replays, "engine_steps": eng.steps, "build_s": build_s,
+            "engine_time": {k: (round(v, 3) if isinstance(v, float) else v) for k, v in eng.acct.items()},
             "gpu_launches": _cuda.launch_count - launches0, "dtype": "int8 weights+activations, bf16 KV" if args.weights == "int8" else "bf16",
             "data": "synthetic", "timing": "CUDA events around the whole run, max over ranks"}
 
@@ -291,8 +294,8 @@ def main(argv=None):
     ap.add_argument("--concurrency", type=int, default=256)
     ap.add_argument("--out-tokens", type=int, default=256)
     ap.add_argument("--no-graphs", action="store_true")
-    ap.add_argument("--admit-batch", type=int, default=16, help="serve-tp: admit new requests in groups of this many")
-    ap.add_argument("--prefill-budget", type=int, default=8192, help="serve-tp: prompt tokens per scheduler step")
+    ap.add_argument("--admit-batch", type=int, default=1, help="serve-tp: admit new requests in groups of this many")
+    ap.add_argument("--prefill-budget", type=int, default=0, help="serve-tp: prompt tokens per scheduler step")
     ap.add_argument("--stuck-after", type=int, default=600, help="seconds before a stuck rank dumps its stack and exits")
     a = ap.parse_args(argv)
     if a.which == "cpu-dp" and not a.layers:

@@ -21,6 +21,7 @@ prefill with prefix-cache reuse).
 from __future__ import annotations
 
 import math
+import time
 from typing import List, Optional, Tuple
 
 import numpy as np
@@ -152,6 +153,10 @@ class QwenEngine:
         self.fault_hook = None
         self._graphs = {}
         self.graph_replays = 0
+        #: host wall time spent inside prefill / decode calls (each ends with a device-to-host read,
+        #: so it covers the device work) and what they processed; a serving run reports the split
+        self.acct = {"prefill_s": 0.0, "prefill_calls": 0, "prefill_tokens": 0, "prefill_seqs": 0,
+                     "decode_s": 0.0, "decode_calls": 0, "decode_rows": 0}
 
     # ------------------------------------------------------------------ accounting
     def kv_pool_bytes(self) -> int:
@@ -337,15 +342,23 @@ class QwenEngine:
                       greedy: bool = True):
         """Process prompt positions [start, start+n) of one sequence.  Returns (first token, top-k
         candidates) when ``last`` (else (None, None))."""
-        x, delta = self._prefill_forward(tokens, start, block_table)
-        if not last:
-            return None, None
-        t, tk = self._head(x[-1:], delta[-1:], greedy)
-        first = int(t.cpu()[0])
-        if tk is None:
-            return first, None
-        idx, vals = tk[0].cpu()[0].tolist(), tk[1].cpu()[0].tolist()
-        return first, list(zip(idx, vals))
+        t0 = time.perf_counter()
+        try:
+            x, delta = self._prefill_forward(tokens, start, block_table)
+            if not last:
+                return None, None
+            t, tk = self._head(x[-1:], delta[-1:], greedy)
+            first = int(t.cpu()[0])
+            if tk is None:
+                return first, None
+            idx, vals = tk[0].cpu()[0].tolist(), tk[1].cpu()[0].tolist()
+            return first, list(zip(idx, vals))
+        finally:
+            a = self.acct
+            a["prefill_s"] += time.perf_counter() - t0
+            a["prefill_calls"] += 1
+            a["prefill_seqs"] += 1
+            a["prefill_tokens"] += int(tokens.shape[0])
 
     @torch.no_grad()
     def prefill_batch(self, items):
@@ -358,6 +371,7 @@ class QwenEngine:
             return [self.prefill_chunk(t, st, bt, last, greedy)]
         if self.fault_hook is not None:
             self.fault_hook("prefill")
+        t0 = time.perf_counter()
         dev = self.device
         lens = [int(it[0].shape[0]) for it in items]
         offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
@@ -400,6 +414,11 @@ class QwenEngine:
         for j, i in enumerate(final):
             cand = list(zip(idx[j], vals[j])) if tk is not None else None
             results[i] = (int(firsts[j]), cand)
+        a = self.acct
+        a["prefill_s"] += time.perf_counter() - t0
+        a["prefill_calls"] += 1
+        a["prefill_seqs"] += len(items)
+        a["prefill_tokens"] += n
         return results
 
     @torch.no_grad()
@@ -411,6 +430,17 @@ class QwenEngine:
             self.fault_hook("decode")
         dev = self.device
         B = int(tokens.shape[0])
+        t0 = time.perf_counter()
+        try:
+            return self._decode(tokens, positions, block_tables, window, greedy)
+        finally:
+            a = self.acct
+            a["decode_s"] += time.perf_counter() - t0
+            a["decode_calls"] += 1
+            a["decode_rows"] += B * window
+
+    def _decode(self, tokens, positions, block_tables, window, greedy):
+        dev = self.device
         if self.cuda_graphs and (greedy or window > 1):
             out = self._decode_graphed(tokens, positions, block_tables, window)
             return [row.tolist() for row in out], None
