@@ -94,7 +94,7 @@ def elementwise_suite(a, dev, bw):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "flash", "i8", "copy", "elementwise"])
+    ap.add_argument("what", choices=["gemm", "flash", "i8", "copy", "elementwise", "decode"])
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
@@ -106,6 +106,8 @@ def main(argv=None):
     ap.add_argument("--hk", type=int, default=8)
     ap.add_argument("--hd", type=int, default=128)
     ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--seqlen", type=int, default=1200, help="decode: keys per sequence")
+    ap.add_argument("--kv-int8", action="store_true", help="decode: int8 KV pools with per-row scales")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--library", action="store_true", help="also time the cuBLAS / SDPA baseline")
@@ -163,6 +165,40 @@ def main(argv=None):
             A, B, C = sets[0]
             tl = timeit([lambda: torch.matmul(A, B.t(), out=C)], a.iters, a.warmup)
             out["library_tflops"] = fl / tl / 1e12
+    elif a.what == "decode":
+        # split-KV paged decode attention: every K and V row of every sequence is read once
+        from brain_b200.ops._cuda import call, stream_ptr
+        B_, hq, hk, hd, S, bs = a.b, a.hq, a.hk, a.hd, a.seqlen, 16
+        per = -(-S // bs)
+        nb = B_ * per
+        es = 1 if a.kv_int8 else 2
+        if a.kv_int8:
+            kc = torch.randint(-127, 128, (nb, hk, bs, hd), device=dev, dtype=torch.int8)
+            vc = torch.randint(-127, 128, (nb, hk, bs, hd), device=dev, dtype=torch.int8)
+            ks = torch.rand(nb, hk, bs, device=dev) * 0.02
+            vs = torch.rand(nb, hk, bs, device=dev) * 0.02
+        else:
+            kc = torch.randn(nb, hk, bs, hd, device=dev).bfloat16()
+            vc = torch.randn(nb, hk, bs, hd, device=dev).bfloat16()
+        bts = torch.randperm(nb, device=dev).to(torch.int32).reshape(B_, per)
+        seqlens = torch.full((B_,), S, device=dev, dtype=torch.int32)
+        q = torch.randn(B_, hq * hd, device=dev).bfloat16()
+        o = torch.empty_like(q)
+        splits = max(1, min(16, (4 * 148 + B_ * hk - 1) // (B_ * hk)))
+        po = torch.empty(B_ * hq * splits * hd, device=dev)
+        pm = torch.empty(B_ * hq * splits * 2, device=dev)
+
+        def run():
+            if a.kv_int8:
+                call("paged_decode_i8", q, q.stride(0), kc, vc, ks, vs, bts, per, seqlens, o, o.stride(0), po, pm,
+                     B_, hq, hk, hd, bs, splits, float(hd ** -0.5), stream_ptr())
+            else:
+                call("paged_decode", q, q.stride(0), kc, vc, bts, per, seqlens, o, o.stride(0), po, pm,
+                     B_, hq, hk, hd, bs, splits, float(hd ** -0.5), stream_ptr())
+        t = timeit([run], a.iters, a.warmup)
+        nbytes = 2.0 * B_ * S * hk * hd * es + (8.0 * B_ * S * hk if a.kv_int8 else 0.0)
+        out.update(B=B_, S=S, hq=hq, hk=hk, hd=hd, kv="int8" if a.kv_int8 else "bf16", splits=splits, seconds=t,
+                   gbs=nbytes / t / 1e9, frac_of_peak=nbytes / t / bw)
     else:
         B_, T, hq, hk, hd = a.b, a.t, a.hq, a.hk, a.hd
         sets = []
