@@ -373,17 +373,45 @@ class LlmResident(ResidentModel):
 
 
 # ------------------------------------------------------------------------------------ registry
-def load_llm_from_env(device: str = "auto") -> Optional[LlmResident]:
+def resolve_env_model():
+    """``BRAIN_QWEN_WEIGHTS`` (a file) or ``BRAIN_MODEL`` (a ``<vendor>/<repo>[:owner:name:tag]``
+    reference looked up in the model store; nothing is fetched) -> (weights, tokenizer, adapter
+    file or None, served id or None); None when neither is set.  Raises FileNotFoundError for a
+    reference that is not on disk."""
     w = os.environ.get("BRAIN_QWEN_WEIGHTS")
-    if not w:
+    if w:
+        t = os.environ.get("BRAIN_QWEN_TOKENIZER") or os.path.join(os.path.dirname(w) or ".", "tokenizer.json")
+        return w, t, None, None
+    name = os.environ.get("BRAIN_MODEL")
+    if not name:
         return None
+    from ..modelref import ModelRef, canonical
+    from ..modelstore import Store, default_root
+    ref = ModelRef.parse(canonical(name))
+    root = default_root()
+    m = Store(root).local(ref) if root else None
+    if m is None:
+        raise FileNotFoundError(f"model {ref} is not in the model store ({root}); nothing is fetched automatically")
+    t = os.environ.get("BRAIN_QWEN_TOKENIZER") or m.tokenizer or os.path.join(m.dir, "tokenizer.json")
+    return m.weights, t, m.adapter, str(ref)
+
+
+def load_llm_from_env(device: str = "auto") -> Optional[LlmResident]:
+    sel = resolve_env_model()
+    if sel is None:
+        return None
+    w, t, adapter, served_id = sel
     import torch
     from ..checkpoint import st
     from ..data.tokenizer import load_tokenizer
     from ..train import pick_device
-    t = os.environ.get("BRAIN_QWEN_TOKENIZER") or os.path.join(os.path.dirname(w) or ".", "tokenizer.json")
     dev = pick_device(device)
     model, _, card = st.load_model(w, device=dev, dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32)
+    if adapter:
+        from ..models.lora import fold_adapter_into
+        tens, acfg, _ = st.load(adapter)
+        fold_adapter_into(model, {k: v.to(dev) for k, v in tens.items()}, int(acfg["rank"]),
+                          float(acfg.get("alpha", acfg["rank"])))
     model.eval()
     mode = "int8" if os.environ.get("BRAIN_QWEN_INT8") == "1" and dev.type == "cuda" else "bf16"
     kv8 = os.environ.get("BRAIN_QWEN_KV_INT8") == "1"
@@ -391,23 +419,24 @@ def load_llm_from_env(device: str = "auto") -> Optional[LlmResident]:
     if kv8 and os.environ.get("BRAIN_QWEN_KV_CALIB") == "1":
         from ..serve.calib import load_kv_clip
         clip = load_kv_clip(w)
-    return LlmResident(model, load_tokenizer(t), card.id if card is not None and card.id else "brain/qwen3",
-                       weights=mode, kv_dtype="int8" if kv8 else "bf16", kv_clip=clip)
+    mid = served_id or (card.id if card is not None and card.id else "brain/qwen3")
+    return LlmResident(model, load_tokenizer(t), mid, weights=mode, kv_dtype="int8" if kv8 else "bf16", kv_clip=clip)
 
 
 def registry_from_env(load: bool = True, device: str = "auto") -> Dict[str, ResidentModel]:
-    """Models selected by the environment: ``BRAIN_MOCK`` (non-empty) and ``BRAIN_QWEN_WEIGHTS``.
+    """Models selected by the environment: ``BRAIN_MOCK`` (non-empty), ``BRAIN_QWEN_WEIGHTS`` (a
+    checkpoint file) or ``BRAIN_MODEL`` (a reference into the model store).
     ``load=False`` lists what would be served without reading weights (for ``brain caps``)."""
     reg: Dict[str, ResidentModel] = {}
     if os.environ.get("BRAIN_MOCK"):
         reg[MockResident.id] = MockResident()
-    if os.environ.get("BRAIN_QWEN_WEIGHTS"):
+    if os.environ.get("BRAIN_QWEN_WEIGHTS") or os.environ.get("BRAIN_MODEL"):
         if load:
             m = load_llm_from_env(device)
             reg[m.id] = m
         else:
             class _Stub(ResidentModel):
-                id = "brain/qwen3"
+                id = os.environ.get("BRAIN_MODEL") or "brain/qwen3"
 
                 def manifest(self):
                     return Manifest(self.id, "Qwen-family decoder", [generate_spec("chat / text generation")])

@@ -53,12 +53,12 @@ def run_serve(argv: List[str], device: str = "auto") -> int:
     a.finish()
     if not stdio and not ports:
         print("usage: brain serve [--stdio | --openai [PORT] --anthropic [PORT] --openrouter [PORT]] "
-              "[--api-keys-out FILE --ready-file PATH -v N]   (models: BRAIN_MOCK=1, BRAIN_QWEN_WEIGHTS=…)",
+              "[--api-keys-out FILE --ready-file PATH -v N]   (models: BRAIN_MOCK=1, BRAIN_QWEN_WEIGHTS=FILE, BRAIN_MODEL=vendor/repo[:owner:name:tag])",
               file=sys.stderr)
         return 2
     models = registry_from_env(load=True, device=device)
     if not models:
-        print("serve: no model selected — set BRAIN_QWEN_WEIGHTS (and BRAIN_QWEN_TOKENIZER) or BRAIN_MOCK=1",
+        print("serve: no model selected — set BRAIN_QWEN_WEIGHTS (and BRAIN_QWEN_TOKENIZER), BRAIN_MODEL (a model-store reference) or BRAIN_MOCK=1",
               file=sys.stderr)
         return 1
     ex = Executor(models)

@@ -338,16 +338,16 @@ def parse_adapter_spec(spec: str):
 
 
 def models_dir(flag: Optional[str] = None) -> Optional[str]:
-    if flag:
-        return flag
-    if os.environ.get("BRAIN_MODELS_DIR"):
-        return os.environ["BRAIN_MODELS_DIR"]
-    home = os.environ.get("HOME")
-    return os.path.join(home, ".brain", "models") if home else None
+    from ..modelstore import default_root
+    return default_root(flag)
 
 
 def adapter_path(root: str, base_id: str, owner: str, name: str, tag: str) -> str:
-    return os.path.join(root, base_id.replace("/", "--"), "adapters", owner, name, tag, "adapter.safetensors")
+    """``<root>/<vendor>/<repo>/adapters/<owner>/<name>/<tag>/adapter.brain.safetensors``."""
+    from ..modelref import ModelRef
+    from ..modelstore import Store
+    ref = ModelRef.parse(base_id if "/" in base_id else f"local/{base_id}").base()
+    return Store(root).adapter_weights_path(ref.with_adapter(owner, name, tag))
 
 
 def _finetune_lora(args, device):

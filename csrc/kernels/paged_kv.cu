@@ -138,51 +138,118 @@ struct alignas(N) i8vec {
   uint32_t w[N / 4];
 };
 
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)),
+               "l"(gmem)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)),
+               "l"(gmem)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // One CTA (4 warps) per (sequence b, kv head, split).  G = query heads per kv head (<= 8).
 // q: [B, hq*hd]; block_tables: int32 [B, max_blocks]; seqlens: int32[B] (keys visible to the query).
 // part_o: fp32 [B, hq, splits, hd], part_ml: fp32 [B, hq, splits, 2] (running max in log2 domain, sum).
 //
+// Data movement: the CTA walks its keys 16 at a time.  The 16 K rows and 16 V rows of a step are
+// copied global -> shared with cp.async (16 bytes per request, no registers held), NST steps deep,
+// so each CTA keeps (NST-1) x 16 x 2 rows in flight; with three CTAs per SM that is enough
+// outstanding bytes to cover HBM latency.  (Register prefetch of one step ahead left ~16 KB per SM
+// in flight and reached about a third of the copy bandwidth.)
+//
 // Work layout: the head dimension is split over 8 lanes (HD/8 contiguous dims each), so a warp holds
 // four 8-lane groups and each group owns one key per step; the CTA's 4 warps x 4 groups take the 16
-// keys of one KV block per step (one block-table lookup per warp and step).  The query slice and the
-// output accumulators of all G heads stay in registers; a key's dot products are finished by a
-// 3-step butterfly inside its group, which leaves the score in all 8 lanes, so P.V needs no further
-// exchange.  Every group keeps its own running (max, sum, output) and the 16 partial states are
-// merged once at the end.  An earlier form (one lane per key, query read from shared memory for
-// every multiply) spent ~300 us per layer at batch 256 and was the largest item of a decode step.
+// keys of a step.  The query slice and the output accumulators of all G heads stay in registers; a
+// key's dot products are finished by a 3-step butterfly inside its group, which leaves the score in
+// all 8 lanes, so P.V needs no further exchange.  Every group keeps its own running (max, sum,
+// output) and the 16 partial states are merged once at the end.
 //
 // I8: kc/vc point at int8 pools and ks/vs at their per-row scales; a lane's slice of a row is DPL
 // bytes, the dot product runs on the integer values and the key's scale multiplies the score, the
 // value's scale multiplies the probability.
 template <int HD, int G, bool I8>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
                     const void* __restrict__ kc_, const void* __restrict__ vc_,
                     const float* __restrict__ ks, const float* __restrict__ vs,
                     const int* __restrict__ block_tables, int max_blocks,
                     const int* __restrict__ seqlens, float* __restrict__ part_o,
                     float* __restrict__ part_ml, int hq, int hk, int bs, int splits,
-                    float scale_log2) {
-  constexpr int DPL = HD / 8;   // dims per lane: 16 (hd 128) or 8 (hd 64)
-  constexpr int NV = I8 ? 1 : DPL / 8;   // raw vectors per lane per row: one DPL-byte (int8) / 16-byte (bf16)
-  using Raw = typename std::conditional<I8, i8vec<DPL>, bf16x8>::type;
-  using Elem = typename std::conditional<I8, int8_t, __nv_bfloat16>::type;
-  const Elem* __restrict__ kc = static_cast<const Elem*>(kc_);
-  const Elem* __restrict__ vc = static_cast<const Elem*>(vc_);
-  const int b = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+                    float scale_log2, int gsplit) {
+  // gsplit > 1: a kv head's query heads are divided over gsplit CTAs of G heads each (8 heads per
+  // kv head would need 256 registers for q and o alone); the siblings re-read K/V through L2.
+  constexpr int DPL = HD / 8;            // dims per lane: 16 (hd 128) or 8 (hd 64)
+  constexpr int ES = I8 ? 1 : 2;         // bytes per stored element
+  constexpr int ROWB = HD * ES;          // bytes per K or V row
+  constexpr int CPR = ROWB / 16;         // 16-byte requests per row
+  constexpr int NST = 4;                 // pipeline depth (steps of 16 keys)
+  constexpr int STAGE = 16 * ROWB;       // bytes per stage per tensor
+  constexpr int PIPE_BYTES = 2 * NST * STAGE;
+  constexpr int MERGE_BYTES = 4 * G * HD * 4;
+  constexpr int SMEM_BYTES = PIPE_BYTES > MERGE_BYTES ? PIPE_BYTES : MERGE_BYTES;
+  __shared__ __align__(16) unsigned char s_raw[SMEM_BYTES];   // pipeline stages, then the merge buffer
+  __shared__ float s_sc[NST][2][16];                          // I8: row scales (K, V) per stage
+  __shared__ float s_m[4][G], s_l[4][G];
+  unsigned char* s_k = s_raw;
+  unsigned char* s_v = s_raw + NST * STAGE;
+  const unsigned char* kc = static_cast<const unsigned char*>(kc_);
+  const unsigned char* vc = static_cast<const unsigned char*>(vc_);
+
+  const int b = blockIdx.x, kvh = blockIdx.y / gsplit, sp = blockIdx.z;
+  const int head0 = (kvh * gsplit + blockIdx.y % gsplit) * G;   // first query head of this CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grp = lane >> 3, sub = lane & 7;
   const int S = seqlens[b];
   const int per_split = ((S + splits - 1) / splits + 31) / 32 * 32;
   const int k_begin = sp * per_split;
   const int k_end = min(S, k_begin + per_split);
-  __shared__ float s_o[4][G][HD];
-  __shared__ float s_m[4][G], s_l[4][G];
+  const int nsteps = k_end > k_begin ? (k_end - k_begin + 15) >> 4 : 0;
+  const int* bt = block_tables + (size_t)b * max_blocks;
+
+  // copy the rows of step i into its stage (rows past k_end are left as they are and never used)
+  auto issue = [&](int i) {
+    const int st = i % NST;
+    const int k0 = k_begin + i * 16;
+#pragma unroll
+    for (int c = threadIdx.x; c < 16 * CPR; c += 128) {
+      const int kl = c / CPR, part = c % CPR;
+      const int key = k0 + kl;
+      if (key < k_end) {
+        const int blk = bt[key / bs], off = key % bs;
+        const size_t r = ((size_t)blk * hk + kvh) * bs + off;
+        cp_async16(s_k + st * STAGE + kl * ROWB + part * 16, kc + r * ROWB + part * 16);
+        cp_async16(s_v + st * STAGE + kl * ROWB + part * 16, vc + r * ROWB + part * 16);
+      }
+    }
+    if constexpr (I8) {
+      if (threadIdx.x < 32) {
+        const int kl = threadIdx.x & 15, which = threadIdx.x >> 4;
+        const int key = k0 + kl;
+        if (key < k_end) {
+          const int blk = bt[key / bs], off = key % bs;
+          const size_t r = ((size_t)blk * hk + kvh) * bs + off;
+          cp_async4(&s_sc[st][which][kl], (which ? vs : ks) + r);
+        }
+      }
+    }
+  };
+#pragma unroll
+  for (int i = 0; i < NST - 1; ++i) {
+    if (i < nsteps) issue(i);
+    cp_async_commit();
+  }
 
   float qr[G][DPL];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    const bf16x8* qp = reinterpret_cast<const bf16x8*>(q + (size_t)b * ldq + (kvh * G + g) * HD + sub * DPL);
+    const bf16x8* qp = reinterpret_cast<const bf16x8*>(q + (size_t)b * ldq + (head0 + g) * HD + sub * DPL);
 #pragma unroll
     for (int v = 0; v < DPL / 8; ++v) {
       float f[8];
@@ -199,90 +266,81 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
 #pragma unroll
     for (int j = 0; j < DPL; ++j) o[g][j] = 0.f;
   }
-  const int* bt = block_tables + (size_t)b * max_blocks;
-  // 16 keys per CTA step: warp w takes keys [k0 + 4w, k0 + 4w + 4), group g one of them.  The rows of
-  // the NEXT step are fetched before the current ones are used, so two steps of loads are in flight.
-  Raw kraw[NV], vraw[NV], knext[NV], vnext[NV];
-  float ksc = 1.f, vsc = 1.f, ksc_next = 1.f, vsc_next = 1.f;
-  auto fetch = [&](int k0, Raw (&kk)[NV], Raw (&vv)[NV], float& sk, float& sv) -> bool {
-    const int key = k0 + warp * 4 + grp;
-    if (key >= k_end) return false;
-    const int blk = bt[key / bs], off = key % bs;
-    const size_t r = ((size_t)blk * hk + kvh) * bs + off;
-    const size_t row = r * HD + sub * DPL;
-    const Raw* kr = reinterpret_cast<const Raw*>(kc + row);
-    const Raw* vr = reinterpret_cast<const Raw*>(vc + row);
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      kk[v] = kr[v];
-      vv[v] = vr[v];
-    }
-    if constexpr (I8) {
-      sk = ks[r];
-      sv = vs[r];
-    }
-    return true;
-  };
-  bool valid = fetch(k_begin, kraw, vraw, ksc, vsc);
-  for (int k0 = k_begin; k0 < k_end; k0 += 16) {
-    const bool valid_next = (k0 + 16 < k_end) ? fetch(k0 + 16, knext, vnext, ksc_next, vsc_next) : false;
-    if (valid) {
-      float kf[DPL], vf[DPL];
+
+  const int kl = warp * 4 + grp;   // this group's key within a step
+  for (int i = 0; i < nsteps; ++i) {
+    cp_async_wait<NST - 2>();      // step i has landed (for this thread's requests)
+    __syncthreads();               // ... for everyone's; and everyone is done with step i-1's stage
+    if (i + NST - 1 < nsteps) issue(i + NST - 1);
+    cp_async_commit();
+    const int st = i % NST;
+    if (k_begin + i * 16 + kl < k_end) {
+      float xf[DPL];
+      float sc[G];
+      const unsigned char* krow = s_k + st * STAGE + kl * ROWB + sub * DPL * ES;
       if constexpr (I8) {
+        const i8vec<DPL> raw = *reinterpret_cast<const i8vec<DPL>*>(krow);
 #pragma unroll
-        for (int v = 0; v < DPL / 4; ++v) {
+        for (int v = 0; v < DPL / 4; ++v)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            kf[v * 4 + j] = (float)(int8_t)(kraw[0].w[v] >> (8 * j));
-            vf[v * 4 + j] = (float)(int8_t)(vraw[0].w[v] >> (8 * j));
-          }
-        }
+          for (int j = 0; j < 4; ++j) xf[v * 4 + j] = (float)(int8_t)(raw.w[v] >> (8 * j));
       } else {
 #pragma unroll
-        for (int v = 0; v < NV; ++v) {
+        for (int v = 0; v < DPL / 8; ++v) {
           float t[8];
-          unpack8(kraw[v], t);
+          unpack8(reinterpret_cast<const bf16x8*>(krow)[v], t);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) kf[v * 8 + j] = t[j];
-          unpack8(vraw[v], t);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) vf[v * 8 + j] = t[j];
+          for (int j = 0; j < 8; ++j) xf[v * 8 + j] = t[j];
         }
       }
+      // the 8 lanes of a group are all valid or all invalid, so they shuffle among themselves
+      const unsigned int gm = 0xffu << (grp * 8);
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        float sc = 0.f;
+        float a = 0.f;
 #pragma unroll
-        for (int j = 0; j < DPL; ++j) sc += kf[j] * qr[g][j];
-        if constexpr (I8) sc *= ksc;
-        // the 8 lanes of a group are all valid or all invalid, so they shuffle among themselves
-        const unsigned int gm = 0xffu << (grp * 8);
-        sc += __shfl_xor_sync(gm, sc, 1);
-        sc += __shfl_xor_sync(gm, sc, 2);
-        sc += __shfl_xor_sync(gm, sc, 4);
-        if (sc > m[g]) {   // new running maximum: rescale what this group accumulated so far
-          const float alpha = exp2f(m[g] - sc);   // exp2(-inf) = 0 on the first key
+        for (int j = 0; j < DPL; ++j) a += xf[j] * qr[g][j];
+        a += __shfl_xor_sync(gm, a, 1);
+        a += __shfl_xor_sync(gm, a, 2);
+        a += __shfl_xor_sync(gm, a, 4);
+        if constexpr (I8) a *= s_sc[st][0][kl];
+        sc[g] = a;
+      }
+      const unsigned char* vrow = s_v + st * STAGE + kl * ROWB + sub * DPL * ES;
+      if constexpr (I8) {
+        const i8vec<DPL> raw = *reinterpret_cast<const i8vec<DPL>*>(vrow);
+#pragma unroll
+        for (int v = 0; v < DPL / 4; ++v)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) xf[v * 4 + j] = (float)(int8_t)(raw.w[v] >> (8 * j));
+      } else {
+#pragma unroll
+        for (int v = 0; v < DPL / 8; ++v) {
+          float t[8];
+          unpack8(reinterpret_cast<const bf16x8*>(vrow)[v], t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) xf[v * 8 + j] = t[j];
+        }
+      }
+      const float vscale = I8 ? s_sc[st][1][kl] : 1.f;
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        if (sc[g] > m[g]) {   // new running maximum: rescale what this group accumulated so far
+          const float alpha = exp2f(m[g] - sc[g]);   // exp2(-inf) = 0 on the first key
           l[g] *= alpha;
 #pragma unroll
           for (int j = 0; j < DPL; ++j) o[g][j] *= alpha;
-          m[g] = sc;
+          m[g] = sc[g];
         }
-        const float pg = exp2f(sc - m[g]);
+        const float pg = exp2f(sc[g] - m[g]);
         l[g] += pg;
-        const float pv = I8 ? pg * vsc : pg;
+        const float pv = I8 ? pg * vscale : pg;
 #pragma unroll
-        for (int j = 0; j < DPL; ++j) o[g][j] += pv * vf[j];
+        for (int j = 0; j < DPL; ++j) o[g][j] += pv * xf[j];
       }
     }
-    valid = valid_next;
-    ksc = ksc_next;
-    vsc = vsc_next;
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      kraw[v] = knext[v];
-      vraw[v] = vnext[v];
-    }
   }
+  cp_async_wait<0>();
   // merge the 4 groups of the warp (lanes sub, sub+8, sub+16, sub+24 hold the same dims)
 #pragma unroll
   for (int step = 8; step <= 16; step <<= 1) {
@@ -302,7 +360,9 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
       m[g] = mm;
     }
   }
-  // merge the 4 warps of the CTA
+  // merge the 4 warps of the CTA through shared memory (the pipeline stages are free now)
+  __syncthreads();
+  float* s_o = reinterpret_cast<float*>(s_raw);   // [4][G][HD]
   if (grp == 0) {
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -311,7 +371,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
         s_l[warp][g] = l[g];
       }
 #pragma unroll
-      for (int j = 0; j < DPL; ++j) s_o[warp][g][sub * DPL + j] = o[g][j];
+      for (int j = 0; j < DPL; ++j) s_o[(warp * G + g) * HD + sub * DPL + j] = o[g][j];
     }
   }
   __syncthreads();
@@ -323,9 +383,9 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
     for (int w = 0; w < 4; ++w) {
       const float a = (s_m[w][g] == -INFINITY) ? 0.f : exp2f(s_m[w][g] - mm);
       ll += s_l[w][g] * a;
-      oo += s_o[w][g][c] * a;
+      oo += s_o[(w * G + g) * HD + c] * a;
     }
-    const size_t idx = ((size_t)b * hq + kvh * G + g) * splits + sp;
+    const size_t idx = ((size_t)b * hq + head0 + g) * splits + sp;
     part_o[idx * HD + c] = oo;
     if (c == 0) {
       part_ml[idx * 2] = mm;
@@ -399,7 +459,8 @@ static int launch_paged_decode(bool i8, const void* q, int ldq, const void* kc, 
   if (B <= 0) return BB_OK;
   if (hq % hk || splits < 1) return BB_EARG;
   const int G = hq / hk;
-  dim3 grid(B, hk, splits);
+  const int gsplit = G == 8 ? 2 : 1;
+  dim3 grid(B, hk * gsplit, splits);
   const float sl2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
 #define BB_LAUNCH_PD(HD_, G_)                                                                     \
@@ -407,18 +468,18 @@ static int launch_paged_decode(bool i8, const void* q, int ldq, const void* kc, 
     if (i8)                                                                                       \
       paged_decode_kernel<HD_, G_, true><<<grid, 128, 0, s>>>(                                    \
           (const __nv_bfloat16*)q, ldq, kc, vc, ks, vs, block_tables, max_blocks, seqlens,        \
-          part_o, part_ml, hq, hk, bs, splits, sl2);                                              \
+          part_o, part_ml, hq, hk, bs, splits, sl2, gsplit);                                      \
     else                                                                                          \
       paged_decode_kernel<HD_, G_, false><<<grid, 128, 0, s>>>(                                   \
           (const __nv_bfloat16*)q, ldq, kc, vc, nullptr, nullptr, block_tables, max_blocks,       \
-          seqlens, part_o, part_ml, hq, hk, bs, splits, sl2);                                     \
+          seqlens, part_o, part_ml, hq, hk, bs, splits, sl2, gsplit);                             \
   } while (0)
   if (hd == 128) {
     switch (G) {
       case 1: BB_LAUNCH_PD(128, 1); break;
       case 2: BB_LAUNCH_PD(128, 2); break;
       case 4: BB_LAUNCH_PD(128, 4); break;
-      case 8: BB_LAUNCH_PD(128, 8); break;
+      case 8: BB_LAUNCH_PD(128, 4); break;   // two CTAs of 4 heads per kv head
       default: return BB_EARG;
     }
   } else if (hd == 64) {
