@@ -117,6 +117,18 @@ def attention_qkv(qkv, w_q, w_k, cos, sin, pos, B, T, hq, hk, hd, eps=1e-6, scal
     return _AttnQKV.apply(qkv, w_q, w_k, cos, sin, pos, B, T, hq, hk, hd, eps, scale)
 
 
+def flash_attention_into(out, q, k, v, B, T, hq, hk, hd, causal=True, scale=None, S=None, lse=None):
+    """Inference form of :func:`flash_attention` on CUDA: no autograd node, rows may be strided views
+    (last dimension contiguous) and the result is written into ``out`` [B*T, hq*hd]."""
+    S = T if S is None else S
+    scale = 1.0 / math.sqrt(hd) if scale is None else scale
+    if lse is None:
+        lse = torch.empty(B, hq, T, device=q.device, dtype=torch.float32)
+    call("flash_fwd", q, q.stride(0), k, k.stride(0), v, v.stride(0), out, out.stride(0), lse,
+         B, T, S, hq, hk, hd, float(scale), int(causal), stream_ptr())
+    return out
+
+
 def flash_attention(q, k, v, B, T, hq, hk, hd, causal=True, scale=None, S=None):
     """q: [B*T, hq*hd]; k, v: [B*S, hk*hd] (S defaults to T) -> [B*T, hq*hd]."""
     S = T if S is None else S

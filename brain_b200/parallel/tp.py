@@ -113,11 +113,9 @@ class TensorParallel:
         dist.all_reduce(y, group=self.group)
         return y
 
-    def _all_reduce2(self, x):
-        """Two-shot peer-memory all-reduce; the result is a view of this rank's symmetric result
-        buffer (two alternate, so a result stays valid across ONE later all-reduce)."""
-        from ..ops._cuda import L, call, stream_ptr
-        n = x.numel()
+    def ensure_ar2(self, n: int):
+        """Symmetric staging + two result buffers of the two-shot all-reduce, holding >= ``n``
+        elements (collective: every rank calls it with the same ``n``)."""
         if self._ar2 is None or self._ar2["cap"] < n:
             cap = max(n, 1 << 22)
             stage = self.arena.alloc(cap, torch.bfloat16)
@@ -127,7 +125,14 @@ class TensorParallel:
                          "res_ptrs": [self._U64(*self.arena.peer_ptrs(r)) for r in res]}
             if dist.is_initialized():
                 dist.barrier(group=self.group)      # nobody signals into buffers that do not exist yet
-        st = self._ar2
+        return self._ar2
+
+    def _all_reduce2(self, x):
+        """Two-shot peer-memory all-reduce; the result is a view of this rank's symmetric result
+        buffer (two alternate, so a result stays valid across ONE later all-reduce)."""
+        from ..ops._cuda import L, call, stream_ptr
+        n = x.numel()
+        st = self.ensure_ar2(n)
         which = self.ar2_calls & 1
         self.ar2_calls += 1
         xc = x.contiguous()

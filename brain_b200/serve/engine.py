@@ -21,6 +21,7 @@ prefill with prefix-cache reuse).
 from __future__ import annotations
 
 import math
+import os
 import time
 from typing import List, Optional, Tuple
 
@@ -31,7 +32,7 @@ from ..models.config import QwenConfig
 from ..ops import functional as F
 from ..ops import reference as ref
 from ..ops._cuda import L, call, stream_ptr
-from ..ops.attention import flash_attention
+from ..ops.attention import flash_attention, flash_attention_into
 
 
 class _Lin:
@@ -73,7 +74,7 @@ class QwenEngine:
     def __init__(self, model, block_size: int = 16, num_blocks: int = 1024, max_seq_len: int = 4096,
                  max_prefill: int = 512, weights: str = "bf16", topk: int = 64, tp=None,
                  decode_splits: int = 0, cuda_graphs: bool = True, kv_dtype: str = "bf16",
-                 kv_clip=None):
+                 kv_clip=None, native: Optional[bool] = None):
         cfg: QwenConfig = model.cfg
         self.cfg = cfg
         self.tp = tp
@@ -96,6 +97,7 @@ class QwenEngine:
         r = self.tp_rank
         q, kv, ff = cfg.q_dim, cfg.kv_dim, cfg.d_ff
         ql, kl, fl = q // w, kv // w, ff // w
+        self.ff_local = fl
 
         def cast(t):
             return t.detach().to(dev, self.dtype)
@@ -153,6 +155,17 @@ class QwenEngine:
         self.fault_hook = None
         self._graphs = {}
         self.graph_replays = 0
+        #: the layer sequence issued by one native call per layer half / per decode step instead of
+        #: one Python wrapper per kernel (CUDA only; same kernels, same results)
+        self.native = None
+        if native is None:
+            native = os.environ.get("BRAIN_SERVE_NATIVE", "0") == "1"
+        if native and self.cuda:
+            from .native import NativeForward
+            tp_ok = self.tp is None or self.tp_world == 1 or \
+                (getattr(self.tp, "impl", "") == "fused" and cfg.d_model % (8 * self.tp_world) == 0)
+            if tp_ok and NativeForward.supported(self):
+                self.native = NativeForward(self)
         #: host wall time spent inside prefill / decode calls (each ends with a device-to-host read,
         #: so it covers the device work) and what they processed; a serving run reports the split
         self.acct = {"prefill_s": 0.0, "prefill_calls": 0, "prefill_tokens": 0, "prefill_seqs": 0,
@@ -243,15 +256,19 @@ class QwenEngine:
         off = t % self.block_size
         return (self.kc[li][blk, :, off].reshape(S, -1), self.vc[li][blk, :, off].reshape(S, -1))
 
+    def _splits(self, B: int) -> int:
+        """KV splits of the decode attention: enough CTAs to fill the machine (B * hk * splits >= ~4
+        per SM)."""
+        if self.decode_splits > 0:
+            return self.decode_splits
+        return max(1, min(16, (4 * 148 + B * self.hk - 1) // (B * self.hk)))
+
     def _paged_attention(self, li: int, q, block_tables, seqlens):
         B = q.shape[0]
         hq, hk, hd = self.hq, self.hk, self.hd
         scale = 1.0 / math.sqrt(hd)
         if self.cuda:
-            splits = self.decode_splits
-            if splits <= 0:
-                # enough CTAs to fill the machine: B * hk * splits >= ~4 per SM
-                splits = max(1, min(16, (4 * 148 + B * hk - 1) // (B * hk)))
+            splits = self._splits(B)
             out = torch.empty(B, hq * hd, device=self.device, dtype=self.dtype)
             part_o = torch.empty(B * hq * splits * hd, device=self.device, dtype=torch.float32)
             part_ml = torch.empty(B * hq * splits * 2, device=self.device, dtype=torch.float32)
@@ -291,7 +308,14 @@ class QwenEngine:
         return x, m
 
     def _head(self, x, delta, greedy: bool):
+        """LM head over rows of the residual stream ``x`` + pending MLP output ``delta``; with
+        ``delta`` None, ``x`` is already the final-normed hidden state (native path)."""
+        if delta is None:
+            return self._head_normed(x, greedy)
         h, _ = F.rmsnorm(delta, self.norm, self.cfg.rms_eps, residual=x)
+        return self._head_normed(h, greedy)
+
+    def _head_normed(self, h, greedy: bool):
         logits = self.head(h)
         if greedy:
             return F.argmax_rows(logits), None
@@ -312,6 +336,8 @@ class QwenEngine:
         slots = self._slots(bt[None, :].expand(n, -1), pos)
         S = start + n
         hq, hk, hd = self.hq, self.hk, self.hd
+        if self.native is not None:
+            return self._native_prefill(tok, pos, slots, [(0, n, start, bt)])
 
         def attn(li, q, k, v):
             self._append_kv(li, k, v, slots)
@@ -326,6 +352,32 @@ class QwenEngine:
             x, delta = self._layer(li, x, delta, pos, attn)
         self.steps += 1
         return x, delta
+
+    def _native_prefill(self, tok, pos, slots, seqs):
+        """Packed rows through the native layer halves; ``seqs``: (row offset, rows, start, block
+        table) per sequence, attention per sequence in between.  Returns (normed hidden [n, d], None):
+        the final RMSNorm is already applied."""
+        nat = self.native
+        n = int(tok.shape[0])
+        hq, hk, hd = self.hq, self.hk, self.hd
+        sc = nat.scratch(-(-n // 256) * 256, 1, key="prefill")
+        nat.begin(sc, tok.to(torch.int32), n)
+        qw = hq * hd
+        lse = torch.empty(hq * max(l for _, l, _, _ in seqs), device=self.device, dtype=torch.float32)
+        for li in range(len(self.layers)):
+            nat.pre_attn(sc, li, pos, slots, n)
+            for o, l, start, bt in seqs:
+                q = sc.qk[o:o + l, :qw]
+                out = sc.o[o:o + l]
+                if start == 0:
+                    flash_attention_into(out, q, sc.qk[o:o + l, qw:], sc.qkv[o:o + l, qw + hk * hd:], 1, l, hq, hk, hd,
+                                         True, lse=lse)
+                else:
+                    kk, vv = self._gather_kv(li, bt, start + l)
+                    flash_attention_into(out, q, kk, vv, 1, l, hq, hk, hd, True, S=start + l, lse=lse)
+            nat.post_attn(sc, li, n)
+        self.steps += 1
+        return nat.finish(sc, n), None
 
     @torch.no_grad()
     def verify_chunk(self, tokens: np.ndarray, start: int, block_table: np.ndarray) -> np.ndarray:
@@ -347,7 +399,7 @@ class QwenEngine:
             x, delta = self._prefill_forward(tokens, start, block_table)
             if not last:
                 return None, None
-            t, tk = self._head(x[-1:], delta[-1:], greedy)
+            t, tk = self._head(x[-1:], delta[-1:] if delta is not None else None, greedy)
             first = int(t.cpu()[0])
             if tk is None:
                 return first, None
@@ -383,6 +435,10 @@ class QwenEngine:
         slots = torch.cat([self._slots(bt[None, :].expand(l, -1), pos[o:o + l])
                            for bt, l, o in zip(bts, lens, offs[:-1].tolist())])
         hq, hk, hd = self.hq, self.hk, self.hd
+        if self.native is not None:
+            x, delta = self._native_prefill(tok, pos, slots, [(o, l, it[1], bt) for it, bt, l, o in
+                                                              zip(items, bts, lens, offs[:-1].tolist())])
+            return self._prefill_batch_results(items, offs, x, delta, n, t0)
 
         def attn(li, q, k, v):
             self._append_kv(li, k, v, slots)
@@ -401,20 +457,28 @@ class QwenEngine:
         for li in range(len(self.layers)):
             x, delta = self._layer(li, x, delta, pos, attn)
         self.steps += 1
+        return self._prefill_batch_results(items, offs, x, delta, n, t0)
+
+    def _prefill_batch_results(self, items, offs, x, delta, n, t0):
+        dev = self.device
+        a = self.acct
         final = [i for i, it in enumerate(items) if it[3]]
         results = [(None, None)] * len(items)
         if not final:
+            a["prefill_s"] += time.perf_counter() - t0
+            a["prefill_calls"] += 1
+            a["prefill_seqs"] += len(items)
+            a["prefill_tokens"] += n
             return results
         rows = torch.tensor([int(offs[i + 1]) - 1 for i in final], device=dev, dtype=torch.long)
         all_greedy = all(items[i][4] for i in final)
-        t, tk = self._head(x[rows], delta[rows], all_greedy)
+        t, tk = self._head(x[rows], delta[rows] if delta is not None else None, all_greedy)
         firsts = t.cpu().tolist()
         if tk is not None:
             idx, vals = tk[0].cpu().tolist(), tk[1].cpu().tolist()
         for j, i in enumerate(final):
             cand = list(zip(idx[j], vals[j])) if tk is not None else None
             results[i] = (int(firsts[j]), cand)
-        a = self.acct
         a["prefill_s"] += time.perf_counter() - t0
         a["prefill_calls"] += 1
         a["prefill_seqs"] += len(items)
@@ -460,6 +524,22 @@ class QwenEngine:
         B = tok.shape[0]
         outs = []
         topks = None
+        if self.native is not None:
+            nat = self.native
+            sc = nat.scratch(B, self._splits(B), key=("decode", B))
+            tok = tok.to(torch.int32)
+            for w in range(window):
+                slots = self._slots(bts, pos)
+                seqlens = (pos + 1).to(torch.int32)
+                hn = nat.decode(sc, tok, pos, slots, bts, seqlens, B)
+                t, tk = self._head_normed(hn, greedy)
+                outs.append(t)
+                if tk is not None:
+                    topks = tk
+                tok = t
+                pos = pos + 1
+                self.steps += 1
+            return torch.stack(outs, dim=1), topks
         for w in range(window):
             slots = self._slots(bts, pos)
             seqlens = (pos + 1).to(torch.int32)

@@ -173,3 +173,53 @@ def test_engine_int8_kv_tracks_bf16_kv():
     assert len(common) >= 32
     spread = max(outs[0].values()) - min(outs[0].values())
     assert max(abs(outs[0][t] - outs[1][t]) for t in common) < 0.1 * spread
+
+
+@pytest.mark.parametrize("weights,kv", [("bf16", "bf16"), ("int8", "int8")])
+def test_native_forward_matches_python_path(weights, kv):
+    """The native layer sequence issues the same kernels in the same order as the Python wrappers:
+    prefill (fresh chunk, chunk with a past, packed chunks), eager decode and graph decode agree."""
+    from brain_b200.models.config import QwenConfig
+    from brain_b200.models.qwen3 import Qwen3
+    from brain_b200.ops import _cuda
+    from brain_b200.serve.engine import QwenEngine
+    cfg = QwenConfig(vocab=512, block_size=512, n_layers=3, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, d_ff=512)
+    m = Qwen3(cfg).init_weights(3)
+    with torch.no_grad():
+        for p in m.parameters():
+            p.mul_(3.0)
+    m = m.to("cuda", torch.bfloat16)
+    mk = lambda native, graphs: QwenEngine(m, block_size=16, num_blocks=128, max_seq_len=512, max_prefill=256,
+                                           weights=weights, kv_dtype=kv, native=native, cuda_graphs=graphs)
+    e_py, e_nat, e_graph = mk(False, False), mk(True, False), mk(True, True)
+    assert e_py.native is None and e_nat.native is not None
+    rng = np.random.default_rng(0)
+    toks = rng.integers(0, 512, 200).astype(np.int32)
+    bt0, bt1, bt2 = (np.arange(32, dtype=np.int32) + 32 * i for i in range(3))
+    res = []
+    for e in (e_py, e_nat, e_graph):
+        r = {}
+        e.prefill_chunk(toks[:128], 0, bt0, False)
+        r["first"], r["cand"] = e.prefill_chunk(toks[128:], 128, bt0, True, greedy=False)
+        items = [(toks[:70], 0, bt1, True, True), (toks[50:141], 0, bt2, True, True)]
+        r["packed"] = [t for t, _ in e.prefill_batch(items)]
+        r["verify"] = e.verify_chunk(toks[10:30], 200, bt0).tolist()
+        tok = np.array([r["first"], r["packed"][0], r["packed"][1]], dtype=np.int32)
+        pos = np.array([220, 70, 91], dtype=np.int32)
+        bts = np.stack([bt0, bt1, bt2])
+        out, _ = e.decode(tok, pos, bts, window=3, greedy=True)
+        r["decode"] = out
+        _, c = e.decode(np.array([5, 6, 7], dtype=np.int32), pos + 3, bts, window=1, greedy=False)
+        r["dcand"] = c
+        res.append(r)
+    _cuda.check_error()
+    py, nat, gr = res
+    assert e_graph.graph_replays >= 1
+    for other in (nat, gr):
+        assert other["first"] == py["first"] and other["packed"] == py["packed"] and other["verify"] == py["verify"]
+        assert other["decode"] == py["decode"]
+        a, b = dict(py["cand"]), dict(other["cand"])
+        assert set(a) == set(b) and max(abs(a[t] - b[t]) for t in a) < 1e-3
+        for ca, cb in zip(py["dcand"], other["dcand"]):
+            a, b = dict(ca), dict(cb)
+            assert set(a) == set(b) and max(abs(a[t] - b[t]) for t in a) < 1e-3
