@@ -14,6 +14,7 @@ from typing import Callable, Optional
 import torch
 
 from . import _cuda, reference as ref
+from ..utils import tune as _tune
 from ._cuda import L, call, stream_ptr
 
 IGNORE_INDEX = ref.IGNORE_INDEX
@@ -49,6 +50,12 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, ac
     mode = 3 if gelu else (0 if out.dtype == torch.bfloat16 else (2 if accumulate else 1))
     if M == 0 or N == 0:
         return out
+    if bn == 0 and _tune._TUNER is not None and not accumulate and not torch.cuda.is_current_stream_capturing():
+        # autotune (off by default): time the tile widths once per shape, then use the cached winner
+        t = _tune._TUNER
+        bn = t.pick(t.key("gemm_bf16", M, N, K, int(a_mn), int(b_mn), mode), _tune.GEMM_BN,
+                    lambda c: call("gemm_bf16", a, b, out, bias, M, N, K, a.stride(0), b.stride(0), out.stride(0),
+                                   int(a_mn), int(b_mn), mode, float(alpha), int(c), int(max_ctas), stream_ptr()))
     call("gemm_bf16", a, b, out, bias, M, N, K, a.stride(0), b.stride(0), out.stride(0),
          int(a_mn), int(b_mn), mode, float(alpha), int(bn), int(max_ctas), stream_ptr())
     return out
