@@ -249,7 +249,7 @@ def _gradcheck(args, device):
     which = a.str_or("--model", "gpt")
     dirs = a.int_or("--dirs", 4)
     a.finish()
-    names = ("gpt", "qwen", "qwen2", "qwen_lora", "moe", "qwen_moe") if which == "all" else tuple(which.split(","))
+    names = ("gpt", "qwen", "qwen2", "qwen_lora", "qwen3_weighted", "moe", "qwen_moe") if which == "all" else tuple(which.split(","))
     fails = gradcheck.run_gate(names, n_dirs=dirs)
     return 1 if fails else 0
 

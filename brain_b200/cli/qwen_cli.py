@@ -256,10 +256,11 @@ def _train(args, device, base: Optional[str]):
     save_secs = a.int_or("--save-secs", 600)
     dp_n = a.int_or("--dp", 1)
     preset = a.take_str("--preset")
+    weighted = a.take_flag("--weighted")
     a.finish()
     if data_dir is None:
         print("usage: brain qwen3 {train|finetune} <data_dir> --out F [--steps N --batch B --block T --lr X "
-              "--mask = --align --dp N --preset 0.6b]", file=sys.stderr)
+              "--mask = --align --dp N --preset 0.6b --weighted]", file=sys.stderr)
         return 2
     if dp_n > 1:
         return _relaunch(dp_n, ["qwen3", "finetune" if base else "train"] + args +
@@ -268,7 +269,10 @@ def _train(args, device, base: Optional[str]):
                 min_lr=lr * 0.1, weight_decay=0.1, grad_clip=1.0, grad_accum=1,
                 eval_interval=max(steps // 10, 1), eval_batches=20, checkpoint_secs=save_secs,
                 mask_before=mask, mask_per_line=mask is not None, align_to_lines=align, seed=seed,
-                device=device)
+                device=device, weighted=weighted)
+    if weighted and not os.path.exists(os.path.join(data_dir, "train.weight.bin")):
+        print(f"--weighted: {data_dir}/train.weight.bin not found", file=sys.stderr)
+        return 1
 
     def build(vocab, blk):
         if preset:

@@ -57,15 +57,19 @@ class Trainer:
             return t
         return t.to(self.device, non_blocking=True)
 
-    def forward_backward(self, tokens, targets, micro_batch: int, loss_scale: float):
-        """Accumulate gradients of sum(token losses) * loss_scale over the rows of ``tokens``.
-        Returns the accumulated (device) loss."""
+    def forward_backward(self, tokens, targets, micro_batch: int, loss_scale: float, weights=None):
+        """Accumulate gradients of sum(token losses) * loss_scale over the rows of ``tokens``
+        (``weights``: per-position loss weights, models that take them).  Returns the accumulated
+        (device) loss."""
         B = tokens.shape[0]
         total = None
         for r0 in range(0, B, micro_batch):
             tok = self._to_device(tokens[r0:r0 + micro_batch])
             tgt = self._to_device(targets[r0:r0 + micro_batch])
-            loss = self.model.loss(tok, tgt, loss_scale)
+            if weights is not None:
+                loss = self.model.loss(tok, tgt, loss_scale, self._to_device(weights[r0:r0 + micro_batch]))
+            else:
+                loss = self.model.loss(tok, tgt, loss_scale)
             loss.backward()
             total = loss.detach() if total is None else total + loss.detach()
         if not self.cuda:

@@ -169,6 +169,19 @@ def check_qwen2(n_dirs: int = 4, eps: float = 5e-3, seed: int = 0, dtype=torch.f
     return _model_check(m, cfg.vocab, 2, 6, n_dirs, eps, seed, dtype)
 
 
+def check_qwen3_weighted(n_dirs: int = 4, eps: float = 5e-3, seed: int = 0, dtype=torch.float32) -> Report:
+    """Per-position weighted loss sum_i w_i CE_i / count with weights of both signs and a zero
+    (crates/gradcheck ``check_qwen3_weighted``)."""
+    from .models.config import QwenConfig
+    from .models.qwen3 import Qwen3
+    cfg = QwenConfig.tiny()
+    model = Qwen3(cfg).init_weights(1).to(dtype)
+    x, y = _fixed_batch(cfg.vocab, 2, 6)
+    w = torch.tensor([1.0, -0.5, 2.0, 0.0, 0.25, 1.5] * 2, dtype=dtype).view(2, 6)
+    params = {n: p for n, p in model.named_parameters() if p.requires_grad}
+    return directional_check(lambda: model.loss(x, y, None, w), params, eps, n_dirs, seed)
+
+
 def check_qwen_lora(n_dirs: int = 4, eps: float = 5e-3, seed: int = 0, dtype=torch.float32) -> Report:
     from .models.config import LoraCfg, QwenConfig
     from .models.lora import attach_lora
@@ -207,7 +220,7 @@ def check_qwen_moe(n_dirs: int = 4, eps: float = 1e-5, seed: int = 0, dtype=torc
 
 GATES = {
     "gpt": check_gpt, "qwen": check_qwen, "qwen2": check_qwen2, "qwen_lora": check_qwen_lora,
-    "moe": check_moe, "qwen_moe": check_qwen_moe,
+    "qwen3_weighted": check_qwen3_weighted, "moe": check_moe, "qwen_moe": check_qwen_moe,
 }
 
 

@@ -227,9 +227,10 @@ class Qwen3(nn.Module):
             return h
         return x + delta if delta is not None else x
 
-    def forward(self, tokens, targets=None, loss_scale=None):
+    def forward(self, tokens, targets=None, loss_scale=None, weights=None):
         """tokens [B,T] -> logits [B,T,V] (targets None) or the summed token loss * loss_scale
-        (default 1/#counted targets, i.e. the mean)."""
+        (default 1/#counted targets, i.e. the mean); ``weights`` [B,T] multiplies each position's
+        loss (weighted-loss training)."""
         B, T = tokens.shape
         h = self.hidden(tokens)
         w = self.head_weight()
@@ -237,10 +238,11 @@ class Qwen3(nn.Module):
             assert self.tp is None, "logits of a tensor-parallel model: use hidden() and gather the rows"
             return F.linear(h, w).reshape(B, T, -1)
         # under tensor parallelism h holds this rank's rows: the loss is this rank's partial sum
-        return F.lm_head_ce(h, w, self.local_rows(targets.reshape(-1)), loss_scale, self.ce_chunk_rows)
+        wl = self.local_rows(weights.reshape(-1)) if weights is not None else None
+        return F.lm_head_ce(h, w, self.local_rows(targets.reshape(-1)), loss_scale, self.ce_chunk_rows, wl)
 
-    def loss(self, tokens, targets, loss_scale=None):
-        return self.forward(tokens, targets, loss_scale)
+    def loss(self, tokens, targets, loss_scale=None, weights=None):
+        return self.forward(tokens, targets, loss_scale, weights)
 
     # ------------------------------------------------------------------ checkpoint naming
     def reference_state(self) -> Dict[str, torch.Tensor]:

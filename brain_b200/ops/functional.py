@@ -429,7 +429,7 @@ class _LMHeadCE(torch.autograd.Function):
     exact, which holds when the loss is what ``backward()`` is called on."""
 
     @staticmethod
-    def forward(ctx, x, w, targets, scale, chunk_rows):
+    def forward(ctx, x, w, targets, scale, chunk_rows, weights=None):
         d = x.shape[-1]
         x2 = x.reshape(-1, d)
         if x2.stride(-1) != 1:
@@ -437,6 +437,7 @@ class _LMHeadCE(torch.autograd.Function):
         n = x2.shape[0]
         V = w.shape[0]
         t32 = targets.reshape(-1).to(torch.int32)
+        wts = weights.reshape(-1).float() if weights is not None else None
         loss_rows = torch.empty(n, device=x.device, dtype=torch.float32)
         need_grad = x.requires_grad or w.requires_grad
         dx = torch.empty_like(x2) if need_grad else None
@@ -454,6 +455,9 @@ class _LMHeadCE(torch.autograd.Function):
             gemm(x2[r0:r1], w, out=lg)
             call("cross_entropy", lg, L(lg.stride(0)), t32[r0:r1], loss_rows[r0:r1], None, m, V,
                  1 if need_grad else 0, None, float(scale), stream_ptr())
+            if wts is not None and need_grad:
+                # per-position weights: d(sum_i w_i CE_i)/d(logits) is the row gradient times w_i
+                lg.mul_(wts[r0:r1, None].to(lg.dtype))
             if need_grad:
                 gemm(lg, w, b_mn=True, out=dx[r0:r1])
                 if dw_acc is not None:
@@ -463,6 +467,8 @@ class _LMHeadCE(torch.autograd.Function):
         ctx.w_ref = w
         ctx.dw = None if (mg is not None or dw_acc is None) else dw_acc
         ctx.used_main = mg is not None and dw_acc is not None
+        if wts is not None:
+            return (loss_rows * wts).sum() * scale
         return loss_rows.sum() * scale
 
     @staticmethod
@@ -474,18 +480,23 @@ class _LMHeadCE(torch.autograd.Function):
             gw = (ctx.dw * dl.float()).to(ctx.w_ref.dtype)
         if ctx.used_main:
             _notify(ctx.w_ref)
-        return gx, gw, None, None, None
+        return gx, gw, None, None, None, None
 
 
-def lm_head_ce(x, w, targets, scale=None, chunk_rows=8192):
-    """sum over counted tokens of CE(x @ w^T, target) * scale  (scale defaults to 1/count)."""
+def lm_head_ce(x, w, targets, scale=None, chunk_rows=8192, weights=None):
+    """sum over counted tokens of CE(x @ w^T, target) * scale  (scale defaults to 1/count).
+    ``weights`` (one per position) turns it into sum_i w_i CE_i * scale — the reward / advantage
+    weighted loss of crates/qwen3/src/model.rs:1320-1334."""
     if scale is None:
         scale = 1.0 / max(int((targets >= 0).sum().item()), 1)
     if not x.is_cuda:
         logits = ref.linear(x, w)
+        if weights is not None:
+            rows = ref.cross_entropy(logits.reshape(-1, logits.shape[-1]), targets.reshape(-1), reduction="none")
+            return (rows * weights.reshape(-1).to(rows.dtype)).sum() * scale
         return ref.cross_entropy(logits.reshape(-1, logits.shape[-1]), targets.reshape(-1),
                                  reduction="sum") * scale
-    return _LMHeadCE.apply(x, w, targets, float(scale), int(chunk_rows))
+    return _LMHeadCE.apply(x, w, targets, float(scale), int(chunk_rows), weights)
 
 
 # --------------------------------------------------------------------------------------- misc

@@ -41,6 +41,7 @@ class FitOpts:
     align_to_lines: bool = False
     betas: Tuple[float, float] = (0.9, 0.999)
     device: str = "auto"
+    weighted: bool = False                    # per-position loss weights from train.weight.bin
 
 
 def load_dataset(dirpath: str, opts: FitOpts):
@@ -131,11 +132,13 @@ def fit(data_dir: str, build_model: Callable[[int, int], torch.nn.Module], opts:
         lr = cosine_lr(step, opts.lr, opts.min_lr, opts.warmup, opts.decay_iters)
         trainer.zero_grads()
         step_loss = 0.0
-        batches = [tr_ds.get_batch(bc, rng, pin=pin) for _ in range(accum)]
-        count = sum(int((y >= 0).sum()) for _, y in batches)
+        batches = [tr_ds.get_batch(bc, rng, weighted=opts.weighted, pin=pin) for _ in range(accum)]
+        count = sum(int((b[1] >= 0).sum()) for b in batches)
         world = dp.world if dp is not None else 1
-        for x, y in batches:
-            loss = trainer.forward_backward(x, y, x.shape[0], 1.0 / max(count * world, 1))
+        for b in batches:
+            x, y = b[0], b[1]
+            loss = trainer.forward_backward(x, y, x.shape[0], 1.0 / max(count * world, 1),
+                                            b[2] if opts.weighted else None)
             step_loss += float(loss) * world
         trainer.optimizer_step(lr)
         last_train = step_loss

@@ -449,3 +449,35 @@ def test_cost_registry_and_roof():
     r = Roof(6551.0, 1640.0, 1384.0)
     assert r.bound(1e15, 1e6) == "compute" and r.bound(1e6, 1e12) == "memory"
     assert r.min_seconds(1640e12, 0) == pytest.approx(1.0)
+
+
+def test_weighted_loss_and_fit(tmp_path):
+    """sum_i w_i CE_i / count: unit weights reproduce the plain loss, zero weights give zero loss and
+    zero gradients, and ``fit(weighted=True)`` trains from train.weight.bin."""
+    import numpy as np
+    import torch
+    from brain_b200 import gradcheck
+    from brain_b200.data import binio
+    from brain_b200.models.config import QwenConfig
+    from brain_b200.models.qwen3 import Qwen3
+    from brain_b200.train import FitOpts, fit
+    cfg = QwenConfig.tiny()
+    m = Qwen3(cfg).init_weights(1)
+    x = torch.randint(0, cfg.vocab, (2, 6), dtype=torch.int32)
+    y = torch.randint(0, cfg.vocab, (2, 6))
+    plain = m.loss(x, y)
+    assert torch.allclose(m.loss(x, y, None, torch.ones(2, 6)), plain, atol=1e-6)
+    assert torch.allclose(m.loss(x, y, None, torch.full((2, 6), 2.0)), 2 * plain, atol=1e-5)
+    z = m.loss(x, y, None, torch.zeros(2, 6))
+    z.backward()
+    assert float(z) == 0.0 and all(p.grad is None or float(p.grad.abs().max()) == 0.0 for p in m.parameters())
+    assert gradcheck.run_gate(("qwen3_weighted",), out=lambda s: None) == 0
+    d = str(tmp_path / "w")
+    rng = np.random.default_rng(0)
+    toks = rng.integers(0, 20, 600)
+    binio.write_dataset(d, toks[:500], toks[500:], vocab_size=20, weights=rng.random(500).astype("float32"))
+    o = FitOpts(steps=4, batch_size=2, block_size=8, eval_interval=0, checkpoint_secs=0, device="cpu", weighted=True)
+    build = lambda vocab, blk: Qwen3(QwenConfig(vocab=vocab, block_size=blk, n_layers=1, d_model=16, n_heads=2,
+                                                n_kv_heads=1, head_dim=8, d_ff=32))
+    l0, l1 = fit(d, build, o, None, log=lambda s: None)
+    assert l0 == l0 and l1 == l1

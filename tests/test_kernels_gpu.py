@@ -242,6 +242,27 @@ def test_lm_head_ce_fused():
     assert rel_err(w.grad, wr.grad) < 3e-2
 
 
+def test_lm_head_ce_weighted():
+    """Per-position weights (both signs, zeros) in the fused LM head + CE."""
+    torch.manual_seed(12)
+    n, d, V = 260, 128, 1000
+    x = (0.5 * torch.randn(n, d, device=dev())).bfloat16().requires_grad_()
+    w = (0.1 * torch.randn(V, d, device=dev())).bfloat16().requires_grad_()
+    tgt = torch.randint(0, V, (n,), device=dev())
+    tgt[:5] = -1
+    wts = torch.randn(n, device=dev())
+    wts[10:20] = 0
+    loss = F.lm_head_ce(x, w, tgt, chunk_rows=128, weights=wts)
+    loss.backward()
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    rows = ref.cross_entropy(ref.linear(xr, wr), tgt, reduction="none")
+    lossr = (rows * wts).sum() / (tgt >= 0).sum()
+    lossr.backward()
+    assert abs(loss.item() - lossr.item()) < 2e-2 * max(abs(lossr.item()), 0.1)
+    assert rel_err(x.grad, xr.grad) < 3e-2
+    assert rel_err(w.grad, wr.grad) < 3e-2
+
+
 def test_adamw_and_gradnorm():
     torch.manual_seed(11)
     n = 100003
