@@ -264,3 +264,56 @@ def test_trainer3d_matches_single_process(tp, pp, sched):
     assert set(got) == set(ref_state)
     for k, v in ref_state.items():
         assert torch.allclose(got[k], v.detach().reshape(-1), atol=2e-4), k
+
+
+def _trainer_ep_worker(rank, world):
+    from brain_b200.models.config import MoeConfig
+    from brain_b200.models.moe import MoeModel
+    from brain_b200.parallel.ep import ExpertParallel
+    from brain_b200.parallel.trainer_ep import TrainerEP, is_expert_param
+    cfg = MoeConfig(vocab=64, block_size=16, n_layers=2, d_model=32, n_heads=4, n_kv_heads=2, head_dim=8, n_experts=4,
+                    top_k=2, d_ff=16, aux_coef=0.0, z_coef=0.0, tie_embeddings=True)
+    ep = ExpertParallel(impl="nccl")
+    model = MoeModel(cfg, ep=ep).init_weights(7)
+    tr = TrainerEP(model, "cpu", betas=(0.9, 0.95), weight_decay=0.1, grad_clip=1.0)
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, 64, (4, 16), generator=g, dtype=torch.int32)
+    tgts = torch.randint(0, 64, (4, 16), generator=g)
+    mine = slice(2 * rank, 2 * rank + 2)
+    losses = []
+    for _ in range(2):
+        losses.append(float(tr.train_step(toks[mine], tgts[mine], 1e-2, global_count=4 * 16)))
+    state = {n: p.detach().clone() for n, p in model.named_parameters()}
+    return {"losses": losses, "norm": float(tr.last_grad_norm), "state": state,
+            "e_first": model.blocks[0].moe.e_first, "e_local": model.blocks[0].moe.e_local}
+
+
+def test_trainer_ep_two_gloo_ranks_match_single_process():
+    """Expert-parallel training (experts split over 2 CPU ranks, each rank its own sequences)
+    reproduces single-process training on all sequences: summed losses, global gradient norm,
+    shared weights and each rank's expert slice after two optimiser steps."""
+    from brain_b200.engine import Trainer
+    from brain_b200.models.config import MoeConfig
+    from brain_b200.models.moe import MoeModel
+    from brain_b200.parallel.trainer_ep import is_expert_param
+    res = run_ranks(_trainer_ep_worker, 2)
+    cfg = MoeConfig(vocab=64, block_size=16, n_layers=2, d_model=32, n_heads=4, n_kv_heads=2, head_dim=8, n_experts=4,
+                    top_k=2, d_ff=16, aux_coef=0.0, z_coef=0.0, tie_embeddings=True)
+    full = MoeModel(cfg).init_weights(7)
+    tr = Trainer(full, device="cpu", betas=(0.9, 0.95), weight_decay=0.1, grad_clip=1.0)
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, 64, (4, 16), generator=g, dtype=torch.int32)
+    tgts = torch.randint(0, 64, (4, 16), generator=g)
+    want = [float(tr.train_step(toks, tgts, 1e-2, micro_batch=2)) for _ in range(2)]
+    got = [res[0]["losses"][i] + res[1]["losses"][i] for i in range(2)]
+    assert got == pytest.approx(want, rel=2e-4)
+    assert res[0]["norm"] == pytest.approx(float(tr.opt.last_grad_norm), rel=2e-3)
+    assert res[1]["norm"] == pytest.approx(res[0]["norm"], rel=1e-6)
+    ref_state = dict(full.named_parameters())
+    for r in res:
+        lo, n = r["e_first"], r["e_local"]
+        for k, v in r["state"].items():
+            want_t = ref_state[k].detach()
+            if is_expert_param(k):
+                want_t = want_t[lo:lo + n]
+            assert torch.allclose(v, want_t, atol=2e-4), (k, float((v - want_t).abs().max()))
