@@ -35,7 +35,6 @@ class Trainer3D:
         from ..models.qwen3 import Qwen3
         from .tp import TensorParallel
         model_cls = model_cls or Qwen3
-        assert grid.dp == 1, "the data axis of the 3-D trainer is not wired yet: use ZeroDP for pure data parallelism"
         self.grid = grid
         self.device = torch.device(device)
         cuda = self.device.type == "cuda"
@@ -130,22 +129,30 @@ class Trainer3D:
         t = total.float().reshape(1)
         if dist.get_world_size() > 1:
             dist.all_reduce(t)
-        return t
+        # after the data-parallel reduction every replica holds the same gradients: count them once
+        return t / float(self.grid.dp)
 
     # ------------------------------------------------------------------ step
     def train_step(self, micro_tokens: List[torch.Tensor], micro_targets: List[torch.Tensor], lr: float,
                    global_count: Optional[int] = None):
-        """One optimiser step over the micro-batches (every rank passes the same lists).  Returns
-        the mean loss (a tensor on the last stage's first tensor-parallel rank's device; all ranks
+        """One optimiser step over the micro-batches (every rank passes the same lists; data-parallel
+        replica r of ``dp`` takes micro-batches r, r+dp, ...).  Returns the mean loss (all ranks
         receive the same value)."""
         if global_count is None:
             global_count = sum(int((t >= 0).sum()) for t in micro_targets)
+        dp = self.grid.dp
+        if dp > 1:
+            assert len(micro_tokens) % dp == 0, "the number of micro-batches must be a multiple of the dp degree"
+            micro_tokens = micro_tokens[self.pgs.dp_coord::dp]
+            micro_targets = micro_targets[self.pgs.dp_coord::dp]
         self.store.zero_grads()
         loss = self.pipe.forward_backward(micro_tokens, micro_targets, 1.0 / max(global_count, 1))
         if self.device.type == "cpu":
             self.store.collect_autograd_grads()
         self.pipe.sync_tied_embeddings()
         self._sync_replicated()
+        if dp > 1:
+            dist.all_reduce(self.store.grads[: self.store.n_train], group=self.pgs.group("dp"))
         ss = self._global_sumsq() if self.clip else None
         self.opt.step(lr, self.wd, self.clip, sumsq=ss)
         if ss is not None:
