@@ -67,8 +67,10 @@ def make_app(provider: str, ex: Executor, key: str) -> web.Application:
     app[SURFACE_KEY] = surface
 
     async def stats(_req):
-        return web.json_response({"executor": ex.stats(), "accounting": surface.acct.snapshot(),
-                                  "in_flight": ex.in_flight()})
+        from ..utils.stats import snapshot
+        snap = snapshot(ex, {provider: surface})
+        snap.update({"accounting": surface.acct.snapshot(), "in_flight": ex.in_flight()})
+        return web.json_response(snap)
     app.router.add_get("/stats", stats)
     return app
 

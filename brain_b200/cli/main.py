@@ -44,7 +44,8 @@ infrastructure
   devices                                         list compute devices
   flops --model qwen|gpt [--weights F --batch B --block T --train --i8 --stages N --run]
   gradcheck [--model gpt|qwen|qwen2|qwen_lora|moe|qwen_moe|all] [--dirs N]
-  perf list | run <scenario> [...] | compare A B | gate A B [--tolerance X]
+  perf list | run <scenario> [...] | compare A B | gate A B [--tolerance X] | faults [NAME…]
+  top --url http://HOST:PORT (--key K | --api-keys FILE) [--interval S --once --json]
   bench [--gpus N --steps K --warmup W]           the training benchmark (bench.py)
   federated split|verify|merge|assemble|train-expert ...
   caps                                            capability manifests of the servable models
@@ -93,7 +94,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     trace.event("cli", 3, "command", argv=" ".join(argv), device=device)
     verb, rest = argv[0], argv[1:]
     infra = {"data": _data, "devices": _devices, "flops": _flops, "gradcheck": _gradcheck, "perf": _perf,
-             "bench": _bench, "federated": _federated, "caps": _caps, "serve": _serve}
+             "bench": _bench, "federated": _federated, "caps": _caps, "serve": _serve, "top": _top}
     if verb in infra and not (rest and archs.by_id(rest[0]) and verb == "serve"):
         return infra[verb](rest, device) or 0
     r = resolve(argv)
@@ -105,6 +106,11 @@ def main(argv: Optional[List[str]] = None) -> int:
         return _quantize(r.rest, device) or 0
     print(f"unknown command {r.word!r}; try `brain help`", file=sys.stderr)
     return 2
+
+
+def _top(rest: List[str], device: str) -> int:
+    from .top import run_top
+    return run_top(rest)
 
 
 def _dispatch_arch(arch_id: str, rest: List[str], device: str) -> int:

@@ -159,7 +159,7 @@ class QwenEngine:
         #: one Python wrapper per kernel (CUDA only; same kernels, same results)
         self.native = None
         if native is None:
-            native = os.environ.get("BRAIN_SERVE_NATIVE", "0") == "1"
+            native = os.environ.get("BRAIN_SERVE_NATIVE", "1") == "1"
         if native and self.cuda:
             from .native import NativeForward
             tp_ok = self.tp is None or self.tp_world == 1 or \

@@ -353,3 +353,21 @@ def test_brain_py_jsonl_stdio():
         with pytest.raises(BrainError):
             b.run("brain/none", "generate", {"prompt": "x"})
         assert len(b.embed("abc")) == 8
+
+
+def test_stats_snapshot_and_brain_top(srv, capsys):
+    """GET /stats carries the whole snapshot (models with their actions, executor, accounting), is
+    refused without a key, and ``brain top --once`` renders it."""
+    from brain_b200.cli.main import main
+    code, _, body = call(srv, "openai", "/stats")
+    assert code == 200
+    snap = json.loads(body)
+    assert {"ts", "accelerators", "models", "executor", "requests", "connections", "accounting"} <= set(snap)
+    assert snap["models"][0]["id"] == MockResident.id and "generate" in snap["models"][0]["actions"]
+    assert call(srv, "openai", "/stats", key=None)[0] == 401
+    url = f"http://127.0.0.1:{srv.bound['openai']}"
+    assert main(["top", "--url", url, "--key", srv.keys["openai"], "--once"]) == 0
+    out = capsys.readouterr().out
+    assert "brain top" in out and MockResident.id in out and "connections" in out
+    assert main(["top", "--url", url, "--key", "sk-brain-" + "0" * 32, "--once"]) == 1
+    assert main(["top", "--url", url]) == 2
