@@ -8,6 +8,8 @@ import json
 import os
 from typing import Dict, Optional
 
+import torch
+
 from ..models.config import QwenConfig
 from . import st
 from .card import ModelCard
@@ -66,6 +68,18 @@ def _shard_index(hf_dir: str) -> Dict[str, str]:
         return {n: single for n in r.names()}
 
 
+def dequant_block(raw: torch.Tensor, scale_inv: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """Block-wise FP8 checkpoint weight -> fp32: ``raw`` [rows, cols] are the decoded E4M3 values and
+    ``scale_inv`` [ceil(rows/block), ceil(cols/block)] the per-block multipliers (reference:
+    crates/model/src/fp8.rs:29-76).  A shape mismatch is an error, never a silent broadcast."""
+    rows, cols = raw.shape
+    want = (-(-rows // block), -(-cols // block))
+    if tuple(scale_inv.shape) != want:
+        raise ValueError(f"scale grid {tuple(scale_inv.shape)} does not match weight {rows}x{cols} at block {block}")
+    s = scale_inv.float().repeat_interleave(block, 0)[:rows].repeat_interleave(block, 1)[:, :cols]
+    return raw.float() * s
+
+
 def import_qwen(hf_dir: str, out: str, block: Optional[int] = None, dtype: str = "F32",
                 model_id: Optional[str] = None) -> QwenConfig:
     with open(os.path.join(hf_dir, "config.json")) as f:
@@ -92,6 +106,17 @@ def import_qwen(hf_dir: str, out: str, block: Optional[int] = None, dtype: str =
             if r is None:
                 r = readers[path] = st.WeightReader(path)
             t = r.read(src)
+            if r.dtype(src) == "F8_E4M3":
+                # block-128 FP8 export: the multipliers ship as <name>_scale_inv (bf16)
+                sname = src + "_scale_inv"
+                spath = where.get(sname)
+                if spath is None:
+                    raise KeyError(f"{hf_dir}: {src} is FP8 but {sname} is missing")
+                rs = readers.get(spath)
+                if rs is None:
+                    rs = readers[spath] = st.WeightReader(spath)
+                blk = int((hf.get("quantization_config") or {}).get("weight_block_size", [128, 128])[0])
+                t = dequant_block(t, rs.read(sname), blk)
             if t.numel() != numel:
                 raise ValueError(f"{src}: {t.numel()} elements, config expects {numel}")
             w.write(name, t)

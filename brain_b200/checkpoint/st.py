@@ -31,7 +31,7 @@ _host.register({
 })
 
 _DT = {"F32": 0, "F16": 1, "BF16": 2}
-_ES = {"F32": 4, "F16": 2, "BF16": 2, "I8": 1, "U8": 1, "I32": 4, "U32": 4, "I64": 8, "F64": 8}
+_ES = {"F32": 4, "F16": 2, "BF16": 2, "I8": 1, "U8": 1, "I32": 4, "U32": 4, "I64": 8, "F64": 8, "F8_E4M3": 1}
 _TORCH = {"I8": torch.int8, "U8": torch.uint8, "I32": torch.int32, "I64": torch.int64,
           "F64": torch.float64, "U32": torch.int32}
 
@@ -100,6 +100,13 @@ class WeightReader:
             if rc != 0:
                 raise IOError(f"read of {name} failed ({rc})")
             return out.view(shape)
+        if dt == "F8_E4M3":
+            # raw (unscaled) fp8 values as fp32; block scales are applied by the importer
+            out = torch.empty(numel, dtype=torch.uint8)
+            rc = _host.lib().bbh_st_read_raw(self._h, b, en - b, out.data_ptr())
+            if rc != 0:
+                raise IOError(f"read of {name} failed ({rc})")
+            return out.view(torch.float8_e4m3fn).float().view(shape)
         raise ValueError(f"{name}: unsupported dtype {dt}")
 
     def config(self) -> Optional[dict]:

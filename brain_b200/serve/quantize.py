@@ -106,3 +106,31 @@ def load_quantized(path: str, device="cpu", dtype=None):
     if device != "cpu" or dtype is not None:
         model = model.to(device=device, dtype=dtype)
     return model
+
+
+# ------------------------------------------------------------------------------------ 4-bit storage
+def quantize_weight_q4(w: torch.Tensor):
+    """Per-output-row symmetric 4-bit storage: ``w`` [n, k] (k % 8 == 0) -> (int32 words [n, k/8]
+    holding 8 two's-complement nibbles each, element b of a group in bits 4b..4b+3; fp32 row scales
+    ``max(|row|, 1e-8) / 7``), values clamped to ±7 (reference: crates/model/src/int4.rs:46-73).
+    A storage format here: weights are dequantised (to bf16 / int8) when loaded."""
+    n, k = w.shape
+    if k % 8:
+        raise ValueError(f"q4 K must be a multiple of 8 (got {k})")
+    wf = w.detach().float()
+    sw = wf.abs().amax(dim=1).clamp_min(1e-8) / 7.0
+    q = torch.clamp(torch.round(wf / sw[:, None]), -7, 7).to(torch.int64) & 0xF
+    shifts = (4 * torch.arange(8, dtype=torch.int64))[None, None, :]
+    words = (q.view(n, k // 8, 8) << shifts).sum(dim=-1)
+    words = torch.where(words >= (1 << 31), words - (1 << 32), words)      # as signed 32-bit
+    return words.to(torch.int32), sw
+
+
+def dequantize_weight_q4(words: torch.Tensor, sw: torch.Tensor) -> torch.Tensor:
+    """Inverse of :func:`quantize_weight_q4`; every nibble is SIGN-extended (bit 3 set = negative)."""
+    n, kg = words.shape
+    u = words.to(torch.int64) & 0xFFFFFFFF
+    shifts = (4 * torch.arange(8, dtype=torch.int64))[None, None, :]
+    nib = (u[:, :, None] >> shifts) & 0xF
+    nib = torch.where(nib >= 8, nib - 16, nib)
+    return nib.reshape(n, kg * 8).float() * sw.float()[:, None]

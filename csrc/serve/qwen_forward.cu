@@ -219,7 +219,10 @@ BB_API int bb_serve_post_attn(const BbServeCfg* c, int li, const BbServeWork* w,
 BB_API int bb_serve_finish(const BbServeCfg* c, const BbServeWork* w, const void* norm_w, void* hn,
                            int n, BbServeState* s, void* stream) {
   if (!c || !w || !s || !s->delta || n <= 0 || n > w->rows) return BB_EARG;
-  return bb_rmsnorm_fwd(s->delta, s->x, norm_w, hn, nullptr, w->rstd, n, c->d_model, c->eps, stream);
+  // the sum x + delta is also written out (to the free residual buffer): the kernel then normalises
+  // the bf16-rounded sum, exactly as every other residual step of the stack does
+  void* xn = (s->x == w->xa) ? w->xb : w->xa;
+  return bb_rmsnorm_fwd(s->delta, s->x, norm_w, hn, xn, w->rstd, n, c->d_model, c->eps, stream);
 }
 
 // One decode step for n sequences (one new token each): embedding, every layer with split-KV paged

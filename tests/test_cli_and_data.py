@@ -481,3 +481,79 @@ def test_weighted_loss_and_fit(tmp_path):
                                                 n_kv_heads=1, head_dim=8, d_ff=32))
     l0, l1 = fit(d, build, o, None, log=lambda s: None)
     assert l0 == l0 and l1 == l1
+
+
+def test_q4_storage_and_fp8_block_import(tmp_path):
+    """4-bit nibble packing round-trips with sign extension; an FP8-E4M3 export with 128x128 block
+    multipliers imports to the same weights as its bf16 original (within fp8 resolution)."""
+    import json
+    import torch
+    from brain_b200.checkpoint import st
+    from brain_b200.checkpoint.hf_import import dequant_block, hf_name, import_qwen
+    from brain_b200.models.config import QwenConfig
+    from brain_b200.serve.quantize import dequantize_weight_q4, quantize_weight_q4
+    w = torch.tensor([[7.0, -7.0, 1.0, -1.0, 0.0, 3.5, -3.5, 6.9] * 2, [0.1] * 8 + [-0.2] * 8])
+    words, sw = quantize_weight_q4(w)
+    assert words.shape == (2, 2) and words.dtype == torch.int32
+    back = dequantize_weight_q4(words, sw)
+    assert torch.allclose(back[0, :4], torch.tensor([7.0, -7.0, 1.0, -1.0]))       # negatives survive
+    assert (back - w).abs().max() <= sw.max() / 2 + 1e-6
+    with pytest.raises(ValueError):
+        quantize_weight_q4(torch.zeros(2, 12))
+    raw = torch.randn(200, 300)
+    sc = torch.rand(2, 3) + 0.5
+    full = dequant_block(raw, sc, 128)
+    assert torch.allclose(full[130, 260], raw[130, 260] * sc[1, 2]) and torch.allclose(full[0, 0], raw[0, 0] * sc[0, 0])
+    with pytest.raises(ValueError):
+        dequant_block(raw, torch.ones(2, 2), 128)
+
+    # a tiny HF-layout export whose 2-D projection weights are fp8 + *_scale_inv
+    cfg = QwenConfig(vocab=32, block_size=16, n_layers=1, d_model=128, n_heads=2, n_kv_heads=1, head_dim=64, d_ff=256,
+                     tie_embeddings=True)
+    g = torch.Generator().manual_seed(0)
+    hf_dir = tmp_path / "hf"
+    hf_dir.mkdir()
+    tensors, specs = {}, []
+    shapes = cfg.param_shapes() if hasattr(cfg, "param_shapes") else None
+    for name, numel in cfg.param_list():
+        src = hf_name(name)
+        if src.endswith("proj.weight"):
+            rows = {"q_proj": 128, "k_proj": 64, "v_proj": 64, "o_proj": 128, "gate_proj": 256, "up_proj": 256,
+                    "down_proj": 128}[src.split(".")[-2]]
+            wt = torch.randn(rows, numel // rows, generator=g) * 0.05
+            s_inv = wt.abs().amax() / 400.0 * torch.ones(-(-rows // 128), -(-(numel // rows) // 128))
+            q8 = (wt / s_inv[0, 0]).to(torch.float8_e4m3fn)
+            tensors[src] = ("F8_E4M3", q8.view(torch.uint8), (rows, numel // rows))
+            tensors[src + "_scale_inv"] = ("BF16", s_inv, tuple(s_inv.shape))
+            tensors["_want_" + name] = q8.float() * s_inv[0, 0].bfloat16().float()
+        else:
+            t = torch.randn(numel, generator=g) * 0.05
+            tensors[src] = ("BF16", t, (numel,))
+            tensors["_want_" + name] = t.bfloat16().float()
+    names = [k for k in tensors if not k.startswith("_want_")]
+    wtr = st.StWriter(str(hf_dir / "model.safetensors"), [(n, tensors[n][2], "U8" if tensors[n][0] == "F8_E4M3" else "BF16")
+                                                          for n in names], {"format": "pt"}, "BF16")
+    for n in names:
+        wtr.write(n, tensors[n][1])
+    wtr.close()
+    # the writer stores raw bytes under U8; patch the header dtype to F8_E4M3 the way an fp8 export labels it
+    path = str(hf_dir / "model.safetensors")
+    blob = open(path, "rb").read()
+    hlen = int.from_bytes(blob[:8], "little")
+    header = json.loads(blob[8:8 + hlen])
+    for n in names:
+        if tensors[n][0] == "F8_E4M3":
+            header[n]["dtype"] = "F8_E4M3"
+    hb = json.dumps(header, separators=(",", ":")).encode()
+    hb += b" " * (-len(hb) % 8)
+    open(path, "wb").write(len(hb).to_bytes(8, "little") + hb + blob[8 + hlen:])
+    (hf_dir / "config.json").write_text(json.dumps({
+        "model_type": "qwen3", "vocab_size": 32, "hidden_size": 128, "num_hidden_layers": 1, "num_attention_heads": 2,
+        "num_key_value_heads": 1, "head_dim": 64, "intermediate_size": 256, "max_position_embeddings": 16,
+        "rms_norm_eps": 1e-6, "rope_theta": 1e6, "tie_word_embeddings": True,
+        "quantization_config": {"quant_method": "fp8", "weight_block_size": [128, 128]}}))
+    out = str(tmp_path / "q.safetensors")
+    import_qwen(str(hf_dir), out)
+    got, _, _ = st.load(out)
+    for name, _ in cfg.param_list():
+        assert torch.allclose(got[name].reshape(-1), tensors["_want_" + name].reshape(-1), atol=1e-6), name
