@@ -310,9 +310,11 @@ def test_router_topk(E, k):
 
 def test_quant_and_argmax():
     torch.manual_seed(13)
-    x = torch.randn(100, 520, device=dev()).bfloat16()
-    q, s = F.quant_rows(x)
-    qr, sr = ref.quant_rows(x)
-    assert torch.allclose(s, sr, rtol=1e-6) and (q.int() - qr.int()).abs().max() <= 1
+    for k in (520, 4096, 516):          # 16-byte vector path (k % 8 == 0) and the scalar fallback
+        x = torch.randn(100, k, device=dev()).bfloat16()
+        q, s = F.quant_rows(x)
+        qr, sr = ref.quant_rows(x)
+        assert torch.allclose(s, sr, rtol=1e-6) and (q.int() - qr.int()).abs().max() <= 1
+        assert ((q.int() - qr.int()).abs() > 0).float().mean() < 1e-3
     lg = torch.randn(7, 151936, device=dev()).bfloat16()
     assert (F.argmax_rows(lg).long() == lg.float().argmax(-1)).all()
