@@ -117,7 +117,9 @@ class TensorParallel:
         """Symmetric staging + two result buffers of the two-shot all-reduce, holding >= ``n``
         elements (collective: every rank calls it with the same ``n``)."""
         if self._ar2 is None or self._ar2["cap"] < n:
-            cap = max(n, 1 << 22)
+            # grow by powers of two: the arena never frees, so a capacity that crept up with every
+            # slightly longer prompt would eat it
+            cap = max(1 << (int(n) - 1).bit_length(), 1 << 22)
             stage = self.arena.alloc(cap, torch.bfloat16)
             res = [self.arena.alloc(cap, torch.bfloat16) for _ in range(2)]
             self._ar2 = {"cap": cap, "stage": stage, "res": res,
