@@ -28,7 +28,7 @@ class Layer(C.Structure):
 class Cfg(C.Structure):
     _fields_ = [("d_model", C.c_int), ("hq", C.c_int), ("hk", C.c_int), ("hd", C.c_int), ("ff", C.c_int),
                 ("block_size", C.c_int), ("kv_int8", C.c_int), ("n_layers", C.c_int),
-                ("eps", C.c_float), ("tp_world", C.c_int), ("tp_rank", C.c_int), ("pad_", C.c_int),
+                ("eps", C.c_float), ("tp_world", C.c_int), ("tp_rank", C.c_int), ("fuse_quant", C.c_int),
                 ("cos_t", P), ("sin_t", P), ("layers", P),
                 ("stage_ptrs", P), ("res_ptrs", P * 2), ("sig_ptrs", P), ("res", P * 2),
                 ("epoch_dev", P), ("counters", P), ("wait_seconds", C.c_double), ("ar_cap", C.c_long)]
@@ -111,6 +111,7 @@ class NativeForward:
         c.cos_t, c.sin_t = _ptr(eng.cos), _ptr(eng.sin)
         c.layers = C.cast(self._layers, P)
         c.tp_world, c.tp_rank = eng.tp_world, eng.tp_rank
+        c.fuse_quant = 1     # W8A8: norm / SwiGLU kernels that write int8 rows + scales (same values)
         self.state = State()
         self._scratch: Dict[tuple, Scratch] = {}
         for name in ("bb_serve_begin", "bb_serve_pre_attn", "bb_serve_post_attn", "bb_serve_finish",

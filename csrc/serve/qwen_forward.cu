@@ -50,6 +50,9 @@ int bb_paged_decode_i8(const void* q, int ldq, const void* kc, const void* vc, c
                        void* out, int ldo, float* part_o, float* part_ml, int B, int hq, int hk,
                        int hd, int bs, int splits, float scale, void* stream);
 int bb_swiglu_fwd(const void* gu, void* h, long rows, int ff, void* stream);
+int bb_rmsnorm_q8(const void* x, const void* res, const void* w, void* h_out, void* q, float* scale,
+                  int rows, int d, float eps, void* stream);
+int bb_swiglu_q8(const void* gu, void* q, float* scale, int rows, int ff, void* stream);
 int bb_embed_fwd(const int* tok, const void* emb, const void* pos_emb, int T, void* out, long n_tok,
                  int d, int vocab, void* stream);
 int bb_tp_allreduce2(const uint64_t* stage_ptrs, const uint64_t* result_ptrs,
@@ -78,7 +81,8 @@ struct BbServeLayer {
 struct BbServeCfg {
   int d_model, hq, hk, hd, ff, block_size, kv_int8, n_layers;
   float eps;
-  int tp_world, tp_rank, pad_;
+  int tp_world, tp_rank;
+  int fuse_quant;            // W8A8: norms and SwiGLU emit int8 rows + scales directly
   const float *cos_t, *sin_t;
   const BbServeLayer* layers;
   const uint64_t* stage_ptrs;
@@ -124,6 +128,26 @@ namespace {
     if (rc_ != 0) return rc_; \
   } while (0)
 
+int linear(const BbLin& L, const void* x, int ldx, void* y, int rows, const BbServeWork& w, void* stream);
+
+// y = (w.xq * w.sx) . W^T for rows already quantised into the scratch.
+int linear_q8(const BbLin& L, void* y, int rows, const BbServeWork& w, void* stream) {
+  return bb_gemm_i8(w.xq, L.w, y, w.sx, L.scale, rows, L.n, L.k, L.k, L.k, L.n, 0, 0, stream);
+}
+
+// h = RMSNorm(x [+ res]) * g followed by the projection L; with W8A8 and fusion on, the norm emits
+// the int8 rows itself (w.h is then not written).
+int norm_linear(const BbServeCfg& c, const BbLin& L, const void* x, const void* res, const void* g,
+                void* h_out, void* y, int rows, const BbServeWork& w, void* stream) {
+  if (c.fuse_quant && L.scale && !L.bias) {
+    const int rc = bb_rmsnorm_q8(x, res, g, h_out, w.xq, w.sx, rows, c.d_model, c.eps, stream);
+    if (rc == BB_OK) return linear_q8(L, y, rows, w, stream);
+    if (rc != BB_ESIZE) return rc;
+  }
+  BB_TRY(bb_rmsnorm_fwd(x, res, g, w.h, h_out, w.rstd, rows, c.d_model, c.eps, stream));
+  return linear(L, w.h, c.d_model, y, rows, w, stream);
+}
+
 int linear(const BbLin& L, const void* x, int ldx, void* y, int rows, const BbServeWork& w,
            void* stream) {
   if (L.scale) {
@@ -156,13 +180,12 @@ int pre_attn(const BbServeCfg& c, int li, const BbServeWork& w, const int* pos, 
   const int d = c.d_model, qkv_ld = (c.hq + 2 * c.hk) * c.hd, qk_ld = (c.hq + c.hk) * c.hd;
   if (s.delta) {
     void* xn = (s.x == w.xa) ? w.xb : w.xa;
-    BB_TRY(bb_rmsnorm_fwd(s.delta, s.x, L.ln1, w.h, xn, w.rstd, n, d, c.eps, stream));
+    BB_TRY(norm_linear(c, L.qkv, s.delta, s.x, L.ln1, xn, w.qkv, n, w, stream));
     s.x = xn;
     s.delta = nullptr;
   } else {
-    BB_TRY(bb_rmsnorm_fwd(s.x, nullptr, L.ln1, w.h, nullptr, w.rstd, n, d, c.eps, stream));
+    BB_TRY(norm_linear(c, L.qkv, s.x, nullptr, L.ln1, nullptr, w.qkv, n, w, stream));
   }
-  BB_TRY(linear(L.qkv, w.h, d, w.qkv, n, w, stream));
   BB_TRY(bb_qknorm_rope_fwd(w.qkv, qkv_ld, L.q_norm, L.k_norm, c.cos_t, c.sin_t, pos, w.qk, qk_ld,
                             L.q_norm ? w.rstd : nullptr, n, c.hq, c.hk, c.hd, c.eps, stream));
   const char* k = static_cast<const char*>(w.qk) + (size_t)c.hq * c.hd * 2;
@@ -181,11 +204,18 @@ int post_attn(const BbServeCfg& c, int li, const BbServeWork& w, int n, BbServeS
   BB_TRY(linear(L.wo, w.o, c.hq * c.hd, w.proj, n, w, stream));
   BB_TRY(all_reduce(c, s, w.proj, (long)n * d, &a, stream));
   void* xn = (s.x == w.xa) ? w.xb : w.xa;
-  BB_TRY(bb_rmsnorm_fwd(a, s.x, L.ln2, w.h, xn, w.rstd, n, d, c.eps, stream));
+  BB_TRY(norm_linear(c, L.gate_up, a, s.x, L.ln2, xn, w.gu, n, w, stream));
   s.x = xn;
-  BB_TRY(linear(L.gate_up, w.h, d, w.gu, n, w, stream));
-  BB_TRY(bb_swiglu_fwd(w.gu, w.act, n, c.ff, stream));
-  BB_TRY(linear(L.down, w.act, c.ff, w.mlp, n, w, stream));
+  int rq = BB_ESIZE;
+  if (c.fuse_quant && L.down.scale && !L.down.bias) {
+    rq = bb_swiglu_q8(w.gu, w.xq, w.sx, n, c.ff, stream);
+    if (rq == BB_OK) BB_TRY(linear_q8(L.down, w.mlp, n, w, stream));
+    else if (rq != BB_ESIZE) return rq;
+  }
+  if (rq != BB_OK) {
+    BB_TRY(bb_swiglu_fwd(w.gu, w.act, n, c.ff, stream));
+    BB_TRY(linear(L.down, w.act, c.ff, w.mlp, n, w, stream));
+  }
   void* m = nullptr;
   BB_TRY(all_reduce(c, s, w.mlp, (long)n * d, &m, stream));
   s.delta = m;

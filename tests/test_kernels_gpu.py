@@ -263,6 +263,38 @@ def test_lm_head_ce_weighted():
     assert rel_err(w.grad, wr.grad) < 3e-2
 
 
+@pytest.mark.parametrize("rows,d", [(37, 1024), (300, 4096), (5, 5120), (64, 768)])
+def test_fused_norm_and_swiglu_quant_are_bit_identical_to_the_unfused_pairs(rows, d):
+    """rmsnorm_q8 == quant_rows(rmsnorm(...)) and swiglu_q8 == quant_rows(swiglu(...)), bit for bit,
+    including the residual sum the norm writes out."""
+    torch.manual_seed(21)
+    x = torch.randn(rows, d, device=dev()).bfloat16()
+    r = torch.randn(rows, d, device=dev()).bfloat16()
+    w = (1 + 0.1 * torch.randn(d, device=dev())).bfloat16()
+    s = _cuda.stream_ptr()
+    for res in (None, r):
+        if res is None:
+            y = F.rmsnorm(x, w, 1e-6)
+            h = None
+        else:
+            y, h = F.rmsnorm(x, w, 1e-6, residual=res)
+        q_want, s_want = F.quant_rows(y)
+        q = torch.empty(rows, d, device=dev(), dtype=torch.int8)
+        sc = torch.empty(rows, device=dev())
+        h_out = torch.empty_like(x) if res is not None else None
+        _cuda.call("rmsnorm_q8", x, res, w, h_out, q, sc, rows, d, 1e-6, s)
+        assert torch.equal(q, q_want) and torch.equal(sc, s_want)
+        if res is not None:
+            assert torch.equal(h_out, h)
+    gu = torch.randn(rows, 2 * d, device=dev()).bfloat16()
+    q_want, s_want = F.quant_rows(F.swiglu(gu))
+    q = torch.empty(rows, d, device=dev(), dtype=torch.int8)
+    sc = torch.empty(rows, device=dev())
+    _cuda.call("swiglu_q8", gu, q, sc, rows, d, s)
+    assert torch.equal(q, q_want) and torch.equal(sc, s_want)
+    _cuda.check_error()
+
+
 def test_adamw_and_gradnorm():
     torch.manual_seed(11)
     n = 100003
