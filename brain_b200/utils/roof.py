@@ -90,7 +90,25 @@ def probe(budget_s: Optional[float] = None) -> Roof:
     sm = torch.ones(M, device=dev)
     t = _time_events(lambda: F.gemm_i8(xq, wq, sm, sm), 8, budget / 3)
     i8 = 2.0 * M ** 3 / t / 1e12
-    return Roof(hbm, bf16, bf16 * 0.85, i8, source="probe", device=torch.cuda.get_device_name(dev))
+    return Roof(hbm, bf16, bf16 * 0.85, i8, probe_nvlink(budget / 3) or NVLINK_P2P_GBS_DEFAULT, source="probe",
+                device=torch.cuda.get_device_name(dev))
+
+
+def probe_nvlink(budget_s: float = 2.0) -> Optional[float]:
+    """Peer-copy bandwidth (GB/s, one direction) from the current device to the next visible one,
+    or None with fewer than two peer-accessible GPUs in this process."""
+    if torch.cuda.device_count() < 2:
+        return None
+    src = torch.cuda.current_device()
+    dst = (src + 1) % torch.cuda.device_count()
+    if not torch.cuda.can_device_access_peer(src, dst):
+        return None
+    n = 256 << 20
+    a = torch.empty(n, device=torch.device("cuda", src), dtype=torch.uint8)
+    b = torch.empty(n, device=torch.device("cuda", dst), dtype=torch.uint8)
+    t = _time_events(lambda: b.copy_(a, non_blocking=True), 8, budget_s)
+    torch.cuda.synchronize(dst)
+    return n / t / 1e9
 
 
 def measure(refresh: bool = False) -> Roof:
