@@ -524,6 +524,19 @@ def argmax_rows(logits):
     return out
 
 
+def topk_rows(logits, k: int):
+    """The k largest logits of every row, descending (lowest index first among equals):
+    (int32 indices [rows, k], fp32 values [rows, k])."""
+    lg = logits.reshape(-1, logits.shape[-1])
+    if not lg.is_cuda or lg.dtype != torch.bfloat16:
+        vals, idx = torch.topk(lg.float(), k, dim=-1)
+        return idx.to(torch.int32), vals
+    idx = torch.empty(lg.shape[0], k, device=lg.device, dtype=torch.int32)
+    vals = torch.empty(lg.shape[0], k, device=lg.device, dtype=torch.float32)
+    call("topk_rows", lg, L(lg.stride(0)), lg.shape[0], lg.shape[1], int(k), idx, vals, stream_ptr())
+    return idx, vals
+
+
 def router_topk(logits, k, norm_topk_prob=True, scale=1.0, counts=None):
     """(probs, topk_idx, topk_w, lse) — see ``reference.router_topk``; CUDA path is one warp per token."""
     if not logits.is_cuda:

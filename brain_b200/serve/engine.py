@@ -320,7 +320,7 @@ class QwenEngine:
         if greedy:
             return F.argmax_rows(logits), None
         k = min(self.topk_capacity, logits.shape[-1])
-        vals, idx = torch.topk(logits.float(), k, dim=-1)
+        idx, vals = F.topk_rows(logits, k)
         return idx[:, 0].to(torch.int32), (idx, vals)
 
     def _prefill_forward(self, tokens: np.ndarray, start: int, block_table: np.ndarray):

@@ -186,6 +186,73 @@ __global__ void argmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, lon
   }
 }
 
+// Top-K per row by K rounds of "largest remaining" (value descending, lowest index first on ties —
+// the order of crates/kernels/wgsl/topk_extract_step.wgsl).  One block per row; every round is one
+// pass over the row (it stays in L2), "remaining" = lexicographically after the previous pick.
+__global__ void topk_rows_kernel(const __nv_bfloat16* __restrict__ logits, long ld, int V, int K,
+                                 int* __restrict__ out_idx, float* __restrict__ out_val) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ float s_last_v;
+  __shared__ int s_last_i;
+  const __nv_bfloat16* row = logits + (size_t)blockIdx.x * ld;
+  if (threadIdx.x == 0) {
+    s_last_v = INFINITY;
+    s_last_i = -1;
+  }
+  __syncthreads();
+  for (int k = 0; k < K; ++k) {
+    const float lv = s_last_v;
+    const int li = s_last_i;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float f = __bfloat162float(row[i]);
+      const bool remaining = f < lv || (f == lv && i > li);
+      if (remaining && (f > best || (f == best && i < bi))) {
+        best = f;
+        bi = i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float b2 = __shfl_xor_sync(0xffffffffu, best, o);
+      const int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (b2 > best || (b2 == best && i2 < bi)) {
+        best = b2;
+        bi = i2;
+      }
+    }
+    if ((threadIdx.x & 31) == 0) {
+      sv[threadIdx.x >> 5] = best;
+      si[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const int nw = blockDim.x >> 5;
+      best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
+      bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float b2 = __shfl_xor_sync(0xffffffffu, best, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (b2 > best || (b2 == best && i2 < bi)) {
+          best = b2;
+          bi = i2;
+        }
+      }
+      if (threadIdx.x == 0) {
+        const bool found = bi != 0x7fffffff;
+        out_idx[(size_t)blockIdx.x * K + k] = found ? bi : 0;
+        out_val[(size_t)blockIdx.x * K + k] = found ? best : -INFINITY;
+        s_last_v = found ? best : -INFINITY;
+        s_last_i = found ? bi : 0x7fffffff;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace bb
 
 using namespace bb;
@@ -215,6 +282,16 @@ BB_API int bb_quant_rows(const void* x, void* q, float* scale, int rows, int k, 
   else
     quant_rows_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)x, (int8_t*)q,
                                                                     scale, rows, k);
+  return (int)cudaGetLastError();
+}
+
+// idx[rows, K] int32, val[rows, K] fp32: the K largest logits of every row, descending.
+BB_API int bb_topk_rows(const void* logits, long ld, int rows, int V, int K, int* idx, float* val,
+                        void* stream) {
+  if (rows <= 0) return BB_OK;
+  if (K < 1 || K > V) return BB_EARG;
+  topk_rows_kernel<<<rows, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ld, V, K,
+                                                          idx, val);
   return (int)cudaGetLastError();
 }
 

@@ -350,3 +350,11 @@ def test_quant_and_argmax():
         assert ((q.int() - qr.int()).abs() > 0).float().mean() < 1e-3
     lg = torch.randn(7, 151936, device=dev()).bfloat16()
     assert (F.argmax_rows(lg).long() == lg.float().argmax(-1)).all()
+    # top-k rows: values descending and equal to the library's; among equal values lowest index first
+    idx, val = F.topk_rows(lg, 64)
+    want_v, _ = torch.topk(lg.float(), 64, dim=-1)
+    assert torch.equal(val, want_v)
+    assert torch.equal(lg.float().gather(1, idx.long()), val)
+    small = torch.tensor([[1.0, 3.0, 3.0, -2.0, 3.0, 0.5, 0.5, 7.0]], device=dev()).bfloat16()
+    i2, v2 = F.topk_rows(small, 8)
+    assert i2[0].tolist() == [7, 1, 2, 4, 0, 5, 6, 3] and v2[0, 0].item() == 7.0
