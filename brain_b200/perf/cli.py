@@ -24,14 +24,17 @@ def _arrival(a: Args) -> Arrival:
     return Arrival.closed_loop(a.int_or("--concurrency", 8))
 
 
-def _make_target(spec: str, device: str, a_conc: int, ctx: int, weights: str):
+def _make_target(spec: str, device: str, a_conc: int, ctx: int, weights: str, **sched_kw):
+    """(factory of fresh targets, vocabulary size); ``sched_kw`` reaches the in-process scheduler
+    targets (prefix_cache=, policy=, policy_arg=, ...)."""
     if spec == "fake":
         return (lambda: FakeTarget(max(a_conc, 1), 2)), 32000
     if spec.startswith("qwen-synth:"):
         from ..train import pick_device
         dev = pick_device(device)
         model = synth_qwen(spec.split(":", 1)[1], dev)
-        return (lambda: SchedulerTarget(model, max_batch=max(a_conc, 1), ctx=ctx, weights=weights, name=spec)), model.cfg.vocab
+        return (lambda: SchedulerTarget(model, max_batch=max(a_conc, 1), ctx=ctx, weights=weights, name=spec,
+                                        **sched_kw)), model.cfg.vocab
     if spec.startswith("weights:"):
         import torch
         from ..checkpoint import st
@@ -40,7 +43,8 @@ def _make_target(spec: str, device: str, a_conc: int, ctx: int, weights: str):
         model, _, _ = st.load_model(spec.split(":", 1)[1], device=dev,
                                     dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32)
         model.eval()
-        return (lambda: SchedulerTarget(model, max_batch=max(a_conc, 1), ctx=ctx, weights=weights, name=spec)), model.cfg.vocab
+        return (lambda: SchedulerTarget(model, max_batch=max(a_conc, 1), ctx=ctx, weights=weights, name=spec,
+                                        **sched_kw)), model.cfg.vocab
     if spec.startswith("http:"):
         # http:<base_url>|<api_key>|<model>
         base, key, model = spec[5:].split("|")
@@ -115,6 +119,76 @@ def run_perf(argv: List[str], device: str = "auto") -> int:
         checks = gate.compare(c, b, floor)
         print(gate.render(checks, floor))
         return 0 if (sub == "compare" or gate.passed(checks)) else 1
+    if sub == "scenario":
+        from . import scenarios as sc
+        a = Args(argv[1:])
+        name = a.positional() or ""
+        target = a.str_or("--target", "fake")
+        n = a.int_or("--requests", 32)
+        seed = a.int_or("--seed", 0)
+        ctx = a.int_or("--ctx", 4096)
+        conc = a.int_or("--concurrency", 8)
+        weights = a.str_or("--weights-dtype", "bf16")
+        rate = a.float_or("--rate", 0.0)
+        seconds = a.float_or("--seconds", 10.0)
+        inp = a.int_or("--input", 0) or None
+        out = a.take_str("--out")
+        a.finish()
+        if name not in sc.TIER1 + sc.TIER2:
+            print(f"usage: brain perf scenario <{'|'.join(sc.TIER1 + sc.TIER2)}> [--target T --requests N "
+                  "--concurrency C --rate R --seconds S --input L --out F]", file=sys.stderr)
+            return 2
+        if name == "faults":
+            return run_perf(["faults"], device)
+        try:
+            mk, vocab = _make_target(target, device, conc, ctx, weights)
+            if name == "latency":
+                res = sc.latency(mk, n=n, seed=seed, vocab=vocab, input_override=inp)
+            elif name == "throughput":
+                res = sc.throughput(mk, n=n, seed=seed, vocab=vocab, input_override=inp)
+            elif name == "serve":
+                if rate <= 0:
+                    print("serve needs --rate R (requests per second)", file=sys.stderr)
+                    return 2
+                res = sc.serve(mk, rate, n=n, seed=seed, vocab=vocab, input_override=inp)
+            elif name == "sweep":
+                ladder = [c for c in (1, 2, 4, 8, 16, 32, 64, 128, 256) if c <= max(conc, 1)]
+                mk_big, _ = _make_target(target, device, ladder[-1], ctx, weights)
+                res = sc.sweep(mk_big, ladder, n=n, seed=seed, vocab=vocab, input_override=inp)
+            elif name == "startup":
+                res = sc.startup(mk, vocab=vocab, seed=seed)
+            elif name == "mixed":
+                res = sc.mixed(mk, n=n, concurrency=conc, seed=seed, vocab=vocab)
+            elif name == "soak":
+                res = sc.soak(mk, seconds=seconds, concurrency=conc, seed=seed, vocab=vocab)
+            elif name == "cancel":
+                mk_nc, _ = _make_target(target, device, conc, ctx, weights, **({} if target == "fake" else {"prefix_cache": False}))
+                res = sc.cancel(mk_nc, n=n, seed=seed, vocab=vocab)
+            elif name == "kvcache":
+                if target == "fake" or target.startswith("http:"):
+                    print("kvcache needs an in-process engine target (qwen-synth: or weights:)", file=sys.stderr)
+                    return 2
+                mk_c, _ = _make_target(target, device, conc, ctx, weights, prefix_cache=True)
+                mk_u, _ = _make_target(target, device, conc, ctx, weights, prefix_cache=False)
+                res = sc.kvcache(mk_c, mk_u, n=n, seed=seed, vocab=vocab)
+            else:   # overload
+                if target == "fake" or target.startswith("http:"):
+                    print("overload needs an in-process engine target (qwen-synth: or weights:)", file=sys.stderr)
+                    return 2
+                cap = sc.throughput(mk, n=max(n // 2, 8), seed=seed, vocab=vocab, input_override=inp)
+                per_s = max(cap["summary"]["requests_per_s"], 1e-3)
+                mk_b, _ = _make_target(target, device, conc, ctx, weights, policy="max_queue_depth",
+                                       policy_arg=float(2 * conc))
+                res = sc.overload(mk_b, per_s, n=n, seed=seed, vocab=vocab, input_override=inp)
+        except ValueError as e:
+            print(str(e), file=sys.stderr)
+            return 2
+        text = json.dumps(res)
+        if out:
+            open(out, "w").write(text + "\n")
+        else:
+            print(text)
+        return 0 if res.get("passed", True) else 1
     if sub == "faults":
         from . import faults
         names = [n for n in argv[1:] if not n.startswith("-")] or None
@@ -128,5 +202,5 @@ def run_perf(argv: List[str], device: str = "auto") -> int:
                   f"{str(r.survived):<5} {'PASS' if r.passed else 'FAIL'}  {r.detail}")
         return 0 if all(r.passed for r in res) else 1
     print("usage: brain perf list | run <workload> [--target T --requests N --concurrency C --out F] | "
-          "compare A B | gate A B [--tolerance X] | faults [NAME…]", file=sys.stderr)
+          "compare A B | gate A B [--tolerance X] | scenario <name> [...] | faults [NAME…]", file=sys.stderr)
     return 2

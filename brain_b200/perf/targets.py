@@ -88,13 +88,19 @@ class FakeTarget(PerfTarget):
     def outputs(self, rid):
         return self.out[rid]
 
+    def cancel(self, rid):
+        self.run.pop(rid, None)
+        if rid in self.wait:
+            self.wait.remove(rid)
+
 
 class SchedulerTarget(PerfTarget):
     """A model behind the paged-KV engine and continuous-batching scheduler, driven in-process."""
 
     def __init__(self, model, max_batch: int = 256, ctx: int = 4096, block_size: int = 16, weights: str = "bf16",
                  num_blocks: Optional[int] = None, tp=None, name: str = "qwen", engine=None, admit_batch: int = 1,
-                 prefix_cache: bool = True, prefill_budget: int = 0):
+                 prefix_cache: bool = True, prefill_budget: int = 0, policy: str = "unbounded_queue",
+                 policy_arg: float = 0.0):
         from ..serve.engine import QwenEngine
         from ..serve.scheduler import Scheduler
         per_seq = -(-ctx // block_size)
@@ -102,7 +108,8 @@ class SchedulerTarget(PerfTarget):
         self.engine = engine or QwenEngine(model, block_size=block_size, num_blocks=nb, max_seq_len=ctx,
                                            max_prefill=min(ctx, 2048), weights=weights, tp=tp)
         self.sched = Scheduler(self.engine, max_batch=max_batch, eos=None, admit_batch=admit_batch,
-                               prefix_cache=prefix_cache, prefill_budget=prefill_budget)
+                               prefix_cache=prefix_cache, prefill_budget=prefill_budget, policy=policy,
+                               policy_arg=policy_arg)
         self.live: Dict[int, bool] = {}
         self.admitted: Dict[int, bool] = {}
         self.info = {"model": name, "artifact_unit": "token", "max_batch": max_batch, "ctx": ctx,
@@ -133,6 +140,18 @@ class SchedulerTarget(PerfTarget):
 
     def outputs(self, rid):
         return self.sched.tokens_of(rid)
+
+    def cancel(self, rid):
+        self.sched.cancel(rid)
+        self.live.pop(rid, None)
+
+    def free_blocks(self) -> int:
+        """Blocks available to new work: free ones plus those only the prefix cache still holds."""
+        st = self.sched.stats()
+        return int(st["free_blocks"]) + int(st.get("prefix_entries", 0))
+
+    def prefill_tokens(self) -> int:
+        return int(self.engine.acct["prefill_tokens"])
 
 
 def synth_qwen(spec: str, device=None, dtype=None):
