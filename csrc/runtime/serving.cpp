@@ -393,14 +393,22 @@ class Scheduler {
     }
     decode_all_greedy = all_greedy;
     decode_window = 1;
-    if (cfg_.window > 1 && waiting_.empty() && prefill_plan.empty() && all_greedy && !decode_plan.empty() &&
-        alloc_.free_blocks() >= decode_plan.size() * cfg_.window) {
+    // A window of on-device steps is taken when nobody could be admitted during it anyway: the
+    // queue is empty, every slot is taken (the window never outlives a sequence, so no slot frees
+    // inside it), or admission is being held back for batching (then at most up to its next turn).
+    const bool slots_full = running_.size() >= cfg_.max_batch;
+    const bool held = !waiting_.empty() && !admit_now && !slots_full;
+    if (cfg_.window > 1 && (waiting_.empty() || slots_full || held) && prefill_plan.empty() && all_greedy &&
+        !decode_plan.empty() && alloc_.free_blocks() >= decode_plan.size() * cfg_.window) {
       uint32_t w = cfg_.window;
+      if (held)
+        w = std::min<uint32_t>(w, admit_max_wait_ > steps_since_admit_ ? admit_max_wait_ - steps_since_admit_ : 1);
       for (int64_t id : decode_plan) {
         Seq& s = *seqs_[id];
         w = std::min<uint32_t>(w, s.max_new - static_cast<uint32_t>(s.out.size()) + 1);
       }
       decode_window = std::max<uint32_t>(1, w);
+      steps_since_admit_ += decode_window - 1;   // the window is that many scheduler steps
     }
     // back the positions the decode steps will write
     std::vector<int64_t> ok;

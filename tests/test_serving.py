@@ -289,11 +289,11 @@ def test_admission_batching_takes_requests_in_groups():
     from brain_b200.perf.workload import Arrival, standard
     m = synth_qwen("1x32x4x300", "cpu")
 
-    def run(admit):
+    def run(admit, wait=64):
         wl = standard("serving_mix", Arrival.closed_loop(8), 32, seed=0, vocab=300)
         wl.classes[0].input.lo, wl.classes[0].input.hi = 16, 64
         wl.classes[0].output = type(wl.classes[0].output).uniform(4, 24)
-        t = SchedulerTarget(m, max_batch=8, ctx=256, admit_batch=admit)
+        t = SchedulerTarget(m, max_batch=8, ctx=256, admit_batch=admit, admit_max_wait=wait)
         r = drive(t, wl, max_seconds=120)
         s = Summary.build(r.records, r.wall_s, wl.classes[0].slo)
         return s, t.sched.stats(), [t.outputs(i) for i in r.ids]
@@ -301,3 +301,8 @@ def test_admission_batching_takes_requests_in_groups():
     s4, st4, o4 = run(4)
     assert s1.completed == s4.completed == 32 and s4.output_artifacts == s1.output_artifacts
     assert o1 == o4                                  # batching admissions never changes greedy outputs
+    # admission every few steps: held requests do not switch off the on-device decode window, so
+    # there are fewer engine calls for the same tokens, and still the same outputs
+    sw, stw, ow = run(8, wait=3)
+    assert sw.completed == 32 and ow == o1
+    assert stw["steps"] <= st1["steps"]
