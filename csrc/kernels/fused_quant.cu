@@ -38,31 +38,36 @@ __global__ void rmsnorm_q8_kernel(const __nv_bfloat16* __restrict__ x, const __n
   const bf16x8* rr = res ? reinterpret_cast<const bf16x8*>(res + (size_t)row * d) : nullptr;
   bf16x8* hr = h_out ? reinterpret_cast<bf16x8*>(h_out + (size_t)row * d) : nullptr;
   const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
-  bf16x8 hv[MAXV];
+  // every load of the row is issued before the first use (a load inside the compute loop waits
+  // for the previous iteration's store to the residual stream and serialises the row)
+  bf16x8 hv[MAXV], rv[MAXV], wv[MAXV];
+#pragma unroll
+  for (int t = 0; t < MAXV; ++t) {
+    const int i = lane + 32 * t;
+    if (i < nv) {
+      hv[t] = xr[i];
+      if (rr) rv[t] = rr[i];
+      wv[t] = wr[i];
+    }
+  }
   float ss = 0.f;
 #pragma unroll
   for (int t = 0; t < MAXV; ++t) {
     const int i = lane + 32 * t;
     if (i < nv) {
       float f[8];
-      unpack8(xr[i], f);
+      unpack8(hv[t], f);
       if (rr) {
         float g[8];
-        unpack8(rr[i], g);
+        unpack8(rv[t], g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] += g[j];
-        if (hr) {
-          hv[t] = pack8(f);
-          hr[i] = hv[t];
-          unpack8(hv[t], f);   // normalise exactly what the residual stream stores
-#pragma unroll
-          for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
-          continue;
-        }
+        hv[t] = pack8(f);      // the residual stream value: normalise exactly what is stored
+        hr[i] = hv[t];
+        unpack8(hv[t], f);
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
-      hv[t] = pack8(f);   // no residual: f came from bf16, the round trip is exact
     }
   }
   ss = warp_sum(ss);
@@ -74,7 +79,7 @@ __global__ void rmsnorm_q8_kernel(const __nv_bfloat16* __restrict__ x, const __n
     if (i < nv) {
       float f[8], g[8];
       unpack8(hv[t], f);
-      unpack8(wr[i], g);
+      unpack8(wv[t], g);
 #pragma unroll
       for (int j = 0; j < 8; ++j) f[j] = f[j] * rstd * g[j];
       hv[t] = pack8(f);          // the bf16 value the unfused norm would have stored
@@ -108,15 +113,23 @@ __global__ void swiglu_q8_kernel(const __nv_bfloat16* __restrict__ gu, int8_t* _
   if (row >= rows) return;
   const int nv = ff >> 3;
   const bf16x8* gr = reinterpret_cast<const bf16x8*>(gu + (size_t)row * 2 * ff);
-  bf16x8 hv[MAXV];
+  bf16x8 hv[MAXV], uv[MAXV];
+#pragma unroll
+  for (int t = 0; t < MAXV; ++t) {
+    const int i = lane + 32 * t;
+    if (i < nv) {
+      hv[t] = gr[i];
+      uv[t] = gr[nv + i];
+    }
+  }
   float mx = 0.f;
 #pragma unroll
   for (int t = 0; t < MAXV; ++t) {
     const int i = lane + 32 * t;
     if (i < nv) {
       float g[8], u[8], o[8];
-      unpack8(gr[i], g);
-      unpack8(gr[nv + i], u);
+      unpack8(hv[t], g);
+      unpack8(uv[t], u);
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
       hv[t] = pack8(o);
@@ -146,7 +159,7 @@ __global__ void swiglu_q8_kernel(const __nv_bfloat16* __restrict__ gu, int8_t* _
 using namespace bb;
 
 // q[rows, d] int8, scale[rows] = quant_rows(RMSNorm(x [+ res]) * w); h_out (required when res is
-// given) receives x + res.  d % 8 == 0, d <= 8192.
+// given) receives x + res.  d % 8 == 0, d <= 4096 (BB_ESIZE beyond).
 BB_API int bb_rmsnorm_q8(const void* x, const void* res, const void* w, void* h_out, void* q,
                          float* scale, int rows, int d, float eps, void* stream) {
   if (rows <= 0) return BB_OK;
@@ -160,13 +173,12 @@ BB_API int bb_rmsnorm_q8(const void* x, const void* res, const void* w, void* h_
   if (d <= 256 * 4) BB_RQ(4);
   else if (d <= 256 * 8) BB_RQ(8);
   else if (d <= 256 * 16) BB_RQ(16);
-  else if (d <= 256 * 32) BB_RQ(32);
-  else return BB_ESIZE;
+  else return BB_ESIZE;   // wider rows do not fit the register file: run the norm and the quant apart
 #undef BB_RQ
   return (int)cudaGetLastError();
 }
 
-// q[rows, ff] int8, scale[rows] = quant_rows(silu(gu[:, :ff]) * gu[:, ff:]).  ff % 8 == 0, ff <= 8192.
+// q[rows, ff] int8, scale[rows] = quant_rows(silu(gu[:, :ff]) * gu[:, ff:]).  ff % 8 == 0, ff <= 4096 (BB_ESIZE beyond).
 BB_API int bb_swiglu_q8(const void* gu, void* q, float* scale, int rows, int ff, void* stream) {
   if (rows <= 0) return BB_OK;
   if (ff % 8) return BB_EARG;
@@ -177,7 +189,6 @@ BB_API int bb_swiglu_q8(const void* gu, void* q, float* scale, int rows, int ff,
   if (ff <= 256 * 4) BB_SQ(4);
   else if (ff <= 256 * 8) BB_SQ(8);
   else if (ff <= 256 * 16) BB_SQ(16);
-  else if (ff <= 256 * 32) BB_SQ(32);
   else return BB_ESIZE;
 #undef BB_SQ
   return (int)cudaGetLastError();

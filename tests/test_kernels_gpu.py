@@ -263,7 +263,7 @@ def test_lm_head_ce_weighted():
     assert rel_err(w.grad, wr.grad) < 3e-2
 
 
-@pytest.mark.parametrize("rows,d", [(37, 1024), (300, 4096), (5, 5120), (64, 768)])
+@pytest.mark.parametrize("rows,d", [(37, 1024), (300, 4096), (5, 2048), (64, 768)])
 def test_fused_norm_and_swiglu_quant_are_bit_identical_to_the_unfused_pairs(rows, d):
     """rmsnorm_q8 == quant_rows(rmsnorm(...)) and swiglu_q8 == quant_rows(swiglu(...)), bit for bit,
     including the residual sum the norm writes out."""
