@@ -64,6 +64,29 @@ def test_flash_bwd(B, T, hq, hk, hd, causal):
     assert rel_err(v.grad, vr.grad) < 3e-2
 
 
+def test_flash_fwd_first_form_still_matches():
+    """BB_FA_FWD=1 selects the single-buffer forward kernel (the one with timeline stamps); it is
+    read once per process, so the check runs in a child process."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import math, torch\n"
+        "from brain_b200.ops import _cuda, reference as ref\n"
+        "from brain_b200.ops.attention import flash_attention\n"
+        "torch.manual_seed(0)\n"
+        "for (B,T,hq,hk,hd,S) in ((2,256,4,2,128,256),(1,200,2,1,64,200),(1,72,4,2,64,200)):\n"
+        "    q=torch.randn(B*T,hq*hd,device='cuda').bfloat16(); k=torch.randn(B*S,hk*hd,device='cuda').bfloat16(); v=torch.randn(B*S,hk*hd,device='cuda').bfloat16()\n"
+        "    o=flash_attention(q,k,v,B,T,hq,hk,hd,True,S=S); _cuda.check_error()\n"
+        "    w=ref.attention(q.float().reshape(B,T,hq,hd),k.float().reshape(B,S,hk,hd),v.float().reshape(B,S,hk,hd),True,1/math.sqrt(hd)).reshape(B*T,hq*hd)\n"
+        "    assert ((o.float()-w).norm()/w.norm()).item() < 2e-2\n"
+        "print('ok')\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, BB_FA_FWD="1", PYTHONPATH=root),
+                       capture_output=True, text=True, timeout=300, cwd=root)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
+
+
 def test_flash_fwd_prefix_offset():
     """Queries are the last T positions of an S-long context (chunked prefill shape)."""
     torch.manual_seed(5)
