@@ -57,9 +57,11 @@ __global__ void __launch_bounds__(256) tp_allreduce_kernel(const ArArgs a) {
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nv;
        i += (long)gridDim.x * blockDim.x)
     mine[i] = reinterpret_cast<const bf16x8*>(a.x)[i];
-  __threadfence_system();
+  // one system-scope fence per block, after the block barrier (it is cumulative over the writes the
+  // barrier ordered before it); a fence in every thread made thousands of MEMBAR.SYS queue up
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     s_ok = 1;
     const unsigned int done = atomicAdd(a.counter, 1u);
     if (done == gridDim.x - 1) {
@@ -128,9 +130,9 @@ __global__ void __launch_bounds__(256) tp_allreduce2_kernel(const Ar2Args a) {
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x;
   bf16x8* mine = reinterpret_cast<bf16x8*>(a.stage.p[a.rank]);
   for (long i = tid; i < nv; i += stride) mine[i] = reinterpret_cast<const bf16x8*>(a.x)[i];
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();   // one per block: cumulative over the block's writes ordered by the barrier
     if (atomicAdd(a.counters, 1u) == gridDim.x - 1) {
       a.counters[0] = 0u;
       for (int r = 0; r < a.world; ++r)
@@ -151,20 +153,26 @@ __global__ void __launch_bounds__(256) tp_allreduce2_kernel(const Ar2Args a) {
     for (long j = tid; j < per; j += stride) {
       const long i = lo + j;
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int r = 0; r < a.world; ++r) {
-        const uint4 raw = ld_volatile_u4(reinterpret_cast<const uint4*>(a.stage.p[r]) + i);
-        float f[8];
-        unpack8(*reinterpret_cast<const bf16x8*>(&raw), f);
+      uint4 raw[MAX_RANKS];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) acc[q] += f[q];
+      for (int r = 0; r < MAX_RANKS; ++r)   // all peer loads in flight before the first add
+        if (r < a.world) raw[r] = ld_volatile_u4(reinterpret_cast<const uint4*>(a.stage.p[r]) + i);
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r) {
+        if (r < a.world) {
+          float f[8];
+          unpack8(*reinterpret_cast<const bf16x8*>(&raw[r]), f);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[q] += f[q];
+        }
       }
       const bf16x8 out = pack8(acc);
       for (int r = 0; r < a.world; ++r) reinterpret_cast<bf16x8*>(a.result.p[r])[i] = out;
     }
   }
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     if (atomicAdd(a.counters + 1, 1u) == gridDim.x - 1) {
       a.counters[1] = 0u;
       for (int r = 0; r < a.world; ++r)
