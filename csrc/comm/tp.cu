@@ -116,6 +116,10 @@ struct Ar2Args {
   int* err;
 };
 
+// W > 0: the world size as a compile-time constant, with 8 / W slices of the loop in flight per
+// thread (at W = 2 a thread otherwise has only two 16-byte peer loads outstanding per NVLink round
+// trip and the reduce phase is latency-bound); W = 0: any world size up to MAX_RANKS.
+template <int W>
 __global__ void __launch_bounds__(256) tp_allreduce2_kernel(const Ar2Args a) {
   __shared__ unsigned int s_e;
   __shared__ int s_ok;
@@ -150,24 +154,57 @@ __global__ void __launch_bounds__(256) tp_allreduce2_kernel(const Ar2Args a) {
   if (s_ok) {
     const long per = nv / a.world;  // host guarantees divisibility
     const long lo = (long)a.rank * per;
-    for (long j = tid; j < per; j += stride) {
-      const long i = lo + j;
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      uint4 raw[MAX_RANKS];
+    if constexpr (W > 0) {
+      constexpr int U = 8 / W > 0 ? 8 / W : 1;   // loop slices in flight per thread
+      for (long j0 = tid; j0 < per; j0 += stride * U) {
+        uint4 raw[U][W];
 #pragma unroll
-      for (int r = 0; r < MAX_RANKS; ++r)   // all peer loads in flight before the first add
-        if (r < a.world) raw[r] = ld_volatile_u4(reinterpret_cast<const uint4*>(a.stage.p[r]) + i);
+        for (int u = 0; u < U; ++u) {
+          const long j = j0 + (long)u * stride;
+          if (j < per) {
 #pragma unroll
-      for (int r = 0; r < MAX_RANKS; ++r) {
-        if (r < a.world) {
-          float f[8];
-          unpack8(*reinterpret_cast<const bf16x8*>(&raw[r]), f);
+            for (int r = 0; r < W; ++r)
+              raw[u][r] = ld_volatile_u4(reinterpret_cast<const uint4*>(a.stage.p[r]) + lo + j);
+          }
+        }
 #pragma unroll
-          for (int q = 0; q < 8; ++q) acc[q] += f[q];
+        for (int u = 0; u < U; ++u) {
+          const long j = j0 + (long)u * stride;
+          if (j < per) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+            for (int r = 0; r < W; ++r) {   // rank order: the sum is bit-identical on every rank
+              float f[8];
+              unpack8(*reinterpret_cast<const bf16x8*>(&raw[u][r]), f);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) acc[q] += f[q];
+            }
+            const bf16x8 out = pack8(acc);
+#pragma unroll
+            for (int r = 0; r < W; ++r) reinterpret_cast<bf16x8*>(a.result.p[r])[lo + j] = out;
+          }
         }
       }
-      const bf16x8 out = pack8(acc);
-      for (int r = 0; r < a.world; ++r) reinterpret_cast<bf16x8*>(a.result.p[r])[i] = out;
+    } else {
+      for (long j = tid; j < per; j += stride) {
+        const long i = lo + j;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        uint4 raw[MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)   // all peer loads in flight before the first add
+          if (r < a.world) raw[r] = ld_volatile_u4(reinterpret_cast<const uint4*>(a.stage.p[r]) + i);
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r) {
+          if (r < a.world) {
+            float f[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(&raw[r]), f);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[q] += f[q];
+          }
+        }
+        const bf16x8 out = pack8(acc);
+        for (int r = 0; r < a.world; ++r) reinterpret_cast<bf16x8*>(a.result.p[r])[i] = out;
+      }
     }
   }
   __syncthreads();
@@ -291,6 +328,12 @@ BB_API int bb_tp_allreduce2(const uint64_t* stage_ptrs, const uint64_t* result_p
   long blocks = ((n >> 3) + 255) / 256;
   if (blocks > sm_count()) blocks = sm_count();  // every block waits on peers: keep them co-resident
   if (blocks < 1) blocks = 1;
-  tp_allreduce2_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(a);
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (world) {
+    case 2: tp_allreduce2_kernel<2><<<(int)blocks, 256, 0, s>>>(a); break;
+    case 4: tp_allreduce2_kernel<4><<<(int)blocks, 256, 0, s>>>(a); break;
+    case 8: tp_allreduce2_kernel<8><<<(int)blocks, 256, 0, s>>>(a); break;
+    default: tp_allreduce2_kernel<0><<<(int)blocks, 256, 0, s>>>(a); break;
+  }
   return (int)cudaGetLastError();
 }
