@@ -605,290 +605,6 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   }
 }
 
-// Third form: the two-unit pipeline of the second form with TWO softmax threads per query row
-// (320 threads: producer warp, MMA warp, two softmax warpgroups), so twice as many warps hide the
-// MUFU and TMEM-load latency of the serial softmax chain.
-template <int HD>
-__global__ void __launch_bounds__(320, 2)
-fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-               const __grid_constant__ CUtensorMap tmV, const FaFwdArgs args) {
-  using Cfg = FaFwdCfg<HD>;
-  constexpr int NSUB = Cfg::NSUB;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~uintptr_t(1023));
-  uint8_t* sQ = smem + Cfg::OFF_Q;
-  uint8_t* sK = smem + Cfg::OFF_K;
-  uint8_t* sV = smem + Cfg::OFF_V;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
-  uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;
-  uint64_t* k_empty = bars + 2;
-  uint64_t* v_full = bars + 3;
-  uint64_t* v_empty = bars + 4;
-  uint64_t* s_full = bars + 5;    // [2], one per score buffer
-  uint64_t* p_ready = bars + 7;   // [2], 256 arrivals each
-  uint64_t* pv_done = bars + 9;   // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
-  float* s_x = reinterpret_cast<float*>(smem + Cfg::OFF_BAR + 256);   // [2][2][128] row max / sum exchange
-                                                                      // (2 KB past the barrier block: the launch adds them)
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int T = args.T, S = args.S;
-  const int q0 = qt * 128;
-  const int kvh = h / (args.hq / args.hk);
-  const int off = S - T;
-  int n_blocks = (S + 127) / 128;
-  if (args.causal) {
-    const int last = (q0 + 127 + off) / 128 + 1;
-    n_blocks = last < n_blocks ? last : n_blocks;
-  }
-  const int n_units = 2 * n_blocks;
-
-  if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(k_full, 1);
-    mbar_init(k_empty, 1);
-    mbar_init(v_full, 1);
-    mbar_init(v_empty, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(s_full + i, 1);
-      mbar_init(p_ready + i, 256);
-      mbar_init(pv_done + i, 1);
-    }
-    mbar_fence_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_O = tmem_base + 128;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      mbar_expect_tx(q_full, Cfg::TILE_BYTES);
-#pragma unroll
-      for (int c = 0; c < NSUB; ++c)
-        tma_load_2d(sQ + c * Cfg::SUB_BYTES, &tmQ, q_full, h * HD + c * 64, b * T + q0);
-      for (int j = 0; j < n_blocks; ++j) {
-        const uint32_t ph = j & 1;
-        if (!mbar_wait(k_empty, ph ^ 1)) {
-          set_error(args.err, ERR_WAIT_PRODUCER);
-          break;
-        }
-        mbar_expect_tx(k_full, Cfg::TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < NSUB; ++c)
-          tma_load_2d(sK + c * Cfg::SUB_BYTES, &tmK, k_full, kvh * HD + c * 64, b * S + j * 128);
-        if (!mbar_wait(v_empty, ph ^ 1)) {
-          set_error(args.err, ERR_WAIT_PRODUCER);
-          break;
-        }
-        mbar_expect_tx(v_full, Cfg::TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < NSUB; ++c)
-          tma_load_2d(sV + c * Cfg::SUB_BYTES, &tmV, v_full, kvh * HD + c * 64, b * S + j * 128);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = umma_idesc(1, 1, 1, 0, 0, 128, 64);
-      constexpr uint32_t idesc_pv = umma_idesc(1, 1, 1, 0, 1, 128, HD);
-      const uint32_t aq = smem_u32(sQ), bk = smem_u32(sK), bv = smem_u32(sV);
-      bool ok = mbar_wait(q_full, 0);
-      if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
-      // S(u) = Q . K[unit u]^T into score buffer u & 1 (64 keys = rows half*64.. of the K tile)
-      auto issue_s = [&](int u) -> bool {
-        const int j = u >> 1, half = u & 1;
-        if (half == 0) {
-          if (!mbar_wait(k_full, j & 1)) return false;
-          tc_fence_after();
-        }
-#pragma unroll
-        for (int t = 0; t < HD / 16; ++t) {
-          const uint32_t o = (t / 4) * Cfg::SUB_BYTES + (t % 4) * 32;
-          umma_f16_ss(tmem_base + half * 64, umma_smem_desc(aq + o, 16, 1024),
-                      umma_smem_desc(bk + o + half * 8192, 16, 1024), idesc_qk, t != 0);
-        }
-        umma_commit(s_full + half);
-        if (half == 1) umma_commit(k_empty);
-        return true;
-      };
-      if (ok && n_units > 0) ok = issue_s(0);
-      if (ok && n_units > 1) ok = issue_s(1);
-      if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
-      for (int u = 0; u < n_units && ok; ++u) {
-        const int j = u >> 1, half = u & 1;
-        if (!mbar_wait(p_ready + half, j & 1) || (half == 0 && !mbar_wait(v_full, j & 1))) {
-          set_error(args.err, ERR_WAIT_MMA_TMEM);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        // O += P(u) V[unit u]: A = packed bf16 P in TMEM (8 columns per 16-key step), B = V MN-major
-#pragma unroll
-        for (int t = 0; t < 4; ++t)
-          umma_f16_ts(tmem_O, tmem_base + half * 64 + t * 8,
-                      umma_smem_desc(bv + (half * 4 + t) * 2048, Cfg::SUB_BYTES, 1024), idesc_pv,
-                      (u | t) != 0);
-        umma_commit(pv_done + half);
-        if (half == 1) umma_commit(v_empty);
-        if (u + 2 < n_units && !issue_s(u + 2)) {
-          set_error(args.err, ERR_WAIT_MMA_FULL);
-          ok = false;
-        }
-      }
-    }
-  } else {
-    // ------------------------------------------------------------ softmax + epilogue
-    // Two threads per query row: warpgroup 0 (warps 2..5) takes columns 0..31 of a unit, warpgroup
-    // 1 (warps 6..9) columns 32..63 (warps w and w+4 reach the same TMEM lanes).  The row maximum is
-    // exchanged through shared memory once per unit; both threads then follow the same running
-    // reference, so their partial sums simply add at the end.
-    const int wg = (warp - 2) >> 2;
-    const int sw = warp & 3;
-    const int row = sw * 32 + lane;
-    const int q_idx = q0 + row;
-    const uint32_t lane_sel = (uint32_t)(sw * 32) << 16;
-    const int kv_limit_row = args.causal ? min(q_idx + off, S - 1) : S - 1;
-    const uint32_t tO = tmem_O + lane_sel;
-    float m_ref = -INFINITY, l = 0.f;
-    bool ok = true;
-    // Every thread passes the same number of named barriers whatever happens: after a timed-out
-    // wait a warp keeps walking the units (doing nothing) so that the other warpgroup never waits
-    // at a barrier its partner will not reach.
-    for (int u = 0; u < n_units; ++u) {
-      const int half = u & 1;
-      const uint32_t tS = tmem_base + half * 64 + lane_sel;
-      if (ok) {
-        ok = mbar_wait(s_full + half, (u >> 1) & 1);
-        ok = __all_sync(0xffffffffu, ok);
-      }
-      uint32_t r0[32];
-      const int kv0 = u * 64 + wg * 32;
-      const bool need_mask = (kv0 + 31 > kv_limit_row);
-      const int lim = kv_limit_row - kv0;  // columns <= lim are visible
-      float mx = -INFINITY;
-      if (ok) {
-        tc_fence_after();
-        tmem_ld32(tS + wg * 32, r0);
-        tmem_wait_ld();
-        if (!need_mask) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r0[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (i <= lim) mx = fmaxf(mx, __uint_as_float(r0[i]));
-        }
-      }
-      float* xbuf = s_x + (u & 1) * 256;
-      xbuf[wg * 128 + row] = mx;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (!ok) continue;
-      mx = fmaxf(mx, xbuf[(wg ^ 1) * 128 + row]);
-      mx *= args.scale_log2;
-      float m_new = m_ref;
-      if (mx > m_ref + 8.f) m_new = mx;  // lazy: keep the old reference while p stays <= 2^8
-      const float alpha =
-          (m_new == m_ref) ? 1.f : ((m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new));
-      if (u > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        // O changes scale: every PV issued so far must have landed first; each warpgroup rescales
-        // its half of the columns
-        ok = mbar_wait(pv_done + ((u - 1) & 1), ((u - 1) >> 1) & 1);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) continue;
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = wg * (HD / 64); c < (wg + 1) * (HD / 64); ++c) {
-          uint32_t r[32];
-          tmem_ld32(tO + c * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st32(tO + c * 32, r);
-        }
-      }
-      l *= alpha;
-      m_ref = m_new;
-      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-      const float sc = args.scale_log2;
-      uint32_t pk[16];  // 32 probabilities as 16 packed bf16x2 words
-      float ls = 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        float a0 = exp2f(__uint_as_float(r0[i]) * sc - m_use);
-        float a1 = exp2f(__uint_as_float(r0[i + 1]) * sc - m_use);
-        if (need_mask) {
-          if (i > lim) a0 = 0.f;
-          if (i + 1 > lim) a1 = 0.f;
-        }
-        ls += a0 + a1;
-        pk[i >> 1] = pack_bf16x2_alu(a0, a1);
-      }
-      l += ls;
-      tmem_st16(tS + wg * 16, pk);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(p_ready + half);
-    }
-    if (ok && n_units > 0) {
-      ok = mbar_wait(pv_done + ((n_units - 1) & 1), ((n_units - 1) >> 1) & 1);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    // both threads of a row add their partial sums (every thread reaches this barrier, also after
-    // a timed-out wait, so the other warpgroup is never left waiting)
-    float* xbuf = s_x + (n_units & 1) * 256;
-    xbuf[wg * 128 + row] = l;
-    asm volatile("bar.sync 2, 256;" ::: "memory");
-    l += xbuf[(wg ^ 1) * 128 + row];
-    if (!ok) {
-      if (lane == 0) set_error(args.err, ERR_WAIT_SOFTMAX);
-    } else {
-      tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = args.O + (size_t)(b * T + q_idx) * args.ldo + h * HD;
-#pragma unroll 1
-      for (int c = wg * (HD / 64); c < (wg + 1) * (HD / 64); ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld32(tO + c * 32, r);
-        tmem_wait_ld();
-        if (q_idx < T) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(r[q * 8 + 0]) * inv, __uint_as_float(r[q * 8 + 1]) * inv);
-            o.y = pack_bf16x2(__uint_as_float(r[q * 8 + 2]) * inv, __uint_as_float(r[q * 8 + 3]) * inv);
-            o.z = pack_bf16x2(__uint_as_float(r[q * 8 + 4]) * inv, __uint_as_float(r[q * 8 + 5]) * inv);
-            o.w = pack_bf16x2(__uint_as_float(r[q * 8 + 6]) * inv, __uint_as_float(r[q * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = o;
-          }
-        }
-      }
-      if (wg == 0 && args.lse && q_idx < T)
-        args.lse[((size_t)b * args.hq + h) * T + q_idx] =
-            (l > 0.f) ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
-  }
-}
-
 template <int HD>
 static int launch_fa_fwd(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
                          const FaFwdArgs& a, cudaStream_t stream) {
@@ -911,9 +627,6 @@ static int launch_fa_fwd(const void* q, int ldq, const void* k, int ldk, const v
     e = cudaFuncSetAttribute(fa_fwd2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(fa_fwd3_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg::SMEM + 2048);
-    if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
   dim3 grid((a.T + 127) / 128, a.hq, a.B);
@@ -921,11 +634,9 @@ static int launch_fa_fwd(const void* q, int ldq, const void* k, int ldk, const v
   // the first form, which also carries the timeline stamps
   static const int form = [] {
     const char* e = getenv("BB_FA_FWD");
-    return (e && e[0] == '1') ? 1 : ((e && e[0] == '3') ? 3 : 2);
+    return (e && e[0] == '1') ? 1 : 2;
   }();
-  if (form == 3 && a.timeline == nullptr)
-    fa_fwd3_kernel<HD><<<grid, 320, Cfg::SMEM + 2048, stream>>>(tmQ, tmK, tmV, a);
-  else if (form == 2 && a.timeline == nullptr)
+  if (form == 2 && a.timeline == nullptr)
     fa_fwd2_kernel<HD><<<grid, 192, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, a);
   else
     fa_fwd_kernel<HD><<<grid, 192, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, a);
