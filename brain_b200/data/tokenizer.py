@@ -88,6 +88,7 @@ class BpeTokenizer:
             lib.bbh_bpe_add_merge(self._h, lb, len(lb), rb, len(rb), rank)
         self.vocab_size = max([lib.bbh_bpe_vocab_size(self._h)] + [i + 1 for i in self.special.values()])
         self.eos_id = self.special.get(eos) if eos else None
+        self.chat_template = None     # a checkpoint's own Jinja template (data.chat_template.ChatTemplate)
         self._buf = np.empty(4096, dtype=np.int32)
 
     def __del__(self):
@@ -106,7 +107,10 @@ class BpeTokenizer:
         special = {t["content"]: t["id"] for t in d.get("added_tokens", [])}
         eos = next((s for s in ("<|im_end|>", "<|endoftext|>") if s in special), None)
         pat = QWEN_SPLIT if "<|im_end|>" in special or len(model["vocab"]) > 60000 else GPT2_SPLIT
-        return BpeTokenizer(model["vocab"], model["merges"], special, pat, eos)
+        tok = BpeTokenizer(model["vocab"], model["merges"], special, pat, eos)
+        from .chat_template import ChatTemplate
+        tok.chat_template = ChatTemplate.beside(path)
+        return tok
 
     @staticmethod
     def byte_level(merges: Sequence = (), special: Optional[Dict[str, int]] = None) -> "BpeTokenizer":
@@ -168,7 +172,11 @@ class BpeTokenizer:
         """ChatML rendering used by the Qwen family (reference: crates/data/src/qwen_tokenizer.rs
         ``apply_chat_template``): ``<|im_start|>role\ncontent<|im_end|>\n`` per message, an open
         assistant turn when generating, and an empty think block when thinking is disabled.
-        ``messages`` is a sequence of (role, content) pairs or {"role", "content"} dicts."""
+        ``messages`` is a sequence of (role, content) pairs or {"role", "content"} dicts.  When the
+        checkpoint ships its own template (``tokenizer_config.json`` / ``chat_template.jinja``) that
+        template is rendered instead."""
+        if self.chat_template is not None:
+            return self.chat_template.render(messages, add_generation_prompt, tools, enable_thinking=enable_thinking)
         return render_chatml(messages, add_generation_prompt, enable_thinking, tools)
 
 

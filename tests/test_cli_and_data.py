@@ -557,3 +557,48 @@ def test_q4_storage_and_fp8_block_import(tmp_path):
     got, _, _ = st.load(out)
     for name, _ in cfg.param_list():
         assert torch.allclose(got[name].reshape(-1), tensors["_want_" + name].reshape(-1), atol=1e-6), name
+
+
+def test_checkpoint_chat_template_is_rendered(tmp_path):
+    """A tokenizer directory with its own Jinja chat template: rendered through the sandboxed
+    environment (raise_exception, tojson with source key order, generation prompt), and picked up by
+    ``BpeTokenizer.from_file``; without one the built-in ChatML form is used."""
+    import json
+    from brain_b200.data.chat_template import ChatTemplate, TemplateError
+    from brain_b200.data.tokenizer import BpeTokenizer, bytes_to_unicode, render_chatml
+    src = ("{%- if tools %}<tools>{% for t in tools %}{{ t | tojson }}{% endfor %}</tools>{{ '\\n' }}{% endif -%}"
+           "{%- for m in messages -%}"
+           "{%- if m.role not in ['system', 'user', 'assistant'] %}{{ raise_exception('bad role ' + m.role) }}{% endif -%}"
+           "{{ '<|im_start|>' + m.role + '\\n' + m.content + '<|im_end|>' + '\\n' }}"
+           "{%- endfor -%}"
+           "{%- if add_generation_prompt %}{{ '<|im_start|>assistant\\n' }}"
+           "{%- if enable_thinking is defined and enable_thinking is false %}{{ '<think>\\n\\n</think>\\n\\n' }}{% endif %}{% endif %}")
+    t = ChatTemplate(src)
+    msgs = [("system", "be brief"), ("user", "hi")]
+    assert t.render(msgs, True) == render_chatml(msgs, True)
+    assert t.render(msgs, True, enable_thinking=False) == render_chatml(msgs, True, enable_thinking=False)
+    tool = {"type": "function", "function": {"name": "zeta", "parameters": {"b": 1, "a": 2}}}
+    out = t.render(msgs, False, tools=[tool])
+    assert out.startswith('<tools>{"type": "function", "function": {"name": "zeta", "parameters": {"b": 1, "a": 2}}}</tools>')
+    with pytest.raises(TemplateError, match="bad role"):
+        t.render([("tool", "x")])
+    with pytest.raises(TemplateError):
+        ChatTemplate("{% for %}")
+    with pytest.raises(TemplateError):          # sandbox: no attribute walks into Python internals
+        ChatTemplate("{{ messages.__class__.__mro__ }}").render(msgs)
+
+    d = tmp_path / "tok"
+    d.mkdir()
+    b2u = bytes_to_unicode()
+    vocab = {b2u[b]: b for b in range(256)}
+    (d / "tokenizer.json").write_text(json.dumps({"model": {"vocab": vocab, "merges": []},
+                                                  "added_tokens": [{"content": "<|im_start|>", "id": 256},
+                                                                   {"content": "<|im_end|>", "id": 257}]}))
+    plain = BpeTokenizer.from_file(str(d / "tokenizer.json"))
+    assert plain.chat_template is None and plain.apply_chat_template(msgs) == render_chatml(msgs, True)
+    (d / "tokenizer_config.json").write_text(json.dumps({"chat_template": "{% for m in messages %}[{{ m.role }}] {{ m.content }}\\n{% endfor %}{{ eos_token }}",
+                                                         "eos_token": {"content": "<|im_end|>"}}))
+    own = BpeTokenizer.from_file(str(d / "tokenizer.json"))
+    assert own.apply_chat_template(msgs) == "[system] be brief\\n[user] hi\\n<|im_end|>"
+    (d / "chat_template.jinja").write_text("J:{{ messages | length }}")
+    assert BpeTokenizer.from_file(str(d / "tokenizer.json")).apply_chat_template(msgs) == "J:2"
