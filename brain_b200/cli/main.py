@@ -57,6 +57,8 @@ infrastructure
 global flags
   --device auto|cpu|cuda[:N]      --trace-<family> 0-5   --trace name=level[,…]
   --trace-format text|json        --trace-output -|PATH   (env: BRAIN_TRACE, BRAIN_DEVICE, BRAIN_PROFILE)
+  --device: cpu | gpu | gpuN | gpu0,gpu1 | cpuN | cpuA-B | gpu1,cpu0-3   (indexed CPU selections pin the
+            process affinity and size the thread pool; GPU indices are sorted by PCI bus id)
 """
 
 

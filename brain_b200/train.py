@@ -67,11 +67,12 @@ def load_dataset(dirpath: str, opts: FitOpts):
 
 
 def pick_device(name: str = "auto") -> torch.device:
-    if name in ("auto", ""):
-        return torch.device("cuda:0") if torch.cuda.is_available() else torch.device("cpu")
-    if name in ("gpu", "cuda"):
-        return torch.device("cuda:0")
-    return torch.device(name)
+    """The device single-device work runs on for a ``--device`` selection (see utils.devices for
+    the grammar); an indexed CPU selection also pins the affinity and sizes the thread pool."""
+    from .utils.devices import apply_selection, parse_selection
+    if name in ("cuda",) or name.startswith("cuda:"):
+        return torch.device(name if ":" in name else "cuda:0")
+    return apply_selection(parse_selection(name)).first()
 
 
 def fit(data_dir: str, build_model: Callable[[int, int], torch.nn.Module], opts: FitOpts,

@@ -602,3 +602,32 @@ def test_checkpoint_chat_template_is_rendered(tmp_path):
     assert own.apply_chat_template(msgs) == "[system] be brief\\n[user] hi\\n<|im_end|>"
     (d / "chat_template.jinja").write_text("J:{{ messages | length }}")
     assert BpeTokenizer.from_file(str(d / "tokenizer.json")).apply_chat_template(msgs) == "J:2"
+
+
+def test_device_selection_grammar():
+    import os
+    import torch
+    from brain_b200.train import pick_device
+    from brain_b200.utils.devices import apply_selection, parse_selection
+    s = parse_selection("")
+    assert s.gpus is None and s.cpu and s.cores is None
+    assert parse_selection("cpu").gpus == [] and parse_selection("cpu").first() == torch.device("cpu")
+    assert parse_selection("gpu").gpus is None and not parse_selection("gpu").cpu
+    s = parse_selection("gpu1,cpu0-3")
+    assert s.gpus == [1] and s.cpu and s.cores == [0, 1, 2, 3]
+    assert parse_selection("gpu0,gpu1").gpus == [0, 1] and parse_selection("cuda:2").gpus == [2]
+    assert parse_selection("cpu21").cores == [21] and parse_selection("gpu,cpu").gpus is None
+    for bad in ("npu", "vulkan", "tpu", "cpu3-1", "cpux"):
+        with pytest.raises(ValueError):
+            parse_selection(bad)
+    before = os.sched_getaffinity(0)
+    threads = torch.get_num_threads()
+    try:
+        core = min(before)
+        assert pick_device(f"cpu{core}") == torch.device("cpu")
+        assert os.sched_getaffinity(0) == {core} and torch.get_num_threads() == 1
+        with pytest.raises(ValueError):
+            apply_selection(parse_selection("cpu100000"))
+    finally:
+        os.sched_setaffinity(0, before)
+        torch.set_num_threads(threads)
