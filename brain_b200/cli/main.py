@@ -51,7 +51,8 @@ infrastructure
   caps                                            capability manifests of the servable models
   serve [--stdio | --openai [8788] --anthropic [8787] --openrouter [8789]] [--api-keys-out F
         --ready-file P --max-new N --temp X --top-k K --seed S -v N]
-  import <FILE|DIR> [--out F]     quantize <SRC> [--out F]
+  import <FILE|DIR> [--out F | --id VENDOR/REPO [--models-dir D]] | import --list
+  quantize <SRC> [--out F --tier Q8_0 --keep SUBSTR... --plan]
   help | --help | --version
 
 global flags
@@ -293,9 +294,14 @@ def _import_file(rest, device):
     """``brain import <FILE|DIR>``: a Hugging Face directory (or one safetensors file inside one)."""
     from .qwen_cli import run_qwen
     a = Args(rest)
+    if a.take_flag("--list"):
+        for arch in archs.all_archs():
+            print(f"{arch.id:<14} {'importable (Hugging Face safetensors directory)' if arch.id == 'qwen3' else 'no importer in this build'}")
+        return 0
     src = a.positional()
     if src is None:
-        print("usage: brain import <hf_dir|model.safetensors> [--out F]", file=sys.stderr)
+        print("usage: brain import <hf_dir|model.safetensors> [--out F | --id VENDOR/REPO] | brain import --list",
+              file=sys.stderr)
         return 2
     d = src if os.path.isdir(src) else os.path.dirname(src) or "."
     return run_qwen(["import", "--hf", d] + a.leftover(), device)
@@ -306,11 +312,32 @@ def _quantize(rest, device):
     a = Args(rest)
     src = a.positional()
     out = a.take_str("--out")
+    tier = (a.take_str("--tier") or "Q8_0").upper()
+    keep = a.take_all("--keep")
+    plan_only = a.take_flag("--plan")
     a.finish()
     if src is None:
-        print("usage: brain quantize <SRC.safetensors> [--out F]", file=sys.stderr)
+        print("usage: brain quantize <SRC.safetensors> [--out F --tier Q8_0 --keep SUBSTR... --plan]", file=sys.stderr)
         return 2
+    if tier not in ("Q8_0", "W8", "INT8"):
+        print(f"--tier {tier}: this build writes per-row symmetric int8 (Q8_0-class) only; the GGUF k-quant tiers "
+              "are not built", file=sys.stderr)
+        return 2
+    if plan_only:
+        from ..checkpoint import st as _st
+        from ..serve.quantize import _rows, plan as _plan
+        with _st.WeightReader(src) as r:
+            rows = _rows(r.config())
+            sizes = []
+            for n in r.names():
+                k = 1
+                for dim in r.shape(n):
+                    k *= dim
+                sizes.append((n, k))
+        for n, d in _plan(sizes, rows, keep):
+            print(f"{d:>5}  {n}")
+        return 0
     out = out or src.replace(".safetensors", "") + ".w8.safetensors"
-    info = quantize_checkpoint(src, out)
+    info = quantize_checkpoint(src, out, keep=keep)
     print(f"ok: wrote {out} ({info['tensors']} int8 tensors, {info['bytes_in'] / 2**20:.1f} MiB -> "
           f"{info['bytes_out'] / 2**20:.1f} MiB)")

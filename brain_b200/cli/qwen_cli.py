@@ -65,19 +65,52 @@ def _import(args, device):
     from ..checkpoint.hf_import import import_qwen
     a = Args(args)
     hf = a.str_or("--hf", "")
-    out = a.str_or("--out", "qwen.safetensors")
+    out = a.take_str("--out")
     block = a.opt_int("--block")
     dtype = a.str_or("--dtype", "F32").upper()
+    model_id = a.take_str("--id")
+    mdir = a.take_str("--models-dir")
+    if not hf:
+        hf = a.positional() or ""
+        if hf and os.path.isfile(hf):
+            hf = os.path.dirname(hf) or "."
     a.finish()
     if not hf:
-        print("usage: brain qwen3 import --hf <dir> --out qwen.safetensors", file=sys.stderr)
+        print("usage: brain qwen3 import <hf_dir|model.safetensors> [--out F | --id VENDOR/REPO [--models-dir D]] "
+              "[--block T --dtype F32|BF16]", file=sys.stderr)
         return 2
+    ref = None
+    if model_id:
+        from ..modelref import ModelRef, RefError
+        try:
+            ref = ModelRef.parse(model_id).base()
+        except RefError as e:
+            print(f"--id: {e}", file=sys.stderr)
+            return 2
+    tmp_out = out or ("qwen.safetensors" if ref is None else os.path.join(hf, ".brain_import.safetensors"))
     try:
-        import_qwen(hf, out, block, dtype)
+        import_qwen(hf, tmp_out, block, dtype, model_id=str(ref) if ref else None)
     except Exception as e:  # noqa: BLE001
         print(f"import failed: {e}", file=sys.stderr)
         return 1
-    print(f"ok: wrote {out}")
+    if ref is not None:
+        # place the converted weights (and the tokenizer files next to the source) in the model store
+        import shutil
+        from ..modelstore import Store
+        root = models_dir(mdir)
+        if not root:
+            print("no models directory resolved (set --models-dir, BRAIN_MODELS_DIR, or HOME)", file=sys.stderr)
+            return 1
+        tok = os.path.join(hf, "tokenizer.json")
+        lm = Store(root).install(ref, tmp_out, tok if os.path.exists(tok) else None)
+        for extra in ("tokenizer_config.json", "chat_template.jinja"):
+            if os.path.exists(os.path.join(hf, extra)):
+                shutil.copyfile(os.path.join(hf, extra), os.path.join(lm.dir, extra))
+        if out is None:
+            os.remove(tmp_out)
+        print(f"ok: installed {ref} -> {lm.weights}")
+    else:
+        print(f"ok: wrote {tmp_out}")
 
 
 def _export(args, device):

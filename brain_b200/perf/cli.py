@@ -35,6 +35,8 @@ def _make_target(spec: str, device: str, a_conc: int, ctx: int, weights: str, **
         model = synth_qwen(spec.split(":", 1)[1], dev)
         return (lambda: SchedulerTarget(model, max_batch=max(a_conc, 1), ctx=ctx, weights=weights, name=spec,
                                         **sched_kw)), model.cfg.vocab
+    if spec.startswith("qwen:"):
+        spec = "weights:" + spec[5:]
     if spec.startswith("weights:"):
         import torch
         from ..checkpoint import st
@@ -59,6 +61,9 @@ def run_perf(argv: List[str], device: str = "auto") -> int:
         print("targets:   fake | qwen-synth:LxDxH[xV] | weights:FILE | http:URL|KEY|MODEL")
         print("arrivals:  --concurrency N (closed loop) | --saturated | --rate R [--burstiness K]")
         return 0
+    if sub == "run" and len(argv) > 1 and argv[1] in ("latency", "throughput", "serve", "sweep", "startup", "mixed",
+                                                      "overload", "cancel", "kvcache", "soak", "faults"):
+        return run_perf(["scenario"] + argv[1:], device)     # `perf run <scenario>` as the reference spells it
     if sub == "run":
         a = Args(argv[1:])
         name = a.positional() or "interactive"

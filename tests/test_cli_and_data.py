@@ -228,6 +228,22 @@ def test_hf_import_export_roundtrip(tmp_path):
     a, _, _ = st.load(src)
     b, _, _ = st.load(back)
     assert list(a) == list(b) and all(torch.equal(a[k], b[k]) for k in a)
+    # `brain import <dir> --id VENDOR/REPO` converts and installs into the model store; the stored
+    # model is then what BRAIN_MODEL resolves
+    from brain_b200.cli.main import main
+    from brain_b200.modelref import ModelRef
+    from brain_b200.modelstore import Store
+    (tmp_path / "hf" / "tokenizer.json").write_text("{}")
+    (tmp_path / "hf" / "tokenizer_config.json").write_text('{"chat_template": "x"}')
+    root = str(tmp_path / "models")
+    assert main(["import", str(tmp_path / "hf"), "--id", "Acme/Tiny-0.1B", "--models-dir", root, "--block", "16"]) == 0
+    lm = Store(root).local(ModelRef.parse("Acme/Tiny-0.1B"))
+    assert lm is not None and lm.card.id == "Acme/Tiny-0.1B" and lm.tokenizer.endswith("tokenizer.json")
+    assert os.path.exists(os.path.join(lm.dir, "tokenizer_config.json"))
+    c, _, _ = st.load(lm.weights)
+    assert all(torch.equal(a[k], c[k]) for k in a)
+    assert main(["import", str(tmp_path / "hf"), "--id", "no-slash"]) == 2
+    assert main(["import", "--list"]) == 0
 
 
 def test_quantize_checkpoint(tmp_path):
@@ -346,6 +362,12 @@ def test_cli_end_to_end(tmp_path, capsys):
     assert main(["gradcheck"]) == 0
     assert "0 failures" in capsys.readouterr().out
     assert main(["quantize", q, "--out", os.path.join(o, "q.w8.safetensors")]) == 0
+    capsys.readouterr()
+    assert main(["quantize", q, "--plan", "--keep", "blocks.0."]) == 0
+    plan = capsys.readouterr().out.splitlines()
+    assert any(l.split() == ["q8", "blocks.1.attn.wq.weight"] for l in plan)
+    assert any(l.split() == ["bf16", "blocks.0.attn.wq.weight"] for l in plan)        # kept by --keep
+    assert main(["quantize", q, "--tier", "Q4_K_M"]) == 2
 
 
 def test_console_script_runs():
