@@ -152,6 +152,81 @@ class MockResident(ResidentModel):
                        {"embeddings": Blob("bytes", raw, {"shape": [1, EMBED_DIM]})})
 
 
+# ------------------------------------------------------------------------------------ GPT (char level)
+class GptResident(ResidentModel):
+    """A character-level GPT checkpoint (``brain gpt2 train``) behind the ``generate`` action: the
+    prompt is continued token by token without a KV cache — these are small models — and every
+    character is streamed as it is sampled (reference: ``brain serve --stdio --gpt <ckpt>``,
+    crates/cli/src/run_cli.rs:186-263)."""
+
+    def __init__(self, model, itos, model_id: str = "brain/gpt2", defaults: Optional[Dict] = None):
+        from ..data.tokenizer import CharTokenizer
+        self.id = model_id
+        self.model = model.eval()
+        self.tok = CharTokenizer(itos)
+        self.defaults = dict(defaults or {})
+        self._lock = threading.Lock()
+
+    def manifest(self) -> Manifest:
+        gen = generate_spec("character-level text continuation")
+        for p in gen.params:
+            if p.name in self.defaults:
+                p.default = self.defaults[p.name]
+            if p.name == "chat":
+                p.default = False
+        return Manifest(self.id, "GPT-2 style decoder (character vocabulary)", [gen], self.model.cfg.block_size)
+
+    def context_length(self):
+        return self.model.cfg.block_size
+
+    def run(self, action: str, inv: Invocation, progress: ProgressFn) -> Outcome:
+        if action != "generate":
+            raise ActionError(f"{self.id}: unknown action '{action}'")
+        import torch
+        from ..data.rng import Rng
+        p = inv.params
+        text = last_user_text(p) or "\n"
+        try:
+            ids = self.tok.encode(text)
+        except ValueError as e:
+            raise ActionError("invalid_request", str(e)) from None
+        max_new = max(int(p.get("max_new", 128)), 1)
+        temp, top_k = float(p.get("temp", 0.8)), int(p.get("top_k", 40))
+        rng = Rng(int(p.get("seed", 0)) or 1234)
+        block = self.model.cfg.block_size
+        dev = next(self.model.parameters()).device
+        out: List[int] = []
+        with self._lock, torch.no_grad():
+            for i in range(max_new):
+                if inv.cancel.is_cancelled():
+                    raise ActionError("cancelled", "cancelled")
+                ctx = torch.tensor([(ids + out)[-block:]], device=dev, dtype=torch.int32)
+                logits = self.model(ctx)[0, -1].float()
+                if temp <= 0:
+                    nxt = int(logits.argmax())
+                else:
+                    logits = logits / temp
+                    if 0 < top_k < logits.numel():
+                        thr = torch.topk(logits, top_k).values[-1]
+                        logits = torch.where(logits < thr, torch.full_like(logits, float("-inf")), logits)
+                    cdf = torch.cumsum(torch.softmax(logits, dim=-1).cpu(), 0)
+                    nxt = int(torch.searchsorted(cdf, torch.tensor(rng.next_f32())).clamp_max(cdf.numel() - 1))
+                out.append(nxt)
+                progress(Progress("token", i, max_new, self.tok.decode([nxt])))
+        return Outcome({"prompt_tokens": len(ids), "completion_tokens": len(out), "finish_reason": "length"},
+                       {"text": Blob("text", self.tok.decode(out).encode())})
+
+
+def load_gpt(path: str, device: str = "auto", defaults: Optional[Dict] = None) -> GptResident:
+    from ..checkpoint import st
+    from ..train import pick_device
+    model, cfg, card = st.load_model(path, device=pick_device(device))
+    itos = (cfg or {}).get("itos")
+    if not itos:
+        raise ValueError(f"{path}: the checkpoint carries no character vocabulary (train it with `brain gpt2 train`)")
+    return GptResident(model, itos, card.id if card is not None and card.id else "brain/gpt2", defaults)
+
+
 # ------------------------------------------------------------------------------------ language model
 class _Job:
     __slots__ = ("prompt", "max_new", "params", "seed", "ignore_eos", "stops", "on_token", "done", "rid",
@@ -430,6 +505,9 @@ def registry_from_env(load: bool = True, device: str = "auto") -> Dict[str, Resi
     reg: Dict[str, ResidentModel] = {}
     if os.environ.get("BRAIN_MOCK"):
         reg[MockResident.id] = MockResident()
+    if os.environ.get("BRAIN_GPT_WEIGHTS") and load:
+        g = load_gpt(os.environ["BRAIN_GPT_WEIGHTS"], device)
+        reg[g.id] = g
     if os.environ.get("BRAIN_QWEN_WEIGHTS") or os.environ.get("BRAIN_MODEL"):
         if load:
             m = load_llm_from_env(device)

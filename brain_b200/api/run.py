@@ -45,9 +45,12 @@ def run_serve(argv: List[str], device: str = "auto") -> int:
         v = a.take_str(flag)
         if v is not None:
             defaults[key] = conv(v)
-    for f in ("--dbus", "--dbus-system", "--yolo", "--gpt"):
+    gpt_ckpt = a.take_str("--gpt")
+    for f in ("--dbus", "--dbus-system"):
         if a.take_flag(f):
-            print(f"serve: {f} is not available in this build (no D-Bus / vision stack); ignoring", file=sys.stderr)
+            print(f"serve: {f} is not available in this build (no D-Bus); ignoring", file=sys.stderr)
+    if a.take_str("--yolo") is not None:
+        print("serve: --yolo is not available in this build (no vision stack); ignoring", file=sys.stderr)
     for f in ("--dbus-name", "--reserve-gb", "--models-dir", "--conf"):
         a.take_str(f)
     a.finish()
@@ -57,6 +60,14 @@ def run_serve(argv: List[str], device: str = "auto") -> int:
               file=sys.stderr)
         return 2
     models = registry_from_env(load=True, device=device)
+    if gpt_ckpt:
+        from .resident import load_gpt
+        try:
+            g = load_gpt(gpt_ckpt, device, defaults)
+        except Exception as e:  # noqa: BLE001
+            print(f"serve: --gpt {gpt_ckpt}: {e}", file=sys.stderr)
+            return 1
+        models[g.id] = g
     if not models:
         print("serve: no model selected — set BRAIN_QWEN_WEIGHTS (and BRAIN_QWEN_TOKENIZER), BRAIN_MODEL (a model-store reference) or BRAIN_MOCK=1",
               file=sys.stderr)

@@ -371,3 +371,32 @@ def test_stats_snapshot_and_brain_top(srv, capsys):
     assert "brain top" in out and MockResident.id in out and "connections" in out
     assert main(["top", "--url", url, "--key", "sk-brain-" + "0" * 32, "--once"]) == 1
     assert main(["top", "--url", url]) == 2
+
+
+def test_serve_stdio_with_a_gpt_checkpoint(tmp_path):
+    """``brain serve --stdio --gpt <ckpt>``: a character-level GPT checkpoint is served through the
+    same capability API (manifest, streamed tokens, seeded sampling, vocabulary errors)."""
+    import torch
+    from brain_b200.checkpoint import st
+    from brain_b200.models.config import GptConfig
+    from brain_b200.models.gpt2 import Gpt2
+    itos = list("\n abcdefghijklmnopqrstuvwxyz=+0123456789")
+    cfg = GptConfig(vocab=len(itos), block_size=32, n_layers=1, d_model=16, n_heads=2, d_ff=32)
+    m = Gpt2(cfg).init_weights(1)
+    ck = str(tmp_path / "g.safetensors")
+    conf = m.config_json()
+    conf["itos"] = itos
+    st.save(ck, m.reference_state(), conf, None)
+    with Brain(transport="jsonl", args=["--gpt", ck, "--max-new", "6", "--seed", "7"], device="cpu") as b:
+        man = next(x for x in b.manifests() if x["model"] == "brain/gpt2")
+        gen = next(a for a in man["actions"] if a["name"] == "generate")
+        assert next(p for p in gen["params"] if p["name"] == "max_new")["default"] == 6
+        toks = []
+        out = b.generate(prompt="abc", model="brain/gpt2", on_token=toks.append)
+        assert len(out.text()) == 6 and "".join(toks) == out.text() and out.get("completion_tokens") == 6
+        again = b.generate(prompt="abc", model="brain/gpt2")
+        assert again.text() == out.text()                       # same seed, same text
+        greedy = b.generate(prompt="abc", model="brain/gpt2", temp=0.0, max_new=4)
+        assert len(greedy.text()) == 4
+        with pytest.raises(BrainError):
+            b.generate(prompt="ABC!", model="brain/gpt2")        # characters outside the vocabulary
