@@ -505,9 +505,18 @@ def registry_from_env(load: bool = True, device: str = "auto") -> Dict[str, Resi
     reg: Dict[str, ResidentModel] = {}
     if os.environ.get("BRAIN_MOCK"):
         reg[MockResident.id] = MockResident()
-    if os.environ.get("BRAIN_GPT_WEIGHTS") and load:
-        g = load_gpt(os.environ["BRAIN_GPT_WEIGHTS"], device)
-        reg[g.id] = g
+    if os.environ.get("BRAIN_GPT_WEIGHTS"):
+        if load:
+            g = load_gpt(os.environ["BRAIN_GPT_WEIGHTS"], device)
+            reg[g.id] = g
+        else:
+            class _GptStub(ResidentModel):
+                id = "brain/gpt2"
+
+                def manifest(self):
+                    return Manifest(self.id, "GPT-2 style decoder (character vocabulary)",
+                                    [generate_spec("character-level text continuation")])
+            reg[_GptStub.id] = _GptStub()
     if os.environ.get("BRAIN_QWEN_WEIGHTS") or os.environ.get("BRAIN_MODEL"):
         if load:
             m = load_llm_from_env(device)
