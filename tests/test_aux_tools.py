@@ -1,0 +1,86 @@
+"""Auxiliary tools that run without a GPU: profile table (roof percentages and the impossible-rate
+flag), ncu launch-list aggregation, KV calibration and its use by the int8 KV cache, model
+evaluation helpers."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+
+def test_profile_table_flags_rates_above_the_roof():
+    from brain_b200.utils import profile
+    from brain_b200.utils.roof import Roof
+    roof = Roof(hbm_gbs=6000.0, bf16_tflops=1600.0, bf16_tflops_sustained=1400.0, i8_tops=3000.0, source="test")
+    agg = {
+        "gemm_bf16": {"n": 4, "ms": 4.0, "flops": 4 * 1.2e12, "int_ops": 0.0, "bytes": 4 * 2e8, "uncosted": 0},
+        "rmsnorm_fwd": {"n": 8, "ms": 0.4, "flops": 0.0, "int_ops": 0.0, "bytes": 8 * 2.0e8, "uncosted": 0},
+        "bogus": {"n": 1, "ms": 0.001, "flops": 1e13, "int_ops": 0.0, "bytes": 0.0, "uncosted": 0},
+    }
+    text = profile.render(agg, "unit", roof)
+    lines = {l.split()[0]: l for l in text.splitlines() if l and not l.startswith("-")}
+    assert "compute" in lines["gemm_bf16"] and "memory" in lines["rmsnorm_fwd"]
+    gemm_pct = float(lines["gemm_bf16"].split()[-1])
+    assert gemm_pct == pytest.approx(100 * (1.2e12 / 1600e12) / 1e-3, rel=1e-3)      # 75 % of the roof
+    assert "above the measured roof" in lines["bogus"] and "above" not in lines["gemm_bf16"]
+    assert "roof: HBM 6000 GB/s" in text
+
+
+def test_launch_list_aggregation(tmp_path):
+    from brain_b200.perf import launch_list
+    p = tmp_path / "l.csv"
+    p.write_text("==PROF== header line\n"
+                 '"ID","Process ID","Process Name","Host Name","Kernel Name","Context","Stream","Block Size","Grid Size",'
+                 '"Device","CC","Section Name","Metric Name","Metric Unit","Metric Value"\n'
+                 '"0","1","python","h","void bb::gemm_kernel<256, 0>(CUtensorMap_st)","1","7","(256, 1, 1)","(148, 1, 1)","0","10.0","Command line profiler metrics","gpu__time_duration.sum","ns","150,000"\n'
+                 '"1","1","python","h","void bb::gemm_kernel<256, 0>(CUtensorMap_st)","1","7","(256, 1, 1)","(148, 1, 1)","0","10.0","Command line profiler metrics","gpu__time_duration.sum","ns","50,000"\n'
+                 '"2","1","python","h","bb::adamw_kernel(float*)","1","7","(256, 1, 1)","(148, 1, 1)","0","10.0","Command line profiler metrics","gpu__time_duration.sum","us","100"\n')
+    agg, total, n = launch_list.aggregate(str(p))
+    assert n == 3 and total == pytest.approx(300.0)
+    assert agg["void bb::gemm_kernel<256, 0>"] == [2, pytest.approx(200.0)]
+    text = launch_list.render(agg, total, n)
+    assert text.splitlines()[2].split()[1] == "66.7%" and "adamw_kernel" in text
+
+
+def test_kv_calibration_feeds_the_int8_cache(tmp_path):
+    from brain_b200.models.config import QwenConfig
+    from brain_b200.models.qwen3 import Qwen3
+    from brain_b200.serve.calib import collect_kv_stats, load_kv_clip
+    from brain_b200.serve.engine import QwenEngine
+    cfg = QwenConfig(vocab=61, block_size=64, n_layers=2, d_model=32, n_heads=4, n_kv_heads=2, head_dim=8, d_ff=64)
+    m = Qwen3(cfg).init_weights(5).eval()
+    rng = np.random.RandomState(0)
+    seqs = [rng.randint(0, 61, n).tolist() for n in (20, 33, 7)]
+    stats = collect_kv_stats(m, seqs, percentile=0.99, block_size=8)
+    assert stats["tokens"] == 60 and len(stats["k_clip"]) == 2 and len(stats["k_clip"][0]) == 2
+    for li in range(2):
+        for h in range(2):
+            assert 0 < stats["k_clip"][li][h] <= stats["layers"][li]["k_absmax"][h]
+            assert 0 < stats["v_clip"][li][h] <= stats["layers"][li]["v_absmax"][h]
+    w = tmp_path / "model" / "w.safetensors"
+    w.parent.mkdir()
+    w.write_bytes(b"")
+    assert load_kv_clip(str(w)) is None
+    (w.parent / "kv_calib.json").write_text(json.dumps({"percentile": 0.99, "k": stats["k_clip"], "v": stats["v_clip"]}))
+    clip = load_kv_clip(str(w))
+    eng = QwenEngine(m, block_size=8, num_blocks=16, max_seq_len=64, max_prefill=64, kv_dtype="int8", kv_clip=clip)
+    bt = np.arange(8, dtype=np.int32)
+    eng.prefill_chunk(np.asarray(seqs[1], dtype=np.int32), 0, bt, True)
+    for li in range(2):        # no stored row scale exceeds its head's ceiling / 127
+        for h in range(2):
+            assert float(eng.ks[li][:, h].max()) <= stats["k_clip"][li][h] / 127 + 1e-9
+            assert float(eng.vs[li][:, h].max()) <= stats["v_clip"][li][h] / 127 + 1e-9
+
+
+def test_eval_helpers(tmp_path):
+    from brain_b200.cli.main import main
+    from brain_b200.eval import exact_match, val_perplexity
+    d, w = str(tmp_path / "calc"), str(tmp_path / "g.safetensors")
+    assert main(["data", "gen", "calculator", "--out", d, "--n", "300", "--seed", "2"]) == 0
+    assert main(["gpt2", "train", d, "--out", w, "--steps", "4", "--batch", "4", "--block", "16", "--layers", "1",
+                 "--d-model", "16", "--heads", "2", "--mask", "=", "--align", "--device", "cpu"]) == 0
+    ppl = val_perplexity(w, d, batches=2)
+    assert ppl == ppl and 1.0 < ppl < 1e4
+    em = exact_match(w, d, samples=4)
+    assert 0.0 <= (em if isinstance(em, float) else em[0]) <= 1.0
