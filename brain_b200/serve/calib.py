@@ -21,9 +21,10 @@ def collect_kv_stats(model, seqs: Sequence[Sequence[int]], percentile: float = 0
     nblk = -(-longest // block_size)
     eng = QwenEngine(model, block_size=block_size, num_blocks=nblk + 1, max_seq_len=nblk * block_size,
                      max_prefill=min(longest, 2048))
+    from ..utils.actstats import Collector
     L, hk = len(eng.layers), eng.hk
-    k_abs: List[List[List[torch.Tensor]]] = [[[] for _ in range(hk)] for _ in range(L)]
-    v_abs: List[List[List[torch.Tensor]]] = [[[] for _ in range(hk)] for _ in range(L)]
+    cap = max(2, (min(max_samples, 1 << 20) // 2) * 2)
+    stats = Collector(cap)                      # bounded memory however long the calibration set is
     table = np.arange(nblk, dtype=np.int32)
     total = 0
     for s in seqs:
@@ -37,23 +38,20 @@ def collect_kv_stats(model, seqs: Sequence[Sequence[int]], percentile: float = 0
         used = -(-n // block_size)
         for li in range(L):
             # pool layout [blocks][hk][bs][hd] -> per head [tokens, hd]
-            k = eng.kc[li][:used].permute(1, 0, 2, 3).reshape(hk, used * block_size, -1)[:, :n].abs().float()
-            v = eng.vc[li][:used].permute(1, 0, 2, 3).reshape(hk, used * block_size, -1)[:, :n].abs().float()
+            k = eng.kc[li][:used].permute(1, 0, 2, 3).reshape(hk, used * block_size, -1)[:, :n]
+            v = eng.vc[li][:used].permute(1, 0, 2, 3).reshape(hk, used * block_size, -1)[:, :n]
             for h in range(hk):
-                k_abs[li][h].append(k[h].reshape(-1).cpu())
-                v_abs[li][h].append(v[h].reshape(-1).cpu())
+                stats.observe(f"k.{li}.{h}", k[h])
+                stats.observe(f"v.{li}.{h}", v[h])
         total += n
 
-    def reduce(parts):
-        x = torch.cat(parts)
-        if x.numel() > max_samples:
-            x = x[torch.randperm(x.numel(), generator=torch.Generator().manual_seed(0))[:max_samples]]
-        return float(x.max()), float(torch.quantile(x, percentile))
+    def reduce(name):
+        return stats.streams[name].absmax, stats.quantile(name, percentile)
 
     out = {"tokens": total, "percentile": percentile, "layers": [], "k_clip": [], "v_clip": []}
     for li in range(L):
-        ks = [reduce(k_abs[li][h]) for h in range(hk)]
-        vs = [reduce(v_abs[li][h]) for h in range(hk)]
+        ks = [reduce(f"k.{li}.{h}") for h in range(hk)]
+        vs = [reduce(f"v.{li}.{h}") for h in range(hk)]
         out["layers"].append({"layer": li, "k_absmax": [a for a, _ in ks], "v_absmax": [a for a, _ in vs]})
         out["k_clip"].append([q for _, q in ks])
         out["v_clip"].append([q for _, q in vs])

@@ -84,3 +84,20 @@ def test_eval_helpers(tmp_path):
     assert ppl == ppl and 1.0 < ppl < 1e4
     em = exact_match(w, d, samples=4)
     assert 0.0 <= (em if isinstance(em, float) else em[0]) <= 1.0
+
+
+def test_actstats_collector_keeps_a_uniform_strided_subsample():
+    from brain_b200.utils.actstats import Collector
+    c = Collector(cap=64)
+    x = torch.arange(1000, dtype=torch.float32)
+    for lo, hi in ((0, 7), (7, 130), (130, 131), (131, 1000)):      # ragged chunks, one stream
+        c.observe("ramp", -x[lo:hi])                                 # magnitudes are recorded
+    st = c.streams["ramp"]
+    assert st.seen == 1000 and st.absmax == 999.0 and st.stride == 16
+    kept = st.sample[:st.fill]
+    assert torch.equal(kept, torch.arange(0, 1000, 16, dtype=torch.float32))
+    assert c.quantile("ramp", 0.5) == pytest.approx(496.0, abs=16)
+    assert c.quantile("nope", 0.5) is None
+    c.observe("spiky", torch.cat([torch.ones(500), torch.tensor([100.0])]))
+    rep = c.report()
+    assert rep[0].name == "spiky" and rep[0].outlier_ratio == pytest.approx(100.0) and rep[0].seen == 501
