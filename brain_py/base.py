@@ -132,3 +132,9 @@ class BrainBase:
     def embed(self, text: str, *, model: Optional[str] = None, timeout: float = 120.0) -> List[float]:
         out = self.run(self._pick("embed", model), "embed", {"text": text}, timeout=timeout)
         return list(out.get("mean") or [])
+
+    def text2image(self, prompt: str, *, model: Optional[str] = None, timeout: float = 600.0, **params) -> bytes:
+        """Image bytes from the first model that provides ``text2image`` (none of the models this
+        server build ships does: the call then raises ``BrainError`` naming the missing action)."""
+        out = self.run(self._pick("text2image", model), "text2image", dict(params, prompt=prompt), timeout=timeout)
+        return out.bytes("image")

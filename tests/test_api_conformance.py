@@ -353,6 +353,8 @@ def test_brain_py_jsonl_stdio():
         with pytest.raises(BrainError):
             b.run("brain/none", "generate", {"prompt": "x"})
         assert len(b.embed("abc")) == 8
+        with pytest.raises(BrainError):
+            b.text2image("a cat")              # no resident provides the action
 
 
 def test_stats_snapshot_and_brain_top(srv, capsys):
