@@ -44,6 +44,7 @@ infrastructure
   devices                                         list compute devices
   flops --model qwen|gpt [--weights F --batch B --block T --train --i8 --stages N --run]
   gradcheck [--model gpt|qwen|qwen2|qwen_lora|moe|qwen_moe|all] [--dirs N]
+  bench [--gpus N --steps K …] | bench learn [copy mod_add parity] [--arch qwen|gpt --steps N --seed S]
   perf list | run <scenario> [...] | compare A B | gate A B [--tolerance X] | faults [NAME…]
   top --url http://HOST:PORT (--key K | --api-keys FILE) [--interval S --once --json]
   bench [--gpus N --steps K --warmup W]           the training benchmark (bench.py)
@@ -107,6 +108,10 @@ def main(argv: Optional[List[str]] = None) -> int:
         return _import_file(r.rest, device) or 0
     if r.kind == "quantize":
         return _quantize(r.rest, device) or 0
+    if r.word in ("npu", "forecast", "capture", "dbus"):
+        print(f"brain {r.word}: not built by this framework (ONNX/NPU export, the forecasting models, camera "
+              "capture and the D-Bus service are outside what it covers)", file=sys.stderr)
+        return 2
     print(f"unknown command {r.word!r}; try `brain help`", file=sys.stderr)
     return 2
 
@@ -269,7 +274,37 @@ def _perf(args, device):
 
 
 def _bench(args, device):
+    """``brain bench learn [task…]``: the learnability battery (CPU or GPU); ``brain bench [flags]``:
+    the training-throughput benchmark at the repository root (needs a GPU)."""
+    if args and args[0] == "learn":
+        from .. import learnbench
+        from ..train import pick_device
+        a = Args(args[1:])
+        arch = a.str_or("--arch", "qwen")
+        steps = a.int_or("--steps", 400)
+        seed = a.int_or("--seed", 0)
+        names = []
+        while True:
+            n = a.positional()
+            if n is None:
+                break
+            names.append(n)
+        a.finish()
+        if arch not in ("qwen", "gpt"):
+            print("--arch: qwen | gpt", file=sys.stderr)
+            return 2
+        try:
+            res = learnbench.run_battery(names, arch, steps, seed, str(pick_device(device)))
+        except ValueError as e:
+            print(str(e), file=sys.stderr)
+            return 2
+        return 0 if all(r["passed"] for r in res) else 1
     import runpy
+    import torch
+    if not torch.cuda.is_available():
+        print("brain bench: the throughput benchmark needs a CUDA device; `brain bench learn` runs the "
+              "learnability battery on the CPU", file=sys.stderr)
+        return 1
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     sys.argv = [os.path.join(root, "bench.py")] + list(args)
     runpy.run_path(sys.argv[0], run_name="__main__")

@@ -653,3 +653,16 @@ def test_device_selection_grammar():
     finally:
         os.sched_setaffinity(0, before)
         torch.set_num_threads(threads)
+
+
+def test_learnability_battery(capsys):
+    """Tiny decoders learn copy / modular addition / running parity on CPU in a few hundred steps
+    (both families), through the same trainer and kernels' CPU reference path as everything else."""
+    from brain_b200 import learnbench
+    from brain_b200.cli.main import main
+    r = learnbench.run_battery(["copy", "parity"], "qwen", steps=250, log=lambda s: None)
+    assert [x["task"] for x in r] == ["copy", "parity"] and all(x["passed"] for x in r), r
+    assert main(["bench", "learn", "mod_add", "--arch", "gpt", "--steps", "300", "--device", "cpu"]) == 0
+    assert "PASS" in capsys.readouterr().out
+    assert main(["bench", "learn", "nosuchtask", "--device", "cpu"]) == 2
+    assert main(["npu", "export"]) == 2 and "not built" in capsys.readouterr().err
