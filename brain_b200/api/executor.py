@@ -50,8 +50,13 @@ class _Lane:
 
 class Executor:
     def __init__(self, models: Dict[str, ResidentModel], admit_deadline_s: float = ADMIT_DEADLINE_S,
-                 edge_limit: int = EDGE_MAX_CONCURRENT, workers: int = 320):
+                 edge_limit: int = EDGE_MAX_CONCURRENT, workers: int = 320, residency=None):
+        """``models`` are resident from the start; ``residency`` (api.residency.Residency) adds models
+        that are loaded on first use and evicted least-recently-used when memory runs out."""
         self.lanes = {mid: _Lane(m) for mid, m in models.items()}
+        self.residency = residency
+        if residency is not None:
+            residency.on_evict = self._evicted
         self.admit_deadline_s = admit_deadline_s
         self.edge_limit = edge_limit
         self._edge = 0
@@ -61,17 +66,48 @@ class Executor:
 
     # ---- lookup
     def models(self) -> Dict[str, ResidentModel]:
-        return {k: l.model for k, l in self.lanes.items()}
+        """Every model a request may name: loaded ones, and stubs of those loaded on first use."""
+        out = {k: l.model for k, l in self.lanes.items()}
+        if self.residency is not None:
+            for mid in self.residency.known():
+                if mid not in out:
+                    out[mid] = self.residency.describe(mid)
+        return out
 
     def get(self, model_id: str) -> Optional[ResidentModel]:
         lane = self.lanes.get(model_id)
-        return lane.model if lane else None
+        if lane:
+            return lane.model
+        return self.residency.describe(model_id) if self.residency is not None else None
+
+    def _evicted(self, model_id: str, model) -> None:
+        self.lanes.pop(model_id, None)
+
+    def _lane(self, model_id: str):
+        """(lane, release) — loads the model through the residency manager when it is not resident."""
+        lane = self.lanes.get(model_id)
+        if lane is not None and (self.residency is None or model_id not in self.residency.suppliers):
+            return lane, None
+        if self.residency is None or model_id not in self.residency.known():
+            raise KeyError(model_id)
+        from .residency import InsufficientMemory
+        try:
+            model = self.residency.acquire(model_id, COLD_ADMIT_DEADLINE_S)
+        except (InsufficientMemory, TimeoutError) as e:
+            raise Busy(str(e))
+        lane = self.lanes.get(model_id)
+        if lane is None or lane.model is not model:
+            lane = self.lanes[model_id] = _Lane(model)
+        return lane, (lambda: self.residency.release(model_id))
 
     def in_flight(self) -> int:
         return self._edge
 
     def stats(self) -> Dict:
-        return {mid: vars(l.stats).copy() for mid, l in self.lanes.items()}
+        out = {mid: vars(l.stats).copy() for mid, l in self.lanes.items()}
+        if self.residency is not None:
+            out["_residency"] = self.residency.stats()
+        return out
 
     # ---- edge admission (called by the HTTP layer before any work)
     def edge_enter(self) -> None:
@@ -87,13 +123,22 @@ class Executor:
     # ---- run (blocking; call from a worker thread)
     def run(self, model_id: str, action: str, inv: Invocation,
             progress: Optional[Callable[[Progress], None]] = None) -> Outcome:
-        lane = self.lanes.get(model_id)
-        if lane is None:
+        described = self.get(model_id)
+        if described is None:
             raise KeyError(model_id)
-        spec = lane.model.manifest().action(action)
+        spec = described.manifest().action(action)
         if spec is None:
             raise ActionError(f"model '{model_id}' has no action '{action}'", "not_implemented")
-        inv.params = spec.validate(inv.params, inv.blobs)
+        inv.params = spec.validate(inv.params, inv.blobs)     # before any load: a bad request costs nothing
+        lane, release = self._lane(model_id)
+        try:
+            return self._run_on(lane, model_id, action, inv, progress)
+        finally:
+            if release is not None:
+                release()
+
+    def _run_on(self, lane, model_id: str, action: str, inv: Invocation,
+                progress: Optional[Callable[[Progress], None]] = None) -> Outcome:
         deadline = self.admit_deadline_s if lane.warm else max(self.admit_deadline_s, COLD_ADMIT_DEADLINE_S)
         t0 = time.time()
         with lane.lock:
@@ -142,7 +187,9 @@ class Executor:
         return self.pool.submit(self.run, model_id, action, inv, progress)
 
     def close(self):
-        for lane in self.lanes.values():
+        if self.residency is not None:
+            self.residency.close()
+        for lane in list(self.lanes.values()):
             try:
                 lane.model.close()
             except Exception:

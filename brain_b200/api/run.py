@@ -30,6 +30,41 @@ def _port_flag(args: List[str], name: str):
     return DEFAULT_PORTS[name[2:]]
 
 
+def store_residency(models_dir, reserve_gb, device: str, already: set):
+    """Suppliers for every model in the on-disk store (``--models-dir`` / BRAIN_MODELS_DIR; the default
+    root is only used when one of the two names it), loaded on first use.  Budget per device: its
+    memory minus ``--reserve-gb`` (default 8) on a GPU, ``BRAIN_RESIDENCY_BUDGET_GB`` (default 64) on
+    the CPU.  None when there is no store or it is empty."""
+    import os
+    from ..modelstore import Store
+    from .residency import Residency, StoreSupplier
+    root = models_dir or os.environ.get("BRAIN_MODELS_DIR")
+    if not root or not os.path.isdir(root):
+        return None
+    sup = {}
+    for lm in Store(root).scan():
+        if lm.card is not None and getattr(lm.card, "family", "qwen") not in ("qwen", "qwen3"):
+            continue
+        s = StoreSupplier(lm, weights="int8" if os.environ.get("BRAIN_QWEN_INT8") == "1" else "bf16",
+                          kv_dtype="int8" if os.environ.get("BRAIN_QWEN_KV_INT8") == "1" else "bf16")
+        if s.id not in already:
+            sup[s.id] = s
+    if not sup:
+        return None
+    import torch
+    from ..train import pick_device
+    dev = pick_device(device)
+    if dev.type == "cuda":
+        reserve = float(reserve_gb) if reserve_gb else 8.0
+        budgets = {}
+        for i in range(torch.cuda.device_count()):
+            total = torch.cuda.get_device_properties(i).total_memory
+            budgets[f"cuda:{i}"] = max(int(total - reserve * 2**30), 0)
+    else:
+        budgets = {"cpu": int(float(os.environ.get("BRAIN_RESIDENCY_BUDGET_GB", "64")) * 2**30)}
+    return Residency(sup, budgets)
+
+
 def run_serve(argv: List[str], device: str = "auto") -> int:
     args = list(argv)
     ports = {p: _port_flag(args, "--" + p) for p in ("anthropic", "openai", "openrouter")}
@@ -51,12 +86,14 @@ def run_serve(argv: List[str], device: str = "auto") -> int:
             print(f"serve: {f} is not available in this build (no D-Bus); ignoring", file=sys.stderr)
     if a.take_str("--yolo") is not None:
         print("serve: --yolo is not available in this build (no vision stack); ignoring", file=sys.stderr)
-    for f in ("--dbus-name", "--reserve-gb", "--models-dir", "--conf"):
+    models_dir = a.take_str("--models-dir")
+    reserve_gb = a.take_str("--reserve-gb")
+    for f in ("--dbus-name", "--conf"):
         a.take_str(f)
     a.finish()
     if not stdio and not ports:
         print("usage: brain serve [--stdio | --openai [PORT] --anthropic [PORT] --openrouter [PORT]] "
-              "[--api-keys-out FILE --ready-file PATH -v N]   (models: BRAIN_MOCK=1, BRAIN_QWEN_WEIGHTS=FILE, BRAIN_MODEL=vendor/repo[:owner:name:tag])",
+              "[--api-keys-out FILE --ready-file PATH --models-dir DIR --reserve-gb G -v N]   (models: BRAIN_MOCK=1, BRAIN_QWEN_WEIGHTS=FILE, BRAIN_MODEL=vendor/repo[:owner:name:tag])",
               file=sys.stderr)
         return 2
     models = registry_from_env(load=True, device=device)
@@ -68,11 +105,12 @@ def run_serve(argv: List[str], device: str = "auto") -> int:
             print(f"serve: --gpt {gpt_ckpt}: {e}", file=sys.stderr)
             return 1
         models[g.id] = g
-    if not models:
+    residency = store_residency(models_dir, reserve_gb, device, set(models))
+    if not models and residency is None:
         print("serve: no model selected — set BRAIN_QWEN_WEIGHTS (and BRAIN_QWEN_TOKENIZER), BRAIN_MODEL (a model-store reference) or BRAIN_MOCK=1",
               file=sys.stderr)
         return 1
-    ex = Executor(models)
+    ex = Executor(models, residency=residency)
     shutdown.install()
     server = None
     try:
