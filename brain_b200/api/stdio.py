@@ -123,3 +123,75 @@ class StdioServer:
             self.handle(ev)
         for t in self._threads:
             t.join(timeout=30)
+
+
+# ------------------------------------------------------------------------------------ socket transports
+class SocketServer:
+    """The same JSONL protocol over a Unix domain socket or a loopback TCP port, one session per
+    connection (reference: crates/server/src/transport.rs:104-127 ``serve_unix`` / ``serve_tcp``; a
+    stale socket file is removed first).  ``start()`` returns once the listener is bound; ``close()``
+    stops accepting and closes the listener."""
+
+    def __init__(self, ex: Executor, unix_path: Optional[str] = None, tcp_port: Optional[int] = None,
+                 defaults: Optional[Dict] = None, max_connections: int = 64):
+        import socket
+        if (unix_path is None) == (tcp_port is None):
+            raise ValueError("give exactly one of unix_path / tcp_port")
+        self.ex, self.defaults = ex, defaults
+        self.unix_path = unix_path
+        if unix_path is not None:
+            import os
+            try:
+                os.unlink(unix_path)
+            except FileNotFoundError:
+                pass
+            self.sock = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+            self.sock.bind(unix_path)
+            os.chmod(unix_path, 0o600)          # the socket carries no authentication of its own
+        else:
+            self.sock = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+            self.sock.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+            self.sock.bind(("127.0.0.1", int(tcp_port)))      # loopback only, like the HTTP surfaces
+        self.port = self.sock.getsockname()[1] if unix_path is None else None
+        self.sock.listen(max_connections)
+        self._slots = threading.BoundedSemaphore(max_connections)
+        self._closed = False
+        self._thread: Optional[threading.Thread] = None
+
+    def _session(self, conn):
+        try:
+            with conn, conn.makefile("r", encoding="utf-8", newline="\n") as rd, \
+                    conn.makefile("w", encoding="utf-8", newline="\n") as wr:
+                StdioServer(self.ex, rd, wr, defaults=self.defaults).serve()
+        except (OSError, ValueError):
+            pass                                 # the peer went away mid-line
+        finally:
+            self._slots.release()
+
+    def _accept_loop(self):
+        while not self._closed:
+            try:
+                conn, _ = self.sock.accept()
+            except OSError:
+                return
+            if not self._slots.acquire(blocking=False):
+                conn.close()                     # at the connection limit: refuse rather than queue
+                continue
+            threading.Thread(target=self._session, args=(conn,), daemon=True).start()
+
+    def start(self) -> "SocketServer":
+        self._thread = threading.Thread(target=self._accept_loop, name="jsonl-accept", daemon=True)
+        self._thread.start()
+        return self
+
+    def close(self):
+        self._closed = True
+        try:
+            self.sock.close()
+        finally:
+            if self.unix_path is not None:
+                import os
+                try:
+                    os.unlink(self.unix_path)
+                except FileNotFoundError:
+                    pass

@@ -402,3 +402,44 @@ def test_serve_stdio_with_a_gpt_checkpoint(tmp_path):
         assert len(greedy.text()) == 4
         with pytest.raises(BrainError):
             b.generate(prompt="ABC!", model="brain/gpt2")        # characters outside the vocabulary
+
+
+def test_jsonl_protocol_over_unix_socket_and_tcp(tmp_path):
+    """The stdio protocol served per connection over a Unix socket and a loopback TCP port."""
+    import socket
+    from brain_b200.api.stdio import SocketServer
+    ex = Executor({MockResident.id: MockResident()})
+
+    def talk(sock):
+        rd, wr = sock.makefile("r", encoding="utf-8"), sock.makefile("w", encoding="utf-8")
+        assert json.loads(rd.readline())["event"] == "ready"
+        wr.write(json.dumps({"event": "action_request", "req_id": "7", "model": "brain/mock", "action": "generate",
+                             "params": {"prompt": "over a socket"}}) + "\n")
+        wr.flush()
+        text, final = "", None
+        while final is None:
+            ev = json.loads(rd.readline())
+            assert ev.get("req_id") == "7"
+            if ev["event"] == "action_progress":
+                text += ev.get("message", "")
+            elif ev["event"] in ("action_result", "error"):
+                final = ev
+        assert final["event"] == "action_result" and text == "You said: over a socket"
+    path = str(tmp_path / "brain.sock")
+    open(path, "w").write("stale")                       # a stale file at the path is replaced
+    u = SocketServer(ex, unix_path=path).start()
+    t = SocketServer(ex, tcp_port=0).start()
+    try:
+        assert oct(os.stat(path).st_mode & 0o777) == "0o600"
+        with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as s:
+            s.connect(path)
+            talk(s)
+        with socket.create_connection(("127.0.0.1", t.port), timeout=10) as s:
+            talk(s)
+        with pytest.raises(ValueError):
+            SocketServer(ex)
+    finally:
+        u.close()
+        t.close()
+        ex.close()
+    assert not os.path.exists(path)
