@@ -101,3 +101,72 @@ def test_actstats_collector_keeps_a_uniform_strided_subsample():
     c.observe("spiky", torch.cat([torch.ones(500), torch.tensor([100.0])]))
     rep = c.report()
     assert rep[0].name == "spiky" and rep[0].outlier_ratio == pytest.approx(100.0) and rep[0].seen == 501
+
+
+def test_hsm_bubbling_lca_ordering_and_run_to_completion():
+    """A controller in the shape of a serving session: Idle and Busy{Generating, Cancelling} under
+    Root.  Unhandled events bubble; a transition exits up to the least common ancestor and enters
+    down to the target; self-posted reminders are handled after the current event."""
+    from brain_b200.utils.hsm import Handled, Hsm, Super, Tran, Unhandled
+
+    class M:
+        parents = {"root": None, "idle": "root", "busy": "root", "generating": "busy", "cancelling": "busy"}
+
+        def __init__(self):
+            self.log, self.tokens, self.hsm = [], 0, None
+
+        def parent(self, s):
+            return self.parents[s]
+
+        def on_entry(self, s):
+            self.log.append("+" + s)
+
+        def on_exit(self, s):
+            self.log.append("-" + s)
+
+        def dispatch(self, s, ev):
+            if s == "idle" and ev == "user_text":
+                return Tran("generating")
+            if s == "generating" and ev == "tick":
+                self.tokens += 1
+                if self.tokens < 3:
+                    self.hsm.post("tick")          # reminder: one token per self-posted event
+                    return Handled
+                return Tran("idle")
+            if s == "generating" and ev == "cancel":
+                return Tran("cancelling")
+            if s == "cancelling" and ev == "ack":
+                return Tran("idle")
+            if s == "busy" and ev == "status":
+                self.log.append("busy!")
+                return Handled
+            if s == "cancelling" and ev == "status":
+                return Super("busy")
+            if s == "root" and ev == "status":
+                self.log.append("root!")
+                return Handled
+            return Unhandled
+    m = M()
+    h = m.hsm = Hsm(m, "idle")
+    h.init()
+    assert m.log == ["+root", "+idle"] and h.in_state("root") and not h.in_state("busy")
+    m.log.clear()
+    h.send("status")                                   # idle does not handle it: root does
+    assert m.log == ["root!"]
+    m.log.clear()
+    h.post("user_text")
+    h.post("tick")
+    h.run()                                            # the tick posts two more ticks to itself
+    assert m.tokens == 3 and h.state == "idle"
+    assert m.log == ["-idle", "+busy", "+generating", "-generating", "-busy", "+idle"]
+    m.log.clear()
+    m.tokens = 0
+    h.send("user_text")
+    h.send("cancel")                                   # sibling transition: busy is neither left nor re-entered
+    assert m.log == ["-idle", "+busy", "+generating", "-generating", "+cancelling"]
+    m.log.clear()
+    h.send("status")                                   # explicit Super("busy")
+    assert m.log == ["busy!"]
+    h.send("nonsense")                                 # unhandled everywhere: ignored
+    h.send("ack")
+    assert h.state == "idle" and m.log[-3:] == ["-cancelling", "-busy", "+idle"]
