@@ -200,8 +200,18 @@ class Qwen3(nn.Module):
         if pos is None:
             pos = torch.arange(T, device=dev, dtype=torch.int32).repeat(B)
         delta = None
+        recompute = getattr(self, "recompute_blocks", False) and torch.is_grad_enabled()
         for blk in self.blocks:
-            x, delta = blk(x, delta, B, T, cos, sin, pos)
+            if recompute:
+                # activation re-materialisation (the pipeline of crates/model/src/shard.rs:551-652 keeps
+                # only stage inputs and re-runs the forward in backward): keep the block's inputs only
+                from torch.utils.checkpoint import checkpoint
+                if delta is None:
+                    x, delta = checkpoint(lambda a, blk=blk: blk(a, None, B, T, cos, sin, pos), x, use_reentrant=False)
+                else:
+                    x, delta = checkpoint(lambda a, d, blk=blk: blk(a, d, B, T, cos, sin, pos), x, delta, use_reentrant=False)
+            else:
+                x, delta = blk(x, delta, B, T, cos, sin, pos)
         return x, delta
 
     def hidden(self, tokens=None, x_in=None, B=None, T=None):

@@ -31,7 +31,8 @@ def even_bounds(n_layers: int, pp: int) -> List[int]:
 class Trainer3D:
     def __init__(self, cfg, grid: Grid, device, model_cls=None, impl: str = "fused", schedule: str = "1f1b",
                  betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.1, grad_clip: Optional[float] = 1.0,
-                 seed: int = 1234, dtype: Optional[torch.dtype] = None, full_state=None, arena_mb: int = 1024):
+                 seed: int = 1234, dtype: Optional[torch.dtype] = None, full_state=None, arena_mb: int = 1024,
+                 recompute: bool = False):
         from ..models.qwen3 import Qwen3
         from .tp import TensorParallel
         model_cls = model_cls or Qwen3
@@ -76,6 +77,7 @@ class Trainer3D:
             else:
                 model.init_weights(seed)
         self.model = model
+        model.recompute_blocks = bool(recompute)    # keep block inputs only, re-run blocks in backward
         self.store = ParamStore(model, device=self.device, dtype=dt)
         self.opt = AdamW(self.store, betas=betas, eps=eps)
         self.wd, self.clip = weight_decay, grad_clip

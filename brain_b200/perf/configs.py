@@ -196,7 +196,8 @@ def train_3d(args) -> dict:
     cfg = QwenConfig.preset(args.model, args.seq)
     if args.layers:
         cfg.n_layers = args.layers
-    tr = Trainer3D(cfg, Grid(tp=tp, pp=pp, dp=1), dev, impl=args.impl, schedule=args.schedule, seed=1234)
+    tr = Trainer3D(cfg, Grid(tp=tp, pp=pp, dp=1), dev, impl=args.impl, schedule=args.schedule, seed=1234,
+                   recompute=args.recompute)
     gd = torch.Generator(device=dev).manual_seed(0)     # same seed on every rank: same batches
     n_micro, T = args.micro, args.seq
     count = n_micro * T
@@ -285,6 +286,8 @@ def main(argv=None):
     ap.add_argument("--micro-batch", type=int, default=1, help="train-ep: sequences per forward/backward")
     ap.add_argument("--experts", type=int, default=0)
     ap.add_argument("--arena-mb", type=int, default=4096)
+    ap.add_argument("--recompute", action="store_true",
+                    help="train-3d: keep block inputs only and re-run the blocks in backward")
     ap.add_argument("--no-recompute", action="store_true", help="train-ep: keep all block activations (more memory)")
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--layers", type=int, default=0, help="override depth (debug; invalidates the number)")

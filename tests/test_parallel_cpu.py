@@ -219,7 +219,7 @@ def test_pipeline_two_stages_match_single(sched):
             assert torch.allclose(gr, want[n], atol=2e-5), (sched, r, n)
 
 
-def _trainer3d_worker(rank, world, tp, pp, sched, dp=1):
+def _trainer3d_worker(rank, world, tp, pp, sched, dp=1, recompute=False):
     from brain_b200.models.config import QwenConfig
     from brain_b200.models.qwen3 import Qwen3
     from brain_b200.parallel.grid import Grid
@@ -229,7 +229,7 @@ def _trainer3d_worker(rank, world, tp, pp, sched, dp=1):
     full = Qwen3(cfg).init_weights(5)
     state = {k: v.detach().clone() for k, v in full.reference_state().items()}
     tr = Trainer3D(cfg, Grid(tp=tp, pp=pp, dp=dp), "cpu", schedule=sched, full_state=state, grad_clip=1.0,
-                   weight_decay=0.1)
+                   weight_decay=0.1, recompute=recompute)
     g = torch.Generator().manual_seed(3)
     toks = [torch.randint(0, 96, (2, 128), generator=g, dtype=torch.int32) for _ in range(4)]
     tgts = [torch.randint(0, 96, (2, 128), generator=g) for _ in range(4)]
@@ -238,15 +238,16 @@ def _trainer3d_worker(rank, world, tp, pp, sched, dp=1):
     return {"losses": losses, "state": out, "norm": float(tr.last_grad_norm)}
 
 
-@pytest.mark.parametrize("tp,pp,sched,dp", [(2, 2, "1f1b", 1), (2, 1, "1f1b", 1), (1, 2, "gpipe", 1), (1, 2, "1f1b", 2),
-                                             (2, 1, "1f1b", 2)])
-def test_trainer3d_matches_single_process(tp, pp, sched, dp):
+@pytest.mark.parametrize("tp,pp,sched,dp,recompute", [(2, 2, "1f1b", 1, False), (2, 1, "1f1b", 1, False),
+                                                       (1, 2, "gpipe", 1, True), (1, 2, "1f1b", 2, False),
+                                                       (2, 1, "1f1b", 2, True)])
+def test_trainer3d_matches_single_process(tp, pp, sched, dp, recompute):
     """Tensor x pipeline parallel training on gloo CPU ranks reproduces the single-process step:
     same losses, same global gradient norm, same weights after two optimiser steps."""
     from brain_b200.engine import Trainer
     from brain_b200.models.config import QwenConfig
     from brain_b200.models.qwen3 import Qwen3
-    res = run_ranks(_trainer3d_worker, tp * pp * dp, tp, pp, sched, dp)
+    res = run_ranks(_trainer3d_worker, tp * pp * dp, tp, pp, sched, dp, recompute)
     cfg = QwenConfig(vocab=96, block_size=128, n_layers=4, d_model=32, n_heads=4, n_kv_heads=2, head_dim=8, d_ff=64,
                      tie_embeddings=True)
     full = Qwen3(cfg).init_weights(5)
