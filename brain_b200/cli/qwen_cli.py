@@ -290,10 +290,11 @@ def _train(args, device, base: Optional[str]):
     dp_n = a.int_or("--dp", 1)
     preset = a.take_str("--preset")
     weighted = a.take_flag("--weighted")
+    recompute = a.take_flag("--recompute")
     a.finish()
     if data_dir is None:
         print("usage: brain qwen3 {train|finetune} <data_dir> --out F [--steps N --batch B --block T --lr X "
-              "--mask = --align --dp N --preset 0.6b --weighted]", file=sys.stderr)
+              "--mask = --align --dp N --preset 0.6b --weighted --recompute]", file=sys.stderr)
         return 2
     if dp_n > 1:
         return _relaunch(dp_n, ["qwen3", "finetune" if base else "train"] + args +
@@ -308,6 +309,11 @@ def _train(args, device, base: Optional[str]):
         return 1
 
     def build(vocab, blk):
+        m = _build(vocab, blk)
+        m.recompute_blocks = recompute      # keep block inputs only; re-run the blocks in backward
+        return m
+
+    def _build(vocab, blk):
         if preset:
             c = QwenConfig.preset(preset, blk)
             c.vocab = vocab
