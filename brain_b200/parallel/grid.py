@@ -85,3 +85,31 @@ class ProcessGroups:
     def next_stage(self) -> Optional[int]:
         r = self.ranks("pp")
         return r[self.pp_coord + 1] if self.pp_coord + 1 < len(r) else None
+
+
+class LocalGroups:
+    """One ``HostCollective`` group per tensor / pipeline / data group of a Grid, for ranks that are
+    threads of one process (reference: crates/model/src/grid.rs:91-136).  ``tp(r)`` / ``pp(r)`` /
+    ``dp(r)`` return rank ``r``'s collective handle; its ``rank`` attribute is ``r``'s index inside
+    that group."""
+
+    def __init__(self, grid: Grid, timeout_s: float = 60.0):
+        from .collective import HostCollective
+        self.grid = grid
+        self._by_axis = {}
+        for axis in ("tp", "pp", "dp"):
+            handles: List = [None] * grid.world
+            for members in grid.all_groups(axis):
+                group = HostCollective.group(len(members), timeout_s)
+                for i, m in enumerate(members):
+                    handles[m] = group[i]
+            self._by_axis[axis] = handles
+
+    def tp(self, rank: int):
+        return self._by_axis["tp"][rank]
+
+    def pp(self, rank: int):
+        return self._by_axis["pp"][rank]
+
+    def dp(self, rank: int):
+        return self._by_axis["dp"][rank]

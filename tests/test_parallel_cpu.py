@@ -22,6 +22,31 @@ def test_grid_rank_formula_and_groups():
     assert len(g.all_groups("dp")) == 4 and sorted(sum(g.all_groups("pp"), [])) == list(range(8))
 
 
+def test_local_groups_reduce_inside_each_group():
+    """Thread ranks of a 2 x 1 x 2 grid: the tensor-parallel all-reduce sums inside each TP pair, the
+    data-parallel one across the pairs."""
+    import threading
+    from brain_b200.parallel.grid import Grid, LocalGroups
+    g = Grid(tp=2, pp=1, dp=2)
+    lg = LocalGroups(g, timeout_s=10.0)
+    tp_out, dp_out = [None] * 4, [None] * 4
+
+    def work(r):
+        t = torch.full((3,), float(r + 1))
+        lg.tp(r).all_reduce(t)
+        tp_out[r] = t.clone()
+        d = torch.full((3,), float(r + 1))
+        lg.dp(r).all_reduce(d)
+        dp_out[r] = d
+    ths = [threading.Thread(target=work, args=(r,)) for r in range(4)]
+    [t.start() for t in ths]
+    [t.join(20) for t in ths]
+    # ranks 0,1 form one TP group (dp 0), ranks 2,3 the other; DP groups are {0,2} and {1,3}
+    assert [float(t[0]) for t in tp_out] == [3.0, 3.0, 7.0, 7.0]
+    assert [float(t[0]) for t in dp_out] == [4.0, 6.0, 4.0, 6.0]
+    assert lg.pp(2) is not None and lg.tp(0) is not lg.tp(2)
+
+
 def test_planners():
     p = plan_balanced(ShardCost(12, 1.0, 0.0, 0.0), [0, 1, 2])
     assert [(s.start, s.end) for s in p] == [(0, 4), (4, 8), (8, 12)] and p[0].embed and p[-1].head
