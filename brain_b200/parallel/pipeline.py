@@ -7,7 +7,8 @@ reference's all-forward-then-all-backward): forward receives the residual stream
 the previous stage and sends its own on; backward receives the gradient of what it sent and sends
 the gradient of what it received.  Transfers are ``torch.distributed`` p2p (NCCL on GPUs, gloo on
 CPU ranks) issued asynchronously, so a stage computes while its sends drain.  Stage inputs are kept
-for the backward (no recompute).  With tied embeddings the first and last stage both hold
+for the backward; with ``model.recompute_blocks`` only block inputs are kept inside a stage and the
+blocks are re-run in backward (the reference's re-materialisation).  With tied embeddings the first and last stage both hold
 ``tok.weight`` and sum its gradient before the optimiser step.
 
 Reference: crates/model/src/shard.rs:355-652 (Pipeline, GPipe with recompute, fused host AdamW and
