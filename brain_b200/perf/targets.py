@@ -100,7 +100,7 @@ class SchedulerTarget(PerfTarget):
     def __init__(self, model, max_batch: int = 256, ctx: int = 4096, block_size: int = 16, weights: str = "bf16",
                  num_blocks: Optional[int] = None, tp=None, name: str = "qwen", engine=None, admit_batch: int = 1,
                  prefix_cache: bool = True, prefill_budget: int = 0, policy: str = "unbounded_queue",
-                 policy_arg: float = 0.0, admit_max_wait: int = 64, window: int = 4):
+                 policy_arg: float = 0.0, admit_max_wait: int = 64, window: int = 4, mixed: bool = False):
         from ..serve.engine import QwenEngine
         from ..serve.scheduler import Scheduler
         per_seq = -(-ctx // block_size)
@@ -109,7 +109,7 @@ class SchedulerTarget(PerfTarget):
                                            max_prefill=min(ctx, 2048), weights=weights, tp=tp)
         self.sched = Scheduler(self.engine, max_batch=max_batch, eos=None, admit_batch=admit_batch,
                                prefix_cache=prefix_cache, prefill_budget=prefill_budget, policy=policy,
-                               policy_arg=policy_arg, admit_max_wait=admit_max_wait, window=window)
+                               policy_arg=policy_arg, admit_max_wait=admit_max_wait, window=window, mixed=mixed)
         self.live: Dict[int, bool] = {}
         self.admitted: Dict[int, bool] = {}
         self.info = {"model": name, "artifact_unit": "token", "max_batch": max_batch, "ctx": ctx,

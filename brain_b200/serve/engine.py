@@ -169,7 +169,7 @@ class QwenEngine:
         #: host wall time spent inside prefill / decode calls (each ends with a device-to-host read,
         #: so it covers the device work) and what they processed; a serving run reports the split
         self.acct = {"prefill_s": 0.0, "prefill_calls": 0, "prefill_tokens": 0, "prefill_seqs": 0,
-                     "decode_s": 0.0, "decode_calls": 0, "decode_rows": 0}
+                     "decode_s": 0.0, "decode_calls": 0, "decode_rows": 0, "mixed_s": 0.0, "mixed_calls": 0}
 
     # ------------------------------------------------------------------ accounting
     def kv_pool_bytes(self) -> int:
@@ -263,13 +263,16 @@ class QwenEngine:
             return self.decode_splits
         return max(1, min(16, (4 * 148 + B * self.hk - 1) // (B * self.hk)))
 
-    def _paged_attention(self, li: int, q, block_tables, seqlens):
+    def _paged_attention(self, li: int, q, block_tables, seqlens, out=None):
+        """One query row per sequence against its pages; ``q`` (and ``out`` when given) may be row
+        slices of wider buffers."""
         B = q.shape[0]
         hq, hk, hd = self.hq, self.hk, self.hd
         scale = 1.0 / math.sqrt(hd)
         if self.cuda:
             splits = self._splits(B)
-            out = torch.empty(B, hq * hd, device=self.device, dtype=self.dtype)
+            if out is None:
+                out = torch.empty(B, hq * hd, device=self.device, dtype=self.dtype)
             part_o = torch.empty(B * hq * splits * hd, device=self.device, dtype=torch.float32)
             part_ml = torch.empty(B * hq * splits * 2, device=self.device, dtype=torch.float32)
             if self.kv_int8:
@@ -353,17 +356,18 @@ class QwenEngine:
         self.steps += 1
         return x, delta
 
-    def _native_prefill(self, tok, pos, slots, seqs):
+    def _native_prefill(self, tok, pos, slots, seqs, dec=None):
         """Packed rows through the native layer halves; ``seqs``: (row offset, rows, start, block
-        table) per sequence, attention per sequence in between.  Returns (normed hidden [n, d], None):
-        the final RMSNorm is already applied."""
+        table) per sequence, attention per sequence in between.  ``dec`` = (row offset, rows, block
+        tables, lengths) adds one decode row per running sequence, attended by the paged kernel.
+        Returns (normed hidden [n, d], None): the final RMSNorm is already applied."""
         nat = self.native
         n = int(tok.shape[0])
         hq, hk, hd = self.hq, self.hk, self.hd
         sc = nat.scratch(-(-n // 256) * 256, 1, key="prefill")
         nat.begin(sc, tok.to(torch.int32), n)
         qw = hq * hd
-        lse = torch.empty(hq * max(l for _, l, _, _ in seqs), device=self.device, dtype=torch.float32)
+        lse = torch.empty(hq * max([l for _, l, _, _ in seqs] or [1]), device=self.device, dtype=torch.float32)
         for li in range(len(self.layers)):
             nat.pre_attn(sc, li, pos, slots, n)
             for o, l, start, bt in seqs:
@@ -375,6 +379,9 @@ class QwenEngine:
                 else:
                     kk, vv = self._gather_kv(li, bt, start + l)
                     flash_attention_into(out, q, kk, vv, 1, l, hq, hk, hd, True, S=start + l, lse=lse)
+            if dec is not None:
+                o, l, dbts, dlens = dec
+                self._paged_attention(li, sc.qk[o:o + l, :qw], dbts, dlens, out=sc.o[o:o + l])
             nat.post_attn(sc, li, n)
         self.steps += 1
         return nat.finish(sc, n), None
@@ -484,6 +491,86 @@ class QwenEngine:
         a["prefill_seqs"] += len(items)
         a["prefill_tokens"] += n
         return results
+
+    @torch.no_grad()
+    def mixed_step(self, items, tokens: np.ndarray, positions: np.ndarray, block_tables: np.ndarray,
+                   greedy: bool = True):
+        """Prefill chunks AND one decode row per running sequence in ONE packed forward: the
+        projections, norms, MLP and (under tensor parallelism) the two all-reduces per layer run
+        once over the concatenated rows, so the decode step rides along with the prompt work instead
+        of waiting behind it (the reference interleaves both kinds of work inside one scheduler
+        step, crates/qwen3/src/serve.rs:1300-1420).  Attention runs per kind: the flash kernel per
+        prefill sequence, the paged kernel over the decode rows.
+
+        ``items`` as for :meth:`prefill_batch`; ``tokens``/``positions``/``block_tables`` as for
+        :meth:`decode` with a window of 1.  Returns (prefill results, decode tokens [B][1], per-row
+        top-k candidates or None)."""
+        if self.fault_hook is not None:
+            self.fault_hook("prefill")
+            self.fault_hook("decode")
+        t0 = time.perf_counter()
+        dev = self.device
+        B = int(tokens.shape[0])
+        lens = [int(it[0].shape[0]) for it in items]
+        offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        n_pre = int(offs[-1])
+        n = n_pre + B
+        tok_np = np.concatenate([np.asarray(it[0], dtype=np.int32) for it in items]
+                                + [np.asarray(tokens, dtype=np.int32)])
+        pos_np = np.concatenate([np.arange(it[1], it[1] + l, dtype=np.int32) for it, l in zip(items, lens)]
+                                + [np.asarray(positions, dtype=np.int32)])
+        tok = torch.from_numpy(np.ascontiguousarray(tok_np)).to(dev)
+        pos = torch.from_numpy(np.ascontiguousarray(pos_np)).to(dev)
+        bts = [torch.from_numpy(np.ascontiguousarray(it[2])).to(dev) for it in items]
+        dbts = torch.from_numpy(np.ascontiguousarray(block_tables)).to(dev)
+        dpos = pos[n_pre:]
+        dlens = (dpos + 1).to(torch.int32)
+        slots = torch.cat([self._slots(bt[None, :].expand(l, -1), pos[o:o + l])
+                           for bt, l, o in zip(bts, lens, offs[:-1].tolist())] + [self._slots(dbts, dpos)])
+        hq, hk, hd = self.hq, self.hk, self.hd
+        seqs = [(o, l, it[1], bt) for it, bt, l, o in zip(items, bts, lens, offs[:-1].tolist())]
+        if self.native is not None:
+            x, delta = self._native_prefill(tok, pos, slots, seqs, dec=(n_pre, B, dbts, dlens))
+        else:
+            def attn(li, q, k, v):
+                self._append_kv(li, k, v, slots)
+                outs = []
+                for o, l, start, bt in seqs:
+                    qs = q[o:o + l]
+                    if start == 0:
+                        outs.append(flash_attention(qs, k[o:o + l], v[o:o + l], 1, l, hq, hk, hd, causal=True))
+                    else:
+                        kk, vv = self._gather_kv(li, bt, start + l)
+                        outs.append(flash_attention(qs, kk, vv, 1, l, hq, hk, hd, causal=True, S=start + l))
+                outs.append(self._paged_attention(li, q[n_pre:], dbts, dlens))
+                return torch.cat(outs)
+
+            x = F.embedding(tok, self.tok).reshape(n, -1)
+            delta = None
+            for li in range(len(self.layers)):
+                x, delta = self._layer(li, x, delta, pos, attn)
+            self.steps += 1
+        # one head call over the rows that sample: last row of each finishing prompt + decode rows
+        final = [i for i, it in enumerate(items) if it[3]]
+        rows = torch.tensor([int(offs[i + 1]) - 1 for i in final] + list(range(n_pre, n)), device=dev,
+                            dtype=torch.long)
+        t, tk = self._head(x[rows], delta[rows] if delta is not None else None, greedy)
+        picked = t.cpu().tolist()
+        cands = None
+        if tk is not None:
+            idx, vals = tk[0].cpu().tolist(), tk[1].cpu().tolist()
+            cands = [list(zip(i, v)) for i, v in zip(idx, vals)]
+        results = [(None, None)] * len(items)
+        for j, i in enumerate(final):
+            results[i] = (int(picked[j]), cands[j] if cands is not None else None)
+        nf = len(final)
+        a = self.acct
+        a["mixed_s"] += time.perf_counter() - t0
+        a["mixed_calls"] += 1
+        a["prefill_seqs"] += len(items)
+        a["prefill_tokens"] += n_pre
+        a["decode_rows"] += B
+        return results, [[int(p)] for p in picked[nf:]], (cands[nf:] if cands is not None else None)
 
     @torch.no_grad()
     def decode(self, tokens: np.ndarray, positions: np.ndarray, block_tables: np.ndarray,

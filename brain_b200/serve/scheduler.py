@@ -89,6 +89,7 @@ class StepReport:
     prefill_tokens: int = 0
     decoded: int = 0
     window: int = 1
+    mixed: bool = False            # prompt chunks and the decode batch shared one forward
     finished: List[int] = field(default_factory=list)
     new_tokens: Dict[int, List[int]] = field(default_factory=dict)
 
@@ -109,11 +110,14 @@ class Scheduler:
     def __init__(self, decoder: PagedDecoder, max_batch: int = 16, eos: Optional[int] = None,
                  window: int = 4, policy: str = "unbounded_queue", policy_arg: float = 0.0,
                  prefix_cache: bool = True, admit_batch: int = 1, admit_max_wait: int = 64,
-                 prefill_budget: int = 0):
+                 prefill_budget: int = 0, mixed: bool = False):
         """``admit_batch`` > 1 batches admissions: new requests join only once that many slots are
         free (or ``admit_max_wait`` steps passed), trading a little queueing delay for far fewer
-        prefill-carrying steps under a saturated closed loop."""
+        prefill-carrying steps under a saturated closed loop.  ``mixed``: a step that carries both
+        prompt chunks and a decode batch runs them as ONE forward when the decoder offers
+        ``mixed_step`` (one set of per-layer launches and all-reduces instead of two)."""
         self.dec = decoder
+        self.mixed = bool(mixed)
         pol = {"unbounded_queue": 0, "max_queue_depth": 1, "deadline_aware": 2}[policy]
         self.max_blocks = (decoder.max_seq_len + decoder.block_size - 1) // decoder.block_size
         self._h = _host.lib().bbh_sched_new(
@@ -229,19 +233,8 @@ class Scheduler:
             if s.value == info.prefix_hit:
                 rep.admitted += 1
             rep.prefill_tokens += e.value - s.value
-        if plan:
-            batch = getattr(self.dec, "prefill_batch", None)
-            if batch is not None and len(plan) > 1:
-                outs = batch([(p[5], p[1], p[6], p[3], p[4]) for p in plan])
-            else:
-                outs = [self.dec.prefill_chunk(p[5], p[1], p[6], p[3], p[4]) for p in plan]
-            for p, (tok, topk) in zip(plan, outs):
-                if p[3]:
-                    lib.bbh_sched_commit_prefill(self._h, p[0], p[2], 1, self._pick(p[0], tok, topk))
-                else:
-                    lib.bbh_sched_commit_prefill(self._h, p[0], p[2], 0, 0)
-        # ---- one batched decode
         n = nd.value
+        ids = toks = pos = bts = None
         if n:
             ids = np.empty(n, dtype=np.int64)
             toks = np.empty(n, dtype=np.int32)
@@ -249,8 +242,32 @@ class Scheduler:
             bts = np.empty((n, self.max_blocks), dtype=np.int32)
             lib.bbh_sched_decode_batch(self._h, ids.ctypes.data, toks.ctypes.data, pos.ctypes.data,
                                        bts.ctypes.data, self.max_blocks)
-            all_greedy = bool(lib.bbh_sched_decode_all_greedy(self._h))
-            greedy_toks, topks = self.dec.decode(toks, pos, bts, win.value, all_greedy)
+        all_greedy = bool(lib.bbh_sched_decode_all_greedy(self._h)) if n else True
+        outs = decoded = None
+        mixed = getattr(self.dec, "mixed_step", None) if self.mixed else None
+        if plan and n and mixed is not None and win.value == 1:
+            # the decode set was fixed by the plan, so both kinds of rows can share one forward
+            g = all_greedy and all(p[4] for p in plan if p[3])
+            outs, g_toks, topks = mixed([(p[5], p[1], p[6], p[3], p[4]) for p in plan], toks, pos, bts, g)
+            decoded = (g_toks, topks)
+            rep.mixed = True
+        elif plan:
+            batch = getattr(self.dec, "prefill_batch", None)
+            if batch is not None and len(plan) > 1:
+                outs = batch([(p[5], p[1], p[6], p[3], p[4]) for p in plan])
+            else:
+                outs = [self.dec.prefill_chunk(p[5], p[1], p[6], p[3], p[4]) for p in plan]
+        if plan:
+            for p, (tok, topk) in zip(plan, outs):
+                if p[3]:
+                    lib.bbh_sched_commit_prefill(self._h, p[0], p[2], 1, self._pick(p[0], tok, topk))
+                else:
+                    lib.bbh_sched_commit_prefill(self._h, p[0], p[2], 0, 0)
+        # ---- one batched decode
+        if n:
+            if decoded is None:
+                decoded = self.dec.decode(toks, pos, bts, win.value, all_greedy)
+            greedy_toks, topks = decoded
             if all_greedy:
                 out = np.ascontiguousarray(np.asarray(greedy_toks, dtype=np.uint32).reshape(n, win.value))
             else:

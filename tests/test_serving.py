@@ -306,3 +306,24 @@ def test_admission_batching_takes_requests_in_groups():
     sw, stw, ow = run(8, wait=3)
     assert sw.completed == 32 and ow == o1
     assert stw["steps"] <= st1["steps"]
+
+
+def test_mixed_steps_equal_separate_prefill_and_decode():
+    """With ``mixed`` the steps that carry prompt chunks and a decode batch run as one forward; every
+    stream (greedy and seeded sampling) is the same as with separate forwards."""
+    prompts = [[3, 9, 27, 11, 5], list(range(1, 20)), [7], list(range(20, 33)), [4, 4, 8]]
+
+    def run(mixed):
+        eng, _ = _tiny_engine()
+        s = Scheduler(eng, max_batch=2, window=1, mixed=mixed)
+        ids = [s.submit(p, 7) for p in prompts[:4]]
+        ids.append(s.submit(prompts[4], 7, SampleParams(0.8, 5, 0.9), seed=11))
+        n_mixed = 0
+        while not s.is_idle():
+            n_mixed += int(s.step().mixed)
+        return [s.tokens_of(i) for i in ids], n_mixed, eng
+    sep, n0, _ = run(False)
+    mix, n1, eng = run(True)
+    assert n0 == 0 and n1 > 0 and eng.acct["mixed_calls"] == n1
+    assert mix == sep
+    assert mix[0] == _greedy_reference(eng, prompts[0], 7)

@@ -222,13 +222,22 @@ def test_native_forward_matches_python_path(weights, kv):
         r["decode"] = out
         _, c = e.decode(np.array([5, 6, 7], dtype=np.int32), pos + 3, bts, window=1, greedy=False)
         r["dcand"] = c
+        # one forward carrying a fresh prompt AND a decode row per running sequence gives what the
+        # two separate forwards give (same inputs, so the pages are rewritten with the same values)
+        bt3 = np.arange(32, dtype=np.int32) + 96
+        nxt = np.array([8, 9, 10], dtype=np.int32)
+        sep_first, _ = e.prefill_chunk(toks[:60], 0, bt3, True)
+        sep_dec, _ = e.decode(nxt, pos + 4, bts, window=1, greedy=True)
+        mres, mdec, mc = e.mixed_step([(toks[:60], 0, bt3, True, True)], nxt, pos + 4, bts, True)
+        assert mc is None and mres[0][0] == sep_first and mdec == sep_dec
+        r["mixed"] = (mres[0][0], mdec)
         res.append(r)
     _cuda.check_error()
     py, nat, gr = res
     assert e_graph.graph_replays >= 1
     for other in (nat, gr):
         assert other["first"] == py["first"] and other["packed"] == py["packed"] and other["verify"] == py["verify"]
-        assert other["decode"] == py["decode"]
+        assert other["decode"] == py["decode"] and other["mixed"] == py["mixed"]
         _same_candidates(py["cand"], other["cand"])
         for ca, cb in zip(py["dcand"], other["dcand"]):
             _same_candidates(ca, cb)
