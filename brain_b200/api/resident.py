@@ -264,7 +264,7 @@ class LlmResident(ResidentModel):
         ids = tokenizer.encode("<|im_end|>") if hasattr(tokenizer, "special") else []
         self.eos = ids[0] if len(ids) == 1 else getattr(tokenizer, "eos_id", None)
         self.sched = Scheduler(self.engine, max_batch=self.max_batch, eos=self.eos,
-                               mixed=os.environ.get("BRAIN_SERVE_MIXED", "0") == "1")
+                               mixed=os.environ.get("BRAIN_SERVE_MIXED", "1") == "1")
         self._inbox: "queue.Queue[_Job]" = queue.Queue()
         self._jobs: Dict[int, _Job] = {}
         self._stop = threading.Event()
