@@ -87,7 +87,7 @@ class MockResident(ResidentModel):
         user = last_user_text(p)
         if FAIL_TRIGGER in user:
             # an internal-looking message: the HTTP layer must not leak it
-            raise RuntimeError("mock resident action failed: /home/secret/model.bin: boom (internal failure)")
+            raise RuntimeError("mock resident action failed: /srv/secret/model.bin: boom (internal failure)")
         delay = float(os.environ.get("BRAIN_MOCK_DELAY_MS", "0") or 0) / 1e3
         t_end = time.time() + delay
         while time.time() < t_end:
