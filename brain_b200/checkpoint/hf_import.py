@@ -41,6 +41,20 @@ def hf_name(brain_name: str) -> str:
     raise KeyError(brain_name)
 
 
+def _rope_theta(hf: dict) -> float:
+    """RoPE base of a Hugging Face config: top-level ``rope_theta`` (transformers 4) or
+    ``rope_parameters.rope_theta`` (transformers 5).  Scaled variants (yarn, linear, dynamic, llama3)
+    change every frequency; they are refused rather than imported with silently different logits."""
+    rp = hf.get("rope_parameters") or hf.get("rope_scaling") or {}
+    kind = rp.get("rope_type", rp.get("type", "default")) if isinstance(rp, dict) else "default"
+    if kind not in (None, "default"):
+        raise ValueError(f"RoPE scaling {kind!r} is not supported by this importer")
+    theta = hf.get("rope_theta")
+    if theta is None and isinstance(rp, dict):
+        theta = rp.get("rope_theta")
+    return float(theta if theta is not None else 1e6)
+
+
 def config_from_hf(hf: dict, block: Optional[int] = None) -> QwenConfig:
     d = int(hf["hidden_size"])
     heads = int(hf["num_attention_heads"])
@@ -51,7 +65,7 @@ def config_from_hf(hf: dict, block: Optional[int] = None) -> QwenConfig:
     return QwenConfig(vocab=int(hf["vocab_size"]), block_size=blk, n_layers=int(hf["num_hidden_layers"]),
                       d_model=d, n_heads=heads, n_kv_heads=int(hf.get("num_key_value_heads", heads)),
                       head_dim=int(hf.get("head_dim", d // heads)), d_ff=int(hf["intermediate_size"]),
-                      rope_theta=float(hf.get("rope_theta", 1e6)), rms_eps=float(hf.get("rms_norm_eps", 1e-6)),
+                      rope_theta=_rope_theta(hf), rms_eps=float(hf.get("rms_norm_eps", 1e-6)),
                       max_position_embeddings=ctx, tie_embeddings=bool(hf.get("tie_word_embeddings", False)),
                       qk_norm=not qwen2, attn_bias=bool(hf.get("attention_bias", qwen2)))
 

@@ -1,0 +1,98 @@
+"""Upstream parity (the reference compares with goldens dumped from Hugging Face transformers,
+crates/qwen3/tests/parity.rs): a randomly initialised tiny transformers Qwen3 / Qwen2 model is saved
+as a Hugging Face directory, imported with the framework's importer, and both sides must produce
+the same logits; the export writes a directory transformers loads back to the same logits."""
+import json
+import os
+
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+
+def _hf_model(tmp, kind):
+    torch.manual_seed(0)
+    common = dict(vocab_size=97, hidden_size=64, intermediate_size=160, num_hidden_layers=3,
+                  num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
+                  rms_norm_eps=1e-6, rope_theta=10000.0, tie_word_embeddings=(kind == "tied"),
+                  attention_dropout=0.0)
+    if kind == "qwen2":
+        cfg = transformers.Qwen2Config(**common)
+        m = transformers.Qwen2ForCausalLM(cfg)
+    else:
+        cfg = transformers.Qwen3Config(head_dim=32, **common)      # head_dim != hidden / heads on purpose
+        m = transformers.Qwen3ForCausalLM(cfg)
+    m = m.float().eval()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if p.dim() == 1:                 # norm gains (and Qwen2's biases): not all ones / zeros
+                p.add_(0.1 * torch.randn_like(p))
+    d = os.path.join(tmp, kind)
+    m.save_pretrained(d, safe_serialization=True)
+    return m, d
+
+
+@pytest.mark.parametrize("kind", ["qwen3", "tied", "qwen2"])
+def test_imported_checkpoint_matches_transformers_logits(tmp_path, kind):
+    from brain_b200.checkpoint import st
+    from brain_b200.checkpoint.hf_import import export_hf, import_qwen
+    hf, d = _hf_model(str(tmp_path), kind)
+    out = str(tmp_path / f"{kind}.safetensors")
+    import_qwen(d, out, block=64)
+    model, cfg, _ = st.load_model(out)
+    model = model.float().eval()
+    ids = torch.randint(0, 97, (2, 37), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(ids).logits
+        got = model(ids.to(torch.int32)).float()
+    assert got.shape == want.shape
+    err = (got - want).abs().max().item()
+    assert err < 2e-4 * max(want.abs().max().item(), 1.0), err
+    assert (got.argmax(-1) == want.argmax(-1)).all()
+    # and back: the exported directory loads in transformers with the same logits
+    back = str(tmp_path / f"{kind}_export")
+    export_hf(out, back, dtype="F32")
+    assert json.load(open(os.path.join(back, "config.json")))["num_hidden_layers"] == 3
+    cls = transformers.Qwen2ForCausalLM if kind == "qwen2" else transformers.Qwen3ForCausalLM
+    hf2 = cls.from_pretrained(back, torch_dtype=torch.float32).eval()
+    with torch.no_grad():
+        again = hf2(ids).logits
+    assert (again - want).abs().max().item() < 1e-5
+
+
+def test_gpt2_block_semantics_match_transformers(tmp_path):
+    """The GPT-2 model computes what transformers' GPT2LMHeadModel computes (pre-LN blocks, fused
+    qkv with bias, tanh GELU, learned positions, final LayerNorm) once the weights are mapped:
+    transformers stores its projections transposed (Conv1D) and ties the head to the embedding."""
+    from brain_b200.models.config import GptConfig
+    from brain_b200.models.gpt2 import Gpt2
+    torch.manual_seed(0)
+    hc = transformers.GPT2Config(vocab_size=83, n_positions=48, n_embd=48, n_layer=2, n_head=4, n_inner=None,
+                                 resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    hf = transformers.GPT2LMHeadModel(hc).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))      # biases and LayerNorm parameters away from 0 / 1
+    m = Gpt2(GptConfig(vocab=83, block_size=48, n_layers=2, d_model=48, n_heads=4, d_ff=192)).init_weights(1)
+    sd = hf.state_dict()
+    with torch.no_grad():
+        m.tok.copy_(sd["transformer.wte.weight"])
+        m.pos.copy_(sd["transformer.wpe.weight"])
+        m.lm_head.copy_(sd["transformer.wte.weight"])
+        m.ln_w.copy_(sd["transformer.ln_f.weight"])
+        m.ln_b.copy_(sd["transformer.ln_f.bias"])
+        for i, b in enumerate(m.blocks):
+            h = f"transformer.h.{i}."
+            b.ln1_w.copy_(sd[h + "ln_1.weight"]); b.ln1_b.copy_(sd[h + "ln_1.bias"])
+            b.ln2_w.copy_(sd[h + "ln_2.weight"]); b.ln2_b.copy_(sd[h + "ln_2.bias"])
+            b.qkv_w.copy_(sd[h + "attn.c_attn.weight"].t()); b.qkv_b.copy_(sd[h + "attn.c_attn.bias"])
+            b.out_w.copy_(sd[h + "attn.c_proj.weight"].t()); b.out_b.copy_(sd[h + "attn.c_proj.bias"])
+            b.fc_w.copy_(sd[h + "mlp.c_fc.weight"].t()); b.fc_b.copy_(sd[h + "mlp.c_fc.bias"])
+            b.proj_w.copy_(sd[h + "mlp.c_proj.weight"].t()); b.proj_b.copy_(sd[h + "mlp.c_proj.bias"])
+    ids = torch.randint(0, 83, (2, 29), generator=torch.Generator().manual_seed(2))
+    with torch.no_grad():
+        want = hf(ids).logits
+        got = m.eval()(ids.to(torch.int32)).float()
+    assert (got - want).abs().max().item() < 2e-4 * max(want.abs().max().item(), 1.0)
