@@ -64,11 +64,49 @@ class CharTokenizer:
         return "".join(self.itos[i] for i in ids if 0 <= i < self.vocab_size)
 
 
+def _split_pattern(pre) -> Optional[str]:
+    """The regex of a tokenizer.json ``pre_tokenizer`` entry: a ``Split`` with a ``Regex`` pattern, or a
+    ``ByteLevel`` that applies the GPT-2 pattern itself; None when the entry names neither."""
+    if not isinstance(pre, dict):
+        return None
+    kind = pre.get("type")
+    if kind == "Sequence":
+        for sub in pre.get("pretokenizers", []):
+            pat = _split_pattern(sub)
+            if pat is not None:
+                return pat
+        return None
+    if kind == "Split":
+        pat = pre.get("pattern", {})
+        if isinstance(pat, dict) and "Regex" in pat and pre.get("behavior", "Isolated").lower() == "isolated" \
+                and not pre.get("invert", False):
+            return pat["Regex"]
+        return None
+    if kind == "ByteLevel" and pre.get("use_regex", True):
+        return GPT2_SPLIT
+    return None
+
+
+def _normal_form(norm) -> Optional[str]:
+    """Unicode normal form a tokenizer.json ``normalizer`` entry asks for (NFC / NFD / NFKC / NFKD)."""
+    if not isinstance(norm, dict):
+        return None
+    if norm.get("type") in ("NFC", "NFD", "NFKC", "NFKD"):
+        return norm["type"]
+    if norm.get("type") == "Sequence":
+        for sub in norm.get("normalizers", []):
+            f = _normal_form(sub)
+            if f:
+                return f
+    return None
+
+
 class BpeTokenizer:
     def __init__(self, vocab: Dict[str, int], merges: Sequence, special: Optional[Dict[str, int]] = None,
-                 pattern: str = QWEN_SPLIT, eos: Optional[str] = None):
+                 pattern: str = QWEN_SPLIT, eos: Optional[str] = None, normalize: Optional[str] = None):
         import regex
         self._re = regex.compile(pattern)
+        self.normalize = normalize      # Unicode normal form applied before splitting ("NFC" for Qwen)
         self._b2u = bytes_to_unicode()
         self._u2b = {v: k for k, v in self._b2u.items()}
         self.special = dict(special or {})
@@ -106,8 +144,18 @@ class BpeTokenizer:
         model = d["model"]
         special = {t["content"]: t["id"] for t in d.get("added_tokens", [])}
         eos = next((s for s in ("<|im_end|>", "<|endoftext|>") if s in special), None)
-        pat = QWEN_SPLIT if "<|im_end|>" in special or len(model["vocab"]) > 60000 else GPT2_SPLIT
-        tok = BpeTokenizer(model["vocab"], model["merges"], special, pat, eos)
+        # the file's own split pattern and normaliser win; the family heuristic covers files without
+        pat = _split_pattern(d.get("pre_tokenizer"))
+        if pat is not None:
+            import regex
+            try:
+                regex.compile(pat)
+            except regex.error:          # a construct of another regex engine: use the family pattern
+                pat = None
+        if pat is None:
+            pat = QWEN_SPLIT if "<|im_end|>" in special or len(model["vocab"]) > 60000 else GPT2_SPLIT
+        tok = BpeTokenizer(model["vocab"], model["merges"], special, pat, eos,
+                           normalize=_normal_form(d.get("normalizer")))
         from .chat_template import ChatTemplate
         tok.chat_template = ChatTemplate.beside(path)
         return tok
@@ -138,6 +186,9 @@ class BpeTokenizer:
 
     def encode(self, text: str, allow_special: bool = True) -> List[int]:
         out: List[int] = []
+        if self.normalize:
+            import unicodedata
+            text = unicodedata.normalize(self.normalize, text)
         if self._special_re is None or not allow_special:
             self._encode_plain(text, out)
             return out

@@ -96,3 +96,53 @@ def test_gpt2_block_semantics_match_transformers(tmp_path):
         want = hf(ids).logits
         got = m.eval()(ids.to(torch.int32)).float()
     assert (got - want).abs().max().item() < 2e-4 * max(want.abs().max().item(), 1.0)
+
+
+def _hf_bpe(kind, corpus):
+    from tokenizers import Regex, Tokenizer, decoders, models, normalizers, pre_tokenizers, trainers
+    from brain_b200.data.tokenizer import QWEN_SPLIT
+    tok = Tokenizer(models.BPE())
+    if kind == "qwen":
+        tok.normalizer = normalizers.NFC()
+        tok.pre_tokenizer = pre_tokenizers.Sequence([
+            pre_tokenizers.Split(Regex(QWEN_SPLIT), behavior="isolated", invert=False),
+            pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+        special = ["<|endoftext|>", "<|im_start|>", "<|im_end|>"]
+    else:
+        tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+        special = ["<|endoftext|>"]
+    tok.decoder = decoders.ByteLevel()
+    tok.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=600, special_tokens=[], show_progress=False,
+                                                        initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+    tok.add_special_tokens(special)
+    return tok
+
+
+@pytest.mark.parametrize("kind", ["qwen", "gpt2"])
+def test_bpe_tokenizer_matches_the_tokenizers_library(tmp_path, kind):
+    """A byte-level BPE trained with the Hugging Face `tokenizers` library (Qwen-style: NFC + split
+    regex + byte mapping; GPT-2 style: ByteLevel with its own regex) and saved as tokenizer.json
+    encodes and decodes identically through the native merge loop."""
+    pytest.importorskip("tokenizers")
+    import random
+    from brain_b200.data.tokenizer import BpeTokenizer
+    corpus = ["The quick brown fox jumps over the lazy dog. " * 3,
+              "Hello, world! I'm here; you're there — it's 12345 o'clock.",
+              "def f(x):\n    return x**2 + 1\n\n\nprint(f(3))\r\n",
+              "naïve café résumé Ångström 日本語のテキスト 한국어 \U0001f642\U0001f680",
+              "  leading spaces and   multiple   spaces\t\ttabs \n trailing  ",
+              "numbers 3.14159 1,000,000 0x1F 2024-01-01", "I'LL WE'VE DON'T they'D"] * 4
+    hf = _hf_bpe(kind, corpus)
+    path = str(tmp_path / "tokenizer.json")
+    hf.save(path)
+    mine = BpeTokenizer.from_file(path)
+    cases = corpus[:7] + ["<|im_start|>user\nhi there<|im_end|>\n<|im_start|>assistant\n", "é vs é", "", " ",
+                          "\n\n", "a" * 50, "tab\tsep", "mixed123abc456", "'s 'S 't", "x  \n  y", "end<|endoftext|>"]
+    rnd = random.Random(5)
+    alphabet = "abc XYZ 019 .,!?'\n\t\r-_/éü中文́\U0001f600"
+    cases += ["".join(rnd.choice(alphabet) for _ in range(rnd.randint(1, 60))) for _ in range(200)]
+    for s in cases:
+        want = hf.encode(s).ids
+        got = mine.encode(s)
+        assert got == want, repr(s)
+        assert mine.decode(got) == hf.decode(want, skip_special_tokens=False), repr(s)
