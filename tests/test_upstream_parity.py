@@ -146,3 +146,69 @@ def test_bpe_tokenizer_matches_the_tokenizers_library(tmp_path, kind):
         got = mine.encode(s)
         assert got == want, repr(s)
         assert mine.decode(got) == hf.decode(want, skip_special_tokens=False), repr(s)
+
+
+CHATML_TEMPLATE = """{%- if tools %}
+{{- '<|im_start|>system\\n' }}
+{%- if messages[0].role == 'system' %}{{- messages[0].content + '\\n\\n' }}{%- endif %}
+{{- "# Tools\\n<tools>" }}
+{%- for tool in tools %}
+{{- "\\n" }}{{- tool | tojson }}
+{%- endfor %}
+{{- "\\n</tools><|im_end|>\\n" }}
+{%- else %}
+{%- if messages[0].role == 'system' %}{{- '<|im_start|>system\\n' + messages[0].content + '<|im_end|>\\n' }}{%- endif %}
+{%- endif %}
+{%- for message in messages %}
+{%- if message.role == 'user' or (message.role == 'system' and not loop.first) %}
+{{- '<|im_start|>' + message.role + '\\n' + message.content + '<|im_end|>' + '\\n' }}
+{%- elif message.role == 'assistant' %}
+{{- '<|im_start|>assistant\\n' + message.content }}
+{%- if message.tool_calls %}
+{%- for tc in message.tool_calls %}
+{{- '\\n<tool_call>\\n{"name": "' + tc.function.name + '", "arguments": ' }}{{- tc.function.arguments | tojson }}{{- '}\\n</tool_call>' }}
+{%- endfor %}
+{%- endif %}
+{{- '<|im_end|>\\n' }}
+{%- elif message.role == 'tool' %}
+{{- '<|im_start|>user\\n<tool_response>\\n' + message.content + '\\n</tool_response><|im_end|>\\n' }}
+{%- elif message.role == 'system' %}
+{%- else %}
+{{- raise_exception('unknown role ' + message.role) }}
+{%- endif %}
+{%- endfor %}
+{%- if add_generation_prompt %}
+{{- '<|im_start|>assistant\\n' }}
+{%- if enable_thinking is defined and enable_thinking is false %}{{- '<think>\\n\\n</think>\\n\\n' }}{%- endif %}
+{%- endif %}"""
+
+
+def test_chat_template_renders_like_transformers(tmp_path):
+    """The checkpoint's own Jinja chat template renders to the same text as transformers'
+    `apply_chat_template`: whitespace control, the `tojson` filter on non-ASCII text, tool lists, tool
+    calls, extra template variables and `raise_exception`."""
+    pytest.importorskip("tokenizers")
+    from brain_b200.data.chat_template import ChatTemplate, TemplateError
+    hf_tok = transformers.PreTrainedTokenizerFast(tokenizer_object=_hf_bpe("qwen", ["hello world"] * 4),
+                                                  eos_token="<|im_end|>")
+    hf_tok.chat_template = CHATML_TEMPLATE
+    mine = ChatTemplate(CHATML_TEMPLATE, eos_token="<|im_end|>")
+    tools = [{"type": "function", "function": {"name": "väder", "description": "Weather — per city",
+                                               "parameters": {"type": "object", "properties": {"city": {"type": "string"}}}}}]
+    convs = [
+        ([{"role": "user", "content": "hi"}], None, {}),
+        ([{"role": "system", "content": "Be brief."}, {"role": "user", "content": "hi"},
+          {"role": "assistant", "content": "hello"}, {"role": "user", "content": "again\n\nplease "}], None, {}),
+        ([{"role": "system", "content": "S"}, {"role": "user", "content": "weather in Malmö?"},
+          {"role": "assistant", "content": "", "tool_calls": [
+              {"type": "function", "function": {"name": "väder", "arguments": {"city": "Malmö", "n": 2}}}]},
+          {"role": "tool", "content": "{\"temp\": 7}"}], tools, {}),
+        ([{"role": "user", "content": "no thinking"}], None, {"enable_thinking": False}),
+    ]
+    for msgs, tl, extra in convs:
+        for gen in (True, False):
+            want = hf_tok.apply_chat_template(msgs, tools=tl, tokenize=False, add_generation_prompt=gen, **extra)
+            got = mine.render(msgs, add_generation_prompt=gen, tools=tl, **extra)
+            assert got == want
+    with pytest.raises(TemplateError):
+        mine.render([{"role": "narrator", "content": "x"}])
