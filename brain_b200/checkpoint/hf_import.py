@@ -144,6 +144,106 @@ def import_qwen(hf_dir: str, out: str, block: Optional[int] = None, dtype: str =
     return cfg
 
 
+def moe_config_from_hf(hf: dict, block: Optional[int] = None):
+    """``MoeConfig`` of a Hugging Face Qwen3-MoE ``config.json`` (every layer sparse)."""
+    from ..models.config import MoeConfig
+    if hf.get("mlp_only_layers") or int(hf.get("decoder_sparse_step", 1)) != 1:
+        raise ValueError("mixed dense / sparse layer stacks are not supported by this importer")
+    d = int(hf["hidden_size"])
+    heads = int(hf["num_attention_heads"])
+    ctx = int(hf.get("max_position_embeddings", 32768))
+    return MoeConfig(family="qwen3_moe", vocab=int(hf["vocab_size"]), block_size=int(block) if block else min(ctx, 4096),
+                     n_layers=int(hf["num_hidden_layers"]), d_model=d, n_heads=heads,
+                     n_kv_heads=int(hf.get("num_key_value_heads", heads)), head_dim=int(hf.get("head_dim", d // heads)),
+                     n_experts=int(hf["num_experts"] if "num_experts" in hf else hf["num_local_experts"]), top_k=int(hf["num_experts_per_tok"]),
+                     d_ff=int(hf["moe_intermediate_size"]), rope_theta=_rope_theta(hf),
+                     rms_eps=float(hf.get("rms_norm_eps", 1e-6)), aux_coef=float(hf.get("router_aux_loss_coef", 0.001)),
+                     norm_topk_prob=bool(hf.get("norm_topk_prob", False)),
+                     tie_embeddings=bool(hf.get("tie_word_embeddings", False)))
+
+
+def import_qwen_moe(hf_dir: str, out: str, block: Optional[int] = None, dtype: str = "F32",
+                    model_id: Optional[str] = None):
+    """Hugging Face Qwen3-MoE directory -> framework checkpoint.  Attention, norms, embedding and
+    head map like the dense model; the router is ``mlp.gate.weight``; experts are read either per
+    expert (``mlp.experts.{e}.{gate,up,down}_proj.weight``, the published layout) or from the fused
+    ``mlp.experts.gate_up_proj`` [E, 2·ff, d] / ``down_proj`` [E, d, ff] tensors newer transformers
+    versions write.  Tensors stream through one at a time (a fused expert tensor is read once per
+    layer and sliced)."""
+    with open(os.path.join(hf_dir, "config.json")) as f:
+        hf = json.load(f)
+    cfg = moe_config_from_hf(hf, block)
+    where = _shard_index(hf_dir)
+    if not cfg.tie_embeddings and "lm_head.weight" not in where:
+        cfg.tie_embeddings = True
+    plist = cfg.param_list()
+    card = ModelCard(id=model_id or "brain/qwen3moe", family="qwen_moe", architecture=hf.get("model_type", "qwen3_moe"),
+                     param_count=sum(n for _, n in plist), context_length=int(hf.get("max_position_embeddings", 32768)),
+                     capabilities=["generate", "chat"], source_repo=hf.get("_name_or_path") or None)
+    meta = card.to_metadata()
+    meta[st.CONFIG_KEY] = json.dumps(cfg.to_json(), separators=(",", ":"))
+    w = st.StWriter(out, [(n, (k,)) for n, k in plist], meta, dtype)
+    readers: Dict[str, st.WeightReader] = {}
+    fused: Dict[str, torch.Tensor] = {}      # the current layer's fused expert tensors
+
+    def read(src: str) -> torch.Tensor:
+        path = where.get(src)
+        if path is None:
+            raise KeyError(f"{hf_dir}: tensor {src} not found")
+        r = readers.get(path)
+        if r is None:
+            r = readers[path] = st.WeightReader(path)
+        return r.read(src)
+
+    ff, d, E = cfg.d_ff, cfg.d_model, cfg.n_experts
+    try:
+        for name, numel in plist:
+            parts = name.split(".")
+            if len(parts) > 3 and parts[2] == "moe":
+                base = f"model.layers.{parts[1]}.mlp"
+                if parts[3] == "router":
+                    fused.clear()
+                    t = read(f"{base}.gate.weight")
+                else:
+                    e, which = int(parts[4]), parts[5]
+                    per = f"{base}.experts.{e}.{ {'w_gate': 'gate_proj', 'w_up': 'up_proj', 'w_down': 'down_proj'}[which]}.weight"
+                    if per in where:
+                        t = read(per)
+                    else:
+                        key = f"{base}.experts.down_proj" if which == "w_down" else f"{base}.experts.gate_up_proj"
+                        if key not in fused:
+                            fused[key] = read(key)
+                        big = fused[key]
+                        if which == "w_down":
+                            t = big.reshape(E, d, ff)[e]
+                        else:
+                            gu = big.reshape(E, 2 * ff, d)[e]
+                            t = gu[:ff] if which == "w_gate" else gu[ff:]
+            else:
+                t = read(hf_name(name))
+            if t.numel() != numel:
+                raise ValueError(f"{name}: {t.numel()} elements, config expects {numel}")
+            w.write(name, t.contiguous())
+    except BaseException:
+        w.close(abort=True)
+        raise
+    finally:
+        for r in readers.values():
+            r.close()
+    w.close()
+    return cfg
+
+
+def import_hf(hf_dir: str, out: str, block: Optional[int] = None, dtype: str = "F32",
+              model_id: Optional[str] = None):
+    """Import a Hugging Face directory by its ``model_type``: qwen2 / qwen3 (dense) or qwen3_moe."""
+    with open(os.path.join(hf_dir, "config.json")) as f:
+        kind = json.load(f).get("model_type", "qwen3")
+    if kind in ("qwen3_moe", "qwen2_moe"):
+        return import_qwen_moe(hf_dir, out, block, dtype, model_id)
+    return import_qwen(hf_dir, out, block, dtype, model_id)
+
+
 def export_hf(weights: str, out_dir: str, dtype: str = "BF16") -> None:
     """Inverse mapping: framework checkpoint -> ``config.json`` + ``model.safetensors`` with Hugging
     Face names and 2-D shapes (the reference's ``export`` targets an NPU graph format instead; this

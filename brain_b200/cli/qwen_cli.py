@@ -62,7 +62,7 @@ def _eos(tok) -> Optional[int]:
 
 # ------------------------------------------------------------------------------------ import/export
 def _import(args, device):
-    from ..checkpoint.hf_import import import_qwen
+    from ..checkpoint.hf_import import import_hf
     a = Args(args)
     hf = a.str_or("--hf", "")
     out = a.take_str("--out")
@@ -89,7 +89,7 @@ def _import(args, device):
             return 2
     tmp_out = out or ("qwen.safetensors" if ref is None else os.path.join(hf, ".brain_import.safetensors"))
     try:
-        import_qwen(hf, tmp_out, block, dtype, model_id=str(ref) if ref else None)
+        import_hf(hf, tmp_out, block, dtype, model_id=str(ref) if ref else None)   # dense or Qwen3-MoE by model_type
     except Exception as e:  # noqa: BLE001
         print(f"import failed: {e}", file=sys.stderr)
         return 1

@@ -212,3 +212,56 @@ def test_chat_template_renders_like_transformers(tmp_path):
             assert got == want
     with pytest.raises(TemplateError):
         mine.render([{"role": "narrator", "content": "x"}])
+
+
+@pytest.mark.parametrize("layout", ["fused", "per_expert"])
+def test_qwen3_moe_import_matches_transformers_logits(tmp_path, layout):
+    """A tiny random transformers Qwen3-MoE (top-2 of 8 experts, gate weights renormalised in one case and raw in the other) imported
+    from its Hugging Face directory gives the same logits; both expert layouts are read: the fused
+    [E, 2*ff, d] tensors transformers 5 writes and the per-expert tensors of published checkpoints."""
+    from safetensors.torch import load_file, save_file
+    from brain_b200.checkpoint import st
+    from brain_b200.checkpoint.hf_import import import_hf
+    torch.manual_seed(0)
+    hc = transformers.Qwen3MoeConfig(
+        vocab_size=97, hidden_size=64, intermediate_size=160, moe_intermediate_size=48, num_hidden_layers=2,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=32, num_experts=8, num_experts_per_tok=2,
+        norm_topk_prob=(layout == "fused"), decoder_sparse_step=1, mlp_only_layers=[], rope_theta=10000.0,
+        max_position_embeddings=128, tie_word_embeddings=False)
+    hf = transformers.Qwen3MoeForCausalLM(hc).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+            if "experts" in n or "gate.weight" in n:
+                p.normal_(0, 0.2)          # routing far from ties, experts that matter
+    d = str(tmp_path / "hf")
+    hf.save_pretrained(d, safe_serialization=True)
+    if layout == "per_expert":
+        path = os.path.join(d, "model.safetensors")
+        sd = load_file(path)
+        if any(k.endswith("experts.gate_up_proj") for k in sd):
+            new = {}
+            for k, v in sd.items():
+                if k.endswith("experts.gate_up_proj"):
+                    base = k[: -len("gate_up_proj")]
+                    for e in range(v.shape[0]):
+                        new[f"{base}{e}.gate_proj.weight"] = v[e, :48].contiguous()
+                        new[f"{base}{e}.up_proj.weight"] = v[e, 48:].contiguous()
+                elif k.endswith("experts.down_proj"):
+                    base = k[: -len("down_proj")]
+                    for e in range(v.shape[0]):
+                        new[f"{base}{e}.down_proj.weight"] = v[e].contiguous()
+                else:
+                    new[k] = v
+            save_file(new, path, metadata={"format": "pt"})
+    out = str(tmp_path / "moe.safetensors")
+    cfg = import_hf(d, out, block=64)
+    assert cfg.n_experts == 8 and cfg.top_k == 2 and cfg.d_ff == 48 and cfg.rope_theta == 10000.0
+    model, _, card = st.load_model(out)
+    model = model.float().eval()
+    ids = torch.randint(0, 97, (2, 23), generator=torch.Generator().manual_seed(2))
+    with torch.no_grad():
+        want = hf(ids).logits
+        got = model(ids.to(torch.int32)).float()
+    assert (got - want).abs().max().item() < 2e-4 * max(want.abs().max().item(), 1.0)
