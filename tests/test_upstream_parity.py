@@ -299,3 +299,33 @@ def test_trainer_steps_match_a_plain_pytorch_loop():
         assert la == pytest.approx(float(lb), rel=2e-5, abs=2e-5)
     for (n, pa), (_, pb) in zip(a.named_parameters(), b.named_parameters()):
         assert torch.allclose(pa.detach().float(), pb.detach().float(), rtol=2e-4, atol=2e-5), n
+
+
+def test_engine_greedy_tokens_match_transformers_generate(tmp_path):
+    """End to end: transformers model -> Hugging Face directory -> importer -> paged-KV engine and
+    scheduler (chunked prefill, batched decode, mixed steps) produce the greedy continuation that
+    `generate(do_sample=False)` produces."""
+    from brain_b200.checkpoint import st
+    from brain_b200.checkpoint.hf_import import import_hf
+    from brain_b200.serve.engine import QwenEngine
+    from brain_b200.serve.scheduler import Scheduler
+    hf, d = _hf_model(str(tmp_path), "qwen3")
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.mul_(3.0)                      # well separated logits: greedy choices survive rounding
+    hf.save_pretrained(d, safe_serialization=True)
+    out = str(tmp_path / "m.safetensors")
+    import_hf(d, out, block=64)
+    model, _, _ = st.load_model(out)
+    eng = QwenEngine(model.float().eval(), block_size=4, num_blocks=64, max_seq_len=64, max_prefill=8)
+    sched = Scheduler(eng, max_batch=3, window=2, mixed=True)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 97, (n,), generator=g).tolist() for n in (5, 19, 11, 3)]
+    ids = [sched.submit(p, 9) for p in prompts]
+    sched.run_until_idle()
+    for p, r in zip(prompts, ids):
+        with torch.no_grad():
+            ii = torch.tensor([p])       # explicit mask: a prompt may contain the id used for padding
+            want = hf.generate(ii, attention_mask=torch.ones_like(ii), max_new_tokens=9, do_sample=False,
+                               pad_token_id=0, eos_token_id=None)[0, len(p):].tolist()
+        assert sched.tokens_of(r) == want
