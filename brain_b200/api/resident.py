@@ -230,7 +230,7 @@ def load_gpt(path: str, device: str = "auto", defaults: Optional[Dict] = None) -
 # ------------------------------------------------------------------------------------ language model
 class _Job:
     __slots__ = ("prompt", "max_new", "params", "seed", "ignore_eos", "stops", "on_token", "done", "rid",
-                 "text", "emitted", "n_tokens", "finish", "error", "cancel", "n_prompt", "held")
+                 "text", "emitted", "n_tokens", "finish", "error", "cancel", "n_prompt", "held", "raw")
 
     def __init__(self):
         self.done = threading.Event()
@@ -241,6 +241,7 @@ class _Job:
         self.finish = None
         self.error = None
         self.held = ""
+        self.raw = b""             # bytes of an unfinished multi-byte character
 
 
 class LlmResident(ResidentModel):
@@ -350,10 +351,12 @@ class LlmResident(ResidentModel):
 
     # ---- serving thread
     def _finish(self, job: _Job, finish: Optional[str], error: Optional[Exception] = None):
-        if job.held and error is None and finish != "stop_sequence":
-            job.text += job.held
-            job.on_token(job.held)
-            job.held = ""
+        if error is None and finish != "stop_sequence":
+            tail = job.held + job.raw.decode("utf-8", errors="replace")
+            if tail:
+                job.text += tail
+                job.on_token(tail)
+        job.held, job.raw = "", b""
         job.finish, job.error = finish, error
         if job.rid is not None:
             self._jobs.pop(job.rid, None)
@@ -367,12 +370,16 @@ class LlmResident(ResidentModel):
         """Decode incrementally, hold back text that could be the start of a stop sequence;
         returns True when a stop sequence ended the job."""
         job.n_tokens += len(new_tokens)
-        all_toks = self.sched.tokens_of(job.rid)
-        full = self.tok.decode(all_toks, skip_special=True) if hasattr(self.tok, "special") else self.tok.decode(all_toks)
-        if full.endswith("�"):            # an incomplete UTF-8 sequence: wait for the next token
-            return False
-        fresh = full[len(job.text) + len(job.held):] if full.startswith(job.text + job.held) else full[len(job.text):]
-        pending = job.held + fresh if full.startswith(job.text + job.held) else fresh
+        # only the new tokens are decoded (a request of n tokens costs n token lookups, not n^2 / 2);
+        # bytes of a character that is split across tokens wait in job.raw for their continuation
+        if hasattr(self.tok, "decode_bytes"):
+            raw = job.raw + self.tok.decode_bytes(new_tokens, skip_special=True)
+        else:
+            raw = job.raw + self.tok.decode(new_tokens).encode("utf-8")
+        from ..data.tokenizer import utf8_complete
+        cut = utf8_complete(raw)
+        job.raw = raw[cut:]
+        pending = job.held + raw[:cut].decode("utf-8", errors="replace")
         for s in job.stops:
             k = pending.find(s)
             if k >= 0:

@@ -43,6 +43,19 @@ def bytes_to_unicode() -> Dict[int, str]:
     return {b: chr(ch) for b, ch in zip(bs, cs)}
 
 
+def utf8_complete(b: bytes) -> int:
+    """Length of the longest prefix of ``b`` that does not end inside a multi-byte UTF-8 sequence
+    (an incomplete but so far valid tail of up to three bytes is left for the next chunk)."""
+    n = len(b)
+    for k in range(1, min(4, n) + 1):
+        ch = b[n - k]
+        if ch & 0xC0 == 0x80:
+            continue
+        need = 4 if ch >= 0xF0 else 3 if ch >= 0xE0 else 2 if ch >= 0xC0 else 1
+        return n - k if k < need else n
+    return n
+
+
 class CharTokenizer:
     def __init__(self, itos: Sequence[str]):
         self.itos = list(itos)
@@ -201,7 +214,9 @@ class BpeTokenizer:
                 self._encode_plain(part, out)
         return out
 
-    def decode(self, ids: Iterable[int], skip_special: bool = False) -> str:
+    def decode_bytes(self, ids: Iterable[int], skip_special: bool = False) -> bytes:
+        """The raw bytes of a token sequence; a multi-byte character may be split across tokens, so
+        streaming callers join bytes and decode only complete sequences (:func:`utf8_complete`)."""
         lib = _host.lib()
         buf = ctypes.create_string_buffer(256)
         chunks: List[bytes] = []
@@ -216,7 +231,10 @@ class BpeTokenizer:
                 continue
             mapped = buf.raw[:n].decode("utf-8", errors="ignore")
             chunks.append(bytes(self._u2b.get(ch, ord("?")) for ch in mapped))
-        return b"".join(chunks).decode("utf-8", errors="replace")
+        return b"".join(chunks)
+
+    def decode(self, ids: Iterable[int], skip_special: bool = False) -> str:
+        return self.decode_bytes(ids, skip_special).decode("utf-8", errors="replace")
 
     def apply_chat_template(self, messages, add_generation_prompt: bool = True,
                             enable_thinking: bool = True, tools=None) -> str:

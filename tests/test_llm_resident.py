@@ -134,3 +134,45 @@ def test_http_serves_the_model(llm):
     finally:
         s.shutdown()
         ex.pool.shutdown(wait=False)
+
+
+def test_streaming_joins_characters_split_across_tokens():
+    """Tokens are decoded once each as they arrive; a multi-byte character whose bytes come in
+    different tokens is emitted when its last byte arrives, a stop sequence straddling two tokens
+    still stops, and the streamed pieces concatenate to the one-shot decoding."""
+    from types import SimpleNamespace
+    from brain_b200.api.resident import LlmResident, _Job
+    from brain_b200.data.tokenizer import BpeTokenizer, utf8_complete
+    assert utf8_complete("é".encode()[:1]) == 0 and utf8_complete("aé".encode()) == 3
+    assert utf8_complete("a🙂".encode()[:3]) == 1 and utf8_complete(b"abc") == 3 and utf8_complete(b"") == 0
+    assert utf8_complete(b"a\x80\x80") == 3          # stray continuation bytes are not held back
+    tok = BpeTokenizer.byte_level()                  # one token per byte
+    me = SimpleNamespace(tok=tok)
+    text = "naïve 🙂 日本 done"
+    ids = tok.encode(text)
+    assert len(ids) == len(text.encode())
+
+    def stream(stops, chunk):
+        job = _Job()
+        job.stops = stops
+        pieces = []
+        job.on_token = pieces.append
+        stopped = False
+        for i in range(0, len(ids), chunk):
+            if LlmResident._deliver(me, job, ids[i:i + chunk]):
+                stopped = True
+                break
+        if not stopped:          # what _finish does with the tail
+            tail = job.held + job.raw.decode("utf-8", errors="replace")
+            if tail:
+                pieces.append(tail)
+        return pieces, stopped, job
+    for chunk in (1, 2, 3, 5):
+        pieces, stopped, job = stream([], chunk)
+        assert "".join(pieces) == text and not stopped
+        assert all("�" not in p for p in pieces)
+        assert job.n_tokens == len(ids)
+    pieces, stopped, _ = stream(["本 d"], 1)
+    assert stopped and "".join(pieces) == "naïve 🙂 日"
+    pieces, stopped, _ = stream(["zzz", "🙂 日x"], 2)      # a prefix of a stop is held, then released
+    assert not stopped and "".join(pieces) == text
