@@ -329,3 +329,18 @@ def test_engine_greedy_tokens_match_transformers_generate(tmp_path):
             want = hf.generate(ii, attention_mask=torch.ones_like(ii), max_new_tokens=9, do_sample=False,
                                pad_token_id=0, eos_token_id=None)[0, len(p):].tolist()
         assert sched.tokens_of(r) == want
+
+
+def test_rng_is_splitmix64_offset_by_one_step():
+    """The dataset generator is SplitMix64 whose state starts one increment past the seed
+    (crates/data/src/rng.rs:20-35): seed 0 yields the published SplitMix64 test vector from its
+    second value on, and the float helpers use the top 53 bits."""
+    from brain_b200.data.rng import Rng
+    published = [0xE220A8397B1DCDAF, 0x6E789E6AA1B965F4, 0x06C45D188009454F, 0xF88BB8A8724C81EC]
+    r = Rng(0)
+    assert [r.next_u64() for _ in range(3)] == published[1:]
+    r = Rng(0)
+    assert r.next_f64() == (published[1] >> 11) / float(1 << 53)
+    r = Rng(0)
+    assert r.gen_range_inclusive(3, 12) == 3 + published[1] % 10
+    assert Rng(2**64 - 1).next_u64() == Rng(-1 & (2**64 - 1)).next_u64()      # wrapping seed arithmetic
