@@ -74,6 +74,7 @@ def run_perf(argv: List[str], device: str = "auto") -> int:
         weights = a.str_or("--weights-dtype", "bf16")
         out = a.take_str("--out")
         skip_fid = a.take_flag("--no-fidelity")
+        mixed = a.take_flag("--mixed")      # prompt chunks and the decode batch of a step in one forward
         arrival = _arrival(a)
         a.finish()
         wl = standard(name, arrival, n, seed)
@@ -81,7 +82,8 @@ def run_perf(argv: List[str], device: str = "auto") -> int:
             print(f"unknown workload {name!r}; have: {' '.join(standard_names())}", file=sys.stderr)
             return 2
         try:
-            make, vocab = _make_target(target, device, arrival.concurrency if arrival.kind == "closed_loop" else 256, ctx, weights)
+            make, vocab = _make_target(target, device, arrival.concurrency if arrival.kind == "closed_loop" else 256, ctx, weights,
+                                       **({"mixed": True} if mixed and target != "fake" else {}))
             wl.vocab = vocab
         except ValueError as e:
             print(str(e), file=sys.stderr)
@@ -206,6 +208,6 @@ def run_perf(argv: List[str], device: str = "auto") -> int:
             print(f"{r.fault:<22} reported {str(r.reported):<5} clean {str(r.clean):<5} survived "
                   f"{str(r.survived):<5} {'PASS' if r.passed else 'FAIL'}  {r.detail}")
         return 0 if all(r.passed for r in res) else 1
-    print("usage: brain perf list | run <workload> [--target T --requests N --concurrency C --out F] | "
+    print("usage: brain perf list | run <workload> [--target T --requests N --concurrency C --mixed --out F] | "
           "compare A B | gate A B [--tolerance X] | scenario <name> [...] | faults [NAME…]", file=sys.stderr)
     return 2
