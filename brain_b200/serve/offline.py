@@ -22,7 +22,7 @@ def serve_prompts(model, prompts: Sequence[Sequence[int]], max_new: int = 64, bl
     eng = QwenEngine(model, block_size=block_size, num_blocks=blocks_per_seq * n + n,
                      max_seq_len=blocks_per_seq * block_size, max_prefill=max(max_prompt, 1),
                      weights=weights, tp=tp, kv_dtype=kv_dtype, kv_clip=kv_clip)
-    sched = Scheduler(eng, max_batch=max_batch or n, eos=eos)
+    sched = Scheduler(eng, max_batch=max_batch or n, eos=eos, mixed=True)
     ids = [sched.submit(list(p), max_new, params, seed=seed + i) for i, p in enumerate(prompts)]
     t0 = time.perf_counter()
     sched.run_until_idle()
