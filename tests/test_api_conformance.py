@@ -443,3 +443,105 @@ def test_jsonl_protocol_over_unix_socket_and_tcp(tmp_path):
         t.close()
         ex.close()
     assert not os.path.exists(path)
+
+
+# ------------------------------------------------------------------------------------ response schemas
+# A compact restatement of the required fields and types of the published response objects (the
+# reference validates against vendored OpenAPI documents, crates/apiserve/tests/api.rs); a value is a
+# type, a tuple of alternatives, a dict of required fields, a one-element list (array of that), or
+# a callable predicate.  Keys ending in "?" are optional but typed when present.
+NULLABLE_STR = (str, type(None))
+USAGE = {"prompt_tokens": int, "completion_tokens": int, "total_tokens": int}
+TOOL_CALL = {"id": str, "type": lambda v: v == "function", "function": {"name": str, "arguments": str}}
+CHAT_COMPLETION = {
+    "id": str, "object": lambda v: v == "chat.completion", "created": int, "model": str,
+    "choices": [{"index": int, "finish_reason": lambda v: v in ("stop", "length", "tool_calls", "content_filter"),
+                 "message": {"role": lambda v: v == "assistant", "content": NULLABLE_STR, "tool_calls?": [TOOL_CALL]}}],
+    "usage": USAGE}
+CHAT_CHUNK = {
+    "id": str, "object": lambda v: v == "chat.completion.chunk", "created": int, "model": str,
+    "choices": [{"index": int, "delta": dict,
+                 "finish_reason": lambda v: v in (None, "stop", "length", "tool_calls", "content_filter")}],
+    "usage?": (USAGE, type(None))}
+MODEL_LIST = {"object": lambda v: v == "list", "data": [{"id": str, "object": lambda v: v == "model",
+                                                          "created": int, "owned_by": str}]}
+EMBEDDINGS = {"object": lambda v: v == "list", "model": str, "usage": {"prompt_tokens": int, "total_tokens": int},
+              "data": [{"object": lambda v: v == "embedding", "index": int, "embedding": [float]}]}
+OPENAI_ERROR = {"error": {"message": str, "type": str, "param": NULLABLE_STR, "code": NULLABLE_STR}}
+ANTHROPIC_MESSAGE = {
+    "id": str, "type": lambda v: v == "message", "role": lambda v: v == "assistant", "model": str,
+    "content": [{"type": lambda v: v in ("text", "tool_use", "thinking")}],
+    "stop_reason": lambda v: v in ("end_turn", "max_tokens", "stop_sequence", "tool_use"),
+    "stop_sequence": NULLABLE_STR, "usage": {"input_tokens": int, "output_tokens": int}}
+ANTHROPIC_ERROR = {"type": lambda v: v == "error", "error": {"type": str, "message": str}}
+
+
+def conforms(value, schema, path="$"):
+    """Raise AssertionError naming the first path where ``value`` departs from ``schema``."""
+    if isinstance(schema, dict):
+        assert isinstance(value, dict), f"{path}: expected an object, got {type(value).__name__}"
+        for key, sub in schema.items():
+            opt = key.endswith("?")
+            k = key[:-1] if opt else key
+            if k not in value:
+                assert opt, f"{path}.{k}: missing"
+                continue
+            conforms(value[k], sub, f"{path}.{k}")
+    elif isinstance(schema, list):
+        assert isinstance(value, list), f"{path}: expected an array"
+        for i, v in enumerate(value):
+            conforms(v, schema[0], f"{path}[{i}]")
+    elif isinstance(schema, tuple):
+        errs = []
+        for alt in schema:
+            try:
+                conforms(value, alt, path)
+                return
+            except AssertionError as e:
+                errs.append(str(e))
+        raise AssertionError(f"{path}: no alternative matched ({'; '.join(errs)})")
+    elif isinstance(schema, type):
+        ok = isinstance(value, schema) and not (schema is int and isinstance(value, bool))
+        if schema is float:
+            ok = isinstance(value, (int, float)) and not isinstance(value, bool)
+        assert ok, f"{path}: expected {schema.__name__}, got {value!r}"
+    else:
+        assert schema(value), f"{path}: unexpected value {value!r}"
+
+
+def test_response_objects_conform_to_the_published_schemas(srv):
+    with pytest.raises(AssertionError):
+        conforms({"id": "x"}, CHAT_COMPLETION)                  # the checker itself rejects a stub
+    for provider in ("openai", "openrouter"):
+        st, _, raw = call(srv, provider, "/v1/models")
+        conforms(json.loads(raw), MODEL_LIST)
+        st, _, raw = chat(srv, provider=provider, max_tokens=5)
+        assert st == 200
+        conforms(json.loads(raw), CHAT_COMPLETION)
+        tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object"}}}]
+        st, _, raw = chat(srv, TOOL_CALL_TRIGGER, provider=provider, tools=tools)
+        d = json.loads(raw)
+        conforms(d, CHAT_COMPLETION)
+        assert d["choices"][0]["finish_reason"] == "tool_calls" and d["choices"][0]["message"]["tool_calls"]
+        st, _, raw = chat(srv, provider=provider, stream=True, stream_options={"include_usage": True})
+        events = [d for _, d in sse(raw)]
+        assert events[-1] == "[DONE]"
+        chunks = [json.loads(d) for d in events[:-1]]
+        for c in chunks:
+            conforms(c, CHAT_CHUNK)
+        assert chunks[-1]["usage"] and chunks[0]["choices"][0]["delta"].get("role") == "assistant"
+        # every error status carries the error object
+        for st_want, (path, body, key) in {401: ("/v1/models", None, "bad"), 404: ("/v1/nope", None, "ok"),
+                                           400: ("/v1/chat/completions", {"model": "brain/mock"}, "ok")}.items():
+            st, _, raw = call(srv, provider, path, body, key=key)
+            assert st == st_want
+            conforms(json.loads(raw), OPENAI_ERROR)
+    st, _, raw = call(srv, "openai", "/v1/embeddings", {"model": "brain/mock", "input": ["a", "b"]})
+    conforms(json.loads(raw), EMBEDDINGS)
+    st, _, raw = call(srv, "anthropic", "/v1/messages", {"model": "brain/mock", "max_tokens": 16,
+                                                        "messages": [{"role": "user", "content": "hi"}]})
+    assert st == 200
+    conforms(json.loads(raw), ANTHROPIC_MESSAGE)
+    st, _, raw = call(srv, "anthropic", "/v1/messages", {"model": "brain/mock"})
+    assert st == 400
+    conforms(json.loads(raw), ANTHROPIC_ERROR)
