@@ -128,6 +128,10 @@ class BpeTokenizer:
             self._special_re = regex.compile("(" + "|".join(regex.escape(s) for s in
                                                             sorted(self.special, key=len, reverse=True)) + ")")
         self._id2special = {v: k for k, v in self.special.items()}
+        #: ids dropped by ``skip_special``: control tokens only.  Added tokens a tokenizer.json marks
+        #: ``"special": false`` (Qwen3's <think>, </think>, <tool_call>, ...) are matched as whole
+        #: strings when encoding but are ordinary text when decoding.
+        self.control = set(self._id2special)
         lib = _host.lib()
         self._h = lib.bbh_bpe_new()
         for tok, i in vocab.items():
@@ -169,6 +173,7 @@ class BpeTokenizer:
             pat = QWEN_SPLIT if "<|im_end|>" in special or len(model["vocab"]) > 60000 else GPT2_SPLIT
         tok = BpeTokenizer(model["vocab"], model["merges"], special, pat, eos,
                            normalize=_normal_form(d.get("normalizer")))
+        tok.control = {t["id"] for t in d.get("added_tokens", []) if t.get("special", True)}
         from .chat_template import ChatTemplate
         tok.chat_template = ChatTemplate.beside(path)
         return tok
@@ -223,7 +228,7 @@ class BpeTokenizer:
         for i in ids:
             i = int(i)
             if i in self._id2special:
-                if not skip_special:
+                if not (skip_special and i in self.control):
                     chunks.append(self._id2special[i].encode("utf-8"))
                 continue
             n = lib.bbh_bpe_token(self._h, i, buf, 256)

@@ -115,6 +115,8 @@ def _hf_bpe(kind, corpus):
     tok.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=600, special_tokens=[], show_progress=False,
                                                         initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
     tok.add_special_tokens(special)
+    if kind == "qwen":
+        tok.add_tokens(["<think>", "</think>"])       # added, matched whole, but not control tokens
     return tok
 
 
@@ -141,11 +143,14 @@ def test_bpe_tokenizer_matches_the_tokenizers_library(tmp_path, kind):
     rnd = random.Random(5)
     alphabet = "abc XYZ 019 .,!?'\n\t\r-_/éü中文́\U0001f600"
     cases += ["".join(rnd.choice(alphabet) for _ in range(rnd.randint(1, 60))) for _ in range(200)]
+    cases.append("<|im_start|>assistant\n<think>\nhm</think>\n\nyes<|im_end|>")
     for s in cases:
         want = hf.encode(s).ids
         got = mine.encode(s)
         assert got == want, repr(s)
         assert mine.decode(got) == hf.decode(want, skip_special_tokens=False), repr(s)
+        # control tokens are dropped, added non-special tokens (the reasoning markers) stay
+        assert mine.decode(got, skip_special=True) == hf.decode(want, skip_special_tokens=True), repr(s)
 
 
 CHATML_TEMPLATE = """{%- if tools %}
