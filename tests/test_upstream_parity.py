@@ -349,3 +349,25 @@ def test_rng_is_splitmix64_offset_by_one_step():
     r = Rng(0)
     assert r.gen_range_inclusive(3, 12) == 3 + published[1] % 10
     assert Rng(2**64 - 1).next_u64() == Rng(-1 & (2**64 - 1)).next_u64()      # wrapping seed arithmetic
+
+
+def test_sharded_bf16_directory_imports(tmp_path):
+    """The layout of published checkpoints: bf16 tensors spread over several shard files behind
+    model.safetensors.index.json, tied head absent from the files."""
+    from brain_b200.checkpoint import st
+    from brain_b200.checkpoint.hf_import import import_hf
+    hf, _ = _hf_model(str(tmp_path), "tied")
+    hf = hf.to(torch.bfloat16)
+    d = str(tmp_path / "sharded")
+    hf.save_pretrained(d, safe_serialization=True, max_shard_size="60KB")
+    assert os.path.exists(os.path.join(d, "model.safetensors.index.json"))
+    assert len([f for f in os.listdir(d) if f.endswith(".safetensors")]) > 2
+    out = str(tmp_path / "m.safetensors")
+    import_hf(d, out, block=64, dtype="BF16")
+    model, cfg, _ = st.load_model(out)
+    assert cfg["tie_word_embeddings"] is True
+    ids = torch.randint(0, 97, (1, 17), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf.float()(ids).logits
+        got = model.float()(ids.to(torch.int32)).float()
+    assert (got - want).abs().max().item() < 2e-3
