@@ -371,3 +371,15 @@ def test_sharded_bf16_directory_imports(tmp_path):
         want = hf.float()(ids).logits
         got = model.float()(ids.to(torch.int32)).float()
     assert (got - want).abs().max().item() < 2e-3
+
+
+def test_rope_base_is_read_from_either_config_generation():
+    from brain_b200.checkpoint.hf_import import config_from_hf
+    base = {"hidden_size": 64, "num_attention_heads": 4, "num_hidden_layers": 1, "intermediate_size": 96,
+            "vocab_size": 50, "model_type": "qwen3"}
+    assert config_from_hf(dict(base, rope_theta=5e5)).rope_theta == 5e5
+    assert config_from_hf(dict(base, rope_parameters={"rope_theta": 1e4, "rope_type": "default"})).rope_theta == 1e4
+    assert config_from_hf(dict(base, rope_theta=1e6, rope_scaling=None)).rope_theta == 1e6
+    assert config_from_hf(base).rope_theta == 1e6
+    with pytest.raises(ValueError, match="yarn"):
+        config_from_hf(dict(base, rope_theta=1e6, rope_scaling={"type": "yarn", "factor": 4.0}))
