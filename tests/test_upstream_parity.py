@@ -383,3 +383,52 @@ def test_rope_base_is_read_from_either_config_generation():
     assert config_from_hf(base).rope_theta == 1e6
     with pytest.raises(ValueError, match="yarn"):
         config_from_hf(dict(base, rope_theta=1e6, rope_scaling={"type": "yarn", "factor": 4.0}))
+
+
+def test_user_journey_import_store_serve_chat_matches_transformers(tmp_path):
+    """The whole path a user takes, with real processes: a Hugging Face directory (weights,
+    tokenizer.json, chat template) -> `brain qwen3 import --id` into the model store -> `brain serve
+    --stdio` selected by BRAIN_MODEL -> a chat turn through brain_py.  The reply equals what
+    transformers produces from the same directory (template, tokenizer, greedy generate)."""
+    pytest.importorskip("tokenizers")
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    from brain_py import Brain
+    corpus = ["hello world, how are you today? fine thanks. " * 5, "the capital of sweden is stockholm. " * 5] * 4
+    tok = _hf_bpe("qwen", corpus)
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3Config(vocab_size=tok.get_vocab_size(), hidden_size=64, intermediate_size=160,
+                                   num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                                   max_position_embeddings=256, rope_theta=10000.0, tie_word_embeddings=True)
+    hf = transformers.Qwen3ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.mul_(3.0)
+    d = str(tmp_path / "hf")
+    hf.save_pretrained(d, safe_serialization=True)
+    tok.save(os.path.join(d, "tokenizer.json"))
+    with open(os.path.join(d, "tokenizer_config.json"), "w") as f:
+        json.dump({"chat_template": CHATML_TEMPLATE, "eos_token": "<|im_end|>"}, f)
+    store = str(tmp_path / "store")
+    env = dict(os.environ, PYTHONPATH=root, CUDA_VISIBLE_DEVICES="")
+    brain = os.path.join(root, "brain")
+    r = subprocess.run([sys.executable, brain, "qwen3", "import", d, "--id", "Acme/Tiny-Qwen3", "--models-dir", store,
+                        "--block", "128"], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    msgs = [{"role": "system", "content": "Be brief."}, {"role": "user", "content": "hello world"}]
+    hf_tok = transformers.PreTrainedTokenizerFast(tokenizer_object=tok, eos_token="<|im_end|>")
+    hf_tok.chat_template = CHATML_TEMPLATE
+    ids = hf_tok.apply_chat_template(msgs, add_generation_prompt=True, tokenize=True, return_tensors="pt")
+    ids = ids["input_ids"] if not isinstance(ids, torch.Tensor) else ids
+    with torch.no_grad():
+        gen = hf.generate(ids, attention_mask=torch.ones_like(ids), max_new_tokens=10, do_sample=False,
+                          pad_token_id=0, eos_token_id=None)[0, ids.shape[1]:]
+    env2 = dict(env, BRAIN_MODEL="Acme/Tiny-Qwen3", BRAIN_MODELS_DIR=store, BRAIN_QWEN_CTX="128")
+    with Brain(transport="jsonl", brain_bin=brain, env=env2) as b:
+        assert b.models() == ["Acme/Tiny-Qwen3"]
+        out = b.generate(messages=msgs, model="Acme/Tiny-Qwen3", max_new=10, temp=0.0, ignore_eos=True)
+    assert out.get("prompt_tokens") == ids.shape[1]
+    assert out.get("completion_tokens") == 10
+    assert out.text() == hf_tok.decode(gen, skip_special_tokens=True)
