@@ -325,9 +325,12 @@ class LlmResident(ResidentModel):
         job.ignore_eos = bool(p.get("ignore_eos", False))
         job.stops = [s for s in json.loads(p["stop"]) if s] if p.get("stop") else []
         n = [0]
+        from ..data.chat import ReasoningStream
+        think = ReasoningStream()       # text inside <think>…</think> streams as reasoning, not content
 
         def on_token(piece: str):
-            progress(Progress("token", n[0], job.max_new, piece))
+            for kind, text in think.feed(piece):
+                progress(Progress(kind, n[0], job.max_new, text))
             n[0] += 1
         job.on_token = on_token
         job.cancel = inv.cancel
@@ -337,6 +340,8 @@ class LlmResident(ResidentModel):
         job.done.wait()
         if job.error is not None:
             raise job.error
+        for kind, text in think.flush():         # a held "<" that never became a marker
+            progress(Progress(kind, n[0], job.max_new, text))
         reasoning, visible = split_reasoning(job.text)
         calls, visible2 = parse_tool_calls(visible) if p.get("tools") else ([], visible)
         out = {"prompt_tokens": job.n_prompt, "completion_tokens": job.n_tokens, "finish_reason": job.finish}

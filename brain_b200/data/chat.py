@@ -94,6 +94,44 @@ def split_reasoning(text: str) -> Tuple[Optional[str], str]:
     return None, text
 
 
+class ReasoningStream:
+    """Streaming counterpart of :func:`split_reasoning`: text pieces go in, (kind, text) pairs come
+    out with kind ``"reasoning"`` inside a ``<think>`` block and ``"token"`` outside; the markers
+    themselves are dropped.  A piece that ends in what may be the start of a marker is held until
+    the next piece decides it."""
+
+    OPEN, CLOSE = "<think>", "</think>"
+
+    def __init__(self):
+        self.inside = False
+        self.held = ""
+
+    def feed(self, piece: str) -> List[Tuple[str, str]]:
+        out: List[Tuple[str, str]] = []
+        text = self.held + piece
+        self.held = ""
+        while text:
+            marker = self.CLOSE if self.inside else self.OPEN
+            k = text.find(marker)
+            if k < 0:
+                # keep a possible marker prefix at the end for the next piece
+                hold = next((n for n in range(min(len(marker) - 1, len(text)), 0, -1)
+                             if text.endswith(marker[:n])), 0)
+                if len(text) > hold:
+                    out.append(("reasoning" if self.inside else "token", text[:len(text) - hold]))
+                self.held = text[len(text) - hold:] if hold else ""
+                break
+            if k:
+                out.append(("reasoning" if self.inside else "token", text[:k]))
+            self.inside = not self.inside
+            text = text[k + len(marker):]
+        return out
+
+    def flush(self) -> List[Tuple[str, str]]:
+        held, self.held = self.held, ""
+        return [("reasoning" if self.inside else "token", held)] if held else []
+
+
 def parse_tool_calls(text: str) -> Tuple[List[Dict], str]:
     """All ``<tool_call>{json}</tool_call>`` blocks as ``{"name","arguments"}`` plus the text with
     the blocks removed."""

@@ -176,3 +176,21 @@ def test_streaming_joins_characters_split_across_tokens():
     assert stopped and "".join(pieces) == "naïve 🙂 日"
     pieces, stopped, _ = stream(["zzz", "🙂 日x"], 2)      # a prefix of a stop is held, then released
     assert not stopped and "".join(pieces) == text
+
+
+def test_reasoning_stream_routes_think_blocks():
+    from brain_b200.data.chat import ReasoningStream, split_reasoning
+    text = "<think>\nlet me see < 3 </thin no</think>\n\nThe answer is <b>4</b>."
+    for size in (1, 2, 3, 7, 100):
+        rs = ReasoningStream()
+        got = []
+        for i in range(0, len(text), size):
+            got += rs.feed(text[i:i + size])
+        got += rs.flush()
+        reasoning = "".join(t for k, t in got if k == "reasoning")
+        visible = "".join(t for k, t in got if k == "token")
+        assert "<think>" not in reasoning + visible and "</think>" not in reasoning + visible
+        want_r, want_v = split_reasoning(text)
+        assert reasoning.strip() == want_r and visible.strip() == want_v
+    rs = ReasoningStream()
+    assert rs.feed("plain <") == [("token", "plain ")] and rs.flush() == [("token", "<")]
