@@ -8,8 +8,8 @@ all-gathers its input, a row-parallel linear reduce-scatters its output:
 
 ``impl='fused'`` runs each of these as ONE tcgen05 GEMM launch whose collective half happens inside
 the kernel over NVLink peer memory (``bb_gemm_bf16_tp``: data-mover CTAs + per-tile flags for the
-all-gather side, per-destination TMA stores + a landed handshake for the reduce-scatter side; no
-multicast loads).  ``impl='nccl'`` is the baseline made of ``torch.distributed`` collectives and
+all-gather side, per-destination TMA stores + a landed handshake for the reduce-scatter side; every
+load is issued per CTA).  ``impl='nccl'`` is the baseline made of ``torch.distributed`` collectives and
 separate GEMMs; CPU (gloo) ranks use the same baseline with PyTorch matmuls.
 
 Reference: the column-/row-parallel MLP and attention-by-heads primitives of
