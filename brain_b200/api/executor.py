@@ -61,6 +61,7 @@ class Executor:
         self.edge_limit = edge_limit
         self._edge = 0
         self._edge_lock = threading.Lock()
+        self._lanes_lock = threading.Lock()
         self.pool = ThreadPoolExecutor(max_workers=workers, thread_name_prefix="lane")
         self.started = time.time()
 
@@ -81,7 +82,12 @@ class Executor:
         return self.residency.describe(model_id) if self.residency is not None else None
 
     def _evicted(self, model_id: str, model) -> None:
-        self.lanes.pop(model_id, None)
+        # only the lane of the model that was evicted goes: a request that raced the eviction and
+        # already re-loaded the model holds a newer lane under the same id
+        with self._lanes_lock:
+            lane = self.lanes.get(model_id)
+            if lane is not None and lane.model is model:
+                self.lanes.pop(model_id, None)
 
     def _lane(self, model_id: str):
         """(lane, release) — loads the model through the residency manager when it is not resident."""
@@ -95,9 +101,10 @@ class Executor:
             model = self.residency.acquire(model_id, COLD_ADMIT_DEADLINE_S)
         except (InsufficientMemory, TimeoutError) as e:
             raise Busy(str(e))
-        lane = self.lanes.get(model_id)
-        if lane is None or lane.model is not model:
-            lane = self.lanes[model_id] = _Lane(model)
+        with self._lanes_lock:      # two first requests must share one lane (one semaphore, one stats)
+            lane = self.lanes.get(model_id)
+            if lane is None or lane.model is not model:
+                lane = self.lanes[model_id] = _Lane(model)
         return lane, (lambda: self.residency.release(model_id))
 
     def in_flight(self) -> int:

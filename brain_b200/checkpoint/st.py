@@ -86,9 +86,11 @@ class WeightReader:
         numel = 1
         for s in shape:
             numel *= s
+        if dt not in _ES:
+            raise ValueError(f"{name}: unsupported dtype {dt}")
+        if (en - b) != numel * _ES[dt]:
+            raise ValueError(f"{name}: byte length does not match shape/dtype")
         if dt in _DT:
-            if (en - b) != numel * _ES[dt]:
-                raise ValueError(f"{name}: byte length does not match shape/dtype")
             out = torch.empty(numel, dtype=torch.float32)
             rc = _host.lib().bbh_st_decode_f32(self._h, b, numel, _DT[dt], out.data_ptr())
             if rc != 0:
@@ -99,6 +101,9 @@ class WeightReader:
             rc = _host.lib().bbh_st_read_raw(self._h, b, en - b, out.data_ptr())
             if rc != 0:
                 raise IOError(f"read of {name} failed ({rc})")
+            if dt == "U32":
+                # torch has no arithmetic on uint32: widen, so values >= 2^31 stay positive
+                out = (out.to(torch.int64) & 0xFFFFFFFF)
             return out.view(shape)
         if dt == "F8_E4M3":
             # raw (unscaled) fp8 values as fp32; block scales are applied by the importer

@@ -82,6 +82,11 @@ class Trainer:
         else:
             self.opt.step(lr, self.wd, self.clip, extra_scale)
         self.step_count += 1
+        if self.cuda:
+            # a kernel whose bounded wait ran out skipped its work: stop instead of training on
+            # garbage (non-blocking; reports the previous step's kernels)
+            from .ops import _cuda
+            _cuda.poll_error()
 
     def train_step(self, tokens, targets, lr: float, micro_batch: Optional[int] = None,
                    global_count: Optional[int] = None):

@@ -118,8 +118,30 @@ def read_error(clear: bool = True) -> int:
 
 
 def check_error() -> None:
-    code = read_error(True)
+    code = int(_error_source()) if _error_source is not None else read_error(True)
     if code != 0:
+        raise NativeError(f"device error {code}: {_ERR_NAMES.get(code, 'unknown')}")
+
+
+#: test seam: a callable returning an error code replaces the native poll/read (CPU tests)
+_error_source = None
+
+
+def poll_error() -> None:
+    """Non-blocking check of the device error word, made once per step by the trainers and the
+    serving engine.  Each call harvests the asynchronous copy the previous call enqueued and
+    enqueues a new one on the current stream, so a bounded wait that ran out inside a kernel of
+    step ``n`` raises :class:`NativeError` at step ``n + 1`` without a device synchronisation."""
+    if _error_source is not None:
+        code = int(_error_source())
+    else:
+        fn = lib().bb_poll_error
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_void_p]
+        code = int(fn(stream_ptr()))
+    if code > 0:
+        if _error_source is None:
+            read_error(True)
         raise NativeError(f"device error {code}: {_ERR_NAMES.get(code, 'unknown')}")
 
 

@@ -157,6 +157,9 @@ class Trainer3D:
             dist.all_reduce(self.store.grads[: self.store.n_train], group=self.pgs.group("dp"))
         ss = self._global_sumsq() if self.clip else None
         self.opt.step(lr, self.wd, self.clip, sumsq=ss)
+        if self.opt.store.device.type == "cuda":
+            from ..ops import _cuda
+            _cuda.poll_error()
         if ss is not None:
             self.last_grad_norm = ss.sqrt()
         self.step_count += 1

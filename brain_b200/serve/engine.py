@@ -31,6 +31,7 @@ import torch
 from ..models.config import QwenConfig
 from ..ops import functional as F
 from ..ops import reference as ref
+from ..ops import _cuda
 from ..ops._cuda import L, call, stream_ptr
 from ..ops.attention import flash_attention, flash_attention_into
 
@@ -397,6 +398,12 @@ class QwenEngine:
 
     # ------------------------------------------------------------------ PagedDecoder interface
     @torch.no_grad()
+    def check_device(self) -> None:
+        """Raise if a kernel of the step just read back reported a bounded-wait timeout (the
+        scheduler calls this once per step, after the token read-back, before it commits)."""
+        if self.device.type == "cuda":
+            _cuda.check_error()
+
     def prefill_chunk(self, tokens: np.ndarray, start: int, block_table: np.ndarray, last: bool,
                       greedy: bool = True):
         """Process prompt positions [start, start+n) of one sequence.  Returns (first token, top-k

@@ -257,6 +257,14 @@ class Scheduler:
                 outs = batch([(p[5], p[1], p[6], p[3], p[4]) for p in plan])
             else:
                 outs = [self.dec.prefill_chunk(p[5], p[1], p[6], p[3], p[4]) for p in plan]
+        if n and decoded is None:
+            decoded = self.dec.decode(toks, pos, bts, win.value, all_greedy)
+        # the tokens were read back, so the device is idle: one look at the error word before the
+        # commits.  A kernel whose bounded wait ran out raises here and the caller fails the step's
+        # requests instead of committing garbage tokens.
+        chk = getattr(self.dec, "check_device", None)
+        if chk is not None and (plan or n):
+            chk()
         if plan:
             for p, (tok, topk) in zip(plan, outs):
                 if p[3]:
@@ -265,8 +273,6 @@ class Scheduler:
                     lib.bbh_sched_commit_prefill(self._h, p[0], p[2], 0, 0)
         # ---- one batched decode
         if n:
-            if decoded is None:
-                decoded = self.dec.decode(toks, pos, bts, win.value, all_greedy)
             greedy_toks, topks = decoded
             if all_greedy:
                 out = np.ascontiguousarray(np.asarray(greedy_toks, dtype=np.uint32).reshape(n, win.value))

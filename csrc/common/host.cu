@@ -105,4 +105,38 @@ BB_API int bb_read_error(int clear) {
   return v;
 }
 
+// Non-blocking check of the device error word: each call first harvests the copy that the previous
+// call enqueued (if it has completed) and then enqueues a new async copy of the word into pinned host
+// memory on `stream`.  Returns the last harvested value (0 = clean, >0 = a kernel's bounded wait ran
+// out), -1 on a set-up failure.  The answer therefore trails the kernels by one call; the caller
+// makes one call per step.  A non-zero value is sticky until bb_read_error(1) clears the word.
+BB_API int bb_poll_error(void* stream) {
+  struct Slot { int* host = nullptr; cudaEvent_t ev = nullptr; bool pending = false; int last = 0; };
+  static Slot slots[64];
+  static std::mutex mu;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return -1;
+  int* w = bb::device_error_word();
+  if (!w) return -1;
+  std::lock_guard<std::mutex> lk(mu);
+  Slot& s = slots[dev];
+  if (!s.host) {
+    if (cudaHostAlloc(reinterpret_cast<void**>(&s.host), sizeof(int), cudaHostAllocDefault) != cudaSuccess)
+      return -1;
+    *s.host = 0;
+    if (cudaEventCreateWithFlags(&s.ev, cudaEventDisableTiming) != cudaSuccess) return -1;
+  }
+  if (s.pending) {
+    if (cudaEventQuery(s.ev) != cudaSuccess) return s.last;  // still in flight: keep the older answer
+    s.last = *s.host;
+    s.pending = false;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(s.host, w, sizeof(int), cudaMemcpyDeviceToHost, st) == cudaSuccess &&
+      cudaEventRecord(s.ev, st) == cudaSuccess)
+    s.pending = true;
+  return s.last;
+}
+
 BB_API int bb_sm_count() { return bb::sm_count(); }

@@ -4,6 +4,7 @@
 // contract (who cannot allocate, the size limit, sharing and ordering rules).
 #include "sumsq_noalloc.h"
 
+#include <atomic>
 #include <cstdio>
 
 #include "../common/host.hpp"
@@ -55,13 +56,16 @@ __global__ void noalloc_final_kernel(const float* __restrict__ part, int np, flo
 // Device address of the scratch array, looked up once per device with that device current.
 // In host code `g_noalloc_partials` is only a stand-in symbol, never a usable pointer.
 float* scratch_for_current_device(int* status) {
-  static float* ptrs[64] = {nullptr};
+  // Host threads may make their first call on a device at the same time: the cache entries are
+  // atomics (both threads would store the same address, so relaxed ordering is enough).
+  static std::atomic<float*> ptrs[64];
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     *status = BB_SUMSQ_NOALLOC_ESETUP;
     return nullptr;
   }
-  if (!ptrs[dev]) {
+  float* cached = ptrs[dev].load(std::memory_order_relaxed);
+  if (!cached) {
     float* p = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_partials);
     if (e != cudaSuccess || p == nullptr) {
@@ -70,10 +74,11 @@ float* scratch_for_current_device(int* status) {
       *status = BB_SUMSQ_NOALLOC_ESETUP;
       return nullptr;
     }
-    ptrs[dev] = p;
+    ptrs[dev].store(p, std::memory_order_relaxed);
+    cached = p;
   }
   *status = 0;
-  return ptrs[dev];
+  return cached;
 }
 
 }  // namespace
@@ -99,6 +104,8 @@ extern "C" __attribute__((visibility("default"))) int bb_sumsq_noalloc(const flo
   if (blocks < 1) blocks = 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   noalloc_partial_kernel<<<(int)blocks, 512, 0, s>>>(g, n, scratch);
+  const cudaError_t first = cudaGetLastError();
+  if (first != cudaSuccess) return (int)first;  // never sum stale partials into `out`
   noalloc_final_kernel<<<1, 256, 0, s>>>(scratch, (int)blocks, out, accumulate);
   return (int)cudaGetLastError();
 }

@@ -20,7 +20,8 @@
 //   * `g` must be 16-byte aligned; `out` is one float in device memory supplied by the caller.
 //   * The first call on each device looks up the device address of the scratch array
 //     (cudaGetSymbolAddress).  Make that first call before starting any stream capture on that
-//     device.
+//     device.  First calls made by several host threads at once are safe (the cached address is
+//     an atomic and every thread would store the same value).
 //   * All calls on a device share the one scratch array, which still holds the previous call's
 //     partial sums when the next call starts (every slot that is read is rewritten first, so no
 //     clearing is needed).  Two calls whose kernels overlap on the GPU — different streams, or

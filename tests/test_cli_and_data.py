@@ -173,6 +173,32 @@ def test_chat_and_toolcall_data(tmp_path):
 
 
 # ------------------------------------------------------------------------------------ checkpoints
+def test_safetensors_reader_checks_integer_ranges_and_widens_u32(tmp_path):
+    """A header whose byte range is shorter than shape x element size is refused for every dtype
+    (not only the floats), and U32 values above 2^31 come back positive."""
+    import json
+    import struct
+    import numpy as np
+    from brain_b200.checkpoint import st
+
+    def write(path, hdr, data):
+        h = json.dumps(hdr).encode()
+        h += b" " * (-len(h) % 8)
+        with open(path, "wb") as f:
+            f.write(struct.pack("<Q", len(h)) + h + data)
+
+    vals = np.array([1, 2 ** 31 + 5, 2 ** 32 - 1, 7], dtype=np.uint32)
+    good = str(tmp_path / "u.safetensors")
+    write(good, {"u": {"dtype": "U32", "shape": [4], "data_offsets": [0, 16]}}, vals.tobytes())
+    with st.WeightReader(good) as r:
+        assert r.read("u").tolist() == [1, 2 ** 31 + 5, 2 ** 32 - 1, 7]
+    short = str(tmp_path / "s.safetensors")
+    write(short, {"i": {"dtype": "I32", "shape": [1000], "data_offsets": [0, 16]}}, vals.tobytes())
+    with st.WeightReader(short) as r:
+        with pytest.raises(ValueError, match="byte length"):
+            r.read("i")
+
+
 def test_checkpoint_roundtrip_names_and_metadata(tmp_path):
     from brain_b200.checkpoint import st
     from brain_b200.models.config import GptConfig, QwenConfig

@@ -21,6 +21,7 @@ pytestmark = pytest.mark.gpu
 
 MAX_ELEMS = 1 << 28
 ESIZE = -3
+EARG = -1
 
 
 def _lib():
@@ -74,5 +75,18 @@ def test_noalloc_sumsq_rejects_oversized_input():
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     assert fn(x.data_ptr(), MAX_ELEMS + 1, out.data_ptr(), 0, stream) == ESIZE
     assert fn(x.data_ptr(), -1, out.data_ptr(), 0, stream) == ESIZE
+    torch.cuda.synchronize()
+    assert out.item() == -7.0   # nothing was launched
+
+
+def test_noalloc_sumsq_rejects_bad_pointers():
+    fn, _ = _lib()
+    dev = torch.device("cuda:0")
+    x = torch.ones(64, device=dev)
+    out = torch.full((1,), -7.0, device=dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert fn(x.data_ptr() + 4, 16, out.data_ptr(), 0, stream) == EARG     # input not 16-byte aligned
+    assert fn(x.data_ptr(), 16, None, 0, stream) == EARG                   # no output
+    assert fn(None, 16, out.data_ptr(), 0, stream) == EARG                 # no input
     torch.cuda.synchronize()
     assert out.item() == -7.0   # nothing was launched
