@@ -30,14 +30,17 @@ from ..ops import functional as F
 from ..ops import reference as ref
 
 
+from .symm import default_wait_seconds
+
+
 class ExpertParallel:
     def __init__(self, group=None, impl: str = "fused", device=None, arena_mb: int = 1024,
-                 wait_seconds: float = 20.0):
+                 wait_seconds: float = None):
         self.group = group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.impl = impl
-        self.wait_seconds = wait_seconds
+        self.wait_seconds = default_wait_seconds() if wait_seconds is None else float(wait_seconds)
         self.epoch = 0
         self._slots = {}
         if self.world > 1 and impl == "fused":

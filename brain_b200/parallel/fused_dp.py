@@ -15,8 +15,11 @@ from ..ops._cuda import L, call, stream_ptr
 from .symm import SymmArena
 
 
+from .symm import default_wait_seconds
+
+
 class FusedDP:
-    def __init__(self, dp, store, opt, wait_seconds: float = 20.0):
+    def __init__(self, dp, store, opt, wait_seconds: float = None):
         self.dp, self.store, self.opt = dp, store, opt
         self.world, self.rank = dp.world, dp.rank
         dev = store.device
@@ -50,7 +53,7 @@ class FusedDP:
         if m is not None:
             self.decay_mask = m[opt.lo:opt.hi].contiguous()
         self.epoch = 0
-        self.wait_seconds = wait_seconds
+        self.wait_seconds = default_wait_seconds() if wait_seconds is None else float(wait_seconds)
         torch.cuda.synchronize(dev)
         dist.barrier(group=dp.group)
 

@@ -11,6 +11,15 @@ import torch
 import torch.distributed as dist
 
 
+def default_wait_seconds() -> float:
+    """Limit of every in-kernel wait on a peer (a flag another GPU writes).  Ranks meet at these
+    waits after identical work, so steady-state skew is milliseconds; 2 s covers first-step set-up
+    skew while keeping a shared GPU from being held by a rank whose peer has gone.
+    ``BRAIN_PEER_WAIT_S`` overrides it."""
+    import os
+    return float(os.environ.get("BRAIN_PEER_WAIT_S", "2.0"))
+
+
 class SymmArena:
     def __init__(self, nbytes: int, device, group=None):
         import torch.distributed._symmetric_memory as symm_mem

@@ -26,14 +26,17 @@ import torch.distributed as dist
 from ..ops import functional as F
 
 
+from .symm import default_wait_seconds
+
+
 class TensorParallel:
     def __init__(self, group=None, impl: str = "nccl", device=None, arena_mb: int = 512,
-                 wait_seconds: float = 20.0):
+                 wait_seconds: float = None):
         self.group = group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.impl = impl if self.world > 1 else "none"
-        self.wait_seconds = wait_seconds
+        self.wait_seconds = default_wait_seconds() if wait_seconds is None else float(wait_seconds)
         self.epoch = 0
         self._slots = {}
         if self.impl == "fused":

@@ -152,10 +152,12 @@ class PrefixCache:
         return out[:n].tolist()
 
     def insert_chain(self, prompt, blocks, start: int, alloc: BlockAllocator) -> None:
+        self._alloc = alloc     # the native index is attached to this pool: keep the pool alive longer
         p = np.ascontiguousarray(np.asarray(prompt, dtype=np.uint32))
         b = np.ascontiguousarray(np.asarray(blocks, dtype=np.uint32))
         _host.lib().bbh_prefix_insert_chain(self._h, alloc._h, p.ctypes.data, p.size, b.ctypes.data,
                                             b.size, start)
 
     def evict(self, want: int, alloc: BlockAllocator) -> int:
+        self._alloc = alloc
         return int(_host.lib().bbh_prefix_evict(self._h, alloc._h, want))

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #define BB_API extern "C" __attribute__((visibility("default")))
 
 namespace bb {
@@ -29,6 +31,31 @@ int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int elem_size, const 
 int make_tmap_3d(CUtensorMap* out, CUtensorMapDataType dt, int elem_size, const void* base,
                  uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes, uint64_t s2_bytes,
                  uint32_t box0, uint32_t box1, bool swizzle128 = true);
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) belongs to the (function, device) pair, not to
+// the process: a launcher keeps one of these per kernel instantiation and sets the attribute the
+// first time it runs with each device current.
+struct PerDeviceOnce {
+  std::atomic<bool> done[64];
+  PerDeviceOnce() { for (auto& d : done) d.store(false, std::memory_order_relaxed); }
+  // true when the attribute still has to be set on the current device; `dev` receives its index
+  bool need(int* dev) {
+    *dev = 0;
+    cudaGetDevice(dev);
+    if (*dev < 0 || *dev >= 64) { *dev = -1; return true; }
+    return !done[*dev].load(std::memory_order_acquire);
+  }
+  void mark(int dev) { if (dev >= 0) done[dev].store(true, std::memory_order_release); }
+};
+
+template <typename K>
+inline cudaError_t ensure_dyn_smem(PerDeviceOnce& once, K kernel, int bytes) {
+  int dev;
+  if (!once.need(&dev)) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) once.mark(dev);
+  return e;
+}
 
 int* device_error_word();  // per-device int, zero-initialised, lives until exit
 int sm_count();

@@ -19,6 +19,13 @@
 namespace bb {
 
 struct FaBwdArgs {
+  // row-major operands as plain pointers (leading dimensions in elements): the tiles that stay
+  // resident for a whole CTA are copied global -> registers -> TMEM by the softmax warps
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const __nv_bfloat16* dout;
+  int ldq, ldk, ldv, lddo;
   const float* lse;    // [B, hq, T] natural log
   const float* delta;  // [B, hq, T]
   __nv_bfloat16* dQ;
@@ -104,19 +111,41 @@ __global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ o, int ldo,
 // although it overwrites the TMEM columns that dQ reads its dS operand from.
 // Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9 softmax.
 // TMEM columns: S[g] at g*64, dP[g] at 128 + g*64 (64 fp32 columns each; the packed bf16 dS of a
-// unit overwrites the first 32 columns of its S buffer), dQ at 256.
+// unit overwrites the first 32 columns of its S buffer), dQ at 256, and the CTA's Q and dO tiles as
+// packed bf16 at 384 and 448 (HD/2 columns each).  Q and dO are the A operands of every S and dP
+// MMA of the CTA: held in TMEM they cost no shared-memory bandwidth, which is what bounds an
+// M=128, N=64 MMA whose A operand comes from shared memory (4 KB of A against 2 KB of B per k-step).
 template <int HD>
 struct DqCfg {
   static constexpr int NSUB = HD / 64;
   static constexpr int TILE = NSUB * SUB;
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_DO = OFF_Q + TILE;
-  static constexpr int OFF_K = OFF_DO + TILE;
+  static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + 2 * TILE;
   static constexpr int OFF_BAR = OFF_V + 2 * TILE;
   static constexpr int SMEM_MIN = OFF_BAR + 256 + 1024;
   static constexpr int SMEM = SMEM_MIN < 120 * 1024 ? 120 * 1024 : SMEM_MIN;
+  static constexpr uint32_t TM_DQ = 256, TM_Q = 384, TM_DO = 448;
 };
+
+// Copy one bf16 row of HD elements from global memory into this thread's TMEM lane (packed pairs).
+template <int HD>
+__device__ __forceinline__ void row_to_tmem(const __nv_bfloat16* src, bool valid, uint32_t taddr) {
+#pragma unroll
+  for (int c = 0; c < HD / 64; ++c) {
+    uint32_t w[32];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint4 x = valid ? __ldg(reinterpret_cast<const uint4*>(src + c * 64) + i)
+                            : make_uint4(0u, 0u, 0u, 0u);
+      w[4 * i] = x.x;
+      w[4 * i + 1] = x.y;
+      w[4 * i + 2] = x.z;
+      w[4 * i + 3] = x.w;
+    }
+    tmem_st32(taddr + c * 32, w);
+  }
+  tmem_wait_st();
+}
 
 static constexpr int BWD_THREADS = 320;
 
@@ -138,12 +167,10 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint8_t* sQ = smem + Cfg::OFF_Q;
-  uint8_t* sDO = smem + Cfg::OFF_DO;
   uint8_t* sK = smem + Cfg::OFF_K;
   uint8_t* sV = smem + Cfg::OFF_V;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
-  uint64_t* q_full = bars;         // Q and dO
+  uint64_t* qdo_ready = bars;      // Q and dO rows stored to TMEM (256 arrivals)
   uint64_t* k_full = bars + 1;     // 2 stages
   uint64_t* k_empty = bars + 3;    // 2
   uint64_t* v_full = bars + 5;     // 2
@@ -167,7 +194,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    mbar_init(qdo_ready, 256);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
@@ -187,17 +214,12 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tDQ = tmem_base + 256;
+  const uint32_t tDQ = tmem_base + Cfg::TM_DQ;
+  const uint32_t tQ = tmem_base + Cfg::TM_Q, tDO = tmem_base + Cfg::TM_DO;
   long long* tl = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 ? args.tl : nullptr;
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, 2 * Cfg::TILE);
-#pragma unroll
-      for (int c = 0; c < NSUB; ++c) {
-        tma_load_2d(sQ + c * SUB, &tmQ, q_full, h * HD + c * 64, b * T + q0);
-        tma_load_2d(sDO + c * SUB, &tmDO, q_full, h * HD + c * 64, b * T + q0);
-      }
       bool ok = true;
       for (int j = 0; j < n_blocks && ok; ++j) {
         const int st = j & 1;
@@ -222,11 +244,10 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc(1, 1, 1, 0, 0, 128, 64);
       constexpr uint32_t idesc_dq = umma_idesc(1, 1, 1, 0, 1, 128, HD);
-      bool ok = mbar_wait(q_full, 0);
+      bool ok = mbar_wait(qdo_ready, 0);
       if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
-      const uint32_t aq = smem_u32(sQ), ado = smem_u32(sDO);
-      // S and dP of half g of block j into TMEM buffer g
-      const uint32_t lq = desc_lo_kmajor(smem_u32(sQ)), ldo = desc_lo_kmajor(smem_u32(sDO));
+      tc_fence_after();
+      // S and dP of half g of block j into TMEM buffer g (A = Q / dO rows resident in TMEM)
       auto issue_sdp = [&](int j, int g) {
         const int st = j & 1;
         const uint32_t lk = desc_lo_kmajor(smem_u32(sK + st * Cfg::TILE) + g * 8192);
@@ -234,10 +255,10 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t tS = tmem_base + g * 64, tDP = tmem_base + 128 + g * 64;
 #pragma unroll
         for (int t = 0; t < HD / 16; ++t)
-          umma_f16_ss(tS, desc_of(lq + kstep_kmajor(t)), desc_of(lk + kstep_kmajor(t)), idesc_s, t != 0);
+          umma_f16_ts(tS, tQ + t * 8, desc_of(lk + kstep_kmajor(t)), idesc_s, t != 0);
 #pragma unroll
         for (int t = 0; t < HD / 16; ++t)
-          umma_f16_ss(tDP, desc_of(ldo + kstep_kmajor(t)), desc_of(lv + kstep_kmajor(t)), idesc_s, t != 0);
+          umma_f16_ts(tDP, tDO + t * 8, desc_of(lv + kstep_kmajor(t)), idesc_s, t != 0);
         umma_commit(&sdp_full[g]);
         if (g == 1) umma_commit(&v_empty[st]);
       };
@@ -297,6 +318,14 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float lse2 = row_ok ? args.lse[stat] * 1.4426950408889634f : INFINITY;
     const float dlt = row_ok ? -args.delta[stat] * args.scale : 0.f;  // -delta * scale
     const uint32_t tS = tmem_base + g * 64 + lane_sel, tDP = tmem_base + 128 + g * 64 + lane_sel;
+    // warpgroup 0 parks the Q tile in TMEM, warpgroup 1 the dO tile (one row per thread)
+    {
+      const size_t grow = (size_t)(b * T + (row_ok ? q_idx : 0));
+      const __nv_bfloat16* src = (g == 0 ? args.q + grow * args.ldq : args.dout + grow * args.lddo) + h * HD;
+      row_to_tmem<HD>(src, row_ok, (g == 0 ? tQ : tDO) + lane_sel);
+      tc_fence_before();
+      mbar_arrive(qdo_ready);
+    }
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
       ok = mbar_wait(&sdp_full[g], j & 1);
@@ -674,9 +703,22 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
 template <int HD>
 static int launch_fa_bwd(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
-                         const void* dout, int lddo, const FaBwdArgs& a, cudaStream_t stream) {
+                         const void* dout, int lddo, const FaBwdArgs& a_in, cudaStream_t stream) {
+  FaBwdArgs a = a_in;
+  a.q = static_cast<const __nv_bfloat16*>(q);
+  a.k = static_cast<const __nv_bfloat16*>(k);
+  a.v = static_cast<const __nv_bfloat16*>(v);
+  a.dout = static_cast<const __nv_bfloat16*>(dout);
+  a.ldq = ldq;
+  a.ldk = ldk;
+  a.ldv = ldv;
+  a.lddo = lddo;
   CUtensorMap tmQ, tmK, tmV, tmDO;
   const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(dout)) & 15)
+    return BB_EARG;
+  if ((ldq | ldk | ldv | lddo) & 7) return BB_EARG;
   int rc = make_tmap_2d(&tmQ, bf, 2, q, (uint64_t)a.hq * HD, (uint64_t)a.B * a.T, (uint64_t)ldq * 2,
                         64, 128);
   if (rc) return rc;
@@ -689,16 +731,12 @@ static int launch_fa_bwd(const void* q, int ldq, const void* k, int ldk, const v
   rc = make_tmap_2d(&tmDO, bf, 2, dout, (uint64_t)a.hq * HD, (uint64_t)a.B * a.T,
                     (uint64_t)lddo * 2, 64, 128);
   if (rc) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(fa_bwd_dq_kernel<HD>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         DqCfg<HD>::SMEM);
+  static PerDeviceOnce once_dq, once_dkv;
+  {
+    cudaError_t e = ensure_dyn_smem(once_dq, fa_bwd_dq_kernel<HD>, DqCfg<HD>::SMEM);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(fa_bwd_dkv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             DkvCfg<HD>::SMEM);
+    e = ensure_dyn_smem(once_dkv, fa_bwd_dkv_kernel<HD>, DkvCfg<HD>::SMEM);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
   }
   dim3 gq((a.T + 127) / 128, a.hq, a.B);
   fa_bwd_dq_kernel<HD><<<gq, BWD_THREADS, DqCfg<HD>::SMEM, stream>>>(tmQ, tmK, tmV, tmDO, a);

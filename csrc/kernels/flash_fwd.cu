@@ -619,15 +619,12 @@ static int launch_fa_fwd(const void* q, int ldq, const void* k, int ldk, const v
   rc = make_tmap_2d(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, (uint64_t)a.hk * HD,
                     (uint64_t)a.B * a.S, (uint64_t)ldv * 2, 64, 128);
   if (rc) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<HD>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+  static PerDeviceOnce once1, once2;
+  {
+    cudaError_t e = ensure_dyn_smem(once1, fa_fwd_kernel<HD>, Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(fa_fwd2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg::SMEM);
+    e = ensure_dyn_smem(once2, fa_fwd2_kernel<HD>, Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
   }
   dim3 grid((a.T + 127) / 128, a.hq, a.B);
   // the two-unit form is the default (478 -> 309 us at B4 T4096 16q/8kv hd128); BB_FA_FWD=1 selects

@@ -615,12 +615,10 @@ static int launch_gemm(const void* A, const void* B, const GemmArgs& args, int l
     // K slices add into C concurrently: only the TMA reduce-add epilogue does that atomically
     if (!largs.tma_store || args.tp_mode || args.out_mode != 2) largs.split_k = 1;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, I8>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+  static PerDeviceOnce smem_once;
+  {
+    cudaError_t e = ensure_dyn_smem(smem_once, gemm_kernel<BN, I8>, Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
   }
   const long tiles = (long)((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN) *
                      (args.group_mode == 2 ? args.num_groups : (largs.split_k > 1 ? largs.split_k : 1));

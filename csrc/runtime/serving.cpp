@@ -1,10 +1,8 @@
 // Serving runtime: paged KV bookkeeping and the continuous-batching scheduler.
 //
-//  * BlockAllocator — free list of fixed-size KV blocks with u16 reference counts.
-//  * BlockTable     — a sequence's logical->physical block map (append / reserve / truncate /
-//                     release / fork / unshare_tail / adopt_prefix).
-//  * PrefixCache    — full, immutable prompt blocks keyed by (parent physical block, token ids),
-//                     LRU eviction of cache-only blocks.
+//  * kv::KvPool / kv::SeqBlocks / kv::PrefixIndex (kv_pool.hpp) — block pool with an intrusive
+//                     free stack, per-sequence block maps, and the chain-hashed prefix index with
+//                     its O(1) LRU list of idle cached blocks.
 //  * Scheduler      — per step: admit waiting requests FIFO while their whole budget
 //                     (prompt + max_new) fits the free blocks and the prefill-token budget
 //                     (2 x max_prefill, at least one request) remains, evicting LRU prefix-cache
@@ -15,7 +13,7 @@
 //
 // The scheduler does not touch the GPU: `plan()` emits the prefill chunks and the decode batch as
 // flat arrays, the Python engine launches the kernels and reports sampled tokens back through
-// `commit_*`.  Reference: crates/model/src/paged.rs:20-328, crates/model/src/serve.rs:262-776.
+// `commit_*`.  Reference: crates/model/src/serve.rs:262-776 (scheduler semantics).
 #include <algorithm>
 #include <cstdint>
 #include <cstring>
@@ -26,177 +24,15 @@
 #include <unordered_map>
 #include <vector>
 
+#include "kv_pool.hpp"
+
 #define BBH_API extern "C" __attribute__((visibility("default")))
 
 namespace {
 
-constexpr uint32_t PREFIX_ROOT = 0xFFFFFFFFu;
-
-class BlockAllocator {
- public:
-  BlockAllocator(uint32_t num_blocks, uint32_t block_size)
-      : block_size_(block_size), num_blocks_(num_blocks), refcount_(num_blocks, 0) {
-    free_.reserve(num_blocks);
-    for (uint32_t i = num_blocks; i > 0; --i) free_.push_back(i - 1);  // pop yields low ids first
-  }
-  uint32_t block_size() const { return block_size_; }
-  uint32_t num_blocks() const { return num_blocks_; }
-  uint32_t free_blocks() const { return static_cast<uint32_t>(free_.size()); }
-  uint16_t refcount(uint32_t b) const { return refcount_[b]; }
-  bool alloc(uint32_t* out) {
-    if (free_.empty()) return false;
-    *out = free_.back();
-    free_.pop_back();
-    refcount_[*out] = 1;
-    return true;
-  }
-  void incref(uint32_t b) { ++refcount_[b]; }
-  bool decref(uint32_t b) {  // false = double free
-    if (refcount_[b] == 0) return false;
-    if (--refcount_[b] == 0) free_.push_back(b);
-    return true;
-  }
-
- private:
-  uint32_t block_size_, num_blocks_;
-  std::vector<uint32_t> free_;
-  std::vector<uint16_t> refcount_;
-};
-
-struct BlockTable {
-  std::vector<uint32_t> blocks;
-  uint32_t len = 0;
-
-  bool append(BlockAllocator& a, uint32_t* block, uint32_t* offset) {
-    const uint32_t off = len % a.block_size();
-    if (off == 0) {
-      uint32_t b;
-      if (!a.alloc(&b)) return false;
-      blocks.push_back(b);
-    }
-    *block = blocks.back();
-    *offset = off;
-    ++len;
-    return true;
-  }
-  // Back [len, len+n) with blocks; returns the start position or -1 when the pool is exhausted
-  // (blocks taken so far stay with the table, as in the reference).
-  int64_t reserve(uint32_t n, BlockAllocator& a) {
-    const uint32_t start = len, bs = a.block_size();
-    const uint32_t end = len + n;
-    const uint32_t need = (end + bs - 1) / bs;
-    while (blocks.size() < need) {
-      uint32_t b;
-      if (!a.alloc(&b)) return -1;
-      blocks.push_back(b);
-    }
-    len = end;
-    return start;
-  }
-  void truncate(uint32_t new_len, BlockAllocator& a) {
-    const uint32_t keep = (new_len + a.block_size() - 1) / a.block_size();
-    for (size_t i = keep; i < blocks.size(); ++i) a.decref(blocks[i]);
-    blocks.resize(keep);
-    len = new_len;
-  }
-  void release(BlockAllocator& a) {
-    for (uint32_t b : blocks) a.decref(b);
-    blocks.clear();
-    len = 0;
-  }
-  BlockTable fork(BlockAllocator& a) const {
-    for (uint32_t b : blocks) a.incref(b);
-    return *this;
-  }
-  // Copy-on-write of a shared tail block: returns true and (old, fresh) when a copy is needed.
-  bool unshare_tail(BlockAllocator& a, uint32_t* old_b, uint32_t* new_b) {
-    if (blocks.empty() || a.refcount(blocks.back()) <= 1) return false;
-    uint32_t fresh;
-    if (!a.alloc(&fresh)) return false;
-    *old_b = blocks.back();
-    *new_b = fresh;
-    a.decref(blocks.back());
-    blocks.back() = fresh;
-    return true;
-  }
-  void adopt_prefix(const std::vector<uint32_t>& shared, BlockAllocator& a) {
-    for (uint32_t b : shared) {
-      a.incref(b);
-      blocks.push_back(b);
-    }
-    len = static_cast<uint32_t>(shared.size()) * a.block_size();
-  }
-};
-
-class PrefixCache {
- public:
-  using Key = std::pair<uint32_t, std::vector<uint32_t>>;
-  struct Entry {
-    uint32_t block;
-    uint64_t last_use;
-  };
-  size_t size() const { return map_.size(); }
-
-  std::vector<uint32_t> lookup(const uint32_t* prompt, size_t n, uint32_t bs, size_t max_tokens) {
-    std::vector<uint32_t> out;
-    uint32_t parent = PREFIX_ROOT;
-    for (size_t i = 0; (i + 1) * bs <= n; ++i) {
-      if ((out.size() + 1) * bs > max_tokens) break;
-      Key k{parent, std::vector<uint32_t>(prompt + i * bs, prompt + (i + 1) * bs)};
-      auto it = map_.find(k);
-      if (it == map_.end()) break;
-      it->second.last_use = ++tick_;
-      parent = it->second.block;
-      out.push_back(parent);
-    }
-    return out;
-  }
-  void insert_chain(const uint32_t* prompt, size_t n, const std::vector<uint32_t>& blocks,
-                    size_t from, BlockAllocator& a) {
-    const size_t bs = a.block_size();
-    const size_t full = std::min(n / bs, blocks.size());
-    uint32_t parent = from == 0 ? PREFIX_ROOT : blocks[from - 1];
-    for (size_t i = from; i < full; ++i) {
-      Key k{parent, std::vector<uint32_t>(prompt + i * bs, prompt + (i + 1) * bs)};
-      auto it = map_.find(k);
-      if (it != map_.end()) {
-        parent = it->second.block;  // keep the canonical chain
-        continue;
-      }
-      const uint32_t b = blocks[i];
-      if (by_block_.count(b)) {
-        parent = b;
-        continue;
-      }
-      a.incref(b);
-      map_.emplace(k, Entry{b, ++tick_});
-      by_block_.emplace(b, k);
-      parent = b;
-    }
-  }
-  uint32_t evict(uint32_t want, BlockAllocator& a) {
-    uint32_t freed = 0;
-    while (freed < want) {
-      auto victim = map_.end();
-      for (auto it = map_.begin(); it != map_.end(); ++it)
-        if (a.refcount(it->second.block) == 1 &&
-            (victim == map_.end() || it->second.last_use < victim->second.last_use))
-          victim = it;
-      if (victim == map_.end()) break;
-      const uint32_t b = victim->second.block;
-      by_block_.erase(b);
-      map_.erase(victim);
-      a.decref(b);
-      ++freed;
-    }
-    return freed;
-  }
-
- private:
-  std::map<Key, Entry> map_;
-  std::unordered_map<uint32_t, Key> by_block_;
-  uint64_t tick_ = 0;
-};
+using BlockAllocator = kv::KvPool;
+using BlockTable = kv::SeqBlocks;
+using PrefixCache = kv::PrefixIndex;
 
 // ------------------------------------------------------------------------------------ scheduler
 enum Reject : int { OK = 0, EXCEEDS_CAPACITY = -1, INVALID_TOKEN = -2, POLICY_REJECTED = -3, EMPTY = -4 };

@@ -56,6 +56,38 @@ def test_prefix_cache_lru():
     assert pc.evict(1, a) == 1 and a.refcount(blocks[0]) == 1
 
 
+def test_prefix_index_evicts_leaves_first_and_never_matches_through_a_recycled_parent():
+    a = BlockAllocator(8, 2)
+    pc = PrefixCache()
+    t = BlockTable()
+    prompt = [1, 2, 3, 4, 5, 6]
+    t.reserve(len(prompt), a)
+    blocks = t.blocks()
+    pc.insert_chain(prompt, blocks, 0, a)
+    t.release(a)                                   # three idle cached blocks, tail released first
+    assert pc.evict(1, a) == 1 and a.refcount(blocks[2]) == 0      # the leaf went, not the root
+    assert pc.lookup(prompt, 2, 6) == blocks[:2]
+    # a sequence that adopts the chain pins it: nothing is evictable while it runs
+    t2 = BlockTable()
+    t2.adopt_prefix(pc.lookup(prompt, 2, 4), a)
+    assert pc.evict(4, a) == 0
+    t2.release(a)
+    # evict the root only (touch the second block so the root is the least recently used) ...
+    assert pc.evict(2, a) == 2 and len(pc) == 0
+    # ... and publish other content: an old child hash can never be reached through a new parent
+    t3 = BlockTable()
+    other = [9, 9, 3, 4]
+    t3.reserve(len(other), a)
+    pc.insert_chain(other, t3.blocks(), 0, a)
+    assert pc.lookup([1, 2, 3, 4], 2, 4) == []
+    assert pc.lookup(other, 2, 4) == t3.blocks()
+    # a duplicate of a cached prefix under another physical block keeps the canonical copy
+    t4 = BlockTable()
+    t4.reserve(len(other), a)
+    pc.insert_chain(other, t4.blocks(), 0, a)
+    assert len(pc) == 2 and pc.lookup(other, 2, 4) == t3.blocks()
+
+
 def test_sample_from_topk():
     cands = [(7, 3.0), (2, 2.0), (9, 0.5)]
     assert sample_from_topk(cands, SampleParams.greedy(), Rng(0)) == 7
