@@ -74,7 +74,8 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
 
     def compile_one(so):
         s, o = so
-        _run([nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(s), "-o", str(o)],
+        extra = ["-DBB_TIMELINE"] if os.environ.get("BB_TIMELINE") == "1" else []
+        _run([nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(s), "-o", str(o)],
              log=o.with_suffix(".log"))
         if verbose:
             print(f"[build] {s.relative_to(ROOT)}")

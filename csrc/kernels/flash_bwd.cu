@@ -19,13 +19,6 @@
 namespace bb {
 
 struct FaBwdArgs {
-  // row-major operands as plain pointers (leading dimensions in elements): the tiles that stay
-  // resident for a whole CTA are copied global -> registers -> TMEM by the softmax warps
-  const __nv_bfloat16* q;
-  const __nv_bfloat16* k;
-  const __nv_bfloat16* v;
-  const __nv_bfloat16* dout;
-  int ldq, ldk, ldv, lddo;
   const float* lse;    // [B, hq, T] natural log
   const float* delta;  // [B, hq, T]
   __nv_bfloat16* dQ;
@@ -36,8 +29,20 @@ struct FaBwdArgs {
   float scale, scale_log2;
   int causal;
   int* err;
-  long long* tl;  // optional clock64 stamps of CTA (0,0,0): [0,4096) MMA, then one 4096 block per warpgroup
+#ifdef BB_TIMELINE
+  long long* tl;  // clock64 stamps of CTA (0,0,0): dQ kernel at [0, 3*4096), dK/dV kernel after it
+#endif
 };
+
+// Timeline stamps exist only in builds made with -DBB_TIMELINE (a profiling build); the production
+// kernels carry no clock reads.
+#ifdef BB_TIMELINE
+#define BWD_TL_DECL(base) long long* tl = ((blockIdx.x | blockIdx.y | blockIdx.z) == 0 && args.tl) ? args.tl + (base) : nullptr
+#define BWD_STAMP(slot) do { if (tl && (slot) < 4096 * 3) tl[(slot)] = clock64(); } while (0)
+#else
+#define BWD_TL_DECL(base) do { } while (0)
+#define BWD_STAMP(slot) do { } while (0)
+#endif
 
 static constexpr int SUB = 128 * 128;  // bytes of a [128 rows][64 bf16] swizzled sub-tile
 
@@ -103,59 +108,42 @@ __global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ o, int ldo,
 }
 
 // ------------------------------------------------------------------------------------ dQ
-// Work is cut into UNITS of 64 key columns.  Two softmax warpgroups alternate units (warpgroup g
-// owns half g of every 128-row K/V tile and TMEM buffer g), so while one warpgroup turns S/dP of
-// its unit into dS, the tensor core already runs S/dP of the other unit and the dQ MMA of the unit
-// before: tensor-core order is  SdP(0,0) SdP(0,1) dQ(0,0) SdP(1,0) dQ(0,1) SdP(1,1) dQ(1,0) ...
-// MMAs execute in issue order, so S of unit (j+1,g) may be issued straight after dQ of unit (j,g)
-// although it overwrites the TMEM columns that dQ reads its dS operand from.
+// One CTA per (query tile, query head, batch) walks the KV blocks its rows can see.  Every MMA is
+// 128 wide (see the note on MMA cost at the dK/dV kernel).
+// TMEM (512 columns): S of even blocks at 0, dP at 128, dQ at 256, S of odd blocks at 384.
+// Softmax warpgroup g owns key columns [64g, 64g + 64) of every block; the packed bf16 dS it
+// produces replaces the first 32 of its own S columns, so k-step t of the dQ MMA reads its A operand
+// at column 64*(t/4) + 8*(t%4) of that S buffer.
+// Two phases per block keep MMAs queued while the softmax warps work:
+//   phase 1  P = exp2(S*c - lse)  (registers only)   | tensor core: dQ of the block before, dP of this one
+//   phase 2  dS = P (dP*scale - delta)                | tensor core: S two blocks ahead
 // Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9 softmax.
-// TMEM columns: S[g] at g*64, dP[g] at 128 + g*64 (64 fp32 columns each; the packed bf16 dS of a
-// unit overwrites the first 32 columns of its S buffer), dQ at 256, and the CTA's Q and dO tiles as
-// packed bf16 at 384 and 448 (HD/2 columns each).  Q and dO are the A operands of every S and dP
-// MMA of the CTA: held in TMEM they cost no shared-memory bandwidth, which is what bounds an
-// M=128, N=64 MMA whose A operand comes from shared memory (4 KB of A against 2 KB of B per k-step).
 template <int HD>
 struct DqCfg {
   static constexpr int NSUB = HD / 64;
   static constexpr int TILE = NSUB * SUB;
-  static constexpr int OFF_K = 0;
-  static constexpr int OFF_V = OFF_K + 2 * TILE;
+  static constexpr int KST = 3;                     // K stages: S runs two blocks ahead of dQ
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_DO = OFF_Q + TILE;
+  static constexpr int OFF_K = OFF_DO + TILE;
+  static constexpr int OFF_V = OFF_K + KST * TILE;  // 2 stages
   static constexpr int OFF_BAR = OFF_V + 2 * TILE;
   static constexpr int SMEM_MIN = OFF_BAR + 256 + 1024;
   static constexpr int SMEM = SMEM_MIN < 120 * 1024 ? 120 * 1024 : SMEM_MIN;
-  static constexpr uint32_t TM_DQ = 256, TM_Q = 384, TM_DO = 448;
+  static constexpr uint32_t TM_S0 = 0, TM_DP = 128, TM_DQ = 256, TM_S1 = 384;
 };
 
-// Copy one bf16 row of HD elements from global memory into this thread's TMEM lane (packed pairs).
-template <int HD>
-__device__ __forceinline__ void row_to_tmem(const __nv_bfloat16* src, bool valid, uint32_t taddr) {
-#pragma unroll
-  for (int c = 0; c < HD / 64; ++c) {
-    uint32_t w[32];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint4 x = valid ? __ldg(reinterpret_cast<const uint4*>(src + c * 64) + i)
-                            : make_uint4(0u, 0u, 0u, 0u);
-      w[4 * i] = x.x;
-      w[4 * i + 1] = x.y;
-      w[4 * i + 2] = x.z;
-      w[4 * i + 3] = x.w;
-    }
-    tmem_st32(taddr + c * 32, w);
-  }
-  tmem_wait_st();
-}
-
 static constexpr int BWD_THREADS = 320;
-
-#define BWD_STAMP(slot) do { if (tl) tl[(slot)] = clock64(); } while (0)
 
 // Named barrier over the 128 threads of softmax warpgroup g (barrier 0 is __syncthreads).
 __device__ __forceinline__ void wg_sync(int g) {
   if (g == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
   else asm volatile("bar.sync 2, 128;" ::: "memory");
 }
+
+// TMEM column (relative to the operand's base) of k-step t of a packed bf16 A operand whose two
+// 64-wide halves were written by the two warpgroups into the first 32 columns of their own halves
+__device__ __forceinline__ constexpr uint32_t packed_kstep_col(int t) { return (t >> 2) * 64 + (t & 3) * 8; }
 
 template <int HD>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -164,21 +152,25 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                  const FaBwdArgs args) {
   using Cfg = DqCfg<HD>;
   constexpr int NSUB = Cfg::NSUB;
+  constexpr int KST = Cfg::KST;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
+  uint8_t* sQ = smem + Cfg::OFF_Q;
+  uint8_t* sDO = smem + Cfg::OFF_DO;
   uint8_t* sK = smem + Cfg::OFF_K;
   uint8_t* sV = smem + Cfg::OFF_V;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
-  uint64_t* qdo_ready = bars;      // Q and dO rows stored to TMEM (256 arrivals)
-  uint64_t* k_full = bars + 1;     // 2 stages
-  uint64_t* k_empty = bars + 3;    // 2
-  uint64_t* v_full = bars + 5;     // 2
-  uint64_t* v_empty = bars + 7;    // 2
-  uint64_t* sdp_full = bars + 9;   // 2 (one per TMEM buffer / warpgroup)
-  uint64_t* ds_ready = bars + 11;  // 2 (128 arrivals each)
-  uint64_t* dq_done = bars + 13;   // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* q_full = bars;          // Q and dO
+  uint64_t* k_full = bars + 1;      // KST stages
+  uint64_t* k_empty = bars + 4;     // KST
+  uint64_t* v_full = bars + 7;      // 2
+  uint64_t* v_empty = bars + 9;     // 2
+  uint64_t* s_full = bars + 11;     // 2 (one per S buffer)
+  uint64_t* dp_full = bars + 13;    // 1
+  uint64_t* ds_ready = bars + 14;   // 1 (256 arrivals)
+  uint64_t* dq_done = bars + 15;    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = gridDim.x - 1 - blockIdx.x;
@@ -194,15 +186,18 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 
   if (threadIdx.x == 0) {
-    mbar_init(qdo_ready, 256);
-    for (int i = 0; i < 2; ++i) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < KST; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
-      mbar_init(&sdp_full[i], 1);
-      mbar_init(&ds_ready[i], 128);
+      mbar_init(&s_full[i], 1);
     }
+    mbar_init(dp_full, 1);
+    mbar_init(ds_ready, 256);
     mbar_init(dq_done, 1);
     mbar_fence_init();
   }
@@ -214,100 +209,100 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tDQ = tmem_base + Cfg::TM_DQ;
-  const uint32_t tQ = tmem_base + Cfg::TM_Q, tDO = tmem_base + Cfg::TM_DO;
-  long long* tl = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 ? args.tl : nullptr;
+  const uint32_t tDP = tmem_base + Cfg::TM_DP, tDQ = tmem_base + Cfg::TM_DQ;
+  const uint32_t tSb[2] = {tmem_base + Cfg::TM_S0, tmem_base + Cfg::TM_S1};
+  BWD_TL_DECL(0);
 
   if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      bool ok = true;
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_empty[st], ph ^ 1) || !mbar_wait(&v_empty[st], ph ^ 1)) {
+      mbar_expect_tx(q_full, 2 * Cfg::TILE);
+#pragma unroll
+      for (int c = 0; c < NSUB; ++c) {
+        tma_load_2d(sQ + c * SUB, &tmQ, q_full, h * HD + c * 64, b * T + q0);
+        tma_load_2d(sDO + c * SUB, &tmDO, q_full, h * HD + c * 64, b * T + q0);
+      }
+      for (int j = 0; j < n_blocks; ++j) {
+        const int ks = j % KST, vs = j & 1;
+        if (!mbar_wait(&k_empty[ks], ((j / KST) & 1) ^ 1)) {
           set_error(args.err, ERR_WAIT_PRODUCER);
-          ok = false;
           break;
         }
-        mbar_expect_tx(&k_full[st], Cfg::TILE);
-        mbar_expect_tx(&v_full[st], Cfg::TILE);
+        mbar_expect_tx(&k_full[ks], Cfg::TILE);
 #pragma unroll
-        for (int c = 0; c < NSUB; ++c) {
-          tma_load_2d(sK + st * Cfg::TILE + c * SUB, &tmK, &k_full[st], kvh * HD + c * 64,
-                      b * S + j * 128);
-          tma_load_2d(sV + st * Cfg::TILE + c * SUB, &tmV, &v_full[st], kvh * HD + c * 64,
-                      b * S + j * 128);
+        for (int c = 0; c < NSUB; ++c)
+          tma_load_2d(sK + ks * Cfg::TILE + c * SUB, &tmK, &k_full[ks], kvh * HD + c * 64, b * S + j * 128);
+        if (!mbar_wait(&v_empty[vs], ((j >> 1) & 1) ^ 1)) {
+          set_error(args.err, ERR_WAIT_PRODUCER);
+          break;
         }
+        mbar_expect_tx(&v_full[vs], Cfg::TILE);
+#pragma unroll
+        for (int c = 0; c < NSUB; ++c)
+          tma_load_2d(sV + vs * Cfg::TILE + c * SUB, &tmV, &v_full[vs], kvh * HD + c * 64, b * S + j * 128);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc(1, 1, 1, 0, 0, 128, 64);
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_blocks > 0) {
+      constexpr uint32_t idesc_s = umma_idesc(1, 1, 1, 0, 0, 128, 128);
       constexpr uint32_t idesc_dq = umma_idesc(1, 1, 1, 0, 1, 128, HD);
-      bool ok = mbar_wait(qdo_ready, 0);
+      bool ok = mbar_wait(q_full, 0);
       if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
-      tc_fence_after();
-      // S and dP of half g of block j into TMEM buffer g (A = Q / dO rows resident in TMEM)
-      auto issue_sdp = [&](int j, int g) {
-        const int st = j & 1;
-        const uint32_t lk = desc_lo_kmajor(smem_u32(sK + st * Cfg::TILE) + g * 8192);
-        const uint32_t lv = desc_lo_kmajor(smem_u32(sV + st * Cfg::TILE) + g * 8192);
-        const uint32_t tS = tmem_base + g * 64, tDP = tmem_base + 128 + g * 64;
+      const uint32_t lq = desc_lo_kmajor(smem_u32(sQ)), ldo = desc_lo_kmajor(smem_u32(sDO));
+      // S of block j into S buffer j&1 (waits for the K tile)
+      auto issue_s = [&](int j) -> bool {
+        const int ks = j % KST;
+        if (!mbar_wait(&k_full[ks], (j / KST) & 1)) return false;
+        tc_fence_after();
+        const uint32_t lk = desc_lo_kmajor(smem_u32(sK + ks * Cfg::TILE));
 #pragma unroll
         for (int t = 0; t < HD / 16; ++t)
-          umma_f16_ts(tS, tQ + t * 8, desc_of(lk + kstep_kmajor(t)), idesc_s, t != 0);
-#pragma unroll
-        for (int t = 0; t < HD / 16; ++t)
-          umma_f16_ts(tDP, tDO + t * 8, desc_of(lv + kstep_kmajor(t)), idesc_s, t != 0);
-        umma_commit(&sdp_full[g]);
-        if (g == 1) umma_commit(&v_empty[st]);
+          umma_f16_ss(tSb[j & 1], desc_of(lq + kstep_kmajor(t)), desc_of(lk + kstep_kmajor(t)), idesc_s, t != 0);
+        umma_commit(&s_full[j & 1]);
+        return true;
       };
-      if (ok && n_blocks > 0) {
-        if (!mbar_wait(&k_full[0], 0) || !mbar_wait(&v_full[0], 0)) {
-          set_error(args.err, ERR_WAIT_MMA_FULL);
-          ok = false;
-        } else {
-          tc_fence_after();
-          issue_sdp(0, 0);
-          issue_sdp(0, 1);
-        }
-      }
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t lkm = desc_lo_mnmajor(smem_u32(sK + st * Cfg::TILE));
-        for (int g = 0; g < 2 && ok; ++g) {
-          if (!mbar_wait(&ds_ready[g], j & 1)) {
-            set_error(args.err, ERR_WAIT_MMA_TMEM);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          if (2 * j + g < 1024) BWD_STAMP(4 * j + 2 * g);
-          const uint32_t tS = tmem_base + g * 64;
+      // dP of block j (waits for the V tile, releases it)
+      auto issue_dp = [&](int j) -> bool {
+        const int vs = j & 1;
+        if (!mbar_wait(&v_full[vs], (j >> 1) & 1)) return false;
+        tc_fence_after();
+        const uint32_t lv = desc_lo_kmajor(smem_u32(sV + vs * Cfg::TILE));
 #pragma unroll
-          for (int t = 0; t < 4; ++t)
-            umma_f16_ts(tDQ, tS + t * 8, desc_of(lkm + g * 512 + kstep_mnmajor(t)), idesc_dq,
-                        (j | g | t) != 0);
-          if (g == 1) umma_commit(&k_empty[st]);
-          if (j + 1 < n_blocks) {
-            if (g == 0) {
-              const uint32_t ph = ((j + 1) >> 1) & 1;
-              if (!mbar_wait(&k_full[st ^ 1], ph) || !mbar_wait(&v_full[st ^ 1], ph)) {
-                set_error(args.err, ERR_WAIT_MMA_FULL);
-                ok = false;
-                break;
-              }
-              tc_fence_after();
-            }
-            issue_sdp(j + 1, g);
-          }
-          if (2 * j + g < 1024) BWD_STAMP(4 * j + 2 * g + 1);
+        for (int t = 0; t < HD / 16; ++t)
+          umma_f16_ss(tDP, desc_of(ldo + kstep_kmajor(t)), desc_of(lv + kstep_kmajor(t)), idesc_s, t != 0);
+        umma_commit(dp_full);
+        umma_commit(&v_empty[vs]);
+        return true;
+      };
+      if (ok) ok = issue_s(0) && issue_dp(0);
+      if (ok && n_blocks > 1) ok = issue_s(1);
+      if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        if (!mbar_wait(ds_ready, j & 1)) {
+          set_error(args.err, ERR_WAIT_MMA_TMEM);
+          ok = false;
+          break;
         }
+        tc_fence_after();
+        BWD_STAMP(4 * j);
+        const int ks = j % KST;
+        const uint32_t lkm = desc_lo_mnmajor(smem_u32(sK + ks * Cfg::TILE));
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+          umma_f16_ts(tDQ, tSb[j & 1] + packed_kstep_col(t), desc_of(lkm + kstep_mnmajor(t)), idesc_dq,
+                      (j | t) != 0);
+        umma_commit(&k_empty[ks]);
+        if (j + 1 < n_blocks) ok = issue_dp(j + 1);
+        if (ok && j + 2 < n_blocks) ok = issue_s(j + 2);
+        if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
+        BWD_STAMP(4 * j + 1);
       }
       if (ok) umma_commit(dq_done);
     }
   } else {
-    const int g = (warp - 2) >> 2;  // warpgroup = half of every K/V tile = TMEM buffer
+    // ------------------------------------------------------------ softmax warpgroups
+    const int g = (warp - 2) >> 2;  // owns key columns [64g, 64g + 64) of every block
     const int sw = warp & 3;
     const int row = sw * 32 + lane;
     const int q_idx = q0 + row;
@@ -317,33 +312,30 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const size_t stat = ((size_t)b * args.hq + h) * T + (row_ok ? q_idx : 0);
     const float lse2 = row_ok ? args.lse[stat] * 1.4426950408889634f : INFINITY;
     const float dlt = row_ok ? -args.delta[stat] * args.scale : 0.f;  // -delta * scale
-    const uint32_t tS = tmem_base + g * 64 + lane_sel, tDP = tmem_base + 128 + g * 64 + lane_sel;
-    // warpgroup 0 parks the Q tile in TMEM, warpgroup 1 the dO tile (one row per thread)
-    {
-      const size_t grow = (size_t)(b * T + (row_ok ? q_idx : 0));
-      const __nv_bfloat16* src = (g == 0 ? args.q + grow * args.ldq : args.dout + grow * args.lddo) + h * HD;
-      row_to_tmem<HD>(src, row_ok, (g == 0 ? tQ : tDO) + lane_sel);
-      tc_fence_before();
-      mbar_arrive(qdo_ready);
-    }
+    const uint32_t tD = tDP + g * 64 + lane_sel;
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
-      ok = mbar_wait(&sdp_full[g], j & 1);
+      const uint32_t tS = tSb[j & 1] + g * 64 + lane_sel;
+      // ---- phase 1: P (kept packed in registers)
+      const bool stamper = (warp & 3) == 2 && lane == 0;
+      if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * j);
+      ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      if ((warp & 3) == 2 && lane == 0 && j < 1024) BWD_STAMP(4096 * (1 + g) + 2 * j);
-      const int kv0 = j * 128 + g * 64;
-      const bool need_mask = (kv0 + 63 > kv_limit_row);
+      if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * j + 1);
+      const int kvb = j * 128 + g * 64;
+      const bool need_mask = (kvb + 63 > kv_limit_row);
       uint32_t pk[32];
+      uint32_t rs2[2][32];
+      __syncwarp();
+      tmem_ld32(tS, rs2[0]);        // both halves in flight: one TMEM round trip instead of two
+      tmem_ld32(tS + 32, rs2[1]);
+      tmem_wait_ld();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rp[32];
-        __syncwarp();
-        tmem_ld32(tS + c * 32, rs);
-        tmem_ld32(tDP + c * 32, rp);
-        tmem_wait_ld();
-        const int lim = kv_limit_row - (kv0 + c * 32);
+        const uint32_t (&rs)[32] = rs2[c];
+        const int lim = kv_limit_row - (kvb + c * 32);
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float p0 = exp2f(__uint_as_float(rs[i]) * args.scale_log2 - lse2);
@@ -352,18 +344,38 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (i > lim) p0 = 0.f;
             if (i + 1 > lim) p1 = 0.f;
           }
+          pk[c * 16 + (i >> 1)] = pack_bf16x2_alu(p0, p1);
+        }
+      }
+      // ---- phase 2: dS = P * (dP * scale - delta * scale), packed over this warpgroup's S columns
+      if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * j + 2);
+      ok = mbar_wait(dp_full, j & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * j + 3);
+      uint32_t rp2[2][32];
+      __syncwarp();
+      tmem_ld32(tD, rp2[0]);
+      tmem_ld32(tD + 32, rp2[1]);
+      tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint32_t (&rp)[32] = rp2[c];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const uint32_t w = pk[c * 16 + (i >> 1)];
+          const float p0 = __uint_as_float(w << 16), p1 = __uint_as_float(w & 0xFFFF0000u);
           pk[c * 16 + (i >> 1)] = pack_bf16x2_alu(p0 * fmaf(__uint_as_float(rp[i]), args.scale, dlt),
                                               p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, dlt));
         }
       }
-      // all 64 S columns of this unit are in registers: the packed dS may overwrite them
       tmem_st32(tS, pk);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&ds_ready[g]);
-      if ((warp & 3) == 2 && lane == 0 && j < 1024) BWD_STAMP(4096 * (1 + g) + 2 * j + 1);
+      mbar_arrive(ds_ready);
     }
-    if (ok) {
+    if (ok && n_blocks > 0) {
       ok = mbar_wait(dq_done, 0);
       ok = __all_sync(0xffffffffu, ok);
     }
@@ -377,8 +389,13 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int c = g * (HD / 64); c < (g + 1) * (HD / 64); ++c) {
         uint32_t r[32];
         __syncwarp();
-        tmem_ld32(tDQ + lane_sel + c * 32, r);
-        tmem_wait_ld();
+        if (n_blocks > 0) {
+          tmem_ld32(tDQ + lane_sel + c * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
         if (row_ok) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -402,10 +419,19 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------ dK, dV
-// Same unit pipeline with the roles of rows and columns swapped: a unit is 64 QUERY rows of the
-// current (head, query tile) iteration; warpgroup g owns half g of every 128-row Q/dO tile.
-// TMEM columns: S^T[g] at g*64, dP^T[g] at 128 + g*64, dV at 256, dK at 384.  P^T (packed bf16)
-// overwrites the first 32 columns of its S^T buffer, dS^T those of its dP^T buffer.
+// One CTA per (KV tile, KV head, batch) loops over the query heads of the GQA group and the query
+// tiles that can see the KV tile.  Every MMA is 128 wide: on this part a tcgen05.mma with M = 128,
+// K = 16 takes about 68 clocks for any N <= 128 (129 at N = 256), so narrower tiles waste the
+// tensor pipe in proportion.
+// TMEM (512 columns, all used): S^T at 0 and dP^T at 128 (128 fp32 columns each: one column per
+// query of the tile), dV at 256, dK at 384.  Softmax warpgroup g owns query columns [64g, 64g+64):
+// it replaces the first 32 of ITS OWN columns by the packed bf16 P^T (then dS^T) values, so the two
+// warpgroups never touch each other's columns and the A operand of k-step t of the dV / dK MMAs
+// sits at column 64*(t/4) + 8*(t%4).
+// The work of an iteration is cut in two phases so that the tensor core always has MMAs queued:
+//   phase 1  P^T = exp2(S^T*c - lse)           -> tensor core: dV += P^T dO, then S^T of the next tile
+//   phase 2  dS^T = P^T (dP^T*scale - delta)   -> tensor core: dK += dS^T Q, then dP^T of the next tile
+// MMAs execute in issue order, so "S^T of the next tile" may overwrite the columns dV just read.
 template <int HD>
 struct DkvCfg {
   static constexpr int NSUB = HD / 64;
@@ -418,6 +444,7 @@ struct DkvCfg {
   static constexpr int OFF_BAR = OFF_STAT + 1024;
   static constexpr int SMEM_MIN = OFF_BAR + 256 + 1024;
   static constexpr int SMEM = SMEM_MIN < 120 * 1024 ? 120 * 1024 : SMEM_MIN;
+  static constexpr uint32_t TM_ST = 0, TM_DPT = 128, TM_DV = 256, TM_DK = 384;
 };
 
 template <int HD>
@@ -439,8 +466,10 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint64_t* kv_full = bars;         // K and V tiles (once)
   uint64_t* qdo_full = bars + 1;    // 2 stages: Q and dO of an iteration
   uint64_t* qdo_empty = bars + 3;   // 2
-  uint64_t* st_full = bars + 5;     // 2: S^T and dP^T of a unit ready in TMEM buffer g
-  uint64_t* pds_ready = bars + 7;   // 2: P^T, dS^T written (128 arrivals each)
+  uint64_t* st_full = bars + 5;     // S^T of the iteration is in TMEM
+  uint64_t* dpt_full = bars + 6;    // dP^T of the iteration is in TMEM
+  uint64_t* p_ready = bars + 7;     // P^T written (256 arrivals)
+  uint64_t* ds_ready = bars + 8;    // dS^T written (256 arrivals)
   uint64_t* dkv_done = bars + 9;    // all dV/dK MMAs finished
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
 
@@ -466,9 +495,11 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     for (int i = 0; i < 2; ++i) {
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
-      mbar_init(&st_full[i], 1);
-      mbar_init(&pds_ready[i], 128);
     }
+    mbar_init(st_full, 1);
+    mbar_init(dpt_full, 1);
+    mbar_init(p_ready, 256);
+    mbar_init(ds_ready, 256);
     mbar_init(dkv_done, 1);
     mbar_fence_init();
   }
@@ -480,10 +511,12 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tDV = tmem_base + 256, tDK = tmem_base + 384;
-  long long* tl = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && args.tl ? args.tl + 3 * 4096 : nullptr;
+  const uint32_t tST = tmem_base + Cfg::TM_ST, tDPT = tmem_base + Cfg::TM_DPT;
+  const uint32_t tDV = tmem_base + Cfg::TM_DV, tDK = tmem_base + Cfg::TM_DK;
+  BWD_TL_DECL(3 * 4096);
 
   if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
     if (lane == 0 && n_iter > 0) {
       mbar_expect_tx(kv_full, 2 * Cfg::TILE);
 #pragma unroll
@@ -510,25 +543,26 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
     }
   } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_iter > 0) {
-      constexpr uint32_t idesc_st = umma_idesc(1, 1, 1, 0, 0, 128, 64);
+      constexpr uint32_t idesc_st = umma_idesc(1, 1, 1, 0, 0, 128, 128);
       constexpr uint32_t idesc_acc = umma_idesc(1, 1, 1, 0, 1, 128, HD);
       bool ok = mbar_wait(kv_full, 0);
       if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
-      const uint32_t ak = smem_u32(sK), av = smem_u32(sV);
-      const uint32_t lkk = desc_lo_kmajor(ak), lvv = desc_lo_kmajor(av);
-      auto issue_st = [&](int it, int g) {
-        const int st = it & 1;
-        const uint32_t lq = desc_lo_kmajor(smem_u32(sQ + st * Cfg::TILE) + g * 8192);
-        const uint32_t ldo = desc_lo_kmajor(smem_u32(sDO + st * Cfg::TILE) + g * 8192);
-        const uint32_t tST = tmem_base + g * 64, tDPT = tmem_base + 128 + g * 64;
+      const uint32_t lkk = desc_lo_kmajor(smem_u32(sK)), lvv = desc_lo_kmajor(smem_u32(sV));
+      auto issue_st = [&](int st) {      // S^T = K Q^T for the 128 queries of stage st
+        const uint32_t lq = desc_lo_kmajor(smem_u32(sQ + st * Cfg::TILE));
 #pragma unroll
         for (int t = 0; t < HD / 16; ++t)
           umma_f16_ss(tST, desc_of(lkk + kstep_kmajor(t)), desc_of(lq + kstep_kmajor(t)), idesc_st, t != 0);
+        umma_commit(st_full);
+      };
+      auto issue_dpt = [&](int st) {     // dP^T = V dO^T
+        const uint32_t ldo = desc_lo_kmajor(smem_u32(sDO + st * Cfg::TILE));
 #pragma unroll
         for (int t = 0; t < HD / 16; ++t)
           umma_f16_ss(tDPT, desc_of(lvv + kstep_kmajor(t)), desc_of(ldo + kstep_kmajor(t)), idesc_st, t != 0);
-        umma_commit(&st_full[g]);
+        umma_commit(dpt_full);
       };
       if (ok) {
         if (!mbar_wait(&qdo_full[0], 0)) {
@@ -536,98 +570,115 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           ok = false;
         } else {
           tc_fence_after();
-          issue_st(0, 0);
-          issue_st(0, 1);
+          issue_st(0);
+          issue_dpt(0);
         }
       }
       for (int it = 0; it < n_iter && ok; ++it) {
         const int st = it & 1;
+        const uint32_t ph = it & 1;
         const uint32_t lqm = desc_lo_mnmajor(smem_u32(sQ + st * Cfg::TILE));
         const uint32_t ldom = desc_lo_mnmajor(smem_u32(sDO + st * Cfg::TILE));
-        for (int g = 0; g < 2 && ok; ++g) {
-          if (!mbar_wait(&pds_ready[g], it & 1)) {
-            set_error(args.err, ERR_WAIT_MMA_TMEM);
+        // ---- after phase 1: dV += P^T dO, then S^T of the next tile
+        if (!mbar_wait(p_ready, ph)) {
+          set_error(args.err, ERR_WAIT_MMA_TMEM);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        BWD_STAMP(4 * it);
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+          umma_f16_ts(tDV, tST + packed_kstep_col(t), desc_of(ldom + kstep_mnmajor(t)), idesc_acc,
+                      (it | t) != 0);
+        if (it + 1 < n_iter) {
+          if (!mbar_wait(&qdo_full[st ^ 1], ((it + 1) >> 1) & 1)) {
+            set_error(args.err, ERR_WAIT_MMA_FULL);
             ok = false;
             break;
           }
           tc_fence_after();
-          if (2 * it + g < 1024) BWD_STAMP(4 * it + 2 * g);
-          const uint32_t tST = tmem_base + g * 64, tDPT = tmem_base + 128 + g * 64;
-#pragma unroll
-          for (int t = 0; t < 4; ++t)
-            umma_f16_ts(tDV, tST + t * 8, desc_of(ldom + g * 512 + kstep_mnmajor(t)), idesc_acc,
-                        (it | g | t) != 0);
-#pragma unroll
-          for (int t = 0; t < 4; ++t)
-            umma_f16_ts(tDK, tDPT + t * 8, desc_of(lqm + g * 512 + kstep_mnmajor(t)), idesc_acc,
-                        (it | g | t) != 0);
-          if (g == 1) umma_commit(&qdo_empty[st]);
-          if (it + 1 < n_iter) {
-            if (g == 0) {
-              if (!mbar_wait(&qdo_full[st ^ 1], ((it + 1) >> 1) & 1)) {
-                set_error(args.err, ERR_WAIT_MMA_FULL);
-                ok = false;
-                break;
-              }
-              tc_fence_after();
-            }
-            issue_st(it + 1, g);
-          }
-          if (2 * it + g < 1024) BWD_STAMP(4 * it + 2 * g + 1);
+          issue_st(st ^ 1);
         }
+        BWD_STAMP(4 * it + 1);
+        // ---- after phase 2: dK += dS^T Q, then dP^T of the next tile
+        if (!mbar_wait(ds_ready, ph)) {
+          set_error(args.err, ERR_WAIT_MMA_TMEM);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        BWD_STAMP(4 * it + 2);
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+          umma_f16_ts(tDK, tDPT + packed_kstep_col(t), desc_of(lqm + kstep_mnmajor(t)), idesc_acc,
+                      (it | t) != 0);
+        umma_commit(&qdo_empty[st]);   // both tiles of this stage have been read
+        if (it + 1 < n_iter) issue_dpt(st ^ 1);
+        BWD_STAMP(4 * it + 3);
       }
       if (ok) umma_commit(dkv_done);
     }
   } else {
-    const int g = (warp - 2) >> 2;
+    // ------------------------------------------------------------ softmax warpgroups
+    const int g = (warp - 2) >> 2;    // owns query columns [64g, 64g + 64) of every tile
     const int sw = warp & 3;
     const int row = sw * 32 + lane;   // kv row inside the tile
     const int kv_idx = kv0 + row;
     const uint32_t lane_sel = (uint32_t)(sw * 32) << 16;
     const int wt = threadIdx.x - 64 - g * 128;  // 0..127 inside the warpgroup
-    float* ls = s_stat + g * 128;               // lse2 of the unit's 64 query rows
-    float* dl = ls + 64;                        // -delta * scale of the same rows
-    const uint32_t tST = tmem_base + g * 64 + lane_sel, tDPT = tmem_base + 128 + g * 64 + lane_sel;
+    float* ls = s_stat + g * 128;               // lse2 of this warpgroup's 64 query columns
+    float* dl = ls + 64;                        // -delta * scale of the same columns
+    const uint32_t tS = tST + g * 64 + lane_sel, tD = tDPT + g * 64 + lane_sel;
+    // per-query statistic this thread stages for iteration i: threads 0..63 of the warpgroup carry
+    // lse (in log2 units), threads 64..127 carry -delta * scale (one FMA per element in phase 2)
+    auto load_stat = [&](int i) -> float {
+      const int hh = kvh * group + i / per_head;
+      const int qi = (qt_first + i % per_head) * 128 + g * 64 + (wt & 63);
+      const bool qok = qi < T;
+      const size_t stat = ((size_t)b * args.hq + hh) * T + (qok ? qi : 0);
+      if (wt < 64) return qok ? args.lse[stat] * 1.4426950408889634f : INFINITY;
+      return qok ? -args.delta[stat] * args.scale : 0.f;
+    };
+    float stat_val = n_iter > 0 ? load_stat(0) : 0.f;
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
-      const int h = kvh * group + it / per_head;
       const int qt = qt_first + it % per_head;
       const int q0 = qt * 128 + g * 64;
+      const uint32_t ph = it & 1;
       {
-        // stage the unit's per-query statistics; named barrier 1+g = this warpgroup's 128 threads
-        const int qi = q0 + (wt & 63);
-        const bool qok = qi < T;
-        const size_t stat = ((size_t)b * args.hq + h) * T + (qok ? qi : 0);
-        float val;
-        if (wt < 64) val = qok ? args.lse[stat] * 1.4426950408889634f : INFINITY;
-        else val = qok ? -args.delta[stat] * args.scale : 0.f;  // -delta * scale: one FMA per element below
-        wg_sync(g);    // previous unit's reads done
-        ls[wt] = val;  // wt >= 64 lands in dl[]
+        // stage the per-query statistics; named barrier 1+g = this warpgroup's 128 threads
+        wg_sync(g);         // previous iteration's reads done
+        ls[wt] = stat_val;  // wt >= 64 lands in dl[]
         wg_sync(g);
+        // the next iteration's value is fetched now and lands while this iteration computes
+        if (it + 1 < n_iter) stat_val = load_stat(it + 1);
       }
-      ok = mbar_wait(&st_full[g], it & 1);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      if ((warp & 3) == 2 && lane == 0 && it < 1024) BWD_STAMP(4096 * (1 + g) + 2 * it);
       // column (query) c is visible from this kv row iff kv_idx <= q + off  <=>  q >= kv_idx - off
       const int q_min = args.causal ? (kv_idx - off) : -0x40000000;
       const bool need_mask = args.causal && (q0 < q_min);
-      uint32_t pk[32], dk_[32];
+      // ---- phase 1: P^T
+      const bool stamper = (warp & 3) == 2 && lane == 0;
+      if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * it);
+      ok = mbar_wait(st_full, ph);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * it + 1);
+      uint32_t pk[32];
+      uint32_t rs2[2][32];
+      __syncwarp();
+      tmem_ld32(tS, rs2[0]);        // both halves in flight: one TMEM round trip instead of two
+      tmem_ld32(tS + 32, rs2[1]);
+      tmem_wait_ld();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rp[32];
-        __syncwarp();
-        tmem_ld32(tST + c * 32, rs);
-        tmem_ld32(tDPT + c * 32, rp);
-        tmem_wait_ld();
+        const uint32_t (&rs)[32] = rs2[c];
         const int first_ok = q_min - (q0 + c * 32);  // columns i >= first_ok are visible
-        // the per-query statistics are the same for every thread: fetch them four at a time
         const float4* ls4 = reinterpret_cast<const float4*>(ls + c * 32);
-        const float4* dl4 = reinterpret_cast<const float4*>(dl + c * 32);
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          const float4 l = ls4[i >> 2], d = dl4[i >> 2];
+          const float4 l = ls4[i >> 2];
           float p0 = exp2f(__uint_as_float(rs[i]) * args.scale_log2 - l.x);
           float p1 = exp2f(__uint_as_float(rs[i + 1]) * args.scale_log2 - l.y);
           float p2 = exp2f(__uint_as_float(rs[i + 2]) * args.scale_log2 - l.z);
@@ -640,19 +691,45 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           }
           pk[c * 16 + (i >> 1)] = pack_bf16x2_alu(p0, p1);
           pk[c * 16 + (i >> 1) + 1] = pack_bf16x2_alu(p2, p3);
-          // dS^T = P^T * (dP^T * scale - delta * scale)
-          dk_[c * 16 + (i >> 1)] = pack_bf16x2_alu(p0 * fmaf(__uint_as_float(rp[i]), args.scale, d.x),
-                                               p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, d.y));
-          dk_[c * 16 + (i >> 1) + 1] = pack_bf16x2_alu(p2 * fmaf(__uint_as_float(rp[i + 2]), args.scale, d.z),
-                                                   p3 * fmaf(__uint_as_float(rp[i + 3]), args.scale, d.w));
         }
       }
-      tmem_st32(tST, pk);
-      tmem_st32(tDPT, dk_);
+      // all 64 S^T columns of this warpgroup are in registers: the packed P^T may overwrite them
+      tmem_st32(tS, pk);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&pds_ready[g]);
-      if ((warp & 3) == 2 && lane == 0 && it < 1024) BWD_STAMP(4096 * (1 + g) + 2 * it + 1);
+      mbar_arrive(p_ready);
+      if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * it + 2);
+      // ---- phase 2: dS^T = P^T * (dP^T * scale - delta * scale), P^T as it was rounded for the MMA
+      ok = mbar_wait(dpt_full, ph);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * it + 3);
+      uint32_t rp2[2][32];
+      __syncwarp();
+      tmem_ld32(tD, rp2[0]);
+      tmem_ld32(tD + 32, rp2[1]);
+      tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint32_t (&rp)[32] = rp2[c];
+        const float4* dl4 = reinterpret_cast<const float4*>(dl + c * 32);
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 d = dl4[i >> 2];
+          const uint32_t w0 = pk[c * 16 + (i >> 1)], w1 = pk[c * 16 + (i >> 1) + 1];
+          const float p0 = __uint_as_float(w0 << 16), p1 = __uint_as_float(w0 & 0xFFFF0000u);
+          const float p2 = __uint_as_float(w1 << 16), p3 = __uint_as_float(w1 & 0xFFFF0000u);
+          pk[c * 16 + (i >> 1)] = pack_bf16x2_alu(p0 * fmaf(__uint_as_float(rp[i]), args.scale, d.x),
+                                              p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, d.y));
+          pk[c * 16 + (i >> 1) + 1] = pack_bf16x2_alu(p2 * fmaf(__uint_as_float(rp[i + 2]), args.scale, d.z),
+                                                  p3 * fmaf(__uint_as_float(rp[i + 3]), args.scale, d.w));
+        }
+      }
+      tmem_st32(tD, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(ds_ready);
     }
     if (ok && n_iter > 0) {
       ok = mbar_wait(dkv_done, 0);
@@ -703,22 +780,9 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
 template <int HD>
 static int launch_fa_bwd(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
-                         const void* dout, int lddo, const FaBwdArgs& a_in, cudaStream_t stream) {
-  FaBwdArgs a = a_in;
-  a.q = static_cast<const __nv_bfloat16*>(q);
-  a.k = static_cast<const __nv_bfloat16*>(k);
-  a.v = static_cast<const __nv_bfloat16*>(v);
-  a.dout = static_cast<const __nv_bfloat16*>(dout);
-  a.ldq = ldq;
-  a.ldk = ldk;
-  a.ldv = ldv;
-  a.lddo = lddo;
+                         const void* dout, int lddo, const FaBwdArgs& a, cudaStream_t stream) {
   CUtensorMap tmQ, tmK, tmV, tmDO;
   const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
-       reinterpret_cast<uintptr_t>(dout)) & 15)
-    return BB_EARG;
-  if ((ldq | ldk | ldv | lddo) & 7) return BB_EARG;
   int rc = make_tmap_2d(&tmQ, bf, 2, q, (uint64_t)a.hq * HD, (uint64_t)a.B * a.T, (uint64_t)ldq * 2,
                         64, 128);
   if (rc) return rc;
@@ -749,15 +813,14 @@ static int launch_fa_bwd(const void* q, int ldq, const void* k, int ldk, const v
 
 }  // namespace bb
 
+#ifdef BB_TIMELINE
 static long long* g_bwd_timeline = nullptr;
-
-// Profiling aid: when set to a device buffer of 6*4096 int64, CTA (0,0,0) of the dQ kernel (first
-// 3*4096 slots) and of the dK/dV kernel (next 3*4096) record clock64 stamps: per unit the MMA
-// issuer's [after the dS wait, after issuing], and per warpgroup [S/dP ready, dS handed over].
+// Profiling builds only: device buffer of 6*4096 int64 that CTA (0,0,0) of each kernel stamps.
 BB_API int bb_flash_bwd_timeline(long long* buf) {
   g_bwd_timeline = buf;
   return 0;
 }
+#endif
 
 // Backward of bb_flash_fwd.  `out`/`dout`: [B*T, ld]; lse from the forward; delta: scratch
 // [B, hq, T] fp32 written here; dq/dk/dv: [B*T or B*S, ld] bf16, fully overwritten.
@@ -793,7 +856,9 @@ BB_API int bb_flash_bwd(const void* q, int ldq, const void* k, int ldk, const vo
   a.scale_log2 = scale * 1.4426950408889634f;
   a.causal = causal;
   a.err = device_error_word();
+#ifdef BB_TIMELINE
   a.tl = g_bwd_timeline;
+#endif
   if (hd == 128) return launch_fa_bwd<128>(q, ldq, k, ldk, v, ldv, dout, lddo, a, s);
   if (hd == 64) return launch_fa_bwd<64>(q, ldq, k, ldk, v, ldv, dout, lddo, a, s);
   return BB_EARG;

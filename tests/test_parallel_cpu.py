@@ -4,6 +4,7 @@ schedules — N-rank result == 1-rank result."""
 import threading
 
 import pytest
+import numpy as np
 import torch
 
 from brain_b200.parallel.collective import CollectiveError, HostCollective, NetworkCollective
@@ -61,6 +62,26 @@ def test_planners():
     assert t.degree == 4 and t.fits
     assert not plan_tp(hw, ModelShape(1024, 1024, 4096, 4, 1e6, 10.0)).fits
     assert tp_step_secs(Hardware(), ModelShape(4096, 4096, 16384, 32, 0, 0), 2) > 0
+    # measured, uneven per-layer costs: exact min-max against brute force, slack with the early stages
+    import itertools
+    from brain_b200.parallel.plan import plan_stages
+    rng = np.random.default_rng(0)
+    for _ in range(20):
+        L, k = int(rng.integers(3, 10)), int(rng.integers(2, 4))
+        cost = rng.uniform(0.5, 3.0, L)
+        emb, head = float(rng.uniform(0, 2)), float(rng.uniform(0, 4))
+        got = plan_stages(cost, list(range(k)), emb, head)
+        def worst(cuts):
+            b = [0, *cuts, L]
+            return max(cost[b[i]:b[i + 1]].sum() + (emb if i == 0 else 0) + (head if i == k - 1 else 0) for i in range(k))
+        brute = min(worst(c_) for c_ in itertools.combinations_with_replacement(range(L + 1), k - 1))
+        assert abs(worst([s.end for s in got[:-1]]) - brute) < 1e-9
+    even = plan_stages([1.0] * 10, [0, 1, 2, 3])
+    assert [s.end - s.start for s in even] == [1, 3, 3, 3]      # bottleneck 3; the spare room sits in stage 0
+    big = ModelShape(8192, 8192, 28672, 80, 200.0, 10.0)
+    hw2 = Hardware(n_gpus=8, mem_bytes=1e12)
+    assert plan_tp(hw2, big).degree == 1 and plan_tp(hw2, big, fastest=True).degree == 8
+    assert tp_step_secs(hw2, big, 8) < tp_step_secs(hw2, big, 1)
     assert schedule("1f1b", 0, 4, 6) == [1, 2, 3, 4, -1, 5, -2, 6, -3, -4, -5, -6]
     assert schedule("1f1b", 3, 4, 6) == [1, -1, 2, -2, 3, -3, 4, -4, 5, -5, 6, -6]
     assert schedule("gpipe", 1, 2, 3) == [1, 2, 3, -3, -2, -1]
