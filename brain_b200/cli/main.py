@@ -53,7 +53,7 @@ infrastructure
   serve [--stdio | --openai [8788] --anthropic [8787] --openrouter [8789]] [--api-keys-out F
         --ready-file P --max-new N --temp X --top-k K --seed S -v N]
   import <FILE|DIR> [--out F | --id VENDOR/REPO [--models-dir D]] | import --list
-  quantize <SRC> [--out F --tier Q8_0 --keep SUBSTR... --plan]
+  quantize <SRC> [--out F --tier Q8_0|Q4_0 --format gguf|safetensors --keep SUBSTR... --plan]
   help | --help | --version
 
 global flags
@@ -350,13 +350,33 @@ def _quantize(rest, device):
     tier = (a.take_str("--tier") or "Q8_0").upper()
     keep = a.take_all("--keep")
     plan_only = a.take_flag("--plan")
+    fmt = (a.take_str("--format") or "").lower()
     a.finish()
     if src is None:
-        print("usage: brain quantize <SRC.safetensors> [--out F --tier Q8_0 --keep SUBSTR... --plan]", file=sys.stderr)
+        print("usage: brain quantize <SRC.safetensors|.gguf|.pt> [--out F --tier Q8_0|Q4_0 --format gguf|safetensors "
+              "--keep SUBSTR... --plan]", file=sys.stderr)
         return 2
+    if not fmt:
+        fmt = "gguf" if (out or "").lower().endswith(".gguf") or not src.lower().endswith(".safetensors") \
+            or tier == "Q4_0" else "safetensors"
+    if fmt == "gguf":
+        # any container in, GGUF out: block quantisers Q8_0 / Q4_0, every kept tensor with its reason
+        from ..checkpoint.convert import quantize_to_gguf
+        if tier not in ("Q8_0", "Q4_0"):
+            print(f"--tier {tier}: the GGUF writer encodes Q8_0 and Q4_0 (the k-quant tiers are decode-only)", file=sys.stderr)
+            return 2
+        out = out or os.path.splitext(src)[0] + f".{tier.lower()}.gguf"
+        info = quantize_to_gguf(src, out, tier, keep=keep, plan_only=plan_only)
+        if plan_only:
+            for n, shape, d in info["plan"]:
+                print(f"{d:<48}  {n} {list(shape)}")
+            return 0
+        print(f"ok: wrote {out} ({info['quantized']} {tier} tensors, {info['bytes_in'] / 2**20:.1f} MiB fp32 -> "
+              f"{info['bytes_out'] / 2**20:.1f} MiB)")
+        return 0
     if tier not in ("Q8_0", "W8", "INT8"):
-        print(f"--tier {tier}: this build writes per-row symmetric int8 (Q8_0-class) only; the GGUF k-quant tiers "
-              "are not built", file=sys.stderr)
+        print(f"--tier {tier}: the safetensors output is per-row symmetric int8 (Q8_0-class); use --format gguf for Q4_0",
+              file=sys.stderr)
         return 2
     if plan_only:
         from ..checkpoint import st as _st

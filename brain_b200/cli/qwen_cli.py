@@ -70,13 +70,27 @@ def _import(args, device):
     dtype = a.str_or("--dtype", "F32").upper()
     model_id = a.take_str("--id")
     mdir = a.take_str("--models-dir")
-    if not hf:
+    gguf_src = a.take_str("--gguf")
+    if not hf and not gguf_src:
         hf = a.positional() or ""
-        if hf and os.path.isfile(hf):
+        if hf.lower().endswith(".gguf"):
+            gguf_src, hf = hf, ""
+        elif hf and os.path.isfile(hf):
             hf = os.path.dirname(hf) or "."
     a.finish()
+    if gguf_src:
+        # a llama.cpp-style GGUF of a dense Qwen2 / Qwen3 model, any block type this build decodes
+        from ..checkpoint.convert import import_gguf_qwen
+        dst = out or "qwen.safetensors"
+        try:
+            cfg = import_gguf_qwen(gguf_src, dst, block, dtype, model_id=model_id)
+        except Exception as e:  # noqa: BLE001
+            print(f"import failed: {e}", file=sys.stderr)
+            return 1
+        print(f"ok: wrote {dst} ({cfg.n_layers} layers, d_model {cfg.d_model}, vocab {cfg.vocab})")
+        return 0
     if not hf:
-        print("usage: brain qwen3 import <hf_dir|model.safetensors> [--out F | --id VENDOR/REPO [--models-dir D]] "
+        print("usage: brain qwen3 import <hf_dir|model.safetensors|model.gguf> [--out F | --id VENDOR/REPO [--models-dir D]] "
               "[--block T --dtype F32|BF16]", file=sys.stderr)
         return 2
     ref = None
@@ -119,7 +133,13 @@ def _export(args, device):
     weights = a.str_or("--weights", "")
     out = a.str_or("--out", "qwen-hf")
     dtype = a.str_or("--dtype", "BF16").upper()
+    tier = a.take_str("--tier")
     a.finish()
+    if weights and out.lower().endswith(".gguf"):
+        from ..checkpoint.convert import export_gguf
+        info = export_gguf(weights, out, tier.upper() if tier else None)
+        print(f"ok: wrote {out} ({info['bytes_out'] / 2**20:.1f} MiB, {info.get('quantized', 0)} quantised tensors)")
+        return 0
     if not weights:
         print("usage: brain qwen3 export --weights F --out DIR [--dtype BF16|F32]", file=sys.stderr)
         return 2

@@ -60,7 +60,20 @@ def run_perf(argv: List[str], device: str = "auto") -> int:
         print("workloads: " + " ".join(standard_names()))
         print("targets:   fake | qwen-synth:LxDxH[xV] | weights:FILE | http:URL|KEY|MODEL")
         print("arrivals:  --concurrency N (closed loop) | --saturated | --rate R [--burstiness K]")
+        print("tools:     brain perf tool {kernels|launches|comm|serve-micro|mixed-ab|configs|fa-timeline} [args]")
         return 0
+    if sub == "tool":
+        # measurement tools that are not workloads: each is a module with its own argument parser
+        tools = {"kernels": "kernel_bench", "launches": "launch_list", "comm": "comm_bench",
+                 "serve-micro": "serve_micro", "mixed-ab": "mixed_ab", "configs": "configs",
+                 "fa-timeline": "fa_timeline"}
+        name = argv[1] if len(argv) > 1 else None
+        if name not in tools:
+            print("tools: " + " ".join(sorted(tools)), file=sys.stderr)
+            return 2
+        import importlib
+        mod = importlib.import_module(f"brain_b200.perf.{tools[name]}")
+        return int(mod.main(argv[2:]) or 0)
     if sub == "run" and len(argv) > 1 and argv[1] in ("latency", "throughput", "serve", "sweep", "startup", "mixed",
                                                       "overload", "cancel", "kvcache", "soak", "faults"):
         return run_perf(["scenario"] + argv[1:], device)     # `perf run <scenario>` as the reference spells it

@@ -14,6 +14,8 @@
 // Roles (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane),
 // warp 2 = TMEM allocator, warps 4..7 = epilogue (TMEM -> registers -> global).
 // Two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+#include <cstdlib>
+
 #include "../common/host.hpp"
 #include "../common/peer.cuh"
 #include "../common/ptx.cuh"
@@ -637,6 +639,11 @@ static long long* g_gemm_timeline = nullptr;
 // waits, [5] accumulator ready, [6] accumulator released) for its first 16 tiles.
 BB_API void bb_gemm_set_timeline(long long* buf) { g_gemm_timeline = buf; }
 
+// CTA-pair kernel (gemm_2cta.cu)
+BB_API int bb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, int lda,
+                             int ldb, int ldc, int a_mn, int b_mn, int out_mode, float alpha,
+                             int split_k, int max_ctas, void* stream);
+
 // C ABI ------------------------------------------------------------------------------------------
 // bf16 GEMM.  a_mn/b_mn: 0 = operand stored [rows][K] (K contiguous), 1 = stored [K][rows].
 // lda/ldb/ldc in elements.  out_mode: 0 bf16, 1 fp32, 2 fp32 accumulate, 3 bf16 gelu.
@@ -661,6 +668,7 @@ BB_API int bb_gemm_bf16(const void* A, const void* B, void* C, const float* bias
   a.err = device_error_word();
   a.timeline = g_gemm_timeline;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool auto_bn = bn == 0;
   if (bn == 0) {
     const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
     const long tiles128 = (long)((M + 127) / 128) * ((N + 127) / 128);
@@ -686,6 +694,18 @@ BB_API int bb_gemm_bf16(const void* A, const void* B, void* C, const float* bias
       }
     }
     a.split_k = pick;
+  }
+  // Large plain GEMMs go to the CTA-pair kernel (256 x 256 tiles over two SMs, gemm_2cta.cu): it
+  // halves the B-operand bytes each SM pulls from L2, which is what bounds this kernel at bn 256.
+  static const int pair_mode = [] {
+    const char* e = getenv("BB_GEMM_PAIR");
+    return e ? atoi(e) : 1;
+  }();
+  if (pair_mode && auto_bn && bn == 256 && bias == nullptr && out_mode != 3 && M >= 256 && N >= 256 &&
+      a.timeline == nullptr) {
+    const int rc = bb_gemm_bf16_pair(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_mode, alpha,
+                                     a.split_k, max_ctas, stream);
+    if (rc != BB_ESIZE) return rc;
   }
   switch (bn) {
     case 256: return launch_gemm<256, false>(A, B, a, lda, ldb, s, max_ctas);
@@ -713,6 +733,7 @@ BB_API int bb_gemm_i8(const void* A, const void* B, void* C, const float* scale_
   a.out_mode = 0;
   a.err = device_error_word();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool auto_bn = bn == 0;
   if (bn == 0) {
     const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
     const long tiles128 = (long)((M + 127) / 128) * ((N + 127) / 128);
