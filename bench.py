@@ -29,7 +29,7 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="native", choices=["native", "reference", "nccl"])
+    ap.add_argument("--impl", default="native", choices=["native", "reference", "nccl", "torchlib"])
     ap.add_argument("--model", default="0.6b")
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--global-batch", type=int, default=64)
@@ -127,8 +127,14 @@ def main():
         cfg.n_layers = args.layers
     torch.manual_seed(0)
     model = Qwen3(cfg).init_weights(seed=0)
-    dp = ZeroDP(impl="fused" if args.impl == "native" else "nccl") if world > 1 else None
-    trainer = Trainer(model, device=dev, betas=(0.9, 0.95), weight_decay=0.1, grad_clip=1.0, dp=dp)
+    if args.impl == "torchlib":
+        # stock PyTorch on the same architecture (cuBLAS / SDPA / fused AdamW / DDP): the library
+        # anchor on this box, NOT the reference project and none of this repository's kernels
+        from brain_b200.perf.torchlib_ref import TorchlibTrainer
+        trainer = TorchlibTrainer(cfg, dev, world, betas=(0.9, 0.95), weight_decay=0.1, grad_clip=1.0)
+    else:
+        dp = ZeroDP(impl="fused" if args.impl == "native" else "nccl") if world > 1 else None
+        trainer = Trainer(model, device=dev, betas=(0.9, 0.95), weight_decay=0.1, grad_clip=1.0, dp=dp)
 
     assert args.global_batch % world == 0
     per_rank = args.global_batch // world
@@ -211,7 +217,9 @@ def main():
             "impl": args.impl,
             "config": {"model": f"qwen3-{args.model}", "global_batch": args.global_batch,
                        "seq_len": T, "parallelism": f"dp{world}", "micro_batch": micro,
-                       "layers": cfg.n_layers, "optimizer": "AdamW sharded (ZeRO-1), clip 1.0",
+                       "layers": cfg.n_layers,
+                       "optimizer": ("torch.optim.AdamW(fused), fp32 params under bf16 autocast, DDP, clip 1.0"
+                                     if args.impl == "torchlib" else "AdamW sharded (ZeRO-1), clip 1.0"),
                        "l2": "per-step working set (weights+grads+activations, >10 GB) exceeds the 126 MB L2"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": final_loss,
             "mfu_vs_measured_sustained": None,

@@ -109,16 +109,26 @@ class _Entry:
 class Residency:
     def __init__(self, suppliers: Dict[str, Supplier], budgets: Dict[str, int],
                  pinned: Optional[Dict[str, ResidentModel]] = None,
-                 on_evict: Optional[Callable[[str, ResidentModel], None]] = None):
+                 on_evict: Optional[Callable[[str, ResidentModel], None]] = None, busy_wait_s: float = 0.0):
         """``budgets``: device name -> bytes available to models.  ``pinned``: models that are
         resident from the start, cost nothing against the budgets and are never evicted."""
         self.suppliers = dict(suppliers)
         self.budgets = dict(budgets)
         self.entries: Dict[str, _Entry] = {}
         self.on_evict = on_evict
+        #: how long a load may wait for a busy resident to go idle when nothing can be evicted
+        #: (0: fail at once with InsufficientMemory; a server sets a few seconds)
+        self.busy_wait_s = float(busy_wait_s)
         self._lock = threading.Lock()
+        self._freed = threading.Condition(self._lock)    # signalled when a resident becomes idle
         self._loading: Dict[str, threading.Event] = {}
         self.loads = self.evictions = 0
+        # eviction order: decayed request count per model (half-life 32 requests of any model), so a
+        # burst of one-off requests for the cold tail does not push out the models everybody uses;
+        # ties fall back to least recently used
+        self._heat: Dict[str, float] = {}
+        self._heat_tick: Dict[str, int] = {}
+        self._tick = 0
         for mid, m in (pinned or {}).items():
             self.entries[mid] = _Entry(m, "-", 0, pinned=True)
 
@@ -145,6 +155,14 @@ class Residency:
                              for k, e in self.entries.items()},
                 "budgets": dict(self.budgets), "loads": self.loads, "evictions": self.evictions}
 
+    def _touch(self, mid: str) -> None:
+        self._tick += 1
+        self._heat[mid] = self._heat_now(mid) + 1.0
+        self._heat_tick[mid] = self._tick
+
+    def _heat_now(self, mid: str) -> float:
+        return self._heat.get(mid, 0.0) * 0.5 ** ((self._tick - self._heat_tick.get(mid, self._tick)) / 32.0)
+
     # ---- placement / eviction (call with the lock held)
     def _place(self, need: int) -> Optional[str]:
         """The device with the most free budget that can hold ``need`` bytes, evicting idle residents
@@ -156,10 +174,10 @@ class Residency:
         for dev in order:
             if need > self.budgets[dev]:
                 continue
-            idle = sorted((e.last_used, k) for k, e in self.entries.items()
+            idle = sorted((round(self._heat_now(k), 3), e.last_used, k) for k, e in self.entries.items()
                           if e.device == dev and e.in_use == 0 and not e.pinned)
             freed, victims = self.budgets[dev] - self.used(dev), []
-            for _, k in idle:
+            for _, _, k in idle:
                 if freed >= need:
                     break
                 victims.append(k)
@@ -184,6 +202,8 @@ class Residency:
     # ---- acquire / release
     def acquire(self, mid: str, timeout_s: float = 180.0) -> ResidentModel:
         deadline = time.time() + timeout_s
+        with self._lock:
+            self._touch(mid)
         while True:
             with self._lock:
                 e = self.entries.get(mid)
@@ -205,6 +225,12 @@ class Residency:
             need = int(sup.estimate_bytes())
             with self._lock:
                 dev = self._place(need)
+                # every candidate victim is busy right now: a model that fits some device's budget
+                # waits for a resident to go idle instead of failing the request
+                give_up = min(deadline, time.time() + self.busy_wait_s)
+                while dev is None and any(need <= b for b in self.budgets.values()) and time.time() < give_up:
+                    self._freed.wait(min(0.05, max(give_up - time.time(), 0.0)))
+                    dev = self._place(need)
             if dev is None:
                 raise InsufficientMemory(f"model '{mid}' needs {need / 2**30:.2f} GiB; no device has that much "
                                          "free even after evicting every idle model")
@@ -225,6 +251,8 @@ class Residency:
             if e is not None and e.in_use > 0:
                 e.in_use -= 1
                 e.last_used = time.time()
+                if e.in_use == 0:
+                    self._freed.notify_all()
 
     def close(self) -> None:
         with self._lock:

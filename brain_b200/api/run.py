@@ -62,7 +62,7 @@ def store_residency(models_dir, reserve_gb, device: str, already: set):
             budgets[f"cuda:{i}"] = max(int(total - reserve * 2**30), 0)
     else:
         budgets = {"cpu": int(float(os.environ.get("BRAIN_RESIDENCY_BUDGET_GB", "64")) * 2**30)}
-    return Residency(sup, budgets)
+    return Residency(sup, budgets, busy_wait_s=5.0)   # a load waits briefly for a busy victim before a 429
 
 
 def run_serve(argv: List[str], device: str = "auto") -> int:

@@ -64,6 +64,8 @@ class Trainer:
         B = tokens.shape[0]
         total = None
         for r0 in range(0, B, micro_batch):
+            if r0 + micro_batch >= B and self.dp is not None and hasattr(self.dp, "arm"):
+                self.dp.arm()       # last micro-batch: finished gradient buckets may be reduced under backward
             tok = self._to_device(tokens[r0:r0 + micro_batch])
             tgt = self._to_device(targets[r0:r0 + micro_batch])
             if weights is not None:

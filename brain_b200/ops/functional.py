@@ -72,6 +72,20 @@ def gemm_i8(a_q, b_q, scale_m, scale_n, out=None, bn=0):
     return out
 
 
+def unpack_q4(words, out=None):
+    """int8 [n, 8*kw] operand of :func:`gemm_i8` from 4-bit storage ``words`` int32 [n, kw] (eight
+    two's-complement nibbles per word, element b of a group in bits 4b..4b+3)."""
+    n, kw = words.shape
+    if not words.is_cuda:
+        sh = (4 * torch.arange(8, dtype=torch.int64))[None, None, :]
+        nib = ((words.to(torch.int64) & 0xFFFFFFFF)[:, :, None] >> sh) & 0xF
+        return torch.where(nib >= 8, nib - 16, nib).reshape(n, kw * 8).to(torch.int8)
+    if out is None:
+        out = torch.empty(n, kw * 8, device=words.device, dtype=torch.int8)
+    call("unpack_q4", words.contiguous(), out, L(n * kw), stream_ptr())
+    return out
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias):

@@ -37,6 +37,12 @@ class ZeroDP:
             from .fused_dp import FusedDP
             self._fused = FusedDP(self, store, opt)
 
+    def arm(self):
+        """The trainer calls this right before the last micro-batch of a step: from here on every
+        finished gradient may start its bucket's reduce-scatter (fused engine only)."""
+        if self._fused is not None:
+            self._fused.arm()
+
     def step(self, lr, wd, clip, extra_scale=1.0):
         st, opt = self.store, self.opt
         if self.world == 1:

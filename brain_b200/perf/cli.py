@@ -75,7 +75,8 @@ def run_perf(argv: List[str], device: str = "auto") -> int:
         mod = importlib.import_module(f"brain_b200.perf.{tools[name]}")
         return int(mod.main(argv[2:]) or 0)
     if sub == "run" and len(argv) > 1 and argv[1] in ("latency", "throughput", "serve", "sweep", "startup", "mixed",
-                                                      "overload", "cancel", "kvcache", "soak", "faults"):
+                                                      "overload", "cancel", "kvcache", "soak", "faults",
+                                                      "residency", "placement", "frontend"):
         return run_perf(["scenario"] + argv[1:], device)     # `perf run <scenario>` as the reference spells it
     if sub == "run":
         a = Args(argv[1:])
@@ -160,6 +161,18 @@ def run_perf(argv: List[str], device: str = "auto") -> int:
             return 2
         if name == "faults":
             return run_perf(["faults"], device)
+        if name in ("residency", "placement", "frontend"):
+            # the layers around the engine: residency manager, placer, host-side front end (no target)
+            from . import scenarios2 as s2
+            res = (s2.residency(requests=max(n, 120), concurrency=conc, seed=seed) if name == "residency"
+                   else s2.placement(requests=max(n, 60), seed=seed) if name == "placement"
+                   else s2.frontend(requests=max(n, 20), device_rate_per_s=rate or 200.0, seed=seed))
+            text = json.dumps(res)
+            if out:
+                open(out, "w").write(text + "\n")
+            else:
+                print(text)
+            return 0 if res.get("passed", True) else 1
         try:
             mk, vocab = _make_target(target, device, conc, ctx, weights)
             if name == "latency":

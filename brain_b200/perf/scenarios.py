@@ -243,4 +243,4 @@ def soak(make: Make, seconds: float = 5.0, concurrency: int = 4, seed: int = 0, 
 
 
 TIER1 = ("latency", "throughput", "serve", "sweep", "startup")
-TIER2 = ("mixed", "overload", "cancel", "kvcache", "soak", "faults")
+TIER2 = ("mixed", "overload", "cancel", "kvcache", "soak", "faults", "residency", "placement", "frontend")

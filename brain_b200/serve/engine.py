@@ -11,6 +11,9 @@ prefill with prefix-cache reuse).
   has a past, else the chunk itself).
 * ``decode``: one batched step (or a window of k greedy steps fed back on the device) over all
   running sequences with the split-KV paged attention kernel; greedy head = on-device argmax.
+* ``weights='int4'``: W4A8 — 4-bit per-output-channel symmetric weights (half a byte per parameter in
+  device memory, crates/model/src/int4.rs:46-73) expanded into one shared int8 scratch right before
+  each projection's int8 GEMM; activations as in W8A8.
 * ``weights='int8'``: W8A8 — per-output-channel symmetric int8 weights, dynamic per-token int8
   activations, tcgen05 ``kind::i8`` GEMM with both scales applied in the epilogue
   (crates/model/src/int8.rs:33-59, 221-235).
@@ -37,27 +40,52 @@ from ..ops.attention import flash_attention, flash_attention_into
 
 
 class _Lin:
-    """A projection held either as bf16 weights or as W8A8 int8 weights + per-channel scales."""
+    """A projection held as bf16 weights, as W8A8 int8 weights + per-channel scales, or as W4A8:
+    4-bit weights (half a byte per parameter in memory) that are expanded into a scratch int8 buffer
+    shared by all projections right before the int8 GEMM that consumes them."""
 
-    def __init__(self, w: torch.Tensor, bias: Optional[torch.Tensor] = None, int8: bool = False):
-        self.int8 = int8
+    _scratch = {}       # device -> int8 scratch for the expanded 4-bit weights (grows to the largest)
+
+    def __init__(self, w: torch.Tensor, bias: Optional[torch.Tensor] = None, int8: bool = False,
+                 int4: bool = False):
+        self.int8 = int8 or int4
+        self.int4 = int4
         self.bias = bias.float().contiguous() if bias is not None else None
-        if int8:
+        self.out_features = w.shape[0]
+        if int4:
+            from .quantize import quantize_weight_q4
+            words, sw = quantize_weight_q4(w.float().cpu())
+            self.words, self.sw = words.to(w.device).contiguous(), sw.to(w.device).contiguous()
+            self.shape = (w.shape[0], w.shape[1])
+        elif int8:
             self.wq, self.sw = F.quant_rows(w.float() if not w.is_cuda else w)
             self.wq, self.sw = self.wq.contiguous(), self.sw.contiguous()
-            self.out_features = w.shape[0]
         else:
             self.w = w.contiguous()
-            self.out_features = w.shape[0]
+
+    def _wq(self) -> torch.Tensor:
+        """The int8 operand: resident (W8A8) or expanded from the nibbles into the scratch (W4A8)."""
+        if not self.int4:
+            return self.wq
+        if not self.words.is_cuda:
+            return F.unpack_q4(self.words)
+        n = self.shape[0] * self.shape[1]
+        buf = _Lin._scratch.get(self.words.device)
+        if buf is None or buf.numel() < n:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("the 4-bit expansion scratch must be sized before graph capture")
+            buf = _Lin._scratch[self.words.device] = torch.empty(n, device=self.words.device, dtype=torch.int8)
+        return F.unpack_q4(self.words, buf[:n].view(self.shape))
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         if self.int8:
+            wq = self._wq()
             if x.is_cuda:
                 xq, sx = F.quant_rows(x)
-                y = F.gemm_i8(xq, self.wq, sx, self.sw)
+                y = F.gemm_i8(xq, wq, sx, self.sw)
             else:
                 xq, sx = ref.quant_rows(x)
-                y = ((xq.float() @ self.wq.float().t()) * sx[:, None] * self.sw[None, :]).to(x.dtype)
+                y = ((xq.float() @ wq.float().t()) * sx[:, None] * self.sw[None, :]).to(x.dtype)
             if self.bias is not None:
                 y = y + self.bias.to(y.dtype)
             return y
@@ -66,6 +94,8 @@ class _Lin:
         return ref.linear(x, self.w, self.bias.to(x.dtype) if self.bias is not None else None)
 
     def nbytes(self) -> int:
+        if self.int4:
+            return self.words.numel() * 4 + 4 * self.sw.numel()
         if self.int8:
             return self.wq.numel() + 4 * self.sw.numel()
         return self.w.numel() * self.w.element_size()
@@ -90,7 +120,9 @@ class QwenEngine:
         self.max_seq_len, self.max_prefill_tokens = max_seq_len, max_prefill
         self.topk_capacity = topk
         self.max_blocks = (max_seq_len + block_size - 1) // block_size
-        self.int8 = weights == "int8"
+        assert weights in ("bf16", "int8", "int4"), weights
+        self.int8 = weights in ("int8", "int4")
+        self.int4 = weights == "int4"       # W4A8: nibble storage, expanded per projection call
         w = self.tp_world
         assert cfg.n_heads % w == 0 and cfg.n_kv_heads % w == 0 and cfg.d_ff % w == 0, \
             "tensor-parallel degree must divide the head counts and d_ff"
@@ -120,10 +152,10 @@ class QwenEngine:
                 ln1=cast(blk.ln1), ln2=cast(blk.ln2),
                 q_norm=cast(blk.q_norm) if blk.q_norm is not None else None,
                 k_norm=cast(blk.k_norm) if blk.k_norm is not None else None,
-                qkv=_Lin(cast(rows), bias, self.int8),
-                wo=_Lin(cast(blk.wo.detach()[:, r * ql:(r + 1) * ql]), None, self.int8),
-                gate_up=_Lin(cast(gu_rows), None, self.int8),
-                down=_Lin(cast(blk.down.detach()[:, r * fl:(r + 1) * fl]), None, self.int8),
+                qkv=_Lin(cast(rows), bias, self.int8, self.int4),
+                wo=_Lin(cast(blk.wo.detach()[:, r * ql:(r + 1) * ql]), None, self.int8, self.int4),
+                gate_up=_Lin(cast(gu_rows), None, self.int8, self.int4),
+                down=_Lin(cast(blk.down.detach()[:, r * fl:(r + 1) * fl]), None, self.int8, self.int4),
             ))
         self.norm = cast(model.norm)
         head = model.head_weight().detach()
@@ -161,7 +193,7 @@ class QwenEngine:
         self.native = None
         if native is None:
             native = os.environ.get("BRAIN_SERVE_NATIVE", "1") == "1"
-        if native and self.cuda:
+        if native and self.cuda and not self.int4:    # the native sequence takes resident int8 operands
             from .native import NativeForward
             tp_ok = self.tp is None or self.tp_world == 1 or \
                 (getattr(self.tp, "impl", "") == "fused" and cfg.d_model % (8 * self.tp_world) == 0)

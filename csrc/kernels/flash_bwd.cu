@@ -666,14 +666,12 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc_fence_after();
       if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * it + 1);
       uint32_t pk[32];
-      uint32_t rs2[2][32];
-      __syncwarp();
-      tmem_ld32(tS, rs2[0]);        // both halves in flight: one TMEM round trip instead of two
-      tmem_ld32(tS + 32, rs2[1]);
-      tmem_wait_ld();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        const uint32_t (&rs)[32] = rs2[c];
+        uint32_t rs[32];
+        __syncwarp();
+        tmem_ld32(tS + c * 32, rs);
+        tmem_wait_ld();
         const int first_ok = q_min - (q0 + c * 32);  // columns i >= first_ok are visible
         const float4* ls4 = reinterpret_cast<const float4*>(ls + c * 32);
 #pragma unroll
@@ -705,14 +703,12 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if (!ok) break;
       tc_fence_after();
       if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * it + 3);
-      uint32_t rp2[2][32];
-      __syncwarp();
-      tmem_ld32(tD, rp2[0]);
-      tmem_ld32(tD + 32, rp2[1]);
-      tmem_wait_ld();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        const uint32_t (&rp)[32] = rp2[c];
+        uint32_t rp[32];
+        __syncwarp();
+        tmem_ld32(tD + c * 32, rp);
+        tmem_wait_ld();
         const float4* dl4 = reinterpret_cast<const float4*>(dl + c * 32);
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {

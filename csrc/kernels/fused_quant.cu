@@ -178,6 +178,38 @@ BB_API int bb_rmsnorm_q8(const void* x, const void* res, const void* w, void* h_
   return (int)cudaGetLastError();
 }
 
+namespace bb {
+// 4-bit weight storage -> int8 operand of the kind::i8 GEMM (W4A8): every 32-bit word holds eight
+// two's-complement nibbles, element b of the group in bits 4b..4b+3.  One thread expands one word
+// into eight int8 values (one 8-byte store), so a layer's weights live in HBM at half a byte per
+// parameter and are expanded into a scratch buffer right before the GEMM that consumes them.
+// Reference: crates/model/src/int4.rs:46-73 (storage format), crates/kernels/wgsl/matmul_q4_dyn.wgsl.
+__global__ void unpack_q4_kernel(const int* __restrict__ words, int2* __restrict__ out, long n_words) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_words) return;
+  const int w = __ldg(words + i);
+  int lo = 0, hi = 0;
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const int v0 = (w << (28 - 4 * b)) >> 28;        // sign-extended nibble b
+    const int v1 = (w << (12 - 4 * b)) >> 28;        // nibble b + 4
+    lo |= (v0 & 0xFF) << (8 * b);
+    hi |= (v1 & 0xFF) << (8 * b);
+  }
+  out[i] = make_int2(lo, hi);
+}
+
+}  // namespace bb
+
+// out[8 * n_words] int8 = the sign-extended nibbles of words[n_words]; out must be 8-byte aligned.
+BB_API int bb_unpack_q4(const void* words, void* out, long n_words, void* stream) {
+  if (n_words <= 0) return bb::BB_OK;
+  if (reinterpret_cast<uintptr_t>(out) & 7) return bb::BB_EARG;
+  const long blocks = (n_words + 255) / 256;
+  bb::unpack_q4_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const int*)words, (int2*)out, n_words);
+  return (int)cudaGetLastError();
+}
+
 // q[rows, ff] int8, scale[rows] = quant_rows(silu(gu[:, :ff]) * gu[:, ff:]).  ff % 8 == 0, ff <= 4096 (BB_ESIZE beyond).
 BB_API int bb_swiglu_q8(const void* gu, void* q, float* scale, int rows, int ff, void* stream) {
   if (rows <= 0) return BB_OK;

@@ -11,8 +11,8 @@
 // Every load is a plain per-CTA TMA copy from this GPU's memory into the CTA's own shared memory.
 //
 // Protocol (leader = cluster rank 0, which issues every MMA):
-//   full[s]        in the LEADER's shared memory, 2 arrivals: each CTA's producer posts its own byte
-//                  count on it and its TMA copies complete on it
+//   full[s]        in the LEADER's shared memory, 1 arrival: the leader's producer posts the byte count of
+//                  both CTAs; the TMA copies of both CTAs complete on it
 //   empty[s]       per CTA; the leader's tcgen05.commit arrives on both CTAs' barriers
 //   tmem_full[a]   per CTA; committed to both by the leader when a tile's MMAs are done
 //   tmem_empty[a]  in the leader's shared memory, 8 arrivals: one per epilogue warp of the pair
@@ -24,6 +24,8 @@
 // Replaces, like gemm_tcgen05.cu, the reference's register-tiled GEMMs
 // (crates/kernels/wgsl/matmul_reg3.wgsl, matmul_dx_reg.wgsl, matmul_dw_reg.wgsl).
 #include <cuda_runtime.h>
+
+#include <cstdlib>
 
 #include "../common/host.hpp"
 #include "../common/ptx.cuh"
@@ -99,7 +101,19 @@ struct PairArgs {
   int out_mode;  // 0 bf16 store, 1 fp32 store, 2 fp32 accumulate (TMA reduce-add)
   int split_k;
   int* err;
+#ifdef BB_TIMELINE
+  long long* dbg;  // profiling builds: cycle counters of pair 0 ([0] MMA loop, [1] waiting for data,
+                   // [2] waiting for an accumulator, [3]/[4] leader / peer producer waiting for a free slot)
+#endif
 };
+
+#ifdef BB_TIMELINE
+#define PAIR_CLK() clock64()
+#define PAIR_ADD(slot, v) do { if (args.dbg && pair_id == 0) atomicAdd((unsigned long long*)&args.dbg[slot], (unsigned long long)(v)); } while (0)
+#else
+#define PAIR_CLK() 0LL
+#define PAIR_ADD(slot, v) do { } while (0)
+#endif
 
 static constexpr int BM = 128;        // rows per CTA; the pair tile is 2 * BM rows
 static constexpr int BNP = 256;       // columns of the pair tile; each CTA stages BNP / 2 of them
@@ -143,7 +157,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
-      mbar_init(&full[i], 2);    // one arrival (with its byte count) per CTA of the pair
+      mbar_init(&full[i], 1);    // the leader's producer arrives with the byte count of both CTAs
       mbar_init(&empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -197,15 +211,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int m0 = tm * 2 * BM + (int)rank * BM;       // this CTA's rows of A
         const int n0 = tn * BNP + (int)rank * (BNP / 2);   // this CTA's half of the B columns
         for (int kb = 0; kb < nkb; ++kb) {
+          const long long w0 = PAIR_CLK();
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             set_error(args.err, ERR_WAIT_PRODUCER);
             ok = false;
             break;
           }
+          PAIR_ADD(3 + (int)rank, PAIR_CLK() - w0);
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
+          // Only the leader arrives on full[s], announcing the bytes of BOTH CTAs; the peer's copies
+          // just complete on that barrier (a remote arrive per k-block costs the producer a cluster-
+          // scope release, which made it the slowest role).  Bytes that land before the leader's
+          // announcement leave the count negative for a moment; the phase cannot complete without
+          // the leader's arrival.
           const uint32_t bar = map_to_rank(smem_u32(&full[stage]), 0);
-          mbar_expect_tx_cluster(bar, STAGE_BYTES);
+          if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
           const int k0 = (kb0 + kb) * BK;
           if (!args.a_mn) {
             tma_load_2d_pair(sa, &tmA, bar, k0, m0);
@@ -239,26 +260,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      const long long loop0 = PAIR_CLK();
       for (int t = pair_id; t < ntiles && ok; t += n_pairs) {
         int tm, tn, kb0, nkb;
         if (!tile_info(t, tm, tn, kb0, nkb)) continue;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         ++it;
+        const long long e0 = PAIR_CLK();
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
           set_error(args.err, ERR_WAIT_MMA_TMEM);
           ok = false;
           break;
         }
         tc_fence_after();
+        PAIR_ADD(2, PAIR_CLK() - e0);
         const uint32_t d_tmem = tmem_base + acc * BNP;
         for (int kb = 0; kb < nkb; ++kb) {
+          const long long f0 = PAIR_CLK();
           if (!mbar_wait(&full[stage], phase)) {
             set_error(args.err, ERR_WAIT_MMA_FULL);
             ok = false;
             break;
           }
           tc_fence_after();
+          PAIR_ADD(1, PAIR_CLK() - f0);
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
 #pragma unroll
@@ -282,6 +308,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           umma_commit_pair(map_to_rank(f, 1));
         }
       }
+      PAIR_ADD(0, PAIR_CLK() - loop0);
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
@@ -380,6 +407,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }  // namespace pair
 }  // namespace bb
 
+#ifdef BB_TIMELINE
+static long long* g_pair_dbg = nullptr;
+BB_API int bb_gemm_pair_set_debug(long long* buf) {
+  g_pair_dbg = buf;
+  return 0;
+}
+#endif
+
+// Number of 2-CTA clusters the current device runs at once, as found by the first launch (0 before).
+static std::atomic<int> g_last_pairs_fit{0};
+BB_API int bb_gemm_pair_clusters() { return g_last_pairs_fit.load(); }
+
 // Pair-tile bf16 GEMM (see the top of the file).  Same argument meaning as bb_gemm_bf16; serves
 // out_mode 0 / 1 / 2 without bias.  Returns BB_ESIZE when the shape or alignment does not suit the
 // pair kernel (the caller then uses the single-CTA kernel): C must be 16-byte aligned with a
@@ -434,6 +473,14 @@ BB_API int bb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N
     pairs_fit = n;
     if (dev >= 0 && dev < 64) max_pairs[dev].store(n, std::memory_order_relaxed);
   }
+  {
+    static const int forced = [] {
+      const char* e = getenv("BB_PAIR_CLUSTERS");
+      return e ? atoi(e) : 0;
+    }();
+    if (forced > 0) pairs_fit = forced;
+  }
+  g_last_pairs_fit.store(pairs_fit);
   PairArgs a{};
   a.alpha = alpha;
   a.M = M;
@@ -444,6 +491,9 @@ BB_API int bb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N
   a.out_mode = out_mode;
   a.split_k = (out_mode == 2 && split_k > 1) ? split_k : 1;
   a.err = device_error_word();
+#ifdef BB_TIMELINE
+  a.dbg = g_pair_dbg;
+#endif
   const long tiles = (long)((M + 2 * BM - 1) / (2 * BM)) * ((N + BNP - 1) / BNP) * a.split_k;
   long pairs = tiles < pairs_fit ? tiles : pairs_fit;
   if (max_ctas > 0 && pairs > max_ctas / 2) pairs = max_ctas / 2;

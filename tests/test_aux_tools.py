@@ -170,3 +170,16 @@ def test_hsm_bubbling_lca_ordering_and_run_to_completion():
     h.send("nonsense")                                 # unhandled everywhere: ignored
     h.send("ack")
     assert h.state == "idle" and m.log[-3:] == ["-cancelling", "-busy", "+idle"]
+
+
+def test_torchlib_arm_trains_on_cpu():
+    """The stock-PyTorch arm of the benchmarks (same architecture, none of this repository's
+    kernels) takes the native trainer's call and learns."""
+    import torch
+    from brain_b200.models.config import QwenConfig
+    from brain_b200.perf.torchlib_ref import TorchlibTrainer
+    cfg = QwenConfig(vocab=128, block_size=32, n_layers=2, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, d_ff=128)
+    tr = TorchlibTrainer(cfg, torch.device("cpu"))
+    ids = torch.randint(0, 128, (4, 33), dtype=torch.int32)
+    losses = [float(tr.train_step(ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), 1e-2, 2)) for _ in range(5)]
+    assert abs(losses[0] - 4.85) < 0.3 and losses[-1] < losses[0] - 0.5

@@ -53,6 +53,8 @@ def _gemm_pair(aa, bb, out, a_mn, b_mn, out_mode, alpha=1.0, split_k=1):
                                    (264, 1000, 72)])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
 def test_gemm_pair_kernel(M, N, K, a_mn, b_mn):
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operand needs a 16-byte row pitch")
     torch.manual_seed(M + N + K + 1)
     a = torch.randn(M, K, device=dev()).bfloat16()
     b = torch.randn(N, K, device=dev()).bfloat16()

@@ -365,3 +365,32 @@ def test_trainer_ep_two_gloo_ranks_match_single_process():
             if is_expert_param(k):
                 want_t = want_t[lo:lo + n]
             assert torch.allclose(v, want_t, atol=2e-4), (k, float((v - want_t).abs().max()))
+
+
+def test_bucket_tracker_learns_counts_and_reruns_early_buckets():
+    """Host logic of the overlapped data-parallel step: buckets are cut inside rank shards and listed
+    back to front; a bucket is released by the last expected accumulation of its parameters; an
+    accumulation that arrives after its bucket went out marks the bucket for a second run."""
+    from brain_b200.parallel.fused_dp import BucketTracker, make_buckets
+    buckets = make_buckets(64, 2, 16)
+    assert buckets == [(1, 48, 64), (1, 32, 48), (0, 16, 32), (0, 0, 16)]
+    # parameters: E (tied embedding, accumulated twice) [0,20), A [20,40), B [40,64)
+    slots = [(1, 0, 20), (2, 20, 20), (3, 40, 24)]
+    t = BucketTracker(buckets, slots)
+    order = [1, 3, 2, 1]                        # head's dW into E, then B, A, then the embedding scatter
+    t.begin()
+    assert [t.notify(k) for k in order] == [[], [], [], []]      # first step: nothing is known yet
+    assert t.finish() == [0, 1, 2, 3]
+    t.begin()
+    got = [t.notify(k) for k in order]
+    assert got == [[], [0], [1], [2, 3]]        # B frees bucket 0; A frees 1 (B+A done); E's 2nd frees 2 and 3
+    assert t.finish() == []
+    # a step in which E is accumulated a third time: its buckets were already out -> run again
+    t.begin()
+    for k in order:
+        t.notify(k)
+    assert t.notify(1) == []
+    assert t.finish() == [2, 3]
+    t.begin()                                   # and the new count is the expectation from now on
+    got = [t.notify(k) for k in order + [1]]
+    assert got[-1] == [2, 3] and got[3] == []

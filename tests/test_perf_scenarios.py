@@ -57,3 +57,20 @@ def test_overload_rejects_the_excess(model):
     r = sc.overload(mk, capacity_per_s=50.0, factor=40.0, n=24, vocab=VOCAB, input_override=16)
     assert r["passed"], r
     assert 0 < r["rejected_fraction"] < 1
+
+
+def test_residency_placement_and_frontend_scenarios():
+    """The scenarios around the engine: many models over one budget through the real residency
+    manager (nothing fails or starves under a 4x oversubscribed catalogue with a popularity shift),
+    the placer's mix against the best single device, and the host-side cost per request."""
+    from brain_b200.perf import scenarios2 as s2
+    r = s2.residency(requests=160, seed=1)
+    assert r["passed"], r
+    assert r["oversubscription"] >= 3 and r["evictions"] > 0 and r["hit_rate"] > 0.2
+    assert r["ttfa_warm_p50_ms"] < r["ttfa_cold_p50_ms"]
+    p = s2.placement(requests=80)
+    assert p["passed"] and p["placement_efficiency"] > 1.2, p
+    f = s2.frontend(requests=10)
+    assert f["passed"] and f["host_cores_per_saturated_device"] > 0 and f["dominant_stage"] in f["stage_us_per_request"]
+    from brain_b200.perf.cli import run_perf
+    assert run_perf(["scenario", "frontend", "--requests", "5"]) == 0

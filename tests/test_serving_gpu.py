@@ -241,3 +241,35 @@ def test_native_forward_matches_python_path(weights, kv):
         _same_candidates(py["cand"], other["cand"])
         for ca, cb in zip(py["dcand"], other["dcand"]):
             _same_candidates(ca, cb)
+
+
+def test_w4a8_unpack_kernel_and_engine():
+    """The nibble-expansion kernel is exact against the PyTorch restatement, and the W4A8 engine
+    (4-bit weights expanded per projection into the shared int8 scratch, CUDA-graph decode included)
+    picks tokens whose logits the bf16 engine ranks close to its own best."""
+    from brain_b200.ops import _cuda, functional as F
+    from brain_b200.serve.quantize import quantize_weight_q4
+    torch.manual_seed(0)
+    w = torch.randn(96, 256)
+    words, sw = quantize_weight_q4(w)
+    want = F.unpack_q4(words)                                   # CPU restatement
+    got = F.unpack_q4(words.cuda())
+    assert torch.equal(got.cpu(), want) and int(want.abs().max()) <= 7
+    e4, e16 = _engine("int4"), _engine("bf16")
+    assert e4.native is None and all(l["qkv"].int4 for l in e4.layers)
+    toks = np.random.RandomState(0).randint(0, 512, 48).astype(np.int32)
+    bt = np.arange(32, dtype=np.int32)
+    for e in (e4, e16):
+        e.prefill_chunk(toks, 0, bt, True)
+    nxt = np.array([7], dtype=np.int32)
+    pos = np.array([48], dtype=np.int32)
+    _, c4 = e4.decode(nxt, pos, bt[None, :], greedy=False)
+    _, c16 = e16.decode(nxt, pos, bt[None, :], greedy=False)
+    d4, d16 = dict(c4[0]), dict(c16[0])
+    common = set(d4) & set(d16)
+    spread = max(d16.values()) - min(d16.values())
+    assert len(common) >= 32 and max(abs(d4[t] - d16[t]) for t in common) < 0.35 * spread
+    g1, _ = e4.decode(nxt, pos, bt[None, :], greedy=True)       # graph path: same scratch, same result twice
+    g2, _ = e4.decode(nxt, pos, bt[None, :], greedy=True)
+    assert g1 == g2
+    _cuda.check_error()

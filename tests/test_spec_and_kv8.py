@@ -97,3 +97,29 @@ def test_int8_kv_clip_ceiling():
     e.prefill_chunk(np.arange(20, dtype=np.int32), 0, bt, True)
     assert float(e.ks[0].max()) <= 0.05 / 127 + 1e-9 and float(e.vs[1].max()) <= 0.05 / 127 + 1e-9
     assert int(e.kc[0].abs().max()) == 127
+
+
+def test_w4a8_weights_close_to_full_precision_at_half_a_byte_per_parameter():
+    """4-bit weight storage expanded to the int8 GEMM operand (W4A8): candidate logits stay close
+    to the bf16 engine's, weight memory is a quarter of bf16's, and the nibble expansion is exact."""
+    from brain_b200.ops import functional as Fn
+    from brain_b200.serve.quantize import dequantize_weight_q4, quantize_weight_q4
+    w = torch.randn(24, 64)
+    words, sw = quantize_weight_q4(w)
+    assert torch.equal(Fn.unpack_q4(words).float() * sw[:, None], dequantize_weight_q4(words, sw))
+    m = _model()
+    toks = np.random.RandomState(1).randint(0, 61, 24)
+    bt = np.arange(12, dtype=np.int32)
+    res = {}
+    for mode in ("bf16", "int4"):
+        e = QwenEngine(m, block_size=8, num_blocks=16, max_seq_len=96, max_prefill=32, weights=mode)
+        e.prefill_chunk(toks, 0, bt, True)
+        _, cands = e.decode(np.array([3], dtype=np.int32), np.array([24], dtype=np.int32), bt[None, :], greedy=False)
+        res[mode] = dict(cands[0])
+        res[mode + "_bytes"] = sum(l[k].nbytes() for l in e.layers for k in ("qkv", "wo", "gate_up", "down"))
+    common = set(res["bf16"]) & set(res["int4"])
+    assert len(common) >= 40
+    err = max(abs(res["bf16"][t] - res["int4"][t]) for t in common)
+    spread = max(res["bf16"].values()) - min(res["bf16"].values())
+    assert err < 0.35 * spread, (err, spread)
+    assert res["int4_bytes"] * 6 < res["bf16_bytes"]          # CPU weights are fp32: 4 bytes -> ~0.5
