@@ -134,6 +134,10 @@ class _Linear(torch.autograd.Function):
 
 def linear(x, w, bias=None):
     if not x.is_cuda:
+        if x.dtype == torch.float32 and w.dtype == torch.float32:
+            from . import cpu_native
+            if cpu_native.enabled():      # BRAIN_CPU_NATIVE=1: the AVX2 GEMM of csrc/cpu instead of PyTorch's
+                return cpu_native.linear(x, w, bias)
         return ref.linear(x, w, bias)
     return _Linear.apply(x, w, bias)
 

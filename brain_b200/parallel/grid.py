@@ -71,6 +71,16 @@ class ProcessGroups:
                 if self.rank in ranks:
                     mine = (g, ranks)
             self.groups[axis] = mine
+        # pipeline p2p runs on two communicators of its own, one per direction: activations going
+        # down and gradients coming up then never queue behind each other (or behind the
+        # collectives of the default group) on one NCCL stream
+        for name in ("pp_fwd", "pp_bwd"):
+            mine = None
+            for ranks in grid.all_groups("pp"):
+                g = dist.new_group(ranks, backend=backend) if len(ranks) > 1 else None
+                if self.rank in ranks:
+                    mine = (g, ranks)
+            self.groups[name] = mine
 
     def group(self, axis: str):
         return self.groups[axis][0]

@@ -6,7 +6,9 @@ Each rank of the pipeline group holds one stage (a model built with ``layers=ran
 reference's all-forward-then-all-backward): forward receives the residual stream ``[mb*T, d]`` from
 the previous stage and sends its own on; backward receives the gradient of what it sent and sends
 the gradient of what it received.  Transfers are ``torch.distributed`` p2p (NCCL on GPUs, gloo on
-CPU ranks) issued asynchronously, so a stage computes while its sends drain.  Stage inputs are kept
+CPU ranks) on one communicator per direction; sends are asynchronous and the receive of the NEXT op
+of the schedule is posted before the current op computes, so a stage's transfers run under its
+compute instead of in front of it.  Stage inputs are kept
 for the backward; with ``model.recompute_blocks`` only block inputs are kept inside a stage and the
 blocks are re-run in backward (the reference's re-materialisation).  With tied embeddings the first and last stage both hold
 ``tok.weight`` and sum its gradient before the optimiser step.
@@ -25,10 +27,14 @@ from .plan import schedule as make_schedule
 
 class PipelineStage:
     def __init__(self, model, stage: int, n_stages: int, prev_rank: Optional[int], next_rank: Optional[int],
-                 group=None, tied_group=None, schedule: str = "1f1b", act_dtype=None, row_div: int = 1):
+                 group=None, tied_group=None, schedule: str = "1f1b", act_dtype=None, row_div: int = 1,
+                 group_fwd=None, group_bwd=None):
         self.model, self.stage, self.n_stages = model, stage, n_stages
         self.prev, self.next = prev_rank, next_rank
         self.group, self.tied_group = group, tied_group
+        # activations travel on group_fwd, gradients on group_bwd (both default to ``group``)
+        self.group_fwd = group_fwd if group_fwd is not None else group
+        self.group_bwd = group_bwd if group_bwd is not None else group
         self.schedule = schedule
         p = next(model.parameters())
         self.device = p.device
@@ -45,13 +51,13 @@ class PipelineStage:
     def last(self):
         return self.stage == self.n_stages - 1
 
-    def _recv(self, shape, src):
+    def _post_recv(self, shape, src, group):
+        """Start a receive; returns (work, buffer).  The caller waits right before the data is used."""
         buf = torch.empty(shape, device=self.device, dtype=self.act_dtype)
-        dist.recv(buf, src=src, group=self.group)
-        return buf
+        return dist.irecv(buf, src=src, group=group), buf
 
-    def _send(self, t, dst):
-        self._pending.append((dist.isend(t.contiguous(), dst=dst, group=self.group), t))
+    def _send(self, t, dst, group):
+        self._pending.append((dist.isend(t.contiguous(), dst=dst, group=group), t))
 
     def _drain(self):
         for w, _ in self._pending:
@@ -65,17 +71,44 @@ class PipelineStage:
         on the last stage (None elsewhere)."""
         n_micro = len(micro_tokens)
         ops = make_schedule(self.schedule, self.stage, self.n_stages, n_micro)
+
+        def recv_spec(op):
+            """(shape, source, group) of the transfer op needs before it can run, or None."""
+            B, T = micro_tokens[abs(op) - 1].shape
+            shape = (B * T // self.row_div, self.d_model)
+            if op > 0:
+                return None if self.first else (shape, self.prev, self.group_fwd)
+            return None if self.last else (shape, self.next, self.group_bwd)
+
+        posted = {}
+
+        def post(i):
+            if i < len(ops) and i not in posted:
+                spec = recv_spec(ops[i])
+                posted[i] = self._post_recv(*spec) if spec is not None else None
+
+        def take(i):
+            post(i)
+            r = posted.pop(i)
+            if r is None:
+                return None
+            r[0].wait()
+            return r[1]
+
         stash = {}
         total = None
-        for op in ops:
+        post(0)
+        for i, op in enumerate(ops):
             m = abs(op) - 1
             B, T = micro_tokens[m].shape
+            got = take(i)
+            post(i + 1)          # the next op's input arrives while this op computes
             if op > 0:
                 if self.first:
                     x_in = None
                     out = self.model.hidden(tokens=micro_tokens[m].to(self.device))
                 else:
-                    x_in = self._recv((B * T // self.row_div, self.d_model), self.prev).requires_grad_()
+                    x_in = got.requires_grad_()
                     out = self.model.hidden(x_in=x_in, B=B, T=T)
                 if self.last:
                     from ..ops import functional as F
@@ -87,17 +120,16 @@ class PipelineStage:
                     stash[m] = (x_in, loss)
                     total = loss.detach() if total is None else total + loss.detach()
                 else:
-                    self._send(out.detach(), self.next)
+                    self._send(out.detach(), self.next, self.group_fwd)
                     stash[m] = (x_in, out)
             else:
                 x_in, out = stash.pop(m)
                 if self.last:
                     out.backward()
                 else:
-                    dout = self._recv(tuple(out.shape), self.next)
-                    out.backward(dout)
+                    out.backward(got)
                 if not self.first:
-                    self._send(x_in.grad, self.prev)
+                    self._send(x_in.grad, self.prev, self.group_bwd)
         self._drain()
         return total
 

@@ -85,7 +85,8 @@ class Trainer3D:
         prev_r = pp_ranks[stage - 1] if stage > 0 else None
         next_r = pp_ranks[stage + 1] if stage < grid.pp - 1 else None
         self.pipe = PipelineStage(model, stage, grid.pp, prev_r, next_r, group=None, tied_group=self.tied_group,
-                                  schedule=schedule, act_dtype=dt, row_div=grid.tp)
+                                  schedule=schedule, act_dtype=dt, row_div=grid.tp,
+                                  group_fwd=self.pgs.group("pp_fwd"), group_bwd=self.pgs.group("pp_bwd"))
         self._replicated = [p for p in model.parameters() if getattr(p, "tp_replicated", False)]
         self.step_count = 0
         self.last_grad_norm = None

@@ -64,9 +64,10 @@ def test_flash_bwd(B, T, hq, hk, hd, causal):
     assert rel_err(v.grad, vr.grad) < 3e-2
 
 
-def test_flash_fwd_first_form_still_matches():
-    """BB_FA_FWD=1 selects the single-buffer forward kernel (the one with timeline stamps); it is
-    read once per process, so the check runs in a child process."""
+@pytest.mark.parametrize("form", ["1", "2"])
+def test_flash_fwd_earlier_forms_still_match(form):
+    """BB_FA_FWD=1 selects the single-buffer forward kernel (the one with timeline stamps), =2 the
+    two-unit form; the switch is read once per process, so the check runs in a child process."""
     import os
     import subprocess
     import sys
@@ -82,7 +83,7 @@ def test_flash_fwd_first_form_still_matches():
         "    assert ((o.float()-w).norm()/w.norm()).item() < 2e-2\n"
         "print('ok')\n")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, BB_FA_FWD="1", PYTHONPATH=root),
+    r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, BB_FA_FWD=form, PYTHONPATH=root),
                        capture_output=True, text=True, timeout=300, cwd=root)
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
 

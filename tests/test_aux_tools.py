@@ -183,3 +183,36 @@ def test_torchlib_arm_trains_on_cpu():
     ids = torch.randint(0, 128, (4, 33), dtype=torch.int32)
     losses = [float(tr.train_step(ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), 1e-2, 2)) for _ in range(5)]
     assert abs(losses[0] - 4.85) < 0.3 and losses[-1] < losses[0] - 0.5
+
+
+def test_native_cpu_gemm_and_linear_autograd():
+    """csrc/cpu: the AVX2 GEMM in all three products of a linear layer (odd sizes, strided rows,
+    alpha / beta) and the autograd wrapper against the PyTorch restatement."""
+    import torch
+    from brain_b200.ops import cpu_native, reference as ref
+    torch.manual_seed(0)
+    for M, N, K in ((1, 1, 1), (7, 19, 33), (130, 257, 300), (64, 1030, 520)):
+        a, b = torch.randn(M, K), torch.randn(N, K)
+        want = a @ b.t()
+        assert torch.allclose(cpu_native.gemm(a, b, tb=True), want, rtol=1e-4, atol=1e-3)
+        assert torch.allclose(cpu_native.gemm(a, b.t().contiguous()), want, rtol=1e-4, atol=1e-3)
+        assert torch.allclose(cpu_native.gemm(a.t().contiguous(), b, ta=True, tb=True), want, rtol=1e-4, atol=1e-3)
+    big = torch.randn(40, 100)
+    a = big[:, 10:74]                                            # strided rows
+    b = torch.randn(24, 64)
+    c0 = torch.randn(40, 24)
+    got = cpu_native.gemm(a, b, tb=True, out=c0.clone(), alpha=0.5, beta=2.0)
+    assert torch.allclose(got, 0.5 * (a @ b.t()) + 2.0 * c0, rtol=1e-4, atol=1e-3)
+    x = torch.randn(3, 17, 48, requires_grad=True)
+    w = torch.randn(80, 48, requires_grad=True)
+    bias = torch.randn(80, requires_grad=True)
+    dy = torch.randn(3, 17, 80)
+    y = cpu_native.linear(x, w, bias)
+    y.backward(dy)
+    xr, wr, br = (t.detach().clone().requires_grad_() for t in (x, w, bias))
+    yr = ref.linear(xr, wr, br)
+    yr.backward(dy)
+    for g, r in ((y, yr), (x.grad, xr.grad), (w.grad, wr.grad), (bias.grad, br.grad)):
+        assert torch.allclose(g, r, rtol=1e-4, atol=1e-3)
+    xn, wn = torch.randn(37, 100), torch.randn(100)
+    assert torch.allclose(cpu_native.rmsnorm(xn, wn, 1e-6), ref.rmsnorm(xn, wn, 1e-6), rtol=1e-4, atol=1e-5)
