@@ -59,6 +59,13 @@ class TensorParallel:
             self.ar2_state = torch.zeros(4, device=self.device, dtype=torch.int32)   # [0] epoch, [1..3] counters
             self._ar2 = None
             self.ar2_calls = 0
+            # in-switch (NVLS multimem) form of the same all-reduce: used when the arena is bound to
+            # an NVLink multicast object and BRAIN_TP_NVLS=1; own flags and epoch word
+            import os
+            self.nvls = os.environ.get("BRAIN_TP_NVLS") == "1" and self.arena.multicast_ptr(self.sig) != 0
+            self.mm_sig = self.arena.alloc(self.world, torch.int64)
+            self.mm_sig_ptrs = self._U64(*self.arena.peer_ptrs(self.mm_sig))
+            self.mm_state = torch.zeros(4, device=self.device, dtype=torch.int32)
 
     # ------------------------------------------------------------------ symmetric slots
     def _slot(self, kind: str, numel: int, dtype, parity: int) -> torch.Tensor:
@@ -141,6 +148,12 @@ class TensorParallel:
         which = self.ar2_calls & 1
         self.ar2_calls += 1
         xc = x.contiguous()
+        if self.nvls:
+            # the switch sums the ranks' staging buffers and writes the result into every rank's buffer
+            call("tp_allreduce_mm", st["stage"], ctypes.c_void_p(self.arena.multicast_ptr(st["stage"])),
+                 ctypes.c_void_p(self.arena.multicast_ptr(st["res"][which])), self.mm_sig_ptrs, xc, L(n), self.rank,
+                 self.world, self.mm_state, self.mm_state[1:], ctypes.c_double(self.wait_seconds), stream_ptr())
+            return st["res"][which][:n].view(x.shape)
         call("tp_allreduce2", st["stage_ptrs"], st["res_ptrs"][which], self.ar2_sig_ptrs, xc, L(n), self.rank,
              self.world, self.ar2_state, self.ar2_state[1:], ctypes.c_double(self.wait_seconds), stream_ptr())
         return st["res"][which][:n].view(x.shape)

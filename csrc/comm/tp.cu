@@ -231,6 +231,96 @@ __global__ void __launch_bounds__(256) tp_allreduce2_kernel(const Ar2Args a) {
   }
 }
 
+// In-switch variant of the two-shot all-reduce (NVLS): the staging and result buffers are bound to
+// NVLink multicast addresses, so phase 2 is ONE multimem.ld_reduce per 16 bytes (the switch adds the
+// world's copies in fp32 and returns the sum) and ONE multimem.st (the switch writes the result into
+// every rank's buffer).  Each value crosses this GPU's links once in each direction whatever the
+// world size, and every rank receives bit-identical sums.  Flags and epoch handling are those of
+// tp_allreduce2_kernel; the flag exchange itself stays on plain peer stores.
+struct ArMmArgs {
+  PeerPtrs sig;
+  __nv_bfloat16* stage_local;   // this rank's staging buffer (unicast address)
+  const void* stage_mc;         // multicast address of the staging buffers
+  void* result_mc;              // multicast address of the result buffers
+  const __nv_bfloat16* x;
+  long n;
+  int rank, world;
+  unsigned int* epoch_dev;
+  unsigned int* counters;
+  long long wait_limit;
+  int* err;
+};
+
+__global__ void __launch_bounds__(256) tp_allreduce_mm_kernel(const ArMmArgs a) {
+  __shared__ unsigned int s_e;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_e = *reinterpret_cast<volatile unsigned int*>(a.epoch_dev) + 1u;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const unsigned int e = s_e;
+  const long nv = a.n >> 3;
+  const long stride = (long)gridDim.x * blockDim.x;
+  const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  bf16x8* mine = reinterpret_cast<bf16x8*>(a.stage_local);
+  for (long i = tid; i < nv; i += stride) mine[i] = reinterpret_cast<const bf16x8*>(a.x)[i];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(a.counters, 1u) == gridDim.x - 1) {
+      a.counters[0] = 0u;
+      for (int r = 0; r < a.world; ++r)
+        st_release_sys_u64(reinterpret_cast<uint64_t*>(a.sig.p[r]) + a.rank, (uint64_t)(2u * e - 1u));
+    }
+  }
+  if (threadIdx.x < a.world) {
+    const uint64_t* f = reinterpret_cast<const uint64_t*>(a.sig.p[a.rank]) + threadIdx.x;
+    if (!wait_epoch(f, 2u * e - 1u, 0, a.wait_limit)) {
+      set_error(a.err, ERR_WAIT_PEER);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  if (s_ok) {
+    const long per = nv / a.world;  // host guarantees divisibility
+    const long lo = (long)a.rank * per;
+    const uint4* src = reinterpret_cast<const uint4*>(a.stage_mc) + lo;
+    uint4* dst = reinterpret_cast<uint4*>(a.result_mc) + lo;
+    for (long j = tid; j < per; j += stride) {
+      uint32_t r0, r1, r2, r3;
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                   : "l"(src + j)
+                   : "memory");
+      asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "r"(r0),
+                   "r"(r1), "r"(r2), "r"(r3)
+                   : "memory");
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(a.counters + 1, 1u) == gridDim.x - 1) {
+      a.counters[1] = 0u;
+      for (int r = 0; r < a.world; ++r)
+        st_release_sys_u64(reinterpret_cast<uint64_t*>(a.sig.p[r]) + a.rank, (uint64_t)(2u * e));
+    }
+  }
+  if (threadIdx.x < a.world && s_ok) {
+    const uint64_t* f = reinterpret_cast<const uint64_t*>(a.sig.p[a.rank]) + threadIdx.x;
+    if (!wait_epoch(f, 2u * e, 0, a.wait_limit)) set_error(a.err, ERR_WAIT_PEER);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(a.counters + 2, 1u) == gridDim.x - 1) {
+      a.counters[2] = 0u;
+      *reinterpret_cast<volatile unsigned int*>(a.epoch_dev) = e;
+      __threadfence();
+    }
+  }
+}
+
 // All ranks meet: publish `epoch` to every peer, then wait (bounded) until every peer published it.
 // Orders "my earlier kernels' writes to symmetric memory" before "peers' later reads" without NCCL.
 __global__ void symm_barrier_kernel(PeerPtrs sig, int rank, int world, uint32_t epoch,
@@ -335,5 +425,36 @@ BB_API int bb_tp_allreduce2(const uint64_t* stage_ptrs, const uint64_t* result_p
     case 8: tp_allreduce2_kernel<8><<<(int)blocks, 256, 0, s>>>(a); break;
     default: tp_allreduce2_kernel<0><<<(int)blocks, 256, 0, s>>>(a); break;
   }
+  return (int)cudaGetLastError();
+}
+
+// NVLS form of bb_tp_allreduce2: `stage_local` is this rank's staging buffer, `stage_mc` /
+// `result_mc` the multicast addresses of the symmetric staging and result buffers (the arena must be
+// bound to an NVLink multicast object).  Same state words and epoch rules as bb_tp_allreduce2; the
+// two must not share signal words.
+BB_API int bb_tp_allreduce_mm(void* stage_local, const void* stage_mc, void* result_mc,
+                              const uint64_t* sig_ptrs, const void* x, long n, int rank, int world,
+                              unsigned int* epoch_dev, unsigned int* counters, double wait_seconds,
+                              void* stream) {
+  using namespace bb;
+  if (world < 2 || world > MAX_RANKS || n <= 0 || n % (8L * world)) return BB_EARG;
+  if (!stage_mc || !result_mc) return BB_EARG;
+  ArMmArgs a{};
+  for (int r = 0; r < world; ++r) a.sig.p[r] = reinterpret_cast<void*>(sig_ptrs[r]);
+  a.stage_local = static_cast<__nv_bfloat16*>(stage_local);
+  a.stage_mc = stage_mc;
+  a.result_mc = result_mc;
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.n = n;
+  a.rank = rank;
+  a.world = world;
+  a.epoch_dev = epoch_dev;
+  a.counters = counters;
+  a.wait_limit = (long long)(wait_seconds * 1.9e9);
+  a.err = device_error_word();
+  long blocks = ((n >> 3) + 255) / 256;
+  if (blocks > sm_count()) blocks = sm_count();  // every block waits on peers: keep them co-resident
+  if (blocks < 1) blocks = 1;
+  tp_allreduce_mm_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }

@@ -605,269 +605,6 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   }
 }
 
-// Third form (default): the whole 128-key block in ONE score tile.  A tcgen05.mma with M = 128, K = 16
-// takes about 68 clocks for any N <= 128, so the two 64-key units of the second form ran the S = QK^T
-// MMAs at half the tensor rate.  Here S(j) is one N = 128 MMA group (8 instructions), P(j) overwrites
-// the first 64 columns of the score tile as packed bf16, and PV(j) is 8 TS instructions.  The score
-// tile is single-buffered inside a CTA; the second CTA on the SM keeps the tensor pipe busy while
-// this one's softmax warps work (TMEM: S [0,128), O [128, 128+HD): 256 columns, two CTAs per SM).
-// The softmax makes two passes over the tile (row maximum, then exponentials) so that no thread
-// ever holds more than 32 scores in registers.
-template <int HD>
-__global__ void __launch_bounds__(192, 2)
-fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-               const __grid_constant__ CUtensorMap tmV, const FaFwdArgs args) {
-  using Cfg = FaFwdCfg<HD>;
-  constexpr int NSUB = Cfg::NSUB;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~uintptr_t(1023));
-  uint8_t* sQ = smem + Cfg::OFF_Q;
-  uint8_t* sK = smem + Cfg::OFF_K;
-  uint8_t* sV = smem + Cfg::OFF_V;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
-  uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;
-  uint64_t* k_empty = bars + 2;
-  uint64_t* v_full = bars + 3;
-  uint64_t* v_empty = bars + 4;
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_ready = bars + 6;   // 128 arrivals
-  uint64_t* pv_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int T = args.T, S = args.S;
-  const int q0 = qt * 128;
-  const int kvh = h / (args.hq / args.hk);
-  const int off = S - T;
-  int n_blocks = (S + 127) / 128;
-  if (args.causal) {
-    const int last = (q0 + 127 + off) / 128 + 1;
-    n_blocks = last < n_blocks ? last : n_blocks;
-  }
-
-  if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(k_full, 1);
-    mbar_init(k_empty, 1);
-    mbar_init(v_full, 1);
-    mbar_init(v_empty, 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, 128);
-    mbar_init(pv_done, 1);
-    mbar_fence_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_O = tmem_base + 128;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      mbar_expect_tx(q_full, Cfg::TILE_BYTES);
-#pragma unroll
-      for (int c = 0; c < NSUB; ++c)
-        tma_load_2d(sQ + c * Cfg::SUB_BYTES, &tmQ, q_full, h * HD + c * 64, b * T + q0);
-      for (int j = 0; j < n_blocks; ++j) {
-        const uint32_t ph = j & 1;
-        if (!mbar_wait(k_empty, ph ^ 1)) {
-          set_error(args.err, ERR_WAIT_PRODUCER);
-          break;
-        }
-        mbar_expect_tx(k_full, Cfg::TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < NSUB; ++c)
-          tma_load_2d(sK + c * Cfg::SUB_BYTES, &tmK, k_full, kvh * HD + c * 64, b * S + j * 128);
-        if (!mbar_wait(v_empty, ph ^ 1)) {
-          set_error(args.err, ERR_WAIT_PRODUCER);
-          break;
-        }
-        mbar_expect_tx(v_full, Cfg::TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < NSUB; ++c)
-          tma_load_2d(sV + c * Cfg::SUB_BYTES, &tmV, v_full, kvh * HD + c * 64, b * S + j * 128);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = umma_idesc(1, 1, 1, 0, 0, 128, 128);
-      constexpr uint32_t idesc_pv = umma_idesc(1, 1, 1, 0, 1, 128, HD);
-      const uint32_t aq = smem_u32(sQ), bk = smem_u32(sK), bv = smem_u32(sV);
-      bool ok = mbar_wait(q_full, 0);
-      if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        const uint32_t ph = j & 1;
-        if (!mbar_wait(k_full, ph)) {
-          set_error(args.err, ERR_WAIT_MMA_FULL);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        // S(j) = Q K(j)^T.  In issue order it follows PV(j-1), which read P(j-1) from these columns.
-#pragma unroll
-        for (int t = 0; t < HD / 16; ++t) {
-          const uint32_t o = (t / 4) * Cfg::SUB_BYTES + (t % 4) * 32;
-          umma_f16_ss(tmem_base, umma_smem_desc(aq + o, 16, 1024), umma_smem_desc(bk + o, 16, 1024),
-                      idesc_qk, t != 0);
-        }
-        umma_commit(s_full);
-        umma_commit(k_empty);
-        if (!mbar_wait(p_ready, ph) || !mbar_wait(v_full, ph)) {
-          set_error(args.err, ERR_WAIT_MMA_TMEM);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        // O += P(j) V(j): A = packed bf16 P in TMEM (8 columns per 16-key step), B = V MN-major
-#pragma unroll
-        for (int t = 0; t < 8; ++t)
-          umma_f16_ts(tmem_O, tmem_base + t * 8, umma_smem_desc(bv + t * 2048, Cfg::SUB_BYTES, 1024),
-                      idesc_pv, (j | t) != 0);
-        umma_commit(pv_done);
-        umma_commit(v_empty);
-      }
-    }
-  } else {
-    // ------------------------------------------------------------ softmax + epilogue
-    const int sw = warp & 3;
-    const int row = sw * 32 + lane;
-    const int q_idx = q0 + row;
-    const uint32_t lane_sel = (uint32_t)(sw * 32) << 16;
-    const int kv_limit_row = args.causal ? min(q_idx + off, S - 1) : S - 1;
-    const uint32_t tO = tmem_O + lane_sel;
-    const uint32_t tS = tmem_base + lane_sel;
-    const float sc = args.scale_log2;
-    float m_ref = -INFINITY, l = 0.f;
-    bool ok = true;
-    for (int j = 0; j < n_blocks; ++j) {
-      ok = mbar_wait(s_full, j & 1);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const int kv0 = j * 128;
-      const bool need_mask = (kv0 + 127 > kv_limit_row);
-      const int lim = kv_limit_row - kv0;  // columns <= lim are visible
-      // ---- pass 1: row maximum over the 128 scores
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld32(tS + c * 32, r);
-        tmem_wait_ld();
-        if (!need_mask) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i <= lim) mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
-      }
-      mx *= sc;
-      float m_new = m_ref;
-      if (mx > m_ref + 8.f) m_new = mx;  // lazy: keep the old reference while p stays <= 2^8
-      const float alpha =
-          (m_new == m_ref) ? 1.f : ((m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new));
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        // O changes scale: every PV issued so far must have landed first
-        ok = mbar_wait(pv_done, (j - 1) & 1);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tO + c * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st32(tO + c * 32, r);
-        }
-      }
-      l *= alpha;
-      m_ref = m_new;
-      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-      // ---- pass 2: exponentials; the packed P of chunk c lands in columns [16c, 16c + 16), always
-      // behind the columns still to be read
-      float ls = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32], pk[16];
-        __syncwarp();
-        tmem_ld32(tS + c * 32, r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float a0 = exp2f(__uint_as_float(r[i]) * sc - m_use);
-          float a1 = exp2f(__uint_as_float(r[i + 1]) * sc - m_use);
-          if (need_mask) {
-            if (c * 32 + i > lim) a0 = 0.f;
-            if (c * 32 + i + 1 > lim) a1 = 0.f;
-          }
-          ls += a0 + a1;
-          pk[i >> 1] = pack_bf16x2_alu(a0, a1);
-        }
-        tmem_st16(tS + c * 16, pk);
-      }
-      l += ls;
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(p_ready);
-    }
-    if (ok && n_blocks > 0) {
-      ok = mbar_wait(pv_done, (n_blocks - 1) & 1);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (!ok) {
-      if (lane == 0) set_error(args.err, ERR_WAIT_SOFTMAX);
-    } else {
-      tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = args.O + (size_t)(b * T + q_idx) * args.ldo + h * HD;
-#pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld32(tO + c * 32, r);
-        tmem_wait_ld();
-        if (q_idx < T) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(r[q * 8 + 0]) * inv, __uint_as_float(r[q * 8 + 1]) * inv);
-            o.y = pack_bf16x2(__uint_as_float(r[q * 8 + 2]) * inv, __uint_as_float(r[q * 8 + 3]) * inv);
-            o.z = pack_bf16x2(__uint_as_float(r[q * 8 + 4]) * inv, __uint_as_float(r[q * 8 + 5]) * inv);
-            o.w = pack_bf16x2(__uint_as_float(r[q * 8 + 6]) * inv, __uint_as_float(r[q * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = o;
-          }
-        }
-      }
-      if (args.lse && q_idx < T)
-        args.lse[((size_t)b * args.hq + h) * T + q_idx] =
-            (l > 0.f) ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
-  }
-}
-
 template <int HD>
 static int launch_fa_fwd(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
                          const FaFwdArgs& a, cudaStream_t stream) {
@@ -882,26 +619,23 @@ static int launch_fa_fwd(const void* q, int ldq, const void* k, int ldk, const v
   rc = make_tmap_2d(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, (uint64_t)a.hk * HD,
                     (uint64_t)a.B * a.S, (uint64_t)ldv * 2, 64, 128);
   if (rc) return rc;
-  static PerDeviceOnce once1, once2, once3;
+  static PerDeviceOnce once1, once2;
   {
     cudaError_t e = ensure_dyn_smem(once1, fa_fwd_kernel<HD>, Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
     e = ensure_dyn_smem(once2, fa_fwd2_kernel<HD>, Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
-    e = ensure_dyn_smem(once3, fa_fwd3_kernel<HD>, Cfg::SMEM);
-    if (e != cudaSuccess) return (int)e;
   }
   dim3 grid((a.T + 127) / 128, a.hq, a.B);
-  // the 128-wide form is the default; BB_FA_FWD=2 selects the two-unit form (478 -> 309 us at B4
-  // T4096 16q/8kv hd128 over the first), BB_FA_FWD=1 the first form, which also carries the
-  // timeline stamps
+  // the two-unit form is the default (478 -> 309 us at B4 T4096 16q/8kv hd128); BB_FA_FWD=1 selects
+  // the first form, which also carries the timeline stamps.  (A third form with one 128-key score
+  // tile per block, single-buffered, measured 380 us: with two CTAs per SM the idle tensor time
+  // during a CTA's softmax was not filled by its neighbour.)
   static const int form = [] {
     const char* e = getenv("BB_FA_FWD");
-    return (e && e[0] == '1') ? 1 : ((e && e[0] == '2') ? 2 : 3);
+    return (e && e[0] == '1') ? 1 : 2;
   }();
-  if (form == 3 && a.timeline == nullptr)
-    fa_fwd3_kernel<HD><<<grid, 192, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, a);
-  else if (form == 2 && a.timeline == nullptr)
+  if (form == 2 && a.timeline == nullptr)
     fa_fwd2_kernel<HD><<<grid, 192, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, a);
   else
     fa_fwd_kernel<HD><<<grid, 192, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, a);

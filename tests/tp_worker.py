@@ -60,6 +60,18 @@ def main():
         ok = ok and e < 1e-2
         msgs.append(("ar", it, e))
     _cuda.check_error()
+    if fused.nvls:
+        # BRAIN_TP_NVLS=1 and a multicast binding: the calls above went through the switch; every
+        # rank must hold the SAME bits (one sum per slice, written to all ranks by the switch)
+        t = (torch.randn(64, 2048, device=dev) * (rank + 1)).bfloat16()
+        a = fused.all_reduce(t).clone()
+        ref0 = a.clone()
+        dist.broadcast(ref0, 0)
+        same = bool((ref0 == a).all().item())
+        ok = ok and same
+        msgs.append(("nvls_bit_identical", same))
+    else:
+        msgs.append(("nvls", "off"))
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
