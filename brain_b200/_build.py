@@ -27,6 +27,9 @@ NVCC_FLAGS = [
     "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
     "--expt-relaxed-constexpr", "-Xptxas", "-v",
 ]
+#: translation units whose arithmetic feeds the optimiser state or the loss: compiled without
+#: --use_fast_math (IEEE division and square root in the AdamW update, exact exp/log in the CE)
+EXACT_MATH = {"adamw.cu", "rs_adamw.cu", "ce.cu"}
 CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread", "-march=x86-64-v3"]
 
 
@@ -75,7 +78,10 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     def compile_one(so):
         s, o = so
         extra = ["-DBB_TIMELINE"] if os.environ.get("BB_TIMELINE") == "1" else []
-        _run([nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(s), "-o", str(o)],
+        flags = NVCC_FLAGS
+        if s.name in EXACT_MATH:
+            flags = [f for f in NVCC_FLAGS if f != "--use_fast_math"]
+        _run([nvcc, *flags, *extra, "-I", str(CSRC), "-c", str(s), "-o", str(o)],
              log=o.with_suffix(".log"))
         if verbose:
             print(f"[build] {s.relative_to(ROOT)}")

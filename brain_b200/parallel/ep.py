@@ -4,10 +4,12 @@ runs their grouped tcgen05 GEMMs over the rows that ALL ranks route to them.
 The all-to-all dispatch and combine are not separate collectives: the row movement is the MoE
 kernels' own NVLink peer loads.  Per layer and direction:
 
-  dispatch   the expert owner's gather kernel pulls the routed token rows straight out of every
-             source rank's symmetric activation buffer into its expert-sorted, 128-row-padded
-             operand buffer (the grouped GEMM then TMA-loads it locally — a remote row crosses
-             NVLink once);
+  dispatch   inside the grouped expert GEMM: mover CTAs of that kernel pull the routed token rows
+             straight out of every source rank's symmetric activation buffer into the expert-sorted,
+             128-row-padded operand buffer and publish a flag per 128-row tile; the kernel's TMA
+             producer waits for a tile's flag, so the GEMM of the first experts runs while the rows of
+             the last ones still cross NVLink (a remote row crosses once).  ``BRAIN_EP_FUSED_DISPATCH=0``
+             runs the gather as its own kernel before the GEMM;
   combine    the token owner's combine kernel pulls each of its tokens' top-k expert outputs from
              the owners' symmetric output buffers and applies the routing weights while summing.
 
@@ -50,6 +52,11 @@ class ExpertParallel:
             self.sig = self.arena.alloc(self.world, torch.int64)
             self._U64 = ctypes.c_uint64 * self.world
             self.sig_ptrs = self._U64(*self.arena.peer_ptrs(self.sig))
+            # dispatch fused into the grouped GEMM: per-tile "rows are in place" flags and their epoch
+            import os
+            self.fused_dispatch = os.environ.get("BRAIN_EP_FUSED_DISPATCH", "1") == "1"
+            self.row_flags = torch.zeros(1 << 16, device=self.device, dtype=torch.int32)
+            self.gemm_epoch = 0
 
     # ------------------------------------------------------------------ helpers
     def _slot(self, kind, numel, dtype, parity):
@@ -68,6 +75,22 @@ class ExpertParallel:
 
     def _ptrs(self, t):
         return self._U64(*self.arena.peer_ptrs(t))
+
+    def dispatch_gemm(self, src, n_per_rank, pair_of_pos, pair_w, k, xp, b_stacked, tile_group, b_group_rows,
+                      n_out, b_mn=False):
+        """One launch: mover CTAs pull the routed rows of every rank's ``src`` (symmetric) into the
+        expert-sorted buffer ``xp`` tile by tile while the remaining CTAs run the grouped GEMM over
+        the tiles that are already in place.  Returns C [rows, n_out] (zero where a tile is unused)."""
+        from ..ops._cuda import call, stream_ptr
+        rows, K = xp.shape
+        assert rows // 128 <= self.row_flags.numel()
+        out = torch.zeros(rows, n_out, device=xp.device, dtype=torch.bfloat16)
+        self.gemm_epoch += 1
+        call("gemm_bf16_grouped_ep", xp, b_stacked, out, rows, n_out, K, b_stacked.stride(0), out.stride(0),
+             int(b_mn), tile_group, int(b_group_rows), int(b_stacked.shape[0]), self._ptrs(src), self.world,
+             int(n_per_rank), pair_of_pos, pair_w, int(k), self.row_flags, ctypes.c_uint(self.gemm_epoch), 24,
+             ctypes.c_double(self.wait_seconds), stream_ptr())
+        return out
 
     def _gather_meta(self, t):
         out = torch.empty(self.world * t.shape[0], *t.shape[1:], device=t.device, dtype=t.dtype)
@@ -184,8 +207,11 @@ class _ExpertsEP(torch.autograd.Function):
         xs.copy_(x)
         ep._barrier()                                       # every rank's x and pos table are in place
         xp = torch.empty(max_rows, d, device=dev, dtype=x.dtype)
-        call("moe_gather", ep._ptrs(xs), W, n, pair_of_pos, None, k, xp, offsets, El, d, max_rows, s)
-        gu = grouped_gemm_rows(xp, w_gate_up.view(El * ff2, d), tile_group, ff2, ff2)
+        if ep.fused_dispatch:
+            gu = ep.dispatch_gemm(xs, n, pair_of_pos, None, k, xp, w_gate_up.view(El * ff2, d), tile_group, ff2, ff2)
+        else:
+            call("moe_gather", ep._ptrs(xs), W, n, pair_of_pos, None, k, xp, offsets, El, d, max_rows, s)
+            gu = grouped_gemm_rows(xp, w_gate_up.view(El * ff2, d), tile_group, ff2, ff2)
         h = torch.empty(max_rows, ff, device=dev, dtype=x.dtype)
         call("swiglu_fwd", gu, h, L(max_rows), ff, s)
         yp = ep._slot("yp", max_rows * d, x.dtype, par).view(max_rows, d)
@@ -227,9 +253,13 @@ class _ExpertsEP(torch.autograd.Function):
         call("moe_rowdot", dys, ep._ptrs(yps), ep._ptrs(pos_tab), W, idx, L(ep.rank * n * k), k, El,
              d_w, L(n * k), d, s)
         dyp = torch.empty(max_rows, d, device=dev, dtype=dy.dtype)
-        call("moe_gather", ep._ptrs(dys), W, n, pair_of_pos, w_all.reshape(-1), k, dyp, offsets, El, d,
-             max_rows, s)
-        dh = grouped_gemm_rows(dyp, w_down.view(El * d, ff), tile_group, d, ff, b_mn=True)
+        if ep.fused_dispatch:
+            dh = ep.dispatch_gemm(dys, n, pair_of_pos, w_all.reshape(-1), k, dyp, w_down.view(El * d, ff), tile_group,
+                                  d, ff, b_mn=True)
+        else:
+            call("moe_gather", ep._ptrs(dys), W, n, pair_of_pos, w_all.reshape(-1), k, dyp, offsets, El, d,
+                 max_rows, s)
+            dh = grouped_gemm_rows(dyp, w_down.view(El * d, ff), tile_group, d, ff, b_mn=True)
         dgu = torch.empty_like(gu)
         call("swiglu_bwd", dh, gu, dgu, L(max_rows), ff, s)
         dxp = ep._slot("dxp", max_rows * d, dy.dtype, par).view(max_rows, d)

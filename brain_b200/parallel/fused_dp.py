@@ -115,7 +115,7 @@ class BucketTracker:
 
 class FusedDP:
     def __init__(self, dp, store, opt, wait_seconds: float = None, wire: str = None,
-                 bucket_mb: float = None, overlap_ctas: int = 32):
+                 bucket_mb: float = None, overlap_ctas: int = None):
         self.dp, self.store, self.opt = dp, store, opt
         self.world, self.rank = dp.world, dp.rank
         dev = store.device
@@ -169,7 +169,7 @@ class FusedDP:
                  if s.role != Role.FROZEN and s.name in store.params]
         self.tracker = BucketTracker(self.buckets, slots)
         self.seq = 0
-        self.overlap_ctas = overlap_ctas
+        self.overlap_ctas = int(os.environ.get("BRAIN_DP_CTAS", "32")) if overlap_ctas is None else overlap_ctas
         self.side = torch.cuda.Stream(device=dev)
         self._armed = False
         self.overlapped = 0          # buckets launched under backward in the last step (for reports)

@@ -60,13 +60,13 @@ def run_perf(argv: List[str], device: str = "auto") -> int:
         print("workloads: " + " ".join(standard_names()))
         print("targets:   fake | qwen-synth:LxDxH[xV] | weights:FILE | http:URL|KEY|MODEL")
         print("arrivals:  --concurrency N (closed loop) | --saturated | --rate R [--burstiness K]")
-        print("tools:     brain perf tool {kernels|launches|comm|serve-micro|mixed-ab|configs|fa-timeline} [args]")
+        print("tools:     brain perf tool {kernels|launches|comm|serve-micro|mixed-ab|configs|fa-timeline|mma-probe} [args]")
         return 0
     if sub == "tool":
         # measurement tools that are not workloads: each is a module with its own argument parser
         tools = {"kernels": "kernel_bench", "launches": "launch_list", "comm": "comm_bench",
                  "serve-micro": "serve_micro", "mixed-ab": "mixed_ab", "configs": "configs",
-                 "fa-timeline": "fa_timeline"}
+                 "fa-timeline": "fa_timeline", "mma-probe": "mma_probe"}
         name = argv[1] if len(argv) > 1 else None
         if name not in tools:
             print("tools: " + " ".join(sorted(tools)), file=sys.stderr)

@@ -89,12 +89,31 @@ def elementwise_suite(a, dev, bw):
     w16 = torch.zeros(n, device=dev, dtype=bf)
     coef = torch.ones(1, device=dev)
     rec("adamw", lambda: call("adamw", ms, m_, v_, g, w16, L(n), 1e-4, 0.9, 0.999, 1e-8, 0.1, 3, coef, stream_ptr()), n * 30)
+    del m_, v_, ms, g, w16
+    # router softmax + top-8 over 128 experts (fp32 logits in, probabilities + ids + weights out)
+    E, kk = 128, 8
+    ntok = rows * 8
+    lg = torch.randn(ntok, E, device=dev)
+    probs, lse = torch.empty_like(lg), torch.empty(ntok, device=dev)
+    idx = torch.empty(ntok, kk, device=dev, dtype=torch.int32)
+    tw = torch.empty(ntok, kk, device=dev)
+    cnt = torch.zeros(E, device=dev, dtype=torch.int32)
+    rec("router_topk(128 experts, top-8)", lambda: call("router_topk", lg, probs, lse, idx, tw, cnt, ntok, E, kk, 1, 1.0,
+                                                        stream_ptr()), ntok * (2 * E * 4 + kk * 8 + 4))
+    # masked cross-entropy over a vocabulary chunk: reads the bf16 logits, writes their gradient in place
+    V, crows = 151936, 2048
+    logits = torch.randn(crows, V, device=dev).bfloat16()
+    tgt = torch.randint(0, V, (crows,), device=dev, dtype=torch.int32)
+    lrows = torch.empty(crows, device=dev)
+    rec("cross_entropy(+grad in place)", lambda: call("cross_entropy", logits, L(logits.stride(0)), tgt, lrows, None, crows, V,
+                                                     1, None, 1.0 / crows, stream_ptr()), 2 * crows * V * 2)
     return res
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "flash", "i8", "copy", "elementwise", "decode"])
+    ap.add_argument("what", choices=["gemm", "flash", "i8", "copy", "elementwise", "decode", "grouped"])
+    ap.add_argument("--experts", type=int, default=16, help="grouped: experts (rows are split evenly)")
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
@@ -165,6 +184,18 @@ def main(argv=None):
             A, B, C = sets[0]
             tl = timeit([lambda: torch.matmul(A, B.t(), out=C)], a.iters, a.warmup)
             out["library_tflops"] = fl / tl / 1e12
+    elif a.what == "grouped":
+        # row-grouped expert GEMM: expert-sorted rows, one launch for all experts (gate/up shape of an MoE layer)
+        from brain_b200.ops.moe_cuda import grouped_gemm_rows
+        G, M, N, K = a.experts, a.m, a.n, a.k
+        assert M % (128 * G) == 0
+        x = torch.randn(M, K, device=dev).bfloat16()
+        w = torch.randn(G * N, K, device=dev).bfloat16()
+        tile_group = torch.arange(M // 128, device=dev, dtype=torch.int32) // (M // 128 // G)
+        out_ = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        t = timeit([lambda: grouped_gemm_rows(x, w, tile_group, N, N, out=out_)], a.iters, a.warmup)
+        fl = 2.0 * M * N * K
+        out.update(M=M, N=N, K=K, experts=G, seconds=t, tflops=fl / t / 1e12, frac_of_peak=fl / t / pf)
     elif a.what == "decode":
         # split-KV paged decode attention: every K and V row of every sequence is read once
         from brain_b200.ops._cuda import call, stream_ptr

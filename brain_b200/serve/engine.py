@@ -375,8 +375,12 @@ class QwenEngine:
         if self.native is not None:
             return self._native_prefill(tok, pos, slots, [(0, n, start, bt)])
 
+        paged = self._paged_prefill_meta([(0, n, start, bt)], n) if self._paged_prefill_ok() else None
+
         def attn(li, q, k, v):
             self._append_kv(li, k, v, slots)
+            if paged is not None:
+                return self._paged_prefill_attention(li, q, torch.empty(n, hq * hd, device=q.device, dtype=q.dtype), paged)
             if start == 0:
                 return flash_attention(q, k, v, 1, n, hq, hk, hd, causal=True)
             kk, vv = self._gather_kv(li, bt, S)
@@ -388,6 +392,37 @@ class QwenEngine:
             x, delta = self._layer(li, x, delta, pos, attn)
         self.steps += 1
         return x, delta
+
+    # ------------------------------------------------------------------ paged flash prefill
+    def _paged_prefill_ok(self) -> bool:
+        return (self.cuda and not self.kv_int8 and self.block_size in (16, 32, 64, 128) and self.hd in (64, 128)
+                and os.environ.get("BRAIN_SERVE_PAGED_PREFILL", "1") == "1")
+
+    def _paged_prefill_meta(self, seqs, n):
+        """Device tables for ONE attention launch over all sequences of a packed prefill: ``seqs`` is
+        (row offset, rows, start, block table) per sequence with contiguous row ranges."""
+        dev = self.device
+        row0 = np.array([o for o, _, _, _ in seqs] + [n], dtype=np.int32)
+        ctx = np.array([st + l for _, l, st, _ in seqs], dtype=np.int32)
+        tiles = [(i, qt) for i, (_, l, _, _) in enumerate(seqs) for qt in range(-(-l // 128))]
+        # tiles that see the most keys first, so the tail of the launch is short tiles
+        tiles.sort(key=lambda t: -(int(ctx[t[0]]) - seqs[t[0]][1] + min(seqs[t[0]][1], (t[1] + 1) * 128)))
+        meta = np.concatenate([row0, ctx, np.array([t[0] for t in tiles], dtype=np.int32),
+                               np.array([t[1] for t in tiles], dtype=np.int32)])
+        m = torch.from_numpy(meta).to(dev)
+        ns, nt = len(seqs), len(tiles)
+        tables = torch.stack([bt.to(torch.int32) for _, _, _, bt in seqs]).contiguous()
+        return dict(row0=m[:ns + 1], ctx=m[ns + 1:2 * ns + 1], tile_seq=m[2 * ns + 1:2 * ns + 1 + nt],
+                    tile_qt=m[2 * ns + 1 + nt:], n_tiles=nt, tables=tables, rows=n)
+
+    def _paged_prefill_attention(self, li, q, out, meta):
+        """out[rows] = causal attention of the packed query rows against the paged pool of layer
+        ``li`` (the rows' own K/V were appended before): one launch, keys read through the block tables."""
+        call("flash_fwd_paged", q, q.stride(0), self.kc[li], self.vc[li], out, out.stride(0), meta["tables"],
+             int(meta["tables"].shape[1]), self.block_size, int(self.kc[li].shape[0]), meta["row0"], meta["ctx"],
+             meta["tile_seq"], meta["tile_qt"], meta["n_tiles"], meta["rows"], self.hq, self.hk, self.hd,
+             float(self.hd ** -0.5), stream_ptr())
+        return out
 
     def _native_prefill(self, tok, pos, slots, seqs, dec=None):
         """Packed rows through the native layer halves; ``seqs``: (row offset, rows, start, block
@@ -401,9 +436,13 @@ class QwenEngine:
         nat.begin(sc, tok.to(torch.int32), n)
         qw = hq * hd
         lse = torch.empty(hq * max([l for _, l, _, _ in seqs] or [1]), device=self.device, dtype=torch.float32)
+        n_prompt = sum(l for _, l, _, _ in seqs)
+        paged = self._paged_prefill_meta(seqs, n_prompt) if (seqs and self._paged_prefill_ok()) else None
         for li in range(len(self.layers)):
             nat.pre_attn(sc, li, pos, slots, n)
-            for o, l, start, bt in seqs:
+            if paged is not None:
+                self._paged_prefill_attention(li, sc.qk[:n_prompt, :qw], sc.o[:n_prompt], paged)
+            for o, l, start, bt in (seqs if paged is None else ()):
                 q = sc.qk[o:o + l, :qw]
                 out = sc.o[o:o + l]
                 if start == 0:
@@ -486,8 +525,15 @@ class QwenEngine:
                                                               zip(items, bts, lens, offs[:-1].tolist())])
             return self._prefill_batch_results(items, offs, x, delta, n, t0)
 
+        paged = None
+        if self._paged_prefill_ok():
+            paged = self._paged_prefill_meta([(o, l, it[1], bt) for it, bt, l, o in
+                                              zip(items, bts, lens, offs[:-1].tolist())], n)
+
         def attn(li, q, k, v):
             self._append_kv(li, k, v, slots)
+            if paged is not None:
+                return self._paged_prefill_attention(li, q, torch.empty(n, hq * hd, device=q.device, dtype=q.dtype), paged)
             outs = []
             for (t_, start, _, _, _), bt, l, o in zip(items, bts, lens, offs[:-1].tolist()):
                 qs = q[o:o + l]

@@ -366,8 +366,10 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < 32; i += 2) {
           const uint32_t w = pk[c * 16 + (i >> 1)];
           const float p0 = __uint_as_float(w << 16), p1 = __uint_as_float(w & 0xFFFF0000u);
-          pk[c * 16 + (i >> 1)] = pack_bf16x2_alu(p0 * fmaf(__uint_as_float(rp[i]), args.scale, dlt),
-                                              p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, dlt));
+          // phase 2 has no exponentials, so the conversion unit is free: cvt packs here while the
+          // integer pipe (which phase 1 packs on) only unpacks
+          pk[c * 16 + (i >> 1)] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[i]), args.scale, dlt),
+                                          p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, dlt));
         }
       }
       tmem_st32(tS, pk);
@@ -716,10 +718,10 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           const uint32_t w0 = pk[c * 16 + (i >> 1)], w1 = pk[c * 16 + (i >> 1) + 1];
           const float p0 = __uint_as_float(w0 << 16), p1 = __uint_as_float(w0 & 0xFFFF0000u);
           const float p2 = __uint_as_float(w1 << 16), p3 = __uint_as_float(w1 & 0xFFFF0000u);
-          pk[c * 16 + (i >> 1)] = pack_bf16x2_alu(p0 * fmaf(__uint_as_float(rp[i]), args.scale, d.x),
-                                              p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, d.y));
-          pk[c * 16 + (i >> 1) + 1] = pack_bf16x2_alu(p2 * fmaf(__uint_as_float(rp[i + 2]), args.scale, d.z),
-                                                  p3 * fmaf(__uint_as_float(rp[i + 3]), args.scale, d.w));
+          pk[c * 16 + (i >> 1)] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[i]), args.scale, d.x),
+                                          p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, d.y));
+          pk[c * 16 + (i >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(rp[i + 2]), args.scale, d.z),
+                                              p3 * fmaf(__uint_as_float(rp[i + 3]), args.scale, d.w));
         }
       }
       tmem_st32(tD, pk);

@@ -32,6 +32,14 @@ struct FaFwdArgs {
   int causal;
   int* err;
   long long* timeline;  // optional [n_blocks][8] clock64 stamps of CTA (0,0,0) (profiling aid)
+  // Paged, variable-length form (serving prefill): sequences are packed along the rows of Q / O,
+  // keys and values are read straight from the paged KV pool through the block table.
+  const int* block_tables;   // [n_seq][max_blocks] physical block of every logical block
+  const int* seq_row0;       // [n_seq + 1] first packed row of every sequence
+  const int* seq_ctx;        // [n_seq] context length (cached prefix + new rows)
+  const int* tile_seq;       // [gridDim.x] sequence of every query tile
+  const int* tile_qt;        // [gridDim.x] tile index inside its sequence
+  int max_blocks, block_rows;  // pool block = block_rows token rows per KV head
 };
 
 template <int HD>
@@ -73,7 +81,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  long long* tl = (args.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? args.timeline : nullptr;
+  // stamps exist only in profiling builds (-DBB_TIMELINE); otherwise a compile-time null
+#ifdef BB_TIMELINE
+  long long* const tl = (args.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? args.timeline : nullptr;
+#else
+  long long* const tl = nullptr;
+#endif
   const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
   const int h = blockIdx.y, b = blockIdx.z;
   const int T = args.T, S = args.S;
@@ -339,7 +352,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 // share columns), which left the tensor pipe idle two thirds of the time (ncu: 31 % active).
 // TMEM: S0 [0,64) S1 [64,128) fp32 scores, P(u) packed bf16 over the first 32 columns of its
 // buffer, O [128, 128+HD).  Same shared-memory footprint, still two CTAs per SM.
-template <int HD>
+// PAGED: one CTA per (query tile of a packed sequence, query head); K/V tiles are assembled from
+// the pool's blocks (one TMA copy per block and 64-column half) instead of one copy per tile.
+template <int HD, bool PAGED>
 __global__ void __launch_bounds__(192, 2)
 fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const FaFwdArgs args) {
@@ -363,9 +378,12 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
+  const int seq = PAGED ? args.tile_seq[blockIdx.x] : 0;
+  const int qt = PAGED ? args.tile_qt[blockIdx.x] : (int)(gridDim.x - 1 - blockIdx.x);  // heavy (late) tiles first
   const int h = blockIdx.y, b = blockIdx.z;
-  const int T = args.T, S = args.S;
+  const int row_base = PAGED ? args.seq_row0[seq] : b * args.T;   // first packed row of this sequence
+  const int T = PAGED ? args.seq_row0[seq + 1] - row_base : args.T;
+  const int S = PAGED ? args.seq_ctx[seq] : args.S;
   const int q0 = qt * 128;
   const int kvh = h / (args.hq / args.hk);
   const int off = S - T;
@@ -407,7 +425,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_expect_tx(q_full, Cfg::TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < NSUB; ++c)
-        tma_load_2d(sQ + c * Cfg::SUB_BYTES, &tmQ, q_full, h * HD + c * 64, b * T + q0);
+        tma_load_2d(sQ + c * Cfg::SUB_BYTES, &tmQ, q_full, h * HD + c * 64, row_base + q0);
       for (int j = 0; j < n_blocks; ++j) {
         const uint32_t ph = j & 1;
         if (!mbar_wait(k_empty, ph ^ 1)) {
@@ -415,17 +433,42 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           break;
         }
         mbar_expect_tx(k_full, Cfg::TILE_BYTES);
+        if (PAGED) {
+          // pool layout [blocks][kv heads][block_rows][HD]: block i of this tile lands at row i*block_rows
+          const int br = args.block_rows, per_tile = 128 / br;
+          const int* tab = args.block_tables + (size_t)seq * args.max_blocks + j * per_tile;
+          for (int i = 0; i < per_tile; ++i) {
+            const bool live = (j * 128 + i * br) < S && (j * per_tile + i) < args.max_blocks;
+            const int blk = live ? max(tab[i], 0) : 0;   // dead blocks are masked by the key limit
+            for (int c = 0; c < NSUB; ++c)
+              tma_load_2d(sK + c * Cfg::SUB_BYTES + i * br * 128, &tmK, k_full, c * 64,
+                          (blk * args.hk + kvh) * br);
+          }
+        } else {
 #pragma unroll
-        for (int c = 0; c < NSUB; ++c)
-          tma_load_2d(sK + c * Cfg::SUB_BYTES, &tmK, k_full, kvh * HD + c * 64, b * S + j * 128);
+          for (int c = 0; c < NSUB; ++c)
+            tma_load_2d(sK + c * Cfg::SUB_BYTES, &tmK, k_full, kvh * HD + c * 64, b * S + j * 128);
+        }
         if (!mbar_wait(v_empty, ph ^ 1)) {
           set_error(args.err, ERR_WAIT_PRODUCER);
           break;
         }
         mbar_expect_tx(v_full, Cfg::TILE_BYTES);
+        if (PAGED) {
+          const int br = args.block_rows, per_tile = 128 / br;
+          const int* tab = args.block_tables + (size_t)seq * args.max_blocks + j * per_tile;
+          for (int i = 0; i < per_tile; ++i) {
+            const bool live = (j * 128 + i * br) < S && (j * per_tile + i) < args.max_blocks;
+            const int blk = live ? max(tab[i], 0) : 0;
+            for (int c = 0; c < NSUB; ++c)
+              tma_load_2d(sV + c * Cfg::SUB_BYTES + i * br * 128, &tmV, v_full, c * 64,
+                          (blk * args.hk + kvh) * br);
+          }
+        } else {
 #pragma unroll
-        for (int c = 0; c < NSUB; ++c)
-          tma_load_2d(sV + c * Cfg::SUB_BYTES, &tmV, v_full, kvh * HD + c * 64, b * S + j * 128);
+          for (int c = 0; c < NSUB; ++c)
+            tma_load_2d(sV + c * Cfg::SUB_BYTES, &tmV, v_full, kvh * HD + c * 64, b * S + j * 128);
+        }
       }
     }
   } else if (warp == 1) {
@@ -572,7 +615,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     } else {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = args.O + (size_t)(b * T + q_idx) * args.ldo + h * HD;
+      __nv_bfloat16* orow = args.O + (size_t)(row_base + q_idx) * args.ldo + h * HD;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t r[32];
@@ -591,7 +634,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
         }
       }
-      if (args.lse && q_idx < T)
+      if (!PAGED && args.lse && q_idx < T)
         args.lse[((size_t)b * args.hq + h) * T + q_idx] =
             (l > 0.f) ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
     }
@@ -623,7 +666,7 @@ static int launch_fa_fwd(const void* q, int ldq, const void* k, int ldk, const v
   {
     cudaError_t e = ensure_dyn_smem(once1, fa_fwd_kernel<HD>, Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
-    e = ensure_dyn_smem(once2, fa_fwd2_kernel<HD>, Cfg::SMEM);
+    e = ensure_dyn_smem(once2, fa_fwd2_kernel<HD, false>, Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid((a.T + 127) / 128, a.hq, a.B);
@@ -636,7 +679,7 @@ static int launch_fa_fwd(const void* q, int ldq, const void* k, int ldk, const v
     return (e && e[0] == '1') ? 1 : 2;
   }();
   if (form == 2 && a.timeline == nullptr)
-    fa_fwd2_kernel<HD><<<grid, 192, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, a);
+    fa_fwd2_kernel<HD, false><<<grid, 192, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, a);
   else
     fa_fwd_kernel<HD><<<grid, 192, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, a);
   return (int)cudaGetLastError();
@@ -649,6 +692,62 @@ BB_API int bb_flash_fwd_timeline(const void*, int, const void*, int, const void*
 
 // q: [B*T, ldq] (head h at columns h*hd), k/v: [B*S, ldk/ldv]; out: [B*T, ldo]; lse: [B, hq, T].
 // Requires ldo % 8 == 0 and 16-byte aligned bases.  hd in {64, 128}.
+// Causal attention of packed, variable-length query rows against a PAGED KV pool (serving prefill
+// and mixed steps): sequence s owns rows [seq_row0[s], seq_row0[s+1]) of q / out, its context is the
+// first seq_ctx[s] token rows named by block_tables[s][:] (the new rows' K/V are already in the pool),
+// and query row i of the sequence sees keys [0, seq_ctx[s] - T_s + i].  One launch for all sequences;
+// no gather of the cached prefix into a contiguous buffer.  tile_seq / tile_qt list the 128-row query
+// tiles (host-built).  Pools: bf16 [pool_blocks][hk][block_rows][hd], block_rows in {16, 32, 64, 128}.
+BB_API int bb_flash_fwd_paged(const void* q, int ldq, const void* k_pool, const void* v_pool, void* out,
+                              int ldo, const int* block_tables, int max_blocks, int block_rows,
+                              int pool_blocks, const int* seq_row0, const int* seq_ctx,
+                              const int* tile_seq, const int* tile_qt, int n_tiles, int total_rows, int hq,
+                              int hk, int hd, float scale, void* stream) {
+  using namespace bb;
+  if (n_tiles <= 0) return BB_OK;
+  if (hq % hk || total_rows <= 0 || max_blocks <= 0 || pool_blocks <= 0) return BB_EARG;
+  if (block_rows != 16 && block_rows != 32 && block_rows != 64 && block_rows != 128) return BB_EARG;
+  if (hd != 128 && hd != 64) return BB_EARG;
+  FaFwdArgs a{};
+  a.O = static_cast<__nv_bfloat16*>(out);
+  a.ldo = ldo;
+  a.hq = hq;
+  a.hk = hk;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.causal = 1;
+  a.err = device_error_word();
+  a.block_tables = block_tables;
+  a.seq_row0 = seq_row0;
+  a.seq_ctx = seq_ctx;
+  a.tile_seq = tile_seq;
+  a.tile_qt = tile_qt;
+  a.max_blocks = max_blocks;
+  a.block_rows = block_rows;
+  CUtensorMap tmQ, tmK, tmV;
+  const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  int rc = make_tmap_2d(&tmQ, bf, 2, q, (uint64_t)hq * hd, (uint64_t)total_rows, (uint64_t)ldq * 2, 64, 128);
+  if (rc) return rc;
+  const uint64_t pool_rows = (uint64_t)pool_blocks * hk * block_rows;
+  rc = make_tmap_2d(&tmK, bf, 2, k_pool, (uint64_t)hd, pool_rows, (uint64_t)hd * 2, 64, block_rows);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmV, bf, 2, v_pool, (uint64_t)hd, pool_rows, (uint64_t)hd * 2, 64, block_rows);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  dim3 grid(n_tiles, hq, 1);
+  if (hd == 128) {
+    static PerDeviceOnce once;
+    cudaError_t e = ensure_dyn_smem(once, fa_fwd2_kernel<128, true>, FaFwdCfg<128>::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    fa_fwd2_kernel<128, true><<<grid, 192, FaFwdCfg<128>::SMEM, s>>>(tmQ, tmK, tmV, a);
+  } else {
+    static PerDeviceOnce once;
+    cudaError_t e = ensure_dyn_smem(once, fa_fwd2_kernel<64, true>, FaFwdCfg<64>::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    fa_fwd2_kernel<64, true><<<grid, 192, FaFwdCfg<64>::SMEM, s>>>(tmQ, tmK, tmV, a);
+  }
+  return (int)cudaGetLastError();
+}
+
 BB_API int bb_flash_fwd(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
                         void* out, int ldo, float* lse, int B, int T, int S, int hq, int hk, int hd,
                         float scale, int causal, void* stream) {
@@ -656,7 +755,7 @@ BB_API int bb_flash_fwd(const void* q, int ldq, const void* k, int ldk, const vo
                                causal, nullptr, stream);
 }
 
-// Same, with an optional device buffer of (T/128) x 8 clock64 stamps filled by the CTA of the last
+// Same, with (in builds made with -DBB_TIMELINE only) an optional device buffer of (T/128) x 8 clock64 stamps filled by the CTA of the last
 // query tile of head 0 / batch 0: per KV block [0] scores ready, [1] row in registers, [2] max
 // done, [3] O rescaled, [4] exponentials done, [5] P stored + signalled, [6] PV issued, [7] QK issued.
 BB_API int bb_flash_fwd_timeline(const void* q, int ldq, const void* k, int ldk, const void* v,

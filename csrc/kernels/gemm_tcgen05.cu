@@ -72,7 +72,25 @@ struct GemmArgs {
   const CUtensorMap* tp_cmaps;
   unsigned int* tp_counter;
   long long tp_wait_limit;
+  //  mode 3 "expert dispatch -> grouped GEMM" (row-grouped GEMMs only): the mover CTAs fill the
+  //         expert-sorted operand buffer (tp_full, [M, K]) tile by tile with the token rows routed to
+  //         this rank's experts, pulled from every rank's symmetric activation buffer (tp_src) by the
+  //         dispatch table ep_pair_of_pos (pair = token * ep_k + slot, token = rank * ep_n_per_rank +
+  //         local; < 0 = padding row, zero-filled), optionally scaled by the pair's routing weight.
+  //         A tile's flag is published when its 128 rows are in place and the GEMM side waits per
+  //         tile, so the all-to-all runs under the expert GEMM instead of in front of it.
+  const int* ep_pair_of_pos;
+  const float* ep_w;
+  int ep_n_per_rank, ep_k;
 };
+
+// Per-tile clock64 stamps exist only in profiling builds (-DBB_TIMELINE): in production the stamp
+// pointer is a compile-time null, so the kernels carry no clock reads.
+#ifdef BB_TIMELINE
+#define GEMM_TL(expr) (expr)
+#else
+#define GEMM_TL(expr) (static_cast<long long*>(nullptr))
+#endif
 
 static constexpr int BM = 128;
 static constexpr int TILE_K_BYTES = 128;  // one swizzle row
@@ -186,11 +204,48 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     return nkb > 0;
   };
-  const int n_copy = args.tp_mode == 1 ? args.tp_copy_ctas : 0;
+  const bool gated = args.tp_mode == 1 || args.tp_mode == 3;  // A tiles arrive through mover CTAs
+  const int n_copy = gated ? args.tp_copy_ctas : 0;
   const int cta0 = (int)blockIdx.x - n_copy;
   const int cta_stride = (int)gridDim.x - n_copy;
 
-  if (cta0 < 0) {
+  if (cta0 < 0 && args.tp_mode == 3) {
+    // ---------------------------------------------------------- expert-dispatch data movers
+    const size_t row_vecs = (size_t)K * 2 / 16;  // 16-byte vectors per row
+    for (int tmr = blockIdx.x; tmr < tiles_m; tmr += n_copy) {
+      if (args.tile_group[tmr] < 0) continue;    // unused tile: the GEMM side skips it too
+      for (int r = warp; r < BM; r += 8) {
+        const int pos = tmr * BM + r;
+        const int pair = pos < M ? args.ep_pair_of_pos[pos] : -1;
+        uint4* dst = reinterpret_cast<uint4*>(args.tp_full) + (size_t)pos * row_vecs;
+        if (pos >= M) continue;
+        if (pair < 0) {
+          for (size_t v = lane; v < row_vecs; v += 32) dst[v] = make_uint4(0u, 0u, 0u, 0u);
+          continue;
+        }
+        const int token = pair / args.ep_k;
+        const int src_rank = token / args.ep_n_per_rank;
+        const int local = token - src_rank * args.ep_n_per_rank;
+        const uint4* src = reinterpret_cast<const uint4*>(args.tp_src.p[src_rank]) + (size_t)local * row_vecs;
+        if (args.ep_w) {
+          const float g = args.ep_w[pair];
+          for (size_t v = lane; v < row_vecs; v += 32) {
+            uint4 x = ld_volatile_u4(src + v);
+            uint32_t* w32 = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              w32[q] = pack_bf16x2(__uint_as_float(w32[q] << 16) * g, __uint_as_float(w32[q] & 0xFFFF0000u) * g);
+            dst[v] = x;
+          }
+        } else {
+          for (size_t v = lane; v < row_vecs; v += 32) dst[v] = ld_volatile_u4(src + v);
+        }
+      }
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) st_release_gpu_s32(args.tp_row_flags + tmr, (int)args.tp_epoch);
+    }
+  } else if (cta0 < 0) {
     // ---------------------------------------------------------- all-gather data movers
     __shared__ int s_ok;
     const int per_rank = args.rows_per_rank / BM;
@@ -241,7 +296,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (!tile_info(t, tm, tn, grp, kb0, nkb)) continue;
         const int m0 = tm * BM, n0 = tn * BN;
         const int b_off = args.group_mode == 1 ? grp * args.b_group_rows : 0;
-        if (args.tp_mode == 1) {
+        if (gated) {
           if (!wait_flag_ge(args.tp_row_flags + tm, (int)args.tp_epoch, args.tp_wait_limit)) {
             set_error(args.err, ERR_WAIT_PEER);
             ok = false;
@@ -307,7 +362,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         ++it;
-        long long* tl = (args.timeline && blockIdx.x == 0 && it <= 16) ? args.timeline + (it - 1) * 16 : nullptr;
+        long long* const tl = GEMM_TL((args.timeline && blockIdx.x == 0 && it <= 16) ? args.timeline + (it - 1) * 16 : nullptr);
         if (tl) tl[0] = clock64();
         long long waited = 0;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
@@ -362,7 +417,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       ++it;
-      long long* tl = (args.timeline && blockIdx.x == 0 && it <= 16 && threadIdx.x == 128) ? args.timeline + (it - 1) * 16 : nullptr;
+      long long* const tl = GEMM_TL((args.timeline && blockIdx.x == 0 && it <= 16 && threadIdx.x == 128) ? args.timeline + (it - 1) * 16 : nullptr);
       if (tl) tl[4] = clock64();
       bool ok = mbar_wait(&tmem_full[acc], acc_phase);
       ok = __all_sync(0xffffffffu, ok);
@@ -633,11 +688,15 @@ static int launch_gemm(const void* A, const void* B, const GemmArgs& args, int l
 
 }  // namespace bb
 
+#ifdef BB_TIMELINE
 static long long* g_gemm_timeline = nullptr;
 // Profiling aid: when set, CTA 0 of the next bf16 GEMMs writes per-tile clock64 stamps
 // ([0] tile start, [1] first TMA wait, [2] cycles waiting on TMA, [3] MMAs issued, [4] epilogue
 // waits, [5] accumulator ready, [6] accumulator released) for its first 16 tiles.
 BB_API void bb_gemm_set_timeline(long long* buf) { g_gemm_timeline = buf; }
+#else
+static long long* const g_gemm_timeline = nullptr;
+#endif
 
 // CTA-pair kernel (gemm_2cta.cu)
 BB_API int bb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, int lda,
@@ -791,6 +850,55 @@ BB_API int bb_gemm_bf16_grouped(const void* A, const void* B, void* C, int M, in
     case 128: return launch_gemm<128, false>(A, Bp, a, lda, ldb, s, 0, b_total_rows);
     case 64: return launch_gemm<64, false>(A, Bp, a, lda, ldb, s, 0, b_total_rows);
     default: return BB_EARG;
+  }
+}
+
+// Expert-parallel dispatch fused into the row-grouped GEMM (tp_mode 3 of the kernel): `xp` [M, K] is
+// the local expert-sorted operand buffer that the kernel's mover CTAs fill from `src_ptrs[r]` (every
+// rank's [n_per_rank, K] activations, symmetric memory) by `pair_of_pos` (int32 [M], -1 = padding),
+// scaled by `w[pair]` when given; the GEMM side consumes each 128-row tile as soon as it is in place.
+// `row_flags`: persistent int32 [>= M/128], compared against the increasing `epoch`.  The caller
+// orders "every rank's activations are written" before this launch (a symmetric barrier).
+BB_API int bb_gemm_bf16_grouped_ep(void* xp, const void* B, void* C, int M, int N, int K, int ldb, int ldc,
+                                   int b_mn, const int* tile_group, int b_group_rows, int b_total_rows,
+                                   const uint64_t* src_ptrs, int world, int n_per_rank,
+                                   const int* pair_of_pos, const float* w, int k, int* row_flags,
+                                   unsigned int epoch, int copy_ctas, double wait_seconds, void* stream) {
+  using namespace bb;
+  if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > MAX_RANKS || M % BM || K % 8) return BB_EARG;
+  GemmArgs a{};
+  a.C = C;
+  a.alpha = 1.f;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.ldc = ldc;
+  a.b_mn = b_mn;
+  a.out_mode = 0;
+  a.group_mode = 1;
+  a.tile_group = tile_group;
+  a.b_group_rows = b_group_rows;
+  a.err = device_error_word();
+  a.tp_mode = 3;
+  a.tp_world = world;
+  for (int r = 0; r < world; ++r) a.tp_src.p[r] = reinterpret_cast<void*>(src_ptrs[r]);
+  a.tp_full = xp;
+  a.tp_row_flags = row_flags;
+  a.tp_epoch = epoch;
+  a.tp_wait_limit = (long long)(wait_seconds * 1.9e9);
+  a.tp_copy_ctas = copy_ctas > 0 ? copy_ctas : 24;
+  if (a.tp_copy_ctas > sm_count() / 2) a.tp_copy_ctas = sm_count() / 2;
+  a.ep_pair_of_pos = pair_of_pos;
+  a.ep_w = w;
+  a.ep_n_per_rank = n_per_rank;
+  a.ep_k = k;
+  const int bn = (N >= 256) ? 256 : (N >= 128 ? 128 : 64);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int force_grid = sm_count();  // movers and consumers must be co-resident
+  switch (bn) {
+    case 256: return launch_gemm<256, false>(xp, B, a, K, ldb, s, 0, b_total_rows, force_grid);
+    case 128: return launch_gemm<128, false>(xp, B, a, K, ldb, s, 0, b_total_rows, force_grid);
+    default: return launch_gemm<64, false>(xp, B, a, K, ldb, s, 0, b_total_rows, force_grid);
   }
 }
 

@@ -132,3 +132,51 @@ def test_attention_from_fused_qkv(B, T, hq, hk, hd, norm):
     assert rel_err(dx1.cpu()[:, qkw:], dx0[:, qkw:]) < 3e-2
     if norm:
         assert rel_err(dq1.cpu(), dq0) < 5e-2 and rel_err(dk1.cpu(), dk0) < 5e-2
+
+
+@pytest.mark.parametrize("hd,block_rows", [(128, 16), (64, 32)])
+def test_paged_varlen_flash_forward(hd, block_rows):
+    """One launch over packed sequences of different lengths whose keys and values live in a paged
+    pool (shuffled blocks, cached prefixes of different lengths) against plain attention per sequence."""
+    import math
+    from brain_b200.ops import _cuda, reference as ref
+    from brain_b200.ops._cuda import call, stream_ptr
+    torch.manual_seed(7)
+    hq, hk = 4, 2
+    seqs = [(0, 200), (48, 130), (300, 17), (16, 256)]            # (cached prefix, new rows)
+    max_blocks = 40
+    pool_blocks = 160
+    kc = torch.randn(pool_blocks, hk, block_rows, hd, device="cuda").bfloat16()
+    vc = torch.randn(pool_blocks, hk, block_rows, hd, device="cuda").bfloat16()
+    perm = torch.randperm(pool_blocks).tolist()
+    tables, row0, ctx, tiles, qs, wants = [], [0], [], [], [], []
+    used = 0
+    for si, (start, new) in enumerate(seqs):
+        S = start + new
+        nb = -(-S // block_rows)
+        blocks = perm[used:used + nb]
+        used += nb
+        tables.append(blocks + [-1] * (max_blocks - nb))
+        k = torch.cat([kc[b] for b in blocks], dim=1)[:, :S]      # [hk, S, hd]
+        v = torch.cat([vc[b] for b in blocks], dim=1)[:, :S]
+        q = torch.randn(new, hq * hd, device="cuda").bfloat16()
+        qs.append(q)
+        w = ref.attention(q.float().reshape(1, new, hq, hd), k.float().transpose(0, 1).reshape(1, S, hk, hd),
+                          v.float().transpose(0, 1).reshape(1, S, hk, hd), True, 1 / math.sqrt(hd)).reshape(new, hq * hd)
+        wants.append(w)
+        row0.append(row0[-1] + new)
+        ctx.append(S)
+        tiles += [(si, t) for t in range(-(-new // 128))]
+    q = torch.cat(qs)
+    n = q.shape[0]
+    pad = torch.full((n + 2, hq * hd), 9.0, device="cuda", dtype=torch.bfloat16)   # canary rows around the output
+    out = pad[1:n + 1]
+    dev_i = lambda x: torch.tensor(x, device="cuda", dtype=torch.int32)
+    call("flash_fwd_paged", q, q.stride(0), kc, vc, out, out.stride(0), dev_i(tables), max_blocks, block_rows, pool_blocks,
+         dev_i(row0), dev_i(ctx), dev_i([t[0] for t in tiles]), dev_i([t[1] for t in tiles]), len(tiles), n, hq, hk, hd,
+         float(hd ** -0.5), stream_ptr())
+    torch.cuda.synchronize()
+    _cuda.check_error()
+    want = torch.cat(wants)
+    assert ((out.float() - want).norm() / want.norm()).item() < 2e-2
+    assert (pad[0] == 9).all() and (pad[-1] == 9).all()

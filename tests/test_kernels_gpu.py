@@ -410,3 +410,28 @@ def test_quant_and_argmax():
     small = torch.tensor([[1.0, 3.0, 3.0, -2.0, 3.0, 0.5, 0.5, 7.0]], device=dev()).bfloat16()
     i2, v2 = F.topk_rows(small, 8)
     assert i2[0].tolist() == [7, 1, 2, 4, 0, 5, 6, 3] and v2[0, 0].item() == 7.0
+
+
+def test_adamw_tracks_the_fp32_oracle_over_twenty_steps():
+    """The optimiser kernel is compiled without fast-math: 20 steps on the device stay within fp32
+    rounding of the PyTorch restatement (master weights and both moments)."""
+    from brain_b200.ops._cuda import L, call, stream_ptr
+    torch.manual_seed(11)
+    n = 1 << 16
+    p0 = torch.randn(n)
+    pm, m, v = p0.clone().cuda(), torch.zeros(n, device=dev()), torch.zeros(n, device=dev())
+    w16 = torch.empty(n, device=dev(), dtype=torch.bfloat16)
+    rp, rm, rv = p0.clone().double(), torch.zeros(n).double(), torch.zeros(n).double()
+    coef = torch.ones(1, device=dev())
+    lr, b1, b2, eps, wd = 3e-4, 0.9, 0.95, 1e-8, 0.1
+    for t in range(1, 21):
+        g = torch.randn(n) * (0.1 + 0.05 * t)
+        call("adamw", pm, m, v, g.cuda(), w16, L(n), lr, b1, b2, eps, wd, t, coef, stream_ptr())
+        gd = g.double()
+        rm = b1 * rm + (1 - b1) * gd
+        rv = b2 * rv + (1 - b2) * gd * gd
+        rp = rp - lr * ((rm / (1 - b1 ** t)) / ((rv / (1 - b2 ** t)).sqrt() + eps) + wd * rp)
+    torch.cuda.synchronize()
+    assert float((pm.cpu().double() - rp).abs().max()) < 2e-6
+    assert float((m.cpu().double() - rm).abs().max()) < 1e-6 and float((v.cpu().double() - rv).abs().max()) < 1e-6
+    assert rel_err(w16.cpu(), rp.float()) < 4e-3
