@@ -10,8 +10,8 @@
 //             dV += P^T dO, dK += dS^T Q             (TMEM accumulators)
 // Operands that are needed "transposed" are not copied: the same 128-byte-swizzled shared-memory
 // tile is described K-major for one MMA and MN-major for the other.
-// Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9 softmax
-// (two warpgroups that alternate 64-wide units so the tensor core never waits for the exponentials).
+// Roles (576 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..17 softmax
+// (four warpgroups, each owning 32 of the 128 score columns of every block).
 // Replaces crates/kernels/wgsl/gqa_bwd_{dscores,dv,dq,dk}.wgsl (which read a saved T x T probs buffer).
 #include "../common/host.hpp"
 #include "../common/ptx.cuh"
@@ -111,13 +111,13 @@ __global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ o, int ldo,
 // One CTA per (query tile, query head, batch) walks the KV blocks its rows can see.  Every MMA is
 // 128 wide (see the note on MMA cost at the dK/dV kernel).
 // TMEM (512 columns): S of even blocks at 0, dP at 128, dQ at 256, S of odd blocks at 384.
-// Softmax warpgroup g owns key columns [64g, 64g + 64) of every block; the packed bf16 dS it
-// produces replaces the first 32 of its own S columns, so k-step t of the dQ MMA reads its A operand
-// at column 64*(t/4) + 8*(t%4) of that S buffer.
+// Softmax warpgroup g (of four) owns key columns [32g, 32g + 32) of every block; the packed bf16 dS it
+// produces replaces the first 16 of its own S columns, so k-step t of the dQ MMA reads its A operand
+// at column 32*(t/2) + 8*(t%2) of that S buffer.
 // Two phases per block keep MMAs queued while the softmax warps work:
 //   phase 1  P = exp2(S*c - lse)  (registers only)   | tensor core: dQ of the block before, dP of this one
 //   phase 2  dS = P (dP*scale - delta)                | tensor core: S two blocks ahead
-// Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9 softmax.
+// Roles (576 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..17 softmax.
 template <int HD>
 struct DqCfg {
   static constexpr int NSUB = HD / 64;
@@ -133,17 +133,24 @@ struct DqCfg {
   static constexpr uint32_t TM_S0 = 0, TM_DP = 128, TM_DQ = 256, TM_S1 = 384;
 };
 
-static constexpr int BWD_THREADS = 320;
+// Four softmax warpgroups (16 warps) of 32 score columns each: with two (8 warps, 64 columns per
+// thread) no pipe was saturated (ncu: 32 % XU, 35 % ALU, 19 % FMA, 1.8 instructions per clock) and
+// only two warps per scheduler were there to hide the TMEM round trips; sixteen warps at half the
+// registers give every scheduler four.
+static constexpr int NWG = 4;
+static constexpr int WCOLS = 128 / NWG;               // score columns per warpgroup and block
+static constexpr int BWD_THREADS = 64 + 128 * NWG;    // producer warp, MMA warp, softmax warps
 
 // Named barrier over the 128 threads of softmax warpgroup g (barrier 0 is __syncthreads).
 __device__ __forceinline__ void wg_sync(int g) {
-  if (g == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
-  else asm volatile("bar.sync 2, 128;" ::: "memory");
+  asm volatile("bar.sync %0, 128;" ::"r"(g + 1) : "memory");
 }
 
-// TMEM column (relative to the operand's base) of k-step t of a packed bf16 A operand whose two
-// 64-wide halves were written by the two warpgroups into the first 32 columns of their own halves
-__device__ __forceinline__ constexpr uint32_t packed_kstep_col(int t) { return (t >> 2) * 64 + (t & 3) * 8; }
+// TMEM column (relative to the operand's base) of k-step t (16 score columns) of a packed bf16 A
+// operand: every warpgroup packs its WCOLS columns into the first WCOLS / 2 columns of its own range
+__device__ __forceinline__ constexpr uint32_t packed_kstep_col(int t) {
+  return (t / (WCOLS / 16)) * WCOLS + (t % (WCOLS / 16)) * 8;
+}
 
 template <int HD>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -197,7 +204,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&s_full[i], 1);
     }
     mbar_init(dp_full, 1);
-    mbar_init(ds_ready, 256);
+    mbar_init(ds_ready, 128 * NWG);
     mbar_init(dq_done, 1);
     mbar_fence_init();
   }
@@ -302,7 +309,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------ softmax warpgroups
-    const int g = (warp - 2) >> 2;  // owns key columns [64g, 64g + 64) of every block
+    const int g = (warp - 2) >> 2;  // owns key columns [WCOLS*g, WCOLS*g + WCOLS) of every block
     const int sw = warp & 3;
     const int row = sw * 32 + lane;
     const int q_idx = q0 + row;
@@ -312,30 +319,28 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const size_t stat = ((size_t)b * args.hq + h) * T + (row_ok ? q_idx : 0);
     const float lse2 = row_ok ? args.lse[stat] * 1.4426950408889634f : INFINITY;
     const float dlt = row_ok ? -args.delta[stat] * args.scale : 0.f;  // -delta * scale
-    const uint32_t tD = tDP + g * 64 + lane_sel;
+    const uint32_t tD = tDP + g * WCOLS + lane_sel;
+    static_assert(WCOLS == 32, "one 32-column TMEM access per phase and thread");
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
-      const uint32_t tS = tSb[j & 1] + g * 64 + lane_sel;
+      const uint32_t tS = tSb[j & 1] + g * WCOLS + lane_sel;
       // ---- phase 1: P (kept packed in registers)
-      const bool stamper = (warp & 3) == 2 && lane == 0;
+      const bool stamper = g < 2 && (warp & 3) == 2 && lane == 0;
       if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * j);
       ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * j + 1);
-      const int kvb = j * 128 + g * 64;
-      const bool need_mask = (kvb + 63 > kv_limit_row);
-      uint32_t pk[32];
-      uint32_t rs2[2][32];
-      __syncwarp();
-      tmem_ld32(tS, rs2[0]);        // both halves in flight: one TMEM round trip instead of two
-      tmem_ld32(tS + 32, rs2[1]);
-      tmem_wait_ld();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const uint32_t (&rs)[32] = rs2[c];
-        const int lim = kv_limit_row - (kvb + c * 32);
+      const int kvb = j * 128 + g * WCOLS;
+      const bool need_mask = (kvb + WCOLS - 1 > kv_limit_row);
+      const int lim = kv_limit_row - kvb;   // columns <= lim are visible
+      uint32_t pk[16];
+      {
+        uint32_t rs[32];
+        __syncwarp();
+        tmem_ld32(tS, rs);
+        tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float p0 = exp2f(__uint_as_float(rs[i]) * args.scale_log2 - lse2);
@@ -344,7 +349,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (i > lim) p0 = 0.f;
             if (i + 1 > lim) p1 = 0.f;
           }
-          pk[c * 16 + (i >> 1)] = pack_bf16x2_alu(p0, p1);
+          pk[i >> 1] = pack_bf16x2_alu(p0, p1);
         }
       }
       // ---- phase 2: dS = P * (dP * scale - delta * scale), packed over this warpgroup's S columns
@@ -354,25 +359,22 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * j + 3);
-      uint32_t rp2[2][32];
-      __syncwarp();
-      tmem_ld32(tD, rp2[0]);
-      tmem_ld32(tD + 32, rp2[1]);
-      tmem_wait_ld();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const uint32_t (&rp)[32] = rp2[c];
+      {
+        uint32_t rp[32];
+        __syncwarp();
+        tmem_ld32(tD, rp);
+        tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const uint32_t w = pk[c * 16 + (i >> 1)];
+          const uint32_t w = pk[i >> 1];
           const float p0 = __uint_as_float(w << 16), p1 = __uint_as_float(w & 0xFFFF0000u);
           // phase 2 has no exponentials, so the conversion unit is free: cvt packs here while the
           // integer pipe (which phase 1 packs on) only unpacks
-          pk[c * 16 + (i >> 1)] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[i]), args.scale, dlt),
-                                          p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, dlt));
+          pk[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[i]), args.scale, dlt),
+                                   p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, dlt));
         }
       }
-      tmem_st32(tS, pk);
+      tmem_st16(tS, pk);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(ds_ready);
@@ -385,10 +387,10 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lane == 0) set_error(args.err, ERR_WAIT_SOFTMAX);
     } else {
       tc_fence_after();
-      // warpgroup g writes columns [g*HD/2, (g+1)*HD/2) of dQ
+      // the warpgroups share the 32-column chunks of dQ round-robin
       __nv_bfloat16* orow = args.dQ + (size_t)(b * T + q_idx) * args.lddq + h * HD;
 #pragma unroll 1
-      for (int c = g * (HD / 64); c < (g + 1) * (HD / 64); ++c) {
+      for (int c = g; c < HD / 32; c += NWG) {
         uint32_t r[32];
         __syncwarp();
         if (n_blocks > 0) {
@@ -426,10 +428,10 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // K = 16 takes about 68 clocks for any N <= 128 (129 at N = 256), so narrower tiles waste the
 // tensor pipe in proportion.
 // TMEM (512 columns, all used): S^T at 0 and dP^T at 128 (128 fp32 columns each: one column per
-// query of the tile), dV at 256, dK at 384.  Softmax warpgroup g owns query columns [64g, 64g+64):
-// it replaces the first 32 of ITS OWN columns by the packed bf16 P^T (then dS^T) values, so the two
-// warpgroups never touch each other's columns and the A operand of k-step t of the dV / dK MMAs
-// sits at column 64*(t/4) + 8*(t%4).
+// query of the tile), dV at 256, dK at 384.  Softmax warpgroup g (of four) owns query columns
+// [32g, 32g+32): it replaces the first 16 of ITS OWN columns by the packed bf16 P^T (then dS^T) values,
+// so the warpgroups never touch each other's columns and the A operand of k-step t of the dV / dK
+// MMAs sits at column 32*(t/2) + 8*(t%2).
 // The work of an iteration is cut in two phases so that the tensor core always has MMAs queued:
 //   phase 1  P^T = exp2(S^T*c - lse)           -> tensor core: dV += P^T dO, then S^T of the next tile
 //   phase 2  dS^T = P^T (dP^T*scale - delta)   -> tensor core: dK += dS^T Q, then dP^T of the next tile
@@ -500,8 +502,8 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
     mbar_init(st_full, 1);
     mbar_init(dpt_full, 1);
-    mbar_init(p_ready, 256);
-    mbar_init(ds_ready, 256);
+    mbar_init(p_ready, 128 * NWG);
+    mbar_init(ds_ready, 128 * NWG);
     mbar_init(dkv_done, 1);
     mbar_fence_init();
   }
@@ -623,35 +625,37 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------ softmax warpgroups
-    const int g = (warp - 2) >> 2;    // owns query columns [64g, 64g + 64) of every tile
+    const int g = (warp - 2) >> 2;    // owns query columns [WCOLS*g, WCOLS*g + WCOLS) of every tile
     const int sw = warp & 3;
     const int row = sw * 32 + lane;   // kv row inside the tile
     const int kv_idx = kv0 + row;
     const uint32_t lane_sel = (uint32_t)(sw * 32) << 16;
     const int wt = threadIdx.x - 64 - g * 128;  // 0..127 inside the warpgroup
-    float* ls = s_stat + g * 128;               // lse2 of this warpgroup's 64 query columns
-    float* dl = ls + 64;                        // -delta * scale of the same columns
-    const uint32_t tS = tST + g * 64 + lane_sel, tD = tDPT + g * 64 + lane_sel;
-    // per-query statistic this thread stages for iteration i: threads 0..63 of the warpgroup carry
-    // lse (in log2 units), threads 64..127 carry -delta * scale (one FMA per element in phase 2)
+    float* ls = s_stat + g * (2 * WCOLS);       // lse2 of this warpgroup's query columns
+    float* dl = ls + WCOLS;                     // -delta * scale of the same columns
+    const uint32_t tS = tST + g * WCOLS + lane_sel, tD = tDPT + g * WCOLS + lane_sel;
+    static_assert(WCOLS == 32, "one 32-column TMEM access per phase and thread");
+    // per-query statistic this thread stages for iteration i: threads 0..31 of the warpgroup carry
+    // lse (in log2 units), threads 32..63 carry -delta * scale (one FMA per element in phase 2)
     auto load_stat = [&](int i) -> float {
+      if (wt >= 2 * WCOLS) return 0.f;
       const int hh = kvh * group + i / per_head;
-      const int qi = (qt_first + i % per_head) * 128 + g * 64 + (wt & 63);
+      const int qi = (qt_first + i % per_head) * 128 + g * WCOLS + (wt & (WCOLS - 1));
       const bool qok = qi < T;
       const size_t stat = ((size_t)b * args.hq + hh) * T + (qok ? qi : 0);
-      if (wt < 64) return qok ? args.lse[stat] * 1.4426950408889634f : INFINITY;
+      if (wt < WCOLS) return qok ? args.lse[stat] * 1.4426950408889634f : INFINITY;
       return qok ? -args.delta[stat] * args.scale : 0.f;
     };
     float stat_val = n_iter > 0 ? load_stat(0) : 0.f;
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int qt = qt_first + it % per_head;
-      const int q0 = qt * 128 + g * 64;
+      const int q0 = qt * 128 + g * WCOLS;
       const uint32_t ph = it & 1;
       {
         // stage the per-query statistics; named barrier 1+g = this warpgroup's 128 threads
-        wg_sync(g);         // previous iteration's reads done
-        ls[wt] = stat_val;  // wt >= 64 lands in dl[]
+        wg_sync(g);                               // previous iteration's reads done
+        if (wt < 2 * WCOLS) ls[wt] = stat_val;    // wt >= WCOLS lands in dl[]
         wg_sync(g);
         // the next iteration's value is fetched now and lands while this iteration computes
         if (it + 1 < n_iter) stat_val = load_stat(it + 1);
@@ -659,23 +663,22 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       // column (query) c is visible from this kv row iff kv_idx <= q + off  <=>  q >= kv_idx - off
       const int q_min = args.causal ? (kv_idx - off) : -0x40000000;
       const bool need_mask = args.causal && (q0 < q_min);
+      const int first_ok = q_min - q0;  // columns i >= first_ok are visible
       // ---- phase 1: P^T
-      const bool stamper = (warp & 3) == 2 && lane == 0;
+      const bool stamper = g < 2 && (warp & 3) == 2 && lane == 0;
       if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * it);
       ok = mbar_wait(st_full, ph);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * it + 1);
-      uint32_t pk[32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      uint32_t pk[16];
+      {
         uint32_t rs[32];
         __syncwarp();
-        tmem_ld32(tS + c * 32, rs);
+        tmem_ld32(tS, rs);
         tmem_wait_ld();
-        const int first_ok = q_min - (q0 + c * 32);  // columns i >= first_ok are visible
-        const float4* ls4 = reinterpret_cast<const float4*>(ls + c * 32);
+        const float4* ls4 = reinterpret_cast<const float4*>(ls);
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 l = ls4[i >> 2];
@@ -689,12 +692,12 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             if (i + 2 < first_ok) p2 = 0.f;
             if (i + 3 < first_ok) p3 = 0.f;
           }
-          pk[c * 16 + (i >> 1)] = pack_bf16x2_alu(p0, p1);
-          pk[c * 16 + (i >> 1) + 1] = pack_bf16x2_alu(p2, p3);
+          pk[i >> 1] = pack_bf16x2_alu(p0, p1);
+          pk[(i >> 1) + 1] = pack_bf16x2_alu(p2, p3);
         }
       }
-      // all 64 S^T columns of this warpgroup are in registers: the packed P^T may overwrite them
-      tmem_st32(tS, pk);
+      // this warpgroup's S^T columns are in registers: the packed P^T may overwrite them
+      tmem_st16(tS, pk);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_ready);
@@ -705,26 +708,25 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if (!ok) break;
       tc_fence_after();
       if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * it + 3);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      {
         uint32_t rp[32];
         __syncwarp();
-        tmem_ld32(tD + c * 32, rp);
+        tmem_ld32(tD, rp);
         tmem_wait_ld();
-        const float4* dl4 = reinterpret_cast<const float4*>(dl + c * 32);
+        const float4* dl4 = reinterpret_cast<const float4*>(dl);
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 d = dl4[i >> 2];
-          const uint32_t w0 = pk[c * 16 + (i >> 1)], w1 = pk[c * 16 + (i >> 1) + 1];
+          const uint32_t w0 = pk[i >> 1], w1 = pk[(i >> 1) + 1];
           const float p0 = __uint_as_float(w0 << 16), p1 = __uint_as_float(w0 & 0xFFFF0000u);
           const float p2 = __uint_as_float(w1 << 16), p3 = __uint_as_float(w1 & 0xFFFF0000u);
-          pk[c * 16 + (i >> 1)] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[i]), args.scale, d.x),
-                                          p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, d.y));
-          pk[c * 16 + (i >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(rp[i + 2]), args.scale, d.z),
-                                              p3 * fmaf(__uint_as_float(rp[i + 3]), args.scale, d.w));
+          pk[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[i]), args.scale, d.x),
+                                   p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, d.y));
+          pk[(i >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(rp[i + 2]), args.scale, d.z),
+                                         p3 * fmaf(__uint_as_float(rp[i + 3]), args.scale, d.w));
         }
       }
-      tmem_st32(tD, pk);
+      tmem_st16(tD, pk);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(ds_ready);
@@ -737,13 +739,13 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if (lane == 0) set_error(args.err, ERR_WAIT_SOFTMAX);
     } else {
       tc_fence_after();
-      // warpgroup 0 writes dV, warpgroup 1 writes dK
+      // the lower half of the warpgroups writes dV, the upper half dK; each pair shares the chunks
       const bool row_ok = kv_idx < S;
-      const bool is_k = g == 1;
+      const bool is_k = g >= NWG / 2;
       __nv_bfloat16* drow = (is_k ? args.dK + (size_t)(b * S + kv_idx) * args.lddk
                                   : args.dV + (size_t)(b * S + kv_idx) * args.lddv) + kvh * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = g % (NWG / 2); c < HD / 32; c += NWG / 2) {
         uint32_t r[32];
         __syncwarp();
         if (n_iter > 0) {
