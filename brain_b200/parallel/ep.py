@@ -10,8 +10,12 @@ kernels' own NVLink peer loads.  Per layer and direction:
              producer waits for a tile's flag, so the GEMM of the first experts runs while the rows of
              the last ones still cross NVLink (a remote row crosses once).  ``BRAIN_EP_FUSED_DISPATCH=0``
              runs the gather as its own kernel before the GEMM;
-  combine    the token owner's combine kernel pulls each of its tokens' top-k expert outputs from
-             the owners' symmetric output buffers and applies the routing weights while summing.
+  combine    inside the down-projection's grouped GEMM: its epilogue stores every output row straight
+             into the slot of its (token, choice) pair in the token owner's symmetric slot buffer
+             (plain peer stores, tile by tile, under the GEMM of the following tiles); after one
+             barrier the owner sums its k slots per token with the routing weights, all local.
+             ``BRAIN_EP_FUSED_COMBINE=0`` keeps the expert outputs local and lets the owner's combine
+             kernel pull them over NVLink instead.
 
 Only routing metadata (top-k ids and weights, a few bytes per token) goes through
 ``torch.distributed``.  Ranks meet at bounded in-stream flag barriers (``bb_symm_barrier``) before
@@ -55,8 +59,10 @@ class ExpertParallel:
             # dispatch fused into the grouped GEMM: per-tile "rows are in place" flags and their epoch
             import os
             self.fused_dispatch = os.environ.get("BRAIN_EP_FUSED_DISPATCH", "1") == "1"
+            self.fused_combine = os.environ.get("BRAIN_EP_FUSED_COMBINE", "1") == "1"
             self.row_flags = torch.zeros(1 << 16, device=self.device, dtype=torch.int32)
             self.gemm_epoch = 0
+            self._ident = None
 
     # ------------------------------------------------------------------ helpers
     def _slot(self, kind, numel, dtype, parity):
@@ -90,6 +96,31 @@ class ExpertParallel:
              int(b_mn), tile_group, int(b_group_rows), int(b_stacked.shape[0]), self._ptrs(src), self.world,
              int(n_per_rank), pair_of_pos, pair_w, int(k), self.row_flags, ctypes.c_uint(self.gemm_epoch), 24,
              ctypes.c_double(self.wait_seconds), stream_ptr())
+        return out
+
+    def scatter_gemm(self, a, b_stacked, tile_group, b_group_rows, n_out, pair_of_pos, slots, b_mn=False):
+        """Grouped GEMM whose epilogue delivers row r to slot ``pair_of_pos[r]`` of the token owner's
+        ``slots`` buffer ([pairs_per_rank, n_out], symmetric).  Follow with a barrier."""
+        from ..ops._cuda import call, stream_ptr
+        rows, K = a.shape
+        call("gemm_bf16_grouped_scatter", a, b_stacked, rows, n_out, K, a.stride(0), b_stacked.stride(0),
+             slots.stride(0), int(b_mn), tile_group, int(b_group_rows), int(b_stacked.shape[0]), pair_of_pos,
+             self._ptrs(slots), self.world, int(slots.shape[0]), stream_ptr())
+
+    def _ensure_ident(self, n_pairs):
+        """Identity position table and all-zero expert ids: they make the combine / row-dot kernels
+        read a LOCAL per-pair buffer (rank 0 of a world of one, row = pair)."""
+        if self._ident is None or self._ident.numel() < n_pairs:
+            self._ident = torch.arange(n_pairs, device=self.device, dtype=torch.int32)
+            self._zero_idx = torch.zeros(n_pairs, device=self.device, dtype=torch.int32)
+
+    def sum_slots(self, slots, w, k, out):
+        """out[t] = sum_s (w[t, s] or 1) * slots[t * k + s]: the local half of the fused combine."""
+        from ..ops._cuda import L, call, stream_ptr
+        from ..ops.moe_cuda import _u64
+        self._ensure_ident(slots.shape[0])
+        call("moe_combine", _u64([slots.data_ptr()]), _u64([self._ident.data_ptr()]), 1, self._zero_idx, L(0), w,
+             int(k), 1, out, out.shape[0], out.shape[1], stream_ptr())
         return out
 
     def _gather_meta(self, t):
@@ -214,14 +245,23 @@ class _ExpertsEP(torch.autograd.Function):
             gu = grouped_gemm_rows(xp, w_gate_up.view(El * ff2, d), tile_group, ff2, ff2)
         h = torch.empty(max_rows, ff, device=dev, dtype=x.dtype)
         call("swiglu_fwd", gu, h, L(max_rows), ff, s)
-        yp = ep._slot("yp", max_rows * d, x.dtype, par).view(max_rows, d)
-        grouped_gemm_rows(h, w_down.view(El * d, ff), tile_group, d, d, out=yp)
-        ep._barrier()                                       # every rank's expert outputs are in place
         y = torch.empty(n, d, device=dev, dtype=x.dtype)
         wc = w.contiguous()
-        call("moe_combine", ep._ptrs(yp), ep._ptrs(pos_tab), W, idx, L(ep.rank * n * k), wc, k, El,
-             y, n, d, s)
-        yp_keep = yp.clone()   # the symmetric slot is recycled two calls later
+        if ep.fused_combine:
+            # every (token, choice) pair of mine is produced by exactly one expert row somewhere, so
+            # all n*k slots are overwritten by the GEMMs of this call: no zero fill
+            ys = ep._slot("ys", n * k * d, x.dtype, par).view(n * k, d)
+            ep.scatter_gemm(h, w_down.view(El * d, ff), tile_group, d, d, pair_of_pos, ys)
+            ep._barrier()                                   # every rank's GEMM has delivered its rows
+            ep.sum_slots(ys, wc, k, y)
+            yp_keep = ys.clone()   # per pair, not per position; the symmetric slot is recycled
+        else:
+            yp = ep._slot("yp", max_rows * d, x.dtype, par).view(max_rows, d)
+            grouped_gemm_rows(h, w_down.view(El * d, ff), tile_group, d, d, out=yp)
+            ep._barrier()                                   # every rank's expert outputs are in place
+            call("moe_combine", ep._ptrs(yp), ep._ptrs(pos_tab), W, idx, L(ep.rank * n * k), wc, k, El,
+                 y, n, d, s)
+            yp_keep = yp.clone()   # the symmetric slot is recycled two calls later
         ctx.save_for_backward(xp, gu, h, yp_keep, wc, w_all, idx, idx_all, offsets, tile_group,
                               pos_tab.clone(), pair_of_pos)
         ctx.ep, ctx.w_refs = ep, (w_gate_up, w_down)
@@ -246,12 +286,20 @@ class _ExpertsEP(torch.autograd.Function):
         dys.copy_(dy)
         pos_tab = ep._slot("pos", n_pairs_all, torch.int32, par)
         pos_tab.copy_(pos_keep)
-        yps = ep._slot("yp", max_rows * d, dy.dtype, par).view(max_rows, d)
-        yps.copy_(yp)
-        ep._barrier()
         d_w = torch.empty(n, k, device=dev, dtype=torch.float32)
-        call("moe_rowdot", dys, ep._ptrs(yps), ep._ptrs(pos_tab), W, idx, L(ep.rank * n * k), k, El,
-             d_w, L(n * k), d, s)
+        if ep.fused_combine:
+            # forward kept my pairs' expert outputs by pair: the routing-weight gradient is local
+            from ..ops.moe_cuda import _u64
+            ep._ensure_ident(n * k)
+            ep._barrier()
+            call("moe_rowdot", dys, _u64([yp.data_ptr()]), _u64([ep._ident.data_ptr()]), 1, ep._zero_idx, L(0),
+                 k, 1, d_w, L(n * k), d, s)
+        else:
+            yps = ep._slot("yp", max_rows * d, dy.dtype, par).view(max_rows, d)
+            yps.copy_(yp)
+            ep._barrier()
+            call("moe_rowdot", dys, ep._ptrs(yps), ep._ptrs(pos_tab), W, idx, L(ep.rank * n * k), k, El,
+                 d_w, L(n * k), d, s)
         dyp = torch.empty(max_rows, d, device=dev, dtype=dy.dtype)
         if ep.fused_dispatch:
             dh = ep.dispatch_gemm(dys, n, pair_of_pos, w_all.reshape(-1), k, dyp, w_down.view(El * d, ff), tile_group,
@@ -262,13 +310,19 @@ class _ExpertsEP(torch.autograd.Function):
             dh = grouped_gemm_rows(dyp, w_down.view(El * d, ff), tile_group, d, ff, b_mn=True)
         dgu = torch.empty_like(gu)
         call("swiglu_bwd", dh, gu, dgu, L(max_rows), ff, s)
-        dxp = ep._slot("dxp", max_rows * d, dy.dtype, par).view(max_rows, d)
-        dxp.zero_()
-        grouped_gemm_rows(dgu, w_gate_up.view(El * 2 * ff, d), tile_group, 2 * ff, d, b_mn=True, out=dxp)
-        ep._barrier()
         dx = torch.empty(n, d, device=dev, dtype=dy.dtype)
-        call("moe_combine", ep._ptrs(dxp), ep._ptrs(pos_tab), W, idx, L(ep.rank * n * k), None, k, El,
-             dx, n, d, s)
+        if ep.fused_combine:
+            dxs = ep._slot("dxs", n * k * d, dy.dtype, par).view(n * k, d)
+            ep.scatter_gemm(dgu, w_gate_up.view(El * 2 * ff, d), tile_group, 2 * ff, d, pair_of_pos, dxs, b_mn=True)
+            ep._barrier()
+            ep.sum_slots(dxs, None, k, dx)
+        else:
+            dxp = ep._slot("dxp", max_rows * d, dy.dtype, par).view(max_rows, d)
+            dxp.zero_()
+            grouped_gemm_rows(dgu, w_gate_up.view(El * 2 * ff, d), tile_group, 2 * ff, d, b_mn=True, out=dxp)
+            ep._barrier()
+            call("moe_combine", ep._ptrs(dxp), ep._ptrs(pos_tab), W, idx, L(ep.rank * n * k), None, k, El,
+                 dx, n, d, s)
         grads = []
         for wp, a_rows, b_rows in ((w_down, dyp, h), (w_gate_up, dgu, xp)):
             mg = getattr(wp, "main_grad", None)

@@ -137,6 +137,22 @@ struct DqCfg {
 // thread) no pipe was saturated (ncu: 32 % XU, 35 % ALU, 19 % FMA, 1.8 instructions per clock) and
 // only two warps per scheduler were there to hide the TMEM round trips; sixteen warps at half the
 // registers give every scheduler four.
+// Packing to bf16 by TRUNCATION (one PRMT per pair) instead of round-to-nearest (a conversion on the
+// unit the exponentials need, or three integer instructions): the value to be packed is first scaled
+// by (1 + 0.0029), which is free because it folds into the exponent offset (P) or into the two
+// constants of the FMA (dP*scale - delta*scale).  0.0029 is about 3/8 of a bf16 ulp relative to the
+// value, so truncation then lands within +-1/2 ulp of the exact value for most mantissas and the
+// mean error over mantissas is ~0 (truncation alone would be biased by -1/2 ulp).
+static constexpr float kTruncScale = 1.0029f;
+static constexpr float kTruncLog2 = 0.0041778f;   // log2(1.0029)
+__device__ __forceinline__ uint32_t pack_bf16x2_trunc(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
+}
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
 static constexpr int NWG = 4;
 static constexpr int WCOLS = 128 / NWG;               // score columns per warpgroup and block
 static constexpr int BWD_THREADS = 64 + 128 * NWG;    // producer warp, MMA warp, softmax warps
@@ -317,8 +333,9 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int kv_limit_row = args.causal ? min(q_idx + off, S - 1) : S - 1;
     const bool row_ok = q_idx < T;
     const size_t stat = ((size_t)b * args.hq + h) * T + (row_ok ? q_idx : 0);
-    const float lse2 = row_ok ? args.lse[stat] * 1.4426950408889634f : INFINITY;
-    const float dlt = row_ok ? -args.delta[stat] * args.scale : 0.f;  // -delta * scale
+    const float lse2 = row_ok ? args.lse[stat] * 1.4426950408889634f - kTruncLog2 : INFINITY;
+    const float scale_t = args.scale * kTruncScale;
+    const float dlt = row_ok ? -args.delta[stat] * scale_t : 0.f;  // -delta * scale
     const uint32_t tD = tDP + g * WCOLS + lane_sel;
     static_assert(WCOLS == 32, "one 32-column TMEM access per phase and thread");
     bool ok = true;
@@ -349,7 +366,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (i > lim) p0 = 0.f;
             if (i + 1 > lim) p1 = 0.f;
           }
-          pk[i >> 1] = pack_bf16x2_alu(p0, p1);
+          pk[i >> 1] = pack_bf16x2_trunc(p0, p1);
         }
       }
       // ---- phase 2: dS = P * (dP * scale - delta * scale), packed over this warpgroup's S columns
@@ -366,12 +383,11 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const uint32_t w = pk[i >> 1];
-          const float p0 = __uint_as_float(w << 16), p1 = __uint_as_float(w & 0xFFFF0000u);
-          // phase 2 has no exponentials, so the conversion unit is free: cvt packs here while the
-          // integer pipe (which phase 1 packs on) only unpacks
-          pk[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[i]), args.scale, dlt),
-                                   p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, dlt));
+          // the factor is packed by truncation (see kTruncScale) and multiplied in bf16x2: one FMA per
+          // element, one PRMT and one packed multiply per pair, nothing on the conversion unit
+          const uint32_t t = pack_bf16x2_trunc(fmaf(__uint_as_float(rp[i]), scale_t, dlt),
+                                               fmaf(__uint_as_float(rp[i + 1]), scale_t, dlt));
+          pk[i >> 1] = mul_bf16x2(pk[i >> 1], t);
         }
       }
       tmem_st16(tS, pk);
@@ -643,11 +659,12 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const int qi = (qt_first + i % per_head) * 128 + g * WCOLS + (wt & (WCOLS - 1));
       const bool qok = qi < T;
       const size_t stat = ((size_t)b * args.hq + hh) * T + (qok ? qi : 0);
-      if (wt < WCOLS) return qok ? args.lse[stat] * 1.4426950408889634f : INFINITY;
-      return qok ? -args.delta[stat] * args.scale : 0.f;
+      if (wt < WCOLS) return qok ? args.lse[stat] * 1.4426950408889634f - kTruncLog2 : INFINITY;
+      return qok ? -args.delta[stat] * (args.scale * kTruncScale) : 0.f;
     };
     float stat_val = n_iter > 0 ? load_stat(0) : 0.f;
     bool ok = true;
+    const float scale_t = args.scale * kTruncScale;
     for (int it = 0; it < n_iter; ++it) {
       const int qt = qt_first + it % per_head;
       const int q0 = qt * 128 + g * WCOLS;
@@ -692,8 +709,8 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             if (i + 2 < first_ok) p2 = 0.f;
             if (i + 3 < first_ok) p3 = 0.f;
           }
-          pk[i >> 1] = pack_bf16x2_alu(p0, p1);
-          pk[(i >> 1) + 1] = pack_bf16x2_alu(p2, p3);
+          pk[i >> 1] = pack_bf16x2_trunc(p0, p1);
+          pk[(i >> 1) + 1] = pack_bf16x2_trunc(p2, p3);
         }
       }
       // this warpgroup's S^T columns are in registers: the packed P^T may overwrite them
@@ -717,13 +734,12 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 d = dl4[i >> 2];
-          const uint32_t w0 = pk[i >> 1], w1 = pk[(i >> 1) + 1];
-          const float p0 = __uint_as_float(w0 << 16), p1 = __uint_as_float(w0 & 0xFFFF0000u);
-          const float p2 = __uint_as_float(w1 << 16), p3 = __uint_as_float(w1 & 0xFFFF0000u);
-          pk[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[i]), args.scale, d.x),
-                                   p1 * fmaf(__uint_as_float(rp[i + 1]), args.scale, d.y));
-          pk[(i >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(rp[i + 2]), args.scale, d.z),
-                                         p3 * fmaf(__uint_as_float(rp[i + 3]), args.scale, d.w));
+          const uint32_t t0 = pack_bf16x2_trunc(fmaf(__uint_as_float(rp[i]), scale_t, d.x),
+                                                fmaf(__uint_as_float(rp[i + 1]), scale_t, d.y));
+          const uint32_t t1 = pack_bf16x2_trunc(fmaf(__uint_as_float(rp[i + 2]), scale_t, d.z),
+                                                fmaf(__uint_as_float(rp[i + 3]), scale_t, d.w));
+          pk[i >> 1] = mul_bf16x2(pk[i >> 1], t0);
+          pk[(i >> 1) + 1] = mul_bf16x2(pk[(i >> 1) + 1], t1);
         }
       }
       tmem_st16(tD, pk);

@@ -82,6 +82,14 @@ struct GemmArgs {
   const int* ep_pair_of_pos;
   const float* ep_w;
   int ep_n_per_rank, ep_k;
+  // "grouped GEMM -> expert combine" (row-grouped, bf16 output): output row `row` belongs to routed
+  // pair sc_pair[row] (< 0: padding row, not stored); the epilogue stores it straight into slot
+  // (pair % sc_pairs_per_rank) of the [pairs_per_rank, ldc] slot buffer of the rank that owns the
+  // token (pair / sc_pairs_per_rank; sc_dst.p[rank], symmetric memory), so the return all-to-all is
+  // the GEMM's own stores, tile by tile, and the owner only sums its k slots per token afterwards.
+  const int* sc_pair;
+  PeerPtrs sc_dst;
+  int sc_pairs_per_rank;
 };
 
 // Per-tile clock64 stamps exist only in profiling builds (-DBB_TIMELINE): in production the stamp
@@ -525,6 +533,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (tl) tl[6] = clock64();
         continue;
       }
+      // combine epilogue: this thread's row goes to the token owner's slot buffer (or nowhere)
+      __nv_bfloat16* sc_base = nullptr;
+      bool sc_skip = false;
+      if (args.sc_pair) {
+        const int pair = row_ok ? args.sc_pair[row] : -1;
+        if (pair < 0) {
+          sc_skip = true;
+        } else {
+          const int dest = pair / args.sc_pairs_per_rank;
+          sc_base = reinterpret_cast<__nv_bfloat16*>(args.sc_dst.p[dest]) +
+                    (size_t)(pair - dest * args.sc_pairs_per_rank) * args.ldc;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -532,7 +553,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tmem_ld32(t_row + c * 32, r);
         tmem_wait_ld();
         const int col0 = n0 + c * 32;
-        if (!row_ok || col0 >= N) continue;
+        if (!row_ok || col0 >= N || sc_skip) continue;
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -551,8 +572,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
           }
-          __nv_bfloat16* crow =
-              reinterpret_cast<__nv_bfloat16*>(args.C) + c_off + (size_t)row * args.ldc + col0;
+          __nv_bfloat16* crow = sc_base ? sc_base + col0
+                                        : reinterpret_cast<__nv_bfloat16*>(args.C) + c_off +
+                                              (size_t)row * args.ldc + col0;
           if (full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
             uint4* dst = reinterpret_cast<uint4*>(crow);
 #pragma unroll
@@ -668,6 +690,7 @@ static int launch_gemm(const void* A, const void* B, const GemmArgs& args, int l
                              ces, args.C, args.N, rows, (uint64_t)args.ldc * ces, f32out ? 32 : 64, BM);
       if (rc2 == 0) largs.tma_store = 1;
     }
+    if (args.sc_pair) largs.tma_store = 0;  // rows scatter to per-row destinations: direct stores
     if (!largs.tma_store) tmC = tmA;  // unused, but the parameter must be a valid object
     // K slices add into C concurrently: only the TMA reduce-add epilogue does that atomically
     if (!largs.tma_store || args.tp_mode || args.out_mode != 2) largs.split_k = 1;
@@ -850,6 +873,44 @@ BB_API int bb_gemm_bf16_grouped(const void* A, const void* B, void* C, int M, in
     case 128: return launch_gemm<128, false>(A, Bp, a, lda, ldb, s, 0, b_total_rows);
     case 64: return launch_gemm<64, false>(A, Bp, a, lda, ldb, s, 0, b_total_rows);
     default: return BB_EARG;
+  }
+}
+
+// Row-grouped GEMM whose epilogue is the expert-parallel combine's transfer: output row r (an
+// expert-sorted position) is stored into slot pair_of_pos[r] % pairs_per_rank of rank
+// pair_of_pos[r] / pairs_per_rank's [pairs_per_rank, ldc] bf16 slot buffer (dst_ptrs[rank]; the
+// local rank's own pointer for a single GPU); rows with pair_of_pos < 0 are padding and dropped.
+// The caller orders the launch against the slot buffers' previous readers and follows it with a
+// symmetric barrier before any rank sums its slots.
+BB_API int bb_gemm_bf16_grouped_scatter(const void* A, const void* B, int M, int N, int K, int lda, int ldb,
+                                        int ldc, int b_mn, const int* tile_group, int b_group_rows,
+                                        int b_total_rows, const int* pair_of_pos, const uint64_t* dst_ptrs,
+                                        int world, int pairs_per_rank, void* stream) {
+  using namespace bb;
+  if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > MAX_RANKS || pairs_per_rank <= 0 || !pair_of_pos)
+    return BB_EARG;
+  GemmArgs a{};
+  a.C = reinterpret_cast<void*>(dst_ptrs[0]);
+  a.alpha = 1.f;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.ldc = ldc;
+  a.b_mn = b_mn;
+  a.out_mode = 0;
+  a.group_mode = 1;
+  a.tile_group = tile_group;
+  a.b_group_rows = b_group_rows;
+  a.err = device_error_word();
+  a.sc_pair = pair_of_pos;
+  for (int r = 0; r < world; ++r) a.sc_dst.p[r] = reinterpret_cast<void*>(dst_ptrs[r]);
+  a.sc_pairs_per_rank = pairs_per_rank;
+  const int bn = (N >= 256) ? 256 : (N >= 128 ? 128 : 64);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (bn) {
+    case 256: return launch_gemm<256, false>(A, B, a, lda, ldb, s, 0, b_total_rows);
+    case 128: return launch_gemm<128, false>(A, B, a, lda, ldb, s, 0, b_total_rows);
+    default: return launch_gemm<64, false>(A, B, a, lda, ldb, s, 0, b_total_rows);
   }
 }
 

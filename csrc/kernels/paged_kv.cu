@@ -246,16 +246,50 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
     cp_async_commit();
   }
 
-  float qr[G][DPL];
+  // bf16: the query slice as floats (pre-scaled).  I8: the query slice as two int8 terms per element,
+  // q ~ qs * (hi + lo / 128) with qs = absmax / 127 per head, so that a key's dot product runs on
+  // dp4a over the stored bytes (no int8 -> float conversion of K at all); 14 bits relative to the
+  // head's largest component keep more of q than its bf16 storage does for all but tiny components.
+  float qr[I8 ? 1 : G][I8 ? 1 : DPL];
+  int qhi[I8 ? G : 1][I8 ? DPL / 4 : 1], qlo[I8 ? G : 1][I8 ? DPL / 4 : 1];
+  float qs[I8 ? G : 1];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     const bf16x8* qp = reinterpret_cast<const bf16x8*>(q + (size_t)b * ldq + (head0 + g) * HD + sub * DPL);
+    float qf[DPL];
 #pragma unroll
     for (int v = 0; v < DPL / 8; ++v) {
       float f[8];
       unpack8(qp[v], f);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) qr[g][v * 8 + j] = f[j] * scale_log2;
+      for (int j = 0; j < 8; ++j) qf[v * 8 + j] = f[j];
+    }
+    if constexpr (I8) {
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) amax = fmaxf(amax, fabsf(qf[j]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+      const float inv = amax > 0.f ? 127.f / amax : 0.f;
+      qs[g] = amax * (1.f / 127.f) * scale_log2;
+#pragma unroll
+      for (int v = 0; v < DPL / 4; ++v) {
+        uint32_t hi = 0, lo = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float x = qf[v * 4 + j] * inv;
+          const int h = __float2int_rn(x);                       // |h| <= 127
+          const int r = __float2int_rn((x - (float)h) * 128.f);  // |r| <= 64
+          hi |= (uint32_t)(h & 0xff) << (8 * j);
+          lo |= (uint32_t)(r & 0xff) << (8 * j);
+        }
+        qhi[g][v] = (int)hi;
+        qlo[g][v] = (int)lo;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) qr[g][j] = qf[j] * scale_log2;
     }
   }
   float m[G], l[G], o[G][DPL];
@@ -278,12 +312,26 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
       float xf[DPL];
       float sc[G];
       const unsigned char* krow = s_k + st * STAGE + kl * ROWB + sub * DPL * ES;
+      // the 8 lanes of a group are all valid or all invalid, so they shuffle among themselves
+      const unsigned int gm = 0xffu << (grp * 8);
       if constexpr (I8) {
         const i8vec<DPL> raw = *reinterpret_cast<const i8vec<DPL>*>(krow);
+        const float kscale = s_sc[st][0][kl];
 #pragma unroll
-        for (int v = 0; v < DPL / 4; ++v)
+        for (int g = 0; g < G; ++g) {
+          int ah = 0, al = 0;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) xf[v * 4 + j] = (float)(int8_t)(raw.w[v] >> (8 * j));
+          for (int v = 0; v < DPL / 4; ++v) {
+            ah = __dp4a((int)raw.w[v], qhi[g][v], ah);
+            al = __dp4a((int)raw.w[v], qlo[g][v], al);
+          }
+          // |ah| <= 128*127*127 and |al| <= 128*127*64 per head: 128*ah + al fits an int
+          int a = ah * 128 + al;
+          a += __shfl_xor_sync(gm, a, 1);
+          a += __shfl_xor_sync(gm, a, 2);
+          a += __shfl_xor_sync(gm, a, 4);
+          sc[g] = (float)a * (qs[g] * (1.f / 128.f)) * kscale;
+        }
       } else {
 #pragma unroll
         for (int v = 0; v < DPL / 8; ++v) {
@@ -292,19 +340,16 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
 #pragma unroll
           for (int j = 0; j < 8; ++j) xf[v * 8 + j] = t[j];
         }
-      }
-      // the 8 lanes of a group are all valid or all invalid, so they shuffle among themselves
-      const unsigned int gm = 0xffu << (grp * 8);
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float a = 0.f;
+        for (int g = 0; g < G; ++g) {
+          float a = 0.f;
 #pragma unroll
-        for (int j = 0; j < DPL; ++j) a += xf[j] * qr[g][j];
-        a += __shfl_xor_sync(gm, a, 1);
-        a += __shfl_xor_sync(gm, a, 2);
-        a += __shfl_xor_sync(gm, a, 4);
-        if constexpr (I8) a *= s_sc[st][0][kl];
-        sc[g] = a;
+          for (int j = 0; j < DPL; ++j) a += xf[j] * qr[g][j];
+          a += __shfl_xor_sync(gm, a, 1);
+          a += __shfl_xor_sync(gm, a, 2);
+          a += __shfl_xor_sync(gm, a, 4);
+          sc[g] = a;
+        }
       }
       const unsigned char* vrow = s_v + st * STAGE + kl * ROWB + sub * DPL * ES;
       if constexpr (I8) {
