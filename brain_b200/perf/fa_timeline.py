@@ -52,6 +52,12 @@ def main(argv=None):
             print(name, ": no stamps")
             continue
         print(f"{name}: {len(m)} iterations stamped, {(m[-1, 0] - m[0, 0]) / (len(m) - 1):.0f} clk per iteration")
+        mm = m[2:-2]
+        if base == 0:
+            print(f"  MMA thread: issue of dQ, next dP, next S (with waits for K/V tiles) {np.mean(mm[:, 1] - mm[:, 0]):.0f} clk")
+        else:
+            print(f"  MMA thread: dV + next S^T issue {np.mean(mm[:, 1] - mm[:, 0]):.0f}, wait for dS {np.mean(mm[:, 2] - mm[:, 1]):.0f}, "
+                  f"dK + next dP^T issue {np.mean(mm[:, 3] - mm[:, 2]):.0f} clk")
         for g in (0, 1):
             w = t[base + 4096 * (1 + g): base + 4096 * (2 + g)].reshape(-1, 4)
             w = w[w[:, 0] > 0]

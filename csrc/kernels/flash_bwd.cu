@@ -19,6 +19,9 @@
 namespace bb {
 
 struct FaBwdArgs {
+  const __nv_bfloat16* q;     // [B*T, ldq]: the dQ kernel parks its tile's rows in TMEM
+  const __nv_bfloat16* dout;  // [B*T, lddo]
+  int ldq, lddo;
   const float* lse;    // [B, hq, T] natural log
   const float* delta;  // [B, hq, T]
   __nv_bfloat16* dQ;
@@ -30,6 +33,7 @@ struct FaBwdArgs {
   int causal;
   int* err;
 #ifdef BB_TIMELINE
+  int dbg;         // profiling builds: bit 0 = softmax phases skip their math, bit 1 = and their TMEM traffic
   long long* tl;  // clock64 stamps of CTA (0,0,0): dQ kernel at [0, 3*4096), dK/dV kernel after it
 #endif
 };
@@ -37,9 +41,11 @@ struct FaBwdArgs {
 // Timeline stamps exist only in builds made with -DBB_TIMELINE (a profiling build); the production
 // kernels carry no clock reads.
 #ifdef BB_TIMELINE
+#define BWD_DBG (args.dbg)
 #define BWD_TL_DECL(base) long long* tl = ((blockIdx.x | blockIdx.y | blockIdx.z) == 0 && args.tl) ? args.tl + (base) : nullptr
 #define BWD_STAMP(slot) do { if (tl && (slot) < 4096 * 3) tl[(slot)] = clock64(); } while (0)
 #else
+#define BWD_DBG 0
 #define BWD_TL_DECL(base) do { } while (0)
 #define BWD_STAMP(slot) do { } while (0)
 #endif
@@ -110,28 +116,54 @@ __global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ o, int ldo,
 // ------------------------------------------------------------------------------------ dQ
 // One CTA per (query tile, query head, batch) walks the KV blocks its rows can see.  Every MMA is
 // 128 wide (see the note on MMA cost at the dK/dV kernel).
-// TMEM (512 columns): S of even blocks at 0, dP at 128, dQ at 256, S of odd blocks at 384.
+// The tile's Q and dO rows are the A operands of every S and dP MMA of the CTA.  Read from shared
+// memory they cost 2 x 32 KB of shared-memory bandwidth per block, and with them a block's MMAs move
+// 224 KB through shared memory (operands plus the TMA writes of K and V): more than the 128 B/clock
+// an SM delivers in the time the math takes.  A timeline build with the softmax work switched off
+// measured 2229 clocks per block against 1716 of math.  So the softmax warps park both tiles in TMEM
+// once (packed bf16, HD/2 columns each) and the MMAs read them there.
+// TMEM (512 columns): S at 0, dP at 128, dQ at 256, Q at 384, dO at 384 + HD/2.
 // Softmax warpgroup g (of four) owns key columns [32g, 32g + 32) of every block; the packed bf16 dS it
-// produces replaces the first 16 of its own S columns, so k-step t of the dQ MMA reads its A operand
-// at column 32*(t/2) + 8*(t%2) of that S buffer.
-// Two phases per block keep MMAs queued while the softmax warps work:
+// produces replaces the first 16 of its own dP columns, so k-step t of the dQ MMA reads its A operand
+// at column 32*(t/2) + 8*(t%2) of the dP buffer.  S has one buffer: the softmax warps pull a block's
+// scores into registers at once and release the buffer (s_free), so S of the next block is computed
+// while they work.  Per block:
 //   phase 1  P = exp2(S*c - lse)  (registers only)   | tensor core: dQ of the block before, dP of this one
-//   phase 2  dS = P (dP*scale - delta)                | tensor core: S two blocks ahead
+//   phase 2  dS = P (dP*scale - delta)                | tensor core: S of the next block
+// MMAs execute in issue order, so "dP of the next block" may overwrite the columns dQ just read.
 // Roles (576 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..17 softmax.
 template <int HD>
 struct DqCfg {
   static constexpr int NSUB = HD / 64;
   static constexpr int TILE = NSUB * SUB;
-  static constexpr int KST = 3;                     // K stages: S runs two blocks ahead of dQ
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_DO = OFF_Q + TILE;
-  static constexpr int OFF_K = OFF_DO + TILE;
+  static constexpr int KST = 3;                     // K stages: S runs a block ahead of dQ, one in flight
+  static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + KST * TILE;  // 2 stages
   static constexpr int OFF_BAR = OFF_V + 2 * TILE;
   static constexpr int SMEM_MIN = OFF_BAR + 256 + 1024;
   static constexpr int SMEM = SMEM_MIN < 120 * 1024 ? 120 * 1024 : SMEM_MIN;
-  static constexpr uint32_t TM_S0 = 0, TM_DP = 128, TM_DQ = 256, TM_S1 = 384;
+  static constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DQ = 256, TM_Q = 384, TM_DO = 384 + HD / 2;
 };
+
+// Copy one bf16 row of HD elements from global memory into this thread's TMEM lane (packed pairs).
+template <int HD>
+__device__ __forceinline__ void row_to_tmem(const __nv_bfloat16* src, bool valid, uint32_t taddr) {
+#pragma unroll
+  for (int c = 0; c < HD / 64; ++c) {
+    uint32_t w[32];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint4 x = valid ? __ldg(reinterpret_cast<const uint4*>(src + c * 64) + i)
+                            : make_uint4(0u, 0u, 0u, 0u);
+      w[4 * i] = x.x;
+      w[4 * i + 1] = x.y;
+      w[4 * i + 2] = x.z;
+      w[4 * i + 3] = x.w;
+    }
+    tmem_st32(taddr + c * 32, w);
+  }
+  tmem_wait_st();
+}
 
 // Four softmax warpgroups (16 warps) of 32 score columns each: with two (8 warps, 64 columns per
 // thread) no pipe was saturated (ncu: 32 % XU, 35 % ALU, 19 % FMA, 1.8 instructions per clock) and
@@ -153,6 +185,13 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
+// Experiment switch: one exponential in kPolyEvery evaluated by exp2_poly on the FMA pipe instead of
+// the special-function unit.  0 = none, which is what measures fastest: with every fourth on the FMA
+// pipe the dQ iteration grew from 2812 to 2951 clocks and the dK/dV iteration from 3234 to 4454.
+#ifndef BB_FA_POLY_EVERY
+#define BB_FA_POLY_EVERY 0
+#endif
+static constexpr int kPolyEvery = BB_FA_POLY_EVERY;
 static constexpr int NWG = 4;
 static constexpr int WCOLS = 128 / NWG;               // score columns per warpgroup and block
 static constexpr int BWD_THREADS = 64 + 128 * NWG;    // producer warp, MMA warp, softmax warps
@@ -179,19 +218,18 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint8_t* sQ = smem + Cfg::OFF_Q;
-  uint8_t* sDO = smem + Cfg::OFF_DO;
   uint8_t* sK = smem + Cfg::OFF_K;
   uint8_t* sV = smem + Cfg::OFF_V;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
-  uint64_t* q_full = bars;          // Q and dO
+  uint64_t* qdo_ready = bars;       // Q and dO rows parked in TMEM (256 arrivals)
   uint64_t* k_full = bars + 1;      // KST stages
   uint64_t* k_empty = bars + 4;     // KST
   uint64_t* v_full = bars + 7;      // 2
   uint64_t* v_empty = bars + 9;     // 2
-  uint64_t* s_full = bars + 11;     // 2 (one per S buffer)
+  uint64_t* s_full = bars + 11;     // S of a block is in TMEM
+  uint64_t* s_free = bars + 12;     // ... and has been pulled into registers (128 * NWG arrivals)
   uint64_t* dp_full = bars + 13;    // 1
-  uint64_t* ds_ready = bars + 14;   // 1 (256 arrivals)
+  uint64_t* ds_ready = bars + 14;   // 1 (128 * NWG arrivals)
   uint64_t* dq_done = bars + 15;    // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
 
@@ -209,7 +247,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    mbar_init(qdo_ready, 256);
     for (int i = 0; i < KST; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
@@ -217,8 +255,9 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1);
     }
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 128 * NWG);
     mbar_init(dp_full, 1);
     mbar_init(ds_ready, 128 * NWG);
     mbar_init(dq_done, 1);
@@ -232,19 +271,13 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tDP = tmem_base + Cfg::TM_DP, tDQ = tmem_base + Cfg::TM_DQ;
-  const uint32_t tSb[2] = {tmem_base + Cfg::TM_S0, tmem_base + Cfg::TM_S1};
+  const uint32_t tS = tmem_base + Cfg::TM_S, tDP = tmem_base + Cfg::TM_DP, tDQ = tmem_base + Cfg::TM_DQ;
+  const uint32_t tQ = tmem_base + Cfg::TM_Q, tDO = tmem_base + Cfg::TM_DO;
   BWD_TL_DECL(0);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_expect_tx(q_full, 2 * Cfg::TILE);
-#pragma unroll
-      for (int c = 0; c < NSUB; ++c) {
-        tma_load_2d(sQ + c * SUB, &tmQ, q_full, h * HD + c * 64, b * T + q0);
-        tma_load_2d(sDO + c * SUB, &tmDO, q_full, h * HD + c * 64, b * T + q0);
-      }
       for (int j = 0; j < n_blocks; ++j) {
         const int ks = j % KST, vs = j & 1;
         if (!mbar_wait(&k_empty[ks], ((j / KST) & 1) ^ 1)) {
@@ -270,10 +303,10 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0 && n_blocks > 0) {
       constexpr uint32_t idesc_s = umma_idesc(1, 1, 1, 0, 0, 128, 128);
       constexpr uint32_t idesc_dq = umma_idesc(1, 1, 1, 0, 1, 128, HD);
-      bool ok = mbar_wait(q_full, 0);
+      bool ok = mbar_wait(qdo_ready, 0);
       if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
-      const uint32_t lq = desc_lo_kmajor(smem_u32(sQ)), ldo = desc_lo_kmajor(smem_u32(sDO));
-      // S of block j into S buffer j&1 (waits for the K tile)
+      tc_fence_after();
+      // S of block j (A = the Q rows in TMEM; waits for the K tile)
       auto issue_s = [&](int j) -> bool {
         const int ks = j % KST;
         if (!mbar_wait(&k_full[ks], (j / KST) & 1)) return false;
@@ -281,11 +314,11 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t lk = desc_lo_kmajor(smem_u32(sK + ks * Cfg::TILE));
 #pragma unroll
         for (int t = 0; t < HD / 16; ++t)
-          umma_f16_ss(tSb[j & 1], desc_of(lq + kstep_kmajor(t)), desc_of(lk + kstep_kmajor(t)), idesc_s, t != 0);
-        umma_commit(&s_full[j & 1]);
+          umma_f16_ts(tS, tQ + t * 8, desc_of(lk + kstep_kmajor(t)), idesc_s, t != 0);
+        umma_commit(s_full);
         return true;
       };
-      // dP of block j (waits for the V tile, releases it)
+      // dP of block j (A = the dO rows in TMEM; waits for the V tile, releases it)
       auto issue_dp = [&](int j) -> bool {
         const int vs = j & 1;
         if (!mbar_wait(&v_full[vs], (j >> 1) & 1)) return false;
@@ -293,15 +326,28 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t lv = desc_lo_kmajor(smem_u32(sV + vs * Cfg::TILE));
 #pragma unroll
         for (int t = 0; t < HD / 16; ++t)
-          umma_f16_ss(tDP, desc_of(ldo + kstep_kmajor(t)), desc_of(lv + kstep_kmajor(t)), idesc_s, t != 0);
+          umma_f16_ts(tDP, tDO + t * 8, desc_of(lv + kstep_kmajor(t)), idesc_s, t != 0);
         umma_commit(dp_full);
         umma_commit(&v_empty[vs]);
         return true;
       };
       if (ok) ok = issue_s(0) && issue_dp(0);
-      if (ok && n_blocks > 1) ok = issue_s(1);
       if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
       for (int j = 0; j < n_blocks && ok; ++j) {
+        if (j + 1 < n_blocks) {
+          // the scores of block j are in registers: the buffer takes the next block's
+          if (!mbar_wait(s_free, j & 1)) {
+            set_error(args.err, ERR_WAIT_MMA_TMEM);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (!issue_s(j + 1)) {
+            set_error(args.err, ERR_WAIT_MMA_FULL);
+            ok = false;
+            break;
+          }
+        }
         if (!mbar_wait(ds_ready, j & 1)) {
           set_error(args.err, ERR_WAIT_MMA_TMEM);
           ok = false;
@@ -313,12 +359,13 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t lkm = desc_lo_mnmajor(smem_u32(sK + ks * Cfg::TILE));
 #pragma unroll
         for (int t = 0; t < 8; ++t)
-          umma_f16_ts(tDQ, tSb[j & 1] + packed_kstep_col(t), desc_of(lkm + kstep_mnmajor(t)), idesc_dq,
+          umma_f16_ts(tDQ, tDP + packed_kstep_col(t), desc_of(lkm + kstep_mnmajor(t)), idesc_dq,
                       (j | t) != 0);
         umma_commit(&k_empty[ks]);
-        if (j + 1 < n_blocks) ok = issue_dp(j + 1);
-        if (ok && j + 2 < n_blocks) ok = issue_s(j + 2);
-        if (!ok) set_error(args.err, ERR_WAIT_MMA_FULL);
+        if (j + 1 < n_blocks && !issue_dp(j + 1)) {
+          set_error(args.err, ERR_WAIT_MMA_FULL);
+          ok = false;
+        }
         BWD_STAMP(4 * j + 1);
       }
       if (ok) umma_commit(dq_done);
@@ -337,14 +384,22 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float scale_t = args.scale * kTruncScale;
     const float dlt = row_ok ? -args.delta[stat] * scale_t : 0.f;  // -delta * scale
     const uint32_t tD = tDP + g * WCOLS + lane_sel;
+    const uint32_t tSg = tS + g * WCOLS + lane_sel;
     static_assert(WCOLS == 32, "one 32-column TMEM access per phase and thread");
+    // warpgroup 0 parks the Q rows of the tile in TMEM, warpgroup 1 the dO rows (one row per thread)
+    if (g < 2) {
+      const size_t grow = (size_t)(b * T + (row_ok ? q_idx : 0));
+      const __nv_bfloat16* src = (g == 0 ? args.q + grow * args.ldq : args.dout + grow * args.lddo) + h * HD;
+      row_to_tmem<HD>(src, row_ok, (g == 0 ? tQ : tDO) + lane_sel);
+      tc_fence_before();
+      mbar_arrive(qdo_ready);
+    }
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
-      const uint32_t tS = tSb[j & 1] + g * WCOLS + lane_sel;
       // ---- phase 1: P (kept packed in registers)
       const bool stamper = g < 2 && (warp & 3) == 2 && lane == 0;
       if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * j);
-      ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1);
+      ok = mbar_wait(s_full, j & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -356,12 +411,23 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       {
         uint32_t rs[32];
         __syncwarp();
-        tmem_ld32(tS, rs);
-        tmem_wait_ld();
+        if (!(BWD_DBG & 2)) {
+          tmem_ld32(tSg, rs);
+          tmem_wait_ld();
+        }
+        // the block's scores are in registers: the S buffer may take the next block's
+        tc_fence_before();
+        mbar_arrive(s_free);
+        if (BWD_DBG & 1) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) pk[i >> 1] = (BWD_DBG & 2) ? 0u : rs[i];
+        } else
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float p0 = exp2f(__uint_as_float(rs[i]) * args.scale_log2 - lse2);
-          float p1 = exp2f(__uint_as_float(rs[i + 1]) * args.scale_log2 - lse2);
+          // every fourth exponential runs as a polynomial on the FMA pipe (kPolyEvery)
+          const float x1 = __uint_as_float(rs[i + 1]) * args.scale_log2 - lse2;
+          float p1 = (kPolyEvery && (i + 1) % (kPolyEvery ? kPolyEvery : 1) == kPolyEvery - 1) ? exp2_poly(x1) : exp2f(x1);
           if (need_mask) {
             if (i > lim) p0 = 0.f;
             if (i + 1 > lim) p1 = 0.f;
@@ -369,7 +435,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           pk[i >> 1] = pack_bf16x2_trunc(p0, p1);
         }
       }
-      // ---- phase 2: dS = P * (dP * scale - delta * scale), packed over this warpgroup's S columns
+      // ---- phase 2: dS = P * (dP * scale - delta * scale), packed over this warpgroup's dP columns
       if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * j + 2);
       ok = mbar_wait(dp_full, j & 1);
       ok = __all_sync(0xffffffffu, ok);
@@ -379,8 +445,14 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       {
         uint32_t rp[32];
         __syncwarp();
-        tmem_ld32(tD, rp);
-        tmem_wait_ld();
+        if (!(BWD_DBG & 2)) {
+          tmem_ld32(tD, rp);
+          tmem_wait_ld();
+        }
+        if (BWD_DBG & 1) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) pk[i >> 1] ^= (BWD_DBG & 2) ? 0u : rp[i];
+        } else
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           // the factor is packed by truncation (see kTruncScale) and multiplied in bf16x2: one FMA per
@@ -390,8 +462,10 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           pk[i >> 1] = mul_bf16x2(pk[i >> 1], t);
         }
       }
-      tmem_st16(tS, pk);
-      tmem_wait_st();
+      if (!(BWD_DBG & 2)) {
+        tmem_st16(tD, pk);
+        tmem_wait_st();
+      }
       tc_fence_before();
       mbar_arrive(ds_ready);
     }
@@ -461,7 +535,8 @@ struct DkvCfg {
   static constexpr int OFF_Q = OFF_V + TILE;        // 2 stages
   static constexpr int OFF_DO = OFF_Q + 2 * TILE;   // 2 stages
   static constexpr int OFF_STAT = OFF_DO + 2 * TILE;  // per warpgroup: lse2[64], delta[64]
-  static constexpr int OFF_BAR = OFF_STAT + 1024;
+  static constexpr int OFF_RAW = OFF_STAT + 1024;     // per warpgroup: 2 stages x 64 raw values
+  static constexpr int OFF_BAR = OFF_RAW + 2048;
   static constexpr int SMEM_MIN = OFF_BAR + 256 + 1024;
   static constexpr int SMEM = SMEM_MIN < 120 * 1024 ? 120 * 1024 : SMEM_MIN;
   static constexpr uint32_t TM_ST = 0, TM_DPT = 128, TM_DV = 256, TM_DK = 384;
@@ -651,18 +726,24 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     float* dl = ls + WCOLS;                     // -delta * scale of the same columns
     const uint32_t tS = tST + g * WCOLS + lane_sel, tD = tDPT + g * WCOLS + lane_sel;
     static_assert(WCOLS == 32, "one 32-column TMEM access per phase and thread");
-    // per-query statistic this thread stages for iteration i: threads 0..31 of the warpgroup carry
-    // lse (in log2 units), threads 32..63 carry -delta * scale (one FMA per element in phase 2)
-    auto load_stat = [&](int i) -> float {
-      if (wt >= 2 * WCOLS) return 0.f;
+    // Per-query statistics of iteration i: threads 0..31 of the warpgroup fetch lse, threads 32..63
+    // delta, one value each, with a 4-byte cp.async into a two-stage raw buffer one iteration ahead
+    // (a plain global load issued "early" can be moved next to its use by the compiler, which put
+    // a full memory latency at the top of every iteration); the same thread later converts its own
+    // value (lse -> log2 units minus the truncation offset, delta -> -delta * scale) into ls / dl.
+    float* raw = reinterpret_cast<float*>(smem + Cfg::OFF_RAW) + g * (4 * WCOLS);
+    auto fetch_stat = [&](int i) {
+      if (wt >= 2 * WCOLS) return;
       const int hh = kvh * group + i / per_head;
       const int qi = (qt_first + i % per_head) * 128 + g * WCOLS + (wt & (WCOLS - 1));
-      const bool qok = qi < T;
-      const size_t stat = ((size_t)b * args.hq + hh) * T + (qok ? qi : 0);
-      if (wt < WCOLS) return qok ? args.lse[stat] * 1.4426950408889634f - kTruncLog2 : INFINITY;
-      return qok ? -args.delta[stat] * (args.scale * kTruncScale) : 0.f;
+      const size_t stat = ((size_t)b * args.hq + hh) * T + (qi < T ? qi : 0);
+      const float* src = (wt < WCOLS ? args.lse : args.delta) + stat;
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(raw + (i & 1) * (2 * WCOLS) + wt)),
+                   "l"(src)
+                   : "memory");
     };
-    float stat_val = n_iter > 0 ? load_stat(0) : 0.f;
+    if (n_iter > 0) fetch_stat(0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
     bool ok = true;
     const float scale_t = args.scale * kTruncScale;
     for (int it = 0; it < n_iter; ++it) {
@@ -670,12 +751,17 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const int q0 = qt * 128 + g * WCOLS;
       const uint32_t ph = it & 1;
       {
-        // stage the per-query statistics; named barrier 1+g = this warpgroup's 128 threads
-        wg_sync(g);                               // previous iteration's reads done
-        if (wt < 2 * WCOLS) ls[wt] = stat_val;    // wt >= WCOLS lands in dl[]
+        asm volatile("cp.async.wait_group 0;" ::: "memory");   // this thread's value of iteration it
+        wg_sync(g);                                            // previous iteration's reads of ls / dl done
+        if (wt < 2 * WCOLS) {
+          const float r = raw[(it & 1) * (2 * WCOLS) + wt];
+          const bool qok = qt * 128 + g * WCOLS + (wt & (WCOLS - 1)) < T;
+          ls[wt] = wt < WCOLS ? (qok ? r * 1.4426950408889634f - kTruncLog2 : INFINITY)
+                              : (qok ? -r * scale_t : 0.f);    // wt >= WCOLS lands in dl[]
+        }
+        if (it + 1 < n_iter) fetch_stat(it + 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
         wg_sync(g);
-        // the next iteration's value is fetched now and lands while this iteration computes
-        if (it + 1 < n_iter) stat_val = load_stat(it + 1);
       }
       // column (query) c is visible from this kv row iff kv_idx <= q + off  <=>  q >= kv_idx - off
       const int q_min = args.causal ? (kv_idx - off) : -0x40000000;
@@ -693,16 +779,23 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       {
         uint32_t rs[32];
         __syncwarp();
-        tmem_ld32(tS, rs);
-        tmem_wait_ld();
+        if (!(BWD_DBG & 2)) {
+          tmem_ld32(tS, rs);
+          tmem_wait_ld();
+        }
         const float4* ls4 = reinterpret_cast<const float4*>(ls);
+        if (BWD_DBG & 1) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) pk[i >> 1] = (BWD_DBG & 2) ? 0u : rs[i];
+        } else
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 l = ls4[i >> 2];
           float p0 = exp2f(__uint_as_float(rs[i]) * args.scale_log2 - l.x);
           float p1 = exp2f(__uint_as_float(rs[i + 1]) * args.scale_log2 - l.y);
           float p2 = exp2f(__uint_as_float(rs[i + 2]) * args.scale_log2 - l.z);
-          float p3 = exp2f(__uint_as_float(rs[i + 3]) * args.scale_log2 - l.w);
+          const float x3 = __uint_as_float(rs[i + 3]) * args.scale_log2 - l.w;
+          float p3 = (kPolyEvery && (i + 3) % (kPolyEvery ? kPolyEvery : 1) == kPolyEvery - 1) ? exp2_poly(x3) : exp2f(x3);
           if (need_mask) {
             if (i < first_ok) p0 = 0.f;
             if (i + 1 < first_ok) p1 = 0.f;
@@ -714,8 +807,10 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
       }
       // this warpgroup's S^T columns are in registers: the packed P^T may overwrite them
-      tmem_st16(tS, pk);
-      tmem_wait_st();
+      if (!(BWD_DBG & 2)) {
+        tmem_st16(tS, pk);
+        tmem_wait_st();
+      }
       tc_fence_before();
       mbar_arrive(p_ready);
       if (stamper) BWD_STAMP(4096 * (1 + g) + 4 * it + 2);
@@ -728,9 +823,15 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       {
         uint32_t rp[32];
         __syncwarp();
-        tmem_ld32(tD, rp);
-        tmem_wait_ld();
+        if (!(BWD_DBG & 2)) {
+          tmem_ld32(tD, rp);
+          tmem_wait_ld();
+        }
         const float4* dl4 = reinterpret_cast<const float4*>(dl);
+        if (BWD_DBG & 1) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) pk[i >> 1] ^= (BWD_DBG & 2) ? 0u : rp[i];
+        } else
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 d = dl4[i >> 2];
@@ -742,8 +843,10 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           pk[(i >> 1) + 1] = mul_bf16x2(pk[(i >> 1) + 1], t1);
         }
       }
-      tmem_st16(tD, pk);
-      tmem_wait_st();
+      if (!(BWD_DBG & 2)) {
+        tmem_st16(tD, pk);
+        tmem_wait_st();
+      }
       tc_fence_before();
       mbar_arrive(ds_ready);
     }
@@ -855,6 +958,10 @@ BB_API int bb_flash_bwd(const void* q, int ldq, const void* k, int ldk, const vo
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   FaBwdArgs a{};
+  a.q = static_cast<const __nv_bfloat16*>(q);
+  a.dout = static_cast<const __nv_bfloat16*>(dout);
+  a.ldq = ldq;
+  a.lddo = lddo;
   a.lse = lse;
   a.delta = delta;
   a.dQ = static_cast<__nv_bfloat16*>(dq);
@@ -874,6 +981,10 @@ BB_API int bb_flash_bwd(const void* q, int ldq, const void* k, int ldk, const vo
   a.err = device_error_word();
 #ifdef BB_TIMELINE
   a.tl = g_bwd_timeline;
+  {
+    const char* e = std::getenv("BB_FA_DEBUG");   // profiling builds only
+    a.dbg = e ? std::atoi(e) : 0;
+  }
 #endif
   if (hd == 128) return launch_fa_bwd<128>(q, ldq, k, ldk, v, ldv, dout, lddo, a, s);
   if (hd == 64) return launch_fa_bwd<64>(q, ldq, k, ldk, v, ldv, dout, lddo, a, s);
