@@ -123,9 +123,42 @@ def build_host(force: bool = False, verbose: bool = False) -> Path:
     return HOST_LIB
 
 
+#: translation units of the bounds-checking library (kernels whose addresses depend on data) and
+#: what they need at link time
+BOUNDS_TUS = ["kernels/elementwise.cu", "kernels/ce.cu", "kernels/moe.cu", "common/host.cu"]
+BOUNDS_LIB = LIBDIR / "libbrain_b200_bounds.so"
+
+
+def build_bounds(force: bool = False, verbose: bool = False) -> Path:
+    """A second, small library of the index-driven kernels compiled with -DBB_DEBUG_BOUNDS: every
+    data-dependent index is checked against its extent, a violation writes an error code and skips
+    the access.  Loaded by tests only: production code never links it."""
+    OBJDIR.mkdir(parents=True, exist_ok=True)
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    hdr = _newest_header()
+    nvcc = _nvcc()
+    objs, jobs = [], []
+    for rel in BOUNDS_TUS:
+        s = CSRC / rel
+        o = OBJDIR / ("bounds__" + rel.replace("/", "__") + ".o")
+        objs.append(o)
+        if force or _stale(s, o, hdr):
+            jobs.append((s, o))
+    for s, o in jobs:
+        flags = [f for f in NVCC_FLAGS if f != "--use_fast_math"] if s.name in EXACT_MATH else NVCC_FLAGS
+        _run([nvcc, *flags, "-DBB_DEBUG_BOUNDS", "-I", str(CSRC), "-c", str(s), "-o", str(o)],
+             log=o.with_suffix(".log"))
+        if verbose:
+            print(f"[build] bounds {s.relative_to(ROOT)}")
+    if jobs or not BOUNDS_LIB.exists():
+        _run([nvcc, "-shared", "-o", str(BOUNDS_LIB), *map(str, objs), "-lcudart"])
+    return BOUNDS_LIB
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_host(force, verbose)
     build_cuda(force, verbose)
+    build_bounds(force, verbose)
 
 
 def ptxas_report() -> str:

@@ -22,6 +22,7 @@ enum ErrCode : int {
   ERR_WAIT_SOFTMAX = 5,
   ERR_WAIT_PEER = 6,       // a peer flag never arrived (fused comm kernels)
   ERR_BAD_ARG = 7,
+  ERR_BOUNDS = 8,          // bounds-checking builds: a data-dependent index was out of range (access skipped)
 };
 
 __device__ __forceinline__ void set_error(int* err, int code) {
@@ -69,6 +70,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
   }
 }
+
+// ---------------------------------------------------------------- bounds-checking builds
+// -DBB_DEBUG_BOUNDS (the small library built from the index-driven kernels for tests): kernels whose
+// addresses depend on DATA (token ids, class targets, routing tables) take the per-device error word
+// as one more parameter, check the index against its extent before using it, and on a violation
+// record ERR_BOUNDS and skip the access.  No trap, no assert: the context stays usable and the host
+// reads the word.  In production builds the three macros expand to nothing / true.
+#ifdef BB_DEBUG_BOUNDS
+#define BB_ERR_PARAM , int* bb_bounds_err
+#define BB_ERR_ARG , ::bb::device_error_word()
+#define BB_INDEX_OK(i, n) ::bb::bounds_ok(bb_bounds_err, (long long)(i), (long long)(n))
+__device__ __forceinline__ bool bounds_ok(int* err, long long i, long long n) {
+  if (i >= 0 && i < n) return true;
+  if (err) atomicCAS(err, 0, (int)ERR_BOUNDS);
+  return false;
+}
+#else
+#define BB_ERR_PARAM
+#define BB_ERR_ARG
+#define BB_INDEX_OK(i, n) true
+#endif
 
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {

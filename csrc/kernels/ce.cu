@@ -56,11 +56,14 @@ template <bool GRAD>
 __global__ void __launch_bounds__(512)
 ce_kernel(__nv_bfloat16* __restrict__ logits, long ld, const int* __restrict__ tgt,
           float* __restrict__ loss, float* __restrict__ lse_out, int V, const float* scale_ptr,
-          float scale_mul) {
+          float scale_mul BB_ERR_PARAM) {
   __shared__ float sh[66];
   const int r = blockIdx.x;
   __nv_bfloat16* row = logits + (size_t)r * ld;
   const int t = tgt[r];
+  // a negative target is the ignore mark; one past the vocabulary is a caller error that production
+  // builds treat as ignored and bounds-checking builds also record
+  if (t >= 0 && threadIdx.x == 0) (void)BB_INDEX_OK(t, V);
   const int nv = V >> 3;  // V % 8 == 0 enforced by the launcher
   if (t < 0 || t >= V) {
     if (threadIdx.x == 0) {
@@ -127,9 +130,9 @@ BB_API int bb_cross_entropy(void* logits, long ld, const int* tgt, float* loss, 
   const int threads = V >= 8192 ? 512 : 128;
   if (grad)
     ce_kernel<true><<<n, threads, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)logits, ld, tgt, loss,
-                                                            lse, V, scale_ptr, scale_mul);
+                                                            lse, V, scale_ptr, scale_mul BB_ERR_ARG);
   else
     ce_kernel<false><<<n, threads, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)logits, ld, tgt,
-                                                             loss, lse, V, scale_ptr, scale_mul);
+                                                             loss, lse, V, scale_ptr, scale_mul BB_ERR_ARG);
   return (int)cudaGetLastError();
 }

@@ -102,12 +102,13 @@ __global__ void add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloa
 // out[t, :] = emb[tok[t], :] (+ pos_emb[t % T, :])
 __global__ void embed_fwd_kernel(const int* __restrict__ tok, const __nv_bfloat16* __restrict__ emb,
                                  const __nv_bfloat16* __restrict__ pos_emb, int T,
-                                 __nv_bfloat16* __restrict__ out, long n_tok, int dv, int vocab) {
+                                 __nv_bfloat16* __restrict__ out, long n_tok, int dv, int vocab BB_ERR_PARAM) {
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n_tok * dv;
        i += (long)gridDim.x * blockDim.x) {
     const long t = i / dv;
     const int c = (int)(i % dv);
     int id = tok[t];
+    if (!BB_INDEX_OK(id, vocab)) continue;   // bounds-checking builds: recorded, row left untouched
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     bf16x8 v = reinterpret_cast<const bf16x8*>(emb)[(size_t)id * dv + c];
     if (pos_emb) {
@@ -125,13 +126,14 @@ __global__ void embed_fwd_kernel(const int* __restrict__ tok, const __nv_bfloat1
 // demb[tok[t], :] += dout[t, :]  (fp32 main-grad, red.global.add) ; dpos[t % T, :] += dout[t, :]
 __global__ void embed_bwd_kernel(const int* __restrict__ tok, const __nv_bfloat16* __restrict__ dout,
                                  float* __restrict__ demb, float* __restrict__ dpos, int T,
-                                 long n_tok, int d, int vocab) {
+                                 long n_tok, int d, int vocab BB_ERR_PARAM) {
   const int dp = d >> 1;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n_tok * dp;
        i += (long)gridDim.x * blockDim.x) {
     const long t = i / dp;
     const int c = (int)(i % dp) * 2;
     int id = tok[t];
+    if (!BB_INDEX_OK(id, vocab)) continue;
     if (id < 0 || id >= vocab) continue;
     const float2 g =
         __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dout + (size_t)t * d + c));
@@ -207,7 +209,7 @@ BB_API int bb_embed_fwd(const int* tok, const void* emb, const void* pos_emb, in
   if (n_tok <= 0) return BB_OK;
   embed_fwd_kernel<<<ew_grid(n_tok * (d / 8)), 256, 0, (cudaStream_t)stream>>>(
       tok, (const __nv_bfloat16*)emb, (const __nv_bfloat16*)pos_emb, T, (__nv_bfloat16*)out, n_tok,
-      d / 8, vocab);
+      d / 8, vocab BB_ERR_ARG);
   return (int)cudaGetLastError();
 }
 BB_API int bb_embed_bwd(const int* tok, const void* dout, float* demb, float* dpos, int T,
@@ -215,7 +217,7 @@ BB_API int bb_embed_bwd(const int* tok, const void* dout, float* demb, float* dp
   if (d % 2) return BB_EARG;
   if (n_tok <= 0) return BB_OK;
   embed_bwd_kernel<<<ew_grid(n_tok * (d / 2)), 256, 0, (cudaStream_t)stream>>>(
-      tok, (const __nv_bfloat16*)dout, demb, dpos, T, n_tok, d, vocab);
+      tok, (const __nv_bfloat16*)dout, demb, dpos, T, n_tok, d, vocab BB_ERR_ARG);
   return (int)cudaGetLastError();
 }
 BB_API int bb_cast_f32_bf16(const float* x, void* y, long n, void* stream) {

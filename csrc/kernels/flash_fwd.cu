@@ -648,10 +648,6 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   }
 }
 
-}  // namespace bb
-#include "flash_fwd_pp.cuh"
-namespace bb {
-
 template <int HD>
 static int launch_fa_fwd(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
                          const FaFwdArgs& a, cudaStream_t stream) {
@@ -666,29 +662,27 @@ static int launch_fa_fwd(const void* q, int ldq, const void* k, int ldk, const v
   rc = make_tmap_2d(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, (uint64_t)a.hk * HD,
                     (uint64_t)a.B * a.S, (uint64_t)ldv * 2, 64, 128);
   if (rc) return rc;
-  static PerDeviceOnce once1, once2, once3;
+  static PerDeviceOnce once1, once2;
   {
     cudaError_t e = ensure_dyn_smem(once1, fa_fwd_kernel<HD>, Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
     e = ensure_dyn_smem(once2, fa_fwd2_kernel<HD, false>, Cfg::SMEM);
-    if (e != cudaSuccess) return (int)e;
-    e = ensure_dyn_smem(once3, fa_fwd_pp_kernel<HD>, FaPpCfg<HD>::SMEM);
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid((a.T + 127) / 128, a.hq, a.B);
   // the two-unit form is the default (478 -> 309 us at B4 T4096 16q/8kv hd128); BB_FA_FWD=1 selects
   // the first form, which also carries the timeline stamps.  (A third form with one 128-key score
   // tile per block, single-buffered, measured 380 us: with two CTAs per SM the idle tensor time
-  // during a CTA's softmax was not filled by its neighbour.)
+  // during a CTA's softmax was not filled by its neighbour.  A fourth form, one CTA per SM working
+  // on two query tiles that take turns on the tensor pipe, 128-wide score MMAs, one softmax
+  // warpgroup of one row per thread per tile, all 512 TMEM columns, was correct and measured 372 us:
+  // each tile is one serial chain scores -> 128 exponentials per thread -> PV -> next scores, and two
+  // such chains per SM hide less than the four shorter ones of this form.)
   static const int form = [] {
     const char* e = getenv("BB_FA_FWD");
-    return (e && e[0] >= '1' && e[0] <= '3') ? e[0] - '0' : 2;
+    return (e && e[0] == '1') ? 1 : 2;
   }();
-  if (form == 3 && a.timeline == nullptr) {
-    // two query tiles per CTA taking turns on the tensor pipe (flash_fwd_pp.cuh)
-    dim3 gp(((a.T + 127) / 128 + 1) / 2, a.hq, a.B);
-    fa_fwd_pp_kernel<HD><<<gp, FaPpCfg<HD>::THREADS, FaPpCfg<HD>::SMEM, stream>>>(tmQ, tmK, tmV, a);
-  } else if (form == 2 && a.timeline == nullptr)
+  if (form == 2 && a.timeline == nullptr)
     fa_fwd2_kernel<HD, false><<<grid, 192, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, a);
   else
     fa_fwd_kernel<HD><<<grid, 192, Cfg::SMEM, stream>>>(tmQ, tmK, tmV, a);

@@ -91,7 +91,7 @@ __global__ void moe_positions_kernel(const int* __restrict__ idx, long n_pairs, 
 // `src` rows are addressed as (rank = token / n_per_rank, local = token % n_per_rank).
 __global__ void moe_gather_kernel(MoePeers src, int n_per_rank, const int* __restrict__ pair_of_pos,
                                   const float* __restrict__ w, int k, __nv_bfloat16* __restrict__ xp,
-                                  const int* __restrict__ offsets, int E, int dv) {
+                                  const int* __restrict__ offsets, int E, int dv, int world BB_ERR_PARAM) {
   const int rows = offsets[E];
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -106,6 +106,9 @@ __global__ void moe_gather_kernel(MoePeers src, int n_per_rank, const int* __res
       continue;
     }
     const int token = pair / k;
+    // the pair id comes from the routing tables: beyond the tokens of the ranks that were passed it
+    // would select a null base pointer (bounds-checking builds record it and leave the row alone)
+    if (!BB_INDEX_OK(token, (long long)n_per_rank * world)) continue;
     const int rank = token / n_per_rank, local = token - rank * n_per_rank;
     const bf16x8* s = reinterpret_cast<const bf16x8*>(src.p[rank]) + (size_t)local * dv;
     if (w) {
@@ -216,7 +219,8 @@ BB_API int bb_moe_gather(const uint64_t* src_ptrs, int world, int n_per_rank,
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   moe_gather_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, n_per_rank, pair_of_pos, w, k,
-                                                             (__nv_bfloat16*)xp, offsets, E, d / 8);
+                                                             (__nv_bfloat16*)xp, offsets, E, d / 8,
+                                                             world BB_ERR_ARG);
   return (int)cudaGetLastError();
 }
 
