@@ -343,6 +343,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   }
 }
 
+static constexpr float kFwdTruncLog2 = 0.0041778f;   // log2(1.0029), see the packing note in fa_fwd2_kernel
+
 // Second form of the forward kernel: the KV block is processed as two 64-key UNITS with two score
 // buffers in TMEM, so the tensor pipe never sits on the softmax's critical path:
 //   issue order   S(0) S(1) | P(0)? PV(0) S(2) | P(1)? PV(1) S(3) | ...
@@ -579,7 +581,10 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       l *= alpha;
       m_ref = m_new;
-      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      // P is packed by truncation (one PRMT per pair) after a 1.0029 pre-scale that folds into the
+      // exponent offset: truncation of the scaled value is unbiased on average, the row sum runs over
+      // the same scaled values (so O / l is unchanged) and the stored log-sum-exp takes the factor out
+      const float m_use = ((m_ref == -INFINITY) ? 0.f : m_ref) - kFwdTruncLog2;
       const float sc = args.scale_log2;
       uint32_t pk[32];  // 64 probabilities as 32 packed bf16x2 words
       float ls = 0.f;
@@ -597,8 +602,8 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         ls += (a0 + a1) + (b0 + b1);
         // integer-pipe packing: cvt.rn.bf16x2 would share the quarter-rate unit with ex2
-        pk[i >> 1] = pack_bf16x2_alu(a0, a1);         // keys  0..31 of the unit -> words  0..15
-        pk[16 + (i >> 1)] = pack_bf16x2_alu(b0, b1);  // keys 32..63             -> words 16..31
+        pk[i >> 1] = __byte_perm(__float_as_uint(a0), __float_as_uint(a1), 0x7632);         // keys  0..31 -> words  0..15
+        pk[16 + (i >> 1)] = __byte_perm(__float_as_uint(b0), __float_as_uint(b1), 0x7632);  // keys 32..63 -> words 16..31
       }
       l += ls;
       tmem_st32(tS, pk);
@@ -636,7 +641,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       if (!PAGED && args.lse && q_idx < T)
         args.lse[((size_t)b * args.hq + h) * T + q_idx] =
-            (l > 0.f) ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
+            (l > 0.f) ? (m_ref + log2f(l) - kFwdTruncLog2) * 0.6931471805599453f : -INFINITY;
     }
   }
 

@@ -87,6 +87,16 @@ __device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// int8 operands, s32 accumulator (K = 32 per instruction: the same 32 bytes per operand row)
+__device__ __forceinline__ void umma_i8_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on the barrier at `cluster_addr` (either CTA of the pair) once every MMA issued so far by
 // this thread has completed.
 __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
@@ -95,6 +105,8 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
 }
 
 struct PairArgs {
+  const float* scale_m;  // int8: per-row (token) scale
+  const float* scale_n;  // int8: per-column (channel) scale
   float alpha;
   int M, N, K;
   int a_mn, b_mn;
@@ -117,7 +129,7 @@ struct PairArgs {
 
 static constexpr int BM = 128;        // rows per CTA; the pair tile is 2 * BM rows
 static constexpr int BNP = 256;       // columns of the pair tile; each CTA stages BNP / 2 of them
-static constexpr int BK = 64;
+static constexpr int BK = 64;         // bf16 elements per k-block (128 bytes); the int8 form has 128
 static constexpr int A_BYTES = BM * 128;
 static constexpr int B_BYTES = (BNP / 2) * 128;
 static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // 32 KB
@@ -125,6 +137,7 @@ static constexpr int STAGES = 6;
 static constexpr int OUT_STAGE_BYTES = 128 * 128;
 static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * OUT_STAGE_BYTES + 1024 + 256;
 
+template <bool I8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const PairArgs args) {
@@ -151,7 +164,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int tiles_n = (N + BNP - 1) / BNP;
   const int split_k = args.split_k > 1 ? args.split_k : 1;
   const int ntiles = tiles_m * tiles_n * split_k;
-  const int nkb_all = (K + BK - 1) / BK;
+  constexpr int BKE = I8 ? 2 * BK : BK;   // elements per 128-byte k-block
+  const int nkb_all = (K + BKE - 1) / BKE;
   const int kb_per_split = (nkb_all + split_k - 1) / split_k;
   constexpr int GROUP_M = 8;
 
@@ -227,7 +241,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           // the leader's arrival.
           const uint32_t bar = map_to_rank(smem_u32(&full[stage]), 0);
           if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
-          const int k0 = (kb0 + kb) * BK;
+          const int k0 = (kb0 + kb) * BKE;
           if (!args.a_mn) {
             tma_load_2d_pair(sa, &tmA, bar, k0, m0);
           } else {
@@ -250,8 +264,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && leader) {
-      const uint32_t idesc = umma_idesc(1, 1, 1, 0, 0, 2 * BM, BNP) | (uint32_t)(args.a_mn & 1) << 15 |
-                             (uint32_t)(args.b_mn & 1) << 16;
+      const uint32_t idesc = (I8 ? umma_idesc(2, 1, 1, 0, 0, 2 * BM, BNP) : umma_idesc(1, 1, 1, 0, 0, 2 * BM, BNP)) |
+                             (uint32_t)(args.a_mn & 1) << 15 | (uint32_t)(args.b_mn & 1) << 16;
       const uint32_t a_adv = args.a_mn ? 16 * 128 : 32;
       const uint32_t b_adv = args.b_mn ? 16 * 128 : 32;
       const uint32_t a_lbo = args.a_mn ? BK * 128 : 16;
@@ -291,7 +305,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t da = umma_smem_desc(sa + k * a_adv, a_lbo, 1024);
             const uint64_t db = umma_smem_desc(sb + k * b_adv, b_lbo, 1024);
-            umma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0);
+            if (I8) umma_i8_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0);
+            else umma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0);
           }
           // the slot is free in BOTH CTAs once these MMAs have read it
           const uint32_t e = smem_u32(&empty[stage]);
@@ -351,8 +366,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (lane == 0) mbar_arrive_cluster(acc ? tmem_empty_leader1 : tmem_empty_leader0);
         }
         float v[32];
+        if (I8) {
+          const int grow = y0 + r_tile;
+          const float sm = (args.scale_m && grow < M) ? args.scale_m[grow] * alpha : alpha;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
+          for (int j = 0; j < 32; ++j) {
+            const float sn = args.scale_n ? ((col0 + j < N) ? args.scale_n[col0 + j] : 0.f) : 1.f;
+            v[j] = (float)(int)r[j] * sm * sn;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
+        }
         const int slab = f32out ? c : (c >> 1);
         const bool first_half = f32out || (c & 1) == 0;
         const bool last_half = f32out || (c & 1) == 1 || col0 + 32 >= N;
@@ -423,29 +448,33 @@ BB_API int bb_gemm_pair_clusters() { return g_last_pairs_fit.load(); }
 // out_mode 0 / 1 / 2 without bias.  Returns BB_ESIZE when the shape or alignment does not suit the
 // pair kernel (the caller then uses the single-CTA kernel): C must be 16-byte aligned with a
 // 16-byte pitch, and the grid is sized to whole CTA pairs.
-BB_API int bb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, int lda,
-                             int ldb, int ldc, int a_mn, int b_mn, int out_mode, float alpha,
-                             int split_k, int max_ctas, void* stream) {
+template <bool I8>
+static int launch_pair(const void* A, const void* B, void* C, const float* scale_m, const float* scale_n, int M,
+                       int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_mode, float alpha,
+                       int split_k, int max_ctas, void* stream) {
   using namespace bb;
   using namespace bb::pair;
   if (M <= 0 || N <= 0 || K <= 0 || out_mode < 0 || out_mode > 2) return BB_EARG;
+  if (I8 && (a_mn || b_mn || out_mode != 0)) return BB_EARG;
   const bool f32out = out_mode != 0;
   const int ces = f32out ? 4 : 2;
   if ((reinterpret_cast<uintptr_t>(C) & 15) || ((uint64_t)ldc * ces) % 16) return BB_ESIZE;
-  const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUtensorMapDataType dt = I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  constexpr int ES = I8 ? 1 : 2;             // operand element bytes
+  constexpr int BKE = I8 ? 2 * BK : BK;      // elements per 128-byte k-block
   CUtensorMap tmA, tmB, tmC;
-  int rc = !a_mn ? make_tmap_2d(&tmA, dt, 2, A, K, M, (uint64_t)lda * 2, BK, BM)
-                 : make_tmap_2d(&tmA, dt, 2, A, M, K, (uint64_t)lda * 2, 64, BK);
+  int rc = !a_mn ? make_tmap_2d(&tmA, dt, ES, A, K, M, (uint64_t)lda * ES, BKE, BM)
+                 : make_tmap_2d(&tmA, dt, ES, A, M, K, (uint64_t)lda * ES, 64, BK);
   if (rc) return rc;
-  rc = !b_mn ? make_tmap_2d(&tmB, dt, 2, B, K, N, (uint64_t)ldb * 2, BK, BNP / 2)
-             : make_tmap_2d(&tmB, dt, 2, B, N, K, (uint64_t)ldb * 2, 64, BK);
+  rc = !b_mn ? make_tmap_2d(&tmB, dt, ES, B, K, N, (uint64_t)ldb * ES, BKE, BNP / 2)
+             : make_tmap_2d(&tmB, dt, ES, B, N, K, (uint64_t)ldb * ES, 64, BK);
   if (rc) return rc;
   rc = make_tmap_2d(&tmC, f32out ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, ces,
                     C, N, M, (uint64_t)ldc * ces, f32out ? 32 : 64, BM);
   if (rc) return rc;
   static PerDeviceOnce smem_once;
   {
-    cudaError_t e = ensure_dyn_smem(smem_once, gemm_pair_kernel, SMEM);
+    cudaError_t e = ensure_dyn_smem(smem_once, gemm_pair_kernel<I8>, SMEM);
     if (e != cudaSuccess) return (int)e;
   }
   // how many 2-CTA clusters the device holds at once (an odd SM count per GPC leaves one SM out)
@@ -466,7 +495,7 @@ BB_API int bb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N
     cfg.attrs = at;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<I8>, &cfg) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = sm_count() / 2 - 2;
     }
@@ -482,6 +511,8 @@ BB_API int bb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N
   }
   g_last_pairs_fit.store(pairs_fit);
   PairArgs a{};
+  a.scale_m = scale_m;
+  a.scale_n = scale_n;
   a.alpha = alpha;
   a.M = M;
   a.N = N;
@@ -498,6 +529,21 @@ BB_API int bb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N
   long pairs = tiles < pairs_fit ? tiles : pairs_fit;
   if (max_ctas > 0 && pairs > max_ctas / 2) pairs = max_ctas / 2;
   if (pairs < 1) pairs = 1;
-  gemm_pair_kernel<<<(int)(2 * pairs), 256, SMEM, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, tmC, a);
+  gemm_pair_kernel<I8><<<(int)(2 * pairs), 256, SMEM, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, tmC, a);
   return (int)cudaGetLastError();
+}
+
+BB_API int bb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, int lda,
+                             int ldb, int ldc, int a_mn, int b_mn, int out_mode, float alpha,
+                             int split_k, int max_ctas, void* stream) {
+  return launch_pair<false>(A, B, C, nullptr, nullptr, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_mode, alpha,
+                            split_k, max_ctas, stream);
+}
+
+// W8A8 on CTA pairs: C[M,N] bf16 = (A[M,K] int8 . B[N,K]^T int8) * scale_m[row] * scale_n[col].
+// Same restrictions as the bf16 form (BB_ESIZE when C's alignment does not suit the TMA store).
+BB_API int bb_gemm_i8_pair(const void* A, const void* B, void* C, const float* scale_m, const float* scale_n,
+                           int M, int N, int K, int lda, int ldb, int ldc, int max_ctas, void* stream) {
+  if ((lda % 16) || (ldb % 16)) return bb::BB_ESIZE;   // TMA pitch: multiples of 16 bytes
+  return launch_pair<true>(A, B, C, scale_m, scale_n, M, N, K, lda, ldb, ldc, 0, 0, 0, 1.f, 1, max_ctas, stream);
 }

@@ -722,6 +722,16 @@ static long long* const g_gemm_timeline = nullptr;
 #endif
 
 // CTA-pair kernel (gemm_2cta.cu)
+BB_API int bb_gemm_i8_pair(const void* A, const void* B, void* C, const float* scale_m, const float* scale_n,
+                           int M, int N, int K, int lda, int ldb, int ldc, int max_ctas, void* stream);
+// BB_GEMM_PAIR=0 keeps every GEMM on the single-CTA kernel
+static int pair_enabled() {
+  static const int mode = [] {
+    const char* e = getenv("BB_GEMM_PAIR");
+    return e ? atoi(e) : 1;
+  }();
+  return mode;
+}
 BB_API int bb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, int lda,
                              int ldb, int ldc, int a_mn, int b_mn, int out_mode, float alpha,
                              int split_k, int max_ctas, void* stream);
@@ -779,10 +789,7 @@ BB_API int bb_gemm_bf16(const void* A, const void* B, void* C, const float* bias
   }
   // Large plain GEMMs go to the CTA-pair kernel (256 x 256 tiles over two SMs, gemm_2cta.cu): it
   // halves the B-operand bytes each SM pulls from L2, which is what bounds this kernel at bn 256.
-  static const int pair_mode = [] {
-    const char* e = getenv("BB_GEMM_PAIR");
-    return e ? atoi(e) : 1;
-  }();
+  const int pair_mode = pair_enabled();
   if (pair_mode && auto_bn && bn == 256 && bias == nullptr && out_mode != 3 && M >= 256 && N >= 256 &&
       a.timeline == nullptr) {
     const int rc = bb_gemm_bf16_pair(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_mode, alpha,
@@ -821,6 +828,12 @@ BB_API int bb_gemm_i8(const void* A, const void* B, void* C, const float* scale_
     const long tiles128 = (long)((M + 127) / 128) * ((N + 127) / 128);
     const int sms = sm_count();
     bn = (tiles256 >= sms) ? 256 : (tiles128 >= sms / 2 ? 128 : 64);
+  }
+  // prefill-sized problems go to the CTA-pair kernel (each SM stages half of B: the single-CTA
+  // int8 kernel is bound by its L2 -> shared-memory fill at a third of the tensor rate)
+  if (pair_enabled() && auto_bn && bn == 256 && M >= 256 && N >= 256 && K >= 256) {
+    const int rc = bb_gemm_i8_pair(A, B, C, scale_m, scale_n, M, N, K, lda, ldb, ldc, max_ctas, stream);
+    if (rc != BB_ESIZE) return rc;
   }
   switch (bn) {
     case 256: return launch_gemm<256, true>(A, B, a, lda, ldb, s, max_ctas);

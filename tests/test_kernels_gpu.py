@@ -122,7 +122,8 @@ def test_gemm_strided_views_and_canaries():
     assert (pad[:, :8] == 7).all() and (pad[:, 8 + N:] == 7).all()
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 1024), (70, 200, 384), (512, 1536, 4096)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 1024), (70, 200, 384), (512, 1536, 4096),
+                                   (300, 520, 400), (1024, 768, 4096)])   # the last four run on CTA pairs
 def test_gemm_i8(M, N, K):
     torch.manual_seed(2)
     x = torch.randn(M, K, device=dev())
@@ -133,6 +134,13 @@ def test_gemm_i8(M, N, K):
     got = F.gemm_i8(xq, wq, sx, sw)
     assert rel_err(got, want) < 1e-2
     assert rel_err(got, x @ w.t()) < 5e-2
+    # output inside a sentinel frame: partial tiles at the right and bottom edges must be clipped
+    pad = torch.full((M + 2, N + 16), 7.0, device=dev(), dtype=torch.bfloat16)
+    out = pad[1:M + 1, 8:8 + N]
+    F.gemm_i8(xq, wq, sx, sw, out=out)
+    assert rel_err(out, want) < 1e-2
+    assert (pad[0] == 7).all() and (pad[-1] == 7).all()
+    assert (pad[:, :8] == 7).all() and (pad[:, 8 + N:] == 7).all()
 
 
 def test_linear_autograd_matches_reference():
