@@ -171,6 +171,13 @@ class FusedDP:
         self.seq = 0
         self.overlap_ctas = int(os.environ.get("BRAIN_DP_CTAS", "32")) if overlap_ctas is None else overlap_ctas
         self.side = torch.cuda.Stream(device=dev)
+        # Overlap with backward pays when the reduce is long enough to be worth hiding: the bucket
+        # kernels under backward are held to ``overlap_ctas`` CTAs and every bucket costs two event
+        # hand-offs.  For a 0.6 B-parameter model the whole bf16 reduce-scatter is ~1 ms at 4 ranks:
+        # there is nothing to hide, and the overlapped form measured 1 % behind the unfused NCCL arm at
+        # 2 and 4 ranks.  ``auto`` turns the overlap on from 4 GB of fp32 gradients upwards.
+        mode = os.environ.get("BRAIN_DP_OVERLAP", "auto").lower()
+        self.overlap = mode in ("1", "on", "true") or (mode == "auto" and n * 4 >= (4 << 30))
         self._armed = False
         self.overlapped = 0          # buckets launched under backward in the last step (for reports)
         torch.cuda.synchronize(dev)
@@ -179,7 +186,7 @@ class FusedDP:
     # ------------------------------------------------------------------ overlap with backward
     def arm(self):
         """Called by the trainer right before the LAST micro-batch's forward/backward."""
-        if self.wire != "bf16":
+        if self.wire != "bf16" or not self.overlap:
             return
         self.tracker.begin()
         self.overlapped = 0
