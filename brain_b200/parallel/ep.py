@@ -94,7 +94,8 @@ class ExpertParallel:
         self.gemm_epoch += 1
         call("gemm_bf16_grouped_ep", xp, b_stacked, out, rows, n_out, K, b_stacked.stride(0), out.stride(0),
              int(b_mn), tile_group, int(b_group_rows), int(b_stacked.shape[0]), self._ptrs(src), self.world,
-             int(n_per_rank), pair_of_pos, pair_w, int(k), self.row_flags, ctypes.c_uint(self.gemm_epoch), 24,
+             int(n_per_rank), pair_of_pos, pair_w, int(k), self.row_flags, ctypes.c_uint(self.gemm_epoch),
+             16 if pair_w is None else 32,   # mover CTAs: copy-engine rows need few, weight-scaled rows go through registers
              ctypes.c_double(self.wait_seconds), stream_ptr())
         return out
 

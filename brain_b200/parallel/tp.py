@@ -62,6 +62,7 @@ class TensorParallel:
             # in-switch (NVLS multimem) form of the same all-reduce: used when the arena is bound to
             # an NVLink multicast object and BRAIN_TP_NVLS=1; own flags and epoch word
             import os
+            self.ag_copy_ctas = int(os.environ.get("BRAIN_TP_COPY_CTAS", "0"))   # 0: the kernel's default (12)
             self.nvls = os.environ.get("BRAIN_TP_NVLS") == "1" and self.arena.multicast_ptr(self.sig) != 0
             self.mm_sig = self.arena.alloc(self.world, torch.int64)
             self.mm_sig_ptrs = self._U64(*self.arena.peer_ptrs(self.mm_sig))
@@ -174,7 +175,7 @@ class TensorParallel:
             y = torch.empty(M, w.shape[0], device=x_shard.device, dtype=x_shard.dtype)
             call("gemm_bf16_tp", 1, x_full, w, y, M, w.shape[0], K, K, w.stride(0), y.stride(0),
                  self.rank, self.world, rows, self._U64(*self.arena.peer_ptrs(send)), self.row_flags,
-                 16, self.sig_ptrs, ctypes.c_uint(self.epoch), None, None,
+                 self.ag_copy_ctas, self.sig_ptrs, ctypes.c_uint(self.epoch), None, None,
                  ctypes.c_double(self.wait_seconds), stream_ptr())
             return y, x_full
         x_full = self.all_gather_rows(x_shard)

@@ -101,6 +101,28 @@ struct GemmArgs {
 #endif
 
 static constexpr int BM = 128;
+
+// Peer-memory copy of n 16-byte vectors by `nthreads` threads (this one is `tid`): every thread issues
+// U loads before its first store, so U x 16 bytes per thread are in flight.  (A load-then-store loop
+// keeps ONE load per thread in flight: with a peer round trip of about 2 us, 16 mover CTAs of 256
+// threads then pull 32 GB/s over a 770 GB/s link.)
+template <int U>
+__device__ __forceinline__ void copy_vecs_batched(uint4* __restrict__ dst, const uint4* src, size_t n, int tid,
+                                                  int nthreads) {
+  for (size_t v0 = tid; v0 < n; v0 += (size_t)nthreads * U) {
+    uint4 x[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = v0 + (size_t)u * nthreads;
+      if (v < n) x[u] = ld_volatile_u4(src + v);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = v0 + (size_t)u * nthreads;
+      if (v < n) dst[v] = x[u];
+    }
+  }
+}
 static constexpr int TILE_K_BYTES = 128;  // one swizzle row
 
 template <int BN>
@@ -217,8 +239,90 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int cta0 = (int)blockIdx.x - n_copy;
   const int cta_stride = (int)gridDim.x - n_copy;
 
-  if (cta0 < 0 && args.tp_mode == 3) {
-    // ---------------------------------------------------------- expert-dispatch data movers
+  if (cta0 < 0 && args.tp_mode == 3 && args.ep_w == nullptr &&
+      (size_t)K * 2 <= (size_t)Cfg::STAGE_BYTES) {
+    // ---------------------------------------------------------- expert-dispatch data movers (copy engine)
+    // Unscaled rows: one thread per mover CTA drives bulk copies (peer or local row -> a slot of this
+    // CTA's unused stage ring -> the expert-sorted operand buffer), R rows per slot, S slots in
+    // flight; the other warps zero-fill the padding rows at the tail of the tile.  A tile's routed
+    // rows form a prefix of its 128 positions (positions are handed out consecutively per expert
+    // and experts are padded to whole tiles); a tile where that does not hold takes the register path.
+    __shared__ int s_pair[BM];
+    const size_t row_bytes = (size_t)K * 2;
+    const int R = (int)(Cfg::STAGE_BYTES / row_bytes);
+    constexpr int LA = S - 2;
+    long n_ld = 0, n_st = 0;          // slot uses so far (thread 0 only)
+    for (int tmr = blockIdx.x; tmr < tiles_m; tmr += n_copy) {
+      if (args.tile_group[tmr] < 0) continue;    // unused tile: the GEMM side skips it too
+      __syncthreads();                           // s_pair of the previous tile is no longer read
+      if (threadIdx.x < BM) s_pair[threadIdx.x] = args.ep_pair_of_pos[tmr * BM + threadIdx.x];
+      const int n_valid = __syncthreads_count(threadIdx.x < BM && s_pair[threadIdx.x] >= 0);
+      const int prefix_ok = __syncthreads_and(threadIdx.x >= BM || ((s_pair[threadIdx.x] >= 0) == ((int)threadIdx.x < n_valid)));
+      uint8_t* tile_dst = reinterpret_cast<uint8_t*>(args.tp_full) + (size_t)tmr * BM * row_bytes;
+      if (!prefix_ok) {
+        for (int r = warp; r < BM; r += 8) {
+          uint4* dst = reinterpret_cast<uint4*>(tile_dst + (size_t)r * row_bytes);
+          const int pair = s_pair[r];
+          if (pair < 0) {
+            for (size_t v = lane; v < row_bytes / 16; v += 32) dst[v] = make_uint4(0u, 0u, 0u, 0u);
+            continue;
+          }
+          const int token = pair / args.ep_k;
+          const int src_rank = token / args.ep_n_per_rank;
+          const int local = token - src_rank * args.ep_n_per_rank;
+          copy_vecs_batched<8>(dst, reinterpret_cast<const uint4*>(args.tp_src.p[src_rank]) + (size_t)local * (row_bytes / 16),
+                               row_bytes / 16, lane, 32);
+        }
+      } else if (threadIdx.x == 0) {
+        const int G = (n_valid + R - 1) / R;
+        bool ok = true;
+        for (int g = 0; g < G + LA && ok; ++g) {
+          if (g < G) {
+            const int slot = (int)(n_ld % S);
+            if (n_ld >= S) tma_store_wait_read<1>();
+            const int r0 = g * R, r1 = min(r0 + R, n_valid);
+            mbar_expect_tx(&full[slot], (uint32_t)((r1 - r0) * row_bytes));
+            for (int r = r0; r < r1; ++r) {
+              const int pair = s_pair[r];
+              const int token = pair / args.ep_k;
+              const int src_rank = token / args.ep_n_per_rank;
+              const int local = token - src_rank * args.ep_n_per_rank;
+              bulk_load(smem + (size_t)slot * Cfg::STAGE_BYTES + (size_t)(r - r0) * row_bytes,
+                        reinterpret_cast<const uint8_t*>(args.tp_src.p[src_rank]) + (size_t)local * row_bytes,
+                        (uint32_t)row_bytes, &full[slot]);
+            }
+            ++n_ld;
+          }
+          const int k = g - LA;
+          if (k >= 0 && k < G) {
+            const int slot = (int)(n_st % S);
+            if (!mbar_wait(&full[slot], (uint32_t)((n_st / S) & 1))) {
+              set_error(args.err, ERR_WAIT_PEER);
+              ok = false;
+              break;
+            }
+            const int r0 = k * R, r1 = min(r0 + R, n_valid);
+            bulk_store(tile_dst + (size_t)r0 * row_bytes, smem + (size_t)slot * Cfg::STAGE_BYTES,
+                       (uint32_t)((r1 - r0) * row_bytes));
+            tma_store_commit();
+            ++n_st;
+          }
+        }
+        tma_store_wait<0>();                     // the tile's routed rows are written
+        asm volatile("fence.proxy.async;" ::: "memory");
+      } else if (warp >= 1) {
+        for (int r = n_valid + (warp - 1); r < BM; r += 7) {
+          uint4* dst = reinterpret_cast<uint4*>(tile_dst + (size_t)r * row_bytes);
+          for (size_t v = lane; v < row_bytes / 16; v += 32) dst[v] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) st_release_gpu_s32(args.tp_row_flags + tmr, (int)args.tp_epoch);
+    }
+  } else if (cta0 < 0 && args.tp_mode == 3) {
+    // ---------------------------------------------------------- expert-dispatch data movers (registers:
+    // rows scaled by their routing weight on the way, or rows wider than a ring slot)
     const size_t row_vecs = (size_t)K * 2 / 16;  // 16-byte vectors per row
     for (int tmr = blockIdx.x; tmr < tiles_m; tmr += n_copy) {
       if (args.tile_group[tmr] < 0) continue;    // unused tile: the GEMM side skips it too
@@ -237,16 +341,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const uint4* src = reinterpret_cast<const uint4*>(args.tp_src.p[src_rank]) + (size_t)local * row_vecs;
         if (args.ep_w) {
           const float g = args.ep_w[pair];
-          for (size_t v = lane; v < row_vecs; v += 32) {
-            uint4 x = ld_volatile_u4(src + v);
-            uint32_t* w32 = reinterpret_cast<uint32_t*>(&x);
+          for (size_t v0 = lane; v0 < row_vecs; v0 += 32 * 8) {
+            uint4 x[8];
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-              w32[q] = pack_bf16x2(__uint_as_float(w32[q] << 16) * g, __uint_as_float(w32[q] & 0xFFFF0000u) * g);
-            dst[v] = x;
+            for (int u = 0; u < 8; ++u)
+              if (v0 + u * 32 < row_vecs) x[u] = ld_volatile_u4(src + v0 + u * 32);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              if (v0 + u * 32 >= row_vecs) continue;
+              auto scaled = [g](uint32_t w) {
+                return pack_bf16x2(__uint_as_float(w << 16) * g, __uint_as_float(w & 0xFFFF0000u) * g);
+              };
+              dst[v0 + u * 32] = make_uint4(scaled(x[u].x), scaled(x[u].y), scaled(x[u].z), scaled(x[u].w));
+            }
           }
         } else {
-          for (size_t v = lane; v < row_vecs; v += 32) dst[v] = ld_volatile_u4(src + v);
+          copy_vecs_batched<8>(dst, src, row_vecs, lane, 32);
         }
       }
       __threadfence();
@@ -255,39 +365,87 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   } else if (cta0 < 0) {
     // ---------------------------------------------------------- all-gather data movers
-    __shared__ int s_ok;
+    // One thread per mover CTA drives the copy engine: bulk loads pull a peer's rows into this CTA's
+    // (otherwise unused) stage ring, bulk stores put them into the local landing buffer.  S slots
+    // of STAGE_BYTES are in flight per CTA without holding a register, which is what it takes to
+    // fill an NVLink with a few CTAs (a register copy keeps 32 KB per CTA in flight at best).
     const int per_rank = args.rows_per_rank / BM;
-    if (threadIdx.x == 0) s_ok = 1;
     if (blockIdx.x == 0 && threadIdx.x < args.tp_world) {  // "my shard is complete"
       __threadfence_system();
       st_release_sys_u64(reinterpret_cast<uint64_t*>(args.tp_sig.p[threadIdx.x]) + args.tp_rank,
                          (uint64_t)args.tp_epoch);
     }
-    __syncthreads();
-    const size_t row_vecs = (size_t)K * (I8 ? 1 : 2) / 16;  // 16-byte vectors per row
-    // tile rows in the order the GEMM consumes them, dealt round-robin to the copy CTAs
-    for (int i = blockIdx.x; i < tiles_m && s_ok; i += n_copy) {
-      const int tmr = (i + args.tp_rank * per_rank) % tiles_m;
-      const int src_rank = tmr / per_rank;
-      if (threadIdx.x == 0) {
-        const uint64_t* flag =
-            reinterpret_cast<const uint64_t*>(args.tp_sig.p[args.tp_rank]) + src_rank;
-        if (!wait_epoch(flag, args.tp_epoch, 0, args.tp_wait_limit)) {
-          set_error(args.err, ERR_WAIT_PEER);
-          s_ok = 0;
+    if (threadIdx.x == 0) {
+      const size_t row_bytes = (size_t)K * (I8 ? 1 : 2);
+      constexpr uint32_t SLOT = Cfg::STAGE_BYTES;
+      constexpr int LA = S - 2;          // loads run LA chunks ahead of the stores
+      // chunk cursor: (tile slot i of this CTA, byte offset inside the tile)
+      struct Cur {
+        int i;
+        size_t off;
+      };
+      auto tile_of = [&](int i) { return (i + args.tp_rank * per_rank) % tiles_m; };
+      auto tile_bytes = [&](int tmr) { return (size_t)min(BM, M - tmr * BM) * row_bytes; };
+      auto advance = [&](Cur& c) {
+        c.off += SLOT;
+        if (c.off >= tile_bytes(tile_of(c.i))) {
+          c.i += n_copy;
+          c.off = 0;
+        }
+      };
+      Cur ld{(int)blockIdx.x, 0}, stc{(int)blockIdx.x, 0};
+      bool ok = true;
+      int waited_rank = -1;
+      for (long n = 0; ok; ++n) {
+        const bool have_load = ld.i < tiles_m;
+        if (!have_load && stc.i >= tiles_m) break;
+        if (have_load) {
+          const int tmr = tile_of(ld.i);
+          const int src_rank = tmr / per_rank;
+          if (ld.off == 0 && src_rank != waited_rank) {   // first touch of a peer's shard: it must be complete
+            const uint64_t* flag = reinterpret_cast<const uint64_t*>(args.tp_sig.p[args.tp_rank]) + src_rank;
+            if (!wait_epoch(flag, args.tp_epoch, 0, args.tp_wait_limit)) {
+              set_error(args.err, ERR_WAIT_PEER);
+              ok = false;
+              break;
+            }
+            waited_rank = src_rank;
+          }
+          if (n >= S) tma_store_wait_read<1>();             // the store that last read this slot is done with it
+          const size_t tb = tile_bytes(tmr);
+          const uint32_t bytes = (uint32_t)min((size_t)SLOT, tb - ld.off);
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(args.tp_src.p[src_rank]) +
+                               (size_t)(tmr - src_rank * per_rank) * BM * row_bytes + ld.off;
+          const int slot = (int)(n % S);
+          mbar_expect_tx(&full[slot], bytes);
+          bulk_load(smem + (size_t)slot * SLOT, src, bytes, &full[slot]);
+          advance(ld);
+        }
+        const long k = n - LA;
+        if (k >= 0 && stc.i < tiles_m) {
+          const int slot = (int)(k % S);
+          if (!mbar_wait(&full[slot], (uint32_t)((k / S) & 1))) {
+            set_error(args.err, ERR_WAIT_PEER);
+            ok = false;
+            break;
+          }
+          const int tmr = tile_of(stc.i);
+          const size_t tb = tile_bytes(tmr);
+          const uint32_t bytes = (uint32_t)min((size_t)SLOT, tb - stc.off);
+          uint8_t* dst = reinterpret_cast<uint8_t*>(args.tp_full) + (size_t)tmr * BM * row_bytes + stc.off;
+          bulk_store(dst, smem + (size_t)slot * SLOT, bytes);
+          tma_store_commit();
+          const bool tile_done = stc.off + SLOT >= tb;
+          advance(stc);
+          if (tile_done) {
+            tma_store_wait<0>();                            // the tile's rows are written
+            asm volatile("fence.proxy.async;" ::: "memory");
+            __threadfence();
+            st_release_gpu_s32(args.tp_row_flags + tmr, (int)args.tp_epoch);
+          }
         }
       }
-      __syncthreads();
-      if (!s_ok) break;
-      const int rows = min(BM, M - tmr * BM);
-      const uint4* src = reinterpret_cast<const uint4*>(args.tp_src.p[src_rank]) +
-                         (size_t)(tmr - src_rank * per_rank) * BM * row_vecs;
-      uint4* dst = reinterpret_cast<uint4*>(args.tp_full) + (size_t)tmr * BM * row_vecs;
-      const size_t nvec = (size_t)rows * row_vecs;
-      for (size_t v = threadIdx.x; v < nvec; v += blockDim.x) dst[v] = ld_volatile_u4(src + v);
-      __threadfence();
-      __syncthreads();
-      if (threadIdx.x == 0) st_release_gpu_s32(args.tp_row_flags + tmr, (int)args.tp_epoch);
+      tma_store_wait<0>();
     }
   } else
 
@@ -1015,7 +1173,7 @@ BB_API int bb_gemm_bf16_tp(int mode, const void* A, const void* B, void* C, int 
     for (int r = 0; r < world; ++r) a.tp_src.p[r] = reinterpret_cast<void*>(a_src_ptrs[r]);
     a.tp_full = const_cast<void*>(A);
     a.tp_row_flags = row_flags;
-    a.tp_copy_ctas = copy_ctas > 0 ? copy_ctas : 16;
+    a.tp_copy_ctas = copy_ctas > 0 ? copy_ctas : 12;   // copy-engine movers: 12 x (S slots of a stage) in flight
     if (a.tp_copy_ctas > sm_count() / 2) a.tp_copy_ctas = sm_count() / 2;
   } else {
     a.tp_cmaps = static_cast<const CUtensorMap*>(cmaps);
