@@ -8,14 +8,15 @@ kernels' own NVLink peer loads.  Per layer and direction:
              straight out of every source rank's symmetric activation buffer into the expert-sorted,
              128-row-padded operand buffer and publish a flag per 128-row tile; the kernel's TMA
              producer waits for a tile's flag, so the GEMM of the first experts runs while the rows of
-             the last ones still cross NVLink (a remote row crosses once).  ``BRAIN_EP_FUSED_DISPATCH=0``
-             runs the gather as its own kernel before the GEMM;
+             the last ones still cross NVLink (a remote row crosses once); the alternative is the same
+             gather as its own full-width kernel before the GEMM;
   combine    inside the down-projection's grouped GEMM: its epilogue stores every output row straight
              into the slot of its (token, choice) pair in the token owner's symmetric slot buffer
              (plain peer stores, tile by tile, under the GEMM of the following tiles); after one
-             barrier the owner sums its k slots per token with the routing weights, all local.
-             ``BRAIN_EP_FUSED_COMBINE=0`` keeps the expert outputs local and lets the owner's combine
-             kernel pull them over NVLink instead.
+             barrier the owner sums its k slots per token with the routing weights, all local; the
+             alternative keeps the expert outputs local and lets the owner's combine kernel pull them
+             over NVLink.  ``BRAIN_EP_FUSED_DISPATCH`` / ``BRAIN_EP_FUSED_COMBINE`` = ``auto`` (default: inside
+             the GEMM from an expert GEMM width of 4096 columns, separate kernels below), ``1``, ``0``.
 
 Only routing metadata (top-k ids and weights, a few bytes per token) goes through
 ``torch.distributed``.  Ranks meet at bounded in-stream flag barriers (``bb_symm_barrier``) before
@@ -58,13 +59,31 @@ class ExpertParallel:
             self.sig_ptrs = self._U64(*self.arena.peer_ptrs(self.sig))
             # dispatch fused into the grouped GEMM: per-tile "rows are in place" flags and their epoch
             import os
-            self.fused_dispatch = os.environ.get("BRAIN_EP_FUSED_DISPATCH", "1") == "1"
-            self.fused_combine = os.environ.get("BRAIN_EP_FUSED_COMBINE", "1") == "1"
+            # Whether the row transfers ride inside the grouped GEMMs ("1"), run as their own full-width
+            # peer-load kernels ("0"), or are chosen per layer ("auto", the default): with small experts
+            # a routed row costs about as long to move (d x 2 bytes over NVLink) as to multiply
+            # (2 x d x n_out FLOPs), the mover CTAs taken from the GEMM cannot keep up, and the separate
+            # kernels measured 9 % faster on 2 ranks (128 experts, top-8, d 2048, expert width 768);
+            # from an expert GEMM width of 4096 upwards the multiply is long enough to hide the moves.
+            self._fuse_mode = (os.environ.get("BRAIN_EP_FUSED_DISPATCH", "auto").lower(),
+                               os.environ.get("BRAIN_EP_FUSED_COMBINE", "auto").lower())
+            # mover CTAs of the dispatch GEMM: plain rows ride the copy engine and need few; rows scaled
+            # by their routing weight on the way (backward) go through registers and need more
+            cc = os.environ.get("BRAIN_EP_COPY_CTAS", "16,32").split(",")
+            self.copy_ctas = (int(cc[0]), int(cc[-1]))
             self.row_flags = torch.zeros(1 << 16, device=self.device, dtype=torch.int32)
             self.gemm_epoch = 0
             self._ident = None
 
     # ------------------------------------------------------------------ helpers
+    def fuse_dispatch(self, n_out: int) -> bool:
+        m = self._fuse_mode[0]
+        return m == "1" or (m == "auto" and n_out >= 4096)
+
+    def fuse_combine(self, n_out: int) -> bool:
+        m = self._fuse_mode[1]
+        return m == "1" or (m == "auto" and n_out >= 4096)
+
     def _slot(self, kind, numel, dtype, parity):
         key = (kind, numel, dtype, parity)
         t = self._slots.get(key)
@@ -95,7 +114,7 @@ class ExpertParallel:
         call("gemm_bf16_grouped_ep", xp, b_stacked, out, rows, n_out, K, b_stacked.stride(0), out.stride(0),
              int(b_mn), tile_group, int(b_group_rows), int(b_stacked.shape[0]), self._ptrs(src), self.world,
              int(n_per_rank), pair_of_pos, pair_w, int(k), self.row_flags, ctypes.c_uint(self.gemm_epoch),
-             16 if pair_w is None else 32,   # mover CTAs: copy-engine rows need few, weight-scaled rows go through registers
+             self.copy_ctas[0 if pair_w is None else 1],
              ctypes.c_double(self.wait_seconds), stream_ptr())
         return out
 
@@ -219,6 +238,7 @@ class _ExpertsEP(torch.autograd.Function):
         dev = x.device
         s = stream_ptr()
         par = (ep.epoch // 2) & 1   # two barriers per call: slots alternate per call
+        fd, fc = ep.fuse_dispatch(ff2), ep.fuse_combine(ff2)   # decided per layer, remembered for backward
         # routing metadata of every rank (ids, weights) and the global load of my experts
         idx_all = ep._gather_meta(idx)                      # [W*n, k] int32
         w_all = ep._gather_meta(w.contiguous())             # [W*n, k] fp32
@@ -239,7 +259,7 @@ class _ExpertsEP(torch.autograd.Function):
         xs.copy_(x)
         ep._barrier()                                       # every rank's x and pos table are in place
         xp = torch.empty(max_rows, d, device=dev, dtype=x.dtype)
-        if ep.fused_dispatch:
+        if fd:
             gu = ep.dispatch_gemm(xs, n, pair_of_pos, None, k, xp, w_gate_up.view(El * ff2, d), tile_group, ff2, ff2)
         else:
             call("moe_gather", ep._ptrs(xs), W, n, pair_of_pos, None, k, xp, offsets, El, d, max_rows, s)
@@ -248,7 +268,7 @@ class _ExpertsEP(torch.autograd.Function):
         call("swiglu_fwd", gu, h, L(max_rows), ff, s)
         y = torch.empty(n, d, device=dev, dtype=x.dtype)
         wc = w.contiguous()
-        if ep.fused_combine:
+        if fc:
             # every (token, choice) pair of mine is produced by exactly one expert row somewhere, so
             # all n*k slots are overwritten by the GEMMs of this call: no zero fill
             ys = ep._slot("ys", n * k * d, x.dtype, par).view(n * k, d)
@@ -266,6 +286,7 @@ class _ExpertsEP(torch.autograd.Function):
         ctx.save_for_backward(xp, gu, h, yp_keep, wc, w_all, idx, idx_all, offsets, tile_group,
                               pos_tab.clone(), pair_of_pos)
         ctx.ep, ctx.w_refs = ep, (w_gate_up, w_down)
+        ctx.fuse = (fd, fc)
         ctx.dims = (n, d, k, El, ff, max_rows, W)
         return y
 
@@ -276,6 +297,7 @@ class _ExpertsEP(torch.autograd.Function):
         (xp, gu, h, yp, wc, w_all, idx, idx_all, offsets, tile_group, pos_keep,
          pair_of_pos) = ctx.saved_tensors
         ep = ctx.ep
+        fd, fc = ctx.fuse
         w_gate_up, w_down = ctx.w_refs
         n, d, k, El, ff, max_rows, W = ctx.dims
         dev = dy.device
@@ -288,7 +310,7 @@ class _ExpertsEP(torch.autograd.Function):
         pos_tab = ep._slot("pos", n_pairs_all, torch.int32, par)
         pos_tab.copy_(pos_keep)
         d_w = torch.empty(n, k, device=dev, dtype=torch.float32)
-        if ep.fused_combine:
+        if fc:
             # forward kept my pairs' expert outputs by pair: the routing-weight gradient is local
             from ..ops.moe_cuda import _u64
             ep._ensure_ident(n * k)
@@ -302,7 +324,7 @@ class _ExpertsEP(torch.autograd.Function):
             call("moe_rowdot", dys, ep._ptrs(yps), ep._ptrs(pos_tab), W, idx, L(ep.rank * n * k), k, El,
                  d_w, L(n * k), d, s)
         dyp = torch.empty(max_rows, d, device=dev, dtype=dy.dtype)
-        if ep.fused_dispatch:
+        if fd:
             dh = ep.dispatch_gemm(dys, n, pair_of_pos, w_all.reshape(-1), k, dyp, w_down.view(El * d, ff), tile_group,
                                   d, ff, b_mn=True)
         else:
@@ -312,7 +334,7 @@ class _ExpertsEP(torch.autograd.Function):
         dgu = torch.empty_like(gu)
         call("swiglu_bwd", dh, gu, dgu, L(max_rows), ff, s)
         dx = torch.empty(n, d, device=dev, dtype=dy.dtype)
-        if ep.fused_combine:
+        if fc:
             dxs = ep._slot("dxs", n * k * d, dy.dtype, par).view(n * k, d)
             ep.scatter_gemm(dgu, w_gate_up.view(El * 2 * ff, d), tile_group, 2 * ff, d, pair_of_pos, dxs, b_mn=True)
             ep._barrier()
