@@ -548,9 +548,16 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const int lim = kv_limit_row - kv0;  // columns <= lim are visible
       float mx = -INFINITY;
       if (!need_mask) {
+        // four independent running maxima: one chain of 32 dependent FMNMX would leave the two warps
+        // a scheduler holds here waiting on its latency
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          mx = fmaxf(mx, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
+        for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            m4[q] = fmaxf(m4[q], fmaxf(__uint_as_float(r0[i + q]), __uint_as_float(r1[i + q])));
+        }
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -587,7 +594,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const float m_use = ((m_ref == -INFINITY) ? 0.f : m_ref) - kFwdTruncLog2;
       const float sc = args.scale_log2;
       uint32_t pk[32];  // 64 probabilities as 32 packed bf16x2 words
-      float ls = 0.f;
+      float ls = 0.f, ls_b = 0.f;    // two running sums (alternating iterations) halve the add chain
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
         float a0 = exp2f(__uint_as_float(r0[i]) * sc - m_use);
@@ -600,12 +607,13 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (i + 32 > lim) b0 = 0.f;
           if (i + 33 > lim) b1 = 0.f;
         }
-        ls += (a0 + a1) + (b0 + b1);
+        if (i & 2) ls_b += (a0 + a1) + (b0 + b1);
+        else ls += (a0 + a1) + (b0 + b1);
         // integer-pipe packing: cvt.rn.bf16x2 would share the quarter-rate unit with ex2
         pk[i >> 1] = __byte_perm(__float_as_uint(a0), __float_as_uint(a1), 0x7632);         // keys  0..31 -> words  0..15
         pk[16 + (i >> 1)] = __byte_perm(__float_as_uint(b0), __float_as_uint(b1), 0x7632);  // keys 32..63 -> words 16..31
       }
-      l += ls;
+      l += ls + ls_b;
       tmem_st32(tS, pk);
       tmem_wait_st();
       tc_fence_before();
