@@ -394,3 +394,38 @@ def test_bucket_tracker_learns_counts_and_reruns_early_buckets():
     t.begin()                                   # and the new count is the expectation from now on
     got = [t.notify(k) for k in order + [1]]
     assert got[-1] == [2, 3] and got[3] == []
+
+
+def test_ep_row_transfers_go_inside_the_gemm_only_for_wide_experts(monkeypatch):
+    """``auto``: the dispatch / combine ride inside the grouped GEMMs from an expert GEMM width of 4096
+    columns; explicit 1 / 0 override it in both directions."""
+    from brain_b200.parallel.ep import ExpertParallel
+    ep = ExpertParallel.__new__(ExpertParallel)
+    ep._fuse_mode = ("auto", "auto")
+    assert not ep.fuse_dispatch(1536) and not ep.fuse_combine(1536)
+    assert ep.fuse_dispatch(4096) and ep.fuse_combine(8192)
+    ep._fuse_mode = ("1", "0")
+    assert ep.fuse_dispatch(64) and not ep.fuse_combine(1 << 20)
+
+
+def test_dp_buckets_cover_every_shard_once_and_in_backward_order():
+    from brain_b200.parallel.fused_dp import BucketTracker, make_buckets
+    n, world = 8 * 4 * 100, 4
+    b = make_buckets(n, world, 8 * 30)
+    covered = sorted((a, e) for _, a, e in b)
+    assert covered[0][0] == 0 and covered[-1][1] == n
+    assert all(covered[i][1] == covered[i + 1][0] for i in range(len(covered) - 1))
+    shard = n // world
+    assert all(a // shard == o and (e - 1) // shard == o for o, a, e in b), "a bucket crosses its owner's shard"
+    assert [a for _, a, _ in b] == sorted((a for _, a, _ in b), reverse=True), "buckets are listed from the end"
+    # a parameter spanning two buckets completes both; a second accumulation (tied weight) is awaited
+    slots = [(1, 0, 300), (2, 300, n - 300)]
+    t = BucketTracker(b, slots)
+    t.notify(2); t.notify(1); t.notify(1)
+    assert sorted(t.finish()) == list(range(len(b)))          # first step: learning, everything runs after backward
+    t.begin()
+    first = t.notify(2)
+    assert first and all(i not in first for i in t.of_param[1]), "buckets fed by parameter 1 must wait for it"
+    assert t.notify(1) == []                                   # parameter 1 accumulates twice per backward
+    rest = t.notify(1)
+    assert sorted(first + rest) == list(range(len(b))) and t.finish() == []
