@@ -385,13 +385,15 @@ class _ExpertsA2A(torch.autograd.Function):
             part = _Experts.apply(xa_g, wl_g, w_gate_up, w_down, li.contiguous(), counts)
         y = torch.empty_like(x)
         dist.reduce_scatter_tensor(y, part.detach().contiguous(), group=ep.group)
-        ctx.save_for_backward(xa_g, wl_g, part, mine)
+        # plain attributes, not save_for_backward: under activation recomputation saved tensors come
+        # back as other objects, and the inner backward below leaves its gradients on THESE leaves
+        ctx.inner = (xa_g, wl_g, part, mine)
         ctx.ep = ep
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        xa_g, wl_g, part, mine = ctx.saved_tensors
+        xa_g, wl_g, part, mine = ctx.inner
         ep = ctx.ep
         dya = ep._gather_meta(dy.contiguous())
         part.backward(dya)

@@ -1,8 +1,8 @@
 // Flash attention backward on tcgen05, recompute-based, deterministic (no atomics):
 //   delta = rowsum(dO * O)                                  fa_delta_kernel
 //   dQ    : one CTA per (query tile, query head, batch)     fa_bwd_dq_kernel
-//             per KV block:  S = Q K^T, dP = dO V^T  (TMEM) -> dS = P*(dP-delta)*scale (packed bf16,
-//                            written back over S in TMEM)
+//             per KV block:  S = Q K^T, dP = dO V^T  (TMEM; Q and dO are read from TMEM too)
+//                            -> dS = P*(dP-delta)*scale (packed bf16, written back over dP in TMEM)
 //                            dQ += dS K               (TMEM accumulator)
 //   dK,dV : one CTA per (KV tile, KV head, batch), looping over the query heads of the GQA group
 //           and the query tiles that can see the KV tile   fa_bwd_dkv_kernel
@@ -51,27 +51,6 @@ struct FaBwdArgs {
 #endif
 
 static constexpr int SUB = 128 * 128;  // bytes of a [128 rows][64 bf16] swizzled sub-tile
-
-// Write 32 consecutive bf16 (columns c0..c0+31 of `row`) of a [128][128] operand tile stored as two
-// K-major 128B-swizzled sub-tiles.
-__device__ __forceinline__ void store_row_chunk32(uint8_t* tile, int row, int c, const uint32_t (&pk)[16]) {
-  uint8_t* prow = tile + (c >> 1) * SUB + row * 128;
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    const int chunk = ((c & 1) * 4 + q) ^ (row & 7);
-    *reinterpret_cast<uint4*>(prow + chunk * 16) =
-        make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
-  }
-}
-
-// K-major A/B operand: k-step t covers 16 columns: sub-tile t/4, 32-byte offset (t%4)
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int t) {
-  return umma_smem_desc(base + (t / 4) * SUB + (t % 4) * 32, 16, 1024);
-}
-// MN-major B operand over a [rows = K][HD] tile: k-step t covers 16 rows
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int t) {
-  return umma_smem_desc(base + t * 2048, SUB, 1024);
-}
 
 // Hoisted descriptor arithmetic for the single MMA-issuing thread: the upper descriptor word is a
 // constant, the lower word is (address >> 4) | (lbo >> 4) << 16, so stepping through a tile is one
