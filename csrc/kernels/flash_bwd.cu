@@ -1,5 +1,5 @@
 // Flash attention backward on tcgen05, recompute-based, deterministic (no atomics):
-//   delta = rowsum(dO * O)                                  taken in the dQ kernel while it parks dO
+//   delta = rowsum(dO * O)                                  fa_delta_kernel
 //   dQ    : one CTA per (query tile, query head, batch)     fa_bwd_dq_kernel
 //             per KV block:  S = Q K^T, dP = dO V^T  (TMEM; Q and dO are read from TMEM too)
 //                            -> dS = P*(dP-delta)*scale (packed bf16, written back over dP in TMEM)
@@ -21,9 +21,7 @@ namespace bb {
 struct FaBwdArgs {
   const __nv_bfloat16* q;     // [B*T, ldq]: the dQ kernel parks its tile's rows in TMEM
   const __nv_bfloat16* dout;  // [B*T, lddo]
-  const __nv_bfloat16* out;   // [B*T, ldo]: forward output (delta = rowsum(dO * O) is taken in the dQ kernel)
-  int ldq, lddo, ldo;
-  float* delta_out;           // [B, hq, T]: written by the dQ kernel, read by the dK/dV kernel
+  int ldq, lddo;
   const float* lse;    // [B, hq, T] natural log
   const float* delta;  // [B, hq, T]
   __nv_bfloat16* dQ;
@@ -68,6 +66,42 @@ __device__ __forceinline__ uint64_t desc_of(uint32_t lo) { return ((uint64_t)DES
 // offsets, in 16-byte units, of k-step t inside a tile
 __device__ __forceinline__ constexpr uint32_t kstep_kmajor(int t) { return (t / 4) * (SUB >> 4) + (t % 4) * 2; }
 __device__ __forceinline__ constexpr uint32_t kstep_mnmajor(int t) { return t * 128; }
+
+// ------------------------------------------------------------------------------------ delta
+// delta[b, h, t] = sum_d dO[t, h, d] * O[t, h, d].  hd / 8 lanes per (row, head), 16 bytes per lane and
+// tensor: the two rows are read once, fully coalesced (the first form read 4 bytes per lane and
+// reached 0.37 of the copy bandwidth).  Taking delta inside the dQ kernel instead (the thread that
+// parks a dO row in TMEM also reading the O row) was built and measured slower: 1003 against 984 us
+// for the whole backward, the row dot product sits in the kernel's serial prologue.
+template <int LANES>   // lanes per (row, head) = hd / 8: 16 (hd 128) or 8 (hd 64)
+__global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ o, int ldo,
+                                const __nv_bfloat16* __restrict__ dout, int lddo,
+                                float* __restrict__ delta, int B, int T, int hq) {
+  const long gt = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long item = gt / LANES;            // (row, head)
+  const int sub = (int)(gt % LANES);
+  const long total = (long)B * T * hq;
+  const bool live = item < total;
+  const long row = live ? item / hq : 0;
+  const int h = live ? (int)(item % hq) : 0;
+  float acc = 0.f;
+  if (live) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + row * ldo + h * (LANES * 8) + sub * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(dout + row * lddo + h * (LANES * 8) + sub * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      acc += __uint_as_float(aw[q] << 16) * __uint_as_float(gw[q] << 16);
+      acc += __uint_as_float(aw[q] & 0xFFFF0000u) * __uint_as_float(gw[q] & 0xFFFF0000u);
+    }
+  }
+#pragma unroll
+  for (int m = LANES / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+  if (live && sub == 0) {
+    const int b = (int)(row / T), t = (int)(row % T);
+    delta[((size_t)b * hq + h) * T + t] = acc;
+  }
+}
 
 // ------------------------------------------------------------------------------------ dQ
 // One CTA per (query tile, query head, batch) walks the KV blocks its rows can see.  Every MMA is
@@ -150,36 +184,6 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
 static constexpr int kPolyEvery = BB_FA_POLY_EVERY;
 static constexpr int NWG = 4;
 static constexpr int WCOLS = 128 / NWG;               // score columns per warpgroup and block
-// Same for a dO row, which is also multiplied into the matching row of O on the way:
-// returns sum_d dO[d] * O[d] (the softmax backward's delta).
-template <int HD>
-__device__ __forceinline__ float row_to_tmem_dot(const __nv_bfloat16* src, const __nv_bfloat16* o, bool valid,
-                                                 uint32_t taddr) {
-  float acc = 0.f;
-#pragma unroll
-  for (int c = 0; c < HD / 64; ++c) {
-    uint32_t w[32];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint4 x = valid ? __ldg(reinterpret_cast<const uint4*>(src + c * 64) + i) : make_uint4(0u, 0u, 0u, 0u);
-      const uint4 y = valid ? __ldg(reinterpret_cast<const uint4*>(o + c * 64) + i) : make_uint4(0u, 0u, 0u, 0u);
-      w[4 * i] = x.x;
-      w[4 * i + 1] = x.y;
-      w[4 * i + 2] = x.z;
-      w[4 * i + 3] = x.w;
-      const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        acc += __uint_as_float(xw[q] << 16) * __uint_as_float(yw[q] << 16);
-        acc += __uint_as_float(xw[q] & 0xFFFF0000u) * __uint_as_float(yw[q] & 0xFFFF0000u);
-      }
-    }
-    tmem_st32(taddr + c * 32, w);
-  }
-  tmem_wait_st();
-  return acc;
-}
-
 static constexpr int BWD_THREADS = 64 + 128 * NWG;    // producer warp, MMA warp, softmax warps
 
 // Named barrier over the 128 threads of softmax warpgroup g (barrier 0 is __syncthreads).
@@ -368,28 +372,18 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const size_t stat = ((size_t)b * args.hq + h) * T + (row_ok ? q_idx : 0);
     const float lse2 = row_ok ? args.lse[stat] * 1.4426950408889634f - kTruncLog2 : INFINITY;
     const float scale_t = args.scale * kTruncScale;
+    const float dlt = row_ok ? -args.delta[stat] * scale_t : 0.f;  // -delta * scale
     const uint32_t tD = tDP + g * WCOLS + lane_sel;
     const uint32_t tSg = tS + g * WCOLS + lane_sel;
     static_assert(WCOLS == 32, "one 32-column TMEM access per phase and thread");
     // warpgroup 0 parks the Q rows of the tile in TMEM, warpgroup 1 the dO rows (one row per thread)
-    // and, having the row in hand, takes delta = rowsum(dO * O) for it: shared with the other
-    // warpgroups through s_delta and left in global memory for the dK/dV kernel.
-    __shared__ float s_delta[128];
     if (g < 2) {
       const size_t grow = (size_t)(b * T + (row_ok ? q_idx : 0));
-      if (g == 0) {
-        row_to_tmem<HD>(args.q + grow * args.ldq + h * HD, row_ok, tQ + lane_sel);
-      } else {
-        const float d = row_to_tmem_dot<HD>(args.dout + grow * args.lddo + h * HD, args.out + grow * args.ldo + h * HD,
-                                            row_ok, tDO + lane_sel);
-        s_delta[row] = d;
-        if (row_ok) args.delta_out[stat] = d;
-      }
+      const __nv_bfloat16* src = (g == 0 ? args.q + grow * args.ldq : args.dout + grow * args.lddo) + h * HD;
+      row_to_tmem<HD>(src, row_ok, (g == 0 ? tQ : tDO) + lane_sel);
       tc_fence_before();
       mbar_arrive(qdo_ready);
     }
-    asm volatile("bar.sync 5, %0;" ::"n"(128 * NWG) : "memory");   // all softmax threads: s_delta is complete
-    const float dlt = row_ok ? -s_delta[row] * scale_t : 0.f;       // -delta * scale
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
       // ---- phase 1: P (kept packed in registers)
@@ -948,16 +942,25 @@ BB_API int bb_flash_bwd(const void* q, int ldq, const void* k, int ldk, const vo
   if (B <= 0 || T <= 0 || S < T || hq % hk) return BB_EARG;
   if ((lddq % 8) || (lddk % 8) || (lddv % 8)) return BB_EARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // 16-byte row loads in the dQ kernel (Q, dO and O rows): the pitches must keep them aligned
-  if ((ldq % 8) || (ldo % 8) || (lddo % 8) || (hd != 64 && hd != 128)) return BB_EARG;
+  {
+    // 16-byte loads: the row pitches and the head offset must keep them aligned
+    if ((ldo % 8) || (lddo % 8) || (hd != 64 && hd != 128)) return BB_EARG;
+    const long threads = (long)B * T * hq * (hd / 8);
+    const int blocks = (int)((threads + 255) / 256);
+    if (hd == 128)
+      fa_delta_kernel<16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)out, ldo, (const __nv_bfloat16*)dout, lddo,
+                                                 delta, B, T, hq);
+    else
+      fa_delta_kernel<8><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)out, ldo, (const __nv_bfloat16*)dout, lddo,
+                                                delta, B, T, hq);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
   FaBwdArgs a{};
   a.q = static_cast<const __nv_bfloat16*>(q);
   a.dout = static_cast<const __nv_bfloat16*>(dout);
-  a.out = static_cast<const __nv_bfloat16*>(out);
   a.ldq = ldq;
   a.lddo = lddo;
-  a.ldo = ldo;
-  a.delta_out = delta;
   a.lse = lse;
   a.delta = delta;
   a.dQ = static_cast<__nv_bfloat16*>(dq);

@@ -287,9 +287,11 @@ def _trainer3d_worker(rank, world, tp, pp, sched, dp=1, recompute=False):
 @pytest.mark.parametrize("tp,pp,sched,dp,recompute", [(2, 2, "1f1b", 1, False), (2, 1, "1f1b", 1, False),
                                                        (1, 2, "gpipe", 1, True), (1, 2, "1f1b", 2, False),
                                                        (2, 1, "1f1b", 2, True)])
-def test_trainer3d_matches_single_process(tp, pp, sched, dp, recompute):
+def test_trainer3d_matches_single_process(tp, pp, sched, dp, recompute, monkeypatch):
     """Tensor x pipeline parallel training on gloo CPU ranks reproduces the single-process step:
-    same losses, same global gradient norm, same weights after two optimiser steps."""
+    same losses, same global gradient norm, same weights after two optimiser steps.  The gpipe case
+    also posts its stage-to-stage receives one op ahead (second step on), the others where needed."""
+    monkeypatch.setenv("BRAIN_PP_PREFETCH", "1" if sched == "gpipe" else "0")
     from brain_b200.engine import Trainer
     from brain_b200.models.config import QwenConfig
     from brain_b200.models.qwen3 import Qwen3
