@@ -216,3 +216,20 @@ def test_native_cpu_gemm_and_linear_autograd():
         assert torch.allclose(g, r, rtol=1e-4, atol=1e-3)
     xn, wn = torch.randn(37, 100), torch.randn(100)
     assert torch.allclose(cpu_native.rmsnorm(xn, wn, 1e-6), ref.rmsnorm(xn, wn, 1e-6), rtol=1e-4, atol=1e-5)
+
+
+def test_bench_reference_arm_reports_unavailable_and_exits_zero():
+    """``bench.py --impl reference`` cannot run the reference here (a Rust / graphics-API workspace): it
+    must say so in one JSON line and exit 0, whatever the other flags are."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "2",
+                        "--steps", "3", "--warmup", "3"], capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [l for l in p.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and isinstance(d.get("unavailable"), str) and d["unavailable"]
