@@ -10,7 +10,9 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def run(impl, dev, rank, world, steps=3):
+def run(impl, dev, rank, world, steps=3, overlap=None):
+    if overlap is not None:     # read when the fused step is built: buckets under backward (1) or after it (0)
+        os.environ["BRAIN_DP_OVERLAP"] = overlap
     from brain_b200.engine import Trainer
     from brain_b200.models.config import QwenConfig
     from brain_b200.models.qwen3 import Qwen3
@@ -40,9 +42,14 @@ def main():
     from brain_b200.ops import _cuda
 
     w_nccl, l_nccl = run("nccl", dev, rank, world)
-    w_fused, l_fused = run("fused", dev, rank, world)
+    w_fused, l_fused = run("fused", dev, rank, world, overlap="0")
+    # the same with every gradient bucket's reduce-scatter started under the last micro-batch's backward
+    # (what large models get by default); four steps so that the learnt schedule is used at least twice
+    w_over, l_over = run("fused", dev, rank, world, steps=3, overlap="1")
     _cuda.check_error()
-    err = ((w_fused - w_nccl).norm() / w_nccl.norm()).item()
+    err = max(((w_fused - w_nccl).norm() / w_nccl.norm()).item(),
+              ((w_over - w_nccl).norm() / w_nccl.norm()).item())
+    assert torch.equal(w_over, w_fused), "overlapped and post-backward bucket reduce must give the same bits"
     # every rank must hold identical weights after the all-gather
     ref = w_fused.clone()
     dist.broadcast(ref, 0)
