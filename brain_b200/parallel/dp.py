@@ -35,6 +35,13 @@ class DataParallel:
         self.opt = AdamW(self.stores[0], betas=betas, eps=eps)
         self.n_micro = 0
         self.last_losses: List[float] = []
+        # the native CPU GEMM runs a worker pool per calling thread: give every replica its share of
+        # the cores unless the user fixed the count (two pools of 8 on 8 cores measured 158 tok/s on
+        # GPT-2 small, two of 4 measured 208)
+        import os
+        from ..ops import cpu_native
+        if cpu_native.enabled() and "BRAIN_CPU_THREADS" not in os.environ:
+            cpu_native.threads = max(1, (os.cpu_count() or 1) // n_workers)
 
     def forward_backward(self, micro_batches: Sequence, loss_scale: Optional[float] = None) -> float:
         """``micro_batches``: list of (tokens, targets).  Gradients accumulate in each replica's
