@@ -25,6 +25,7 @@
 #include <cstdint>
 #include <atomic>
 #include <condition_variable>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <memory>
@@ -327,7 +328,12 @@ static int gemm_impl(const float* A, const float* B, float* C, int M, int N, int
 
 BBH_API int bbh_cpu_gemm(const float* A, const float* B, float* C, int M, int N, int K, int lda, int ldb,
                          int ldc, int ta, int tb, float alpha, float beta, int threads) {
-  static const bool wide = __builtin_cpu_supports("avx512f");
+  // BRAIN_CPU_ISA=avx2 keeps the 6 x 16 AVX2 micro-kernel on CPUs that have AVX-512 (tests cover both)
+  static const bool wide = [] {
+    const char* e = std::getenv("BRAIN_CPU_ISA");
+    if (e && std::strcmp(e, "avx2") == 0) return false;
+    return (bool)__builtin_cpu_supports("avx512f");
+  }();
   return wide ? gemm_impl<MicroAvx512>(A, B, C, M, N, K, lda, ldb, ldc, ta, tb, alpha, beta, threads)
               : gemm_impl<MicroAvx2>(A, B, C, M, N, K, lda, ldb, ldc, ta, tb, alpha, beta, threads);
 }

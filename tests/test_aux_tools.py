@@ -233,3 +233,26 @@ def test_bench_reference_arm_reports_unavailable_and_exits_zero():
     assert len(lines) == 1
     d = json.loads(lines[0])
     assert d["impl"] == "reference" and isinstance(d.get("unavailable"), str) and d["unavailable"]
+
+
+def test_native_cpu_gemm_on_the_avx2_micro_kernel():
+    """On a CPU with AVX-512 the GEMM picks its 12 x 32 tile at run time; ``BRAIN_CPU_ISA=avx2`` (read once per
+    process, hence the child process) keeps the 6 x 16 AVX2 tile, which must give the same products."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import sys, torch\n"
+        f"sys.path.insert(0, {root!r})\n"
+        "from brain_b200.ops import cpu_native\n"
+        "torch.manual_seed(1)\n"
+        "for M, N, K in ((5, 17, 9), (97, 130, 300), (256, 515, 257)):\n"
+        "    a, b = torch.randn(M, K), torch.randn(N, K)\n"
+        "    want = a @ b.t()\n"
+        "    assert torch.allclose(cpu_native.gemm(a, b, tb=True), want, rtol=1e-4, atol=1e-3)\n"
+        "    assert torch.allclose(cpu_native.gemm(a.t().contiguous(), b.t().contiguous(), ta=True), want, rtol=1e-4, atol=1e-3)\n"
+        "print('ok')\n")
+    p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
+                       env=dict(os.environ, BRAIN_CPU_ISA="avx2"))
+    assert p.returncode == 0 and "ok" in p.stdout, p.stderr[-2000:]
