@@ -62,7 +62,7 @@ class TensorParallel:
             # in-switch (NVLS multimem) form of the same all-reduce: used when the arena is bound to
             # an NVLink multicast object and BRAIN_TP_NVLS=1; own flags and epoch word
             import os
-            self.ag_copy_ctas = int(os.environ.get("BRAIN_TP_COPY_CTAS", "0"))   # 0: the kernel default (8)
+            self.ag_copy_ctas = int(os.environ.get("BRAIN_TP_COPY_CTAS", "0"))   # 0: the kernel default (four per rank)
             self.nvls = os.environ.get("BRAIN_TP_NVLS") == "1" and self.arena.multicast_ptr(self.sig) != 0
             self.mm_sig = self.arena.alloc(self.world, torch.int64)
             self.mm_sig_ptrs = self._U64(*self.arena.peer_ptrs(self.mm_sig))

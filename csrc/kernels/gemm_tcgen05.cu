@@ -1174,7 +1174,9 @@ BB_API int bb_gemm_bf16_tp(int mode, const void* A, const void* B, void* C, int 
     for (int r = 0; r < world; ++r) a.tp_src.p[r] = reinterpret_cast<void*>(a_src_ptrs[r]);
     a.tp_full = const_cast<void*>(A);
     a.tp_row_flags = row_flags;
-    a.tp_copy_ctas = copy_ctas > 0 ? copy_ctas : 8;   // copy-engine movers (4: 918 us, 8: 675 us, 12: 686 us at 16384 x 6144 x 4096 on 2 ranks)
+    // copy-engine movers: four per rank (16384 rows x 4096: 2 ranks 4 -> 918 us, 8 -> 675, 12 -> 686;
+    // 4 ranks 8 -> 511 us, 16 -> 373, 24 -> 384), at most 32
+    a.tp_copy_ctas = copy_ctas > 0 ? copy_ctas : (4 * world < 32 ? 4 * world : 32);
     if (a.tp_copy_ctas > sm_count() / 2) a.tp_copy_ctas = sm_count() / 2;
   } else {
     a.tp_cmaps = static_cast<const CUtensorMap*>(cmaps);
