@@ -25,6 +25,11 @@ def cpu_dp(args) -> dict:
     from ..models.gpt2 import Gpt2
     from ..parallel.dp import DataParallel
     torch.manual_seed(0)
+    # the native GEMM of csrc/cpu is the CPU backend's linear layer in this configuration unless the
+    # caller chose (BRAIN_CPU_NATIVE=0 runs the PyTorch ops, the oracle, for comparison)
+    import os
+    os.environ.setdefault("BRAIN_CPU_NATIVE", "1")
+    from ..ops import cpu_native
     cfg = GptConfig(vocab=50257, block_size=1024, n_layers=args.layers, d_model=768, n_heads=12, d_ff=3072)
     workers, B, T = 2, 4, 128
 
@@ -52,6 +57,7 @@ def cpu_dp(args) -> dict:
             "value": workers * B * T / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms, "steps": args.steps,
             "loss_first": losses[0], "loss_last": losses[-1], "loss_decreased": losses[-1] < losses[0],
             "build_s": build_s, "threads": torch.get_num_threads(),
+            "linear": "native csrc/cpu GEMM" if cpu_native.enabled() else "PyTorch ops",
             "gradcheck": {"model": "gpt 2-layer d64", "tensors": len(report.entries), "failures": len(fails),
                           "worst_rel": worst.rel if worst else None, "worst_name": worst.name if worst else None},
             "dtype": "fp32", "data": "synthetic"}
