@@ -66,7 +66,7 @@ class MoeBlock(nn.Module):
         self.ln2 = nn.Parameter(torch.ones(d))
         self.moe = MoeLayer(cfg, ep)
 
-    def forward(self, x, B, T, cos, sin, pos):
+    def forward(self, x, B, T, cos, sin, pos, recompute_experts=False):
         cfg = self.cfg
         hq, hk, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
         h = F.rmsnorm(x, self.ln1, cfg.rms_eps)
@@ -84,7 +84,14 @@ class MoeBlock(nn.Module):
         o = flash_attention(qk[:, : hq * hd], qk[:, hq * hd:], v, B, T, hq, hk, hd, causal=True)
         x = x + F.linear(o, self.wo)
         h2 = F.rmsnorm(x, self.ln2, cfg.rms_eps)
-        y, aux = self.moe(h2)
+        if recompute_experts:
+            # the routed rows and the experts' intermediates (top_k rows of d + 3*ff values per token)
+            # are most of a block's activations: keep only the layer's input and run router, dispatch,
+            # experts and combine again inside backward; the attention half keeps what it saved
+            from torch.utils.checkpoint import checkpoint
+            y, aux = checkpoint(self.moe, h2, use_reentrant=False)
+        else:
+            y, aux = self.moe(h2)
         return x + y, aux
 
 
@@ -145,6 +152,7 @@ class MoeModel(nn.Module):
         pos = torch.arange(T, device=x.device, dtype=torch.int32).repeat(B)
         aux_total = None
         recompute = getattr(self, "recompute_blocks", False) and torch.is_grad_enabled()
+        experts_only = getattr(self, "recompute_experts", False) and torch.is_grad_enabled() and not recompute
         for blk in self.blocks:
             if recompute:
                 # activation recomputation: keep only the block input, re-run the block (including
@@ -152,7 +160,7 @@ class MoeModel(nn.Module):
                 from torch.utils.checkpoint import checkpoint
                 x, aux = checkpoint(blk, x, B, T, cos, sin, pos, use_reentrant=False)
             else:
-                x, aux = blk(x, B, T, cos, sin, pos)
+                x, aux = blk(x, B, T, cos, sin, pos, experts_only)
             aux_total = aux if aux_total is None else aux_total + aux
         return F.rmsnorm(x, self.norm, self.cfg.rms_eps), aux_total
 

@@ -256,7 +256,8 @@ def train_ep(args) -> dict:
                 p.fill_(1.0)
             else:
                 p.normal_(0.0, 0.02, generator=gen_local if ".moe.w_" in name else gen)
-    model.recompute_blocks = not args.no_recompute
+    model.recompute_blocks = not (args.no_recompute or args.recompute_experts)
+    model.recompute_experts = args.recompute_experts
     tr = TrainerEP(model, dev, dtype=torch.bfloat16)
     g = torch.Generator().manual_seed(rank)
     B, T = args.seqs_per_gpu, args.seq
@@ -275,7 +276,7 @@ def train_ep(args) -> dict:
             "value": count / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "ms_per_step": ms, "steps": args.steps,
             "warmup": args.warmup, "seqs_per_gpu": B, "seq_len": T, "micro_batch": args.micro_batch, "impl": args.impl,
             "layers": cfg.n_layers, "experts": cfg.n_experts, "final_loss": float(loss_t),
-            "recompute_blocks": bool(model.recompute_blocks), "shared_params_b": tr.shared.n_train / 1e9, "expert_params_per_rank_b": tr.expert.n_train / 1e9,
+            "recompute_blocks": bool(model.recompute_blocks), "recompute_experts": bool(model.recompute_experts), "shared_params_b": tr.shared.n_train / 1e9, "expert_params_per_rank_b": tr.expert.n_train / 1e9,
             "mem_gb": torch.cuda.max_memory_allocated() / 2**30, "gpu_launches": _cuda.launch_count - launches0,
             "dtype": "bf16", "data": "synthetic", "timing": "CUDA events, max over ranks"}
 
@@ -295,6 +296,8 @@ def main(argv=None):
     ap.add_argument("--recompute", action="store_true",
                     help="train-3d: keep block inputs only and re-run the blocks in backward")
     ap.add_argument("--no-recompute", action="store_true", help="train-ep: keep all block activations (more memory)")
+    ap.add_argument("--recompute-experts", action="store_true",
+                    help="train-ep: re-run only the expert layers in backward (attention keeps its activations)")
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--layers", type=int, default=0, help="override depth (debug; invalidates the number)")
     ap.add_argument("--model", default="8b")

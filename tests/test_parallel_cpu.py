@@ -316,7 +316,7 @@ def test_trainer3d_matches_single_process(tp, pp, sched, dp, recompute, monkeypa
         assert torch.allclose(got[k], v.detach().reshape(-1), atol=2e-4), k
 
 
-def _trainer_ep_worker(rank, world):
+def _trainer_ep_worker(rank, world, recompute="none"):
     from brain_b200.models.config import MoeConfig
     from brain_b200.models.moe import MoeModel
     from brain_b200.parallel.ep import ExpertParallel
@@ -325,6 +325,8 @@ def _trainer_ep_worker(rank, world):
                     top_k=2, d_ff=16, aux_coef=0.0, z_coef=0.0, tie_embeddings=True)
     ep = ExpertParallel(impl="nccl")
     model = MoeModel(cfg, ep=ep).init_weights(7)
+    model.recompute_blocks = recompute == "blocks"
+    model.recompute_experts = recompute == "experts"
     tr = TrainerEP(model, "cpu", betas=(0.9, 0.95), weight_decay=0.1, grad_clip=1.0)
     g = torch.Generator().manual_seed(3)
     toks = torch.randint(0, 64, (4, 16), generator=g, dtype=torch.int32)
@@ -338,15 +340,18 @@ def _trainer_ep_worker(rank, world):
             "e_first": model.blocks[0].moe.e_first, "e_local": model.blocks[0].moe.e_local}
 
 
-def test_trainer_ep_two_gloo_ranks_match_single_process():
+@pytest.mark.parametrize("recompute", ["none", "experts", "blocks"])
+def test_trainer_ep_two_gloo_ranks_match_single_process(recompute):
     """Expert-parallel training (experts split over 2 CPU ranks, each rank its own sequences)
     reproduces single-process training on all sequences: summed losses, global gradient norm,
-    shared weights and each rank's expert slice after two optimiser steps."""
+    shared weights and each rank's expert slice after two optimiser steps.  The same holds when
+    backward re-runs only the expert layers, or whole blocks, instead of keeping their activations
+    (the re-run repeats the dispatch and combine collectives on every rank alike)."""
     from brain_b200.engine import Trainer
     from brain_b200.models.config import MoeConfig
     from brain_b200.models.moe import MoeModel
     from brain_b200.parallel.trainer_ep import is_expert_param
-    res = run_ranks(_trainer_ep_worker, 2)
+    res = run_ranks(_trainer_ep_worker, 2, recompute)
     cfg = MoeConfig(vocab=64, block_size=16, n_layers=2, d_model=32, n_heads=4, n_kv_heads=2, head_dim=8, n_experts=4,
                     top_k=2, d_ff=16, aux_coef=0.0, z_coef=0.0, tie_embeddings=True)
     full = MoeModel(cfg).init_weights(7)
@@ -431,3 +436,25 @@ def test_dp_buckets_cover_every_shard_once_and_in_backward_order():
     assert t.notify(1) == []                                   # parameter 1 accumulates twice per backward
     rest = t.notify(1)
     assert sorted(first + rest) == list(range(len(b))) and t.finish() == []
+
+
+def test_experts_only_recompute_keeps_loss_and_gradients_with_router_losses():
+    """Re-running only the expert layers in backward changes neither the loss nor any gradient,
+    the router's auxiliary and z losses included."""
+    from brain_b200.models.config import MoeConfig
+    from brain_b200.models.moe import MoeModel
+    cfg = MoeConfig(vocab=64, block_size=16, n_layers=2, d_model=32, n_heads=4, n_kv_heads=2, head_dim=8, n_experts=4,
+                    top_k=2, d_ff=16, aux_coef=0.01, z_coef=0.001, tie_embeddings=True)
+    g = torch.Generator().manual_seed(5)
+    toks = torch.randint(0, 64, (2, 16), generator=g, dtype=torch.int32)
+    tgts = torch.randint(0, 64, (2, 16), generator=g)
+    out = {}
+    for mode in ("none", "experts"):
+        m = MoeModel(cfg).init_weights(11)
+        m.recompute_experts = mode == "experts"
+        loss = m.loss(toks, tgts)
+        loss.backward()
+        out[mode] = (float(loss), {n: p.grad.clone() for n, p in m.named_parameters()})
+    assert out["none"][0] == out["experts"][0]
+    for n, gref in out["none"][1].items():
+        assert torch.equal(out["experts"][1][n], gref), n
