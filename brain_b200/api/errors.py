@@ -65,6 +65,8 @@ def from_exception(e: BaseException) -> ApiError:
             return ApiError("context_length_exceeded", msg)
         if e.kind == "not_implemented":
             return ApiError("not_implemented", str(e))
+        if e.kind == "rate_limit_exceeded":     # the scheduler's admission policy turned it away
+            return ApiError("rate_limit_exceeded", "The model is busy; retry shortly.", 1)
         if e.kind == "cancelled":
             return ApiError("invalid_request", "request cancelled")
         return ApiError("invalid_request", str(e))

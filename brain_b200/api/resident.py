@@ -264,8 +264,11 @@ class LlmResident(ResidentModel):
                                  kv_dtype=kv_dtype, kv_clip=kv_clip)
         ids = tokenizer.encode("<|im_end|>") if hasattr(tokenizer, "special") else []
         self.eos = ids[0] if len(ids) == 1 else getattr(tokenizer, "eos_id", None)
+        # admission policy: "name" or "name:arg", e.g. max_queue_depth:64, ttft_budget:1000 (ms)
+        pol, _, pol_arg = os.environ.get("BRAIN_SCHED_POLICY", "unbounded_queue").partition(":")
         self.sched = Scheduler(self.engine, max_batch=self.max_batch, eos=self.eos,
-                               mixed=os.environ.get("BRAIN_SERVE_MIXED", "1") == "1")
+                               mixed=os.environ.get("BRAIN_SERVE_MIXED", "1") == "1",
+                               policy=pol, policy_arg=float(pol_arg or 0))
         self._inbox: "queue.Queue[_Job]" = queue.Queue()
         self._jobs: Dict[int, _Job] = {}
         self._stop = threading.Event()
@@ -422,7 +425,8 @@ class LlmResident(ResidentModel):
                     job.rid = self.sched.submit(job.prompt, job.max_new, job.params, job.seed, job.ignore_eos)
                     self._jobs[job.rid] = job
                 except RejectReason as e:
-                    kind = "context_length_exceeded" if e.kind == "exceeds_capacity" else "invalid_request"
+                    kind = {"exceeds_capacity": "context_length_exceeded",
+                            "policy_rejected": "rate_limit_exceeded"}.get(e.kind, "invalid_request")
                     self._finish(job, None, ActionError(str(e), kind))
             for job in [j for j in self._jobs.values() if j.cancel.is_cancelled()]:
                 self.sched.cancel(job.rid)

@@ -10,6 +10,7 @@ Reference: crates/model/src/serve.rs:374-776 (Scheduler), :262-307 (admission po
 from __future__ import annotations
 
 import ctypes
+import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Protocol, Sequence, Tuple
 
@@ -50,6 +51,8 @@ _host.register({
                                            c.c_uint32]),
     "bbh_sched_step_tokens": (c.c_uint32, [c.c_void_p]),
     "bbh_sched_set_service_ms": (None, [c.c_void_p, c.c_double]),
+    "bbh_sched_set_prefill_rate": (None, [c.c_void_p, c.c_double]),
+    "bbh_sched_pending_prefill": (c.c_uint64, [c.c_void_p]),
     "bbh_sched_stats": (None, [c.c_void_p, c.c_void_p]),
 })
 
@@ -115,10 +118,22 @@ class Scheduler:
         free (or ``admit_max_wait`` steps passed), trading a little queueing delay for far fewer
         prefill-carrying steps under a saturated closed loop.  ``mixed``: a step that carries both
         prompt chunks and a decode batch runs them as ONE forward when the decoder offers
-        ``mixed_step`` (one set of per-layer launches and all-reduces instead of two)."""
+        ``mixed_step`` (one set of per-layer launches and all-reduces instead of two).
+
+        Admission policies (``policy`` / ``policy_arg``): ``max_queue_depth`` rejects once that many
+        requests wait; ``deadline_aware`` rejects while queue length x mean time in the system
+        exceeds ``policy_arg`` ms; ``ttft_budget`` rejects a request whose first token, at the
+        measured prefill rate, would come later than ``policy_arg`` ms (prompt tokens queued and
+        mid-prefill ahead of it plus its own).  Both measured quantities are running means that
+        ``step`` keeps from its own clock; nothing is rejected before the first measurement."""
         self.dec = decoder
         self.mixed = bool(mixed)
-        pol = {"unbounded_queue": 0, "max_queue_depth": 1, "deadline_aware": 2}[policy]
+        pol = {"unbounded_queue": 0, "max_queue_depth": 1, "deadline_aware": 2, "ttft_budget": 3}[policy]
+        self._measure = pol >= 2
+        self.clock = time.perf_counter      # replaceable (tests drive a synthetic clock)
+        self._t_submit: Dict[int, float] = {}
+        self.service_ms = 0.0               # running mean: submit -> finished
+        self.prefill_tokens_per_ms = 0.0    # running mean over steps that carried prompt tokens
         self.max_blocks = (decoder.max_seq_len + decoder.block_size - 1) // decoder.block_size
         self._h = _host.lib().bbh_sched_new(
             decoder.num_blocks, decoder.block_size, max_batch, decoder.max_prefill_tokens,
@@ -165,11 +180,14 @@ class Scheduler:
         if rid == -4:
             raise RejectReason("empty_prompt", "empty prompt")
         self._rngs[rid] = Rng(seed)
+        if self._measure:
+            self._t_submit[rid] = self.clock()
         return rid
 
     def cancel(self, rid: int) -> List[int]:
         toks = self.tokens_of(rid)
         _host.lib().bbh_sched_cancel(self._h, rid)
+        self._t_submit.pop(rid, None)
         return toks
 
     def is_idle(self) -> bool:
@@ -212,8 +230,32 @@ class Scheduler:
             return int(greedy_tok)
         return sample_from_topk(topk, info.params, self._rngs[rid])
 
+    def pending_prefill_tokens(self) -> int:
+        """Prompt tokens queued or mid-prefill (what a new request's first token waits for)."""
+        return int(_host.lib().bbh_sched_pending_prefill(self._h))
+
+    def _update_measurements(self, rep: "StepReport", t0: float) -> None:
+        """Feed the admission policies: a step's prompt tokens over its duration (decode rows that
+        shared the step count as prefill time, which errs toward rejecting), and the time each
+        finished request spent in the system."""
+        lib = _host.lib()
+        now = self.clock()
+        ms = (now - t0) * 1e3
+        if rep.prefill_tokens and ms > 0:
+            rate = rep.prefill_tokens / ms
+            self.prefill_tokens_per_ms = rate if self.prefill_tokens_per_ms == 0 else \
+                0.8 * self.prefill_tokens_per_ms + 0.2 * rate
+            lib.bbh_sched_set_prefill_rate(self._h, self.prefill_tokens_per_ms)
+        for rid in rep.finished:
+            ts = self._t_submit.pop(rid, None)
+            if ts is not None:
+                took = (now - ts) * 1e3
+                self.service_ms = took if self.service_ms == 0 else 0.8 * self.service_ms + 0.2 * took
+                lib.bbh_sched_set_service_ms(self._h, self.service_ms)
+
     def step(self) -> StepReport:
         lib = _host.lib()
+        t_step = self.clock() if self._measure else 0.0
         npf, nd, win = c.c_uint32(), c.c_uint32(), c.c_uint32()
         lib.bbh_sched_plan(self._h, c.byref(npf), c.byref(nd), c.byref(win))
         rep = StepReport(window=win.value)
@@ -301,6 +343,8 @@ class Scheduler:
                     t += k
                 if fin and rid_v not in rep.finished:
                     rep.finished.append(rid_v)
+        if self._measure:
+            self._update_measurements(rep, t_step)
         return rep
 
     def run_until_idle(self, max_steps: int = 1 << 30) -> None:

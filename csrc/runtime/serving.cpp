@@ -61,7 +61,7 @@ struct Config {
   uint32_t num_blocks, block_size, max_batch, max_prefill, max_seq_len, vocab;
   int64_t eos;        // < 0: none
   uint32_t window;    // on-device greedy steps per decode call when idle-queue (>= 1)
-  int policy;         // 0 unbounded queue, 1 max queue depth, 2 deadline aware
+  int policy;         // 0 unbounded queue, 1 max queue depth, 2 deadline aware, 3 first-token budget
   double policy_arg;
   int prefix_cache;   // 0/1
 };
@@ -87,6 +87,12 @@ class Scheduler {
     if (cfg_.policy == 1 && waiting_.size() >= static_cast<size_t>(cfg_.policy_arg)) return POLICY_REJECTED;
     if (cfg_.policy == 2 && mean_service_ms_ > 0 &&
         static_cast<double>(waiting_.size()) * mean_service_ms_ > cfg_.policy_arg)
+      return POLICY_REJECTED;
+    // first-token budget: the new request's first token comes after every prompt token that is
+    // queued or still being prefilled ahead of it, plus its own; at the measured prefill rate that
+    // must fit in policy_arg milliseconds (nothing is rejected before a rate was measured)
+    if (cfg_.policy == 3 && prefill_tokens_per_ms_ > 0 &&
+        static_cast<double>(pending_prefill_tokens() + n) / prefill_tokens_per_ms_ > cfg_.policy_arg)
       return POLICY_REJECTED;
     auto s = std::make_unique<Seq>();
     s->id = next_id_++;
@@ -123,6 +129,18 @@ class Scheduler {
   }
 
   bool idle() const { return waiting_.empty() && running_.empty(); }
+
+  // prompt tokens whose K/V are not stored yet: whole prompts in the queue (a prefix-cache hit is
+  // only known at admission, so it is not discounted) and the rest of prompts that are mid-prefill
+  uint64_t pending_prefill_tokens() const {
+    uint64_t t = 0;
+    for (int64_t id : waiting_) t += seqs_.at(id)->prompt.size();
+    for (int64_t id : running_) {
+      const Seq& r = *seqs_.at(id);
+      if (r.prefilled < r.prompt.size()) t += r.prompt.size() - r.prefilled;
+    }
+    return t;
+  }
 
   // ---- step planning ----------------------------------------------------------------------
   struct PrefillItem {
@@ -310,7 +328,7 @@ class Scheduler {
   uint64_t last_need_ = 0, last_bad_token_ = 0;
   uint64_t prefix_hit_tokens_ = 0, prefix_lookup_tokens_ = 0, steps_ = 0, submitted_ = 0, finished_ = 0,
            cancelled_ = 0, generated_ = 0;
-  double mean_service_ms_ = 0;
+  double mean_service_ms_ = 0, prefill_tokens_per_ms_ = 0;
 
  private:
   // Back `n` more positions of `s`; when the pool is short, evict least-recently-used prefix-cache
@@ -533,6 +551,10 @@ BBH_API uint32_t bbh_sched_step_report(void* s, int64_t* ids, uint32_t* n_new, i
 BBH_API uint32_t bbh_sched_step_tokens(void* s) { return static_cast<uint32_t>(static_cast<Scheduler*>(s)->step_tokens.size()); }
 BBH_API void bbh_sched_forget(void* s, int64_t id) { static_cast<Scheduler*>(s)->forget(id); }
 BBH_API void bbh_sched_set_service_ms(void* s, double ms) { static_cast<Scheduler*>(s)->mean_service_ms_ = ms; }
+BBH_API void bbh_sched_set_prefill_rate(void* s, double tokens_per_ms) {
+  static_cast<Scheduler*>(s)->prefill_tokens_per_ms_ = tokens_per_ms;
+}
+BBH_API uint64_t bbh_sched_pending_prefill(void* s) { return static_cast<Scheduler*>(s)->pending_prefill_tokens(); }
 // stats: [free_blocks, num_blocks, waiting, running, steps, submitted, finished, cancelled,
 //         generated, prefix_hit_tokens, prefix_lookup_tokens, prefix_entries]
 BBH_API void bbh_sched_stats(void* s, uint64_t* out) {

@@ -95,6 +95,22 @@ def test_capacity_error_maps_to_context_length(llm):
     assert err.code == "context_length_exceeded" and err.status == 400 and "256" in err.message
 
 
+def test_policy_rejection_maps_to_429(monkeypatch):
+    """A request the scheduler's admission policy turns away is a rate-limit error (HTTP 429 with
+    Retry-After), not a client error.  Queue depth 0 rejects everything, which needs no timing."""
+    monkeypatch.setenv("BRAIN_SCHED_POLICY", "max_queue_depth:0")
+    tok = BpeTokenizer.byte_level(["t h"], {"<|im_start|>": 258, "<|im_end|>": 259, "<|endoftext|>": 260})
+    cfg = QwenConfig(vocab=264, block_size=64, n_layers=1, d_model=32, n_heads=4, n_kv_heads=2, head_dim=8, d_ff=64)
+    r = LlmResident(Qwen3(cfg).init_weights(3).eval(), tok, "brain/tiny", ctx=64, max_batch=2)
+    try:
+        with pytest.raises(ActionError) as e:
+            run(r, prompt="hello", chat=False, max_new=4)
+        err = from_exception(e.value)
+        assert err.code == "rate_limit_exceeded" and err.status == 429 and err.headers() == {"Retry-After": "1"}
+    finally:
+        r.close()
+
+
 def test_cancel_frees_blocks(llm):
     r, _, _ = llm
     free0 = r.stats()["free_blocks"]

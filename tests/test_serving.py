@@ -359,3 +359,77 @@ def test_mixed_steps_equal_separate_prefill_and_decode():
     assert n0 == 0 and n1 > 0 and eng.acct["mixed_calls"] == n1
     assert mix == sep
     assert mix[0] == _greedy_reference(eng, prompts[0], 7)
+
+
+def test_first_token_budget_policy_bounds_the_queue_by_measured_prefill_rate():
+    """``ttft_budget``: admission rejects a request whose first token, at the prefill rate the
+    scheduler measured from its own steps, would come after the budget.  A synthetic clock makes a
+    prompt token cost exactly one millisecond."""
+    class Clock:
+        t = 0.0
+
+        def __call__(self):
+            return self.t
+
+    class TimedDecoder(FakeDecoder):
+        def __init__(self, clock):
+            super().__init__()
+            self.clock = clock
+
+        def prefill_chunk(self, tokens, start, block_table, last, greedy):
+            self.clock.t += len(tokens) * 1e-3
+            return super().prefill_chunk(tokens, start, block_table, last, greedy)
+
+    clk = Clock()
+    s = Scheduler(TimedDecoder(clk), max_batch=1, window=1, policy="ttft_budget", policy_arg=20.0)
+    s.clock = clk
+    # no measurement yet: nothing is rejected, however long the queue
+    a = s.submit(list(range(16)), 2)
+    b = s.submit(list(range(16)), 2)
+    assert s.pending_prefill_tokens() == 32
+    s.step()                                  # prefills 8 tokens of `a` in 8 ms -> 1 token / ms
+    assert s.prefill_tokens_per_ms == pytest.approx(1.0)
+    assert s.pending_prefill_tokens() == 24
+    # 24 tokens ahead: a 4-token prompt would see its first token after 28 ms > 20 ms
+    with pytest.raises(RejectReason) as e:
+        s.submit([1, 2, 3, 4], 2)
+    assert e.value.kind == "policy_rejected"
+    s.step()                                  # rest of `a`
+    assert s.pending_prefill_tokens() == 16
+    c_ = s.submit([1, 2, 3, 4], 2)            # 16 + 4 = 20 ms: inside the budget
+    with pytest.raises(RejectReason):
+        s.submit([1], 2)                      # 21 ms
+    s.run_until_idle()
+    for r in (a, b, c_):
+        assert s.info(r).state == FINISHED
+    assert s.pending_prefill_tokens() == 0
+    s.submit(list(range(20)), 2)              # an empty engine takes a prompt as long as the budget
+
+
+def test_deadline_aware_policy_is_fed_by_the_measured_time_in_system():
+    """``deadline_aware`` rejects while queue length x mean time in the system exceeds the budget;
+    the mean comes from the scheduler's own clock (submit -> finished)."""
+    class Clock:
+        t = 0.0
+
+        def __call__(self):
+            return self.t
+
+    clk = Clock()
+
+    class TimedDecoder(FakeDecoder):
+        def decode(self, tokens, positions, block_tables, window, greedy):
+            clk.t += 5e-3
+            return super().decode(tokens, positions, block_tables, window, greedy)
+
+    s = Scheduler(TimedDecoder(), max_batch=1, window=1, policy="deadline_aware", policy_arg=25.0)
+    s.clock = clk
+    r = s.submit([1, 2], 3)                   # first token from prefill, then two decode steps of 5 ms
+    s.run_until_idle()
+    assert s.info(r).state == FINISHED and s.service_ms == pytest.approx(10.0)
+    ids = [s.submit([1, 2], 3) for _ in range(3)]      # queue 0, 1, 2 -> 0, 10, 20 ms: admitted
+    with pytest.raises(RejectReason) as e:
+        s.submit([1, 2], 3)                            # queue 3 -> 30 ms > 25 ms
+    assert e.value.kind == "policy_rejected"
+    s.run_until_idle()
+    assert all(s.info(i).state == FINISHED for i in ids)
