@@ -3,19 +3,39 @@
 GPU: fp32 master weights and moments (optionally only this rank's shard of them — ZeRO-1), one
 fused kernel that applies the clip coefficient, updates master/m/v and writes the bf16 working
 weights; the gradient norm is a two-stage deterministic reduction and the clip coefficient stays
-on the device (no host sync in the step).  CPU backend: the same arithmetic in PyTorch fp32.
+on the device (no host sync in the step).  CPU backend: the same arithmetic in one native
+multi-threaded pass over the flat buffers (csrc/runtime/host_adam.cpp; no temporaries, where the
+PyTorch expression allocates five of the model's size per step); ``BRAIN_CPU_ADAM=torch`` runs the
+PyTorch fp32 expression instead.
 
 Reference: crates/optim/src/lib.rs:40-217 (AdamW + clip as a cached dispatch graph),
 crates/kernels/wgsl/{adamw,gradnorm_part,clip_coef_wg}.wgsl; coef = min(1, max_norm/(||g||+1e-6))."""
 from __future__ import annotations
 
+import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
 
+from .. import _host
 from ..ops import _cuda, reference as ref
 from ..ops._cuda import L, call, stream_ptr
 from ..paramstore import ParamStore
+
+_host.register({
+    "bbh_sumsq_f32": (ctypes.c_double, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]),
+    "bbh_adamw_f32": (None, [ctypes.c_void_p] * 5 + [ctypes.c_int64] + [ctypes.c_float] * 5 +
+                      [ctypes.c_int64, ctypes.c_float, ctypes.c_int]),
+})
+
+
+def _native_cpu() -> bool:
+    return os.environ.get("BRAIN_CPU_ADAM", "native") != "torch"
+
+
+def _flat_f32(*ts) -> bool:
+    return all(t.dtype == torch.float32 and t.is_contiguous() and t.device.type == "cpu" for t in ts)
 
 
 class AdamW:
@@ -80,6 +100,9 @@ class AdamW:
         if self.cuda:
             call("sumsq", g, L(g.numel()), self._scratch, self._sumsq, 0, stream_ptr())
             ss = self._sumsq
+        elif _native_cpu() and _flat_f32(g):
+            ss = torch.tensor([_host.lib().bbh_sumsq_f32(g.data_ptr(), g.numel(), torch.get_num_threads())],
+                              dtype=torch.float32)
         else:
             ss = (g.double() ** 2).sum().float().reshape(1)
         if self.world > 1:
@@ -120,10 +143,17 @@ class AdamW:
                 norm = float(ss.sqrt())
                 self.last_grad_norm = torch.tensor([norm])
                 coef = min(1.0, clip / (norm + 1e-6)) * extra_scale
+            native = _native_cpu() and _flat_f32(self.master, self.m, self.v, g)
             for a, b, dec in self._runs:
                 o, n = a - self.lo, b - a
-                ref.adamw_(self.master[o:o + n], self.m[o:o + n], self.v[o:o + n], g[o:o + n], lr,
-                           self.beta1, self.beta2, self.eps, wd if dec else 0.0, self.t, coef)
+                if native:
+                    _host.lib().bbh_adamw_f32(self.master[o:].data_ptr(), self.m[o:].data_ptr(),
+                                              self.v[o:].data_ptr(), g[o:].data_ptr(), None, n, lr, self.beta1,
+                                              self.beta2, self.eps, wd if dec else 0.0, self.t, coef,
+                                              torch.get_num_threads())
+                else:
+                    ref.adamw_(self.master[o:o + n], self.m[o:o + n], self.v[o:o + n], g[o:o + n], lr,
+                               self.beta1, self.beta2, self.eps, wd if dec else 0.0, self.t, coef)
             if self.master.data_ptr() != st.weights[self.lo:self.hi].data_ptr():
                 st.weights[self.lo:self.hi].copy_(self.master.to(st.dtype))
 

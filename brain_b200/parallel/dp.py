@@ -36,12 +36,13 @@ class DataParallel:
         self.n_micro = 0
         self.last_losses: List[float] = []
         # the native CPU GEMM runs a worker pool per calling thread: give every replica its share of
-        # the cores unless the user fixed the count (two pools of 8 on 8 cores measured 158 tok/s on
-        # GPT-2 small, two of 4 measured 208)
+        # the cores unless the user fixed the count, and so does PyTorch's own thread team (set per
+        # replica thread in forward_backward): two teams of 8 on 8 cores cost a third of the throughput
         import os
         from ..ops import cpu_native
+        self.threads_per_replica = max(1, (os.cpu_count() or 1) // n_workers)
         if cpu_native.enabled() and "BRAIN_CPU_THREADS" not in os.environ:
-            cpu_native.threads = max(1, (os.cpu_count() or 1) // n_workers)
+            cpu_native.threads = self.threads_per_replica
 
     def forward_backward(self, micro_batches: Sequence, loss_scale: Optional[float] = None) -> float:
         """``micro_batches``: list of (tokens, targets).  Gradients accumulate in each replica's
@@ -53,6 +54,7 @@ class DataParallel:
 
         def work(r: int):
             try:
+                torch.set_num_threads(self.threads_per_replica)   # per calling thread: this replica's share
                 m, st = self.models[r], self.stores[r]
                 for i in range(r, len(micro_batches), self.n):
                     tok, tgt = micro_batches[i]

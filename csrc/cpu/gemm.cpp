@@ -9,9 +9,9 @@
 // Method: both operands are packed into K-major panels (MR rows of A, NR columns of B, zero padded),
 // so the micro-kernel is the same for every layout: MR x NR = 6 x 16 accumulators in twelve ymm
 // registers (AVX2) or 12 x 32 in twenty-four zmm registers (AVX-512), one broadcast of A per row and two
-// loads of B per k.  Panels of B are packed once per call
-// and shared by all threads; every thread packs the A rows it owns.  K is cut into KC-deep slabs so
-// a B slab (KC x NC) stays in L2.  A task owns a block of up to MC rows: it packs them once per slab and
+// loads of B per k.  A slab of B (KC x NC) is packed by all threads together and shared; every thread
+// packs the A rows it owns.  Packs that transpose go through registers in 8 x 8 blocks.  Column slabs
+// are the outer loop and K slabs the inner one, so a task's part of C stays in cache while K is summed.  A task owns a block of up to MC rows: it packs them once per slab and
 // sweeps them over the slab one B panel at a time, so a B panel is pulled into L1 once per block instead
 // of once per 6-row panel.  Worker threads are persistent (one pool per calling thread).
 //
@@ -52,12 +52,13 @@ class Pool {
     for (int t = 0; t < workers; ++t) th_.emplace_back([this] { loop(); });
   }
   ~Pool() {
+    unsigned long g1;
     {
       std::lock_guard<std::mutex> g(m_);
-      stop_ = true;
-      ++gen_;
-      gen_pub_.store(gen_, std::memory_order_release);
+      stop_.store(true, std::memory_order_release);
+      g1 = ++gen_;
     }
+    gen_pub_.store(g1, std::memory_order_release);
     cv_.notify_all();
     for (auto& t : th_) t.join();
   }
@@ -71,21 +72,26 @@ class Pool {
       return;
     }
     std::function<void(int)> f = std::ref(fn);
+    // The job is written first and published by the release store of the generation: workers that
+    // spin pick it up without the mutex.  (Publishing inside the critical section sent every spinning
+    // worker straight into a blocked lock, a sleep and a wake-up per parallel region.)
+    job_ = &f;
+    n_ = n;
+    next_.store(0, std::memory_order_relaxed);
+    left_.store((int)th_.size(), std::memory_order_relaxed);
+    unsigned long g1;
     {
       std::lock_guard<std::mutex> g(m_);
-      job_ = &f;
-      n_ = n;
-      next_.store(0, std::memory_order_relaxed);
-      pending_ = (int)th_.size();
-      left_.store(pending_, std::memory_order_relaxed);
-      ++gen_;
-      gen_pub_.store(gen_, std::memory_order_release);
+      g1 = ++gen_;
     }
-    cv_.notify_all();
+    gen_pub_.store(g1, std::memory_order_release);
+    if (parked_.load(std::memory_order_acquire) != 0) cv_.notify_all();
     for (int i; (i = next_.fetch_add(1, std::memory_order_relaxed)) < n;) fn(i);
-    for (int spin = 0; spin < 20000 && left_.load(std::memory_order_acquire) != 0; ++spin) _mm_pause();
-    std::unique_lock<std::mutex> g(m_);
-    done_.wait(g, [this] { return pending_ == 0; });
+    for (int spin = 0; spin < 200000 && left_.load(std::memory_order_acquire) != 0; ++spin) _mm_pause();
+    if (left_.load(std::memory_order_acquire) != 0) {
+      std::unique_lock<std::mutex> g(m_);
+      done_.wait(g, [this] { return left_.load(std::memory_order_acquire) == 0; });
+    }
     job_ = nullptr;
   }
 
@@ -93,24 +99,30 @@ class Pool {
   void loop() {
     unsigned long seen = 0;
     for (;;) {
-      std::function<void(int)>* f;
-      int n;
       // a GEMM is several short parallel regions back to back: spin for the next one for a while
       // before parking (a condition-variable wake-up costs tens of microseconds per region)
-      for (int spin = 0; spin < 20000 && gen_pub_.load(std::memory_order_acquire) == seen; ++spin) _mm_pause();
-      {
+      // generations only grow; "newer than seen" (not "different") because a worker that was woken
+      // through gen_ can be one step ahead of gen_pub_ for a moment
+      auto newer = [&](unsigned long g) { return (long)(g - seen) > 0; };
+      for (int spin = 0; spin < 20000 && !newer(gen_pub_.load(std::memory_order_acquire)); ++spin) _mm_pause();
+      unsigned long cur = gen_pub_.load(std::memory_order_acquire);
+      if (!newer(cur)) {
         std::unique_lock<std::mutex> g(m_);
-        cv_.wait(g, [&] { return gen_ != seen; });
-        seen = gen_;
-        if (stop_) return;
-        f = job_;
-        n = n_;
+        parked_.fetch_add(1, std::memory_order_acq_rel);
+        cv_.wait(g, [&] { return newer(gen_); });
+        parked_.fetch_sub(1, std::memory_order_acq_rel);
+        cur = gen_;
       }
+      // run() starts the next generation only after every worker has finished this one, so the
+      // job fields are stable from here to the decrement below
+      seen = cur;
+      if (stop_.load(std::memory_order_acquire)) return;
+      std::function<void(int)>* f = job_;
+      const int n = n_;
       for (int i; (i = next_.fetch_add(1, std::memory_order_relaxed)) < n;) (*f)(i);
-      {
-        std::lock_guard<std::mutex> g(m_);
-        left_.store(pending_ - 1, std::memory_order_release);
-        if (--pending_ == 0) done_.notify_one();
+      if (left_.fetch_sub(1, std::memory_order_acq_rel) == 1) {
+        std::lock_guard<std::mutex> g(m_);   // the caller may be asleep on done_: wake it under the lock
+        done_.notify_one();
       }
     }
   }
@@ -121,9 +133,10 @@ class Pool {
   std::atomic<int> next_{0};
   std::atomic<int> left_{0};
   std::atomic<unsigned long> gen_pub_{0};   // copy of gen_ the spinning workers poll without the lock
-  int n_ = 0, pending_ = 0;
+  std::atomic<int> parked_{0};              // workers asleep on cv_ (run() skips the notify when none are)
+  int n_ = 0;
   unsigned long gen_ = 0;
-  bool stop_ = false;
+  std::atomic<bool> stop_{false};
 };
 
 Pool& pool_for(int threads) {
@@ -142,9 +155,66 @@ void parallel_for(int n, int threads, F fn) {
   pool_for(threads).run(n, fn);
 }
 
-// element (r, k) of op(A) / (k, c) of op(B) from the stored matrix
-inline float a_at(const float* A, int lda, int ta, int r, int k) { return ta ? A[(size_t)k * lda + r] : A[(size_t)r * lda + k]; }
-inline float b_at(const float* B, int ldb, int tb, int k, int c) { return tb ? B[(size_t)c * ldb + k] : B[(size_t)k * ldb + c]; }
+// dst[k * W + j] = src[j * ld + k] for j < rows, k < kc; columns rows..W-1 of dst are zero.  The
+// source rows are contiguous in k, so the copy is a transpose: 8 x 8 blocks go through registers
+// (eight loads, three rounds of shuffles, eight stores), 4 x 4 blocks likewise with SSE, the rest
+// element by element.  Element-wise strided stores made the two transposing packs a quarter of a
+// layer-sized GEMM's time.
+inline void pack_transposed(const float* src, size_t ld, int rows, int kc, float* dst, int W) {
+  int j = 0;
+  for (; j + 8 <= rows; j += 8) {
+    const float* s = src + (size_t)j * ld;
+    int k = 0;
+    for (; k + 8 <= kc; k += 8) {
+      __m256 r0 = _mm256_loadu_ps(s + 0 * ld + k), r1 = _mm256_loadu_ps(s + 1 * ld + k);
+      __m256 r2 = _mm256_loadu_ps(s + 2 * ld + k), r3 = _mm256_loadu_ps(s + 3 * ld + k);
+      __m256 r4 = _mm256_loadu_ps(s + 4 * ld + k), r5 = _mm256_loadu_ps(s + 5 * ld + k);
+      __m256 r6 = _mm256_loadu_ps(s + 6 * ld + k), r7 = _mm256_loadu_ps(s + 7 * ld + k);
+      const __m256 t0 = _mm256_unpacklo_ps(r0, r1), t1 = _mm256_unpackhi_ps(r0, r1);
+      const __m256 t2 = _mm256_unpacklo_ps(r2, r3), t3 = _mm256_unpackhi_ps(r2, r3);
+      const __m256 t4 = _mm256_unpacklo_ps(r4, r5), t5 = _mm256_unpackhi_ps(r4, r5);
+      const __m256 t6 = _mm256_unpacklo_ps(r6, r7), t7 = _mm256_unpackhi_ps(r6, r7);
+      r0 = _mm256_shuffle_ps(t0, t2, 0x44); r1 = _mm256_shuffle_ps(t0, t2, 0xEE);
+      r2 = _mm256_shuffle_ps(t1, t3, 0x44); r3 = _mm256_shuffle_ps(t1, t3, 0xEE);
+      r4 = _mm256_shuffle_ps(t4, t6, 0x44); r5 = _mm256_shuffle_ps(t4, t6, 0xEE);
+      r6 = _mm256_shuffle_ps(t5, t7, 0x44); r7 = _mm256_shuffle_ps(t5, t7, 0xEE);
+      float* d = dst + (size_t)k * W + j;
+      _mm256_storeu_ps(d + 0 * (size_t)W, _mm256_permute2f128_ps(r0, r4, 0x20));
+      _mm256_storeu_ps(d + 1 * (size_t)W, _mm256_permute2f128_ps(r1, r5, 0x20));
+      _mm256_storeu_ps(d + 2 * (size_t)W, _mm256_permute2f128_ps(r2, r6, 0x20));
+      _mm256_storeu_ps(d + 3 * (size_t)W, _mm256_permute2f128_ps(r3, r7, 0x20));
+      _mm256_storeu_ps(d + 4 * (size_t)W, _mm256_permute2f128_ps(r0, r4, 0x31));
+      _mm256_storeu_ps(d + 5 * (size_t)W, _mm256_permute2f128_ps(r1, r5, 0x31));
+      _mm256_storeu_ps(d + 6 * (size_t)W, _mm256_permute2f128_ps(r2, r6, 0x31));
+      _mm256_storeu_ps(d + 7 * (size_t)W, _mm256_permute2f128_ps(r3, r7, 0x31));
+    }
+    for (; k < kc; ++k)
+      for (int jj = 0; jj < 8; ++jj) dst[(size_t)k * W + j + jj] = s[(size_t)jj * ld + k];
+  }
+  for (; j + 4 <= rows; j += 4) {
+    const float* s = src + (size_t)j * ld;
+    int k = 0;
+    for (; k + 4 <= kc; k += 4) {
+      __m128 r0 = _mm_loadu_ps(s + 0 * ld + k), r1 = _mm_loadu_ps(s + 1 * ld + k);
+      __m128 r2 = _mm_loadu_ps(s + 2 * ld + k), r3 = _mm_loadu_ps(s + 3 * ld + k);
+      _MM_TRANSPOSE4_PS(r0, r1, r2, r3);
+      float* d = dst + (size_t)k * W + j;
+      _mm_storeu_ps(d + 0 * (size_t)W, r0);
+      _mm_storeu_ps(d + 1 * (size_t)W, r1);
+      _mm_storeu_ps(d + 2 * (size_t)W, r2);
+      _mm_storeu_ps(d + 3 * (size_t)W, r3);
+    }
+    for (; k < kc; ++k)
+      for (int jj = 0; jj < 4; ++jj) dst[(size_t)k * W + j + jj] = s[(size_t)jj * ld + k];
+  }
+  for (; j < rows; ++j) {
+    const float* s = src + (size_t)j * ld;
+    for (int k = 0; k < kc; ++k) dst[(size_t)k * W + j] = s[k];
+  }
+  if (rows < W)
+    for (int k = 0; k < kc; ++k)
+      for (int jj = rows; jj < W; ++jj) dst[(size_t)k * W + jj] = 0.f;
+}
 
 // C tile [mr x nr] = (first k-slab ? beta * C : C) + alpha * Ap[kc][MR] * Bp[kc][NR]: the ragged-edge
 // write-back shared by both micro-kernels
@@ -266,30 +336,40 @@ static int gemm_impl(const float* A, const float* B, float* C, int M, int N, int
   while (mc > MR && (M + mc - 1) / mc < 2 * threads) mc -= MR;
   const int m_blocks = (M + mc - 1) / mc;
   std::vector<float> Bp((size_t)((std::min(N, NC) + NR - 1) / NR) * NR * KC);
-  for (int k0 = 0; k0 < K; k0 += KC) {
-    const int kc = std::min(KC, K - k0);
-    const bool first_k = k0 == 0;
-    for (int n0 = 0; n0 < N; n0 += NC) {
-      const int nc = std::min(NC, N - n0);
-      const int n_panels = (nc + NR - 1) / NR;
+  // column slabs outside, K slabs inside: a task's part of C (its rows x NC columns) is accumulated
+  // over all of K while it is still in cache; with K outside, a wide C (the LM head's) went to
+  // memory and back once per K slab
+  for (int n0 = 0; n0 < N; n0 += NC) {
+    const int nc = std::min(NC, N - n0);
+    const int n_panels = (nc + NR - 1) / NR;
+    for (int k0 = 0; k0 < K; k0 += KC) {
+      const int kc = std::min(KC, K - k0);
+      const bool first_k = k0 == 0;
       // pack the B slab: panel p holds columns [n0 + p*NR, +NR) as [kc][NR]
-      parallel_for(n_panels, threads, [&](int p) {
-        float* dst = Bp.data() + (size_t)p * NR * KC;
-        const int c0 = n0 + p * NR, nr = std::min(NR, N - c0);
-        if (tb && nr == NR) {           // B stored [N][K]: 16 rows of the source, transposed on the way
-          for (int j = 0; j < NR; ++j) {
-            const float* src = B + (size_t)(c0 + j) * ldb + k0;
-            for (int k = 0; k < kc; ++k) dst[(size_t)k * NR + j] = src[k];
+      if (!tb) {
+        // B stored [K][N]: tasks own runs of k rows and read each row of the slab front to back (one
+        // sequential stream), dealing it out NR floats at a time to the panels; copying panel by
+        // panel instead touched two cache lines per row of a panel, a page apart each
+        constexpr int KR = 16;
+        const int full = nc / NR, rem = nc - full * NR;
+        parallel_for((kc + KR - 1) / KR, threads, [&](int t) {
+          for (int k = t * KR; k < std::min(kc, (t + 1) * KR); ++k) {
+            const float* src = B + (size_t)(k0 + k) * ldb + n0;
+            float* dst = Bp.data() + (size_t)k * NR;
+            for (int q = 0; q < full; ++q) std::memcpy(dst + (size_t)q * NR * KC, src + (size_t)q * NR, NR * sizeof(float));
+            if (rem) {
+              float* d = dst + (size_t)full * NR * KC;
+              for (int j = 0; j < rem; ++j) d[j] = src[(size_t)full * NR + j];
+              for (int j = rem; j < NR; ++j) d[j] = 0.f;
+            }
           }
-        } else if (!tb && nr == NR) {   // B stored [K][N]: contiguous 16-float rows
-          for (int k = 0; k < kc; ++k) std::memcpy(dst + (size_t)k * NR, B + (size_t)(k0 + k) * ldb + c0, NR * sizeof(float));
-        } else {
-          for (int k = 0; k < kc; ++k) {
-            for (int j = 0; j < nr; ++j) dst[(size_t)k * NR + j] = b_at(B, ldb, tb, k0 + k, c0 + j);
-            for (int j = nr; j < NR; ++j) dst[(size_t)k * NR + j] = 0.f;
-          }
-        }
-      });
+        });
+      } else {
+        parallel_for(n_panels, threads, [&](int p) {   // B stored [N][K]: NR source rows, transposed on the way
+          const int c0 = n0 + p * NR, nr = std::min(NR, N - c0);
+          pack_transposed(B + (size_t)c0 * ldb + k0, (size_t)ldb, nr, kc, Bp.data() + (size_t)p * NR * KC, NR);
+        });
+      }
       // every task packs its block of A once and sweeps it over the B slab panel by panel: a B panel
       // (16 KB) is read into L1 once per block and reused by all of the block's row panels
       parallel_for(m_blocks, threads, [&](int mb) {
@@ -300,16 +380,14 @@ static int gemm_impl(const float* A, const float* B, float* C, int M, int N, int
           float* ap = Ap.data() + (size_t)pi * MR * kc;
           const int r0 = r_lo + pi * MR, mr = std::min(MR, M - r0);
           if (!ta) {
-            for (int i = 0; i < mr; ++i) {
-              const float* src = A + (size_t)(r0 + i) * lda + k0;
-              for (int k = 0; k < kc; ++k) ap[(size_t)k * MR + i] = src[k];
-            }
+            pack_transposed(A + (size_t)r0 * lda + k0, (size_t)lda, mr, kc, ap, MR);
           } else {
-            for (int k = 0; k < kc; ++k)
-              for (int i = 0; i < mr; ++i) ap[(size_t)k * MR + i] = A[(size_t)(k0 + k) * lda + r0 + i];
+            for (int k = 0; k < kc; ++k) {
+              const float* src = A + (size_t)(k0 + k) * lda + r0;
+              for (int i = 0; i < mr; ++i) ap[(size_t)k * MR + i] = src[i];
+              for (int i = mr; i < MR; ++i) ap[(size_t)k * MR + i] = 0.f;
+            }
           }
-          for (int i = mr; i < MR; ++i)
-            for (int k = 0; k < kc; ++k) ap[(size_t)k * MR + i] = 0.f;
         }
         for (int p = 0; p < n_panels; ++p) {
           const int c0 = n0 + p * NR, nr = std::min(NR, N - c0);

@@ -3,6 +3,7 @@
 // Reference behaviour: crates/optim/src/lib.rs (OffloadAdam: moments in host RAM, the step runs on
 // the CPU, updated weights are uploaded) — here the update is split over std::thread workers and
 // writes the bf16 copy that is uploaded in the same pass.
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -37,22 +38,37 @@ void parallel_for(int64_t n, int threads, F&& fn) {
 
 }  // namespace
 
-// sum of squares in double, deterministic for a fixed thread count (fixed chunking + ordered sum)
+// sum of squares in double.  The vector is cut into fixed pieces of 2^18 elements whose partial sums
+// are added in index order, so the result does not depend on the number of threads.
 BBH_API double bbh_sumsq_f32(const float* g, int64_t n, int threads) {
     if (threads < 1) threads = 1;
-    std::vector<double> part(size_t(threads), 0.0);
-    int64_t chunk = (n + threads - 1) / threads;
-    std::vector<std::thread> pool;
-    for (int t = 0; t < threads; ++t) {
-        int64_t a = t * chunk, b = std::min<int64_t>(n, a + chunk);
-        if (a >= b) break;
-        pool.emplace_back([=, &part] {
-            double s = 0.0;
-            for (int64_t i = a; i < b; ++i) s += double(g[i]) * double(g[i]);
-            part[size_t(t)] = s;
-        });
+    constexpr int64_t PIECE = int64_t(1) << 18;
+    const int64_t pieces = (n + PIECE - 1) / PIECE;
+    if (pieces <= 0) return 0.0;
+    std::vector<double> part(size_t(pieces), 0.0);
+    auto run = [&](int64_t first, int64_t step) {
+        for (int64_t p = first; p < pieces; p += step) {
+            const int64_t a = p * PIECE, b = std::min<int64_t>(n, a + PIECE);
+            double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+            int64_t i = a;
+            for (; i + 4 <= b; i += 4) {
+                s0 += double(g[i]) * double(g[i]);
+                s1 += double(g[i + 1]) * double(g[i + 1]);
+                s2 += double(g[i + 2]) * double(g[i + 2]);
+                s3 += double(g[i + 3]) * double(g[i + 3]);
+            }
+            for (; i < b; ++i) s0 += double(g[i]) * double(g[i]);
+            part[size_t(p)] = (s0 + s1) + (s2 + s3);
+        }
+    };
+    const int64_t nt = std::min<int64_t>(threads, pieces);
+    if (nt <= 1) {
+        run(0, 1);
+    } else {
+        std::vector<std::thread> pool;
+        for (int64_t t = 0; t < nt; ++t) pool.emplace_back(run, t, nt);
+        for (auto& th : pool) th.join();
     }
-    for (auto& th : pool) th.join();
     double s = 0.0;
     for (double p : part) s += p;
     return s;

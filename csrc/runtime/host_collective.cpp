@@ -14,6 +14,7 @@
 #include <sys/socket.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <cerrno>
 #include <condition_variable>
 #include <cstdint>
@@ -135,15 +136,29 @@ BBH_API int bbh_hc_all_reduce(void* h, int rank, float* data, int64_t n) {
   c->slots[rank] = data;
   c->lens[rank] = n;
   if (!c->bar.wait(c->timeout_s)) return -1;
-  std::vector<float> sum(static_cast<size_t>(n), 0.f);
-  for (int r = 0; r < c->world; ++r) {
+  for (int r = 0; r < c->world; ++r)
     if (c->lens[r] != n) return -2;
-    const float* s = c->slots[r];
-    for (int64_t i = 0; i < n; ++i) sum[i] += s[i];
+  // In place, no staging copy: rank r owns the r-th slice of EVERY rank's buffer, adds the ranks'
+  // values in rank order (so each element gets the same bits whichever rank computes it) and writes
+  // the sum back into all of them.  No other rank touches that slice between the two barriers.
+  const int64_t chunk = ((n + c->world - 1) / c->world + 15) & ~int64_t(15);
+  const int64_t a = std::min<int64_t>(n, rank * chunk), b = std::min<int64_t>(n, a + chunk);
+  if (c->world == 2) {
+    float* p0 = const_cast<float*>(c->slots[0]);
+    float* p1 = const_cast<float*>(c->slots[1]);
+    for (int64_t i = a; i < b; ++i) {
+      const float s = p0[i] + p1[i];
+      p0[i] = s;
+      p1[i] = s;
+    }
+  } else {
+    for (int64_t i = a; i < b; ++i) {
+      float s = c->slots[0][i];
+      for (int r = 1; r < c->world; ++r) s += c->slots[r][i];
+      for (int r = 0; r < c->world; ++r) const_cast<float*>(c->slots[r])[i] = s;
+    }
   }
-  if (!c->bar.wait(c->timeout_s)) return -1;  // everyone has read every slot
-  std::memcpy(data, sum.data(), static_cast<size_t>(n) * 4);
-  if (!c->bar.wait(c->timeout_s)) return -1;
+  if (!c->bar.wait(c->timeout_s)) return -1;  // every slice of every buffer holds the sum
   return 0;
 }
 BBH_API int bbh_hc_all_gather(void* h, int rank, const float* data, int64_t n, float* out) {

@@ -458,3 +458,49 @@ def test_experts_only_recompute_keeps_loss_and_gradients_with_router_losses():
     assert out["none"][0] == out["experts"][0]
     for n, gref in out["none"][1].items():
         assert torch.equal(out["experts"][1][n], gref), n
+
+
+def test_native_cpu_adamw_and_norm_match_the_pytorch_expression(monkeypatch):
+    """The CPU backend's one-pass native AdamW (with clipping and a no-decay run) tracks the PyTorch
+    fp32 expression, and its gradient norm does not depend on the thread count."""
+    from brain_b200 import _host
+    from brain_b200.models.config import GptConfig
+    from brain_b200.models.gpt2 import Gpt2
+    from brain_b200.optim.adamw import AdamW
+    from brain_b200.paramstore import ParamStore
+    cfg = GptConfig(vocab=64, block_size=16, n_layers=2, d_model=32, n_heads=4, d_ff=64)
+    out = {}
+    for mode in ("native", "torch"):
+        monkeypatch.setenv("BRAIN_CPU_ADAM", mode)
+        st = ParamStore(Gpt2(cfg).init_weights(3), device="cpu")
+        opt = AdamW(st, betas=(0.9, 0.95))
+        g = torch.Generator().manual_seed(1)
+        for _ in range(3):
+            st.grads.copy_(torch.randn(st.grads.shape, generator=g) * 0.3)
+            opt.step(1e-2, 0.1, clip=1.0, extra_scale=0.5)
+        out[mode] = (st.weights.clone(), opt.m.clone(), opt.v.clone(), float(opt.last_grad_norm))
+    for a, b in zip(out["native"][:3], out["torch"][:3]):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-7)
+    assert out["native"][3] == pytest.approx(out["torch"][3], rel=1e-6)
+    x = torch.randn(1_000_003, generator=torch.Generator().manual_seed(2))
+    ss = [_host.lib().bbh_sumsq_f32(x.data_ptr(), x.numel(), t) for t in (1, 3, 8)]
+    assert ss[0] == ss[1] == ss[2] and ss[0] == pytest.approx(float((x.double() ** 2).sum()), rel=1e-12)
+
+
+def test_host_all_reduce_in_place_gives_every_rank_the_same_bits():
+    """Thread ranks: each rank sums its slice of every rank's buffer in rank order and writes it
+    back into all of them; odd lengths and three ranks included."""
+    import threading
+    from brain_b200.parallel.collective import HostCollective
+    for world, n in ((2, 1000), (3, 70001), (4, 17)):
+        coll = HostCollective.group(world)
+        g = torch.Generator().manual_seed(world)
+        bufs = [torch.randn(n, generator=g) for _ in range(world)]
+        want = bufs[0].clone()
+        for b in bufs[1:]:
+            want = want + b
+        ths = [threading.Thread(target=lambda r=r: coll[r].all_reduce(bufs[r])) for r in range(world)]
+        [t.start() for t in ths]
+        [t.join() for t in ths]
+        for b in bufs:
+            assert torch.equal(b, want)
