@@ -44,17 +44,25 @@ def cpu_dp(args) -> dict:
     for _ in range(workers):
         toks = torch.from_numpy(rng.tokens(B * (T + 1), cfg.vocab).astype("int64")).view(B, T + 1)
         mbs.append((toks[:, :-1].to(torch.int32).contiguous(), toks[:, 1:].contiguous()))
+    opt_times = []
     for step in range(args.steps):
         t1 = time.perf_counter()
-        losses.append(dp.train_step(mbs, 3e-4, wd=0.1, clip=1.0))
-        times.append(time.perf_counter() - t1)
+        losses.append(dp.forward_backward(mbs))
+        t2 = time.perf_counter()
+        dp.adamw_step(3e-4, 0.1, 1.0)       # all-reduce over the replicas, clip, AdamW, weights to every replica
+        t3 = time.perf_counter()
+        times.append(t3 - t1)
+        opt_times.append(t3 - t2)
     steady = times[2:] if len(times) > 4 else times
     ms = 1e3 * sum(steady) / len(steady)
+    opt_steady = opt_times[2:] if len(opt_times) > 4 else opt_times
+    opt_ms = 1e3 * sum(opt_steady) / len(opt_steady)
     report = gradcheck.check_gpt(n_dirs=4, d_model=64)
     fails = report.failures()
     worst = report.worst()
     return {"config": "cpu-dp", "metric": "train tok/s (GPT-2 small fp32, CPU backend, 2 DP thread workers)",
-            "value": workers * B * T / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms, "steps": args.steps,
+            "value": workers * B * T / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms,
+            "forward_backward_ms": ms - opt_ms, "reduce_and_optimiser_ms": opt_ms, "steps": args.steps,
             "loss_first": losses[0], "loss_last": losses[-1], "loss_decreased": losses[-1] < losses[0],
             "build_s": build_s, "threads": torch.get_num_threads(),
             "linear": "native csrc/cpu GEMM" if cpu_native.enabled() else "PyTorch ops",

@@ -110,9 +110,43 @@ def elementwise_suite(a, dev, bw):
     return res
 
 
+def cpu_gemm_suite(threads: int):
+    """The native fp32 GEMM of csrc/cpu against PyTorch's (oneDNN) on GPT-2 small's layer shapes, the
+    three products of a linear layer each; GFLOP/s, best of 6 trials of 5 calls (no GPU needed)."""
+    import time
+    from brain_b200.ops import cpu_native
+    torch.set_num_threads(threads)
+    cpu_native.threads = threads
+
+    def best(fn, n=5, trials=6):
+        fn()
+        fn()
+        b = 1e9
+        for _ in range(trials):
+            t = time.perf_counter()
+            for _ in range(n):
+                fn()
+            b = min(b, (time.perf_counter() - t) / n)
+        return b
+
+    rows = []
+    for M, N, K in ((512, 768, 768), (512, 2304, 768), (512, 3072, 768), (512, 768, 3072), (512, 50257, 768)):
+        x, w, g = torch.randn(M, K), torch.randn(N, K), torch.randn(M, N)
+        fl = 2.0 * M * N * K
+        row = {"m": M, "n": N, "k": K}
+        for name, native, lib in (("fwd", lambda: cpu_native.gemm(x, w, tb=True), lambda: x @ w.t()),
+                                  ("dx", lambda: cpu_native.gemm(g, w), lambda: g @ w),
+                                  ("dw", lambda: cpu_native.gemm(g, x, ta=True), lambda: g.t() @ x)):
+            row[name + "_native_gflops"] = round(fl / best(native) / 1e9)
+            row[name + "_pytorch_gflops"] = round(fl / best(lib) / 1e9)
+        rows.append(row)
+    return {"what": "cpu-gemm", "threads": threads, "shapes": rows}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "flash", "i8", "copy", "elementwise", "decode", "grouped"])
+    ap.add_argument("what", choices=["gemm", "flash", "i8", "copy", "elementwise", "decode", "grouped", "cpu-gemm"])
+    ap.add_argument("--threads", type=int, default=4, help="cpu-gemm: threads of both the native GEMM and PyTorch")
     ap.add_argument("--experts", type=int, default=16, help="grouped: experts (rows are split evenly)")
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=4096)
@@ -131,6 +165,9 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--library", action="store_true", help="also time the cuBLAS / SDPA baseline")
     a = ap.parse_args(argv)
+    if a.what == "cpu-gemm":
+        print(json.dumps(cpu_gemm_suite(a.threads)))
+        return 0
     from brain_b200.ops import _cuda, functional as F
     from brain_b200.ops.attention import flash_attention
 
