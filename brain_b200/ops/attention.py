@@ -134,6 +134,9 @@ def flash_attention(q, k, v, B, T, hq, hk, hd, causal=True, scale=None, S=None):
     S = T if S is None else S
     scale = 1.0 / math.sqrt(hd) if scale is None else scale
     if not q.is_cuda:
+        from . import cpu_native
+        if cpu_native.enabled() and cpu_native.attention_supported(q, hd, S) and k.dtype == v.dtype == q.dtype:
+            return cpu_native.attention(q, k, v, B, T, S, hq, hk, hd, causal, scale)
         o = ref.attention(q.reshape(B, T, hq, hd), k.reshape(B, S, hk, hd), v.reshape(B, S, hk, hd),
                           causal, scale)
         return o.reshape(B * T, hq * hd)

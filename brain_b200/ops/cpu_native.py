@@ -1,8 +1,10 @@
-"""Native part of the CPU backend (csrc/cpu/gemm.cpp): an AVX2 + FMA fp32 GEMM threaded over row
-panels, used for the three products of a linear layer (forward x W^T, dX = dY W, dW = dY^T X) and a
-row-parallel RMSNorm.  ``BRAIN_CPU_NATIVE=1`` routes the CPU path of ``ops.functional.linear``
-through it; the PyTorch restatement in ``ops/reference.py`` stays the oracle the tests compare both
-with.  Reference: crates/backend-cpu/src/fast_ops.rs, par.rs:27-83."""
+"""Native part of the CPU backend: an fp32 GEMM (csrc/cpu/gemm.cpp; AVX2 + FMA, or the AVX-512 tile
+chosen at run time) threaded over row blocks, used for the three products of a linear layer (forward
+x W^T, dX = dY W, dW = dY^T X); a row-parallel RMSNorm; and softmax attention with grouped KV heads,
+forward and backward (csrc/cpu/attention.cpp).  ``BRAIN_CPU_NATIVE=1`` routes the CPU paths of
+``ops.functional.linear`` and ``ops.attention.flash_attention`` through them; the PyTorch restatement
+in ``ops/reference.py`` stays the oracle the tests compare both with.
+Reference: crates/backend-cpu/src/fast_ops.rs, par.rs:27-83."""
 from __future__ import annotations
 
 import ctypes as c
@@ -74,3 +76,61 @@ class _Linear(torch.autograd.Function):
 
 def linear(x, w, bias=None):
     return _Linear.apply(x, w, bias)
+
+
+# ----------------------------------------------------------------------------------- attention
+_host.register({
+    "bbh_cpu_attn_fwd": (c.c_int, [c.c_void_p, c.c_int64] * 4 + [c.c_void_p] + [c.c_int] * 6 + [c.c_float, c.c_int, c.c_int]),
+    "bbh_cpu_attn_bwd": (c.c_int, [c.c_void_p, c.c_int64] * 5 + [c.c_void_p] + [c.c_void_p, c.c_int64] * 3 + [c.c_int] * 6 +
+                         [c.c_float, c.c_int, c.c_int]),
+})
+
+
+def attention_supported(q: torch.Tensor, hd: int, S: int) -> bool:
+    """fp32, head dimension a multiple of 8, and one head's keys and values (S x hd each) within about
+    1 MB: the kernels go through all visible keys once per query row, which is fast while K and V stay in
+    the core's L2 (1.5-3 x the batched-GEMM PyTorch path at 64-wide heads up to 1024 keys) and slow
+    beyond it (0.4 x at 2048 keys of 128-wide heads), so longer contexts keep the PyTorch path."""
+    return q.dtype == torch.float32 and hd % 8 == 0 and S * hd <= 128 * 1024
+
+
+class _Attention(torch.autograd.Function):
+    """Softmax attention with grouped KV heads on the native CPU kernels (csrc/cpu/attention.cpp): no
+    T x S score matrix is kept, backward recomputes probabilities from the saved log-sum-exp."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, B, T, S, hq, hk, hd, causal, scale):
+        q2, k2, v2 = (t if t.stride(-1) == 1 and t.dim() == 2 else t.reshape(-1, t.shape[-1]).contiguous()
+                      for t in (q, k, v))
+        o = torch.empty(B * T, hq * hd, dtype=torch.float32)
+        lse = torch.empty(B, hq, T, dtype=torch.float32)
+        rc = _host.lib().bbh_cpu_attn_fwd(q2.data_ptr(), q2.stride(0), k2.data_ptr(), k2.stride(0), v2.data_ptr(),
+                                          v2.stride(0), o.data_ptr(), o.stride(0), lse.data_ptr(), B, T, S, hq, hk,
+                                          hd, float(scale), int(causal), threads)
+        if rc != 0:
+            raise RuntimeError(f"bbh_cpu_attn_fwd failed ({rc})")
+        ctx.save_for_backward(q2, k2, v2, o, lse)
+        ctx.dims = (B, T, S, hq, hk, hd, bool(causal), float(scale))
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q2, k2, v2, o, lse = ctx.saved_tensors
+        B, T, S, hq, hk, hd, causal, scale = ctx.dims
+        do2 = do if do.stride(-1) == 1 else do.contiguous()
+        dq = torch.empty(B * T, hq * hd, dtype=torch.float32)
+        dk = torch.empty(B * S, hk * hd, dtype=torch.float32)
+        dv = torch.empty(B * S, hk * hd, dtype=torch.float32)
+        rc = _host.lib().bbh_cpu_attn_bwd(q2.data_ptr(), q2.stride(0), k2.data_ptr(), k2.stride(0), v2.data_ptr(),
+                                          v2.stride(0), o.data_ptr(), o.stride(0), do2.data_ptr(), do2.stride(0),
+                                          lse.data_ptr(), dq.data_ptr(), dq.stride(0), dk.data_ptr(), dk.stride(0),
+                                          dv.data_ptr(), dv.stride(0), B, T, S, hq, hk, hd, scale, int(causal), threads)
+        if rc != 0:
+            raise RuntimeError(f"bbh_cpu_attn_bwd failed ({rc})")
+        return dq, dk, dv, None, None, None, None, None, None, None, None
+
+
+def attention(q, k, v, B, T, S, hq, hk, hd, causal=True, scale=None):
+    """q: [B*T, hq*hd]; k, v: [B*S, hk*hd] -> [B*T, hq*hd] (fp32, head dimension a multiple of 8)."""
+    scale = 1.0 / (hd ** 0.5) if scale is None else scale
+    return _Attention.apply(q, k, v, B, T, S, hq, hk, hd, causal, scale)

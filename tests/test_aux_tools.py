@@ -218,6 +218,44 @@ def test_native_cpu_gemm_and_linear_autograd():
     assert torch.allclose(cpu_native.rmsnorm(xn, wn, 1e-6), ref.rmsnorm(xn, wn, 1e-6), rtol=1e-4, atol=1e-5)
 
 
+def test_native_cpu_attention_matches_the_materialised_reference(monkeypatch):
+    """csrc/cpu/attention.cpp against the fp64 materialised-scores reference: causal and full, grouped
+    KV heads, more keys than queries, lengths that are not multiples of 8; forward and all three
+    gradients.  With BRAIN_CPU_NATIVE=1 the CPU path of flash_attention runs on it."""
+    import math
+    from brain_b200.ops import cpu_native, reference as ref
+    from brain_b200.ops.attention import flash_attention
+    torch.manual_seed(0)
+    for B, T, S, hq, hk, hd, causal in ((2, 37, 37, 4, 2, 16, True), (1, 16, 40, 6, 3, 8, True),
+                                        (2, 33, 33, 4, 4, 64, False), (1, 70, 70, 2, 1, 24, True)):
+        q = torch.randn(B * T, hq * hd, requires_grad=True)
+        k = torch.randn(B * S, hk * hd, requires_grad=True)
+        v = torch.randn(B * S, hk * hd, requires_grad=True)
+        o = cpu_native.attention(q, k, v, B, T, S, hq, hk, hd, causal)
+        g = torch.randn_like(o)
+        got = torch.autograd.grad(o, (q, k, v), g)
+        q64, k64, v64 = (t.detach().double().requires_grad_() for t in (q, k, v))
+        want = ref.attention(q64.reshape(B, T, hq, hd), k64.reshape(B, S, hk, hd), v64.reshape(B, S, hk, hd),
+                             causal, 1 / math.sqrt(hd)).reshape(B * T, hq * hd)
+        wgrads = torch.autograd.grad(want, (q64, k64, v64), g.double())
+        assert float((o.detach() - want.detach()).abs().max()) < 5e-6
+        for a, b in zip(got, wgrads):
+            assert float((a - b).abs().max()) < 2e-5
+    # routing: the public op takes the native kernels only when the CPU backend's native part is on
+    q = torch.randn(2 * 16, 4 * 8)
+    k = torch.randn(2 * 16, 2 * 8)
+    v = torch.randn(2 * 16, 2 * 8)
+    monkeypatch.setenv("BRAIN_CPU_NATIVE", "0")
+    base = flash_attention(q, k, v, 2, 16, 4, 2, 8)
+    monkeypatch.setenv("BRAIN_CPU_NATIVE", "1")
+    calls = []
+    real = cpu_native.attention
+    monkeypatch.setattr(cpu_native, "attention", lambda *a, **kw: (calls.append(1), real(*a, **kw))[1])
+    nat = flash_attention(q, k, v, 2, 16, 4, 2, 8)
+    assert calls and torch.allclose(nat, base, atol=1e-5)
+    assert not cpu_native.attention_supported(q, 128, 4096) and not cpu_native.attention_supported(q, 12, 16)
+
+
 def test_bench_reference_arm_reports_unavailable_and_exits_zero():
     """``bench.py --impl reference`` cannot run the reference here (a Rust / graphics-API workspace): it
     must say so in one JSON line and exit 0, whatever the other flags are."""
