@@ -143,9 +143,56 @@ def cpu_gemm_suite(threads: int):
     return {"what": "cpu-gemm", "threads": threads, "shapes": rows}
 
 
+def cpu_attn_suite(threads: int):
+    """Native CPU attention (csrc/cpu/attention.cpp) against the materialised-scores PyTorch path,
+    causal, forward alone and forward + backward; milliseconds, best of 6 trials of 5 calls."""
+    import math
+    import time
+    from brain_b200.ops import cpu_native, reference as ref
+    torch.set_num_threads(threads)
+    cpu_native.threads = threads
+
+    def best(fn, n=5, trials=6):
+        fn()
+        b = 1e9
+        for _ in range(trials):
+            t = time.perf_counter()
+            for _ in range(n):
+                fn()
+            b = min(b, (time.perf_counter() - t) / n)
+        return round(b * 1e3, 2)
+
+    rows = []
+    for B, T, hq, hk, hd in ((4, 128, 12, 12, 64), (2, 1024, 12, 12, 64), (1, 2048, 16, 8, 128)):
+        q = torch.randn(B * T, hq * hd, requires_grad=True)
+        k = torch.randn(B * T, hk * hd, requires_grad=True)
+        v = torch.randn(B * T, hk * hd, requires_grad=True)
+        g = torch.randn(B * T, hq * hd)
+        sc = 1 / math.sqrt(hd)
+
+        def native(train):
+            with torch.set_grad_enabled(train):
+                o = cpu_native.attention(q, k, v, B, T, T, hq, hk, hd, True)
+            if train:
+                torch.autograd.grad(o, (q, k, v), g)
+
+        def lib(train):
+            with torch.set_grad_enabled(train):
+                o = ref.attention(q.reshape(B, T, hq, hd), k.reshape(B, T, hk, hd), v.reshape(B, T, hk, hd), True,
+                                  sc).reshape(B * T, hq * hd)
+            if train:
+                torch.autograd.grad(o, (q, k, v), g)
+
+        rows.append({"batch": B, "seq": T, "heads": f"{hq}q/{hk}kv", "head_dim": hd,
+                     "routed_to_native": cpu_native.attention_supported(q, hd, T),
+                     "native_fwd_ms": best(lambda: native(False)), "native_fwd_bwd_ms": best(lambda: native(True)),
+                     "pytorch_fwd_ms": best(lambda: lib(False)), "pytorch_fwd_bwd_ms": best(lambda: lib(True))})
+    return {"what": "cpu-attn", "threads": threads, "shapes": rows}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "flash", "i8", "copy", "elementwise", "decode", "grouped", "cpu-gemm"])
+    ap.add_argument("what", choices=["gemm", "flash", "i8", "copy", "elementwise", "decode", "grouped", "cpu-gemm", "cpu-attn"])
     ap.add_argument("--threads", type=int, default=4, help="cpu-gemm: threads of both the native GEMM and PyTorch")
     ap.add_argument("--experts", type=int, default=16, help="grouped: experts (rows are split evenly)")
     ap.add_argument("--m", type=int, default=16384)
@@ -167,6 +214,9 @@ def main(argv=None):
     a = ap.parse_args(argv)
     if a.what == "cpu-gemm":
         print(json.dumps(cpu_gemm_suite(a.threads)))
+        return 0
+    if a.what == "cpu-attn":
+        print(json.dumps(cpu_attn_suite(a.threads)))
         return 0
     from brain_b200.ops import _cuda, functional as F
     from brain_b200.ops.attention import flash_attention
