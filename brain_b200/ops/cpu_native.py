@@ -86,17 +86,15 @@ _host.register({
 })
 
 
-def attention_supported(q: torch.Tensor, hd: int, S: int) -> bool:
-    """fp32, head dimension a multiple of 8, and one head's keys and values (S x hd each) within about
-    1 MB: the kernels go through all visible keys once per query row, which is fast while K and V stay in
-    the core's L2 (1.5-3 x the batched-GEMM PyTorch path at 64-wide heads up to 1024 keys) and slow
-    beyond it (0.4 x at 2048 keys of 128-wide heads), so longer contexts keep the PyTorch path."""
-    return q.dtype == torch.float32 and hd % 8 == 0 and S * hd <= 128 * 1024
+def attention_supported(q: torch.Tensor, hd: int, S: int = 0) -> bool:
+    """fp32 and a head dimension that is a multiple of 8 (the kernels' vector width)."""
+    return q.dtype == torch.float32 and hd % 8 == 0 and hd > 0
 
 
 class _Attention(torch.autograd.Function):
-    """Softmax attention with grouped KV heads on the native CPU kernels (csrc/cpu/attention.cpp): no
-    T x S score matrix is kept, backward recomputes probabilities from the saved log-sum-exp."""
+    """Softmax attention with grouped KV heads on the native CPU kernels (csrc/cpu/attention.cpp):
+    tiled with a running softmax, so no T x S score matrix exists at any point; backward recomputes
+    the probabilities from the saved log-sum-exp."""
 
     @staticmethod
     def forward(ctx, q, k, v, B, T, S, hq, hk, hd, causal, scale):

@@ -2,15 +2,15 @@
 // backward, fp32.  Rows are tokens: q [B*T, hq*hd], k and v [B*S, hk*hd] (row strides given), head h
 // at columns [h*hd, (h+1)*hd).  Query row i of a sequence sees keys 0 .. i + (S - T) when causal.
 //
-// Forward, per (sequence, query head) and block of query rows: scores against all visible keys into a
-// small buffer, row maximum, exponentials (vector polynomial), sum, then the weighted sum of V rows in
-// registers; the log-sum-exp of every row is kept for backward.  No T x S matrix outlives a row.
-// Backward in two passes that both recompute the probabilities from the saved log-sum-exp: dQ per
-// block of query rows, then dK / dV per block of keys (scores with the roles swapped), so every output
-// row belongs to exactly one task and nothing is shared between threads.  Dot products and row updates
-// go eight rows at a time (one set of horizontal sums, one load and store of the updated row per eight
-// multiply-adds).  Every query row passes over all its keys, so this is for heads whose K and V fit in
-// the core's L2; the Python side keeps longer contexts on the PyTorch path.
+// Forward, per (sequence, query head) and block of 32 query rows: tiles of 64 keys; each tile is used by
+// every row of the block (scores, running maximum and sum, rescale, weighted sum of the tile's V rows)
+// before the next tile is touched, so K and V are read once per block of rows, not once per row.  The
+// log-sum-exp of every row is kept for backward.  No T x S matrix exists at any point.
+// Backward in two passes that both recompute the probabilities from the saved log-sum-exp: dQ per block
+// of query rows over key tiles, then dK / dV per block of keys over query-row tiles (scores with the
+// roles swapped), so every output row belongs to exactly one task and nothing is shared between threads.
+// Dot products and row updates go eight rows at a time (one set of horizontal sums, one load and store
+// of the updated row per eight multiply-adds).
 //
 // Replaces the attention half of crates/backend-cpu/src/fast_ops.rs; the PyTorch restatement with
 // materialised scores (ops/reference.py) stays the oracle.
@@ -165,7 +165,39 @@ struct Shape {
   int visible(int i) const { return causal ? std::min(S, i + (S - T) + 1) : S; }
 };
 
-constexpr int ROWS_PER_TASK = 32;
+constexpr int ROWS_PER_TASK = 32;   // query rows (dQ, forward) or keys (dK / dV) one task owns
+constexpr int TILE = 64;            // rows of the other operand taken at a time: 64 x 128 floats are 32 KB
+
+// scores of one query row against n (<= TILE) keys starting at kb, times scale; returns their maximum
+inline float tile_scores(const float* qi, const float* kb, int64_t ldk, int n, int hd, float scale, float* sc) {
+  const __m256 vscale = _mm256_set1_ps(scale);
+  __m256 vmax = _mm256_set1_ps(-INFINITY);
+  float m = -INFINITY;
+  int j = 0;
+  for (; j + 8 <= n; j += 8) {
+    const __m256 s8 = _mm256_mul_ps(vscale, dot8(qi, kb + (int64_t)j * ldk, ldk, hd));
+    _mm256_storeu_ps(sc + j, s8);
+    vmax = _mm256_max_ps(vmax, s8);
+  }
+  if (j) {
+    alignas(32) float t[8];
+    _mm256_store_ps(t, vmax);
+    for (int q8 = 0; q8 < 8; ++q8) m = std::max(m, t[q8]);
+  }
+  for (; j < n; ++j) {
+    const float s = scale * dot(qi, kb + (int64_t)j * ldk, hd);
+    sc[j] = s;
+    m = std::max(m, s);
+  }
+  return m;
+}
+
+// y += sum_j a[j] * x_j over n rows
+inline void rows_axpy(const float* a, const float* x, int64_t ldx, int n, float* y, int hd) {
+  int j = 0;
+  for (; j + 8 <= n; j += 8) axpy8(a + j, x + (int64_t)j * ldx, ldx, y, hd);
+  for (; j < n; ++j) axpy(a[j], x + (int64_t)j * ldx, y, hd);
+}
 
 }  // namespace
 
@@ -180,45 +212,48 @@ BBH_API int bbh_cpu_attn_fwd(const float* q, int64_t ldq, const float* k, int64_
   parallel_tasks(B * hq * blocks, threads, [&](int task) {
     const int blk = task % blocks, h = (task / blocks) % hq, b = task / (blocks * hq);
     const int hkv = h / g;
-    std::vector<float> sc((size_t)((S + 7) / 8) * 8);
-    for (int i = blk * ROWS_PER_TASK; i < std::min(T, (blk + 1) * ROWS_PER_TASK); ++i) {
-      const float* qi = q + ((int64_t)b * T + i) * ldq + (int64_t)h * hd;
+    const int i0 = blk * ROWS_PER_TASK, i1 = std::min(T, i0 + ROWS_PER_TASK);
+    float m[ROWS_PER_TASK], l[ROWS_PER_TASK];
+    for (int i = i0; i < i1; ++i) {
+      m[i - i0] = -INFINITY;
+      l[i - i0] = 0.f;
+      std::memset(o + ((int64_t)b * T + i) * ldo + (int64_t)h * hd, 0, sizeof(float) * hd);
+    }
+    alignas(32) float sc[TILE];
+    const int n_max = sh.visible(i1 - 1);   // the block's last row sees the most keys
+    // a tile of keys (and of V rows) is used by every row of the block before the next one is
+    // touched; the running maximum and sum of each row rescale what it has accumulated so far
+    for (int j0 = 0; j0 < n_max; j0 += TILE) {
+      const float* kb = k + ((int64_t)b * S + j0) * ldk + (int64_t)hkv * hd;
+      const float* vb = v + ((int64_t)b * S + j0) * ldv + (int64_t)hkv * hd;
+      for (int i = i0; i < i1; ++i) {
+        const int n = std::min(sh.visible(i), j0 + TILE) - j0;
+        if (n <= 0) continue;
+        const int r = i - i0;
+        const float* qi = q + ((int64_t)b * T + i) * ldq + (int64_t)h * hd;
+        float* oi = o + ((int64_t)b * T + i) * ldo + (int64_t)h * hd;
+        const float mt = tile_scores(qi, kb, ldk, n, hd, scale, sc);
+        const float m_new = std::max(m[r], mt);
+        const float alpha = m[r] == -INFINITY ? 0.f : std::exp(m[r] - m_new);
+        l[r] = l[r] * alpha + exp_rows(sc, n, m_new);
+        m[r] = m_new;
+        if (alpha != 1.f) {
+          const __m256 va = _mm256_set1_ps(alpha);
+          for (int d = 0; d < hd; d += 8) _mm256_storeu_ps(oi + d, _mm256_mul_ps(va, _mm256_loadu_ps(oi + d)));
+        }
+        rows_axpy(sc, vb, ldv, n, oi, hd);
+      }
+    }
+    for (int i = i0; i < i1; ++i) {
+      const int r = i - i0;
       float* oi = o + ((int64_t)b * T + i) * ldo + (int64_t)h * hd;
-      const int n = sh.visible(i);
-      if (n <= 0) {   // a query that sees no key: zero output, lse -inf
-        std::memset(oi, 0, sizeof(float) * hd);
+      if (l[r] > 0.f) {
+        const __m256 inv = _mm256_set1_ps(1.0f / l[r]);
+        for (int d = 0; d < hd; d += 8) _mm256_storeu_ps(oi + d, _mm256_mul_ps(inv, _mm256_loadu_ps(oi + d)));
+        lse[((int64_t)b * hq + h) * T + i] = m[r] + std::log(l[r]);
+      } else {   // a query that sees no key: zero output, lse -inf
         lse[((int64_t)b * hq + h) * T + i] = -INFINITY;
-        continue;
       }
-      float m = -INFINITY;
-      const float* kb = k + (int64_t)b * S * ldk + (int64_t)hkv * hd;
-      int j = 0;
-      __m256 vmax = _mm256_set1_ps(-INFINITY);
-      const __m256 vscale = _mm256_set1_ps(scale);
-      for (; j + 8 <= n; j += 8) {
-        const __m256 s8 = _mm256_mul_ps(vscale, dot8(qi, kb + (int64_t)j * ldk, ldk, hd));
-        _mm256_storeu_ps(sc.data() + j, s8);
-        vmax = _mm256_max_ps(vmax, s8);
-      }
-      if (j) {
-        alignas(32) float t[8];
-        _mm256_store_ps(t, vmax);
-        for (int q8 = 0; q8 < 8; ++q8) m = std::max(m, t[q8]);
-      }
-      for (; j < n; ++j) {
-        const float s = scale * dot(qi, kb + (int64_t)j * ldk, hd);
-        sc[j] = s;
-        m = std::max(m, s);
-      }
-      const float sum = exp_rows(sc.data(), n, m);
-      std::memset(oi, 0, sizeof(float) * hd);
-      const float* vb = v + (int64_t)b * S * ldv + (int64_t)hkv * hd;
-      int jv = 0;
-      for (; jv + 8 <= n; jv += 8) axpy8(sc.data() + jv, vb + (int64_t)jv * ldv, ldv, oi, hd);
-      for (; jv < n; ++jv) axpy(sc[jv], vb + (int64_t)jv * ldv, oi, hd);
-      const __m256 inv = _mm256_set1_ps(1.0f / sum);
-      for (int d = 0; d < hd; d += 8) _mm256_storeu_ps(oi + d, _mm256_mul_ps(inv, _mm256_loadu_ps(oi + d)));
-      lse[((int64_t)b * hq + h) * T + i] = m + std::log(sum);
     }
   });
   return 0;
@@ -237,86 +272,85 @@ BBH_API int bbh_cpu_attn_bwd(const float* q, int64_t ldq, const float* k, int64_
   // delta_i = dO_i . O_i, kept in a [B, hq, T] table both passes read
   std::vector<float> delta((size_t)B * hq * T);
   const int blocks = (T + ROWS_PER_TASK - 1) / ROWS_PER_TASK;
-  // pass 1, one task per (sequence, query head, block of query rows): dQ.  Per row: scores and dO.V
-  // against eight keys at a time, probabilities from the saved log-sum-exp, dS, dQ_i += dS_ij K_j.
+  // pass 1, one task per (sequence, query head, block of query rows): dQ.  Key tile by key tile, every
+  // row of the block: scores and dO.V, probabilities from the saved log-sum-exp, dS, dQ_i += dS_ij K_j.
   parallel_tasks(B * hq * blocks, threads, [&](int task) {
     const int blk = task % blocks, h = (task / blocks) % hq, b = task / (blocks * hq);
     const int hkv = h / g;
-    const float* kb = k + (int64_t)b * S * ldk + (int64_t)hkv * hd;
-    const float* vb = v + (int64_t)b * S * ldv + (int64_t)hkv * hd;
-    std::vector<float> p((size_t)((S + 7) / 8) * 8), dp((size_t)((S + 7) / 8) * 8);
-    for (int i = blk * ROWS_PER_TASK; i < std::min(T, (blk + 1) * ROWS_PER_TASK); ++i) {
+    const int i0 = blk * ROWS_PER_TASK, i1 = std::min(T, i0 + ROWS_PER_TASK);
+    for (int i = i0; i < i1; ++i) {
       const int64_t row = (int64_t)b * T + i;
-      const float* qi = q + row * ldq + (int64_t)h * hd;
-      const float* doi = dout + row * lddo + (int64_t)h * hd;
-      float* dqi = dq + row * lddq + (int64_t)h * hd;
-      std::memset(dqi, 0, sizeof(float) * hd);
-      const float dl = dot(doi, o + row * ldo + (int64_t)h * hd, hd);
-      delta[((size_t)b * hq + h) * T + i] = dl;
-      const int n = sh.visible(i);
-      if (n <= 0) continue;
-      const float l = lse[((int64_t)b * hq + h) * T + i];
-      int j = 0;
-      for (; j + 8 <= n; j += 8) {
-        _mm256_storeu_ps(p.data() + j, _mm256_mul_ps(vscale, dot8(qi, kb + (int64_t)j * ldk, ldk, hd)));
-        _mm256_storeu_ps(dp.data() + j, dot8(doi, vb + (int64_t)j * ldv, ldv, hd));
+      std::memset(dq + row * lddq + (int64_t)h * hd, 0, sizeof(float) * hd);
+      delta[((size_t)b * hq + h) * T + i] = dot(dout + row * lddo + (int64_t)h * hd, o + row * ldo + (int64_t)h * hd, hd);
+    }
+    alignas(32) float p[TILE], dp[TILE];
+    const int n_max = sh.visible(i1 - 1);
+    for (int j0 = 0; j0 < n_max; j0 += TILE) {
+      const float* kb = k + ((int64_t)b * S + j0) * ldk + (int64_t)hkv * hd;
+      const float* vb = v + ((int64_t)b * S + j0) * ldv + (int64_t)hkv * hd;
+      for (int i = i0; i < i1; ++i) {
+        const int n = std::min(sh.visible(i), j0 + TILE) - j0;
+        if (n <= 0) continue;
+        const int64_t row = (int64_t)b * T + i;
+        const float* qi = q + row * ldq + (int64_t)h * hd;
+        const float* doi = dout + row * lddo + (int64_t)h * hd;
+        const float l = lse[((int64_t)b * hq + h) * T + i];
+        const float dl = delta[((size_t)b * hq + h) * T + i];
+        tile_scores(qi, kb, ldk, n, hd, scale, p);
+        int j = 0;
+        for (; j + 8 <= n; j += 8) _mm256_storeu_ps(dp + j, dot8(doi, vb + (int64_t)j * ldv, ldv, hd));
+        for (; j < n; ++j) dp[j] = dot(doi, vb + (int64_t)j * ldv, hd);
+        exp_rows(p, n, l);   // probabilities: exp(score - lse)
+        for (j = 0; j < n; ++j) p[j] = p[j] * (dp[j] - dl) * scale;   // dS
+        rows_axpy(p, kb, ldk, n, dq + row * lddq + (int64_t)h * hd, hd);
       }
-      for (; j < n; ++j) {
-        p[j] = scale * dot(qi, kb + (int64_t)j * ldk, hd);
-        dp[j] = dot(doi, vb + (int64_t)j * ldv, hd);
-      }
-      exp_rows(p.data(), n, l);   // probabilities: exp(score - lse)
-      for (j = 0; j < n; ++j) p[j] = p[j] * (dp[j] - dl) * scale;   // dS
-      for (j = 0; j + 8 <= n; j += 8) axpy8(p.data() + j, kb + (int64_t)j * ldk, ldk, dqi, hd);
-      for (; j < n; ++j) axpy(p[j], kb + (int64_t)j * ldk, dqi, hd);
     }
   });
-  // pass 2, one task per (sequence, KV head, block of keys): dK and dV.  Per key and query head of
-  // the group: the same scores with the roles swapped (eight query rows at a time), then
-  // dV_j += P_ij dO_i and dK_j += dS_ij Q_i into rows only this task writes.
+  // pass 2, one task per (sequence, KV head, block of keys): dK and dV.  Query-row tile by tile, every
+  // key of the block and query head of the group: the same scores with the roles swapped (eight query
+  // rows at a time), then dV_j += P_ij dO_i and dK_j += dS_ij Q_i into rows only this task writes.
   const int kblocks = (S + ROWS_PER_TASK - 1) / ROWS_PER_TASK;
   parallel_tasks(B * hk * kblocks, threads, [&](int task) {
     const int blk = task % kblocks, hkv = (task / kblocks) % hk, b = task / (kblocks * hk);
-    std::vector<float> p((size_t)((T + 7) / 8) * 8 + 8), ds((size_t)((T + 7) / 8) * 8 + 8);
-    for (int j = blk * ROWS_PER_TASK; j < std::min(S, (blk + 1) * ROWS_PER_TASK); ++j) {
-      const int64_t kr = (int64_t)b * S + j;
-      const float* kj = k + kr * ldk + (int64_t)hkv * hd;
-      const float* vj = v + kr * ldv + (int64_t)hkv * hd;
-      float* dkj = dk + kr * lddk + (int64_t)hkv * hd;
-      float* dvj = dv + kr * lddv + (int64_t)hkv * hd;
-      std::memset(dkj, 0, sizeof(float) * hd);
-      std::memset(dvj, 0, sizeof(float) * hd);
-      // query rows that see key j: i >= j - (S - T) when causal, all rows otherwise
-      const int i_lo = causal ? std::max(0, j - (S - T)) : 0;
-      const int n = T - i_lo;
-      if (n <= 0) continue;
-      for (int h = hkv * g; h < (hkv + 1) * g; ++h) {
-        const float* qb = q + ((int64_t)b * T + i_lo) * ldq + (int64_t)h * hd;
-        const float* dob = dout + ((int64_t)b * T + i_lo) * lddo + (int64_t)h * hd;
-        const float* lrow = lse + ((int64_t)b * hq + h) * T + i_lo;
-        const float* drow = delta.data() + ((size_t)b * hq + h) * T + i_lo;
-        int i = 0;
-        for (; i + 8 <= n; i += 8) {
-          const __m256 s8 = _mm256_mul_ps(vscale, dot8(kj, qb + (int64_t)i * ldq, ldq, hd));
-          const __m256 p8 = exp256(_mm256_sub_ps(s8, _mm256_loadu_ps(lrow + i)));
-          const __m256 dp8 = dot8(vj, dob + (int64_t)i * lddo, lddo, hd);
-          _mm256_storeu_ps(p.data() + i, p8);
-          _mm256_storeu_ps(ds.data() + i,
-                           _mm256_mul_ps(_mm256_mul_ps(p8, _mm256_sub_ps(dp8, _mm256_loadu_ps(drow + i))), vscale));
-        }
-        for (; i < n; ++i) {
-          const float sc1 = scale * dot(kj, qb + (int64_t)i * ldq, hd) - lrow[i];
-          const float pi = sc1 < -87.0f ? 0.0f : std::exp(sc1);
-          p[i] = pi;
-          ds[i] = pi * (dot(vj, dob + (int64_t)i * lddo, hd) - drow[i]) * scale;
-        }
-        for (i = 0; i + 8 <= n; i += 8) {
-          axpy8(p.data() + i, dob + (int64_t)i * lddo, lddo, dvj, hd);
-          axpy8(ds.data() + i, qb + (int64_t)i * ldq, ldq, dkj, hd);
-        }
-        for (; i < n; ++i) {
-          axpy(p[i], dob + (int64_t)i * lddo, dvj, hd);
-          axpy(ds[i], qb + (int64_t)i * ldq, dkj, hd);
+    const int j0 = blk * ROWS_PER_TASK, j1 = std::min(S, j0 + ROWS_PER_TASK);
+    for (int j = j0; j < j1; ++j) {
+      std::memset(dk + ((int64_t)b * S + j) * lddk + (int64_t)hkv * hd, 0, sizeof(float) * hd);
+      std::memset(dv + ((int64_t)b * S + j) * lddv + (int64_t)hkv * hd, 0, sizeof(float) * hd);
+    }
+    alignas(32) float p[TILE + 8], ds[TILE + 8];
+    // query rows that see key j: i >= j - (S - T) when causal, all rows otherwise
+    const int first = causal ? std::max(0, j0 - (S - T)) : 0;
+    for (int t0 = first; t0 < T; t0 += TILE) {
+      for (int j = j0; j < j1; ++j) {
+        const int a = std::max(t0, causal ? std::max(0, j - (S - T)) : 0), e = std::min(T, t0 + TILE);
+        const int n = e - a;
+        if (n <= 0) continue;
+        const int64_t kr = (int64_t)b * S + j;
+        const float* kj = k + kr * ldk + (int64_t)hkv * hd;
+        const float* vj = v + kr * ldv + (int64_t)hkv * hd;
+        float* dkj = dk + kr * lddk + (int64_t)hkv * hd;
+        float* dvj = dv + kr * lddv + (int64_t)hkv * hd;
+        for (int h = hkv * g; h < (hkv + 1) * g; ++h) {
+          const float* qb = q + ((int64_t)b * T + a) * ldq + (int64_t)h * hd;
+          const float* dob = dout + ((int64_t)b * T + a) * lddo + (int64_t)h * hd;
+          const float* lrow = lse + ((int64_t)b * hq + h) * T + a;
+          const float* drow = delta.data() + ((size_t)b * hq + h) * T + a;
+          int i = 0;
+          for (; i + 8 <= n; i += 8) {
+            const __m256 s8 = _mm256_mul_ps(vscale, dot8(kj, qb + (int64_t)i * ldq, ldq, hd));
+            const __m256 p8 = exp256(_mm256_sub_ps(s8, _mm256_loadu_ps(lrow + i)));
+            const __m256 dp8 = dot8(vj, dob + (int64_t)i * lddo, lddo, hd);
+            _mm256_storeu_ps(p + i, p8);
+            _mm256_storeu_ps(ds + i, _mm256_mul_ps(_mm256_mul_ps(p8, _mm256_sub_ps(dp8, _mm256_loadu_ps(drow + i))), vscale));
+          }
+          for (; i < n; ++i) {
+            const float sc1 = scale * dot(kj, qb + (int64_t)i * ldq, hd) - lrow[i];
+            const float pi = sc1 < -87.0f ? 0.0f : std::exp(sc1);
+            p[i] = pi;
+            ds[i] = pi * (dot(vj, dob + (int64_t)i * lddo, hd) - drow[i]) * scale;
+          }
+          rows_axpy(p, dob, lddo, n, dvj, hd);
+          rows_axpy(ds, qb, ldq, n, dkj, hd);
         }
       }
     }

@@ -220,14 +220,17 @@ def test_native_cpu_gemm_and_linear_autograd():
 
 def test_native_cpu_attention_matches_the_materialised_reference(monkeypatch):
     """csrc/cpu/attention.cpp against the fp64 materialised-scores reference: causal and full, grouped
-    KV heads, more keys than queries, lengths that are not multiples of 8; forward and all three
+    KV heads, more keys than queries, lengths that are not multiples of 8 and that cross the 64-key and
+    32-row tile edges; forward and all three
     gradients.  With BRAIN_CPU_NATIVE=1 the CPU path of flash_attention runs on it."""
     import math
     from brain_b200.ops import cpu_native, reference as ref
     from brain_b200.ops.attention import flash_attention
     torch.manual_seed(0)
     for B, T, S, hq, hk, hd, causal in ((2, 37, 37, 4, 2, 16, True), (1, 16, 40, 6, 3, 8, True),
-                                        (2, 33, 33, 4, 4, 64, False), (1, 70, 70, 2, 1, 24, True)):
+                                        (2, 33, 33, 4, 4, 64, False), (1, 70, 70, 2, 1, 24, True),
+                                        (1, 150, 150, 2, 1, 16, True), (1, 65, 129, 3, 1, 40, True),
+                                        (1, 130, 67, 2, 2, 32, False)):
         q = torch.randn(B * T, hq * hd, requires_grad=True)
         k = torch.randn(B * S, hk * hd, requires_grad=True)
         v = torch.randn(B * S, hk * hd, requires_grad=True)
@@ -253,7 +256,7 @@ def test_native_cpu_attention_matches_the_materialised_reference(monkeypatch):
     monkeypatch.setattr(cpu_native, "attention", lambda *a, **kw: (calls.append(1), real(*a, **kw))[1])
     nat = flash_attention(q, k, v, 2, 16, 4, 2, 8)
     assert calls and torch.allclose(nat, base, atol=1e-5)
-    assert not cpu_native.attention_supported(q, 128, 4096) and not cpu_native.attention_supported(q, 12, 16)
+    assert cpu_native.attention_supported(q, 128, 4096) and not cpu_native.attention_supported(q, 12, 16)
 
 
 def test_bench_reference_arm_reports_unavailable_and_exits_zero():
