@@ -14,6 +14,9 @@
 // are the outer loop and K slabs the inner one, so a task's part of C stays in cache while K is summed.  A task owns a block of up to MC rows: it packs them once per slab and
 // sweeps them over the slab one B panel at a time, so a B panel is pulled into L1 once per block instead
 // of once per 6-row panel.  Worker threads are persistent (one pool per calling thread).
+// Products with few rows of A (a batch of tokens against a weight matrix) take another route: all of A
+// is packed once, then every task owns a run of columns and packs its own piece of B (one barrier per
+// call).  Scratch buffers are per thread and grow-only; the workers park when a call ends.
 //
 // The CPU backend exists for the CPU-only configuration (GPT-2 small, two data-parallel thread
 // workers) and as an independent check of the PyTorch oracle; replaces crates/backend-cpu/src/fast_ops.rs
@@ -63,6 +66,7 @@ class Pool {
     for (auto& t : th_) t.join();
   }
   int workers() const { return (int)th_.size(); }
+  void quiet() { quiet_.store(true, std::memory_order_release); }
 
   template <typename F>
   void run(int n, F&& fn) {
@@ -77,6 +81,7 @@ class Pool {
     // worker straight into a blocked lock, a sleep and a wake-up per parallel region.)
     job_ = &f;
     n_ = n;
+    quiet_.store(false, std::memory_order_relaxed);
     next_.store(0, std::memory_order_relaxed);
     left_.store((int)th_.size(), std::memory_order_relaxed);
     unsigned long g1;
@@ -104,7 +109,10 @@ class Pool {
       // generations only grow; "newer than seen" (not "different") because a worker that was woken
       // through gen_ can be one step ahead of gen_pub_ for a moment
       auto newer = [&](unsigned long g) { return (long)(g - seen) > 0; };
-      for (int spin = 0; spin < 20000 && !newer(gen_pub_.load(std::memory_order_acquire)); ++spin) _mm_pause();
+      for (int spin = 0; spin < 20000 && !newer(gen_pub_.load(std::memory_order_acquire)) &&
+                         !quiet_.load(std::memory_order_acquire);
+           ++spin)
+        _mm_pause();
       unsigned long cur = gen_pub_.load(std::memory_order_acquire);
       if (!newer(cur)) {
         std::unique_lock<std::mutex> g(m_);
@@ -133,16 +141,25 @@ class Pool {
   std::atomic<int> next_{0};
   std::atomic<int> left_{0};
   std::atomic<unsigned long> gen_pub_{0};   // copy of gen_ the spinning workers poll without the lock
+  std::atomic<bool> quiet_{false};          // set at the end of a GEMM call: park without spinning
   std::atomic<int> parked_{0};              // workers asleep on cv_ (run() skips the notify when none are)
   int n_ = 0;
   unsigned long gen_ = 0;
   std::atomic<bool> stop_{false};
 };
 
+thread_local std::unique_ptr<Pool> tl_pool;
+
 Pool& pool_for(int threads) {
-  thread_local std::unique_ptr<Pool> pool;
-  if (!pool || pool->workers() != threads - 1) pool.reset(new Pool(threads - 1));
-  return *pool;
+  if (!tl_pool || tl_pool->workers() != threads - 1) tl_pool.reset(new Pool(threads - 1));
+  return *tl_pool;
+}
+
+// End of a GEMM call: the workers stop spinning for the next region and park at once.  What follows
+// a GEMM in a training step is other libraries' thread teams on the same cores (bias, activation,
+// normalisation), which spinning workers would be time-sliced against.
+void quiesce_pool() {
+  if (tl_pool) tl_pool->quiet();
 }
 
 template <typename F>
@@ -330,12 +347,85 @@ static int gemm_impl(const float* A, const float* B, float* C, int M, int N, int
     return 0;
   }
   if (threads <= 0) threads = (int)std::max(1u, std::thread::hardware_concurrency());
+  // Few rows (a batch of tokens against a weight matrix: forward, dX, the LM head): the whole of A is
+  // packed once, by all threads together, and after that single barrier every task owns a run of
+  // columns: it packs its own piece of B (which stays in its core's L2 and is read by nobody else) and
+  // takes all rows of A over it, K slab by K slab, so its piece of C stays in cache too.  The row-block
+  // scheme below packs a B slab together, waits, computes, waits, eighteen times for a layer-sized
+  // product, and every core reads the whole slab out of the others' caches.
+  const int total_panels = (N + NR - 1) / NR;
+  if ((size_t)M * KC * sizeof(float) <= (1u << 20) && (size_t)M * K * sizeof(float) <= (8u << 20) &&
+      total_panels >= threads) {
+    const int m_panels = (M + MR - 1) / MR, k_slabs = (K + KC - 1) / KC;
+    // scratch that outlives the call (grow-only, one per calling / worker thread): a fresh megabyte-sized
+    // vector per call is a new mapping whose pages fault in one by one
+    static thread_local std::vector<float> Apack_tl;
+    if (Apack_tl.size() < (size_t)m_panels * MR * K) Apack_tl.resize((size_t)m_panels * MR * K);
+    float* const Apack = Apack_tl.data();   // slab s at m_panels*MR*(s*KC), panel pi at + pi*MR*kc
+    parallel_for(k_slabs * m_panels, threads, [&](int t) {
+      const int sl = t / m_panels, pi = t % m_panels;
+      const int k0 = sl * KC, kc = std::min(KC, K - k0);
+      const int r0 = pi * MR, mr = std::min(MR, M - r0);
+      float* ap = Apack + (size_t)m_panels * MR * k0 + (size_t)pi * MR * kc;
+      if (!ta) {
+        pack_transposed(A + (size_t)r0 * lda + k0, (size_t)lda, mr, kc, ap, MR);
+      } else {
+        for (int k = 0; k < kc; ++k) {
+          const float* src = A + (size_t)(k0 + k) * lda + r0;
+          for (int i = 0; i < mr; ++i) ap[(size_t)k * MR + i] = src[i];
+          for (int i = mr; i < MR; ++i) ap[(size_t)k * MR + i] = 0.f;
+        }
+      }
+    });
+    // panels per task: at most 8 (a 256 KB piece of B), and a task count that is a multiple of the
+    // thread count so that the last round is not one straggler
+    const int rounds = std::max(total_panels >= 4 * threads ? 2 : 1, (total_panels + 8 * threads - 1) / (8 * threads));
+    const int cw = (total_panels + rounds * threads - 1) / (rounds * threads);
+    parallel_for((total_panels + cw - 1) / cw, threads, [&](int t) {
+      const int p_lo = t * cw, p_hi = std::min(total_panels, p_lo + cw);
+      static thread_local std::vector<float> Bq;
+      if (Bq.size() < (size_t)cw * NR * KC) Bq.resize((size_t)cw * NR * KC);
+      for (int k0 = 0; k0 < K; k0 += KC) {
+        const int kc = std::min(KC, K - k0);
+        for (int p = p_lo; p < p_hi; ++p) {
+          float* dst = Bq.data() + (size_t)(p - p_lo) * NR * KC;
+          const int c0 = p * NR, nr = std::min(NR, N - c0);
+          if (tb) {
+            pack_transposed(B + (size_t)c0 * ldb + k0, (size_t)ldb, nr, kc, dst, NR);
+          } else {
+            for (int k = 0; k < kc; ++k) {
+              const float* src = B + (size_t)(k0 + k) * ldb + c0;
+              if (nr == NR) {
+                std::memcpy(dst + (size_t)k * NR, src, NR * sizeof(float));
+              } else {
+                for (int j = 0; j < nr; ++j) dst[(size_t)k * NR + j] = src[j];
+                for (int j = nr; j < NR; ++j) dst[(size_t)k * NR + j] = 0.f;
+              }
+            }
+          }
+        }
+        const float* aslab = Apack + (size_t)m_panels * MR * k0;
+        for (int p = p_lo; p < p_hi; ++p) {
+          const float* bp = Bq.data() + (size_t)(p - p_lo) * NR * KC;
+          const int c0 = p * NR, nr = std::min(NR, N - c0);
+          for (int pi = 0; pi < m_panels; ++pi) {
+            const int r0 = pi * MR, mr = std::min(MR, M - r0);
+            Micro::run(aslab + (size_t)pi * MR * kc, bp, kc, C + (size_t)r0 * ldc + c0, ldc, mr, nr, alpha,
+                       /*accumulate=*/k0 != 0, beta);
+          }
+        }
+      }
+    });
+    return 0;
+  }
   // tasks: MC-row blocks of A (their packed panels stay in the owner's L2 while it sweeps the B slab);
   // small M is cut finer so that every thread gets work
   int mc = MC;
   while (mc > MR && (M + mc - 1) / mc < 2 * threads) mc -= MR;
   const int m_blocks = (M + mc - 1) / mc;
-  std::vector<float> Bp((size_t)((std::min(N, NC) + NR - 1) / NR) * NR * KC);
+  static thread_local std::vector<float> Bp;   // grow-only scratch, see above
+  if (Bp.size() < (size_t)((std::min(N, NC) + NR - 1) / NR) * NR * KC) Bp.resize((size_t)((std::min(N, NC) + NR - 1) / NR) * NR * KC);
+  float* const Bp_data = Bp.data();            // workers use the caller's buffer through this pointer
   // column slabs outside, K slabs inside: a task's part of C (its rows x NC columns) is accumulated
   // over all of K while it is still in cache; with K outside, a wide C (the LM head's) went to
   // memory and back once per K slab
@@ -355,7 +445,7 @@ static int gemm_impl(const float* A, const float* B, float* C, int M, int N, int
         parallel_for((kc + KR - 1) / KR, threads, [&](int t) {
           for (int k = t * KR; k < std::min(kc, (t + 1) * KR); ++k) {
             const float* src = B + (size_t)(k0 + k) * ldb + n0;
-            float* dst = Bp.data() + (size_t)k * NR;
+            float* dst = Bp_data + (size_t)k * NR;
             for (int q = 0; q < full; ++q) std::memcpy(dst + (size_t)q * NR * KC, src + (size_t)q * NR, NR * sizeof(float));
             if (rem) {
               float* d = dst + (size_t)full * NR * KC;
@@ -367,7 +457,7 @@ static int gemm_impl(const float* A, const float* B, float* C, int M, int N, int
       } else {
         parallel_for(n_panels, threads, [&](int p) {   // B stored [N][K]: NR source rows, transposed on the way
           const int c0 = n0 + p * NR, nr = std::min(NR, N - c0);
-          pack_transposed(B + (size_t)c0 * ldb + k0, (size_t)ldb, nr, kc, Bp.data() + (size_t)p * NR * KC, NR);
+          pack_transposed(B + (size_t)c0 * ldb + k0, (size_t)ldb, nr, kc, Bp_data + (size_t)p * NR * KC, NR);
         });
       }
       // every task packs its block of A once and sweeps it over the B slab panel by panel: a B panel
@@ -375,7 +465,8 @@ static int gemm_impl(const float* A, const float* B, float* C, int M, int N, int
       parallel_for(m_blocks, threads, [&](int mb) {
         const int r_lo = mb * mc, rows = std::min(mc, M - r_lo);
         const int panels = (rows + MR - 1) / MR;
-        std::vector<float> Ap((size_t)panels * MR * kc);
+        static thread_local std::vector<float> Ap;
+        if (Ap.size() < (size_t)panels * MR * kc) Ap.resize((size_t)panels * MR * kc);
         for (int pi = 0; pi < panels; ++pi) {
           float* ap = Ap.data() + (size_t)pi * MR * kc;
           const int r0 = r_lo + pi * MR, mr = std::min(MR, M - r0);
@@ -391,7 +482,7 @@ static int gemm_impl(const float* A, const float* B, float* C, int M, int N, int
         }
         for (int p = 0; p < n_panels; ++p) {
           const int c0 = n0 + p * NR, nr = std::min(NR, N - c0);
-          const float* bp = Bp.data() + (size_t)p * NR * KC;
+          const float* bp = Bp_data + (size_t)p * NR * KC;
           for (int pi = 0; pi < panels; ++pi) {
             const int r0 = r_lo + pi * MR, mr = std::min(MR, M - r0);
             Micro::run(Ap.data() + (size_t)pi * MR * kc, bp, kc, C + (size_t)r0 * ldc + c0, ldc, mr, nr, alpha,
@@ -412,8 +503,10 @@ BBH_API int bbh_cpu_gemm(const float* A, const float* B, float* C, int M, int N,
     if (e && std::strcmp(e, "avx2") == 0) return false;
     return (bool)__builtin_cpu_supports("avx512f");
   }();
-  return wide ? gemm_impl<MicroAvx512>(A, B, C, M, N, K, lda, ldb, ldc, ta, tb, alpha, beta, threads)
-              : gemm_impl<MicroAvx2>(A, B, C, M, N, K, lda, ldb, ldc, ta, tb, alpha, beta, threads);
+  const int rc = wide ? gemm_impl<MicroAvx512>(A, B, C, M, N, K, lda, ldb, ldc, ta, tb, alpha, beta, threads)
+                      : gemm_impl<MicroAvx2>(A, B, C, M, N, K, lda, ldb, ldc, ta, tb, alpha, beta, threads);
+  quiesce_pool();
+  return rc;
 }
 
 // y[rows, d] = x / sqrt(mean(x^2) + eps) * w      (row-parallel, AVX2)
